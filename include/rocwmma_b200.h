@@ -1,0 +1,228 @@
+/*
+ * rocwmma_b200 - C ABI of the B200-native GEMM / DLRM / GEMV hot path.
+ *
+ * rocWMMA itself is a header-only device library: its "host entry points" are the kernel
+ * signatures its samples and test harness launch.  Each entry point below replaces one of
+ * those launches; the comment above it cites the reference kernel / host driver it stands in
+ * for (paths relative to the rocWMMA project root).
+ *
+ * Conventions
+ *   - Every function returns a b200wmma_status (0 = success) and never exits the process.
+ *   - Unless the name ends in `_host`, all data pointers are DEVICE pointers on the CUDA
+ *     device that is current in the calling thread; the caller owns every buffer.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = default stream).  Device-pointer
+ *     entry points only enqueue work; they do not synchronise.
+ *   - `_host` entry points take HOST pointers, copy through device buffers held by a
+ *     b200wmma_ctx, run the same kernel and copy the result back, synchronously.
+ *   - Leading dimensions are in elements.  Layout flags: 0 = row major, 1 = column major
+ *     (the order of rocwmma::layout_t, library/include/rocwmma/rocwmma.hpp:104-108).
+ *   - Kernels that wait on hardware barriers do so with a bounded spin; if a wait gives up
+ *     the kernel records B200WMMA_ERR_DEVICE_TIMEOUT in a per-device status word that
+ *     b200wmma_device_status() returns.
+ */
+#ifndef ROCWMMA_B200_H
+#define ROCWMMA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum b200wmma_status
+{
+    B200WMMA_OK                 = 0,
+    B200WMMA_ERR_INVALID_ARG    = 1, /* null pointer, zero/overflowing size, bad enum        */
+    B200WMMA_ERR_UNSUPPORTED    = 2, /* legal request this build has no kernel for           */
+    B200WMMA_ERR_ALIGNMENT      = 3, /* pointer / leading dimension breaks a 16-byte rule    */
+    B200WMMA_ERR_CUDA           = 4, /* a CUDA runtime / driver call failed                  */
+    B200WMMA_ERR_DEVICE_TIMEOUT = 5, /* a bounded device-side wait gave up                   */
+    B200WMMA_ERR_NO_DEVICE      = 6  /* no sm_100 device is current                          */
+} b200wmma_status;
+
+enum { B200WMMA_ROW_MAJOR = 0, B200WMMA_COL_MAJOR = 1 };
+enum { B200WMMA_OUT_F16 = 0, B200WMMA_OUT_F32 = 1 };
+
+/* Human-readable text for the last error raised on the calling thread. */
+const char* b200wmma_last_error_string(void);
+/* Library version as major*10000 + minor*100 + patch. */
+int b200wmma_version(void);
+
+/* Synchronises `stream`, then reads and clears the current device's status word.
+ * *out_status is B200WMMA_OK or B200WMMA_ERR_DEVICE_TIMEOUT; *out_detail (may be NULL)
+ * identifies the wait that gave up (role << 24 | block index). */
+int b200wmma_device_status(void* stream, int* out_status, unsigned* out_detail);
+
+/* ------------------------------------------------------------------------------------------
+ * GEMM: D = alpha * (A x B) + beta * C
+ *
+ * Replaces the launch of gemm_rocwmma_d (samples/perf_hgemm.cpp:515-711, launched at
+ * :820-842) and of the test harness kernel type KernelFunc
+ *   void(*)(m,n,k, a,b,c,d, lda,ldb,ldc,ldd, alpha,beta)
+ * (test/gemm/gemm_kernel_base.hpp:102-114; gemm_PGR1_LB2_MP0_MB_CP,
+ *  test/gemm/gemm_PGR1_LB2_MP0_MB_CP/device/kernel_device_func.hpp:70-283).
+ * Same argument meaning; the compile-time layout / type parameters of the reference become
+ * the trailing flags.  A is m x k, B is k x n, C and D are m x n.  `c` may be NULL when
+ * beta == 0 (it is then not read); `c == d` is allowed.
+ *
+ * f16: fp16 inputs, fp32 accumulate, D/C fp16 or fp32 (out_type).  tcgen05 tensor cores.
+ * i8 : int8 inputs, int32 accumulate / scalars / outputs (wrap-around arithmetic).
+ * f64: fp64 everywhere (DMMA).
+ * Supported layouts: A row major and B column major (both K-contiguous), C/D row major.
+ * Pointers and leading dimensions must keep every row start 16-byte aligned.
+ * ------------------------------------------------------------------------------------------ */
+int b200wmma_gemm_f16(uint32_t m, uint32_t n, uint32_t k,
+                      const void* a, const void* b, const void* c, void* d,
+                      uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                      float alpha, float beta,
+                      int layout_a, int layout_b, int layout_cd, int out_type, void* stream);
+
+int b200wmma_gemm_i8(uint32_t m, uint32_t n, uint32_t k,
+                     const int8_t* a, const int8_t* b, const int32_t* c, int32_t* d,
+                     uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                     int32_t alpha, int32_t beta,
+                     int layout_a, int layout_b, int layout_cd, void* stream);
+
+/* Replaces gemm_rocwmma_d of samples/perf_dgemm.cpp:461 (same 13-argument signature). */
+int b200wmma_gemm_f64(uint32_t m, uint32_t n, uint32_t k,
+                      const double* a, const double* b, const double* c, double* d,
+                      uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                      double alpha, double beta,
+                      int layout_a, int layout_b, int layout_cd, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Structured-sparse and packed-int4 integer GEMM.  rocWMMA v1.6.0 has no counterpart of
+ * these two (no sparse or int4 code in the project); the semantics are those of
+ * b200wmma_gemm_i8 applied to the densified / sign-extended operands.
+ *
+ * sp24: A is 2:4 sparse along K.  a_vals is m x k/2 int8, row major (lda_vals elements per
+ *   row): for each aligned group of 4 K-positions the two kept values in ascending position
+ *   order.  a_meta is m x k/8 bytes, row major (ld_meta bytes per row): one nibble per group,
+ *   idx0 | (idx1 << 2) with idx0 < idx1 the kept positions, two groups per byte, low nibble =
+ *   even group.  B column major int8, C/D row major int32.
+ * i4: A (row major, m x k) and B (column major, k x n) hold int4 values in [-8,7], two per
+ *   byte along K, low nibble = even k.  lda / ldb are in BYTES per row / column.
+ * `workspace` is caller-owned device scratch of at least b200wmma_gemm_*_workspace_bytes().
+ * ------------------------------------------------------------------------------------------ */
+size_t b200wmma_gemm_i8_sp24_workspace_bytes(uint32_t m, uint32_t n, uint32_t k);
+int b200wmma_gemm_i8_sp24(uint32_t m, uint32_t n, uint32_t k,
+                          const int8_t* a_vals, const uint8_t* a_meta,
+                          const int8_t* b, const int32_t* c, int32_t* d,
+                          uint32_t lda_vals, uint32_t ld_meta, uint32_t ldb,
+                          uint32_t ldc, uint32_t ldd,
+                          int32_t alpha, int32_t beta,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
+size_t b200wmma_gemm_i4_workspace_bytes(uint32_t m, uint32_t n, uint32_t k);
+int b200wmma_gemm_i4(uint32_t m, uint32_t n, uint32_t k,
+                     const uint8_t* a_packed, const uint8_t* b_packed,
+                     const int32_t* c, int32_t* d,
+                     uint32_t lda_bytes, uint32_t ldb_bytes, uint32_t ldc, uint32_t ldd,
+                     int32_t alpha, int32_t beta,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Naive fragment-API GEMM: one 16x16 block per warp, written against this repository's
+ * <rocwmma/rocwmma.hpp>.  Replaces the launch of hgemm_rocwmma_d
+ * (samples/simple_hgemm.cpp:81-139, launched at :192-230): A row major, B column major,
+ * C/D row major; out_type selects fp16 (the sample's own) or fp32 C/D.
+ * m, n, k must be multiples of 16.
+ * ------------------------------------------------------------------------------------------ */
+int b200wmma_simple_hgemm(uint32_t m, uint32_t n, uint32_t k,
+                          const void* a, const void* b, const void* c, void* d,
+                          uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                          float alpha, float beta, int out_type, void* stream);
+
+/* perf_hgemm's kernel source pattern (cooperative global reads, shared-memory double buffer,
+ * fragment transforms; samples/perf_hgemm.cpp:515-711) compiled against this repository's
+ * fragment headers: 128x128 macro tile, A column major, B row major, C/D row major fp16 -
+ * the layouts the sample ships with (:264-271).  m, n multiples of 128, k of 16. */
+int b200wmma_perf_hgemm_fragment(uint32_t m, uint32_t n, uint32_t k,
+                                 const void* a, const void* b, const void* c, void* d,
+                                 uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                                 float alpha, float beta, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * DLRM dot interaction.
+ *
+ * Forward replaces dlrmDotFwd (samples/simple_dlrm.cpp:184-284, launched :503-530;
+ * test/dlrm/device/dlrm_dot_fwd.hpp:37-136):
+ *   output[b] = [ input[b,0,0:k] , { Z[i][j] : 0 <= j < i < m, row-major order } ],
+ *   Z = X X^T with fp32 accumulation, stored as fp16.
+ * input  : batch x m_stride x k fp16 (row i of sample b at (b*m_stride + i)*k; rows m..m_stride-1
+ *          are padding and are not read).
+ * output : batch x out_stride fp16, out_stride >= k + m(m-1)/2; columns past the packed
+ *          triangle are written as zero.
+ * The reference's fp32 scratch `acc` is not needed and has no parameter.
+ * Requires m <= 32, k a multiple of 16 with k <= 256, k % 8 == 0 and out_stride % 8 == 0.
+ *
+ * Backward replaces trilReconstruct + dlrmDotBwd (samples/simple_dlrm.cpp:290-331, :349-441,
+ * launched :535-584; test/dlrm/device/dlrm_dot_bwd.hpp:35-172):
+ *   bottom_mlp_grad[b,:] = upstream[b,0:k]            (skipped when the pointer is NULL)
+ *   T = symmetric m x m matrix rebuilt from upstream[b,k:], zero diagonal
+ *   grad[b] = T x X[b]   (fp32 accumulate, stored fp16), rows 0..m-1 only.
+ * With fuse_mlp_into_row0 != 0, upstream[b,0:k] is added to grad[b,0,:] in fp32 before the
+ * fp16 conversion (the bottom-MLP row receives its pass-through gradient in the same pass).
+ * ------------------------------------------------------------------------------------------ */
+int b200wmma_dlrm_fwd(const void* input, void* output,
+                      uint32_t m, uint32_t m_stride, uint32_t k, uint32_t batch,
+                      uint32_t out_stride, void* stream);
+
+int b200wmma_dlrm_bwd(const void* input, const void* upstream, void* grad, void* bottom_mlp_grad,
+                      uint32_t m, uint32_t m_stride, uint32_t k, uint32_t batch,
+                      uint32_t upstream_stride, int fuse_mlp_into_row0, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * GEMV: y = alpha * A x + beta * y  (in place on y), A is m x n.
+ * Replaces sgemv_rocwmma_d / dgemv_rocwmma_d (samples/simple_sgemv.cpp:103-155 launched
+ * :198-227, samples/simple_dgemv.cpp:103) as a true matrix-vector product: x has n elements,
+ * y has m elements, nothing outside them is touched.  layout_a row major (lda >= n) or
+ * column major (lda >= m, the sample's own storage).
+ * ------------------------------------------------------------------------------------------ */
+int b200wmma_gemv_f32(uint32_t m, uint32_t n, const float* a, uint32_t lda, int layout_a,
+                      const float* x, float* y, float alpha, float beta, void* stream);
+int b200wmma_gemv_f64(uint32_t m, uint32_t n, const double* a, uint32_t lda, int layout_a,
+                      const double* x, double* y, double alpha, double beta, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Host-buffer drivers.  These stand in for the reference samples' host functions
+ * gemm_test (samples/perf_hgemm.cpp:713-941), dlrm_test (samples/simple_dlrm.cpp:443-710)
+ * and sgemv_test (samples/simple_sgemv.cpp:157-273): allocate-or-reuse device buffers,
+ * copy the inputs host -> device, launch, copy the result device -> host, synchronise.
+ * A b200wmma_ctx caches the device buffers (grown on demand) and one stream, so repeated
+ * calls do not allocate.  All pointers in *_host calls are host pointers; pinned host
+ * memory gives the fastest copies but pageable memory works.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct b200wmma_ctx b200wmma_ctx;
+int b200wmma_ctx_create(b200wmma_ctx** out_ctx);
+int b200wmma_ctx_destroy(b200wmma_ctx* ctx);
+
+int b200wmma_gemm_f16_host(b200wmma_ctx* ctx, uint32_t m, uint32_t n, uint32_t k,
+                           const void* a, const void* b, const void* c, void* d,
+                           uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                           float alpha, float beta,
+                           int layout_a, int layout_b, int layout_cd, int out_type);
+int b200wmma_gemm_i8_host(b200wmma_ctx* ctx, uint32_t m, uint32_t n, uint32_t k,
+                          const int8_t* a, const int8_t* b, const int32_t* c, int32_t* d,
+                          uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                          int32_t alpha, int32_t beta,
+                          int layout_a, int layout_b, int layout_cd);
+int b200wmma_dlrm_fwd_host(b200wmma_ctx* ctx, const void* input, void* output,
+                           uint32_t m, uint32_t m_stride, uint32_t k, uint32_t batch,
+                           uint32_t out_stride);
+int b200wmma_dlrm_bwd_host(b200wmma_ctx* ctx, const void* input, const void* upstream,
+                           void* grad, void* bottom_mlp_grad,
+                           uint32_t m, uint32_t m_stride, uint32_t k, uint32_t batch,
+                           uint32_t upstream_stride, int fuse_mlp_into_row0);
+int b200wmma_gemv_f32_host(b200wmma_ctx* ctx, uint32_t m, uint32_t n, const float* a,
+                           uint32_t lda, int layout_a, const float* x, float* y,
+                           float alpha, float beta);
+int b200wmma_gemv_f64_host(b200wmma_ctx* ctx, uint32_t m, uint32_t n, const double* a,
+                           uint32_t lda, int layout_a, const double* x, double* y,
+                           double alpha, double beta);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ROCWMMA_B200_H */

@@ -1,0 +1,184 @@
+"""Python host mirror of the rocWMMA sample / test-harness entry points for the hot path.
+
+Every function here forwards to the C ABI (include/rocwmma_b200.h) with device pointers taken
+from torch CUDA tensors and the current torch stream.  torch is plumbing only (memory, streams);
+all arithmetic happens in the hand-written kernels.  Argument names and meaning follow the
+reference kernels: gemm_rocwmma_d (samples/perf_hgemm.cpp:515-528), dlrmDotFwd / dlrmDotBwd
+(samples/simple_dlrm.cpp:184-192, :349-360), sgemv_rocwmma_d (samples/simple_sgemv.cpp:103-116).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ._lib import B200WmmaError, check, lib
+
+ROW_MAJOR, COL_MAJOR = 0, 1
+OUT_F16, OUT_F32 = 0, 1
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(t, dtype, name):
+    if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == dtype):
+        raise TypeError(f"{name} must be a CUDA tensor of dtype {dtype}")
+
+
+def device_status():
+    """Synchronise the current stream and return (status, detail) of the device status word."""
+    st, detail = C.c_int(0), C.c_uint(0)
+    check(lib().b200wmma_device_status(_stream(), C.byref(st), C.byref(detail)))
+    return st.value, detail.value
+
+
+def gemm_f16(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
+             layout_a=ROW_MAJOR, layout_b=COL_MAJOR, layout_cd=ROW_MAJOR):
+    """D = alpha * A x B + beta * C; fp16 inputs, fp32 accumulate, D/C fp16 or fp32 (by d.dtype)."""
+    _need(a, torch.float16, "a"); _need(b, torch.float16, "b")
+    out_type = OUT_F16 if d.dtype == torch.float16 else OUT_F32
+    _need(d, torch.float16 if out_type == OUT_F16 else torch.float32, "d")
+    if c is not None:
+        _need(c, d.dtype, "c")
+    check(lib().b200wmma_gemm_f16(m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc, ldd,
+                                  alpha, beta, layout_a, layout_b, layout_cd, out_type, _stream()))
+
+
+def gemm_i8(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
+            layout_a=ROW_MAJOR, layout_b=COL_MAJOR, layout_cd=ROW_MAJOR):
+    _need(a, torch.int8, "a"); _need(b, torch.int8, "b"); _need(d, torch.int32, "d")
+    if c is not None:
+        _need(c, torch.int32, "c")
+    check(lib().b200wmma_gemm_i8(m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc, ldd,
+                                 alpha, beta, layout_a, layout_b, layout_cd, _stream()))
+
+
+def gemm_f64(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
+             layout_a=ROW_MAJOR, layout_b=COL_MAJOR, layout_cd=ROW_MAJOR):
+    for t, nm in ((a, "a"), (b, "b"), (d, "d")):
+        _need(t, torch.float64, nm)
+    if c is not None:
+        _need(c, torch.float64, "c")
+    check(lib().b200wmma_gemm_f64(m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc, ldd,
+                                  alpha, beta, layout_a, layout_b, layout_cd, _stream()))
+
+
+def gemm_i8_sp24_workspace_bytes(m, n, k):
+    return lib().b200wmma_gemm_i8_sp24_workspace_bytes(m, n, k)
+
+
+def gemm_i8_sp24(m, n, k, a_vals, a_meta, b, c, d, lda_vals, ld_meta, ldb, ldc, ldd, alpha, beta, workspace):
+    _need(a_vals, torch.int8, "a_vals"); _need(a_meta, torch.uint8, "a_meta")
+    _need(b, torch.int8, "b"); _need(d, torch.int32, "d"); _need(workspace, torch.uint8, "workspace")
+    check(lib().b200wmma_gemm_i8_sp24(m, n, k, _ptr(a_vals), _ptr(a_meta), _ptr(b), _ptr(c), _ptr(d),
+                                      lda_vals, ld_meta, ldb, ldc, ldd, alpha, beta,
+                                      _ptr(workspace), workspace.numel(), _stream()))
+
+
+def gemm_i4_workspace_bytes(m, n, k):
+    return lib().b200wmma_gemm_i4_workspace_bytes(m, n, k)
+
+
+def gemm_i4(m, n, k, a_packed, b_packed, c, d, lda_bytes, ldb_bytes, ldc, ldd, alpha, beta, workspace):
+    _need(a_packed, torch.uint8, "a_packed"); _need(b_packed, torch.uint8, "b_packed")
+    _need(d, torch.int32, "d"); _need(workspace, torch.uint8, "workspace")
+    check(lib().b200wmma_gemm_i4(m, n, k, _ptr(a_packed), _ptr(b_packed), _ptr(c), _ptr(d),
+                                 lda_bytes, ldb_bytes, ldc, ldd, alpha, beta,
+                                 _ptr(workspace), workspace.numel(), _stream()))
+
+
+def simple_hgemm(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta):
+    """hgemm_rocwmma_d (samples/simple_hgemm.cpp:81-139) on this repo's fragment headers."""
+    _need(a, torch.float16, "a"); _need(b, torch.float16, "b")
+    out_type = OUT_F16 if d.dtype == torch.float16 else OUT_F32
+    _need(c, d.dtype, "c")
+    check(lib().b200wmma_simple_hgemm(m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc, ldd,
+                                      alpha, beta, out_type, _stream()))
+
+
+def perf_hgemm_fragment(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta):
+    for t, nm in ((a, "a"), (b, "b"), (c, "c"), (d, "d")):
+        _need(t, torch.float16, nm)
+    check(lib().b200wmma_perf_hgemm_fragment(m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d),
+                                             lda, ldb, ldc, ldd, alpha, beta, _stream()))
+
+
+def dlrm_dot_fwd(input, output, m, m_stride, k, batch, out_stride):
+    _need(input, torch.float16, "input"); _need(output, torch.float16, "output")
+    check(lib().b200wmma_dlrm_fwd(_ptr(input), _ptr(output), m, m_stride, k, batch, out_stride, _stream()))
+
+
+def dlrm_dot_bwd(input, upstream, grad, bottom_mlp_grad, m, m_stride, k, batch, upstream_stride,
+                 fuse_mlp_into_row0=False):
+    _need(input, torch.float16, "input"); _need(upstream, torch.float16, "upstream")
+    _need(grad, torch.float16, "grad")
+    if bottom_mlp_grad is not None:
+        _need(bottom_mlp_grad, torch.float16, "bottom_mlp_grad")
+    check(lib().b200wmma_dlrm_bwd(_ptr(input), _ptr(upstream), _ptr(grad), _ptr(bottom_mlp_grad),
+                                  m, m_stride, k, batch, upstream_stride, int(fuse_mlp_into_row0), _stream()))
+
+
+def gemv(m, n, a, lda, x, y, alpha, beta, layout_a=ROW_MAJOR):
+    """y = alpha * A x + beta * y in place; fp32 or fp64 by a.dtype."""
+    if a.dtype == torch.float32:
+        fn = lib().b200wmma_gemv_f32
+    elif a.dtype == torch.float64:
+        fn = lib().b200wmma_gemv_f64
+    else:
+        raise TypeError("gemv: a must be float32 or float64")
+    _need(a, a.dtype, "a"); _need(x, a.dtype, "x"); _need(y, a.dtype, "y")
+    check(fn(m, n, _ptr(a), lda, layout_a, _ptr(x), _ptr(y), alpha, beta, _stream()))
+
+
+class HostContext:
+    """b200wmma_ctx: cached device buffers + stream for the host-buffer drivers (`*_host`)."""
+
+    def __init__(self):
+        self._h = C.c_void_p()
+        check(lib().b200wmma_ctx_create(C.byref(self._h)))
+
+    def close(self):
+        if self._h:
+            lib().b200wmma_ctx_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @staticmethod
+    def _hp(t):
+        """Host pointer of a CPU torch tensor or numpy array (None passes through)."""
+        if t is None:
+            return None
+        if isinstance(t, torch.Tensor):
+            assert not t.is_cuda
+            return C.c_void_p(t.data_ptr())
+        return C.c_void_p(t.ctypes.data)
+
+    def gemm_f16(self, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, out_type):
+        check(lib().b200wmma_gemm_f16_host(self._h, m, n, k, self._hp(a), self._hp(b), self._hp(c), self._hp(d),
+                                           lda, ldb, ldc, ldd, alpha, beta, ROW_MAJOR, COL_MAJOR, ROW_MAJOR, out_type))
+
+    def gemm_i8(self, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta):
+        check(lib().b200wmma_gemm_i8_host(self._h, m, n, k, self._hp(a), self._hp(b), self._hp(c), self._hp(d),
+                                          lda, ldb, ldc, ldd, alpha, beta, ROW_MAJOR, COL_MAJOR, ROW_MAJOR))
+
+    def dlrm_fwd(self, input, output, m, m_stride, k, batch, out_stride):
+        check(lib().b200wmma_dlrm_fwd_host(self._h, self._hp(input), self._hp(output), m, m_stride, k, batch, out_stride))
+
+    def dlrm_bwd(self, input, upstream, grad, bottom_mlp_grad, m, m_stride, k, batch, upstream_stride, fuse):
+        check(lib().b200wmma_dlrm_bwd_host(self._h, self._hp(input), self._hp(upstream), self._hp(grad),
+                                           self._hp(bottom_mlp_grad), m, m_stride, k, batch, upstream_stride, int(fuse)))
+
+    def gemv(self, m, n, a, lda, x, y, alpha, beta, layout_a=ROW_MAJOR, double=False):
+        fn = lib().b200wmma_gemv_f64_host if double else lib().b200wmma_gemv_f32_host
+        check(fn(self._h, m, n, self._hp(a), lda, layout_a, self._hp(x), self._hp(y), alpha, beta))

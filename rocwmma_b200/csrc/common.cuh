@@ -1,0 +1,67 @@
+// Shared host/device plumbing for the rocwmma_b200 kernels: status codes, the thread-local
+// error string, argument checks, the per-device status word that bounded device-side waits
+// report into, and small PTX wrappers (mbarrier, TMA, tcgen05) used by the tensor-core GEMM.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/rocwmma_b200.h"
+
+namespace b200wmma
+{
+    // ---- host-side error reporting -------------------------------------------------------
+    int  set_error(int code, const char* fmt, ...);
+    void clear_error();
+
+#define B200_CHECK_CUDA(expr)                                                                 \
+    do                                                                                        \
+    {                                                                                         \
+        cudaError_t _e = (expr);                                                              \
+        if(_e != cudaSuccess)                                                                 \
+            return ::b200wmma::set_error(B200WMMA_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,   \
+                                         cudaGetErrorString(_e), __FILE__, __LINE__);         \
+    } while(0)
+
+#define B200_REQUIRE(cond, code, ...)                                                         \
+    do                                                                                        \
+    {                                                                                         \
+        if(!(cond))                                                                           \
+            return ::b200wmma::set_error(code, __VA_ARGS__);                                  \
+    } while(0)
+
+    // The current device must be a Blackwell sm_100 part: the kernels are built for sm_100a
+    // only and there is no fallback path.
+    int require_sm100();
+
+    // Device-resident status word {code, detail}; one copy per device (module global).
+    // Kernels with bounded waits get its device address from here.
+    int status_word_ptr(unsigned** out_dev_ptr);
+
+    static inline bool aligned16(const void* p)
+    {
+        return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+    }
+    static inline cudaStream_t as_stream(void* s)
+    {
+        return reinterpret_cast<cudaStream_t>(s);
+    }
+    static inline uint32_t ceil_div(uint32_t a, uint32_t b)
+    {
+        return (a + b - 1) / b;
+    }
+
+    // ---- kernel launchers implemented in the .cu files --------------------------------
+    int launch_gemm_tc05_f16(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b,
+                             const void* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
+                             uint32_t ldd, float alpha, float beta, int out_type,
+                             cudaStream_t stream);
+    int launch_gemm_tc05_i8(uint32_t m, uint32_t n, uint32_t k, const int8_t* a,
+                            const int8_t* b, const int32_t* c, int32_t* d, uint32_t lda,
+                            uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha,
+                            int32_t beta, cudaStream_t stream);
+} // namespace b200wmma

@@ -1,0 +1,211 @@
+// fp64 GEMM D = alpha * (A x B) + beta * C on the double-precision tensor-core path (DMMA).
+//
+// Stands in for gemm_rocwmma_d of samples/perf_dgemm.cpp:461 (the perf_hgemm pipeline with
+// 16x16x16 fp64 blocks).  tcgen05 has no fp64 kind, so the math is warp-level
+// mma.sync.m16n8k4.f64 fed from a 3-stage cp.async shared-memory ring:
+//   CTA tile 128x128, K slab 16, 8 warps as 2 (M) x 4 (N), warp tile 64x32.
+// A row major (K contiguous), B column major (K contiguous), C / D row major.
+#include "common.cuh"
+
+namespace b200wmma
+{
+    namespace f64
+    {
+        constexpr int BM = 128, BN = 128, BK = 16, STAGES = 3, THREADS = 256;
+        constexpr int PITCH       = 20; // doubles per shared row: 16 + 4 pad -> conflict-free 8-byte reads
+        constexpr int TILE_ELEMS  = BM * PITCH;
+        constexpr int STAGE_ELEMS = 2 * TILE_ELEMS;
+        constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * STAGE_ELEMS * sizeof(double);
+
+        __device__ __forceinline__ void cp_async16_zfill(double* dst, const double* src, bool valid)
+        {
+            const uint32_t d  = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+            const int      sz = valid ? 16 : 0; // src-size 0 -> the 16 bytes are zero-filled
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(sz)
+                         : "memory");
+        }
+        __device__ __forceinline__ void cp_async_commit()
+        {
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        template <int N>
+        __device__ __forceinline__ void cp_async_wait()
+        {
+            asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+        }
+        // D(16x8) += A(16x4, row) x B(4x8, col), all fp64
+        __device__ __forceinline__ void dmma_1684(double (&c)[4], double a0, double a1, double b0)
+        {
+            asm volatile("mma.sync.aligned.m16n8k4.row.col.f64.f64.f64.f64 "
+                         "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                         : "+d"(c[0]), "+d"(c[1]), "+d"(c[2]), "+d"(c[3])
+                         : "d"(a0), "d"(a1), "d"(b0));
+        }
+
+        // Loads one 128 x 16 K-major slab (rows `row0..row0+127` of a matrix with `rows` rows and
+        // pitch ld, K columns k0..k0+15) into shared memory; out-of-range chunks become zeros.
+        __device__ __forceinline__ void load_slab(double* dst, const double* src, size_t ld, uint32_t rows,
+                                                  uint32_t kdim, uint32_t row0, uint32_t k0)
+        {
+            // 128 rows x 8 chunks of 2 doubles = 1024 chunks / 256 threads = 4 per thread
+#pragma unroll
+            for(int i = 0; i < 4; ++i)
+            {
+                const uint32_t idx = threadIdx.x + i * THREADS;
+                const uint32_t r = idx >> 3, ch = idx & 7;
+                const uint32_t gr = row0 + r, gk = k0 + ch * 2;
+                const bool     ok = gr < rows && gk < kdim; // kdim is even: a chunk is all in or out
+                const double*  s  = ok ? src + static_cast<size_t>(gr) * ld + gk : src;
+                cp_async16_zfill(dst + r * PITCH + ch * 2, s, ok);
+            }
+        }
+
+        __global__ void __launch_bounds__(THREADS, 1)
+            gemm_f64_kernel(uint32_t m, uint32_t n, uint32_t k, const double* __restrict__ a,
+                            const double* __restrict__ b, const double* __restrict__ c,
+                            double* __restrict__ d, size_t lda, size_t ldb, size_t ldc, size_t ldd,
+                            double alpha, double beta, int vec_ok)
+        {
+            extern __shared__ __align__(16) uint8_t smem_raw[];
+            double*        smem = reinterpret_cast<double*>(smem_raw);
+            const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+            const uint32_t g = lane >> 2, t = lane & 3;
+            const uint32_t wm = warp >> 2, wn = warp & 3; // 2 x 4 warps
+            const uint32_t row0 = blockIdx.y * BM, col0 = blockIdx.x * BN;
+            const uint32_t num_kb = (k + BK - 1) / BK;
+
+            double acc[4][4][4]; // [m16 tile][n8 tile][c0..c3]
+#pragma unroll
+            for(int i = 0; i < 4; ++i)
+#pragma unroll
+                for(int j = 0; j < 4; ++j)
+#pragma unroll
+                    for(int e = 0; e < 4; ++e)
+                        acc[i][j][e] = 0.0;
+
+            // prologue: STAGES-1 slabs in flight
+#pragma unroll
+            for(int s = 0; s < STAGES - 1; ++s)
+            {
+                if(static_cast<uint32_t>(s) < num_kb)
+                {
+                    load_slab(smem + s * STAGE_ELEMS, a, lda, m, k, row0, s * BK);
+                    load_slab(smem + s * STAGE_ELEMS + TILE_ELEMS, b, ldb, n, k, col0, s * BK);
+                }
+                cp_async_commit();
+            }
+
+            for(uint32_t kb = 0; kb < num_kb; ++kb)
+            {
+                cp_async_wait<STAGES - 2>();
+                __syncthreads(); // slab kb visible to all; slab kb-1's buffer is free again
+                {
+                    const uint32_t nxt = kb + STAGES - 1;
+                    if(nxt < num_kb)
+                    {
+                        double* st = smem + (nxt % STAGES) * STAGE_ELEMS;
+                        load_slab(st, a, lda, m, k, row0, nxt * BK);
+                        load_slab(st + TILE_ELEMS, b, ldb, n, k, col0, nxt * BK);
+                    }
+                    cp_async_commit();
+                }
+                const double* as = smem + (kb % STAGES) * STAGE_ELEMS + (wm * 64) * PITCH;
+                const double* bs = smem + (kb % STAGES) * STAGE_ELEMS + TILE_ELEMS + (wn * 32) * PITCH;
+#pragma unroll
+                for(int ks = 0; ks < BK; ks += 4)
+                {
+                    double af[4][2], bf[4];
+#pragma unroll
+                    for(int i = 0; i < 4; ++i)
+                    {
+                        af[i][0] = as[(i * 16 + g) * PITCH + ks + t];
+                        af[i][1] = as[(i * 16 + g + 8) * PITCH + ks + t];
+                    }
+#pragma unroll
+                    for(int j = 0; j < 4; ++j)
+                        bf[j] = bs[(j * 8 + g) * PITCH + ks + t];
+#pragma unroll
+                    for(int i = 0; i < 4; ++i)
+#pragma unroll
+                        for(int j = 0; j < 4; ++j)
+                            dmma_1684(acc[i][j], af[i][0], af[i][1], bf[j]);
+                }
+            }
+            cp_async_wait<0>();
+
+            const bool read_c = (beta != 0.0) && c != nullptr;
+#pragma unroll
+            for(int i = 0; i < 4; ++i)
+#pragma unroll
+                for(int h = 0; h < 2; ++h)
+                {
+                    const uint32_t row = row0 + wm * 64 + i * 16 + g + 8 * h;
+                    if(row >= m)
+                        continue;
+#pragma unroll
+                    for(int j = 0; j < 4; ++j)
+                    {
+                        const uint32_t col = col0 + wn * 32 + j * 8 + 2 * t;
+                        if(col >= n)
+                            continue;
+                        const double v0 = acc[i][j][2 * h], v1 = acc[i][j][2 * h + 1];
+                        double*       dp = d + static_cast<size_t>(row) * ldd + col;
+                        const double* cp = c + static_cast<size_t>(row) * ldc + col;
+                        if(vec_ok && col + 1 < n)
+                        {
+                            double2 cv = make_double2(0.0, 0.0);
+                            if(read_c)
+                                cv = *reinterpret_cast<const double2*>(cp);
+                            *reinterpret_cast<double2*>(dp)
+                                = make_double2(alpha * v0 + beta * cv.x, alpha * v1 + beta * cv.y);
+                        }
+                        else
+                        {
+                            dp[0] = alpha * v0 + beta * (read_c ? cp[0] : 0.0);
+                            if(col + 1 < n)
+                                dp[1] = alpha * v1 + beta * (read_c ? cp[1] : 0.0);
+                        }
+                    }
+                }
+        }
+    } // namespace f64
+} // namespace b200wmma
+
+extern "C" int b200wmma_gemm_f64(uint32_t m, uint32_t n, uint32_t k, const double* a, const double* b,
+                                 const double* c, double* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
+                                 uint32_t ldd, double alpha, double beta, int layout_a, int layout_b,
+                                 int layout_cd, void* stream)
+{
+    using namespace b200wmma;
+    clear_error();
+    B200_REQUIRE((layout_a == 0 || layout_a == 1) && (layout_b == 0 || layout_b == 1)
+                     && (layout_cd == 0 || layout_cd == 1),
+                 B200WMMA_ERR_INVALID_ARG, "gemm_f64: layout flags must be 0 (row) or 1 (col)");
+    B200_REQUIRE(layout_a == B200WMMA_ROW_MAJOR && layout_b == B200WMMA_COL_MAJOR
+                     && layout_cd == B200WMMA_ROW_MAJOR,
+                 B200WMMA_ERR_UNSUPPORTED,
+                 "gemm_f64: only A row-major, B column-major, C/D row-major is implemented");
+    B200_REQUIRE(m && n && k, B200WMMA_ERR_INVALID_ARG, "gemm_f64: m, n, k must be non-zero");
+    B200_REQUIRE(a && b && d, B200WMMA_ERR_INVALID_ARG, "gemm_f64: a, b, d must be non-null");
+    B200_REQUIRE(c || beta == 0.0, B200WMMA_ERR_INVALID_ARG, "gemm_f64: c may be null only when beta == 0");
+    B200_REQUIRE(lda >= k && ldb >= k && ldd >= n && (!c || ldc >= n), B200WMMA_ERR_INVALID_ARG,
+                 "gemm_f64: leading dimension smaller than the row/column it strides");
+    B200_REQUIRE(k % 2 == 0 && lda % 2 == 0 && ldb % 2 == 0 && aligned16(a) && aligned16(b),
+                 B200WMMA_ERR_ALIGNMENT,
+                 "gemm_f64: k, lda, ldb must be even and A, B 16-byte aligned (16-byte async copies)");
+    if(int e = require_sm100())
+        return e;
+    static bool attr_ok = false;
+    if(!attr_ok)
+    {
+        B200_CHECK_CUDA(cudaFuncSetAttribute(f64::gemm_f64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(f64::SMEM_BYTES)));
+        attr_ok = true;
+    }
+    const int vec_ok = aligned16(d) && ldd % 2 == 0 && (!c || (aligned16(c) && ldc % 2 == 0));
+    dim3      grid(ceil_div(n, f64::BN), ceil_div(m, f64::BM));
+    f64::gemm_f64_kernel<<<grid, f64::THREADS, f64::SMEM_BYTES, as_stream(stream)>>>(
+        m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, vec_ok);
+    B200_CHECK_CUDA(cudaGetLastError());
+    return B200WMMA_OK;
+}

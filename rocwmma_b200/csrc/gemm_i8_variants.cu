@@ -1,0 +1,171 @@
+// Integer GEMM on compressed operands: 2:4 structured-sparse int8 A, and packed int4 A / B.
+//
+// rocWMMA v1.6.0 has no sparse or int4 path; the semantics are those of the dense int8 GEMM
+// (gemm_rocwmma_d pattern, samples/perf_hgemm.cpp:515-711 with int8 inputs / int32 compute as
+// in test/gemm/gemm_common_test_params.hpp:51-147) applied to the densified / sign-extended
+// operands, bit-exact in int32.
+//
+// Both variants expand the compressed operand(s) to K-major int8 in a caller-provided device
+// workspace with one streaming pass (16-byte loads and stores), then run the tcgen05 int8
+// GEMM on the expanded operands.
+#include "common.cuh"
+
+namespace b200wmma
+{
+    namespace i8var
+    {
+        constexpr int THREADS = 256;
+
+        // One thread expands 8 groups of a row: 16 value bytes + 4 metadata bytes -> 32 dense bytes.
+        // vals row pitch ldv (bytes), meta row pitch ldm (bytes), dense row pitch k (bytes).
+        __global__ void __launch_bounds__(THREADS)
+            expand_sp24_kernel(const int8_t* __restrict__ vals, const uint8_t* __restrict__ meta,
+                               int8_t* __restrict__ dense, uint32_t m, uint32_t k, size_t ldv,
+                               size_t ldm)
+        {
+            const uint32_t units_per_row = k >> 5; // 32 dense elements per unit
+            const size_t   total         = static_cast<size_t>(m) * units_per_row;
+            for(size_t u = static_cast<size_t>(blockIdx.x) * THREADS + threadIdx.x; u < total;
+                u += static_cast<size_t>(gridDim.x) * THREADS)
+            {
+                const uint32_t row  = static_cast<uint32_t>(u / units_per_row);
+                const uint32_t unit = static_cast<uint32_t>(u - static_cast<size_t>(row) * units_per_row);
+                const uint4    v = __ldcs(reinterpret_cast<const uint4*>(vals + row * ldv + unit * 16));
+                const uint32_t md = __ldcs(reinterpret_cast<const uint32_t*>(meta + row * ldm + unit * 4));
+                const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+                uint32_t       out[8];
+#pragma unroll
+                for(int gi = 0; gi < 8; ++gi)
+                {
+                    // group gi: values at bytes 2*gi, 2*gi+1; nibble gi of the metadata word
+                    const uint32_t pair = (vw[gi >> 1] >> ((gi & 1) * 16)) & 0xFFFFu;
+                    const uint32_t nib  = (md >> (4 * gi)) & 0xFu;
+                    const uint32_t i0 = nib & 3u, i1 = nib >> 2;
+                    out[gi] = ((pair & 0xFFu) << (8 * i0)) | ((pair >> 8) << (8 * i1));
+                }
+                uint4* dst = reinterpret_cast<uint4*>(dense + static_cast<size_t>(row) * k + unit * 32);
+                dst[0]     = make_uint4(out[0], out[1], out[2], out[3]);
+                dst[1]     = make_uint4(out[4], out[5], out[6], out[7]);
+            }
+        }
+
+        // One thread sign-extends 16 packed bytes (32 int4 values, low nibble first) to 32 int8.
+        __global__ void __launch_bounds__(THREADS)
+            unpack_i4_kernel(const uint8_t* __restrict__ packed, int8_t* __restrict__ dense,
+                             uint32_t rows, uint32_t k, size_t ld_bytes)
+        {
+            const uint32_t units_per_row = k >> 5;
+            const size_t   total         = static_cast<size_t>(rows) * units_per_row;
+            for(size_t u = static_cast<size_t>(blockIdx.x) * THREADS + threadIdx.x; u < total;
+                u += static_cast<size_t>(gridDim.x) * THREADS)
+            {
+                const uint32_t row  = static_cast<uint32_t>(u / units_per_row);
+                const uint32_t unit = static_cast<uint32_t>(u - static_cast<size_t>(row) * units_per_row);
+                const uint4    p = __ldcs(reinterpret_cast<const uint4*>(packed + row * ld_bytes + unit * 16));
+                const uint32_t pw[4] = {p.x, p.y, p.z, p.w};
+                uint32_t       out[8];
+#pragma unroll
+                for(int w = 0; w < 4; ++w)
+                {
+                    // bytes b0..b3 of the word -> values (lo0,hi0,lo1,hi1) and (lo2,hi2,lo3,hi3)
+                    const uint32_t x  = pw[w];
+                    const uint32_t lo = x & 0x0F0F0F0Fu, hi = (x >> 4) & 0x0F0F0F0Fu;
+                    // sign-extend each 4-bit field held in its own byte: (v ^ 8) - 8
+                    const uint32_t los = __vsub4(lo ^ 0x08080808u, 0x08080808u);
+                    const uint32_t his = __vsub4(hi ^ 0x08080808u, 0x08080808u);
+                    // interleave bytes: out = lo0 hi0 lo1 hi1 | lo2 hi2 lo3 hi3
+                    out[2 * w]     = __byte_perm(los, his, 0x5140);
+                    out[2 * w + 1] = __byte_perm(los, his, 0x7362);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(dense + static_cast<size_t>(row) * k + unit * 32);
+                dst[0]     = make_uint4(out[0], out[1], out[2], out[3]);
+                dst[1]     = make_uint4(out[4], out[5], out[6], out[7]);
+            }
+        }
+
+        static uint32_t grid_for(size_t units)
+        {
+            const size_t want = (units + THREADS - 1) / THREADS;
+            return static_cast<uint32_t>(want < 148u * 16u ? (want ? want : 1) : 148u * 16u);
+        }
+        static size_t round256(size_t x)
+        {
+            return (x + 255) & ~static_cast<size_t>(255);
+        }
+    } // namespace i8var
+} // namespace b200wmma
+
+using namespace b200wmma;
+
+extern "C" size_t b200wmma_gemm_i8_sp24_workspace_bytes(uint32_t m, uint32_t n, uint32_t k)
+{
+    (void)n;
+    return i8var::round256(static_cast<size_t>(m) * k);
+}
+
+extern "C" size_t b200wmma_gemm_i4_workspace_bytes(uint32_t m, uint32_t n, uint32_t k)
+{
+    return i8var::round256(static_cast<size_t>(m) * k) + i8var::round256(static_cast<size_t>(n) * k);
+}
+
+extern "C" int b200wmma_gemm_i8_sp24(uint32_t m, uint32_t n, uint32_t k, const int8_t* a_vals,
+                                     const uint8_t* a_meta, const int8_t* b, const int32_t* c,
+                                     int32_t* d, uint32_t lda_vals, uint32_t ld_meta, uint32_t ldb,
+                                     uint32_t ldc, uint32_t ldd, int32_t alpha, int32_t beta,
+                                     void* workspace, size_t workspace_bytes, void* stream)
+{
+    clear_error();
+    B200_REQUIRE(m && n && k, B200WMMA_ERR_INVALID_ARG, "gemm_i8_sp24: m, n, k must be non-zero");
+    B200_REQUIRE(a_vals && a_meta && b && d && workspace, B200WMMA_ERR_INVALID_ARG,
+                 "gemm_i8_sp24: a_vals, a_meta, b, d, workspace must be non-null");
+    B200_REQUIRE(k % 32 == 0, B200WMMA_ERR_UNSUPPORTED, "gemm_i8_sp24: k must be a multiple of 32");
+    B200_REQUIRE(lda_vals >= k / 2 && ld_meta >= k / 8, B200WMMA_ERR_INVALID_ARG,
+                 "gemm_i8_sp24: lda_vals / ld_meta smaller than k/2 / k/8");
+    B200_REQUIRE(aligned16(a_vals) && lda_vals % 16 == 0 && (reinterpret_cast<uintptr_t>(a_meta) & 3) == 0
+                     && ld_meta % 4 == 0 && aligned16(workspace),
+                 B200WMMA_ERR_ALIGNMENT,
+                 "gemm_i8_sp24: value rows must be 16-byte aligned, metadata rows 4-byte aligned");
+    B200_REQUIRE(workspace_bytes >= b200wmma_gemm_i8_sp24_workspace_bytes(m, n, k), B200WMMA_ERR_INVALID_ARG,
+                 "gemm_i8_sp24: workspace too small (%zu < %zu bytes)", workspace_bytes,
+                 b200wmma_gemm_i8_sp24_workspace_bytes(m, n, k));
+    if(int e = require_sm100())
+        return e;
+    int8_t*      dense = static_cast<int8_t*>(workspace);
+    const size_t units = static_cast<size_t>(m) * (k / 32);
+    i8var::expand_sp24_kernel<<<i8var::grid_for(units), i8var::THREADS, 0, as_stream(stream)>>>(
+        a_vals, a_meta, dense, m, k, lda_vals, ld_meta);
+    B200_CHECK_CUDA(cudaGetLastError());
+    return launch_gemm_tc05_i8(m, n, k, dense, b, c, d, k, ldb, ldc, ldd, alpha, beta, as_stream(stream));
+}
+
+extern "C" int b200wmma_gemm_i4(uint32_t m, uint32_t n, uint32_t k, const uint8_t* a_packed,
+                                const uint8_t* b_packed, const int32_t* c, int32_t* d,
+                                uint32_t lda_bytes, uint32_t ldb_bytes, uint32_t ldc, uint32_t ldd,
+                                int32_t alpha, int32_t beta, void* workspace, size_t workspace_bytes,
+                                void* stream)
+{
+    clear_error();
+    B200_REQUIRE(m && n && k, B200WMMA_ERR_INVALID_ARG, "gemm_i4: m, n, k must be non-zero");
+    B200_REQUIRE(a_packed && b_packed && d && workspace, B200WMMA_ERR_INVALID_ARG,
+                 "gemm_i4: a_packed, b_packed, d, workspace must be non-null");
+    B200_REQUIRE(k % 32 == 0, B200WMMA_ERR_UNSUPPORTED, "gemm_i4: k must be a multiple of 32");
+    B200_REQUIRE(lda_bytes >= k / 2 && ldb_bytes >= k / 2, B200WMMA_ERR_INVALID_ARG,
+                 "gemm_i4: lda_bytes / ldb_bytes smaller than k/2");
+    B200_REQUIRE(aligned16(a_packed) && aligned16(b_packed) && lda_bytes % 16 == 0 && ldb_bytes % 16 == 0
+                     && aligned16(workspace),
+                 B200WMMA_ERR_ALIGNMENT, "gemm_i4: packed rows must be 16-byte aligned");
+    B200_REQUIRE(workspace_bytes >= b200wmma_gemm_i4_workspace_bytes(m, n, k), B200WMMA_ERR_INVALID_ARG,
+                 "gemm_i4: workspace too small (%zu < %zu bytes)", workspace_bytes,
+                 b200wmma_gemm_i4_workspace_bytes(m, n, k));
+    if(int e = require_sm100())
+        return e;
+    int8_t* dense_a = static_cast<int8_t*>(workspace);
+    int8_t* dense_b = dense_a + i8var::round256(static_cast<size_t>(m) * k);
+    i8var::unpack_i4_kernel<<<i8var::grid_for(static_cast<size_t>(m) * (k / 32)), i8var::THREADS, 0,
+                              as_stream(stream)>>>(a_packed, dense_a, m, k, lda_bytes);
+    i8var::unpack_i4_kernel<<<i8var::grid_for(static_cast<size_t>(n) * (k / 32)), i8var::THREADS, 0,
+                              as_stream(stream)>>>(b_packed, dense_b, n, k, ldb_bytes);
+    B200_CHECK_CUDA(cudaGetLastError());
+    return launch_gemm_tc05_i8(m, n, k, dense_a, dense_b, c, d, k, k, ldc, ldd, alpha, beta,
+                               as_stream(stream));
+}

@@ -1,0 +1,225 @@
+// Thin inline-PTX wrappers for the sm_100a features the tensor-core GEMM uses:
+// mbarrier (with bounded waits), TMA tiled loads, tcgen05 alloc / mma / commit / ld.
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace b200wmma
+{
+    namespace ptx
+    {
+        __device__ __forceinline__ uint32_t smem_u32(const void* p)
+        {
+            return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+        }
+        __device__ __forceinline__ uint64_t globaltimer_ns()
+        {
+            uint64_t t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            return t;
+        }
+
+        // ---- mbarrier -----------------------------------------------------------------
+        __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+        {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count)
+                         : "memory");
+        }
+        __device__ __forceinline__ void fence_barrier_init()
+        {
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __device__ __forceinline__ void fence_proxy_async_smem()
+        {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+        {
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+                         "r"(bytes)
+                         : "memory");
+        }
+        __device__ __forceinline__ void mbar_arrive(uint32_t bar)
+        {
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+        }
+        __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+        {
+            uint32_t ok;
+            asm volatile("{\n"
+                         ".reg .pred p;\n"
+                         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+                         "selp.u32 %0, 1, 0, p;\n"
+                         "}"
+                         : "=r"(ok)
+                         : "r"(bar), "r"(parity)
+                         : "memory");
+            return ok != 0;
+        }
+
+        // Bounded wait.  Returns false when the wait was abandoned: either this thread ran
+        // past `timeout_ns` (it then raises the CTA-wide abort flag and records `who` in the
+        // device status word {code, detail}) or another thread of the CTA already aborted.
+        // No trap, no unbounded loop: the caller unwinds to the kernel's common exit.
+        constexpr unsigned STATUS_TIMEOUT_CODE = 5u; // == B200WMMA_ERR_DEVICE_TIMEOUT
+        __device__ __forceinline__ bool mbar_wait_bounded(uint32_t           bar,
+                                                          uint32_t           parity,
+                                                          volatile uint32_t* cta_abort,
+                                                          unsigned*          status,
+                                                          uint32_t           who,
+                                                          uint64_t           timeout_ns)
+        {
+            if(mbar_try_wait(bar, parity))
+                return true;
+            const uint64_t t0    = globaltimer_ns();
+            uint32_t       spins = 0;
+            while(true)
+            {
+                if(mbar_try_wait(bar, parity))
+                    return true;
+                if((++spins & 0xFFu) == 0u)
+                {
+                    if(*cta_abort)
+                        return false;
+                    if(globaltimer_ns() - t0 > timeout_ns)
+                    {
+                        *cta_abort = 1u;
+                        if(atomicCAS(status, 0u, STATUS_TIMEOUT_CODE) == 0u)
+                            status[1] = who;
+                        return false;
+                    }
+                }
+            }
+        }
+
+        // ---- TMA ------------------------------------------------------------------------
+        __device__ __forceinline__ void prefetch_tensormap(const void* tmap)
+        {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap))
+                         : "memory");
+        }
+        // 2-D tiled load global -> shared (this CTA), completion counted on `bar`.
+        // c0 is the innermost coordinate: c0 * element size must be a multiple of 16 bytes.
+        __device__ __forceinline__ void
+            tma_load_2d(uint32_t dst_smem, const void* tmap, int32_t c0, int32_t c1, uint32_t bar)
+        {
+            asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                         " [%0], [%1, {%2, %3}], [%4];" ::"r"(dst_smem),
+                         "l"(reinterpret_cast<uint64_t>(tmap)),
+                         "r"(c0),
+                         "r"(c1),
+                         "r"(bar)
+                         : "memory");
+        }
+
+        // ---- tcgen05 / tensor memory ----------------------------------------------------
+        __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols)
+        {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             dst_smem),
+                         "r"(ncols)
+                         : "memory");
+        }
+        __device__ __forceinline__ void tmem_relinquish()
+        {
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::
+                             : "memory");
+        }
+        __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols)
+        {
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr),
+                         "r"(ncols)
+                         : "memory");
+        }
+        __device__ __forceinline__ void tc_fence_before_sync()
+        {
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        }
+        __device__ __forceinline__ void tc_fence_after_sync()
+        {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        }
+        // D[tmem] (+)= A[smem] * B[smem]; one thread issues for the whole CTA.
+        __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem,
+                                                   uint64_t a_desc,
+                                                   uint64_t b_desc,
+                                                   uint32_t idesc,
+                                                   uint32_t accumulate)
+        {
+            asm volatile("{\n"
+                         ".reg .pred p;\n"
+                         "setp.ne.b32 p, %4, 0;\n"
+                         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+                         "}" ::"r"(d_tmem),
+                         "l"(a_desc),
+                         "l"(b_desc),
+                         "r"(idesc),
+                         "r"(accumulate)
+                         : "memory");
+        }
+        __device__ __forceinline__ void mma_i8_ss(uint32_t d_tmem,
+                                                  uint64_t a_desc,
+                                                  uint64_t b_desc,
+                                                  uint32_t idesc,
+                                                  uint32_t accumulate)
+        {
+            asm volatile("{\n"
+                         ".reg .pred p;\n"
+                         "setp.ne.b32 p, %4, 0;\n"
+                         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
+                         "}" ::"r"(d_tmem),
+                         "l"(a_desc),
+                         "l"(b_desc),
+                         "r"(idesc),
+                         "r"(accumulate)
+                         : "memory");
+        }
+        // mbarrier arrive once every MMA issued so far by this thread has completed.
+        __device__ __forceinline__ void tc_commit(uint32_t bar)
+        {
+            asm volatile(
+                "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                    bar)
+                : "memory");
+        }
+        // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets lane
+        // (taddr.lane + i), registers j = columns taddr.col + j.
+        __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32])
+        {
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, "
+                "[%32];"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]),
+                  "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+                  "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
+                  "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                  "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+                  "=r"(r[30]), "=r"(r[31])
+                : "r"(taddr)
+                : "memory");
+        }
+        __device__ __forceinline__ void tmem_ld_wait()
+        {
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        }
+
+        // Shared-memory matrix descriptor for a K-major operand tile stored as rows of 128
+        // bytes with the 128-byte swizzle (what a TMA SWIZZLE_128B box load produces):
+        // 8-row groups are 1024 bytes apart (SBO), the leading-dimension offset is unused for
+        // swizzled K-major layouts, descriptor version 1 (sm_100), layout type 2 (SWIZZLE_128B).
+        // The tile base must be 1024-byte aligned; stepping along K inside the 128-byte row
+        // adds the byte offset (>>4) to the start-address field.
+        __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr)
+        {
+            uint64_t desc = 0;
+            desc |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
+            desc |= static_cast<uint64_t>(1u) << 16; // LBO (ignored for swizzled K-major)
+            desc |= static_cast<uint64_t>(1024u >> 4) << 32; // SBO
+            desc |= static_cast<uint64_t>(1u) << 46; // descriptor version
+            desc |= static_cast<uint64_t>(2u) << 61; // SWIZZLE_128B
+            return desc;
+        }
+    } // namespace ptx
+} // namespace b200wmma

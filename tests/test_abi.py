@@ -1,0 +1,69 @@
+"""The C-ABI library loads and exports every symbol include/rocwmma_b200.h declares; argument checks
+that precede any device work return the documented codes.  No GPU needed, no compute calls."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from rocwmma_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "rocwmma_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200wmma_\w+)\s*\(", text)))
+
+
+def test_header_and_binding_agree():
+    assert declared_symbols() == sorted(_lib.SIGNATURES)
+
+
+def test_library_exports_every_declared_symbol():
+    handle = C.CDLL(_lib.LIB_PATH)
+    missing = [s for s in declared_symbols() if not hasattr(handle, s)]
+    assert not missing, f"librocwmma_b200.so lacks: {missing}"
+    assert _lib.lib().b200wmma_version() >= 100
+
+
+def test_no_cpu_fallback_in_product_sources():
+    """The product must not reach the CPU checker: nothing under rocwmma_b200/ or include/ names oracle/."""
+    bad = []
+    for base in ("rocwmma_b200", "include"):
+        for dirpath, _, files in os.walk(os.path.join(ROOT, base)):
+            if "_obj" in dirpath or "__pycache__" in dirpath:
+                continue
+            for f in files:
+                if f.endswith((".py", ".cu", ".cuh", ".h", ".hpp", ".cpp")):
+                    src = open(os.path.join(dirpath, f), errors="ignore").read()
+                    if re.search(r"\boracle\b|ref_port|cpu_ref", src):
+                        bad.append(os.path.join(dirpath, f))
+    assert not bad, bad
+
+
+@pytest.mark.parametrize("call,code", [
+    (lambda L: L.b200wmma_gemm_f16(128, 128, 64, None, None, None, None, 64, 64, 128, 128, 1.0, 0.0, 2, 1, 0, 0, None), 1),
+    (lambda L: L.b200wmma_gemm_f16(128, 128, 64, None, None, None, None, 64, 64, 128, 128, 1.0, 0.0, 1, 0, 0, 0, None), 2),
+    (lambda L: L.b200wmma_gemm_f16(0, 128, 64, 16, 16, None, 16, 64, 64, 128, 128, 1.0, 0.0, 0, 1, 0, 0, None), 1),
+    (lambda L: L.b200wmma_gemm_f16(128, 128, 64, 16, 16, None, 16, 64, 64, 128, 128, 1.0, 1.0, 0, 1, 0, 0, None), 1),
+    (lambda L: L.b200wmma_gemm_i8(128, 128, 64, 16, 16, None, 16, 60, 64, 128, 128, 1, 0, 0, 1, 0, None), 1),
+    (lambda L: L.b200wmma_gemm_i8(128, 128, 64, 16, 16, None, 16, 72, 64, 128, 128, 1, 0, 0, 1, 0, None), 3),
+    (lambda L: L.b200wmma_gemm_f64(8, 8, 7, 16, 16, None, 16, 8, 8, 8, 8, 1.0, 0.0, 0, 1, 0, None), 3),
+    (lambda L: L.b200wmma_gemv_f32(0, 8, 16, 8, 0, 16, 16, 1.0, 0.0, None), 1),
+    (lambda L: L.b200wmma_gemv_f64(8, 8, 16, 4, 0, 16, 16, 1.0, 0.0, None), 1),
+    (lambda L: L.b200wmma_dlrm_fwd(16, 16, 40, 40, 128, 4, 1024, None), 2),
+    (lambda L: L.b200wmma_dlrm_fwd(16, 16, 27, 32, 100, 4, 480, None), 2),
+    (lambda L: L.b200wmma_dlrm_fwd(16, 16, 27, 32, 128, 4, 100, None), 1),
+    (lambda L: L.b200wmma_dlrm_bwd(16, None, 16, None, 27, 32, 128, 4, 480, 0, None), 1),
+    (lambda L: L.b200wmma_gemm_i8_sp24(64, 64, 48, 16, 16, 16, None, 16, 24, 8, 48, 64, 64, 1, 0, 16, 1 << 20, None), 2),
+    (lambda L: L.b200wmma_gemm_i4(64, 64, 64, 16, 16, None, 16, 32, 32, 64, 64, 1, 0, 16, 16, None), 1),
+    (lambda L: L.b200wmma_ctx_create(None), 1),
+], ids=["bad_layout_flag", "unsupported_layout", "zero_m", "null_c_with_beta", "lda_too_small",
+        "lda_not_16B", "f64_odd_k", "gemv_zero_m", "gemv_lda_small", "dlrm_m_gt_32", "dlrm_k_not_16",
+        "dlrm_out_stride_small", "dlrm_bwd_null_upstream", "sp24_k_not_32", "i4_workspace_small", "ctx_null"])
+def test_argument_checks(call, code):
+    L = _lib.lib()
+    assert call(L) == code
+    assert L.b200wmma_last_error_string()  # a message is always recorded

@@ -1,0 +1,215 @@
+"""GPU parity of the tcgen05 GEMM entry points (through the C ABI) against the CPU oracle.
+
+fp16 results are judged with |d - ref| / (|alpha| sum|a||b| + |beta||c|) <= 1e-3 (fp32 out) / 2e-3 (fp16 out);
+fp64 with 1e-12; int8 / int4 / 2:4-sparse must be bit-exact."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import gen_golden as GG
+from conftest import TOL_F16_OUT, TOL_F32_OUT, TOL_F64_OUT, gemm_rel_err
+from gpu_util import assert_status_ok, dev, nan_filled, oracle_gemm_rows
+from oracle import cpu_ref as R
+from rocwmma_b200 import api
+from rocwmma_b200 import datagen as G
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def run_f16(m, n, k, alpha, beta, out_np, seed_shift=0, ldd_pad=0):
+    a = G.uniform_np(G.SEED_A + seed_shift, (m, k), np.float16)
+    b = G.uniform_np(G.SEED_B + seed_shift, (k, n), np.float16)
+    c = G.uniform_np(G.SEED_C + seed_shift, (m, n), out_np)
+    bs = np.ascontiguousarray(b.T)  # column-major storage: n rows of k
+    tdt = torch.float16 if out_np == np.float16 else torch.float32
+    ldd = n + ldd_pad
+    d = nan_filled((m, ldd), tdt)
+    api.gemm_f16(m, n, k, dev(a), dev(bs), dev(c), d, k, k, n, ldd, alpha, beta)
+    assert_status_ok()
+    dh = d.cpu().numpy()
+    ref = oracle_gemm_rows(a, bs, c, alpha, beta, out_np, n, k)
+    bound = R.gemm_abs_bound(m, n, k, a, b, c, alpha, beta)
+    err = gemm_rel_err(dh[:, :n], ref, bound)
+    tol = TOL_F16_OUT if out_np == np.float16 else TOL_F32_OUT
+    assert err <= tol, f"rel err {err:.3e} > {tol}"
+    if ldd_pad:  # contamination: the guard columns keep their marker
+        assert np.isnan(dh[:, n:]).all()
+    return err
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 256), (256, 512, 512), (384, 256, 1024),
+                                   (128, 256, 8), (2048, 2048, 512)])
+def test_gemm_f16_f16out(m, n, k):
+    run_f16(m, n, k, 1.0, 1.0, np.float16)
+
+
+@pytest.mark.parametrize("m,n,k", [(100, 200, 72), (1, 8, 8), (129, 257, 136), (300, 40, 200)])
+def test_gemm_f16_ragged(m, n, k):
+    run_f16(m, n, k, 2.0, 2.0, np.float32, seed_shift=10)
+    run_f16(m, n, k, 1.0, 1.0, np.float16, seed_shift=20, ldd_pad=8)
+
+
+def test_gemm_f16_config1_1024_f32out():
+    """M=N=K=1024, A row / B col fp16, C/D fp32, alpha=beta=2: full-matrix check."""
+    run_f16(1024, 1024, 1024, 2.0, 2.0, np.float32)
+
+
+def test_gemm_f16_beta0_null_c_and_inplace():
+    m, n, k = 256, 256, 128
+    a = G.uniform_np(1, (m, k), np.float16); b = G.uniform_np(2, (k, n), np.float16)
+    bs = np.ascontiguousarray(b.T)
+    d = nan_filled((m, n), torch.float16)
+    api.gemm_f16(m, n, k, dev(a), dev(bs), None, d, k, k, n, n, 1.5, 0.0)
+    ref = oracle_gemm_rows(a, bs, None, 1.5, 0.0, np.float16, n, k)
+    bound = R.gemm_abs_bound(m, n, k, a, b, None, 1.5, 0.0)
+    assert gemm_rel_err(d.cpu().numpy(), ref, bound) <= TOL_F16_OUT
+    # c == d (in place)
+    c = G.uniform_np(3, (m, n), np.float16)
+    cd = dev(c)
+    api.gemm_f16(m, n, k, dev(a), dev(bs), cd, cd, k, k, n, n, 1.0, 1.0)
+    ref = oracle_gemm_rows(a, bs, c, 1.0, 1.0, np.float16, n, k)
+    bound = R.gemm_abs_bound(m, n, k, a, b, c, 1.0, 1.0)
+    assert gemm_rel_err(cd.cpu().numpy(), ref, bound) <= TOL_F16_OUT
+    assert_status_ok()
+
+
+def test_gemm_f16_integer_inputs_exact():
+    """Small signed integers as the reference's test fill uses (test/device/common.hpp:203-240): every
+    product and partial sum is exactly representable, so the result must equal the oracle bit for bit."""
+    m, n, k = 256, 512, 256
+    i, j = np.meshgrid(np.arange(m), np.arange(k), indexing="ij")
+    a = (((i * k + j) % 5) * np.where(((i * k + j) % 5) % 3 == 0, -1, 1)).astype(np.float16)
+    i, j = np.meshgrid(np.arange(k), np.arange(n), indexing="ij")
+    b = (((i * n + j) % 3) * np.where(((i * n + j) % 3) % 3 == 0, -1, 1)).astype(np.float16)
+    c = np.ones((m, n), np.float32)
+    bs = np.ascontiguousarray(b.T)
+    d = nan_filled((m, n), torch.float32)
+    api.gemm_f16(m, n, k, dev(a), dev(bs), dev(c), d, k, k, n, n, 2.0, 2.0)
+    ref = oracle_gemm_rows(a, bs, c, 2.0, 2.0, np.float32, n, k)
+    assert np.array_equal(d.cpu().numpy(), ref)
+    assert_status_ok()
+
+
+def test_gemm_reference_fixtures():
+    """The committed outputs of the reference's own gemm_CPU (tests/golden/gemm_ref.npz)."""
+    gold = np.load(os.path.join(GOLD, "gemm_ref.npz"))
+    for case in GG.GEMM_CASES:
+        name, m, n, k, it, ot, alpha, beta, la, lb, lc, ld = case
+        if (la, lb, lc, ld) != (0, 1, 0, 0) or it == np.float32:
+            continue
+        a, b, c, sa, sb, sc = GG.gemm_inputs(case)
+        ref = gold[name].reshape(m, n)
+        if it == np.float16:
+            d = nan_filled((m, n), torch.float16 if ot == np.float16 else torch.float32)
+            api.gemm_f16(m, n, k, dev(sa), dev(sb), dev(sc), d, k, k, n, n, alpha, beta)
+            bound = R.gemm_abs_bound(m, n, k, a, b, c, alpha, beta)
+            assert gemm_rel_err(d.cpu().numpy(), ref, bound) <= (TOL_F16_OUT if ot == np.float16 else TOL_F32_OUT), name
+        elif it == np.int8:
+            d = nan_filled((m, n), torch.int32)
+            api.gemm_i8(m, n, k, dev(sa), dev(sb), dev(sc), d, k, k, n, n, alpha, beta)
+            assert np.array_equal(d.cpu().numpy(), ref), name
+        elif it == np.float64:
+            d = nan_filled((m, n), torch.float64)
+            api.gemm_f64(m, n, k, dev(sa), dev(sb), dev(sc), d, k, k, n, n, alpha, beta)
+            bound = R.gemm_abs_bound(m, n, k, a, b, c, alpha, beta)
+            assert gemm_rel_err(d.cpu().numpy(), ref, bound) <= TOL_F64_OUT, name
+    assert_status_ok()
+
+
+@pytest.mark.parametrize("m,n,k,alpha,beta", [(128, 256, 128, 1, 0), (256, 256, 1024, 1, 0), (128, 512, 16384, 1, 0),
+                                              (100, 72, 144, 3, -2), (513, 300, 272, 1, 1)])
+def test_gemm_i8_bit_exact(m, n, k, alpha, beta):
+    a = G.int8_np(G.SEED_A, (m, k)); b = G.int8_np(G.SEED_B, (k, n))
+    c = G.int8_np(G.SEED_C, (m, n)).astype(np.int32) * 12345
+    bs = np.ascontiguousarray(b.T)
+    d = nan_filled((m, n), torch.int32)
+    api.gemm_i8(m, n, k, dev(a), dev(bs), dev(c) if beta else None, d, k, k, n, n, alpha, beta)
+    assert_status_ok()
+    ref = oracle_gemm_rows(a, bs, c if beta else None, alpha, beta, np.int32, n, k)
+    assert np.array_equal(d.cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (200, 136, 512), (256, 256, 4096)])
+def test_gemm_i8_sparse24_bit_exact(m, n, k):
+    dense = G.int8_np(G.SEED_A, (m, k)); b = G.int8_np(G.SEED_B, (k, n))
+    vals, meta, densified = G.sparsify_24_np(dense)
+    bs = np.ascontiguousarray(b.T)
+    ws = torch.empty(api.gemm_i8_sp24_workspace_bytes(m, n, k), dtype=torch.uint8, device="cuda")
+    d = nan_filled((m, n), torch.int32)
+    api.gemm_i8_sp24(m, n, k, dev(vals), dev(meta), dev(bs), None, d, k // 2, k // 8, k, n, n, 1, 0, ws)
+    assert_status_ok()
+    ref = oracle_gemm_rows(densified, bs, None, 1, 0, np.int32, n, k)
+    assert np.array_equal(d.cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (200, 136, 512), (256, 256, 4096)])
+def test_gemm_i4_bit_exact(m, n, k):
+    a = G.int4_np(G.SEED_A, (m, k)); b = G.int4_np(G.SEED_B, (k, n))
+    bs = np.ascontiguousarray(b.T)
+    ws = torch.empty(api.gemm_i4_workspace_bytes(m, n, k), dtype=torch.uint8, device="cuda")
+    d = nan_filled((m, n), torch.int32)
+    api.gemm_i4(m, n, k, dev(G.pack_int4_np(a)), dev(G.pack_int4_np(bs)), None, d, k // 2, k // 2, n, n, 1, 0, ws)
+    assert_status_ok()
+    ref = oracle_gemm_rows(a, bs, None, 1, 0, np.int32, n, k)
+    assert np.array_equal(d.cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 136, 72), (512, 384, 256)])
+def test_gemm_f64(m, n, k):
+    a = G.uniform_np(G.SEED_A, (m, k), np.float64); b = G.uniform_np(G.SEED_B, (k, n), np.float64)
+    c = G.uniform_np(G.SEED_C, (m, n), np.float64)
+    bs = np.ascontiguousarray(b.T)
+    d = nan_filled((m, n), torch.float64)
+    api.gemm_f64(m, n, k, dev(a), dev(bs), dev(c), d, k, k, n, n, 1.5, 0.5)
+    ref = oracle_gemm_rows(a, bs, c, 1.5, 0.5, np.float64, n, k)
+    bound = R.gemm_abs_bound(m, n, k, a, b, c, 1.5, 0.5)
+    assert gemm_rel_err(d.cpu().numpy(), ref, bound) <= TOL_F64_OUT
+
+
+def _rows_sample(m, count, seed):
+    rows = (G.raw_np(seed, count) % np.uint64(m)).astype(np.int64)
+    rows[0], rows[-1] = 0, m - 1
+    return np.unique(rows)
+
+
+def test_gemm_f16_full_size_8192_row_sample():
+    """Benchmark size (M=N=K=8192, fp16 C/D, alpha=beta=1): all columns of 48 seeded-random rows are
+    checked against the oracle (rows are independent), and the whole output must be finite."""
+    m = n = k = 8192
+    a = G.fill_torch(torch.empty((m, k), dtype=torch.float16, device="cuda"), G.SEED_A, "uniform")
+    bs = G.fill_torch(torch.empty((n, k), dtype=torch.float16, device="cuda"), G.SEED_B, "uniform")
+    c = G.fill_torch(torch.empty((m, n), dtype=torch.float16, device="cuda"), G.SEED_C, "uniform")
+    d = nan_filled((m, n), torch.float16)
+    api.gemm_f16(m, n, k, a, bs, c, d, k, k, n, n, 1.0, 1.0)
+    assert_status_ok()
+    assert bool(torch.isfinite(d).all())
+    rows = _rows_sample(m, 48, 99)
+    idx = torch.from_numpy(rows).cuda()
+    a_r, c_r, d_r = a[idx].cpu().numpy(), c[idx].cpu().numpy(), d[idx].cpu().numpy()
+    b_h = bs.cpu().numpy()
+    ref = oracle_gemm_rows(a_r, b_h, c_r, 1.0, 1.0, np.float16, n, k)
+    bound = R.gemm_abs_bound(len(rows), n, k, a_r, b_h.T, c_r, 1.0, 1.0)
+    assert gemm_rel_err(d_r, ref, bound) <= TOL_F16_OUT
+
+
+def test_gemm_i8_full_size_row_sample():
+    """M=N=8192, K=16384 int8 -> int32, alpha=1, beta=0: 32 seeded-random rows bit-exact."""
+    m, n, k = 8192, 8192, 16384
+    a = G.fill_torch(torch.empty((m, k), dtype=torch.int8, device="cuda"), G.SEED_A, "int8")
+    bs = G.fill_torch(torch.empty((n, k), dtype=torch.int8, device="cuda"), G.SEED_B, "int8")
+    d = nan_filled((m, n), torch.int32)
+    api.gemm_i8(m, n, k, a, bs, None, d, k, k, n, n, 1, 0)
+    assert_status_ok()
+    rows = _rows_sample(m, 32, 98)
+    idx = torch.from_numpy(rows).cuda()
+    ref = oracle_gemm_rows(a[idx].cpu().numpy(), bs.cpu().numpy(), None, 1, 0, np.int32, n, k)
+    assert np.array_equal(d[idx].cpu().numpy(), ref)
+    # a checksum over the whole output that no element can be missing from: column sums of D equal
+    # (column sums of A) x B, computed exactly in int64 on the device by torch as plumbing
+    col = d.to(torch.int64).sum(dim=0)
+    a_sum = a.to(torch.float64).sum(dim=0)          # exact: |sum| < 2^53
+    expect = (bs.to(torch.float64) @ a_sum)          # n values, each exact in fp64 (|.| < 2^53)
+    assert torch.equal(col.to(torch.float64), expect)
