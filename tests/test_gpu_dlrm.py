@@ -142,10 +142,10 @@ def test_dlrm_full_size_config():
     assert bool(torch.isfinite(out).all()) and bool((out[:, w - 1] == 0).all())
     assert bool((grad[:, m:] == 0).all())
     sel = torch.from_numpy(np.unique((G.raw_np(77, 256) % np.uint64(B)).astype(np.int64))).cuda()
-    xs = x[sel][:, :m].cpu().numpy()
+    xs = np.ascontiguousarray(x[sel][:, :m].cpu().numpy())
     ups = up[sel].cpu().numpy()
     check_fwd(out[sel].cpu().numpy(), xs, R.dlrm_fwd(R.port(), xs, m, k, len(sel)))
-    rg, rm = R.dlrm_bwd(R.port(), xs, ups[:, :w - 1], m, k, len(sel))
+    rg, rm = R.dlrm_bwd(R.port(), xs, np.ascontiguousarray(ups[:, :w - 1]), m, k, len(sel))
     g = grad[sel].cpu().numpy()
     g[:, m:] = np.nan
     check_bwd(g, None, xs, ups, rg, rm, True)
