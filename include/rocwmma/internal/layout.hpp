@@ -1,0 +1,257 @@
+// Register layouts of fragments on 32-thread warps, and the 1-D data-space mappers.
+//
+// rocWMMA leaves the order of fragment elements unspecified ("vector elements have no
+// guaranteed order or locality", library/include/rocwmma/rocwmma.hpp:126).  What user code
+// relies on, and what holds here:
+//   * accumulator fragments of one shape map element i to the same matrix coordinate for
+//     every data type (so `d.x[i] = alpha * acc.x[i] + beta * c.x[i]` is element-wise);
+//   * a fragment's register layout does not depend on its memory data layout, so
+//     applyDataLayout is a re-interpretation;
+//   * matrix_b<BN,BK> is the register-for-register transpose of matrix_a<BM=BN,BK>, so
+//     applyTranspose is a re-interpretation as well;
+//   * num_elements = BlockDim * BlockK / 32.
+//
+// A fragment is a grid of 16-row "atoms" shaped after the operands of NVIDIA's warp-level
+// mma.sync instructions, so that mma_sync needs no shuffles:
+//   element size   A atom (M x K)   instruction            per-lane elements
+//   1 byte         16 x 16          m16n8k16 (s8)          (row g + 8*(i>>2),      col 4t + (i&3))
+//   2 bytes        16 x 16          m16n8k16 (f16)         (row g + 8*((i>>1)&1),  col 2t + (i&1) + 8*(i>>2))
+//   4 bytes        16 x 8           m16n8k8  (tf32)        (row g + 8*(i&1),       col t + 4*(i>>1))
+//   8 bytes        16 x 4           m16n8k4  (f64)         (row g + 8*i,           col t)
+// with g = lane / 4, t = lane % 4.  B atoms are the transposes (k takes the role of col, n of
+// row).  Accumulator atoms are 16 x 16 = two m16n8 result tiles:
+//   (row g + 8*((i>>1)&1), col 2t + (i&1) + 8*(i>>2)).
+#ifndef ROCWMMA_B200_LAYOUT_HPP
+#define ROCWMMA_B200_LAYOUT_HPP
+
+#include "types.hpp"
+#include "utils.hpp"
+
+namespace rocwmma
+{
+    struct row_major
+    {
+    };
+    struct col_major
+    {
+    };
+    struct matrix_a
+    {
+    };
+    struct matrix_b
+    {
+    };
+    struct accumulator
+    {
+    };
+
+    enum layout_t : uint32_t
+    {
+        mem_row_major,
+        mem_col_major
+    };
+
+    namespace detail
+    {
+        // ---- 1-D data space (rocWMMA internal/mapping_util.hpp DataSpace) ---------------------
+        template <typename DataOrientation>
+        struct DataSpace
+        {
+            enum : uint32_t
+            {
+                MajorIndex = std::is_same<DataOrientation, row_major>::value ? 0 : 1,
+                MinorIndex = std::is_same<DataOrientation, row_major>::value ? 1 : 0
+            };
+            using Orientation = DataOrientation;
+            ROCWMMA_HOST_DEVICE constexpr static inline uint32_t leadingDim(Coord2d const& matrixSize)
+            {
+                return get<MinorIndex>(matrixSize);
+            }
+            ROCWMMA_HOST_DEVICE constexpr static inline uint32_t fromMatrixCoord(Coord2d const& c,
+                                                                                 uint32_t       ld)
+            {
+                return get<MajorIndex>(c) * ld + get<MinorIndex>(c);
+            }
+        };
+        template <>
+        struct DataSpace<void>;
+
+        template <typename L>
+        struct OrthoLayout;
+        template <>
+        struct OrthoLayout<row_major>
+        {
+            using type = col_major;
+        };
+        template <>
+        struct OrthoLayout<col_major>
+        {
+            using type = row_major;
+        };
+        template <>
+        struct OrthoLayout<void>
+        {
+            using type = void;
+        };
+
+        // ---- atom geometry by element size --------------------------------------------------
+        template <uint32_t ElemBytes>
+        struct AtomK;
+        template <>
+        struct AtomK<1>
+        {
+            static constexpr uint32_t value = 16;
+        };
+        template <>
+        struct AtomK<2>
+        {
+            static constexpr uint32_t value = 16;
+        };
+        template <>
+        struct AtomK<4>
+        {
+            static constexpr uint32_t value = 8;
+        };
+        template <>
+        struct AtomK<8>
+        {
+            static constexpr uint32_t value = 4;
+        };
+
+        // Coordinates (dim, k) of element `i` of one input atom for lane (g, t); `dim` runs along
+        // the 16-wide block dimension (rows of A / columns of B), `k` along the reduction.
+        // `Run` = number of consecutive elements that are adjacent along k.
+        template <uint32_t ElemBytes>
+        struct InputAtom;
+        template <>
+        struct InputAtom<1>
+        {
+            static constexpr uint32_t Elems = 8, Run = 4;
+            ROCWMMA_DEVICE static inline void coord(uint32_t g, uint32_t t, uint32_t i, uint32_t& dim,
+                                                    uint32_t& k)
+            {
+                dim = g + 8u * (i >> 2);
+                k   = 4u * t + (i & 3u);
+            }
+        };
+        template <>
+        struct InputAtom<2>
+        {
+            static constexpr uint32_t Elems = 8, Run = 2;
+            ROCWMMA_DEVICE static inline void coord(uint32_t g, uint32_t t, uint32_t i, uint32_t& dim,
+                                                    uint32_t& k)
+            {
+                dim = g + 8u * ((i >> 1) & 1u);
+                k   = 2u * t + (i & 1u) + 8u * (i >> 2);
+            }
+        };
+        template <>
+        struct InputAtom<4>
+        {
+            static constexpr uint32_t Elems = 4, Run = 1;
+            ROCWMMA_DEVICE static inline void coord(uint32_t g, uint32_t t, uint32_t i, uint32_t& dim,
+                                                    uint32_t& k)
+            {
+                dim = g + 8u * (i & 1u);
+                k   = t + 4u * (i >> 1);
+            }
+        };
+        template <>
+        struct InputAtom<8>
+        {
+            static constexpr uint32_t Elems = 2, Run = 1;
+            ROCWMMA_DEVICE static inline void coord(uint32_t g, uint32_t t, uint32_t i, uint32_t& dim,
+                                                    uint32_t& k)
+            {
+                dim = g + 8u * i;
+                k   = t;
+            }
+        };
+
+        struct AccAtom
+        {
+            static constexpr uint32_t Elems = 8, Run = 2;
+            ROCWMMA_DEVICE static inline void coord(uint32_t g, uint32_t t, uint32_t i, uint32_t& row,
+                                                    uint32_t& col)
+            {
+                row = g + 8u * ((i >> 1) & 1u);
+                col = 2u * t + (i & 1u) + 8u * (i >> 2);
+            }
+        };
+
+        // ---- whole-fragment geometry -----------------------------------------------------------
+        // Gives, for each fragment kind: block height / width in matrix space, the atom grid and
+        // the map  element index -> (row, col)  inside the block.  `RunAlongCol` says whether
+        // consecutive elements of a run are adjacent along the column (true) or the row (false).
+        template <typename MatrixT, uint32_t BM, uint32_t BN, uint32_t BK, typename DataT>
+        struct FragGeometry;
+
+        template <uint32_t BM, uint32_t BN, uint32_t BK, typename DataT>
+        struct FragGeometry<matrix_a, BM, BN, BK, DataT>
+        {
+            using Atom = InputAtom<sizeof(DataT)>;
+            static constexpr uint32_t KA = AtomK<sizeof(DataT)>::value;
+            static constexpr uint32_t BlockHeight = BM, BlockWidth = BK, BlockDim = BM, KDim = BK;
+            static_assert(BM % 16 == 0, "matrix_a fragments need BlockM to be a multiple of 16");
+            static_assert(BK % KA == 0, "BlockK must be a multiple of the instruction K "
+                                        "(16 for 8/16-bit types, 8 for 32-bit, 4 for 64-bit)");
+            static constexpr uint32_t AtomsDim = BM / 16, AtomsK = BK / KA;
+            static constexpr uint32_t Atoms = AtomsDim * AtomsK, AtomElems = Atom::Elems, Run = Atom::Run;
+            static constexpr uint32_t Size = Atoms * AtomElems;
+            static constexpr bool RunAlongCol = true;
+            ROCWMMA_DEVICE static inline void coord(uint32_t lane, uint32_t atom, uint32_t i, uint32_t& row,
+                                                    uint32_t& col)
+            {
+                uint32_t d, k;
+                Atom::coord(lane >> 2, lane & 3u, i, d, k);
+                row = (atom / AtomsK) * 16u + d;
+                col = (atom % AtomsK) * KA + k;
+            }
+        };
+
+        template <uint32_t BM, uint32_t BN, uint32_t BK, typename DataT>
+        struct FragGeometry<matrix_b, BM, BN, BK, DataT>
+        {
+            using Atom = InputAtom<sizeof(DataT)>;
+            static constexpr uint32_t KA = AtomK<sizeof(DataT)>::value;
+            static constexpr uint32_t BlockHeight = BK, BlockWidth = BN, BlockDim = BN, KDim = BK;
+            static_assert(BN % 16 == 0, "matrix_b fragments need BlockN to be a multiple of 16");
+            static_assert(BK % KA == 0, "BlockK must be a multiple of the instruction K "
+                                        "(16 for 8/16-bit types, 8 for 32-bit, 4 for 64-bit)");
+            static constexpr uint32_t AtomsDim = BN / 16, AtomsK = BK / KA;
+            static constexpr uint32_t Atoms = AtomsDim * AtomsK, AtomElems = Atom::Elems, Run = Atom::Run;
+            static constexpr uint32_t Size = Atoms * AtomElems;
+            static constexpr bool RunAlongCol = false; // runs are adjacent along k = along rows of B
+            ROCWMMA_DEVICE static inline void coord(uint32_t lane, uint32_t atom, uint32_t i, uint32_t& row,
+                                                    uint32_t& col)
+            {
+                uint32_t d, k;
+                Atom::coord(lane >> 2, lane & 3u, i, d, k);
+                row = (atom % AtomsK) * KA + k;
+                col = (atom / AtomsK) * 16u + d;
+            }
+        };
+
+        template <uint32_t BM, uint32_t BN, uint32_t BK, typename DataT>
+        struct FragGeometry<accumulator, BM, BN, BK, DataT>
+        {
+            static constexpr uint32_t BlockHeight = BM, BlockWidth = BN, BlockDim = BM, KDim = BN;
+            static_assert(BM % 16 == 0 && BN % 16 == 0,
+                          "accumulator fragments need BlockM and BlockN to be multiples of 16");
+            static constexpr uint32_t AtomsM = BM / 16, AtomsN = BN / 16;
+            static constexpr uint32_t Atoms = AtomsM * AtomsN, AtomElems = AccAtom::Elems, Run = AccAtom::Run;
+            static constexpr uint32_t Size = Atoms * AtomElems;
+            static constexpr bool RunAlongCol = true;
+            ROCWMMA_DEVICE static inline void coord(uint32_t lane, uint32_t atom, uint32_t i, uint32_t& row,
+                                                    uint32_t& col)
+            {
+                uint32_t r, c;
+                AccAtom::coord(lane >> 2, lane & 3u, i, r, c);
+                row = (atom / AtomsN) * 16u + r;
+                col = (atom % AtomsN) * 16u + c;
+            }
+        };
+    } // namespace detail
+} // namespace rocwmma
+
+#endif

@@ -1,0 +1,93 @@
+// Warp-level mma.sync wrappers, one per supported (input type, compute type) pair.
+// Each takes the per-lane registers of one A atom, one B atom and one 16x16 accumulator atom
+// in the register orders defined in layout.hpp and accumulates acc += A x B.
+#ifndef ROCWMMA_B200_MMA_ATOMS_HPP
+#define ROCWMMA_B200_MMA_ATOMS_HPP
+
+#include "types.hpp"
+
+namespace rocwmma
+{
+    namespace detail
+    {
+        // fp16 x fp16 -> fp32: a = 4 x b32 (8 halfs), b = 4 x b32 ordered
+        // [n-half 0 k-lo, n-half 1 k-lo, n-half 0 k-hi, n-half 1 k-hi], acc = 8 floats (two m16n8 tiles).
+        ROCWMMA_DEVICE inline void mma_atom_f16_f32(float (&acc)[8], const uint32_t (&a)[4],
+                                                    const uint32_t (&b)[4])
+        {
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+                         "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                         : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])
+                         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[2]));
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+                         "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                         : "+f"(acc[4]), "+f"(acc[5]), "+f"(acc[6]), "+f"(acc[7])
+                         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[1]), "r"(b[3]));
+        }
+
+        // int8 x int8 -> int32 (m16n8k16): a = 2 x b32, b = 2 x b32 [n-half 0, n-half 1]
+        ROCWMMA_DEVICE inline void mma_atom_i8_i32(int32_t (&acc)[8], const uint32_t (&a)[2],
+                                                   const uint32_t (&b)[2])
+        {
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 "
+                         "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                         : "+r"(acc[0]), "+r"(acc[1]), "+r"(acc[2]), "+r"(acc[3])
+                         : "r"(a[0]), "r"(a[1]), "r"(b[0]));
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 "
+                         "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                         : "+r"(acc[4]), "+r"(acc[5]), "+r"(acc[6]), "+r"(acc[7])
+                         : "r"(a[0]), "r"(a[1]), "r"(b[1]));
+        }
+
+        // fp64 (m16n8k4): a = 2 doubles, b = 2 doubles [n-half 0, n-half 1]
+        ROCWMMA_DEVICE inline void mma_atom_f64(double (&acc)[8], const double (&a)[2], const double (&b)[2])
+        {
+            asm volatile("mma.sync.aligned.m16n8k4.row.col.f64.f64.f64.f64 "
+                         "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                         : "+d"(acc[0]), "+d"(acc[1]), "+d"(acc[2]), "+d"(acc[3])
+                         : "d"(a[0]), "d"(a[1]), "d"(b[0]));
+            asm volatile("mma.sync.aligned.m16n8k4.row.col.f64.f64.f64.f64 "
+                         "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                         : "+d"(acc[4]), "+d"(acc[5]), "+d"(acc[6]), "+d"(acc[7])
+                         : "d"(a[0]), "d"(a[1]), "d"(b[1]));
+        }
+
+        // fp32 x fp32 -> fp32 on the tf32 tensor path with error compensation (3xTF32):
+        // x = hi + lo with hi = tf32(x); acc += lo_a*hi_b + hi_a*lo_b + hi_a*hi_b.
+        // The dropped lo*lo term is below 2^-22 relative, so results track an fp32 FMA chain.
+        ROCWMMA_DEVICE inline uint32_t to_tf32(float x)
+        {
+            uint32_t r;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+            return r;
+        }
+        ROCWMMA_DEVICE inline void mma_tf32_1688(float* acc, const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+        {
+            asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 "
+                         "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                         : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])
+                         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+        }
+        // a = 4 floats (16x8 atom), b = 4 floats ordered [k-lo n-half0, k-lo n-half1, k-hi n-half0, k-hi n-half1]
+        ROCWMMA_DEVICE inline void mma_atom_f32(float (&acc)[8], const float (&a)[4], const float (&b)[4])
+        {
+            uint32_t ah[4], al[4], bh[4], bl[4];
+#pragma unroll
+            for(int i = 0; i < 4; ++i)
+            {
+                ah[i] = to_tf32(a[i]);
+                al[i] = to_tf32(a[i] - __uint_as_float(ah[i]));
+                bh[i] = to_tf32(b[i]);
+                bl[i] = to_tf32(b[i] - __uint_as_float(bh[i]));
+            }
+            mma_tf32_1688(acc, al, bh[0], bh[2]);
+            mma_tf32_1688(acc, ah, bl[0], bl[2]);
+            mma_tf32_1688(acc, ah, bh[0], bh[2]);
+            mma_tf32_1688(acc + 4, al, bh[1], bh[3]);
+            mma_tf32_1688(acc + 4, ah, bl[1], bl[3]);
+            mma_tf32_1688(acc + 4, ah, bh[1], bh[3]);
+        }
+    } // namespace detail
+} // namespace rocwmma
+
+#endif

@@ -1,0 +1,86 @@
+// Data types of the device API (rocWMMA internal/types.hpp:48-62, :102-114).
+//
+// float16_t in the reference is the compiler's _Float16, which mixes freely with float in
+// expressions such as `alpha * acc.x[i] + beta * c.x[i]` (samples/simple_hgemm.cpp:131-134).
+// CUDA's __half makes `float * __half` ambiguous, so float16_t here is a 2-byte wrapper around
+// the same bits with implicit conversions to and from float and no arithmetic of its own:
+// mixed expressions are evaluated in fp32 and rounded once on assignment.
+#ifndef ROCWMMA_B200_TYPES_HPP
+#define ROCWMMA_B200_TYPES_HPP
+
+#include <cuda_fp16.h>
+#include <cstdint>
+
+#include "config.hpp"
+
+namespace rocwmma
+{
+    struct __align__(2) float16_t
+    {
+        unsigned short bits;
+
+        float16_t() = default;
+        ROCWMMA_HOST_DEVICE float16_t(float f)
+        {
+            bits = __half_as_ushort(__float2half_rn(f));
+        }
+        ROCWMMA_HOST_DEVICE float16_t(double f)
+            : float16_t(static_cast<float>(f))
+        {
+        }
+        ROCWMMA_HOST_DEVICE float16_t(int v)
+            : float16_t(static_cast<float>(v))
+        {
+        }
+        ROCWMMA_HOST_DEVICE float16_t(unsigned v)
+            : float16_t(static_cast<float>(v))
+        {
+        }
+        ROCWMMA_HOST_DEVICE float16_t(__half h)
+        {
+            bits = __half_as_ushort(h);
+        }
+        ROCWMMA_HOST_DEVICE operator float() const
+        {
+            return __half2float(__ushort_as_half(bits));
+        }
+        ROCWMMA_HOST_DEVICE __half as_half() const
+        {
+            return __ushort_as_half(bits);
+        }
+    };
+    static_assert(sizeof(float16_t) == 2, "float16_t must be two bytes");
+
+    using hfloat16_t = __half;
+    using float32_t  = float;
+    using float64_t  = double;
+    using int8_t     = ::int8_t;
+    using uint8_t    = ::uint8_t;
+    using int16_t    = ::int16_t;
+    using int32_t    = ::int32_t;
+    using uint32_t   = ::uint32_t;
+    using int64_t    = ::int64_t;
+    using uint64_t   = ::uint64_t;
+    using index_t    = ::int32_t;
+
+    // Minimal fixed-size vector used as fragment storage (`*frag`, `frag.x`).
+    template <typename T, uint32_t N>
+    struct VecT
+    {
+        T data[N];
+        ROCWMMA_HOST_DEVICE T& operator[](uint32_t i)
+        {
+            return data[i];
+        }
+        ROCWMMA_HOST_DEVICE T const& operator[](uint32_t i) const
+        {
+            return data[i];
+        }
+        ROCWMMA_HOST_DEVICE constexpr static uint32_t size()
+        {
+            return N;
+        }
+    };
+} // namespace rocwmma
+
+#endif

@@ -1,0 +1,424 @@
+// rocWMMA-compatible device API on NVIDIA warps (32 threads, mma.sync tensor-core instructions).
+//
+// Same names, template parameters and semantics as rocWMMA's public header
+// (library/include/rocwmma/rocwmma.hpp:74-316): tags, layout_t, fragment, fill_fragment,
+// load_matrix_sync, store_matrix_sync, mma_sync, synchronize_workgroup.  A kernel written against
+// that header compiles against this one with nvcc for sm_100a; the "wave" is the CUDA warp
+// (Constants::AMDGCN_WAVE_SIZE == 32) and blockDim.x must be a multiple of 32.
+//
+// Supported block shapes: BlockM, BlockN multiples of 16; BlockK a multiple of 16 for 8- and
+// 16-bit inputs, 8 for fp32, 4 for fp64.  Supported mma_sync type pairs (input -> compute):
+// float16_t/hfloat16_t -> float32_t or float16_t, int8_t -> int32_t, float32_t -> float32_t
+// (3xTF32), float64_t -> float64_t.
+#ifndef ROCWMMA_B200_API_HPP
+#define ROCWMMA_B200_API_HPP
+
+#include "internal/config.hpp"
+#include "internal/layout.hpp"
+#include "internal/mapping_util.hpp"
+#include "internal/mma_atoms.hpp"
+#include "internal/types.hpp"
+#include "internal/utils.hpp"
+
+namespace rocwmma
+{
+    // ------------------------------------------------------------------------------------------
+    // fragment  (reference: rocwmma.hpp:127-202)
+    // ------------------------------------------------------------------------------------------
+    template <typename MatrixT, uint32_t BlockM, uint32_t BlockN, uint32_t BlockK, typename DataT,
+              typename DataLayoutT = void>
+    class alignas(alignof(DataT) > 4 ? alignof(DataT) : 4) fragment
+    {
+    public:
+        using Geometry = detail::FragGeometry<MatrixT, BlockM, BlockN, BlockK, DataT>;
+
+        struct Traits
+        {
+            constexpr static uint32_t Size = Geometry::Size;
+            using AccessT  = VecT<DataT, Size>;
+            using StorageT = VecT<DataT, Size>;
+            static_assert(Size * sizeof(DataT) >= 4, "Fragments must occupy at least one 32-bit register");
+        };
+
+        fragment() = default;
+
+        ROCWMMA_DEVICE inline DataT& operator[](uint32_t index)
+        {
+            return x[index];
+        }
+        ROCWMMA_DEVICE inline DataT const& operator[](uint32_t index) const
+        {
+            return x[index];
+        }
+        ROCWMMA_DEVICE inline typename Traits::StorageT& operator*()
+        {
+            return mStorage;
+        }
+        ROCWMMA_DEVICE inline typename Traits::StorageT const& operator*() const
+        {
+            return mStorage;
+        }
+
+        ROCWMMA_HOST_DEVICE constexpr static inline uint32_t height()
+        {
+            return Geometry::BlockHeight;
+        }
+        ROCWMMA_HOST_DEVICE constexpr static inline uint32_t width()
+        {
+            return Geometry::BlockWidth;
+        }
+        ROCWMMA_HOST_DEVICE constexpr static inline uint32_t blockDim()
+        {
+            return Geometry::BlockDim;
+        }
+        ROCWMMA_HOST_DEVICE constexpr static inline uint32_t kDim()
+        {
+            return Geometry::KDim;
+        }
+        ROCWMMA_HOST_DEVICE constexpr static inline uint32_t size()
+        {
+            return Traits::Size;
+        }
+
+        union
+        {
+            typename Traits::StorageT mStorage;
+            typename Traits::AccessT  mAccess;
+            DataT                     x[Traits::Size];
+        };
+
+        constexpr static uint32_t num_elements = Traits::Size;
+        using element_type                     = DataT;
+    };
+
+    // ---- fragment introspection used by kernels (reference: internal/api_fwd.hpp, io_shape.hpp) ----
+    namespace detail
+    {
+        template <typename FragT>
+        struct FragInfo;
+        template <typename MatrixT, uint32_t BM, uint32_t BN, uint32_t BK, typename DataT, typename LayoutT>
+        struct FragInfo<fragment<MatrixT, BM, BN, BK, DataT, LayoutT>>
+        {
+            using Matrix   = MatrixT;
+            using Data     = DataT;
+            using Layout   = LayoutT;
+            using Geometry = FragGeometry<MatrixT, BM, BN, BK, DataT>;
+            static constexpr uint32_t BlockM = BM, BlockN = BN, BlockK = BK;
+        };
+
+        template <typename Geometry_>
+        struct IOShape
+        {
+            enum : uint32_t
+            {
+                BlockHeight = Geometry_::BlockHeight,
+                BlockWidth  = Geometry_::BlockWidth,
+                BlockDim    = Geometry_::BlockDim,
+                KDim        = Geometry_::KDim
+            };
+        };
+    }
+    template <typename FragT>
+    using GetIOShape_t = detail::IOShape<typename detail::FragInfo<std::decay_t<FragT>>::Geometry>;
+    template <typename FragT>
+    using GetDataLayout_t = detail::DataSpace<typename detail::FragInfo<std::decay_t<FragT>>::Layout>;
+    template <typename FragT>
+    using GetDataType_t = typename detail::FragInfo<std::decay_t<FragT>>::Data;
+
+    // ------------------------------------------------------------------------------------------
+    // fill_fragment  (reference: rocwmma.hpp:217-219, rocwmma_impl.hpp:204-217)
+    // ------------------------------------------------------------------------------------------
+    template <typename MatrixT, uint32_t BlockM, uint32_t BlockN, uint32_t BlockK, typename DataT,
+              typename DataLayoutT>
+    ROCWMMA_DEVICE inline void fill_fragment(fragment<MatrixT, BlockM, BlockN, BlockK, DataT, DataLayoutT>& frag,
+                                             DataT value)
+    {
+#pragma unroll
+        for(uint32_t i = 0; i < frag.num_elements; ++i)
+            frag.x[i] = value;
+    }
+
+    namespace detail
+    {
+        template <uint32_t Bytes>
+        struct RawVec;
+        template <>
+        struct RawVec<2>
+        {
+            using type = unsigned short;
+        };
+        template <>
+        struct RawVec<4>
+        {
+            using type = uint32_t;
+        };
+        template <>
+        struct RawVec<8>
+        {
+            using type = uint2;
+        };
+        template <>
+        struct RawVec<16>
+        {
+            using type = uint4;
+        };
+
+        // Moves the atoms [atomBegin, atomEnd) of a fragment between registers and memory.
+        // ColMajorMem selects the memory layout.  When consecutive register elements are adjacent
+        // in memory (Run > 1 and the run direction is the contiguous memory direction) and the
+        // addresses are suitably aligned, a run moves as one 2..16-byte access.
+        template <bool IsLoad, bool ColMajorMem, typename Geometry, typename DataT>
+        ROCWMMA_DEVICE inline void move_atoms(DataT* regs, DataT* mem, uint32_t ldm, uint32_t atomBegin,
+                                              uint32_t atomEnd)
+        {
+            const uint32_t     lane       = threadIdx.x & 31u;
+            constexpr uint32_t Run        = Geometry::Run;
+            constexpr bool     contiguous = (Run > 1) && (Geometry::RunAlongCol != ColMajorMem);
+            constexpr uint32_t VecBytes   = contiguous ? Run * sizeof(DataT) : sizeof(DataT);
+            bool               vec_ok     = false;
+            if constexpr(contiguous)
+                vec_ok = ((reinterpret_cast<uintptr_t>(mem) | (static_cast<uintptr_t>(ldm) * sizeof(DataT)))
+                          % VecBytes)
+                         == 0;
+#pragma unroll
+            for(uint32_t atom = 0; atom < Geometry::Atoms; ++atom)
+            {
+                if(atom < atomBegin || atom >= atomEnd)
+                    continue;
+#pragma unroll
+                for(uint32_t i = 0; i < Geometry::AtomElems; i += Run)
+                {
+                    uint32_t row, col;
+                    Geometry::coord(lane, atom, i, row, col);
+                    DataT* r = regs + atom * Geometry::AtomElems + i;
+                    if constexpr(contiguous)
+                    {
+                        const size_t off = ColMajorMem ? static_cast<size_t>(col) * ldm + row
+                                                       : static_cast<size_t>(row) * ldm + col;
+                        if(vec_ok)
+                        {
+                            // staged through a correctly aligned temporary: the fragment itself is
+                            // only 4-byte aligned
+                            using V = typename RawVec<VecBytes>::type;
+                            V      tmp;
+                            DataT* tp = reinterpret_cast<DataT*>(&tmp);
+                            if constexpr(IsLoad)
+                            {
+                                tmp = *reinterpret_cast<const V*>(mem + off);
+#pragma unroll
+                                for(uint32_t j = 0; j < Run; ++j)
+                                    r[j] = tp[j];
+                            }
+                            else
+                            {
+#pragma unroll
+                                for(uint32_t j = 0; j < Run; ++j)
+                                    tp[j] = r[j];
+                                *reinterpret_cast<V*>(mem + off) = tmp;
+                            }
+                        }
+                        else
+                        {
+#pragma unroll
+                            for(uint32_t j = 0; j < Run; ++j)
+                            {
+                                if constexpr(IsLoad)
+                                    r[j] = mem[off + j];
+                                else
+                                    mem[off + j] = r[j];
+                            }
+                        }
+                    }
+                    else
+                    {
+#pragma unroll
+                        for(uint32_t j = 0; j < Run; ++j)
+                        {
+                            uint32_t rr, cc;
+                            Geometry::coord(lane, atom, i + j, rr, cc);
+                            const size_t off = ColMajorMem ? static_cast<size_t>(cc) * ldm + rr
+                                                           : static_cast<size_t>(rr) * ldm + cc;
+                            if constexpr(IsLoad)
+                                r[j] = mem[off];
+                            else
+                                mem[off] = r[j];
+                        }
+                    }
+                }
+            }
+        }
+    } // namespace detail
+
+    // ------------------------------------------------------------------------------------------
+    // load_matrix_sync  (reference: rocwmma.hpp:235-253, rocwmma_impl.hpp:225-264)
+    // ------------------------------------------------------------------------------------------
+    template <typename MatrixT, uint32_t BlockM, uint32_t BlockN, uint32_t BlockK, typename DataT,
+              typename DataLayoutT>
+    ROCWMMA_DEVICE inline void load_matrix_sync(fragment<MatrixT, BlockM, BlockN, BlockK, DataT, DataLayoutT>& frag,
+                                                const DataT* data, uint32_t ldm)
+    {
+        static_assert(!std::is_same<DataLayoutT, void>::value,
+                      "Must provide layout information. Either statically assign data layout in "
+                      "fragment declaration or use the run-time function overload.");
+        using G = typename fragment<MatrixT, BlockM, BlockN, BlockK, DataT, DataLayoutT>::Geometry;
+        detail::move_atoms<true, std::is_same<DataLayoutT, col_major>::value, G, DataT>(
+            frag.x, const_cast<DataT*>(data), ldm, 0u, G::Atoms);
+    }
+
+    template <typename MatrixT, uint32_t BlockM, uint32_t BlockN, uint32_t BlockK, typename DataT>
+    ROCWMMA_DEVICE inline void load_matrix_sync(fragment<MatrixT, BlockM, BlockN, BlockK, DataT>& frag,
+                                                const DataT* data, uint32_t ldm, layout_t layout)
+    {
+        using G = typename fragment<MatrixT, BlockM, BlockN, BlockK, DataT>::Geometry;
+        if(layout == layout_t::mem_row_major)
+            detail::move_atoms<true, false, G, DataT>(frag.x, const_cast<DataT*>(data), ldm, 0u, G::Atoms);
+        else
+            detail::move_atoms<true, true, G, DataT>(frag.x, const_cast<DataT*>(data), ldm, 0u, G::Atoms);
+    }
+
+    // ------------------------------------------------------------------------------------------
+    // store_matrix_sync  (reference: rocwmma.hpp:269-288, rocwmma_impl.hpp:272-312)
+    // Writes exactly the BlockHeight x BlockWidth block and nothing around it.
+    // ------------------------------------------------------------------------------------------
+    template <typename MatrixT, uint32_t BlockM, uint32_t BlockN, uint32_t BlockK, typename DataT,
+              typename DataLayoutT>
+    ROCWMMA_DEVICE inline void
+        store_matrix_sync(DataT* data, fragment<MatrixT, BlockM, BlockN, BlockK, DataT, DataLayoutT> const& frag,
+                          uint32_t ldm)
+    {
+        static_assert(!std::is_same<DataLayoutT, void>::value,
+                      "Must provide data layout. Either statically assign data layout in "
+                      "fragment declaration or use the run-time function overload.");
+        using G = typename fragment<MatrixT, BlockM, BlockN, BlockK, DataT, DataLayoutT>::Geometry;
+        detail::move_atoms<false, std::is_same<DataLayoutT, col_major>::value, G, DataT>(
+            const_cast<DataT*>(frag.x), data, ldm, 0u, G::Atoms);
+    }
+
+    template <typename MatrixT, uint32_t BlockM, uint32_t BlockN, uint32_t BlockK, typename DataT>
+    ROCWMMA_DEVICE inline void store_matrix_sync(DataT* data,
+                                                 fragment<MatrixT, BlockM, BlockN, BlockK, DataT> const& frag,
+                                                 uint32_t ldm, layout_t layout)
+    {
+        using G = typename fragment<MatrixT, BlockM, BlockN, BlockK, DataT>::Geometry;
+        if(layout == layout_t::mem_row_major)
+            detail::move_atoms<false, false, G, DataT>(const_cast<DataT*>(frag.x), data, ldm, 0u, G::Atoms);
+        else
+            detail::move_atoms<false, true, G, DataT>(const_cast<DataT*>(frag.x), data, ldm, 0u, G::Atoms);
+    }
+
+    // ------------------------------------------------------------------------------------------
+    // mma_sync  (reference: rocwmma.hpp:309-313, rocwmma_impl.hpp:323-364)
+    // d = a x b + c over the whole BlockK; c may alias d.  fp16 compute (ComputeT = float16_t)
+    // accumulates in fp32 and rounds to fp16 once per call, as the reference's MFMA path does
+    // (internal/mfma_impl.hpp:82-114).
+    // ------------------------------------------------------------------------------------------
+    namespace detail
+    {
+        template <typename InputT, typename ComputeT>
+        struct MmaAtomOp;
+
+        template <typename InputT>
+        struct MmaF16Common
+        {
+            using AccT = float;
+            static constexpr uint32_t AElems = 8, BElems = 8;
+            ROCWMMA_DEVICE static inline void exec(float (&acc)[8], const InputT* a, const InputT* b)
+            {
+                mma_atom_f16_f32(acc, *reinterpret_cast<const uint32_t(*)[4]>(a),
+                                 *reinterpret_cast<const uint32_t(*)[4]>(b));
+            }
+        };
+        template <>
+        struct MmaAtomOp<float16_t, float32_t> : MmaF16Common<float16_t>
+        {
+        };
+        template <>
+        struct MmaAtomOp<float16_t, float16_t> : MmaF16Common<float16_t>
+        {
+        };
+        template <>
+        struct MmaAtomOp<hfloat16_t, float32_t> : MmaF16Common<hfloat16_t>
+        {
+        };
+        template <>
+        struct MmaAtomOp<hfloat16_t, hfloat16_t> : MmaF16Common<hfloat16_t>
+        {
+        };
+        template <>
+        struct MmaAtomOp<int8_t, int32_t>
+        {
+            using AccT = int32_t;
+            ROCWMMA_DEVICE static inline void exec(int32_t (&acc)[8], const int8_t* a, const int8_t* b)
+            {
+                mma_atom_i8_i32(acc, *reinterpret_cast<const uint32_t(*)[2]>(a),
+                                *reinterpret_cast<const uint32_t(*)[2]>(b));
+            }
+        };
+        template <>
+        struct MmaAtomOp<float64_t, float64_t>
+        {
+            using AccT = double;
+            ROCWMMA_DEVICE static inline void exec(double (&acc)[8], const double* a, const double* b)
+            {
+                mma_atom_f64(acc, *reinterpret_cast<const double(*)[2]>(a),
+                             *reinterpret_cast<const double(*)[2]>(b));
+            }
+        };
+        template <>
+        struct MmaAtomOp<float32_t, float32_t>
+        {
+            using AccT = float;
+            ROCWMMA_DEVICE static inline void exec(float (&acc)[8], const float* a, const float* b)
+            {
+                mma_atom_f32(acc, *reinterpret_cast<const float(*)[4]>(a),
+                             *reinterpret_cast<const float(*)[4]>(b));
+            }
+        };
+    } // namespace detail
+
+    template <uint32_t BlockM, uint32_t BlockN, uint32_t BlockK, typename InputT, typename ComputeT,
+              typename LayoutA, typename LayoutB, typename LayoutC, typename LayoutD>
+    ROCWMMA_DEVICE inline void mma_sync(fragment<accumulator, BlockM, BlockN, BlockK, ComputeT, LayoutD>&       d,
+                                        fragment<matrix_a, BlockM, BlockN, BlockK, InputT, LayoutA> const&      a,
+                                        fragment<matrix_b, BlockM, BlockN, BlockK, InputT, LayoutB> const&      b,
+                                        fragment<accumulator, BlockM, BlockN, BlockK, ComputeT, LayoutC> const& c)
+    {
+        using Op = detail::MmaAtomOp<InputT, ComputeT>;
+        using AccT = typename Op::AccT;
+        using GA = detail::FragGeometry<matrix_a, BlockM, BlockN, BlockK, InputT>;
+        using GB = detail::FragGeometry<matrix_b, BlockM, BlockN, BlockK, InputT>;
+        using GC = detail::FragGeometry<accumulator, BlockM, BlockN, BlockK, ComputeT>;
+        static_assert(GA::AtomsK == GB::AtomsK, "A and B K dimensions must match");
+
+#pragma unroll
+        for(uint32_t mi = 0; mi < GC::AtomsM; ++mi)
+        {
+#pragma unroll
+            for(uint32_t ni = 0; ni < GC::AtomsN; ++ni)
+            {
+                const uint32_t cbase = (mi * GC::AtomsN + ni) * 8u;
+                AccT           acc[8];
+#pragma unroll
+                for(uint32_t e = 0; e < 8; ++e)
+                    acc[e] = static_cast<AccT>(c.x[cbase + e]);
+#pragma unroll
+                for(uint32_t ki = 0; ki < GA::AtomsK; ++ki)
+                    Op::exec(acc, a.x + (mi * GA::AtomsK + ki) * GA::AtomElems,
+                             b.x + (ni * GB::AtomsK + ki) * GB::AtomElems);
+#pragma unroll
+                for(uint32_t e = 0; e < 8; ++e)
+                    d.x[cbase + e] = static_cast<ComputeT>(acc[e]);
+            }
+        }
+    }
+
+    // ------------------------------------------------------------------------------------------
+    // synchronize_workgroup  (reference: rocwmma.hpp:316, rocwmma_impl.hpp:366-369)
+    // ------------------------------------------------------------------------------------------
+    ROCWMMA_DEVICE inline void synchronize_workgroup()
+    {
+        __syncthreads();
+    }
+} // namespace rocwmma
+
+#endif // ROCWMMA_B200_API_HPP

@@ -1,12 +1,266 @@
-// Placeholder until the fragment-API sample kernels are added.
+// GEMM kernels written against this repository's rocWMMA-compatible fragment API
+// (<rocwmma/rocwmma.hpp>, <rocwmma/rocwmma_coop.hpp>, <rocwmma/rocwmma_transforms.hpp>), i.e. the
+// way a rocWMMA user writes kernels.  They exist to prove the device API end to end:
+//
+//   simple_hgemm         the naive "one 16x16 output block per wave" GEMM of
+//                        samples/simple_hgemm.cpp:81-139 (A row major, B column major, C/D row major,
+//                        fp32 accumulation, D = alpha*A*B + beta*C computed element-wise on fragments).
+//   perf_hgemm_fragment  the cooperative / shared-memory double-buffered pipeline of
+//                        samples/perf_hgemm.cpp:515-711 with the layouts that sample ships with
+//                        (A column major, B row major, C/D row major, LDS column major).
+//
+// The fast GEMM of this library is the tcgen05 kernel (gemm_tc05.cu); these two go through
+// warp-level mma.sync fragments like any user kernel would.
 #include "common.cuh"
-extern "C" int b200wmma_simple_hgemm(uint32_t, uint32_t, uint32_t, const void*, const void*, const void*, void*,
-                                     uint32_t, uint32_t, uint32_t, uint32_t, float, float, int, void*)
+
+#include <rocwmma/rocwmma.hpp>
+#include <rocwmma/rocwmma_coop.hpp>
+#include <rocwmma/rocwmma_transforms.hpp>
+
+namespace b200wmma
 {
-    return b200wmma::set_error(B200WMMA_ERR_UNSUPPORTED, "simple_hgemm: not built yet");
+    namespace fragk
+    {
+        using namespace rocwmma;
+
+        // --------------------------------- simple_hgemm ---------------------------------------
+        constexpr uint32_t SB_M = 16, SB_N = 16, SB_K = 16;
+        constexpr uint32_t S_TBLOCK_X = 4 * Constants::AMDGCN_WAVE_SIZE, S_TBLOCK_Y = 4;
+
+        template <typename OutT>
+        ROCWMMA_KERNEL void simple_hgemm_kernel(uint32_t m, uint32_t n, uint32_t k, float16_t const* a,
+                                                float16_t const* b, OutT const* c, OutT* d, uint32_t lda,
+                                                uint32_t ldb, uint32_t ldc, uint32_t ldd, float32_t alpha,
+                                                float32_t beta)
+        {
+            fragment<matrix_a, SB_M, SB_N, SB_K, float16_t, row_major> fragA;
+            fragment<matrix_b, SB_M, SB_N, SB_K, float16_t, col_major> fragB;
+            fragment<accumulator, SB_M, SB_N, SB_K, OutT>              fragC; // layout given at run time
+            fragment<accumulator, SB_M, SB_N, SB_K, float32_t>         fragAcc;
+            fill_fragment(fragAcc, 0.0f);
+
+            // one output block per wave: wave grid position -> block position
+            const uint32_t waveRow = (blockIdx.x * blockDim.x + threadIdx.x) / Constants::AMDGCN_WAVE_SIZE;
+            const uint32_t waveCol = blockIdx.y * blockDim.y + threadIdx.y;
+            const uint32_t row0 = waveRow * SB_M, col0 = waveCol * SB_N;
+            if(row0 >= m || col0 >= n)
+                return;
+
+            for(uint32_t kk = 0; kk < k; kk += SB_K)
+            {
+                load_matrix_sync(fragA, a + (static_cast<size_t>(row0) * lda + kk), lda);
+                load_matrix_sync(fragB, b + (static_cast<size_t>(col0) * ldb + kk), ldb);
+                mma_sync(fragAcc, fragA, fragB, fragAcc);
+            }
+            load_matrix_sync(fragC, c + (static_cast<size_t>(row0) * ldc + col0), ldc, mem_row_major);
+            for(uint32_t i = 0; i < fragC.num_elements; ++i)
+                fragC.x[i] = alpha * fragAcc.x[i] + beta * fragC.x[i];
+            store_matrix_sync(d + (static_cast<size_t>(row0) * ldd + col0), fragC, ldd, mem_row_major);
+        }
+
+        // ------------------------------ perf_hgemm on fragments --------------------------------
+        // 8 warps as 4 (x) by 2 (y); each warp owns a 32 x 64 tile = 2 x 4 blocks of 16 x 16;
+        // the thread block owns a 128 x 128 macro tile and walks K in steps of 16.
+        constexpr uint32_t P_M = 16, P_N = 16, P_K = 16;
+        constexpr uint32_t P_BLOCKS_X = 2, P_BLOCKS_Y = 4;
+        constexpr uint32_t P_TBLOCK_X = 128, P_TBLOCK_Y = 2;
+        constexpr uint32_t P_WARPS_X = P_TBLOCK_X / Constants::AMDGCN_WAVE_SIZE, P_WARPS_Y = P_TBLOCK_Y;
+        constexpr uint32_t P_WARP_TILE_X = P_BLOCKS_X * P_M, P_WARP_TILE_Y = P_BLOCKS_Y * P_N;
+        constexpr uint32_t P_MACRO_X = P_WARPS_X * P_WARP_TILE_X, P_MACRO_Y = P_WARPS_Y * P_WARP_TILE_Y;
+        constexpr uint32_t P_WARPS = P_WARPS_X * P_WARPS_Y;
+
+        using PIn = float16_t;
+        using POut = float16_t;
+        using PCmp = float32_t;
+        using PLayoutA = col_major;
+        using PLayoutB = row_major;
+        using PLayoutC = row_major;
+        using PLayoutLds = col_major;
+
+        using MmaA   = fragment<matrix_a, P_M, P_N, P_K, PIn, PLayoutA>;
+        using MmaB   = fragment<matrix_b, P_M, P_N, P_K, PIn, PLayoutB>;
+        using MmaC   = fragment<accumulator, P_M, P_N, P_K, POut, PLayoutC>;
+        using MmaAcc = fragment<accumulator, P_M, P_N, P_K, PCmp>;
+        // whole-macro-tile K slabs read cooperatively from global memory
+        using GlobalA = fragment<matrix_a, P_MACRO_X, P_N, P_K, PIn, PLayoutA>;
+        using GlobalB = fragment<matrix_b, P_M, P_MACRO_Y, P_K, PIn, PLayoutB>;
+        // shared memory holds A and B^T stacked, both as "matrix_a"-shaped column-major blocks
+        using LdsWriteA = ApplyDataLayout_t<GlobalA, PLayoutLds>;
+        using LdsWriteB = ApplyDataLayout_t<ApplyTranspose_t<GlobalB>, PLayoutLds>;
+        using LdsReadA  = ApplyDataLayout_t<MmaA, PLayoutLds>;
+        using LdsReadB  = ApplyDataLayout_t<ApplyTranspose_t<MmaB>, PLayoutLds>;
+
+        constexpr uint32_t P_LDS_HEIGHT = GetIOShape_t<LdsWriteA>::BlockHeight + GetIOShape_t<LdsWriteB>::BlockHeight;
+        constexpr uint32_t P_LDS_WIDTH  = P_K;
+        constexpr uint32_t P_LDS_ELEMS  = P_LDS_HEIGHT * P_LDS_WIDTH;
+        constexpr uint32_t P_LDS_LD     = std::is_same<PLayoutLds, row_major>::value ? P_LDS_WIDTH : P_LDS_HEIGHT;
+
+        ROCWMMA_KERNEL void __launch_bounds__(P_TBLOCK_X* P_TBLOCK_Y)
+            perf_hgemm_fragment_kernel(uint32_t m, uint32_t n, uint32_t k, PIn const* a, PIn const* b,
+                                       POut const* c, POut* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
+                                       uint32_t ldd, PCmp alpha, PCmp beta)
+        {
+            extern __shared__ __align__(16) unsigned char lds_raw[];
+            PIn* ldsLo = reinterpret_cast<PIn*>(lds_raw);
+            PIn* ldsHi = ldsLo + P_LDS_ELEMS;
+
+            const auto warpCoord  = make_coord2d(threadIdx.x / Constants::AMDGCN_WAVE_SIZE, threadIdx.y);
+            const auto warpOffset = warpCoord * make_coord2d(P_WARP_TILE_X, P_WARP_TILE_Y);
+            const auto macroCoord = make_coord2d(blockIdx.x, blockIdx.y) * make_coord2d(P_MACRO_X, P_MACRO_Y);
+            const auto tileCoord  = macroCoord + warpOffset;
+            if(get<0>(tileCoord) + P_WARP_TILE_X > m || get<1>(tileCoord) + P_WARP_TILE_Y > n)
+                return; // host guarantees whole macro tiles; nothing to synchronise with in that case
+            const uint32_t warpIndex = get<0>(warpCoord) * P_WARPS_Y + get<1>(warpCoord);
+
+            using MapGA = GetDataLayout_t<GlobalA>;
+            using MapGB = GetDataLayout_t<GlobalB>;
+            using MapLA = GetDataLayout_t<LdsWriteA>;
+            using MapLB = GetDataLayout_t<LdsWriteB>;
+            size_t       offA  = MapGA::fromMatrixCoord(make_coord2d(get<0>(macroCoord), 0u), lda);
+            size_t       offB  = MapGB::fromMatrixCoord(make_coord2d(0u, get<1>(macroCoord)), ldb);
+            const size_t stepA = MapGA::fromMatrixCoord(make_coord2d(0u, P_K), lda);
+            const size_t stepB = MapGB::fromMatrixCoord(make_coord2d(P_K, 0u), ldb);
+
+            const uint32_t ldsWriteA = 0u;
+            const uint32_t ldsWriteB = MapLA::fromMatrixCoord(make_coord2d(GetIOShape_t<LdsWriteA>::BlockHeight, 0u), P_LDS_LD);
+            const uint32_t ldsReadA  = ldsWriteA + MapLA::fromMatrixCoord(make_coord2d(get<0>(warpOffset), 0u), P_LDS_LD);
+            const uint32_t ldsReadB  = ldsWriteB + MapLB::fromMatrixCoord(make_coord2d(get<1>(warpOffset), 0u), P_LDS_LD);
+            const uint32_t blockStepA = GetDataLayout_t<LdsReadA>::fromMatrixCoord(make_coord2d(GetIOShape_t<LdsReadA>::BlockHeight, 0u), P_LDS_LD);
+            const uint32_t blockStepB = GetDataLayout_t<LdsReadB>::fromMatrixCoord(make_coord2d(GetIOShape_t<LdsReadB>::BlockHeight, 0u), P_LDS_LD);
+
+            GlobalA grA;
+            GlobalB grB;
+            auto globalRead = [&]() {
+                load_matrix_coop_sync<P_WARPS>(grA, a + offA, lda, warpIndex);
+                load_matrix_coop_sync<P_WARPS>(grB, b + offB, ldb, warpIndex);
+                offA += stepA;
+                offB += stepB;
+            };
+            auto ldsWrite = [&](PIn* lds) {
+                store_matrix_coop_sync<P_WARPS>(lds + ldsWriteA, applyDataLayout<PLayoutLds, P_WARPS>(grA), P_LDS_LD, warpIndex);
+                store_matrix_coop_sync<P_WARPS>(lds + ldsWriteB, applyDataLayout<PLayoutLds, P_WARPS>(applyTranspose(grB)),
+                                                P_LDS_LD, warpIndex);
+            };
+
+            MmaAcc acc[P_BLOCKS_X][P_BLOCKS_Y];
+#pragma unroll
+            for(uint32_t i = 0; i < P_BLOCKS_X; ++i)
+#pragma unroll
+                for(uint32_t j = 0; j < P_BLOCKS_Y; ++j)
+                    fill_fragment(acc[i][j], 0.0f);
+
+            auto ldsStep = [&](PIn const* lds) {
+                MmaA fa[P_BLOCKS_X];
+                MmaB fb[P_BLOCKS_Y];
+#pragma unroll
+                for(uint32_t i = 0; i < P_BLOCKS_X; ++i)
+                {
+                    LdsReadA tmp;
+                    load_matrix_sync(tmp, lds + ldsReadA + i * blockStepA, P_LDS_LD);
+                    fa[i] = applyDataLayout<PLayoutA>(tmp);
+                }
+#pragma unroll
+                for(uint32_t j = 0; j < P_BLOCKS_Y; ++j)
+                {
+                    LdsReadB tmp;
+                    load_matrix_sync(tmp, lds + ldsReadB + j * blockStepB, P_LDS_LD);
+                    fb[j] = applyDataLayout<PLayoutB>(applyTranspose(tmp));
+                }
+#pragma unroll
+                for(uint32_t i = 0; i < P_BLOCKS_X; ++i)
+#pragma unroll
+                    for(uint32_t j = 0; j < P_BLOCKS_Y; ++j)
+                        mma_sync(acc[i][j], fa[i], fb[j], acc[i][j]);
+            };
+
+            // prologue: first K slab through registers into the low buffer
+            globalRead();
+            ldsWrite(ldsLo);
+            synchronize_workgroup();
+
+            for(uint32_t kk = P_K; kk < k; kk += P_K)
+            {
+                globalRead(); // prefetch slab kk while slab kk - P_K is multiplied
+                ldsStep(ldsLo);
+                ldsWrite(ldsHi);
+                synchronize_workgroup();
+                PIn* t = ldsLo;
+                ldsLo  = ldsHi;
+                ldsHi  = t;
+            }
+            ldsStep(ldsLo);
+
+            using MapC = GetDataLayout_t<MmaC>;
+            const size_t   cBase = MapC::fromMatrixCoord(tileCoord, ldc), dBase = MapC::fromMatrixCoord(tileCoord, ldd);
+#pragma unroll
+            for(uint32_t i = 0; i < P_BLOCKS_X; ++i)
+#pragma unroll
+                for(uint32_t j = 0; j < P_BLOCKS_Y; ++j)
+                {
+                    MmaC fc;
+                    load_matrix_sync(fc, c + cBase + MapC::fromMatrixCoord(make_coord2d(i * P_M, j * P_N), ldc), ldc);
+                    for(uint32_t e = 0; e < fc.num_elements; ++e)
+                        fc.x[e] = static_cast<POut>(alpha * acc[i][j].x[e] + beta * static_cast<PCmp>(fc.x[e]));
+                    store_matrix_sync(d + dBase + MapC::fromMatrixCoord(make_coord2d(i * P_M, j * P_N), ldd), fc, ldd);
+                }
+        }
+    } // namespace fragk
+} // namespace b200wmma
+
+using namespace b200wmma;
+
+extern "C" int b200wmma_simple_hgemm(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b,
+                                     const void* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
+                                     uint32_t ldd, float alpha, float beta, int out_type, void* stream)
+{
+    clear_error();
+    B200_REQUIRE(a && b && c && d, B200WMMA_ERR_INVALID_ARG, "simple_hgemm: a, b, c, d must be non-null");
+    B200_REQUIRE(m && n && k, B200WMMA_ERR_INVALID_ARG, "simple_hgemm: m, n, k must be non-zero");
+    // same size rule as the sample's host check (samples/simple_hgemm.cpp:144-149)
+    B200_REQUIRE(m % fragk::SB_M == 0 && n % fragk::SB_N == 0 && k % fragk::SB_K == 0, B200WMMA_ERR_UNSUPPORTED,
+                 "simple_hgemm: m, n, k must be multiples of 16");
+    B200_REQUIRE(out_type == B200WMMA_OUT_F16 || out_type == B200WMMA_OUT_F32, B200WMMA_ERR_INVALID_ARG,
+                 "simple_hgemm: out_type must be 0 (f16) or 1 (f32)");
+    B200_REQUIRE(lda >= k && ldb >= k && ldc >= n && ldd >= n, B200WMMA_ERR_INVALID_ARG,
+                 "simple_hgemm: leading dimension too small");
+    if(int e = require_sm100())
+        return e;
+    const dim3 block(fragk::S_TBLOCK_X, fragk::S_TBLOCK_Y);
+    const dim3 grid(ceil_div(m, fragk::SB_M * fragk::S_TBLOCK_X / rocwmma::Constants::AMDGCN_WAVE_SIZE),
+                    ceil_div(n, fragk::SB_N * fragk::S_TBLOCK_Y));
+    auto       A = static_cast<const rocwmma::float16_t*>(a);
+    auto       B = static_cast<const rocwmma::float16_t*>(b);
+    if(out_type == B200WMMA_OUT_F16)
+        fragk::simple_hgemm_kernel<rocwmma::float16_t><<<grid, block, 0, as_stream(stream)>>>(
+            m, n, k, A, B, static_cast<const rocwmma::float16_t*>(c), static_cast<rocwmma::float16_t*>(d), lda, ldb,
+            ldc, ldd, alpha, beta);
+    else
+        fragk::simple_hgemm_kernel<float><<<grid, block, 0, as_stream(stream)>>>(
+            m, n, k, A, B, static_cast<const float*>(c), static_cast<float*>(d), lda, ldb, ldc, ldd, alpha, beta);
+    B200_CHECK_CUDA(cudaGetLastError());
+    return B200WMMA_OK;
 }
-extern "C" int b200wmma_perf_hgemm_fragment(uint32_t, uint32_t, uint32_t, const void*, const void*, const void*,
-                                            void*, uint32_t, uint32_t, uint32_t, uint32_t, float, float, void*)
+
+extern "C" int b200wmma_perf_hgemm_fragment(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b,
+                                            const void* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
+                                            uint32_t ldd, float alpha, float beta, void* stream)
 {
-    return b200wmma::set_error(B200WMMA_ERR_UNSUPPORTED, "perf_hgemm_fragment: not built yet");
+    clear_error();
+    B200_REQUIRE(a && b && c && d, B200WMMA_ERR_INVALID_ARG, "perf_hgemm_fragment: a, b, c, d must be non-null");
+    B200_REQUIRE(m && n && k, B200WMMA_ERR_INVALID_ARG, "perf_hgemm_fragment: m, n, k must be non-zero");
+    // the sample's own size rule (samples/perf_hgemm.cpp:757-762): whole macro tiles, whole K steps
+    B200_REQUIRE(m % fragk::P_MACRO_X == 0 && n % fragk::P_MACRO_Y == 0 && k % fragk::P_K == 0,
+                 B200WMMA_ERR_UNSUPPORTED, "perf_hgemm_fragment: m, n must be multiples of 128 and k of 16");
+    B200_REQUIRE(lda >= m && ldb >= n && ldc >= n && ldd >= n, B200WMMA_ERR_INVALID_ARG,
+                 "perf_hgemm_fragment: leading dimension too small (A is column major, B row major)");
+    if(int e = require_sm100())
+        return e;
+    const dim3   block(fragk::P_TBLOCK_X, fragk::P_TBLOCK_Y);
+    const dim3   grid(m / fragk::P_MACRO_X, n / fragk::P_MACRO_Y);
+    const size_t lds = 2 * fragk::P_LDS_ELEMS * sizeof(fragk::PIn);
+    fragk::perf_hgemm_fragment_kernel<<<grid, block, lds, as_stream(stream)>>>(
+        m, n, k, static_cast<const fragk::PIn*>(a), static_cast<const fragk::PIn*>(b),
+        static_cast<const fragk::POut*>(c), static_cast<fragk::POut*>(d), lda, ldb, ldc, ldd, alpha, beta);
+    B200_CHECK_CUDA(cudaGetLastError());
+    return B200WMMA_OK;
 }
