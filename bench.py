@@ -37,7 +37,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
 # (None where no capture exists yet).
 NCU_TRAFFIC_BYTES = {
-    "gemm_f16": None,
+    "gemm_f16": 1.343e9,  # profiles/gemm_tc05_f16_8192.md: 1.215 GB read + 127.7 MB written per launch
 }
 
 
@@ -667,7 +667,11 @@ def run_gpu_arm(args, wl):
         if wl.bound == "tensor":
             peak = peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])
             if wl.dtype == "i8":
-                peak_note = "2x the bf16 figure is the dense int8 rate; fraction quoted against the bf16 TFLOP/s as measured"
+                peak *= 2.0  # the dense int8 tensor rate is twice the 16-bit rate; no int8 figure is measured
+                peak_note = "2 x cuBLAS bf16 8192^3 burst, standing in for the dense int8 rate"
+            elif wl.dtype == "f64":
+                peak = 40.0
+                peak_note = "nominal B200 fp64 tensor rate; no measured figure"
             else:
                 peak_note = "cuBLAS bf16 8192^3 burst"
             achieved = wl.work_local / (ms_step * 1e-3) / 1e12

@@ -1,0 +1,6 @@
+// Usage: simple_dgemv [m n]   (default 32768 x 32768, row-major A, alpha = 1.5, beta = 0.5)
+#include "simple_gemv.hpp"
+int main(int argc, char** argv)
+{
+    return gemv_sample<double>("simple_dgemv", argc, argv, 1e-12, b200wmma_gemv_f64);
+}
