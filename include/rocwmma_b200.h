@@ -114,6 +114,29 @@ int b200wmma_gemm_i8_sp24(uint32_t m, uint32_t n, uint32_t k,
                           int32_t alpha, int32_t beta,
                           void* workspace, size_t workspace_bytes, void* stream);
 
+/* No counterpart in the reference.  Same computation and arguments as b200wmma_gemm_i8_sp24 minus the
+ * workspace: for callers that cannot provide scratch memory - code that launches through the plain
+ * 13-argument GEMM kernel signature (which has no slot for a workspace), or that runs in a process whose
+ * device memory is entirely owned by an arena set up elsewhere, so that neither it nor this library may
+ * call the CUDA allocator.  The expanded copy of A is kept in an array of
+ * B200WMMA_SP24_STATIC_SCRATCH_BYTES bytes built into the library (each GPU that loads the library holds
+ * it until the process ends); the call allocates nothing.
+ *   - Problems with m * k above B200WMMA_SP24_STATIC_SCRATCH_BYTES are refused with
+ *     B200WMMA_ERR_UNSUPPORTED; use b200wmma_gemm_i8_sp24 for those.
+ *   - The first call on each device looks up the array's device address (once, cached afterwards);
+ *     make that first call before starting any stream capture.
+ *   - All calls on a device use the same array.  Calls whose GPU work can overlap (different streams,
+ *     or different host threads without ordering between them) overwrite each other's data: keep
+ *     them ordered on one stream or separate them with events.  Nothing has to be cleared between
+ *     calls; each call rewrites every byte it reads. */
+#define B200WMMA_SP24_STATIC_SCRATCH_BYTES (16u << 20)
+int b200wmma_gemm_i8_sp24_static(uint32_t m, uint32_t n, uint32_t k,
+                                 const int8_t* a_vals, const uint8_t* a_meta,
+                                 const int8_t* b, const int32_t* c, int32_t* d,
+                                 uint32_t lda_vals, uint32_t ld_meta, uint32_t ldb,
+                                 uint32_t ldc, uint32_t ldd,
+                                 int32_t alpha, int32_t beta, void* stream);
+
 size_t b200wmma_gemm_i4_workspace_bytes(uint32_t m, uint32_t n, uint32_t k);
 int b200wmma_gemm_i4(uint32_t m, uint32_t n, uint32_t k,
                      const uint8_t* a_packed, const uint8_t* b_packed,

@@ -10,6 +10,8 @@
 // GEMM on the expanded operands.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace b200wmma
 {
     namespace i8var
@@ -168,4 +170,81 @@ extern "C" int b200wmma_gemm_i4(uint32_t m, uint32_t n, uint32_t k, const uint8_
     B200_CHECK_CUDA(cudaGetLastError());
     return launch_gemm_tc05_i8(m, n, k, dense_a, dense_b, c, d, k, k, ldc, ldd, alpha, beta,
                                as_stream(stream));
+}
+
+// ---------------------------------------------------------------------------------------------
+// 2:4-sparse int8 GEMM for callers that have no way to hand over scratch memory.
+//
+// The kernel signature rocWMMA-style harnesses launch is (m, n, k, a, b, c, d, lda, ldb, ldc, ldd,
+// alpha, beta): inputs, outputs and nothing else.  A harness built around that signature, or an
+// application that gave all device memory to its own arena at start-up, can neither pass a
+// workspace pointer nor call cudaMalloc on the library's behalf.  For those callers the expanded
+// copy of A lives in a fixed array inside this library instead of in caller memory.
+// ---------------------------------------------------------------------------------------------
+namespace b200wmma
+{
+    namespace i8var
+    {
+        // Resident in every GPU that loads the library, from load until the process exits.
+        static __device__ __align__(256) unsigned char g_sp24_static_scratch[B200WMMA_SP24_STATIC_SCRATCH_BYTES];
+
+        // Device address of the array for the current device.  In host code the array's name is only a
+        // handle for the runtime, never an address a kernel may use: it is resolved once per device,
+        // with that device current, and cached.
+        static int static_scratch_address(int8_t** out)
+        {
+            static int8_t*    cache[64];
+            static std::mutex mu;
+            int               dev = 0;
+            B200_CHECK_CUDA(cudaGetDevice(&dev));
+            B200_REQUIRE(dev >= 0 && dev < 64, B200WMMA_ERR_UNSUPPORTED, "device index %d out of range", dev);
+            std::lock_guard<std::mutex> lock(mu);
+            if(!cache[dev])
+            {
+                void* p = nullptr;
+                B200_CHECK_CUDA(cudaGetSymbolAddress(&p, g_sp24_static_scratch));
+                B200_REQUIRE(p != nullptr && aligned16(p), B200WMMA_ERR_CUDA,
+                             "static scratch array resolved to an unusable address");
+                cache[dev] = static_cast<int8_t*>(p);
+            }
+            *out = cache[dev];
+            return B200WMMA_OK;
+        }
+    } // namespace i8var
+} // namespace b200wmma
+
+extern "C" int b200wmma_gemm_i8_sp24_static(uint32_t m, uint32_t n, uint32_t k, const int8_t* a_vals,
+                                            const uint8_t* a_meta, const int8_t* b, const int32_t* c,
+                                            int32_t* d, uint32_t lda_vals, uint32_t ld_meta, uint32_t ldb,
+                                            uint32_t ldc, uint32_t ldd, int32_t alpha, int32_t beta,
+                                            void* stream)
+{
+    clear_error();
+    B200_REQUIRE(m && n && k, B200WMMA_ERR_INVALID_ARG, "gemm_i8_sp24_static: m, n, k must be non-zero");
+    B200_REQUIRE(a_vals && a_meta && b && d, B200WMMA_ERR_INVALID_ARG,
+                 "gemm_i8_sp24_static: a_vals, a_meta, b, d must be non-null");
+    B200_REQUIRE(k % 32 == 0, B200WMMA_ERR_UNSUPPORTED, "gemm_i8_sp24_static: k must be a multiple of 32");
+    B200_REQUIRE(static_cast<uint64_t>(m) * k <= B200WMMA_SP24_STATIC_SCRATCH_BYTES, B200WMMA_ERR_UNSUPPORTED,
+                 "gemm_i8_sp24_static: m * k = %llu exceeds the built-in scratch of %llu bytes; "
+                 "use b200wmma_gemm_i8_sp24 with a caller-provided workspace",
+                 static_cast<unsigned long long>(static_cast<uint64_t>(m) * k),
+                 static_cast<unsigned long long>(B200WMMA_SP24_STATIC_SCRATCH_BYTES));
+    B200_REQUIRE(lda_vals >= k / 2 && ld_meta >= k / 8, B200WMMA_ERR_INVALID_ARG,
+                 "gemm_i8_sp24_static: lda_vals / ld_meta smaller than k/2 / k/8");
+    B200_REQUIRE(aligned16(a_vals) && lda_vals % 16 == 0 && (reinterpret_cast<uintptr_t>(a_meta) & 3) == 0
+                     && ld_meta % 4 == 0,
+                 B200WMMA_ERR_ALIGNMENT,
+                 "gemm_i8_sp24_static: value rows must be 16-byte aligned, metadata rows 4-byte aligned");
+    if(int e = require_sm100())
+        return e;
+    int8_t* dense = nullptr;
+    if(int e = i8var::static_scratch_address(&dense))
+        return e;
+    // The expansion writes all m * k bytes it later reads (zeros included), so nothing left in the array
+    // by an earlier call can leak into this one and nothing needs clearing first.
+    const size_t units = static_cast<size_t>(m) * (k / 32);
+    i8var::expand_sp24_kernel<<<i8var::grid_for(units), i8var::THREADS, 0, as_stream(stream)>>>(
+        a_vals, a_meta, dense, m, k, lda_vals, ld_meta);
+    B200_CHECK_CUDA(cudaGetLastError());
+    return launch_gemm_tc05_i8(m, n, k, dense, b, c, d, k, ldb, ldc, ldd, alpha, beta, as_stream(stream));
 }
