@@ -18,8 +18,11 @@
 //   warp 2-5: epilogue - tcgen05.ld their 32-lane quadrant, alpha/beta, store D
 // Two 256-column accumulator buffers let the epilogue of tile i overlap the MMAs of tile i+1.
 // Every barrier wait is bounded (see ptx::mbar_wait_bounded).
-#include "common.cuh"
-#include "ptx_sm100.cuh"
+#include "gemm_tc05_common.cuh"
+#include "gemm_tc05_pair.cuh"
+
+#include <cstdlib>
+#include <cstring>
 
 namespace b200wmma
 {
@@ -27,7 +30,6 @@ namespace b200wmma
     {
         constexpr uint32_t BLOCK_M       = 128;
         constexpr uint32_t BLOCK_N       = 256;
-        constexpr uint32_t BLOCK_K_BYTES = 128; // one 128-byte swizzle row: 64 fp16 / 128 int8
         constexpr uint32_t STAGES        = 4;
         constexpr uint32_t A_STAGE_BYTES = BLOCK_M * BLOCK_K_BYTES; // 16 KiB
         constexpr uint32_t B_STAGE_BYTES = BLOCK_N * BLOCK_K_BYTES; // 32 KiB
@@ -36,159 +38,6 @@ namespace b200wmma
         constexpr uint32_t TMEM_COLS     = 512; // 2 accumulator buffers x 256 fp32/int32 columns
         constexpr uint32_t GROUP_M       = 16; // tile rasterisation: 16 row tiles share B slabs
         constexpr uint32_t SMEM_BYTES    = 1024 /*alignment slack*/ + STAGES * STAGE_BYTES + 256;
-        constexpr uint64_t WAIT_TIMEOUT_NS = 2000000000ull; // 2 s: far beyond any healthy wait
-
-        enum Kind : int
-        {
-            KIND_F16 = 0,
-            KIND_I8  = 1
-        };
-        enum Role : uint32_t
-        {
-            ROLE_PRODUCER = 1,
-            ROLE_MMA      = 2,
-            ROLE_EPILOGUE = 3
-        };
-
-        // tcgen05 instruction descriptor (32-bit): D format bits [4,6), A format [7,10),
-        // B format [10,13), A/B major bits 15/16 (0 = K-major), N>>3 at [17,23), M>>4 at [24,29).
-        template <int KIND>
-        __host__ __device__ constexpr uint32_t make_idesc()
-        {
-            uint32_t d = 0;
-            if(KIND == KIND_F16)
-            {
-                d |= 1u << 4; // D = F32;  A = B = F16 (format 0)
-            }
-            else
-            {
-                d |= 2u << 4; // D = S32
-                d |= 1u << 7; // A = signed 8-bit
-                d |= 1u << 10; // B = signed 8-bit
-            }
-            d |= (BLOCK_N >> 3) << 17;
-            d |= (BLOCK_M >> 4) << 24;
-            return d;
-        }
-
-        __device__ __forceinline__ void tile_coords(uint32_t  tile,
-                                                    uint32_t  tiles_m,
-                                                    uint32_t  tiles_n,
-                                                    uint32_t& m_idx,
-                                                    uint32_t& n_idx)
-        {
-            const uint32_t group_size = GROUP_M * tiles_n;
-            const uint32_t group      = tile / group_size;
-            const uint32_t first_m    = group * GROUP_M;
-            const uint32_t gm         = min(tiles_m - first_m, GROUP_M);
-            const uint32_t within     = tile - group * group_size;
-            m_idx                     = first_m + within % gm;
-            n_idx                     = within / gm;
-        }
-
-        // ---- epilogue element helpers -----------------------------------------------------
-        __device__ __forceinline__ float epi(float acc, float c, float alpha, float beta)
-        {
-            return alpha * acc + beta * c;
-        }
-        __device__ __forceinline__ int32_t epi(int32_t acc, int32_t c, int32_t alpha, int32_t beta)
-        {
-            // wrap-around int32 arithmetic, as the reference's int32 ComputeT does
-            return static_cast<int32_t>(static_cast<uint32_t>(alpha) * static_cast<uint32_t>(acc)
-                                        + static_cast<uint32_t>(beta) * static_cast<uint32_t>(c));
-        }
-
-        // One thread's 32 consecutive output columns of one row.
-        // OutT = __half: acc is fp32 bits.  OutT = float: fp32.  OutT = int32_t: int32.
-        template <typename OutT, typename ScalarT>
-        __device__ __forceinline__ void epilogue_row_chunk(const uint32_t (&v)[32],
-                                                           const OutT* __restrict__ c_row,
-                                                           OutT* __restrict__ d_row,
-                                                           uint32_t ncols, // valid columns (<= 32)
-                                                           ScalarT  alpha,
-                                                           ScalarT  beta,
-                                                           bool     read_c,
-                                                           bool     vec_ok)
-        {
-            if(ncols == 32 && vec_ok)
-            {
-                if constexpr(sizeof(OutT) == 2)
-                {
-                    // 32 halfs = 4 x 16 bytes
-#pragma unroll
-                    for(int q = 0; q < 4; ++q)
-                    {
-                        uint4 cv = make_uint4(0, 0, 0, 0);
-                        if(read_c)
-                            cv = *reinterpret_cast<const uint4*>(c_row + q * 8);
-                        const __half2* ch = reinterpret_cast<const __half2*>(&cv);
-                        uint4          ov;
-                        __half2*       oh = reinterpret_cast<__half2*>(&ov);
-#pragma unroll
-                        for(int j = 0; j < 4; ++j)
-                        {
-                            const float2 cf = __half22float2(ch[j]);
-                            const float  x0
-                                = epi(__uint_as_float(v[q * 8 + 2 * j]), cf.x, alpha, beta);
-                            const float x1
-                                = epi(__uint_as_float(v[q * 8 + 2 * j + 1]), cf.y, alpha, beta);
-                            oh[j] = __floats2half2_rn(x0, x1);
-                        }
-                        *reinterpret_cast<uint4*>(d_row + q * 8) = ov;
-                    }
-                }
-                else
-                {
-                    // 32 x 4-byte = 8 x 16 bytes
-#pragma unroll
-                    for(int q = 0; q < 8; ++q)
-                    {
-                        uint4 cv = make_uint4(0, 0, 0, 0);
-                        if(read_c)
-                            cv = *reinterpret_cast<const uint4*>(c_row + q * 4);
-                        const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
-                        uint32_t       ow[4];
-#pragma unroll
-                        for(int j = 0; j < 4; ++j)
-                        {
-                            if constexpr(std::is_same<OutT, float>::value)
-                                ow[j] = __float_as_uint(epi(__uint_as_float(v[q * 4 + j]),
-                                                            __uint_as_float(cw[j]),
-                                                            alpha,
-                                                            beta));
-                            else
-                                ow[j] = static_cast<uint32_t>(epi(static_cast<int32_t>(v[q * 4 + j]),
-                                                                  static_cast<int32_t>(cw[j]),
-                                                                  alpha,
-                                                                  beta));
-                        }
-                        *reinterpret_cast<uint4*>(d_row + q * 4)
-                            = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-                    }
-                }
-            }
-            else
-            {
-#pragma unroll
-                for(int j = 0; j < 32; ++j)
-                {
-                    if(static_cast<uint32_t>(j) < ncols)
-                    {
-                        if constexpr(std::is_same<OutT, int32_t>::value)
-                        {
-                            const int32_t cvv = read_c ? c_row[j] : 0;
-                            d_row[j] = epi(static_cast<int32_t>(v[j]), cvv, alpha, beta);
-                        }
-                        else
-                        {
-                            const float cvv = read_c ? static_cast<float>(c_row[j]) : 0.0f;
-                            d_row[j]
-                                = static_cast<OutT>(epi(__uint_as_float(v[j]), cvv, alpha, beta));
-                        }
-                    }
-                }
-            }
-        }
 
         template <int KIND, typename OutT, typename ScalarT>
         __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -205,7 +54,8 @@ namespace b200wmma
                              ScalarT   beta,
                              uint32_t  tiles_m,
                              uint32_t  tiles_n,
-                             int       vec_ok, // C/D rows 16-byte aligned -> vector epilogue
+                             int       vec_ok, // widest aligned epilogue access: 0 / 1 (16 B) / 2 (32 B)
+                             uint32_t  group_m, // rasterisation band height in row tiles
                              unsigned* status)
         {
             extern __shared__ uint8_t smem_raw[];
@@ -268,7 +118,7 @@ namespace b200wmma
                     for(uint32_t tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x)
                     {
                         uint32_t m_idx, n_idx;
-                        tile_coords(tile, tiles_m, tiles_n, m_idx, n_idx);
+                        tile_coords(tile, tiles_m, tiles_n, group_m, m_idx, n_idx);
                         const int32_t row_a = static_cast<int32_t>(m_idx * BLOCK_M);
                         const int32_t row_b = static_cast<int32_t>(n_idx * BLOCK_N);
                         for(uint32_t kb = 0; kb < num_kb; ++kb)
@@ -303,7 +153,7 @@ namespace b200wmma
                 // ------------------------------- MMA issuer -------------------------------
                 if(lane == 0)
                 {
-                    constexpr uint32_t idesc = make_idesc<KIND>();
+                    constexpr uint32_t idesc = make_idesc<KIND, BLOCK_M, BLOCK_N>();
                     uint32_t           stage = 0, phase = 0;
                     uint32_t           iter = 0;
                     bool               ok   = true;
@@ -373,44 +223,15 @@ namespace b200wmma
                     const uint32_t buf    = iter & 1u;
                     const uint32_t bphase = (iter >> 1) & 1u;
                     uint32_t       m_idx, n_idx;
-                    tile_coords(tile, tiles_m, tiles_n, m_idx, n_idx);
-                    ok = ptx::mbar_wait_bounded(tfull_bar + 8 * buf,
-                                                bphase,
-                                                cta_abort,
-                                                status,
-                                                (ROLE_EPILOGUE << 24) | blockIdx.x,
-                                                WAIT_TIMEOUT_NS);
-                    // the warp must stay converged for the .sync.aligned tcgen05.ld below
-                    ok = __all_sync(0xFFFFFFFFu, ok);
+                    tile_coords(tile, tiles_m, tiles_n, group_m, m_idx, n_idx);
+                    ok = ptx::mbar_wait_bounded_warp(tfull_bar + 8 * buf, bphase, cta_abort, status,
+                                                     (ROLE_EPILOGUE << 24) | blockIdx.x, WAIT_TIMEOUT_NS, lane);
                     if(!ok)
                         break;
                     ptx::tc_fence_after_sync();
-                    const uint32_t row     = m_idx * BLOCK_M + quad * 32u + lane;
-                    const bool     row_ok  = row < m;
-                    const uint32_t col_base = n_idx * BLOCK_N;
-                    const OutT*    c_row   = c + static_cast<size_t>(row) * ldc + col_base;
-                    OutT*          d_row   = d + static_cast<size_t>(row) * ldd + col_base;
-#pragma unroll 1
-                    for(uint32_t ch = 0; ch < BLOCK_N / 32; ++ch)
-                    {
-                        uint32_t v[32];
-                        ptx::tmem_ld_32x32b_x32(
-                            tmem_base + ((quad * 32u) << 16) + buf * BLOCK_N + ch * 32u, v);
-                        ptx::tmem_ld_wait();
-                        const uint32_t col0 = col_base + ch * 32u;
-                        if(row_ok && col0 < n)
-                        {
-                            const uint32_t ncols = min(32u, n - col0);
-                            epilogue_row_chunk<OutT, ScalarT>(v,
-                                                              c_row + ch * 32u,
-                                                              d_row + ch * 32u,
-                                                              ncols,
-                                                              alpha,
-                                                              beta,
-                                                              read_c,
-                                                              vec_ok != 0);
-                        }
-                    }
+                    drain_accumulator<OutT, ScalarT, BLOCK_N>(tmem_base + buf * BLOCK_N, quad, lane,
+                                                              m_idx * BLOCK_M, n_idx * BLOCK_N, m, n, c, d, ldc, ldd,
+                                                              alpha, beta, read_c, vec_ok);
                     ptx::tc_fence_before_sync();
                     ptx::mbar_arrive(tempty_bar + 8 * buf);
                 }
@@ -435,68 +256,28 @@ namespace b200wmma
             }
         }
 
-        // ---- host side ------------------------------------------------------------------
-        typedef CUresult (*EncodeTiledFn)(CUtensorMap*,
-                                          CUtensorMapDataType,
-                                          cuuint32_t,
-                                          void*,
-                                          const cuuint64_t*,
-                                          const cuuint64_t*,
-                                          const cuuint32_t*,
-                                          const cuuint32_t*,
-                                          CUtensorMapInterleave,
-                                          CUtensorMapSwizzle,
-                                          CUtensorMapL2promotion,
-                                          CUtensorMapFloatOOBfill);
-
-        static EncodeTiledFn get_encode_fn()
+        // Rasterisation band height; B200WMMA_GROUP_M overrides the built-in value (tuning aid).
+        static uint32_t group_override(uint32_t dflt)
         {
-            static EncodeTiledFn fn = []() -> EncodeTiledFn {
-                void*                           p = nullptr;
-                cudaDriverEntryPointQueryResult q;
-                if(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q)
-                       != cudaSuccess
-                   || q != cudaDriverEntryPointSuccess)
-                    return nullptr;
-                return reinterpret_cast<EncodeTiledFn>(p);
+            static int v = []() {
+                const char* e = std::getenv("B200WMMA_GROUP_M");
+                return e ? std::atoi(e) : 0;
             }();
-            return fn;
+            return v > 0 ? static_cast<uint32_t>(v) : dflt;
         }
 
-        // K-major operand: `rows` rows of `k_elems` contiguous elements, row pitch ld elements.
-        // Box = one 128-byte K slab x box_rows rows, 128-byte swizzle, zero fill out of bounds.
-        static int make_kmajor_tmap(CUtensorMap*        out,
-                                    CUtensorMapDataType dtype,
-                                    uint32_t            elem_bytes,
-                                    const void*         ptr,
-                                    uint32_t            rows,
-                                    uint32_t            k_elems,
-                                    uint32_t            ld,
-                                    uint32_t            box_rows)
+        // 0 = automatic, 1 = one-CTA tiles, 2 = two-CTA tiles (environment override for A/B comparisons)
+        static int forced_variant()
         {
-            EncodeTiledFn fn = get_encode_fn();
-            B200_REQUIRE(fn != nullptr, B200WMMA_ERR_CUDA, "cuTensorMapEncodeTiled not available");
-            cuuint64_t gdim[2]    = {k_elems, rows};
-            cuuint64_t gstride[1] = {static_cast<cuuint64_t>(ld) * elem_bytes};
-            cuuint32_t box[2]     = {BLOCK_K_BYTES / elem_bytes, box_rows};
-            cuuint32_t estr[2]    = {1, 1};
-            CUresult   r          = fn(out,
-                            dtype,
-                            2,
-                            const_cast<void*>(ptr),
-                            gdim,
-                            gstride,
-                            box,
-                            estr,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE,
-                            CU_TENSOR_MAP_SWIZZLE_128B,
-                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-            B200_REQUIRE(r == CUDA_SUCCESS,
-                         B200WMMA_ERR_CUDA,
-                         "cuTensorMapEncodeTiled failed with CUresult %d",
-                         static_cast<int>(r));
-            return B200WMMA_OK;
+            static int v = []() {
+                const char* e = std::getenv("B200WMMA_GEMM_VARIANT");
+                if(e && std::strcmp(e, "1cta") == 0)
+                    return 1;
+                if(e && std::strcmp(e, "2cta") == 0)
+                    return 2;
+                return 0;
+            }();
+            return v;
         }
 
         template <int KIND, typename OutT, typename ScalarT>
@@ -535,18 +316,63 @@ namespace b200wmma
             if(int e = status_word_ptr(&status))
                 return e;
 
-            CUtensorMap               tm_a, tm_b;
             const CUtensorMapDataType dt
                 = (KIND == KIND_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+            // widest epilogue access every C / D row start allows: 32 bytes, 16 bytes, or element-wise
+            auto row_align = [](const void* p, uint32_t ld, size_t es, uint64_t bytes) {
+                return (reinterpret_cast<uintptr_t>(p) % bytes) == 0 && (static_cast<uint64_t>(ld) * es) % bytes == 0;
+            };
+            int vec_ok = 0;
+            if(row_align(d, ldd, sizeof(OutT), 32) && (!c || row_align(c, ldc, sizeof(OutT), 32)))
+                vec_ok = 2;
+            else if(row_align(d, ldd, sizeof(OutT), 16) && (!c || row_align(c, ldc, sizeof(OutT), 16)))
+                vec_ok = 1;
+            int dev = 0, sms = 0;
+            B200_CHECK_CUDA(cudaGetDevice(&dev));
+            B200_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+
+            // Two-CTA tiles (256 x 256 per SM pair) unless the problem has a single 128-row band or
+            // the one-CTA kernel is requested explicitly (B200WMMA_GEMM_VARIANT=1cta, for comparison).
+            const int  forced   = forced_variant();
+            const bool use_pair = forced == 2 || (forced == 0 && m > BLOCK_M);
+            CUtensorMap tm_a, tm_b;
             if(int e = make_kmajor_tmap(&tm_a, dt, EB, a, m, k, lda, BLOCK_M))
                 return e;
-            if(int e = make_kmajor_tmap(&tm_b, dt, EB, b, n, k, ldb, BLOCK_N))
+            if(int e = make_kmajor_tmap(&tm_b, dt, EB, b, n, k, ldb, use_pair ? tc05p::HALF_N : BLOCK_N))
                 return e;
 
-            const bool vec_ok = aligned16(d) && (static_cast<uint64_t>(ldd) * sizeof(OutT)) % 16 == 0
-                                && (!c
-                                    || (aligned16(c)
-                                        && (static_cast<uint64_t>(ldc) * sizeof(OutT)) % 16 == 0));
+            if(use_pair)
+            {
+                auto        kern    = tc05p::gemm_tc05_pair_kernel<KIND, OutT, ScalarT>;
+                static int  max_clusters = 0; // one per template instantiation
+                const uint32_t tiles_m = ceil_div(m, tc05p::PAIR_M), tiles_n = ceil_div(n, tc05p::TILE_N);
+                cudaLaunchConfig_t  cfg = {};
+                cudaLaunchAttribute attr[1];
+                attr[0].id               = cudaLaunchAttributeClusterDimension;
+                attr[0].val.clusterDim.x = 2;
+                attr[0].val.clusterDim.y = 1;
+                attr[0].val.clusterDim.z = 1;
+                cfg.blockDim         = dim3(tc05p::NUM_THREADS);
+                cfg.dynamicSmemBytes = tc05p::SMEM_BYTES;
+                cfg.stream           = stream;
+                cfg.attrs            = attr;
+                cfg.numAttrs         = 1;
+                if(max_clusters == 0)
+                {
+                    B200_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                         tc05p::SMEM_BYTES));
+                    cfg.gridDim = dim3(static_cast<unsigned>(sms) & ~1u);
+                    int nc      = 0;
+                    B200_CHECK_CUDA(cudaOccupancyMaxActiveClusters(&nc, kern, &cfg));
+                    B200_REQUIRE(nc > 0, B200WMMA_ERR_CUDA, "no two-CTA cluster of the GEMM kernel fits on this device");
+                    max_clusters = nc;
+                }
+                const uint32_t pairs = min(tiles_m * tiles_n, static_cast<uint32_t>(max_clusters));
+                cfg.gridDim          = dim3(2 * pairs);
+                B200_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, c, d, m, n, k * EB, ldc, ldd, alpha, beta,
+                                                   tiles_m, tiles_n, vec_ok, group_override(tc05p::GROUP_M), status));
+                return B200WMMA_OK;
+            }
 
             auto        kern    = gemm_tc05_kernel<KIND, OutT, ScalarT>;
             static bool attr_ok = false; // one flag per template instantiation
@@ -556,9 +382,6 @@ namespace b200wmma
                     kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
                 attr_ok = true;
             }
-            int dev = 0, sms = 0;
-            B200_CHECK_CUDA(cudaGetDevice(&dev));
-            B200_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
             const uint32_t tiles_m = ceil_div(m, BLOCK_M), tiles_n = ceil_div(n, BLOCK_N);
             const uint32_t grid = min(tiles_m * tiles_n, static_cast<uint32_t>(sms));
             kern<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tm_a,
@@ -574,7 +397,8 @@ namespace b200wmma
                                                              beta,
                                                              tiles_m,
                                                              tiles_n,
-                                                             vec_ok ? 1 : 0,
+                                                             vec_ok,
+                                                             group_override(GROUP_M),
                                                              status);
             B200_CHECK_CUDA(cudaGetLastError());
             return B200WMMA_OK;

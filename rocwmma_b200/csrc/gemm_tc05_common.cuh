@@ -1,0 +1,288 @@
+// Pieces shared by the one-CTA and the two-CTA tcgen05 GEMM kernels: operand kinds, the
+// instruction descriptor, tile rasterisation, the alpha/beta epilogue on one row chunk, and the
+// host-side TMA tensor-map construction.
+#pragma once
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+#include <type_traits>
+
+namespace b200wmma
+{
+    namespace tc05
+    {
+        constexpr uint32_t BLOCK_K_BYTES   = 128; // one 128-byte swizzle row: 64 fp16 / 128 int8
+        constexpr uint64_t WAIT_TIMEOUT_NS = 2000000000ull; // 2 s: far beyond any healthy wait
+
+        enum Kind : int
+        {
+            KIND_F16 = 0,
+            KIND_I8  = 1
+        };
+        enum Role : uint32_t
+        {
+            ROLE_PRODUCER = 1,
+            ROLE_MMA      = 2,
+            ROLE_EPILOGUE = 3
+        };
+
+        // tcgen05 instruction descriptor (32-bit): D format bits [4,6), A format [7,10),
+        // B format [10,13), A/B major bits 15/16 (0 = K-major), N>>3 at [17,23), M>>4 at [24,29).
+        template <int KIND, uint32_t MMA_M, uint32_t MMA_N>
+        __host__ __device__ constexpr uint32_t make_idesc()
+        {
+            uint32_t d = 0;
+            if(KIND == KIND_F16)
+            {
+                d |= 1u << 4; // D = F32;  A = B = F16 (format 0)
+            }
+            else
+            {
+                d |= 2u << 4; // D = S32
+                d |= 1u << 7; // A = signed 8-bit
+                d |= 1u << 10; // B = signed 8-bit
+            }
+            d |= (MMA_N >> 3) << 17;
+            d |= (MMA_M >> 4) << 24;
+            return d;
+        }
+
+        // Rasterisation: tiles are walked in bands of `GROUP_M` row tiles; inside a band the row index
+        // varies fastest, so CTAs running at the same time share a few B column slabs and the
+        // band's A rows stay hot in L2 while the band sweeps across N.
+        __device__ __forceinline__ void tile_coords(uint32_t  tile,
+                                                    uint32_t  tiles_m,
+                                                    uint32_t  tiles_n,
+                                                    uint32_t  GROUP_M,
+                                                    uint32_t& m_idx,
+                                                    uint32_t& n_idx)
+        {
+            const uint32_t group_size = GROUP_M * tiles_n;
+            const uint32_t group      = tile / group_size;
+            const uint32_t first_m    = group * GROUP_M;
+            const uint32_t gm         = min(tiles_m - first_m, GROUP_M);
+            const uint32_t within     = tile - group * group_size;
+            m_idx                     = first_m + within % gm;
+            n_idx                     = within / gm;
+        }
+
+        // ---- epilogue element helpers -----------------------------------------------------
+        __device__ __forceinline__ float epi(float acc, float c, float alpha, float beta)
+        {
+            return alpha * acc + beta * c;
+        }
+        __device__ __forceinline__ int32_t epi(int32_t acc, int32_t c, int32_t alpha, int32_t beta)
+        {
+            // wrap-around int32 arithmetic, as the reference's int32 ComputeT does
+            return static_cast<int32_t>(static_cast<uint32_t>(alpha) * static_cast<uint32_t>(acc)
+                                        + static_cast<uint32_t>(beta) * static_cast<uint32_t>(c));
+        }
+
+        // 16- or 32-byte global accesses of VW 32-bit words.  C is read once and D written once,
+        // so both use the streaming (evict-first) policy and leave L2 to the A / B slabs.
+        template <int VW>
+        __device__ __forceinline__ void ldg_words(const void* p, uint32_t (&w)[VW])
+        {
+            if constexpr(VW == 8)
+                asm volatile("ld.global.cs.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                             : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]),
+                               "=r"(w[7])
+                             : "l"(p));
+            else
+                asm volatile("ld.global.cs.v4.b32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+                             : "l"(p));
+        }
+        template <int VW>
+        __device__ __forceinline__ void stg_words(void* p, const uint32_t (&w)[VW])
+        {
+            if constexpr(VW == 8)
+                asm volatile("st.global.cs.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(w[0]), "r"(w[1]),
+                             "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+                             : "memory");
+            else
+                asm volatile("st.global.cs.v4.b32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]),
+                             "r"(w[3])
+                             : "memory");
+        }
+
+        // Vector path of one thread's 32 consecutive output columns: VW words per access.
+        template <typename OutT, typename ScalarT, int VW>
+        __device__ __forceinline__ void epilogue_row_chunk_vec(const uint32_t (&v)[32],
+                                                               const OutT* __restrict__ c_row,
+                                                               OutT* __restrict__ d_row, ScalarT alpha,
+                                                               ScalarT beta, bool read_c)
+        {
+            constexpr int EPW   = 4 / sizeof(OutT); // output elements per 32-bit word
+            constexpr int WORDS = 32 / EPW; // words covering 32 columns
+            const uint32_t* cw_ptr = reinterpret_cast<const uint32_t*>(c_row);
+            uint32_t*       dw_ptr = reinterpret_cast<uint32_t*>(d_row);
+#pragma unroll
+            for(int g = 0; g < WORDS / VW; ++g)
+            {
+                uint32_t cw[VW], ow[VW];
+#pragma unroll
+                for(int j = 0; j < VW; ++j)
+                    cw[j] = 0u;
+                if(read_c)
+                    ldg_words<VW>(cw_ptr + g * VW, cw);
+#pragma unroll
+                for(int j = 0; j < VW; ++j)
+                {
+                    const int w = g * VW + j;
+                    if constexpr(EPW == 2)
+                    {
+                        const float2 cf = __half22float2(*reinterpret_cast<const __half2*>(&cw[j]));
+                        const float  x0 = epi(__uint_as_float(v[2 * w]), cf.x, alpha, beta);
+                        const float  x1 = epi(__uint_as_float(v[2 * w + 1]), cf.y, alpha, beta);
+                        const __half2 h = __floats2half2_rn(x0, x1);
+                        ow[j]           = *reinterpret_cast<const uint32_t*>(&h);
+                    }
+                    else if constexpr(std::is_same<OutT, float>::value)
+                        ow[j] = __float_as_uint(epi(__uint_as_float(v[w]), __uint_as_float(cw[j]), alpha, beta));
+                    else
+                        ow[j] = static_cast<uint32_t>(
+                            epi(static_cast<int32_t>(v[w]), static_cast<int32_t>(cw[j]), alpha, beta));
+                }
+                stg_words<VW>(dw_ptr + g * VW, ow);
+            }
+        }
+
+        // One thread's 32 consecutive output columns of one row.
+        // OutT = __half: acc is fp32 bits.  OutT = float: fp32.  OutT = int32_t: int32.
+        // vec: 0 = element-wise, 1 = 16-byte accesses, 2 = 32-byte accesses (rows aligned accordingly).
+        template <typename OutT, typename ScalarT>
+        __device__ __forceinline__ void epilogue_row_chunk(const uint32_t (&v)[32],
+                                                           const OutT* __restrict__ c_row,
+                                                           OutT* __restrict__ d_row,
+                                                           uint32_t ncols, // valid columns (<= 32)
+                                                           ScalarT  alpha,
+                                                           ScalarT  beta,
+                                                           bool     read_c,
+                                                           int      vec)
+        {
+            if(ncols == 32 && vec == 2)
+                epilogue_row_chunk_vec<OutT, ScalarT, 8>(v, c_row, d_row, alpha, beta, read_c);
+            else if(ncols == 32 && vec == 1)
+                epilogue_row_chunk_vec<OutT, ScalarT, 4>(v, c_row, d_row, alpha, beta, read_c);
+            else
+            {
+#pragma unroll
+                for(int j = 0; j < 32; ++j)
+                {
+                    if(static_cast<uint32_t>(j) < ncols)
+                    {
+                        if constexpr(std::is_same<OutT, int32_t>::value)
+                        {
+                            const int32_t cvv = read_c ? c_row[j] : 0;
+                            d_row[j] = epi(static_cast<int32_t>(v[j]), cvv, alpha, beta);
+                        }
+                        else
+                        {
+                            const float cvv = read_c ? static_cast<float>(c_row[j]) : 0.0f;
+                            d_row[j]
+                                = static_cast<OutT>(epi(__uint_as_float(v[j]), cvv, alpha, beta));
+                        }
+                    }
+                }
+            }
+        }
+
+        // Epilogue of one accumulator: the calling warp drains its 32-lane quadrant of a
+        // 128-lane x TILE_N-column accumulator (one output row per thread, 32 columns per step),
+        // applies alpha / beta and stores D.  `tmem_acc` is the accumulator's tensor-memory address
+        // (lane 0, first column); row_base / col_base locate the CTA's 128 x TILE_N block in D.
+        // All 32 lanes must call it together (tcgen05.ld is warp-collective).
+        template <typename OutT, typename ScalarT, uint32_t TILE_N>
+        __device__ __forceinline__ void drain_accumulator(uint32_t tmem_acc, uint32_t quad, uint32_t lane,
+                                                          uint32_t row_base, uint32_t col_base, uint32_t m,
+                                                          uint32_t n, const OutT* __restrict__ c,
+                                                          OutT* __restrict__ d, uint32_t ldc, uint32_t ldd,
+                                                          ScalarT alpha, ScalarT beta, bool read_c, int vec_ok)
+        {
+            const uint32_t row    = row_base + quad * 32u + lane;
+            const bool     row_ok = row < m;
+            const OutT*    c_row  = c + static_cast<size_t>(row) * ldc + col_base;
+            OutT*          d_row  = d + static_cast<size_t>(row) * ldd + col_base;
+#pragma unroll 1
+            for(uint32_t ch = 0; ch < TILE_N / 32; ++ch)
+            {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32b_x32(tmem_acc + ((quad * 32u) << 16) + ch * 32u, v);
+                ptx::tmem_ld_wait();
+                const uint32_t col0 = col_base + ch * 32u;
+                if(row_ok && col0 < n)
+                {
+                    const uint32_t ncols = min(32u, n - col0);
+                    epilogue_row_chunk<OutT, ScalarT>(v, c_row + ch * 32u, d_row + ch * 32u, ncols, alpha, beta,
+                                                      read_c, vec_ok);
+                }
+            }
+        }
+
+        // ---- host side ------------------------------------------------------------------
+        typedef CUresult (*EncodeTiledFn)(CUtensorMap*,
+                                          CUtensorMapDataType,
+                                          cuuint32_t,
+                                          void*,
+                                          const cuuint64_t*,
+                                          const cuuint64_t*,
+                                          const cuuint32_t*,
+                                          const cuuint32_t*,
+                                          CUtensorMapInterleave,
+                                          CUtensorMapSwizzle,
+                                          CUtensorMapL2promotion,
+                                          CUtensorMapFloatOOBfill);
+
+        static EncodeTiledFn get_encode_fn()
+        {
+            static EncodeTiledFn fn = []() -> EncodeTiledFn {
+                void*                           p = nullptr;
+                cudaDriverEntryPointQueryResult q;
+                if(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q)
+                       != cudaSuccess
+                   || q != cudaDriverEntryPointSuccess)
+                    return nullptr;
+                return reinterpret_cast<EncodeTiledFn>(p);
+            }();
+            return fn;
+        }
+
+        // K-major operand: `rows` rows of `k_elems` contiguous elements, row pitch ld elements.
+        // Box = one 128-byte K slab x box_rows rows, 128-byte swizzle, zero fill out of bounds.
+        static int make_kmajor_tmap(CUtensorMap*        out,
+                                    CUtensorMapDataType dtype,
+                                    uint32_t            elem_bytes,
+                                    const void*         ptr,
+                                    uint32_t            rows,
+                                    uint32_t            k_elems,
+                                    uint32_t            ld,
+                                    uint32_t            box_rows)
+        {
+            EncodeTiledFn fn = get_encode_fn();
+            B200_REQUIRE(fn != nullptr, B200WMMA_ERR_CUDA, "cuTensorMapEncodeTiled not available");
+            cuuint64_t gdim[2]    = {k_elems, rows};
+            cuuint64_t gstride[1] = {static_cast<cuuint64_t>(ld) * elem_bytes};
+            cuuint32_t box[2]     = {BLOCK_K_BYTES / elem_bytes, box_rows};
+            cuuint32_t estr[2]    = {1, 1};
+            CUresult   r          = fn(out,
+                            dtype,
+                            2,
+                            const_cast<void*>(ptr),
+                            gdim,
+                            gstride,
+                            box,
+                            estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            B200_REQUIRE(r == CUDA_SUCCESS,
+                         B200WMMA_ERR_CUDA,
+                         "cuTensorMapEncodeTiled failed with CUresult %d",
+                         static_cast<int>(r));
+            return B200WMMA_OK;
+        }
+
+    } // namespace tc05
+} // namespace b200wmma

@@ -92,6 +92,62 @@ namespace b200wmma
             }
         }
 
+        // Warp-wide bounded wait for waits that last a whole tile: lane 0 polls with a short sleep
+        // between tries (31 lanes stop issuing instructions), then every lane confirms the completed
+        // phase itself so that each has observed the barrier.  All 32 lanes must call it.
+        __device__ __forceinline__ bool mbar_wait_bounded_warp(uint32_t           bar,
+                                                               uint32_t           parity,
+                                                               volatile uint32_t* cta_abort,
+                                                               unsigned*          status,
+                                                               uint32_t           who,
+                                                               uint64_t           timeout_ns,
+                                                               uint32_t           lane)
+        {
+            bool ok = true;
+            if(lane == 0 && !mbar_try_wait(bar, parity))
+            {
+                const uint64_t t0    = globaltimer_ns();
+                uint32_t       spins = 0;
+                while(true)
+                {
+                    __nanosleep(64);
+                    if(mbar_try_wait(bar, parity))
+                        break;
+                    if((++spins & 0x3Fu) == 0u)
+                    {
+                        if(*cta_abort)
+                        {
+                            ok = false;
+                            break;
+                        }
+                        if(globaltimer_ns() - t0 > timeout_ns)
+                        {
+                            *cta_abort = 1u;
+                            if(atomicCAS(status, 0u, STATUS_TIMEOUT_CODE) == 0u)
+                                status[1] = who;
+                            ok = false;
+                            break;
+                        }
+                    }
+                }
+            }
+            ok = __shfl_sync(0xFFFFFFFFu, ok ? 1 : 0, 0) != 0;
+            if(ok)
+            {
+                // the phase lane 0 saw complete cannot advance again before this warp releases the
+                // resource it guards, so this returns at once; the bound is a formality
+                uint32_t tries = 0;
+                while(!mbar_try_wait(bar, parity))
+                    if(++tries > (1u << 20))
+                    {
+                        ok = false;
+                        break;
+                    }
+                ok = __all_sync(0xFFFFFFFFu, ok);
+            }
+            return ok;
+        }
+
         // ---- TMA ------------------------------------------------------------------------
         __device__ __forceinline__ void prefetch_tensormap(const void* tmap)
         {
@@ -203,6 +259,109 @@ namespace b200wmma
         __device__ __forceinline__ void tmem_ld_wait()
         {
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        }
+
+
+        // ---- thread-block clusters and the two-CTA (cta_group::2) forms ------------------------
+        __device__ __forceinline__ uint32_t cluster_ctarank()
+        {
+            uint32_t r;
+            asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+            return r;
+        }
+        // Full cluster barrier with release / acquire ordering; every thread of every CTA calls it.
+        __device__ __forceinline__ void cluster_sync()
+        {
+            asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                         "barrier.cluster.wait.acquire.aligned;" ::
+                             : "memory");
+        }
+        // shared::cluster address of the same shared-memory offset in CTA `rank` of this cluster
+        __device__ __forceinline__ uint32_t mapa(uint32_t smem_addr, uint32_t rank)
+        {
+            uint32_t r;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+            return r;
+        }
+        __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+        {
+            asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+                         : "memory");
+        }
+        __device__ __forceinline__ uint32_t ld_shared_cluster_u32(uint32_t cluster_addr)
+        {
+            uint32_t v;
+            asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+            return v;
+        }
+        // 2-D tiled load into THIS CTA's shared memory whose completion bytes are counted on a
+        // barrier that may live in the peer CTA of the pair (`bar_cluster_addr` from mapa).
+        // No multicast: each CTA fetches its own boxes.
+        __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const void* tmap, int32_t c0,
+                                                         int32_t c1, uint32_t bar_cluster_addr)
+        {
+            asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+                         " [%0], [%1, {%2, %3}], [%4];" ::"r"(dst_smem),
+                         "l"(reinterpret_cast<uint64_t>(tmap)),
+                         "r"(c0),
+                         "r"(c1),
+                         "r"(bar_cluster_addr)
+                         : "memory");
+        }
+        __device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols)
+        {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem),
+                         "r"(ncols)
+                         : "memory");
+        }
+        __device__ __forceinline__ void tmem_relinquish_pair()
+        {
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        }
+        __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols)
+        {
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+                         : "memory");
+        }
+        // One MMA spanning both CTAs of the pair: M = 256 (128 rows of A and of D per CTA),
+        // each CTA supplies half of B's N extent from the same shared-memory offset.
+        __device__ __forceinline__ void mma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                        uint32_t idesc, uint32_t accumulate)
+        {
+            asm volatile("{\n"
+                         ".reg .pred p;\n"
+                         "setp.ne.b32 p, %4, 0;\n"
+                         "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+                         "}" ::"r"(d_tmem),
+                         "l"(a_desc),
+                         "l"(b_desc),
+                         "r"(idesc),
+                         "r"(accumulate)
+                         : "memory");
+        }
+        __device__ __forceinline__ void mma_i8_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                       uint32_t idesc, uint32_t accumulate)
+        {
+            asm volatile("{\n"
+                         ".reg .pred p;\n"
+                         "setp.ne.b32 p, %4, 0;\n"
+                         "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n"
+                         "}" ::"r"(d_tmem),
+                         "l"(a_desc),
+                         "l"(b_desc),
+                         "r"(idesc),
+                         "r"(accumulate)
+                         : "memory");
+        }
+        // Once every MMA issued so far by this thread has completed, arrive on the barrier at this
+        // shared-memory offset in each CTA of the pair named by `cta_mask` (bit r = CTA rank r).
+        // This is a barrier signal, not a data transfer: no operand is multicast.
+        __device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t cta_mask)
+        {
+            asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+                         "[%0], %1;" ::"r"(bar),
+                         "h"(cta_mask)
+                         : "memory");
         }
 
         // Shared-memory matrix descriptor for a K-major operand tile stored as rows of 128
