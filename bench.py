@@ -536,9 +536,9 @@ WORKLOADS = {w().name: w for w in (GemmF16, GemmI8, GemmI8Sp24, GemmI4, GemmF64,
 # ---------------------------------------------------------------------------------------- CPU arm
 def cpu_impl():
     from oracle import cpu_ref as R
-    if R.have_reference():
-        return R.reference(), "reference"
-    return R.port(), "port"
+    impl, kind = (R.reference(), "reference") if R.have_reference() else (R.port(), "port")
+    R.use_all_host_threads(impl)  # torchrun exports OMP_NUM_THREADS=1; the CPU arm uses every host thread
+    return impl, kind
 
 
 def cpu_baseline(wl, budget_s=12.0):

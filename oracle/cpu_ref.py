@@ -49,6 +49,8 @@ def _load(path):
     h.oracle_gemv_f64.argtypes = [_u32, _u32, _vp, _u32, C.c_int, _vp, _vp, C.c_double, C.c_double]
     h.oracle_num_threads.restype = C.c_int
     h.oracle_num_threads.argtypes = []
+    h.oracle_set_num_threads.restype = None
+    h.oracle_set_num_threads.argtypes = [C.c_int]
     if hasattr(h, "oracle_gemm_abs_bound"):
         h.oracle_gemm_abs_bound.restype = None
         h.oracle_gemm_abs_bound.argtypes = [_u32, _u32, _u32, _vp, _vp, _vp, C.c_double, C.c_double, _vp]
@@ -145,4 +147,11 @@ def gemm_abs_bound(m, n, k, a_rm, b_rm, c_rm, alpha, beta):
 
 
 def num_threads(impl) -> int:
+    return impl.oracle_num_threads()
+
+
+def use_all_host_threads(impl) -> int:
+    """Let the OpenMP loops use every hardware thread this process may run on; returns the count."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    impl.oracle_set_num_threads(n)
     return impl.oracle_num_threads()

@@ -201,6 +201,18 @@ void oracle_gemm_abs_bound(uint32_t m, uint32_t n, uint32_t k, const double* a_r
         }
 }
 
+/* Thread count for the OpenMP loops above (launchers such as torchrun export OMP_NUM_THREADS=1). */
+void oracle_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    extern void omp_set_num_threads(int);
+    if(n > 0)
+        omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int oracle_num_threads(void)
 {
     int n = 1;

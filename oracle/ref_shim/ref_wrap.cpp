@@ -140,6 +140,9 @@ extern "C" void oracle_gemv_f64(uint32_t m, uint32_t n, const double* a, uint32_
 #ifdef _OPENMP
 #include <omp.h>
 extern "C" int oracle_num_threads(void) { return omp_get_max_threads(); }
+// launchers such as torchrun export OMP_NUM_THREADS=1; the timed baseline asks for all host threads
+extern "C" void oracle_set_num_threads(int n) { if(n > 0) omp_set_num_threads(n); }
 #else
 extern "C" int oracle_num_threads(void) { return 1; }
+extern "C" void oracle_set_num_threads(int) {}
 #endif

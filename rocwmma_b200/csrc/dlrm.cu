@@ -1,59 +1,54 @@
-// DLRM dot-interaction forward and backward, one warp per sample, everything fused.
+// DLRM dot-interaction forward and backward, one warp per sample, everything fused, all global
+// traffic moved by the TMA engine.
 //
 // Forward stands in for dlrmDotFwd (samples/simple_dlrm.cpp:184-284;
 // test/dlrm/device/dlrm_dot_fwd.hpp:37-136).  The reference computes each 16x16 tile of
 // Z = X X^T in its own wave, stores it to a global fp32 scratch, re-reads the scratch and
-// writes the strict lower triangle element by element.  Here a warp brings the sample's
-// X (m x k fp16) into shared memory once, runs the lower-triangle tiles on mma.sync with
-// fp32 accumulators, packs [X row 0 | tril(Z)] into a shared-memory row and writes it with
-// 16-byte coalesced stores: X is read once, the output written once, no scratch.
+// writes the strict lower triangle element by element.  Here each warp owns a small ring of
+// shared-memory sample tiles: one lane asks the TMA unit for the sample's m x k rows (64-column
+// boxes, 128-byte swizzle, so ldmatrix reads are conflict-free), the warp runs the lower-triangle
+// tiles on mma.sync with fp32 accumulators, packs [X row 0 | tril(Z)] into a shared-memory row
+// and one lane hands that row back to the TMA unit as a bulk store.  X is read once, the output
+// written once, no scratch, and no thread computes a global address per element.
 //
 // Backward stands in for trilReconstruct + dlrmDotBwd (samples/simple_dlrm.cpp:290-331,
 // :349-441; test/dlrm/device/dlrm_dot_bwd.hpp:35-172), which rebuild the symmetric matrix in
 // global memory in one kernel, synchronise on the host, and multiply in a second kernel.
-// Here the packed upstream row is expanded to the symmetric m x m fp16 matrix in shared
-// memory, multiplied with X on mma.sync and written back in the same pass, optionally with
-// the bottom-MLP pass-through gradient added to row 0.
+// Here the packed upstream row arrives by bulk copy, is expanded to the symmetric m x m fp16
+// matrix in shared memory, multiplied with X on mma.sync; the product overwrites the X tile in
+// place (16-column slabs) and leaves through TMA tile stores that cover rows 0..m-1 only,
+// optionally with the bottom-MLP pass-through gradient added to row 0.
 //
 // Both are HBM-bound: the arithmetic is 2*m*m*k flop per sample against ~8-15 KB of traffic.
-#include "common.cuh"
+#include "gemm_tc05_common.cuh" // make_kmajor_tmap: 64-column, 128-byte-swizzled box maps
+#include "ptx_sm100.cuh"
 
 namespace b200wmma
 {
     namespace dlrm
     {
-        constexpr int WARPS  = 4;
-        constexpr int MAX_M  = 32;
-        constexpr int MAX_K  = 256;
-        constexpr int TPITCH = 40; // halfs per row of the 32x32 symmetric matrix (+8 pad)
+        constexpr int      WARPS       = 4;
+        constexpr int      MAX_M       = 32;
+        constexpr int      MAX_K       = 256;
+        constexpr int      FWD_STAGES  = 3;
+        constexpr int      BWD_STAGES  = 2;
+        constexpr int      TPITCH      = 40; // halfs per row of the 32x32 symmetric matrix (+8 pad)
+        constexpr uint32_t BOX_BYTES   = MAX_M * 128; // one 64-column box: 32 rows of 128 bytes
+        constexpr uint64_t WAIT_NS     = 2000000000ull;
 
-        __device__ __forceinline__ uint32_t smem_u32(const void* p)
-        {
-            return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-        }
-        __device__ __forceinline__ void cp_async16(void* dst_smem, const void* src)
-        {
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)),
-                         "l"(src)
-                         : "memory");
-        }
-        __device__ __forceinline__ void cp_async_wait_all()
-        {
-            asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
-        }
         __device__ __forceinline__ void
-            ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p)
+            ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr)
         {
             asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                          : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                         : "r"(smem_u32(p)));
+                         : "r"(addr));
         }
         __device__ __forceinline__ void
-            ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p)
+            ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr)
         {
             asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                          : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                         : "r"(smem_u32(p)));
+                         : "r"(addr));
         }
         // D(16x8, fp32) += A(16x16, fp16, row) x B(16x8, fp16, col)
         __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
@@ -65,47 +60,82 @@ namespace b200wmma
                          : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
         }
 
-        // Copies rows 0..m-1 of one sample (k halfs each, contiguous in global memory) into the
-        // padded shared-memory tile with 16-byte async copies.  Whole warp participates.
-        __device__ __forceinline__ void load_sample(__half* xs, uint32_t xpitch, const __half* src,
-                                                    uint32_t m, uint32_t k, uint32_t lane)
+        // Byte offset, inside a sample tile, of the 16-byte chunk holding columns c..c+7 of row r.
+        // The tile is a sequence of 64-column boxes (BOX_BYTES each, rows of 128 bytes) as written by
+        // TMA with the 128-byte swizzle: chunk index XOR (row mod 8).
+        __device__ __forceinline__ uint32_t tile_off(uint32_t r, uint32_t c)
         {
-            const uint32_t chunks_per_row = k >> 3;
-            const uint32_t total          = m * chunks_per_row;
-            for(uint32_t i = lane; i < total; i += 32)
-            {
-                const uint32_t r = i / chunks_per_row, ch = i - r * chunks_per_row;
-                cp_async16(xs + r * xpitch + ch * 8, src + static_cast<size_t>(r) * k + ch * 8);
-            }
+            return (c >> 6) * BOX_BYTES + r * 128u + ((((c >> 3) & 7u) ^ (r & 7u)) << 4);
         }
 
         // ---------------------------------- forward ----------------------------------------
+        // Shared memory per warp: FWD_STAGES sample tiles, two output rows (double-buffered bulk
+        // stores), FWD_STAGES mbarriers.
         __global__ void __launch_bounds__(WARPS * 32)
-            dlrm_fwd_kernel(const __half* __restrict__ input, __half* __restrict__ output,
+            dlrm_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x, __half* __restrict__ output,
                             uint32_t m, uint32_t m_stride, uint32_t k, uint32_t batch,
-                            uint32_t out_stride)
+                            uint32_t out_stride, unsigned* status)
         {
-            extern __shared__ __align__(16) uint8_t smem[];
+            extern __shared__ uint8_t smem_raw[];
+            const uint32_t raw   = ptx::smem_u32(smem_raw);
+            const uint32_t base  = (raw + 1023u) & ~1023u;
+            uint8_t*       smem  = smem_raw + (base - raw);
             const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-            const uint32_t xpitch   = k + 8;
-            const uint32_t per_warp = MAX_M * xpitch + out_stride; // halfs
-            __half*        xs       = reinterpret_cast<__half*>(smem) + warp * per_warp;
-            __half*        orow     = xs + MAX_M * xpitch;
+            const uint32_t nbox      = (k + 63u) >> 6;
+            const uint32_t tile_b    = nbox * BOX_BYTES;
+            const uint32_t orow_b    = out_stride * 2u; // multiple of 16
+            const uint32_t tiles_off = warp * FWD_STAGES * tile_b;
+            const uint32_t orow_off  = WARPS * FWD_STAGES * tile_b + warp * 2u * orow_b;
+            const uint32_t bar_off   = WARPS * FWD_STAGES * tile_b + WARPS * 2u * orow_b + warp * FWD_STAGES * 8u;
+            const uint32_t flag_off  = WARPS * FWD_STAGES * tile_b + WARPS * 2u * orow_b + WARPS * FWD_STAGES * 8u;
+            volatile uint32_t* cta_abort = reinterpret_cast<volatile uint32_t*>(smem + flag_off);
             const uint32_t g = lane >> 2, t = lane & 3;
             const uint32_t tri_end = k + m * (m - 1) / 2;
+            const uint32_t tx_bytes = nbox * m * 128u; // bytes one sample's boxes deliver
 
-            // rows m..31 take part in the MMA tiles as zeros; they are never overwritten
-            for(uint32_t i = m * xpitch + lane; i < MAX_M * xpitch; i += 32)
-                xs[i] = __float2half(0.0f);
+            // rows m..31 take part in the MMA tiles as zeros; TMA never writes them
+            for(uint32_t s = 0; s < FWD_STAGES; ++s)
+                for(uint32_t bx = 0; bx < nbox; ++bx)
+                    for(uint32_t i = m * 128u + lane * 16u; i < BOX_BYTES; i += 512u)
+                        *reinterpret_cast<uint4*>(smem + tiles_off + s * tile_b + bx * BOX_BYTES + i) = make_uint4(0, 0, 0, 0);
             // columns past the packed triangle are written as zero for every sample
-            for(uint32_t i = tri_end + lane; i < out_stride; i += 32)
-                orow[i] = __float2half(0.0f);
-
-            for(uint32_t b = blockIdx.x * WARPS + warp; b < batch; b += gridDim.x * WARPS)
+            for(uint32_t ob = 0; ob < 2; ++ob)
+                for(uint32_t i = tri_end + lane; i < out_stride; i += 32)
+                    reinterpret_cast<__half*>(smem + orow_off + ob * orow_b)[i] = __float2half(0.0f);
+            if(threadIdx.x == 0)
+                *cta_abort = 0u;
+            if(lane == 0)
             {
-                load_sample(xs, xpitch, input + static_cast<size_t>(b) * m_stride * k, m, k, lane);
-                cp_async_wait_all();
-                __syncwarp();
+                for(uint32_t s = 0; s < FWD_STAGES; ++s)
+                    ptx::mbar_init(base + bar_off + 8u * s, 1);
+                ptx::fence_barrier_init();
+            }
+            ptx::fence_proxy_async_smem(); // the zero fills above precede any TMA write to the same tiles
+            __syncthreads();
+
+            const uint32_t stride = gridDim.x * WARPS;
+            const uint32_t first  = blockIdx.x * WARPS + warp;
+            auto issue_load = [&](uint32_t sample, uint32_t stage) {
+                const uint32_t bar = base + bar_off + 8u * stage;
+                ptx::mbar_arrive_expect_tx(bar, tx_bytes);
+                for(uint32_t bx = 0; bx < nbox; ++bx)
+                    ptx::tma_load_2d(base + tiles_off + stage * tile_b + bx * BOX_BYTES, &tmap_x,
+                                     static_cast<int32_t>(bx * 64u), static_cast<int32_t>(sample * m_stride), bar);
+            };
+            if(lane == 0)
+                for(uint32_t s = 0; s < FWD_STAGES; ++s)
+                    if(first + s * stride < batch)
+                        issue_load(first + s * stride, s);
+
+            uint32_t it = 0;
+            for(uint32_t b = first; b < batch; b += stride, ++it)
+            {
+                const uint32_t stage = it % FWD_STAGES, phase = (it / FWD_STAGES) & 1u;
+                bool ok = ptx::mbar_wait_bounded(base + bar_off + 8u * stage, phase, cta_abort, status,
+                                                 (1u << 28) | blockIdx.x, WAIT_NS);
+                if(!__all_sync(0xFFFFFFFFu, ok))
+                    break;
+                const uint32_t xs = base + tiles_off + stage * tile_b;
 
                 // acc0: rows 0-15 x cols 0-15 ; acc1: rows 16-31 x cols 0-31
                 float acc0[2][4] = {}, acc1[4][4] = {};
@@ -113,18 +143,17 @@ namespace b200wmma
                 for(uint32_t ks = 0; ks < k; ks += 16)
                 {
                     uint32_t a0[4], a1[4], bf[8];
-                    ldmatrix_x4(a0[0], a0[1], a0[2], a0[3],
-                                xs + (lane & 15) * xpitch + ks + (lane >> 4) * 8);
+                    const uint32_t acol = ks + (lane >> 4) * 8;
+                    ldmatrix_x4(a0[0], a0[1], a0[2], a0[3], xs + tile_off(lane & 15, acol));
                     // B = X^T: n index = row of X.  One x4 load covers two 8-wide n tiles.
                     const uint32_t brow = (lane & 7) + (lane >> 4) * 8, bcol = ks + ((lane >> 3) & 1) * 8;
-                    ldmatrix_x4(bf[0], bf[1], bf[2], bf[3], xs + brow * xpitch + bcol);
+                    ldmatrix_x4(bf[0], bf[1], bf[2], bf[3], xs + tile_off(brow, bcol));
                     mma_16816(acc0[0], a0, bf[0], bf[1]);
                     mma_16816(acc0[1], a0, bf[2], bf[3]);
                     if(two_blocks)
                     {
-                        ldmatrix_x4(a1[0], a1[1], a1[2], a1[3],
-                                    xs + (16 + (lane & 15)) * xpitch + ks + (lane >> 4) * 8);
-                        ldmatrix_x4(bf[4], bf[5], bf[6], bf[7], xs + (16 + brow) * xpitch + bcol);
+                        ldmatrix_x4(a1[0], a1[1], a1[2], a1[3], xs + tile_off(16 + (lane & 15), acol));
+                        ldmatrix_x4(bf[4], bf[5], bf[6], bf[7], xs + tile_off(16 + brow, bcol));
                         mma_16816(acc1[0], a1, bf[0], bf[1]);
                         mma_16816(acc1[1], a1, bf[2], bf[3]);
                         mma_16816(acc1[2], a1, bf[4], bf[5]);
@@ -132,9 +161,19 @@ namespace b200wmma
                     }
                 }
 
-                // pack: [ X row 0 | strict lower triangle, row-major ]
-                for(uint32_t i = lane; i < k; i += 32)
-                    orow[i] = xs[i];
+                // the output row used two samples ago must have been read by its bulk store
+                const uint32_t ob = it & 1u;
+                if(lane == 0)
+                    ptx::bulk_wait_group_read<1>();
+                __syncwarp();
+                __half* orow = reinterpret_cast<__half*>(smem + orow_off + ob * orow_b);
+                // pass-through: X row 0 (row 0 is not permuted by the swizzle)
+                if(lane < (k >> 3))
+                    reinterpret_cast<uint4*>(orow)[lane]
+                        = *reinterpret_cast<const uint4*>(smem + tiles_off + stage * tile_b + (lane >> 3) * BOX_BYTES + (lane & 7u) * 16u);
+                __syncwarp(); // every lane is done with this sample tile: refill it
+                if(lane == 0 && b + FWD_STAGES * stride < batch)
+                    issue_load(b + FWD_STAGES * stride, stage);
 #pragma unroll
                 for(int nt = 0; nt < 2; ++nt)
 #pragma unroll
@@ -156,51 +195,107 @@ namespace b200wmma
                                 orow[k + r * (r - 1) / 2 + c] = __float2half_rn(acc1[nt][i]);
                         }
                 }
+                ptx::fence_proxy_async_smem(); // generic writes of orow -> visible to the bulk store
                 __syncwarp();
-                uint4*       dst = reinterpret_cast<uint4*>(output + static_cast<size_t>(b) * out_stride);
-                const uint4* src = reinterpret_cast<const uint4*>(orow);
-                for(uint32_t i = lane; i < (out_stride >> 3); i += 32)
-                    __stcs(dst + i, src[i]);
-                __syncwarp(); // xs / orow are rewritten by the next sample
+                if(lane == 0)
+                {
+                    ptx::bulk_store_1d(output + static_cast<size_t>(b) * out_stride, base + orow_off + ob * orow_b, orow_b);
+                    ptx::bulk_commit_group();
+                }
+            }
+            if(lane == 0)
+                ptx::bulk_wait_group<0>(); // shared memory must outlive the stores that read it
+            __syncwarp();
+            if(*cta_abort)
+            {
+                // a wait was abandoned: give copies still in flight a bounded time to land before
+                // this CTA's shared memory is released
+                const uint64_t t0 = ptx::globaltimer_ns();
+                while(ptx::globaltimer_ns() - t0 < 2000000ull)
+                    __nanosleep(1000);
             }
         }
 
         // ---------------------------------- backward ---------------------------------------
+        // Shared memory per warp: BWD_STAGES x (sample tile + upstream row), the symmetric matrix,
+        // BWD_STAGES mbarriers.
         __global__ void __launch_bounds__(WARPS * 32)
-            dlrm_bwd_kernel(const __half* __restrict__ input, const __half* __restrict__ upstream,
-                            __half* __restrict__ grad, __half* __restrict__ bottom_mlp_grad,
-                            uint32_t m, uint32_t m_stride, uint32_t k, uint32_t batch,
-                            uint32_t up_stride, int fuse_mlp)
+            dlrm_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_g,
+                            const __half* __restrict__ upstream, __half* __restrict__ bottom_mlp_grad,
+                            uint32_t m, uint32_t m_stride, uint32_t k, uint32_t batch, uint32_t up_stride,
+                            int fuse_mlp, unsigned* status)
         {
-            extern __shared__ __align__(16) uint8_t smem[];
+            extern __shared__ uint8_t smem_raw[];
+            const uint32_t raw   = ptx::smem_u32(smem_raw);
+            const uint32_t base  = (raw + 1023u) & ~1023u;
+            uint8_t*       smem  = smem_raw + (base - raw);
             const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-            const uint32_t xpitch   = k + 8;
-            const uint32_t per_warp = MAX_M * xpitch + up_stride + MAX_M * TPITCH; // halfs
-            __half*        xs       = reinterpret_cast<__half*>(smem) + warp * per_warp;
-            __half*        gs       = xs + MAX_M * xpitch; // packed upstream row
-            __half*        ts       = gs + up_stride; // symmetric matrix, 32 x TPITCH
+            const uint32_t nbox     = (k + 63u) >> 6;
+            const uint32_t tile_b   = nbox * BOX_BYTES;
+            const uint32_t up_b     = up_stride * 2u; // multiple of 16
+            const uint32_t up_slot  = (up_b + 127u) & ~127u;
+            const uint32_t tiles_off = warp * BWD_STAGES * tile_b;
+            const uint32_t up_off    = WARPS * BWD_STAGES * tile_b + warp * BWD_STAGES * up_slot;
+            const uint32_t t_off     = WARPS * BWD_STAGES * (tile_b + up_slot) + warp * (MAX_M * TPITCH * 2u);
+            const uint32_t bar_off   = WARPS * BWD_STAGES * (tile_b + up_slot) + WARPS * (MAX_M * TPITCH * 2u) + warp * BWD_STAGES * 8u;
+            const uint32_t flag_off  = WARPS * BWD_STAGES * (tile_b + up_slot) + WARPS * (MAX_M * TPITCH * 2u) + WARPS * BWD_STAGES * 8u;
+            volatile uint32_t* cta_abort = reinterpret_cast<volatile uint32_t*>(smem + flag_off);
+            __half*        ts = reinterpret_cast<__half*>(smem + t_off);
             const uint32_t g = lane >> 2, t = lane & 3;
+            const uint32_t tx_bytes = nbox * m * 128u + up_b;
 
-            for(uint32_t b = blockIdx.x * WARPS + warp; b < batch; b += gridDim.x * WARPS)
+            if(threadIdx.x == 0)
+                *cta_abort = 0u;
+            if(lane == 0)
             {
-                // rows m..31 of X must be zero for the MMA; the tile is overwritten with dX
-                // below, so they are cleared for every sample
-                for(uint32_t i = m * xpitch + lane; i < MAX_M * xpitch; i += 32)
-                    xs[i] = __float2half(0.0f);
-                load_sample(xs, xpitch, input + static_cast<size_t>(b) * m_stride * k, m, k, lane);
-                {
-                    const __half* up = upstream + static_cast<size_t>(b) * up_stride;
-                    for(uint32_t i = lane; i < (up_stride >> 3); i += 32)
-                        cp_async16(gs + i * 8, up + i * 8);
-                }
-                cp_async_wait_all();
-                __syncwarp();
+                for(uint32_t s = 0; s < BWD_STAGES; ++s)
+                    ptx::mbar_init(base + bar_off + 8u * s, 1);
+                ptx::fence_barrier_init();
+            }
+            __syncthreads();
+
+            const uint32_t stride = gridDim.x * WARPS;
+            const uint32_t first  = blockIdx.x * WARPS + warp;
+            // rows m..31 of a tile must be zero for the MMA; TMA never writes them
+            auto clear_pad_rows = [&](uint32_t stage) {
+                for(uint32_t bx = 0; bx < nbox; ++bx)
+                    for(uint32_t i = m * 128u + lane * 16u; i < BOX_BYTES; i += 512u)
+                        *reinterpret_cast<uint4*>(smem + tiles_off + stage * tile_b + bx * BOX_BYTES + i) = make_uint4(0, 0, 0, 0);
+            };
+            auto issue_load = [&](uint32_t sample, uint32_t stage) {
+                const uint32_t bar = base + bar_off + 8u * stage;
+                ptx::mbar_arrive_expect_tx(bar, tx_bytes);
+                for(uint32_t bx = 0; bx < nbox; ++bx)
+                    ptx::tma_load_2d(base + tiles_off + stage * tile_b + bx * BOX_BYTES, &tmap_x,
+                                     static_cast<int32_t>(bx * 64u), static_cast<int32_t>(sample * m_stride), bar);
+                ptx::bulk_load_1d(base + up_off + stage * up_slot, upstream + static_cast<size_t>(sample) * up_stride, up_b, bar);
+            };
+            for(uint32_t s = 0; s < BWD_STAGES; ++s)
+                clear_pad_rows(s);
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if(lane == 0)
+                for(uint32_t s = 0; s < BWD_STAGES; ++s)
+                    if(first + s * stride < batch)
+                        issue_load(first + s * stride, s);
+
+            uint32_t it = 0;
+            for(uint32_t b = first; b < batch; b += stride, ++it)
+            {
+                const uint32_t stage = it % BWD_STAGES, phase = (it / BWD_STAGES) & 1u;
+                bool ok = ptx::mbar_wait_bounded(base + bar_off + 8u * stage, phase, cta_abort, status,
+                                                 (2u << 28) | blockIdx.x, WAIT_NS);
+                if(!__all_sync(0xFFFFFFFFu, ok))
+                    break;
+                const uint32_t xs_off = tiles_off + stage * tile_b;
+                const uint32_t xs     = base + xs_off;
+                const __half*  gs     = reinterpret_cast<const __half*>(smem + up_off + stage * up_slot);
 
                 // symmetric matrix with zero diagonal; lane = column index
                 for(uint32_t i = 0; i < MAX_M; ++i)
                 {
-                    const uint32_t j  = lane;
-                    __half         v  = __float2half(0.0f);
+                    const uint32_t j = lane;
+                    __half         v = __float2half(0.0f);
                     if(i < m && j < m && i != j)
                     {
                         const uint32_t hi = max(i, j), lo = min(i, j);
@@ -208,23 +303,17 @@ namespace b200wmma
                     }
                     ts[i * TPITCH + j] = v;
                 }
-                if(bottom_mlp_grad)
-                {
-                    uint4*       dst = reinterpret_cast<uint4*>(bottom_mlp_grad + static_cast<size_t>(b) * k);
-                    const uint4* src = reinterpret_cast<const uint4*>(gs);
-                    for(uint32_t i = lane; i < (k >> 3); i += 32)
-                        __stcs(dst + i, src[i]);
-                }
                 __syncwarp();
 
                 // A fragments of the symmetric matrix: [row block][k step]
                 uint32_t af[2][2][4];
+                const uint32_t ts_addr = base + t_off;
 #pragma unroll
                 for(int rb = 0; rb < 2; ++rb)
 #pragma unroll
                     for(int ks = 0; ks < 2; ++ks)
                         ldmatrix_x4(af[rb][ks][0], af[rb][ks][1], af[rb][ks][2], af[rb][ks][3],
-                                    ts + (16 * rb + (lane & 15)) * TPITCH + 16 * ks + (lane >> 4) * 8);
+                                    ts_addr + ((16 * rb + (lane & 15)) * TPITCH + 16 * ks + (lane >> 4) * 8) * 2u);
 
                 // dX[:, n0:n0+16] depends only on X[:, n0:n0+16]: compute a 16-column slab,
                 // then overwrite those columns of the shared tile with the result.
@@ -235,8 +324,7 @@ namespace b200wmma
 #pragma unroll
                     for(int ks = 0; ks < 2; ++ks)
                         ldmatrix_x4_trans(bf[ks][0], bf[ks][1], bf[ks][2], bf[ks][3],
-                                          xs + (16 * ks + (lane & 7) + ((lane >> 3) & 1) * 8) * xpitch
-                                              + n0 + (lane >> 4) * 8);
+                                          xs + tile_off(16 * ks + (lane & 7) + ((lane >> 3) & 1) * 8, n0 + (lane >> 4) * 8));
 #pragma unroll
                     for(int rb = 0; rb < 2; ++rb)
 #pragma unroll
@@ -260,22 +348,37 @@ namespace b200wmma
                                     v0 += __half2float(gs[c]);
                                     v1 += __half2float(gs[c + 1]);
                                 }
-                                *reinterpret_cast<__half2*>(xs + r * xpitch + c)
+                                *reinterpret_cast<__half2*>(smem + xs_off + tile_off(r, c) + (c & 7u) * 2u)
                                     = __floats2half2_rn(v0, v1);
                             }
                 }
+                ptx::fence_proxy_async_smem(); // generic writes of dX -> visible to the TMA stores
                 __syncwarp();
+                if(lane == 0)
                 {
-                    __half*        dst            = grad + static_cast<size_t>(b) * m_stride * k;
-                    const uint32_t chunks_per_row = k >> 3;
-                    for(uint32_t i = lane; i < m * chunks_per_row; i += 32)
-                    {
-                        const uint32_t r = i / chunks_per_row, ch = i - r * chunks_per_row;
-                        __stcs(reinterpret_cast<uint4*>(dst + static_cast<size_t>(r) * k + ch * 8),
-                               *reinterpret_cast<const uint4*>(xs + r * xpitch + ch * 8));
-                    }
+                    for(uint32_t bx = 0; bx < nbox; ++bx)
+                        ptx::tma_store_2d(&tmap_g, static_cast<int32_t>(bx * 64u), static_cast<int32_t>(b * m_stride),
+                                          xs + bx * BOX_BYTES);
+                    if(bottom_mlp_grad)
+                        ptx::bulk_store_1d(bottom_mlp_grad + static_cast<size_t>(b) * k, base + up_off + stage * up_slot, k * 2u);
+                    ptx::bulk_commit_group();
+                    // the stage is reloaded as soon as the stores above have read it
+                    ptx::bulk_wait_group_read<0>();
                 }
                 __syncwarp();
+                // rows m..31 of the tile still hold zeros: the product of the zero rows of the
+                // symmetric matrix was written over them
+                if(lane == 0 && b + BWD_STAGES * stride < batch)
+                    issue_load(b + BWD_STAGES * stride, stage);
+            }
+            if(lane == 0)
+                ptx::bulk_wait_group<0>();
+            __syncwarp();
+            if(*cta_abort)
+            {
+                const uint64_t t0 = ptx::globaltimer_ns();
+                while(ptx::globaltimer_ns() - t0 < 2000000ull)
+                    __nanosleep(1000);
             }
         }
 
@@ -290,6 +393,8 @@ namespace b200wmma
                          "dlrm: m = %u not supported (this kernel handles m <= %d)", m, MAX_M);
             B200_REQUIRE(k % 16 == 0 && k <= MAX_K, B200WMMA_ERR_UNSUPPORTED,
                          "dlrm: k = %u not supported (multiple of 16, <= %d)", k, MAX_K);
+            B200_REQUIRE(static_cast<uint64_t>(batch) * m_stride < (1ull << 31), B200WMMA_ERR_UNSUPPORTED,
+                         "dlrm: batch * m_stride must stay below 2^31 rows");
             B200_REQUIRE(aligned16(input), B200WMMA_ERR_ALIGNMENT, "dlrm: input must be 16-byte aligned");
             return B200WMMA_OK;
         }
@@ -305,6 +410,13 @@ namespace b200wmma
             const uint32_t want = ceil_div(batch, WARPS);
             const uint32_t cap  = static_cast<uint32_t>(sms) * per_sm;
             return want < cap ? want : cap;
+        }
+
+        // 2-D view [(batch-1)*m_stride + m rows, k columns] of a sample buffer: only real rows are covered.
+        static int sample_tmap(CUtensorMap* out, const void* ptr, uint32_t m, uint32_t m_stride, uint32_t k,
+                               uint32_t batch)
+        {
+            return tc05::make_kmajor_tmap(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, ptr, (batch - 1) * m_stride + m, k, k, m);
         }
     } // namespace dlrm
 } // namespace b200wmma
@@ -326,7 +438,14 @@ extern "C" int b200wmma_dlrm_fwd(const void* input, void* output, uint32_t m, ui
     B200_REQUIRE(out_stride <= 2048, B200WMMA_ERR_UNSUPPORTED, "dlrm_fwd: out_stride too large");
     if(int e = require_sm100())
         return e;
-    const size_t smem = static_cast<size_t>(WARPS) * (MAX_M * (k + 8) + out_stride) * sizeof(__half);
+    unsigned* status = nullptr;
+    if(int e = status_word_ptr(&status))
+        return e;
+    CUtensorMap tm_x;
+    if(int e = sample_tmap(&tm_x, input, m, m_stride, k, batch))
+        return e;
+    const uint32_t nbox = (k + 63) / 64;
+    const size_t   smem = 1024 + static_cast<size_t>(WARPS) * (FWD_STAGES * nbox * BOX_BYTES + 2 * out_stride * 2 + FWD_STAGES * 8) + 16;
     static size_t attr_set = 0;
     if(smem > 48 * 1024 && smem > attr_set)
     {
@@ -335,8 +454,8 @@ extern "C" int b200wmma_dlrm_fwd(const void* input, void* output, uint32_t m, ui
         attr_set = smem;
     }
     const uint32_t grid = grid_for(batch, reinterpret_cast<const void*>(dlrm_fwd_kernel), smem);
-    dlrm_fwd_kernel<<<grid, WARPS * 32, smem, as_stream(stream)>>>(
-        static_cast<const __half*>(input), static_cast<__half*>(output), m, m_stride, k, batch, out_stride);
+    dlrm_fwd_kernel<<<grid, WARPS * 32, smem, as_stream(stream)>>>(tm_x, static_cast<__half*>(output), m, m_stride, k,
+                                                                    batch, out_stride, status);
     B200_CHECK_CUDA(cudaGetLastError());
     return B200WMMA_OK;
 }
@@ -362,8 +481,19 @@ extern "C" int b200wmma_dlrm_bwd(const void* input, const void* upstream, void* 
     B200_REQUIRE(upstream_stride <= 2048, B200WMMA_ERR_UNSUPPORTED, "dlrm_bwd: upstream_stride too large");
     if(int e = require_sm100())
         return e;
-    const size_t smem = static_cast<size_t>(WARPS) * (MAX_M * (k + 8) + upstream_stride + MAX_M * TPITCH)
-                        * sizeof(__half);
+    unsigned* status = nullptr;
+    if(int e = status_word_ptr(&status))
+        return e;
+    CUtensorMap tm_x, tm_g;
+    if(int e = sample_tmap(&tm_x, input, m, m_stride, k, batch))
+        return e;
+    if(int e = sample_tmap(&tm_g, grad, m, m_stride, k, batch))
+        return e;
+    const uint32_t nbox    = (k + 63) / 64;
+    const uint32_t up_slot = (upstream_stride * 2 + 127) & ~127u;
+    const size_t   smem    = 1024
+                        + static_cast<size_t>(WARPS) * (BWD_STAGES * (nbox * BOX_BYTES + up_slot) + MAX_M * TPITCH * 2 + BWD_STAGES * 8)
+                        + 16;
     static size_t attr_set = 0;
     if(smem > 48 * 1024 && smem > attr_set)
     {
@@ -373,8 +503,8 @@ extern "C" int b200wmma_dlrm_bwd(const void* input, const void* upstream, void* 
     }
     const uint32_t grid = grid_for(batch, reinterpret_cast<const void*>(dlrm_bwd_kernel), smem);
     dlrm_bwd_kernel<<<grid, WARPS * 32, smem, as_stream(stream)>>>(
-        static_cast<const __half*>(input), static_cast<const __half*>(upstream), static_cast<__half*>(grad),
-        static_cast<__half*>(bottom_mlp_grad), m, m_stride, k, batch, upstream_stride, fuse_mlp_into_row0);
+        tm_x, tm_g, static_cast<const __half*>(upstream), static_cast<__half*>(bottom_mlp_grad), m, m_stride, k, batch,
+        upstream_stride, fuse_mlp_into_row0, status);
     B200_CHECK_CUDA(cudaGetLastError());
     return B200WMMA_OK;
 }

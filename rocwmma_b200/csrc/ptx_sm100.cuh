@@ -168,6 +168,51 @@ namespace b200wmma
                          : "memory");
         }
 
+        // 1-D bulk copy global -> shared (this CTA); both addresses 16-byte aligned, size a multiple of 16.
+        __device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar)
+        {
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                             dst_smem),
+                         "l"(src),
+                         "r"(bytes),
+                         "r"(bar)
+                         : "memory");
+        }
+        // 1-D bulk copy shared -> global, tracked by the issuing thread's bulk async-group.
+        __device__ __forceinline__ void bulk_store_1d(void* dst, uint32_t src_smem, uint32_t bytes)
+        {
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem),
+                         "r"(bytes)
+                         : "memory");
+        }
+        // 2-D tiled store shared -> global.  c0 * element size must be a multiple of 16 bytes and
+        // neither coordinate may be negative.
+        __device__ __forceinline__ void tma_store_2d(const void* tmap, int32_t c0, int32_t c1, uint32_t src_smem)
+        {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                             reinterpret_cast<uint64_t>(tmap)),
+                         "r"(c0),
+                         "r"(c1),
+                         "r"(src_smem)
+                         : "memory");
+        }
+        __device__ __forceinline__ void bulk_commit_group()
+        {
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        // Wait until at most N of this thread's bulk groups still have to READ their shared-memory source.
+        template <int N>
+        __device__ __forceinline__ void bulk_wait_group_read()
+        {
+            asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+        }
+        // Wait until at most N of this thread's bulk groups are still incomplete (writes performed).
+        template <int N>
+        __device__ __forceinline__ void bulk_wait_group()
+        {
+            asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+        }
+
         // ---- tcgen05 / tensor memory ----------------------------------------------------
         __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols)
         {
