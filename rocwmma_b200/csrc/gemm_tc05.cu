@@ -20,6 +20,7 @@
 // Every barrier wait is bounded (see ptx::mbar_wait_bounded).
 #include "gemm_tc05_common.cuh"
 #include "gemm_tc05_pair.cuh"
+#include "gemm_tc05_pair512.cuh"
 
 #include <cstdlib>
 #include <cstring>
@@ -266,7 +267,8 @@ namespace b200wmma
             return v > 0 ? static_cast<uint32_t>(v) : dflt;
         }
 
-        // 0 = automatic, 1 = one-CTA tiles, 2 = two-CTA tiles (environment override for A/B comparisons)
+        // 0 = automatic, 1 = one-CTA tiles, 2 = two-CTA 256x256 pair tiles, 3 = two-CTA 512x256 pair tiles
+        // (environment override for A/B comparisons)
         static int forced_variant()
         {
             static int v = []() {
@@ -275,6 +277,8 @@ namespace b200wmma
                     return 1;
                 if(e && std::strcmp(e, "2cta") == 0)
                     return 2;
+                if(e && std::strcmp(e, "2cta512") == 0)
+                    return 3;
                 return 0;
             }();
             return v;
@@ -331,15 +335,61 @@ namespace b200wmma
             B200_CHECK_CUDA(cudaGetDevice(&dev));
             B200_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
 
-            // Two-CTA tiles (256 x 256 per SM pair) unless the problem has a single 128-row band or
-            // the one-CTA kernel is requested explicitly (B200WMMA_GEMM_VARIANT=1cta, for comparison).
+            // Tile shape: 512 x 256 per SM pair when there are more than 256 rows, 256 x 256 per pair for
+            // 129..256 rows, one-CTA 128 x 256 tiles for a single 128-row band
+            // (B200WMMA_GEMM_VARIANT=1cta|2cta|2cta512 forces one, for comparison).
             const int  forced   = forced_variant();
-            const bool use_pair = forced == 2 || (forced == 0 && m > BLOCK_M);
+            const bool use_q    = forced == 3 || (forced == 0 && m > tc05p::PAIR_M);
+            const bool use_pair = !use_q && (forced == 2 || (forced == 0 && m > BLOCK_M));
             CUtensorMap tm_a, tm_b;
-            if(int e = make_kmajor_tmap(&tm_a, dt, EB, a, m, k, lda, BLOCK_M))
+            if(int e = make_kmajor_tmap(&tm_a, dt, EB, a, m, k, lda, use_q ? tc05q::CTA_M : BLOCK_M))
                 return e;
-            if(int e = make_kmajor_tmap(&tm_b, dt, EB, b, n, k, ldb, use_pair ? tc05p::HALF_N : BLOCK_N))
+            if(int e = make_kmajor_tmap(&tm_b, dt, EB, b, n, k, ldb, (use_pair || use_q) ? tc05p::HALF_N : BLOCK_N))
                 return e;
+
+            if(use_q)
+            {
+                auto        kern    = tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT>;
+                static int  max_clusters = 0; // one per template instantiation
+                const uint32_t tiles_m = ceil_div(m, tc05q::PAIR_M), tiles_n = ceil_div(n, tc05q::TILE_N);
+                cudaLaunchConfig_t  cfg = {};
+                cudaLaunchAttribute attr[1];
+                attr[0].id               = cudaLaunchAttributeClusterDimension;
+                attr[0].val.clusterDim.x = 2;
+                attr[0].val.clusterDim.y = 1;
+                attr[0].val.clusterDim.z = 1;
+                cfg.blockDim         = dim3(tc05q::NUM_THREADS);
+                cfg.dynamicSmemBytes = tc05q::SMEM_BYTES;
+                cfg.stream           = stream;
+                cfg.attrs            = attr;
+                cfg.numAttrs         = 1;
+                if(max_clusters == 0)
+                {
+                    B200_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                         tc05q::SMEM_BYTES));
+                    cfg.gridDim = dim3(static_cast<unsigned>(sms) & ~1u);
+                    int nc      = 0;
+                    B200_CHECK_CUDA(cudaOccupancyMaxActiveClusters(&nc, kern, &cfg));
+                    B200_REQUIRE(nc > 0, B200WMMA_ERR_CUDA, "no two-CTA cluster of the GEMM kernel fits on this device");
+                    max_clusters = nc;
+                }
+                const uint32_t pairs = min(tiles_m * tiles_n, static_cast<uint32_t>(max_clusters));
+                cfg.gridDim          = dim3(2 * pairs);
+                // C / D staging boxes for the TMA epilogue (used when the rows are 16-byte aligned)
+                CUtensorMap tm_c = tm_a, tm_d = tm_a; // placeholders, never dereferenced when vec_ok == 0
+                if(vec_ok != 0)
+                {
+                    if(int e = make_rowbox_tmap(&tm_d, sizeof(OutT), d, m, n, ldd))
+                        return e;
+                    tm_c = tm_d;
+                    if(c)
+                        if(int e = make_rowbox_tmap(&tm_c, sizeof(OutT), c, m, n, ldc))
+                            return e;
+                }
+                B200_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, tm_c, tm_d, c, d, m, n, k * EB, ldc, ldd, alpha,
+                                                   beta, tiles_m, tiles_n, vec_ok, group_override(tc05q::GROUP_M), status));
+                return B200WMMA_OK;
+            }
 
             if(use_pair)
             {

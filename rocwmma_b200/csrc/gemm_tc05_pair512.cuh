@@ -1,0 +1,410 @@
+// Two-CTA tcgen05 GEMM with 256 x 256 outputs per CTA (512 x 256 per SM pair).
+//
+// Why a second pair kernel: the 256 x 256-per-pair kernel (gemm_tc05_pair.cuh) moves 32 KiB of
+// operands per CTA per 64-wide K slab for 128 x 256 x 64 of work.  Here a CTA keeps 256 rows of A
+// (two 128-row sub-tiles) against the same half B slab: 48 KiB per slab for twice the work, i.e. a
+// quarter less L2 -> SM traffic and fewer DRAM re-reads per flop.  On a power-capped part that is
+// clock speed.  The price: the two 128 x 256 fp32 accumulators fill all 512 tensor-memory columns,
+// so the accumulators are not double-buffered and the epilogue has to be short.  It is made short
+// by (a) eight epilogue warps (one lane quadrant of one accumulator each), (b) moving C and D
+// through small swizzled shared-memory tiles with TMA - a thread-per-row global access touches 32
+// different cache lines per warp instruction, which costs ~32 LSU cycles each and dominated the
+// drain - with the first C steps requested while the tile is still being multiplied, and
+// (c) releasing each accumulator to the MMA issuer separately.
+//
+// Roles (320 threads): warp 0 TMA producer (one lane), warp 1 tensor-memory owner / MMA issuer
+// (one lane, leader CTA only), warps 2-9 epilogue.  Barrier protocol as in gemm_tc05_pair.cuh
+// (loads of both CTAs counted on the leader's full[s]; commits signal both CTAs), with one
+// tmem_full barrier per tile and one tmem_empty barrier per accumulator.
+#pragma once
+#include "gemm_tc05_common.cuh"
+
+namespace b200wmma
+{
+    namespace tc05q
+    {
+        using namespace tc05;
+
+        constexpr uint32_t SUB_M         = 128; // rows per MMA per CTA
+        constexpr uint32_t CTA_M         = 256; // rows of A / D per CTA (two accumulators)
+        constexpr uint32_t PAIR_M        = 512;
+        constexpr uint32_t TILE_N        = 256;
+        constexpr uint32_t HALF_N        = 128;
+        constexpr uint32_t STAGES        = 4;
+        constexpr uint32_t A_STAGE_BYTES = CTA_M * BLOCK_K_BYTES; // 32 KiB
+        constexpr uint32_t B_STAGE_BYTES = HALF_N * BLOCK_K_BYTES; // 16 KiB
+        constexpr uint32_t STAGE_BYTES   = A_STAGE_BYTES + B_STAGE_BYTES;
+        constexpr uint32_t EPI_WARPS     = 8;
+        constexpr uint32_t NUM_THREADS   = 64 + EPI_WARPS * 32;
+        constexpr uint32_t TMEM_COLS     = 512;
+        constexpr uint32_t GROUP_M       = 4; // rasterisation band: 4 pair-row tiles = 2048 rows
+        constexpr uint32_t EPI_BUF_BYTES = 2048; // 32 rows x 64 bytes, TMA SWIZZLE_64B
+        constexpr uint32_t EPI_BYTES     = EPI_WARPS * 2 * EPI_BUF_BYTES; // two staging tiles per epilogue warp
+        constexpr uint32_t MISC_BYTES    = 512; // barriers, tensor-memory slot, abort flag
+        constexpr uint32_t SMEM_BYTES    = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + MISC_BYTES;
+
+        // Epilogue of one warp through shared-memory staging tiles.
+        // A step covers 64 bytes of each of the warp's 32 rows (32 columns of 2-byte outputs, 16
+        // columns of 4-byte outputs).  Per step: tcgen05.ld the accumulator columns, wait for the C
+        // tile of the step (TMA, requested two steps earlier), combine in place (each lane owns one
+        // row of the tile; the 64-byte swizzle keeps the 16-byte accesses conflict-free), hand the
+        // tile to a TMA store and request the C tile two steps ahead into the same buffer once the
+        // store has read it.  TMA clips rows / columns outside the matrix, so ragged edges need no
+        // special case.  All 32 lanes execute every step.
+        template <typename OutT, typename ScalarT>
+        struct StagedDrain
+        {
+            static constexpr uint32_t STEP_COLS = 64 / sizeof(OutT);
+            static constexpr uint32_t STEPS     = TILE_N / STEP_COLS;
+
+            // requests the C tiles of steps 0 and 1 (called while the tile is still being multiplied)
+            __device__ static __forceinline__ void prefetch_c(const CUtensorMap* tmap_c, uint32_t buf0, uint32_t cbar0,
+                                                             uint32_t col_base, uint32_t row0, uint32_t n)
+            {
+                ptx::bulk_wait_group_read<0>(); // the previous tile's last stores have read both buffers
+#pragma unroll
+                for(uint32_t s = 0; s < 2; ++s)
+                {
+                    if(col_base + s * STEP_COLS >= n)
+                        break; // steps that start right of the matrix are skipped everywhere
+                    ptx::mbar_arrive_expect_tx(cbar0 + 8 * s, EPI_BUF_BYTES);
+                    ptx::tma_load_2d(buf0 + s * EPI_BUF_BYTES, tmap_c, static_cast<int32_t>(col_base + s * STEP_COLS),
+                                     static_cast<int32_t>(row0), cbar0 + 8 * s);
+                }
+            }
+
+            __device__ static __forceinline__ bool run(uint32_t tmem_acc, uint32_t quad, uint32_t lane, uint8_t* smem,
+                                                       uint32_t buf_off, uint32_t buf0, uint32_t cbar0,
+                                                       const CUtensorMap* tmap_c, const CUtensorMap* tmap_d,
+                                                       uint32_t col_base, uint32_t row0, uint32_t n, ScalarT alpha,
+                                                       ScalarT beta, bool read_c, uint32_t& cpar,
+                                                       volatile uint32_t* cta_abort, unsigned* status, uint32_t who)
+            {
+                // cpar: bit b = parity of the next completed C load into staging buffer b (kept across tiles)
+                const uint32_t row_sw = (lane >> 1) & 3u; // 64-byte swizzle phase of this lane's row
+#pragma unroll 2
+                for(uint32_t s = 0; s < STEPS; ++s)
+                {
+                    const uint32_t bi = s & 1u;
+                    uint32_t       v[STEP_COLS];
+                    if constexpr(STEP_COLS == 32)
+                        ptx::tmem_ld_32x32b_x32(tmem_acc + ((quad * 32u) << 16) + s * STEP_COLS, v);
+                    else
+                        ptx::tmem_ld_32x32b_x16(tmem_acc + ((quad * 32u) << 16) + s * STEP_COLS, v);
+                    if(col_base + s * STEP_COLS >= n)
+                    {
+                        // this step lies right of the matrix (ragged N): nothing to load, combine or store
+                        ptx::tmem_ld_wait();
+                        continue;
+                    }
+                    if(read_c)
+                    {
+                        bool ok = ptx::mbar_wait_bounded(cbar0 + 8 * bi, (cpar >> bi) & 1u, cta_abort, status, who,
+                                                         WAIT_TIMEOUT_NS);
+                        if(!__all_sync(0xFFFFFFFFu, ok))
+                        {
+                            ptx::tmem_ld_wait();
+                            return false;
+                        }
+                        cpar ^= 1u << bi;
+                    }
+                    else
+                    {
+                        if(lane == 0)
+                            ptx::bulk_wait_group_read<1>(); // the store issued two steps ago has read this buffer
+                        __syncwarp();
+                    }
+                    ptx::tmem_ld_wait();
+                    uint8_t* rowp = smem + buf_off + bi * EPI_BUF_BYTES + lane * 64u;
+#pragma unroll
+                    for(uint32_t q = 0; q < 4; ++q)
+                    {
+                        uint4* cell = reinterpret_cast<uint4*>(rowp + ((q ^ row_sw) << 4));
+                        uint4  cv   = make_uint4(0, 0, 0, 0);
+                        if(read_c)
+                            cv = *cell;
+                        const uint32_t cwv[4] = {cv.x, cv.y, cv.z, cv.w};
+                        uint32_t       ow[4];
+#pragma unroll
+                        for(uint32_t w = 0; w < 4; ++w)
+                        {
+                            if constexpr(sizeof(OutT) == 2)
+                            {
+                                const float2  cf = __half22float2(*reinterpret_cast<const __half2*>(&cwv[w]));
+                                const __half2 h  = __floats2half2_rn(
+                                    epi(__uint_as_float(v[8 * q + 2 * w]), cf.x, alpha, beta),
+                                    epi(__uint_as_float(v[8 * q + 2 * w + 1]), cf.y, alpha, beta));
+                                ow[w] = *reinterpret_cast<const uint32_t*>(&h);
+                            }
+                            else if constexpr(std::is_same<OutT, float>::value)
+                                ow[w] = __float_as_uint(epi(__uint_as_float(v[4 * q + w]), __uint_as_float(cwv[w]), alpha, beta));
+                            else
+                                ow[w] = static_cast<uint32_t>(
+                                    epi(static_cast<int32_t>(v[4 * q + w]), static_cast<int32_t>(cwv[w]), alpha, beta));
+                        }
+                        *cell = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                    }
+                    ptx::fence_proxy_async_smem(); // the tile written above -> visible to the TMA store
+                    __syncwarp();
+                    if(lane == 0)
+                    {
+                        ptx::tma_store_2d(tmap_d, static_cast<int32_t>(col_base + s * STEP_COLS), static_cast<int32_t>(row0),
+                                          buf0 + bi * EPI_BUF_BYTES);
+                        ptx::bulk_commit_group();
+                        if(read_c && s + 2 < STEPS && col_base + (s + 2) * STEP_COLS < n)
+                        {
+                            ptx::bulk_wait_group_read<0>(); // the store has read the buffer: refill it with C
+                            ptx::mbar_arrive_expect_tx(cbar0 + 8 * bi, EPI_BUF_BYTES);
+                            ptx::tma_load_2d(buf0 + bi * EPI_BUF_BYTES, tmap_c,
+                                             static_cast<int32_t>(col_base + (s + 2) * STEP_COLS), static_cast<int32_t>(row0),
+                                             cbar0 + 8 * bi);
+                        }
+                    }
+                }
+                return true;
+            }
+        };
+
+        template <int KIND, typename OutT, typename ScalarT>
+        __global__ void __launch_bounds__(NUM_THREADS, 1)
+            gemm_tc05_pair512_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                     const __grid_constant__ CUtensorMap tmap_b,
+                                     const __grid_constant__ CUtensorMap tmap_c, // 32-row x 64-byte boxes of C
+                                     const __grid_constant__ CUtensorMap tmap_d, // ... and of D (both unused if vec_ok == 0)
+                                     const OutT* __restrict__ c,
+                                     OutT* __restrict__ d,
+                                     uint32_t  m,
+                                     uint32_t  n,
+                                     uint32_t  k_bytes,
+                                     uint32_t  ldc,
+                                     uint32_t  ldd,
+                                     ScalarT   alpha,
+                                     ScalarT   beta,
+                                     uint32_t  tiles_m, // pair tiles along M (512 rows each)
+                                     uint32_t  tiles_n,
+                                     int       vec_ok,
+                                     uint32_t  group_m,
+                                     unsigned* status)
+        {
+            extern __shared__ uint8_t smem_raw[];
+            const uint32_t            raw_addr = ptx::smem_u32(smem_raw);
+            const uint32_t            base     = (raw_addr + 1023u) & ~1023u;
+            uint8_t*                  smem     = smem_raw + (base - raw_addr);
+
+            // [A stages][B stages][epilogue staging tiles][barriers, tensor-memory slot, abort flag]
+            const uint32_t     smem_a     = base;
+            const uint32_t     smem_b     = base + STAGES * A_STAGE_BYTES;
+            const uint32_t     epi_off    = STAGES * STAGE_BYTES;
+            const uint32_t     misc_off   = epi_off + EPI_BYTES;
+            const uint32_t     bar_base   = base + misc_off;
+            const uint32_t     full_bar   = bar_base; // STAGES x 8 (leader's copy in use)
+            const uint32_t     empty_bar  = bar_base + 32;
+            const uint32_t     tfull_bar  = bar_base + 64;
+            const uint32_t     tempty_bar = bar_base + 72; // 2 x 8, one per accumulator (leader's copy in use)
+            const uint32_t     cbar_base  = bar_base + 96; // EPI_WARPS x 2 x 8: C tiles of the epilogue warps
+            uint32_t*          tmem_slot  = reinterpret_cast<uint32_t*>(smem + misc_off + 96 + EPI_WARPS * 16);
+            volatile uint32_t* cta_abort  = tmem_slot + 1;
+
+            const uint32_t warp      = threadIdx.x >> 5;
+            const uint32_t lane      = threadIdx.x & 31u;
+            const uint32_t rank      = ptx::cluster_ctarank();
+            const uint32_t pair      = blockIdx.x >> 1;
+            const uint32_t num_pairs = gridDim.x >> 1;
+            const uint32_t num_tiles = tiles_m * tiles_n;
+            const uint32_t num_kb    = (k_bytes + BLOCK_K_BYTES - 1) / BLOCK_K_BYTES;
+
+            if(threadIdx.x == 0)
+            {
+                ptx::prefetch_tensormap(&tmap_a);
+                ptx::prefetch_tensormap(&tmap_b);
+                ptx::prefetch_tensormap(&tmap_c);
+                ptx::prefetch_tensormap(&tmap_d);
+                for(uint32_t s = 0; s < STAGES; ++s)
+                {
+                    ptx::mbar_init(full_bar + 8 * s, 1);
+                    ptx::mbar_init(empty_bar + 8 * s, 1);
+                }
+                ptx::mbar_init(tfull_bar, 1);
+                ptx::mbar_init(tempty_bar, 8); // accumulator 0: 4 warps x 2 CTAs
+                ptx::mbar_init(tempty_bar + 8, 8); // accumulator 1
+                for(uint32_t i = 0; i < EPI_WARPS * 2; ++i)
+                    ptx::mbar_init(cbar_base + 8 * i, 1);
+                *cta_abort = 0u;
+                ptx::fence_barrier_init();
+                ptx::fence_proxy_async_smem();
+            }
+            if(warp == 1)
+            {
+                ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), TMEM_COLS);
+                ptx::tmem_relinquish_pair();
+            }
+            ptx::tc_fence_before_sync();
+            ptx::cluster_sync();
+            ptx::tc_fence_after_sync();
+            const uint32_t tmem_base = *tmem_slot;
+
+            if(warp == 0)
+            {
+                // ------------------------------ TMA producer (both CTAs) ------------------------------
+                if(lane == 0)
+                {
+                    uint32_t stage = 0, phase = 0;
+                    bool     ok = true;
+                    for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs)
+                    {
+                        uint32_t m_idx, n_idx;
+                        tile_coords(tile, tiles_m, tiles_n, group_m, m_idx, n_idx);
+                        const int32_t row_a = static_cast<int32_t>(m_idx * PAIR_M + rank * CTA_M);
+                        const int32_t row_b = static_cast<int32_t>(n_idx * TILE_N + rank * HALF_N);
+                        for(uint32_t kb = 0; kb < num_kb; ++kb)
+                        {
+                            ok = ptx::mbar_wait_bounded(empty_bar + 8 * stage, phase ^ 1u, cta_abort, status,
+                                                        (ROLE_PRODUCER << 24) | blockIdx.x, WAIT_TIMEOUT_NS);
+                            if(!ok)
+                                break;
+                            if(rank == 0)
+                                ptx::mbar_arrive_expect_tx(full_bar + 8 * stage, 2u * STAGE_BYTES);
+                            const uint32_t leader_full = ptx::mapa(full_bar + 8 * stage, 0u);
+                            const int32_t  kc          = static_cast<int32_t>(
+                                kb * (KIND == KIND_F16 ? BLOCK_K_BYTES / 2 : BLOCK_K_BYTES));
+                            ptx::tma_load_2d_pair(smem_a + stage * A_STAGE_BYTES, &tmap_a, kc, row_a, leader_full);
+                            ptx::tma_load_2d_pair(smem_b + stage * B_STAGE_BYTES, &tmap_b, kc, row_b, leader_full);
+                            if(++stage == STAGES)
+                            {
+                                stage = 0;
+                                phase ^= 1u;
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+            else if(warp == 1)
+            {
+                // ------------------------------- MMA issuer (leader only) -------------------------------
+                if(lane == 0 && rank == 0)
+                {
+                    constexpr uint32_t idesc = make_idesc<KIND, 2 * SUB_M, TILE_N>();
+                    uint32_t           stage = 0, phase = 0, iter = 0;
+                    bool               ok = true;
+                    for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++iter)
+                    {
+                        const uint32_t tphase = iter & 1u;
+                        for(uint32_t kb = 0; kb < num_kb && ok; ++kb)
+                        {
+                            ok = ptx::mbar_wait_bounded(full_bar + 8 * stage, phase, cta_abort, status,
+                                                        (ROLE_MMA << 24) | (1u << 20) | blockIdx.x, WAIT_TIMEOUT_NS);
+                            if(!ok)
+                                break;
+                            ptx::tc_fence_after_sync();
+                            const uint64_t b_desc = ptx::make_kmajor_sw128_desc(smem_b + stage * B_STAGE_BYTES);
+#pragma unroll
+                            for(uint32_t j = 0; j < 2; ++j)
+                            {
+                                if(kb == 0)
+                                {
+                                    // accumulator j of the previous tile must have been drained by both CTAs
+                                    ok = ptx::mbar_wait_bounded(tempty_bar + 8 * j, tphase ^ 1u, cta_abort, status,
+                                                                (ROLE_MMA << 24) | blockIdx.x, WAIT_TIMEOUT_NS);
+                                    if(!ok)
+                                        break;
+                                    ptx::tc_fence_after_sync();
+                                }
+                                const uint64_t a_desc
+                                    = ptx::make_kmajor_sw128_desc(smem_a + stage * A_STAGE_BYTES + j * (SUB_M * BLOCK_K_BYTES));
+#pragma unroll
+                                for(uint32_t ks = 0; ks < BLOCK_K_BYTES / 32; ++ks)
+                                {
+                                    const uint32_t acc = (kb | ks) != 0u ? 1u : 0u;
+                                    if constexpr(KIND == KIND_F16)
+                                        ptx::mma_f16_ss_pair(tmem_base + j * TILE_N, a_desc + 2 * ks, b_desc + 2 * ks, idesc, acc);
+                                    else
+                                        ptx::mma_i8_ss_pair(tmem_base + j * TILE_N, a_desc + 2 * ks, b_desc + 2 * ks, idesc, acc);
+                                }
+                            }
+                            if(!ok)
+                                break;
+                            ptx::tc_commit_pair(empty_bar + 8 * stage, 0x3);
+                            if(++stage == STAGES)
+                            {
+                                stage = 0;
+                                phase ^= 1u;
+                            }
+                        }
+                        if(ok)
+                            ptx::tc_commit_pair(tfull_bar, 0x3);
+                    }
+                }
+                __syncwarp();
+            }
+            else
+            {
+                // -------------------------------- epilogue (both CTAs) --------------------------------
+                const uint32_t e      = warp - 2u; // 0..7
+                const uint32_t quad   = warp & 3u; // lane quadrant this warp may read
+                const uint32_t j      = e >> 2; // accumulator: warps 2-5 -> 0, warps 6-9 -> 1
+                const bool     read_c = (beta != ScalarT(0)) && (c != nullptr);
+                const uint32_t buf_off = epi_off + e * 2u * EPI_BUF_BYTES;
+                const uint32_t buf0    = base + buf_off;
+                const uint32_t cbar0   = cbar_base + e * 16u;
+                using Drain            = StagedDrain<OutT, ScalarT>;
+                uint32_t iter = 0, cpar = 0;
+                bool     ok   = true;
+                for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++iter)
+                {
+                    uint32_t m_idx, n_idx;
+                    tile_coords(tile, tiles_m, tiles_n, group_m, m_idx, n_idx);
+                    const uint32_t row_base = m_idx * PAIR_M + rank * CTA_M + j * SUB_M; // this accumulator's first row
+                    const uint32_t row0     = row_base + quad * 32u; // this warp's first row
+                    const uint32_t col_base = n_idx * TILE_N;
+                    // staged path: needs 16-byte aligned rows (TMA) and a tile that starts inside the matrix
+                    const bool staged = vec_ok != 0 && row0 < m && col_base < n;
+                    // C does not depend on the accumulators: request its first two steps now
+                    if(staged && read_c && lane == 0)
+                        Drain::prefetch_c(&tmap_c, buf0, cbar0, col_base, row0, n);
+                    ok = ptx::mbar_wait_bounded_warp(tfull_bar, iter & 1u, cta_abort, status,
+                                                     (ROLE_EPILOGUE << 24) | blockIdx.x, WAIT_TIMEOUT_NS, lane);
+                    if(!ok)
+                        break;
+                    ptx::tc_fence_after_sync();
+                    const uint32_t tmem_acc = tmem_base + j * TILE_N;
+                    if(staged)
+                        ok = Drain::run(tmem_acc, quad, lane, smem, buf_off, buf0, cbar0, &tmap_c, &tmap_d, col_base, row0, n,
+                                        alpha, beta, read_c, cpar, cta_abort, status,
+                                        (ROLE_EPILOGUE << 24) | (1u << 20) | blockIdx.x);
+                    else if(vec_ok == 0)
+                        drain_accumulator<OutT, ScalarT, TILE_N>(tmem_acc, quad, lane, row_base, col_base, m, n, c, d, ldc,
+                                                                 ldd, alpha, beta, read_c, 0);
+                    // (an aligned tile that lies wholly outside the matrix has nothing to store)
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if(lane == 0)
+                        ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar + 8 * j, 0u));
+                }
+                if(lane == 0)
+                    ptx::bulk_wait_group<0>(); // the staging tiles must outlive the stores that read them
+                __syncwarp();
+            }
+
+            // ---------------------------------- teardown ----------------------------------
+            ptx::tc_fence_before_sync();
+            ptx::cluster_sync();
+            {
+                const uint32_t peer_abort = ptx::ld_shared_cluster_u32(
+                    ptx::mapa(ptx::smem_u32(const_cast<uint32_t*>(cta_abort)), rank ^ 1u));
+                if(*cta_abort || peer_abort)
+                {
+                    const uint64_t t0 = ptx::globaltimer_ns();
+                    while(ptx::globaltimer_ns() - t0 < 2000000ull)
+                        __nanosleep(1000);
+                }
+            }
+            ptx::cluster_sync();
+            if(warp == 1)
+            {
+                ptx::tc_fence_after_sync();
+                ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+            }
+        }
+    } // namespace tc05q
+} // namespace b200wmma

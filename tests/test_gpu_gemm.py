@@ -213,3 +213,42 @@ def test_gemm_i8_full_size_row_sample():
     a_sum = a.to(torch.float64).sum(dim=0)          # exact: |sum| < 2^53
     expect = (bs.to(torch.float64) @ a_sum)          # n values, each exact in fp64 (|.| < 2^53)
     assert torch.equal(col.to(torch.float64), expect)
+
+
+_VARIANT_SCRIPT = r"""
+import sys, numpy as np, torch
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[1] + "/tests")
+from oracle import cpu_ref as R
+from rocwmma_b200 import api, datagen as G
+ok = True
+for (m, n, k) in [(640, 768, 320), (1100, 300, 144), (128, 256, 64)]:
+    a = G.uniform_np(1, (m, k), np.float16); b = G.uniform_np(2, (k, n), np.float16); c = G.uniform_np(3, (m, n), np.float16)
+    bs = np.ascontiguousarray(b.T)
+    d = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+    dev = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    api.gemm_f16(m, n, k, dev(a), dev(bs), dev(c), d, k, k, n, n, 1.0, 1.0)
+    ref = R.gemm(R.port(), m, n, k, a.ravel(), bs.ravel(), c.ravel(), 1.0, 1.0, np.float16).reshape(m, n)
+    bound = R.gemm_abs_bound(m, n, k, a, b, c, 1.0, 1.0)
+    err = np.max(np.abs(d.cpu().numpy().astype(np.float64) - ref.astype(np.float64)) / bound)
+    ok &= bool(np.isfinite(err) and err <= 2e-3)
+    ai = G.int8_np(1, (m, k)); bi = np.ascontiguousarray(G.int8_np(2, (k, n)).T)
+    di = torch.zeros((m, n), dtype=torch.int32, device="cuda")
+    api.gemm_i8(m, n, k, dev(ai), dev(bi), None, di, k, k, n, n, 1, 0)
+    ok &= bool(np.array_equal(di.cpu().numpy(), R.gemm(R.port(), m, n, k, ai.ravel(), bi.ravel(), None, 1, 0, np.int32).reshape(m, n)))
+st, detail = api.device_status()
+print("VARIANT_OK" if ok and st == 0 else f"VARIANT_FAIL status={st}")
+"""
+
+
+@pytest.mark.parametrize("variant", ["1cta", "2cta", "2cta512"])
+def test_gemm_every_tile_variant(variant, tmp_path):
+    """Each tile shape of the tcgen05 GEMM (one-CTA 128x256, pair 256x256, pair 512x256), forced through
+    B200WMMA_GEMM_VARIANT in a fresh process, on shapes with ragged edges; fp16 within tolerance, int8 exact."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "variant_check.py"
+    script.write_text(_VARIANT_SCRIPT)
+    env = dict(os.environ, B200WMMA_GEMM_VARIANT=variant)
+    res = subprocess.run([sys.executable, str(script), root], capture_output=True, text=True, env=env, timeout=600)
+    assert "VARIANT_OK" in res.stdout, res.stdout + res.stderr
