@@ -37,7 +37,12 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
 # (None where no capture exists yet).
 NCU_TRAFFIC_BYTES = {
-    "gemm_f16": 1.343e9,  # profiles/gemm_tc05_f16_8192.md: 1.215 GB read + 127.7 MB written per launch
+    "gemm_f16": 1.141e9,   # profiles/gemm_tc05_f16_8192.md: 1.020 GB read + 120.8 MB written (512x256 pair kernel)
+    "gemm_i8": 1.416e9,    # profiles/gemm_tc05_i8_8192x8192x16384.md (256x256 pair kernel capture)
+    "dlrm_fwd": 119.5e6,   # profiles/dlrm_dot_B16384.md
+    "dlrm_bwd": 195.8e6,   # profiles/dlrm_dot_B16384.md
+    "sgemv": 4.299e9,      # profiles/gemv_32768.md
+    "dgemv": 8.595e9,      # profiles/gemv_32768.md
 }
 
 

@@ -37,7 +37,7 @@ namespace b200wmma
         constexpr uint32_t EPI_WARPS     = 8;
         constexpr uint32_t NUM_THREADS   = 64 + EPI_WARPS * 32;
         constexpr uint32_t TMEM_COLS     = 512;
-        constexpr uint32_t GROUP_M       = 4; // rasterisation band: 4 pair-row tiles = 2048 rows
+        constexpr uint32_t GROUP_M       = 8; // rasterisation band: 8 pair-row tiles = 4096 rows
         constexpr uint32_t EPI_BUF_BYTES = 2048; // 32 rows x 64 bytes, TMA SWIZZLE_64B
         constexpr uint32_t EPI_BYTES     = EPI_WARPS * 2 * EPI_BUF_BYTES; // two staging tiles per epilogue warp
         constexpr uint32_t MISC_BYTES    = 512; // barriers, tensor-memory slot, abort flag

@@ -57,6 +57,22 @@ namespace b200wmma
             return ok != 0;
         }
 
+        // try_wait that lets the hardware park the thread for up to `hint_ns` while the phase is
+        // incomplete (it returns as soon as the phase completes): no instructions issue meanwhile.
+        __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns)
+        {
+            uint32_t ok;
+            asm volatile("{\n"
+                         ".reg .pred p;\n"
+                         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+                         "selp.u32 %0, 1, 0, p;\n"
+                         "}"
+                         : "=r"(ok)
+                         : "r"(bar), "r"(parity), "r"(hint_ns)
+                         : "memory");
+            return ok != 0;
+        }
+
         // Bounded wait.  Returns false when the wait was abandoned: either this thread ran
         // past `timeout_ns` (it then raises the CTA-wide abort flag and records `who` in the
         // device status word {code, detail}) or another thread of the CTA already aborted.
@@ -92,8 +108,8 @@ namespace b200wmma
             }
         }
 
-        // Warp-wide bounded wait for waits that last a whole tile: lane 0 polls with a short sleep
-        // between tries (31 lanes stop issuing instructions), then every lane confirms the completed
+        // Warp-wide bounded wait for waits that last a whole tile: lane 0 waits with the hardware
+        // suspend hint (31 lanes stop issuing instructions), then every lane confirms the completed
         // phase itself so that each has observed the barrier.  All 32 lanes must call it.
         __device__ __forceinline__ bool mbar_wait_bounded_warp(uint32_t           bar,
                                                                uint32_t           parity,
@@ -110,10 +126,9 @@ namespace b200wmma
                 uint32_t       spins = 0;
                 while(true)
                 {
-                    __nanosleep(64);
-                    if(mbar_try_wait(bar, parity))
+                    if(mbar_try_wait_hint(bar, parity, 20000u)) // parked in hardware, woken by the completion
                         break;
-                    if((++spins & 0x3Fu) == 0u)
+                    if((++spins & 0x3u) == 0u)
                     {
                         if(*cta_abort)
                         {
