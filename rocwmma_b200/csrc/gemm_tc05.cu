@@ -335,12 +335,28 @@ namespace b200wmma
             B200_CHECK_CUDA(cudaGetDevice(&dev));
             B200_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
 
-            // Tile shape: 512 x 256 per SM pair when there are more than 256 rows, 256 x 256 per pair for
-            // 129..256 rows, one-CTA 128 x 256 tiles for a single 128-row band
-            // (B200WMMA_GEMM_VARIANT=1cta|2cta|2cta512 forces one, for comparison).
-            const int  forced   = forced_variant();
-            const bool use_q    = forced == 3 || (forced == 0 && m > tc05p::PAIR_M);
-            const bool use_pair = !use_q && (forced == 2 || (forced == 0 && m > BLOCK_M));
+            // Tile shape.  Three kernels exist: 512 x 256 per SM pair (least operand traffic, fastest per
+            // flop), 256 x 256 per pair and 128 x 256 per SM.  All are persistent, so a problem costs
+            // ceil(tiles / slots) rounds of one tile each; pick the shape with the smallest estimated
+            // time = rounds x outputs per SM per tile / relative speed (measured at 8192^3: 1, 0.955, 0.91).
+            // B200WMMA_GEMM_VARIANT=1cta|2cta|2cta512 forces one, for comparison.
+            const int forced = forced_variant();
+            int       pick   = forced;
+            if(pick == 0)
+            {
+                const uint64_t slots1 = static_cast<uint64_t>(sms), slots2 = static_cast<uint64_t>(sms / 2);
+                auto rounds = [](uint64_t tiles, uint64_t slots) { return (tiles + slots - 1) / slots; };
+                const double t512 = rounds(static_cast<uint64_t>(ceil_div(m, 512)) * ceil_div(n, 256), slots2) * 65536.0;
+                const double t256 = rounds(static_cast<uint64_t>(ceil_div(m, 256)) * ceil_div(n, 256), slots2) * 32768.0 / 0.955;
+                const double t128 = rounds(static_cast<uint64_t>(ceil_div(m, 128)) * ceil_div(n, 256), slots1) * 32768.0 / 0.91;
+                pick              = (t512 <= t256 && t512 <= t128) ? 3 : (t256 <= t128 ? 2 : 1);
+                if(m <= BLOCK_M)
+                    pick = 1; // a single 128-row band: pairing would multiply zeros
+                else if(m <= tc05p::PAIR_M && pick == 3)
+                    pick = 2;
+            }
+            const bool use_q    = pick == 3;
+            const bool use_pair = pick == 2;
             CUtensorMap tm_a, tm_b;
             if(int e = make_kmajor_tmap(&tm_a, dt, EB, a, m, k, lda, use_q ? tc05q::CTA_M : BLOCK_M))
                 return e;
