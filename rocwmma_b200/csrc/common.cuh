@@ -50,6 +50,15 @@ namespace b200wmma
     {
         return reinterpret_cast<cudaStream_t>(s);
     }
+    // Kernel attributes and occupancy results are per device: caches of them are arrays indexed by
+    // the current device (a process may drive several GPUs).
+    constexpr int MAX_DEVICES = 64;
+    static inline int current_device_slot()
+    {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        return (dev >= 0 && dev < MAX_DEVICES) ? dev : 0;
+    }
     static inline uint32_t ceil_div(uint32_t a, uint32_t b)
     {
         return (a + b - 1) / b;

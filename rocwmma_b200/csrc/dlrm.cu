@@ -446,7 +446,8 @@ extern "C" int b200wmma_dlrm_fwd(const void* input, void* output, uint32_t m, ui
         return e;
     const uint32_t nbox = (k + 63) / 64;
     const size_t   smem = 1024 + static_cast<size_t>(WARPS) * (FWD_STAGES * nbox * BOX_BYTES + 2 * out_stride * 2 + FWD_STAGES * 8) + 16;
-    static size_t attr_set = 0;
+    static size_t attr_set_dev[MAX_DEVICES];
+    size_t&       attr_set = attr_set_dev[current_device_slot()];
     if(smem > 48 * 1024 && smem > attr_set)
     {
         B200_CHECK_CUDA(cudaFuncSetAttribute(dlrm_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -494,7 +495,8 @@ extern "C" int b200wmma_dlrm_bwd(const void* input, const void* upstream, void* 
     const size_t   smem    = 1024
                         + static_cast<size_t>(WARPS) * (BWD_STAGES * (nbox * BOX_BYTES + up_slot) + MAX_M * TPITCH * 2 + BWD_STAGES * 8)
                         + 16;
-    static size_t attr_set = 0;
+    static size_t attr_set_dev[MAX_DEVICES];
+    size_t&       attr_set = attr_set_dev[current_device_slot()];
     if(smem > 48 * 1024 && smem > attr_set)
     {
         B200_CHECK_CUDA(cudaFuncSetAttribute(dlrm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

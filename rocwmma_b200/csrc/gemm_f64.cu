@@ -195,7 +195,8 @@ extern "C" int b200wmma_gemm_f64(uint32_t m, uint32_t n, uint32_t k, const doubl
                  "gemm_f64: k, lda, ldb must be even and A, B 16-byte aligned (16-byte async copies)");
     if(int e = require_sm100())
         return e;
-    static bool attr_ok = false;
+    static bool attr_ok_dev[MAX_DEVICES];
+    bool&       attr_ok = attr_ok_dev[current_device_slot()];
     if(!attr_ok)
     {
         B200_CHECK_CUDA(cudaFuncSetAttribute(f64::gemm_f64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

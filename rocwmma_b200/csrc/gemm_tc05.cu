@@ -366,7 +366,8 @@ namespace b200wmma
             if(use_q)
             {
                 auto        kern    = tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT>;
-                static int  max_clusters = 0; // one per template instantiation
+                static int max_clusters_dev[MAX_DEVICES]; // per template instantiation and device
+                int&       max_clusters = max_clusters_dev[current_device_slot()];
                 const uint32_t tiles_m = ceil_div(m, tc05q::PAIR_M), tiles_n = ceil_div(n, tc05q::TILE_N);
                 cudaLaunchConfig_t  cfg = {};
                 cudaLaunchAttribute attr[1];
@@ -410,7 +411,8 @@ namespace b200wmma
             if(use_pair)
             {
                 auto        kern    = tc05p::gemm_tc05_pair_kernel<KIND, OutT, ScalarT>;
-                static int  max_clusters = 0; // one per template instantiation
+                static int max_clusters_dev[MAX_DEVICES]; // per template instantiation and device
+                int&       max_clusters = max_clusters_dev[current_device_slot()];
                 const uint32_t tiles_m = ceil_div(m, tc05p::PAIR_M), tiles_n = ceil_div(n, tc05p::TILE_N);
                 cudaLaunchConfig_t  cfg = {};
                 cudaLaunchAttribute attr[1];
@@ -441,7 +443,8 @@ namespace b200wmma
             }
 
             auto        kern    = gemm_tc05_kernel<KIND, OutT, ScalarT>;
-            static bool attr_ok = false; // one flag per template instantiation
+            static bool attr_ok_dev[MAX_DEVICES]; // per template instantiation and device
+            bool&       attr_ok = attr_ok_dev[current_device_slot()];
             if(!attr_ok)
             {
                 B200_CHECK_CUDA(cudaFuncSetAttribute(
