@@ -69,8 +69,10 @@ int b200wmma_device_status(void* stream, int* out_status, unsigned* out_detail);
  * f16: fp16 inputs, fp32 accumulate, D/C fp16 or fp32 (out_type).  tcgen05 tensor cores.
  * i8 : int8 inputs, int32 accumulate / scalars / outputs (wrap-around arithmetic).
  * f64: fp64 everywhere (DMMA).
- * Supported layouts: A row major and B column major (both K-contiguous), C/D row major.
- * Pointers and leading dimensions must keep every row start 16-byte aligned.
+ * f16 / i8 accept every combination of row / column major A, B and C/D (C and D share one layout), as
+ * the reference's NN / NT / TN / TT sweeps do; f64 takes A row major, B column major, C/D row major.
+ * A and B base pointers and leading dimensions (in bytes) must be multiples of 16 (TMA requirement);
+ * C / D may be unaligned (slower element-wise epilogue).
  * ------------------------------------------------------------------------------------------ */
 int b200wmma_gemm_f16(uint32_t m, uint32_t n, uint32_t k,
                       const void* a, const void* b, const void* c, void* d,

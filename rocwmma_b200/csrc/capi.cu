@@ -6,6 +6,7 @@
 #include <cstring>
 #include <mutex>
 #include <new>
+#include <vector>
 
 namespace b200wmma
 {
@@ -74,9 +75,6 @@ namespace b200wmma
     {
         B200_REQUIRE((la == 0 || la == 1) && (lb == 0 || lb == 1) && (lcd == 0 || lcd == 1),
                      B200WMMA_ERR_INVALID_ARG, "%s: layout flags must be 0 (row) or 1 (col)", who);
-        B200_REQUIRE(la == B200WMMA_ROW_MAJOR && lb == B200WMMA_COL_MAJOR && lcd == B200WMMA_ROW_MAJOR,
-                     B200WMMA_ERR_UNSUPPORTED,
-                     "%s: only A row-major, B column-major, C/D row-major is implemented", who);
         return B200WMMA_OK;
     }
 } // namespace b200wmma
@@ -119,8 +117,8 @@ extern "C" int b200wmma_gemm_f16(uint32_t m, uint32_t n, uint32_t k, const void*
     clear_error();
     if(int e = check_layouts("gemm_f16", layout_a, layout_b, layout_cd))
         return e;
-    return launch_gemm_tc05_f16(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, out_type,
-                                as_stream(stream));
+    return launch_gemm_tc05_f16(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, layout_a, layout_b,
+                                layout_cd, out_type, as_stream(stream));
 }
 
 extern "C" int b200wmma_gemm_i8(uint32_t m, uint32_t n, uint32_t k, const int8_t* a, const int8_t* b,
@@ -131,7 +129,8 @@ extern "C" int b200wmma_gemm_i8(uint32_t m, uint32_t n, uint32_t k, const int8_t
     clear_error();
     if(int e = check_layouts("gemm_i8", layout_a, layout_b, layout_cd))
         return e;
-    return launch_gemm_tc05_i8(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, as_stream(stream));
+    return launch_gemm_tc05_i8(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, layout_a, layout_b, layout_cd,
+                               as_stream(stream));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -140,7 +139,9 @@ extern "C" int b200wmma_gemm_i8(uint32_t m, uint32_t n, uint32_t k, const int8_t
 struct b200wmma_ctx
 {
     static constexpr int NBUF = 4;
-    cudaStream_t         stream    = nullptr;
+    cudaStream_t         stream    = nullptr; // compute stream (and the only one for the small drivers)
+    cudaStream_t         s_in = nullptr, s_out = nullptr; // copy-in / copy-out streams of the pipelined GEMM driver
+    std::vector<cudaEvent_t> events;      // reusable, timing disabled
     void*                buf[NBUF] = {nullptr, nullptr, nullptr, nullptr};
     size_t               cap[NBUF] = {0, 0, 0, 0};
     int                  device    = 0;
@@ -185,6 +186,70 @@ namespace
     }
 }
 
+
+namespace
+{
+    int ctx_events(b200wmma_ctx* ctx, size_t count)
+    {
+        while(ctx->events.size() < count)
+        {
+            cudaEvent_t ev = nullptr;
+            B200_CHECK_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+            ctx->events.push_back(ev);
+        }
+        return B200WMMA_OK;
+    }
+
+    // Host-buffer GEMM as a three-stream pipeline over blocks of rows.  B is copied once; then for each
+    // block of rows: copy A / C rows in (copy-in stream), multiply (compute stream), copy the D rows out
+    // (copy-out stream).  Row blocks of a row-major A / C / D are contiguous, and rows of a GEMM are
+    // independent, so the copies of block i+1 and of block i-1 overlap the kernel of block i and the two
+    // copy directions overlap each other.  `launch(rows, a_dev, c_dev, d_dev)` enqueues one block.
+    template <typename Launch>
+    int gemm_host_pipeline(b200wmma_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b,
+                           const void* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                           size_t in_es, size_t out_es, bool use_c, Launch launch)
+    {
+        const size_t ba = extent(m, k, lda) * in_es, bb = extent(n, k, ldb) * in_es;
+        const size_t bc = extent(m, n, ldc) * out_es, bd = extent(m, n, ldd) * out_es;
+        if(int e = ctx_reserve(ctx, 0, ba)) return e;
+        if(int e = ctx_reserve(ctx, 1, bb)) return e;
+        if(int e = ctx_reserve(ctx, 2, use_c ? bc : 16)) return e;
+        if(int e = ctx_reserve(ctx, 3, bd)) return e;
+        const uint32_t block_rows = 1024; // 64 pair tiles of 512 x 256 at n = 8192: one round of the GEMM kernel
+        const uint32_t blocks     = (m + block_rows - 1) / block_rows;
+        if(int e = ctx_events(ctx, 2 * static_cast<size_t>(blocks) + 1)) return e;
+        char*       da = static_cast<char*>(ctx->buf[0]);
+        char*       dc = static_cast<char*>(ctx->buf[2]);
+        char*       dd = static_cast<char*>(ctx->buf[3]);
+        const char* ha = static_cast<const char*>(a);
+        const char* hc = static_cast<const char*>(c);
+        char*       hd = static_cast<char*>(d);
+
+        B200_CHECK_CUDA(cudaMemcpyAsync(ctx->buf[1], b, bb, cudaMemcpyHostToDevice, ctx->s_in));
+        for(uint32_t i = 0; i < blocks; ++i)
+        {
+            const uint32_t r0 = i * block_rows, rows = (m - r0 < block_rows) ? m - r0 : block_rows;
+            const size_t   oa = static_cast<size_t>(r0) * lda * in_es, oc = static_cast<size_t>(r0) * ldc * out_es,
+                         od = static_cast<size_t>(r0) * ldd * out_es;
+            B200_CHECK_CUDA(cudaMemcpyAsync(da + oa, ha + oa, extent(rows, k, lda) * in_es, cudaMemcpyHostToDevice, ctx->s_in));
+            if(use_c)
+                B200_CHECK_CUDA(cudaMemcpyAsync(dc + oc, hc + oc, extent(rows, n, ldc) * out_es, cudaMemcpyHostToDevice, ctx->s_in));
+            cudaEvent_t ev_in = ctx->events[2 * i], ev_done = ctx->events[2 * i + 1];
+            B200_CHECK_CUDA(cudaEventRecord(ev_in, ctx->s_in)); // B (first block) and this block's rows are on the device
+            B200_CHECK_CUDA(cudaStreamWaitEvent(ctx->stream, ev_in, 0));
+            if(int e = launch(rows, da + oa, use_c ? dc + oc : nullptr, dd + od))
+                return e;
+            B200_CHECK_CUDA(cudaEventRecord(ev_done, ctx->stream));
+            B200_CHECK_CUDA(cudaStreamWaitEvent(ctx->s_out, ev_done, 0));
+            B200_CHECK_CUDA(cudaMemcpyAsync(hd + od, dd + od, extent(rows, n, ldd) * out_es, cudaMemcpyDeviceToHost, ctx->s_out));
+        }
+        B200_CHECK_CUDA(cudaStreamSynchronize(ctx->s_out));
+        B200_CHECK_CUDA(cudaStreamSynchronize(ctx->s_in));
+        return finish(ctx);
+    }
+}
+
 extern "C" int b200wmma_ctx_create(b200wmma_ctx** out_ctx)
 {
     clear_error();
@@ -196,8 +261,14 @@ extern "C" int b200wmma_ctx_create(b200wmma_ctx** out_ctx)
     cudaError_t e = cudaGetDevice(&ctx->device);
     if(e == cudaSuccess)
         e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+    if(e == cudaSuccess)
+        e = cudaStreamCreateWithFlags(&ctx->s_in, cudaStreamNonBlocking);
+    if(e == cudaSuccess)
+        e = cudaStreamCreateWithFlags(&ctx->s_out, cudaStreamNonBlocking);
     if(e != cudaSuccess)
     {
+        if(ctx->stream) cudaStreamDestroy(ctx->stream);
+        if(ctx->s_in) cudaStreamDestroy(ctx->s_in);
         delete ctx;
         return set_error(B200WMMA_ERR_CUDA, "ctx_create: %s", cudaGetErrorString(e));
     }
@@ -214,8 +285,14 @@ extern "C" int b200wmma_ctx_destroy(b200wmma_ctx* ctx)
     for(int i = 0; i < b200wmma_ctx::NBUF; ++i)
         if(ctx->buf[i])
             cudaFree(ctx->buf[i]);
+    for(cudaEvent_t ev : ctx->events)
+        cudaEventDestroy(ev);
     if(ctx->stream)
         cudaStreamDestroy(ctx->stream);
+    if(ctx->s_in)
+        cudaStreamDestroy(ctx->s_in);
+    if(ctx->s_out)
+        cudaStreamDestroy(ctx->s_out);
     delete ctx;
     return B200WMMA_OK;
 }
@@ -231,28 +308,22 @@ extern "C" int b200wmma_gemm_f16_host(b200wmma_ctx* ctx, uint32_t m, uint32_t n,
         return e;
     if(int e = check_layouts("gemm_f16_host", layout_a, layout_b, layout_cd))
         return e;
+    B200_REQUIRE(layout_a == B200WMMA_ROW_MAJOR && layout_b == B200WMMA_COL_MAJOR && layout_cd == B200WMMA_ROW_MAJOR,
+                 B200WMMA_ERR_UNSUPPORTED,
+                 "gemm_f16_host: the row-block pipeline needs A row-major, B column-major, C/D row-major");
     B200_REQUIRE(a && b && d && m && n && k, B200WMMA_ERR_INVALID_ARG, "gemm_f16_host: null pointer or zero size");
     B200_REQUIRE(out_type == 0 || out_type == 1, B200WMMA_ERR_INVALID_ARG, "gemm_f16_host: bad out_type");
     B200_REQUIRE(lda >= k && ldb >= k && ldd >= n && ldc >= n, B200WMMA_ERR_INVALID_ARG,
                  "gemm_f16_host: leading dimension too small");
-    const size_t osz = out_type == B200WMMA_OUT_F16 ? 2 : 4;
-    const size_t ba = extent(m, k, lda) * 2, bb = extent(n, k, ldb) * 2;
-    const size_t bc = extent(m, n, ldc) * osz, bd = extent(m, n, ldd) * osz;
+    const size_t osz   = out_type == B200WMMA_OUT_F16 ? 2 : 4;
     const bool   use_c = c != nullptr && beta != 0.0f;
-    if(int e = ctx_reserve(ctx, 0, ba)) return e;
-    if(int e = ctx_reserve(ctx, 1, bb)) return e;
-    if(int e = ctx_reserve(ctx, 2, use_c ? bc : 16)) return e;
-    if(int e = ctx_reserve(ctx, 3, bd)) return e;
-    B200_CHECK_CUDA(cudaMemcpyAsync(ctx->buf[0], a, ba, cudaMemcpyHostToDevice, ctx->stream));
-    B200_CHECK_CUDA(cudaMemcpyAsync(ctx->buf[1], b, bb, cudaMemcpyHostToDevice, ctx->stream));
-    if(use_c)
-        B200_CHECK_CUDA(cudaMemcpyAsync(ctx->buf[2], c, bc, cudaMemcpyHostToDevice, ctx->stream));
-    if(int e = launch_gemm_tc05_f16(m, n, k, ctx->buf[0], ctx->buf[1], use_c ? ctx->buf[2] : nullptr,
-                                    ctx->buf[3], lda, ldb, ldc, ldd, alpha, use_c ? beta : 0.0f,
-                                    out_type, ctx->stream))
-        return e;
-    B200_CHECK_CUDA(cudaMemcpyAsync(d, ctx->buf[3], bd, cudaMemcpyDeviceToHost, ctx->stream));
-    return finish(ctx);
+    B200_REQUIRE(c || beta == 0.0f, B200WMMA_ERR_INVALID_ARG, "gemm_f16_host: c may be null only when beta == 0");
+    return gemm_host_pipeline(ctx, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, 2, osz, use_c,
+                              [&](uint32_t rows, const void* da, const void* dc, void* dd) {
+                                  return launch_gemm_tc05_f16(rows, n, k, da, ctx->buf[1], dc, dd, lda, ldb, ldc, ldd, alpha,
+                                                              use_c ? beta : 0.0f, B200WMMA_ROW_MAJOR, B200WMMA_COL_MAJOR,
+                                                              B200WMMA_ROW_MAJOR, out_type, ctx->stream);
+                              });
 }
 
 extern "C" int b200wmma_gemm_i8_host(b200wmma_ctx* ctx, uint32_t m, uint32_t n, uint32_t k,
@@ -266,28 +337,22 @@ extern "C" int b200wmma_gemm_i8_host(b200wmma_ctx* ctx, uint32_t m, uint32_t n, 
         return e;
     if(int e = check_layouts("gemm_i8_host", layout_a, layout_b, layout_cd))
         return e;
+    B200_REQUIRE(layout_a == B200WMMA_ROW_MAJOR && layout_b == B200WMMA_COL_MAJOR && layout_cd == B200WMMA_ROW_MAJOR,
+                 B200WMMA_ERR_UNSUPPORTED,
+                 "gemm_i8_host: the row-block pipeline needs A row-major, B column-major, C/D row-major");
     B200_REQUIRE(a && b && d && m && n && k, B200WMMA_ERR_INVALID_ARG, "gemm_i8_host: null pointer or zero size");
     B200_REQUIRE(lda >= k && ldb >= k && ldd >= n && ldc >= n, B200WMMA_ERR_INVALID_ARG,
                  "gemm_i8_host: leading dimension too small");
-    const size_t ba = extent(m, k, lda), bb = extent(n, k, ldb);
-    const size_t bc = extent(m, n, ldc) * 4, bd = extent(m, n, ldd) * 4;
-    const bool   use_c = c != nullptr && beta != 0;
-    if(int e = ctx_reserve(ctx, 0, ba)) return e;
-    if(int e = ctx_reserve(ctx, 1, bb)) return e;
-    if(int e = ctx_reserve(ctx, 2, use_c ? bc : 16)) return e;
-    if(int e = ctx_reserve(ctx, 3, bd)) return e;
-    B200_CHECK_CUDA(cudaMemcpyAsync(ctx->buf[0], a, ba, cudaMemcpyHostToDevice, ctx->stream));
-    B200_CHECK_CUDA(cudaMemcpyAsync(ctx->buf[1], b, bb, cudaMemcpyHostToDevice, ctx->stream));
-    if(use_c)
-        B200_CHECK_CUDA(cudaMemcpyAsync(ctx->buf[2], c, bc, cudaMemcpyHostToDevice, ctx->stream));
-    if(int e = launch_gemm_tc05_i8(m, n, k, static_cast<const int8_t*>(ctx->buf[0]),
-                                   static_cast<const int8_t*>(ctx->buf[1]),
-                                   use_c ? static_cast<const int32_t*>(ctx->buf[2]) : nullptr,
-                                   static_cast<int32_t*>(ctx->buf[3]), lda, ldb, ldc, ldd, alpha,
-                                   use_c ? beta : 0, ctx->stream))
-        return e;
-    B200_CHECK_CUDA(cudaMemcpyAsync(d, ctx->buf[3], bd, cudaMemcpyDeviceToHost, ctx->stream));
-    return finish(ctx);
+    const bool use_c = c != nullptr && beta != 0;
+    B200_REQUIRE(c || beta == 0, B200WMMA_ERR_INVALID_ARG, "gemm_i8_host: c may be null only when beta == 0");
+    return gemm_host_pipeline(ctx, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, 1, 4, use_c,
+                              [&](uint32_t rows, const void* da, const void* dc, void* dd) {
+                                  return launch_gemm_tc05_i8(rows, n, k, static_cast<const int8_t*>(da),
+                                                             static_cast<const int8_t*>(ctx->buf[1]),
+                                                             static_cast<const int32_t*>(dc), static_cast<int32_t*>(dd), lda,
+                                                             ldb, ldc, ldd, alpha, use_c ? beta : 0, B200WMMA_ROW_MAJOR,
+                                                             B200WMMA_COL_MAJOR, B200WMMA_ROW_MAJOR, ctx->stream);
+                              });
 }
 
 extern "C" int b200wmma_dlrm_fwd_host(b200wmma_ctx* ctx, const void* input, void* output, uint32_t m,

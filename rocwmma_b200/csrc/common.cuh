@@ -67,10 +67,11 @@ namespace b200wmma
     // ---- kernel launchers implemented in the .cu files --------------------------------
     int launch_gemm_tc05_f16(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b,
                              const void* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
-                             uint32_t ldd, float alpha, float beta, int out_type,
-                             cudaStream_t stream);
+                             uint32_t ldd, float alpha, float beta, int layout_a, int layout_b,
+                             int layout_cd, int out_type, cudaStream_t stream);
     int launch_gemm_tc05_i8(uint32_t m, uint32_t n, uint32_t k, const int8_t* a,
                             const int8_t* b, const int32_t* c, int32_t* d, uint32_t lda,
                             uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha,
-                            int32_t beta, cudaStream_t stream);
+                            int32_t beta, int layout_a, int layout_b, int layout_cd,
+                            cudaStream_t stream);
 } // namespace b200wmma

@@ -137,7 +137,8 @@ extern "C" int b200wmma_gemm_i8_sp24(uint32_t m, uint32_t n, uint32_t k, const i
     i8var::expand_sp24_kernel<<<i8var::grid_for(units), i8var::THREADS, 0, as_stream(stream)>>>(
         a_vals, a_meta, dense, m, k, lda_vals, ld_meta);
     B200_CHECK_CUDA(cudaGetLastError());
-    return launch_gemm_tc05_i8(m, n, k, dense, b, c, d, k, ldb, ldc, ldd, alpha, beta, as_stream(stream));
+    return launch_gemm_tc05_i8(m, n, k, dense, b, c, d, k, ldb, ldc, ldd, alpha, beta, B200WMMA_ROW_MAJOR,
+                               B200WMMA_COL_MAJOR, B200WMMA_ROW_MAJOR, as_stream(stream));
 }
 
 extern "C" int b200wmma_gemm_i4(uint32_t m, uint32_t n, uint32_t k, const uint8_t* a_packed,
@@ -168,8 +169,8 @@ extern "C" int b200wmma_gemm_i4(uint32_t m, uint32_t n, uint32_t k, const uint8_
     i8var::unpack_i4_kernel<<<i8var::grid_for(static_cast<size_t>(n) * (k / 32)), i8var::THREADS, 0,
                               as_stream(stream)>>>(b_packed, dense_b, n, k, ldb_bytes);
     B200_CHECK_CUDA(cudaGetLastError());
-    return launch_gemm_tc05_i8(m, n, k, dense_a, dense_b, c, d, k, k, ldc, ldd, alpha, beta,
-                               as_stream(stream));
+    return launch_gemm_tc05_i8(m, n, k, dense_a, dense_b, c, d, k, k, ldc, ldd, alpha, beta, B200WMMA_ROW_MAJOR,
+                               B200WMMA_COL_MAJOR, B200WMMA_ROW_MAJOR, as_stream(stream));
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -246,5 +247,6 @@ extern "C" int b200wmma_gemm_i8_sp24_static(uint32_t m, uint32_t n, uint32_t k, 
     i8var::expand_sp24_kernel<<<i8var::grid_for(units), i8var::THREADS, 0, as_stream(stream)>>>(
         a_vals, a_meta, dense, m, k, lda_vals, ld_meta);
     B200_CHECK_CUDA(cudaGetLastError());
-    return launch_gemm_tc05_i8(m, n, k, dense, b, c, d, k, ldb, ldc, ldd, alpha, beta, as_stream(stream));
+    return launch_gemm_tc05_i8(m, n, k, dense, b, c, d, k, ldb, ldc, ldd, alpha, beta, B200WMMA_ROW_MAJOR,
+                               B200WMMA_COL_MAJOR, B200WMMA_ROW_MAJOR, as_stream(stream));
 }

@@ -298,6 +298,8 @@ namespace b200wmma
                           uint32_t     ldd,
                           ScalarT      alpha,
                           ScalarT      beta,
+                          bool         a_mn, // A column-major (M contiguous) instead of row-major
+                          bool         b_mn, // B row-major (N contiguous) instead of column-major
                           cudaStream_t stream)
         {
             constexpr uint32_t EB = (KIND == KIND_F16) ? 2u : 1u;
@@ -306,7 +308,7 @@ namespace b200wmma
             B200_REQUIRE(c || beta == ScalarT(0),
                          B200WMMA_ERR_INVALID_ARG,
                          "gemm: c may be null only when beta == 0");
-            B200_REQUIRE(lda >= k && ldb >= k && ldd >= n && (!c || ldc >= n),
+            B200_REQUIRE(lda >= (a_mn ? m : k) && ldb >= (b_mn ? n : k) && ldd >= n && (!c || ldc >= n),
                          B200WMMA_ERR_INVALID_ARG,
                          "gemm: leading dimension smaller than the row/column it strides");
             B200_REQUIRE(aligned16(a) && aligned16(b) && (static_cast<uint64_t>(lda) * EB) % 16 == 0
@@ -340,7 +342,7 @@ namespace b200wmma
             // ceil(tiles / slots) rounds of one tile each; pick the shape with the smallest estimated
             // time = rounds x outputs per SM per tile / relative speed (measured at 8192^3: 1, 0.955, 0.91).
             // B200WMMA_GEMM_VARIANT=1cta|2cta|2cta512 forces one, for comparison.
-            const int forced = forced_variant();
+            const int forced = (a_mn || b_mn) ? 3 : forced_variant(); // MN-major operands: 512 x 256 kernel only
             int       pick   = forced;
             if(pick == 0)
             {
@@ -358,16 +360,24 @@ namespace b200wmma
             const bool use_q    = pick == 3;
             const bool use_pair = pick == 2;
             CUtensorMap tm_a, tm_b;
-            if(int e = make_kmajor_tmap(&tm_a, dt, EB, a, m, k, lda, use_q ? tc05q::CTA_M : BLOCK_M))
+            if(int e = a_mn ? make_mnmajor_tmap(&tm_a, dt, EB, a, m, k, lda)
+                            : make_kmajor_tmap(&tm_a, dt, EB, a, m, k, lda, use_q ? tc05q::CTA_M : BLOCK_M))
                 return e;
-            if(int e = make_kmajor_tmap(&tm_b, dt, EB, b, n, k, ldb, (use_pair || use_q) ? tc05p::HALF_N : BLOCK_N))
+            if(int e = b_mn ? make_mnmajor_tmap(&tm_b, dt, EB, b, n, k, ldb)
+                            : make_kmajor_tmap(&tm_b, dt, EB, b, n, k, ldb, (use_pair || use_q) ? tc05p::HALF_N : BLOCK_N))
                 return e;
 
             if(use_q)
             {
-                auto        kern    = tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT>;
-                static int max_clusters_dev[MAX_DEVICES]; // per template instantiation and device
-                int&       max_clusters = max_clusters_dev[current_device_slot()];
+                using KernT = decltype(&tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT, false, false>);
+                const KernT kerns[4] = {tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT, false, false>,
+                                        tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT, false, true>,
+                                        tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT, true, false>,
+                                        tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT, true, true>};
+                const int   layout_id = (a_mn ? 2 : 0) + (b_mn ? 1 : 0);
+                KernT       kern      = kerns[layout_id];
+                static int  max_clusters_dev[4][MAX_DEVICES]; // per template instantiation, layout and device
+                int&        max_clusters = max_clusters_dev[layout_id][current_device_slot()];
                 const uint32_t tiles_m = ceil_div(m, tc05q::PAIR_M), tiles_n = ceil_div(n, tc05q::TILE_N);
                 cudaLaunchConfig_t  cfg = {};
                 cudaLaunchAttribute attr[1];
@@ -474,30 +484,44 @@ namespace b200wmma
         }
     } // namespace tc05
 
+    // Layout handling shared by both element types.  An operand is "MN-major" when its M / N index
+    // is the contiguous one (column-major A, row-major B).  Column-major C / D is the row-major
+    // transposed problem D^T = alpha * B^T A^T + beta * C^T: swap the operands and m <-> n.
+    template <int KIND, typename OutT, typename ScalarT>
+    static int launch_any_layout(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const OutT* c,
+                                 OutT* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, ScalarT alpha,
+                                 ScalarT beta, int layout_a, int layout_b, int layout_cd, cudaStream_t stream)
+    {
+        const bool a_mn = layout_a == B200WMMA_COL_MAJOR, b_mn = layout_b == B200WMMA_ROW_MAJOR;
+        if(layout_cd == B200WMMA_ROW_MAJOR)
+            return tc05::launch<KIND, OutT, ScalarT>(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, a_mn, b_mn,
+                                                     stream);
+        // B^T (n x k) takes the role of A: it is K-major exactly when B was; likewise A^T for B
+        return tc05::launch<KIND, OutT, ScalarT>(n, m, k, b, a, c, d, ldb, lda, ldc, ldd, alpha, beta, b_mn, a_mn, stream);
+    }
+
     int launch_gemm_tc05_f16(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b,
                              const void* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
-                             uint32_t ldd, float alpha, float beta, int out_type,
-                             cudaStream_t stream)
+                             uint32_t ldd, float alpha, float beta, int layout_a, int layout_b, int layout_cd,
+                             int out_type, cudaStream_t stream)
     {
         if(out_type == B200WMMA_OUT_F16)
-            return tc05::launch<tc05::KIND_F16, __half, float>(m, n, k, a, b,
-                                                               static_cast<const __half*>(c),
-                                                               static_cast<__half*>(d),
-                                                               lda, ldb, ldc, ldd, alpha, beta, stream);
+            return launch_any_layout<tc05::KIND_F16, __half, float>(m, n, k, a, b, static_cast<const __half*>(c),
+                                                                    static_cast<__half*>(d), lda, ldb, ldc, ldd, alpha,
+                                                                    beta, layout_a, layout_b, layout_cd, stream);
         if(out_type == B200WMMA_OUT_F32)
-            return tc05::launch<tc05::KIND_F16, float, float>(m, n, k, a, b,
-                                                              static_cast<const float*>(c),
-                                                              static_cast<float*>(d),
-                                                              lda, ldb, ldc, ldd, alpha, beta, stream);
+            return launch_any_layout<tc05::KIND_F16, float, float>(m, n, k, a, b, static_cast<const float*>(c),
+                                                                   static_cast<float*>(d), lda, ldb, ldc, ldd, alpha, beta,
+                                                                   layout_a, layout_b, layout_cd, stream);
         return set_error(B200WMMA_ERR_INVALID_ARG, "gemm_f16: out_type must be 0 (f16) or 1 (f32)");
     }
 
     int launch_gemm_tc05_i8(uint32_t m, uint32_t n, uint32_t k, const int8_t* a,
                             const int8_t* b, const int32_t* c, int32_t* d, uint32_t lda,
                             uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha,
-                            int32_t beta, cudaStream_t stream)
+                            int32_t beta, int layout_a, int layout_b, int layout_cd, cudaStream_t stream)
     {
-        return tc05::launch<tc05::KIND_I8, int32_t, int32_t>(m, n, k, a, b, c, d, lda, ldb, ldc, ldd,
-                                                             alpha, beta, stream);
+        return launch_any_layout<tc05::KIND_I8, int32_t, int32_t>(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
+                                                                  layout_a, layout_b, layout_cd, stream);
     }
 } // namespace b200wmma

@@ -28,7 +28,7 @@ namespace b200wmma
 
         // tcgen05 instruction descriptor (32-bit): D format bits [4,6), A format [7,10),
         // B format [10,13), A/B major bits 15/16 (0 = K-major), N>>3 at [17,23), M>>4 at [24,29).
-        template <int KIND, uint32_t MMA_M, uint32_t MMA_N>
+        template <int KIND, uint32_t MMA_M, uint32_t MMA_N, bool A_MN = false, bool B_MN = false>
         __host__ __device__ constexpr uint32_t make_idesc()
         {
             uint32_t d = 0;
@@ -42,6 +42,8 @@ namespace b200wmma
                 d |= 1u << 7; // A = signed 8-bit
                 d |= 1u << 10; // B = signed 8-bit
             }
+            d |= (A_MN ? 1u : 0u) << 15; // A major: 0 = K-major, 1 = MN-major
+            d |= (B_MN ? 1u : 0u) << 16; // B major
             d |= (MMA_N >> 3) << 17;
             d |= (MMA_M >> 4) << 24;
             return d;
@@ -281,6 +283,25 @@ namespace b200wmma
                          B200WMMA_ERR_CUDA,
                          "cuTensorMapEncodeTiled failed with CUresult %d",
                          static_cast<int>(r));
+            return B200WMMA_OK;
+        }
+
+        // MN-major operand: `k_extent` rows of `mn_extent` contiguous elements, row pitch ld elements
+        // (a column-major A or a row-major B).  Box = 128 bytes of MN x one K slab of rows.
+        static int make_mnmajor_tmap(CUtensorMap* out, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* ptr,
+                                     uint32_t mn_extent, uint32_t k_extent, uint32_t ld)
+        {
+            EncodeTiledFn fn = get_encode_fn();
+            B200_REQUIRE(fn != nullptr, B200WMMA_ERR_CUDA, "cuTensorMapEncodeTiled not available");
+            cuuint64_t gdim[2]    = {mn_extent, k_extent};
+            cuuint64_t gstride[1] = {static_cast<cuuint64_t>(ld) * elem_bytes};
+            cuuint32_t box[2]     = {128u / elem_bytes, BLOCK_K_BYTES / elem_bytes};
+            cuuint32_t estr[2]    = {1, 1};
+            CUresult   r          = fn(out, dtype, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            B200_REQUIRE(r == CUDA_SUCCESS, B200WMMA_ERR_CUDA,
+                         "cuTensorMapEncodeTiled (MN-major operand) failed with CUresult %d", static_cast<int>(r));
             return B200WMMA_OK;
         }
 

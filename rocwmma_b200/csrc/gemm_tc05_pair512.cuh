@@ -165,7 +165,8 @@ namespace b200wmma
             }
         };
 
-        template <int KIND, typename OutT, typename ScalarT>
+        // A_MN / B_MN: the operand is MN-major (column-major A / row-major B) instead of K-major.
+        template <int KIND, typename OutT, typename ScalarT, bool A_MN = false, bool B_MN = false>
         __global__ void __launch_bounds__(NUM_THREADS, 1)
             gemm_tc05_pair512_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                      const __grid_constant__ CUtensorMap tmap_b,
@@ -265,10 +266,29 @@ namespace b200wmma
                             if(rank == 0)
                                 ptx::mbar_arrive_expect_tx(full_bar + 8 * stage, 2u * STAGE_BYTES);
                             const uint32_t leader_full = ptx::mapa(full_bar + 8 * stage, 0u);
-                            const int32_t  kc          = static_cast<int32_t>(
-                                kb * (KIND == KIND_F16 ? BLOCK_K_BYTES / 2 : BLOCK_K_BYTES));
-                            ptx::tma_load_2d_pair(smem_a + stage * A_STAGE_BYTES, &tmap_a, kc, row_a, leader_full);
-                            ptx::tma_load_2d_pair(smem_b + stage * B_STAGE_BYTES, &tmap_b, kc, row_b, leader_full);
+                            constexpr uint32_t ES       = (KIND == KIND_F16) ? 2u : 1u;
+                            constexpr uint32_t SLAB_K   = BLOCK_K_BYTES / ES; // K elements per slab
+                            constexpr uint32_t MN_GROUP = 128u / ES; // MN elements per 128-byte line
+                            constexpr uint32_t GROUP_B  = SLAB_K * 128u; // bytes of one MN group over a slab
+                            const int32_t      kc       = static_cast<int32_t>(kb * SLAB_K);
+                            if constexpr(A_MN)
+                            {
+#pragma unroll
+                                for(uint32_t gq = 0; gq < CTA_M / MN_GROUP; ++gq)
+                                    ptx::tma_load_2d_pair(smem_a + stage * A_STAGE_BYTES + gq * GROUP_B, &tmap_a,
+                                                          row_a + static_cast<int32_t>(gq * MN_GROUP), kc, leader_full);
+                            }
+                            else
+                                ptx::tma_load_2d_pair(smem_a + stage * A_STAGE_BYTES, &tmap_a, kc, row_a, leader_full);
+                            if constexpr(B_MN)
+                            {
+#pragma unroll
+                                for(uint32_t gq = 0; gq < HALF_N / MN_GROUP; ++gq)
+                                    ptx::tma_load_2d_pair(smem_b + stage * B_STAGE_BYTES + gq * GROUP_B, &tmap_b,
+                                                          row_b + static_cast<int32_t>(gq * MN_GROUP), kc, leader_full);
+                            }
+                            else
+                                ptx::tma_load_2d_pair(smem_b + stage * B_STAGE_BYTES, &tmap_b, kc, row_b, leader_full);
                             if(++stage == STAGES)
                             {
                                 stage = 0;
@@ -284,7 +304,13 @@ namespace b200wmma
                 // ------------------------------- MMA issuer (leader only) -------------------------------
                 if(lane == 0 && rank == 0)
                 {
-                    constexpr uint32_t idesc = make_idesc<KIND, 2 * SUB_M, TILE_N>();
+                    constexpr uint32_t idesc = make_idesc<KIND, 2 * SUB_M, TILE_N, A_MN, B_MN>();
+                    constexpr uint32_t ES      = (KIND == KIND_F16) ? 2u : 1u;
+                    constexpr uint32_t GROUP_B = (BLOCK_K_BYTES / ES) * 128u; // one MN group over a slab
+                    // descriptor start-address step per MMA (32 bytes of K): 32 bytes inside the K-major line,
+                    // or (32 / ES) K rows of 128 bytes for an MN-major tile
+                    constexpr uint32_t A_STEP = A_MN ? ((32u / ES) * 128u) >> 4 : 2u;
+                    constexpr uint32_t B_STEP = B_MN ? ((32u / ES) * 128u) >> 4 : 2u;
                     uint32_t           stage = 0, phase = 0, iter = 0;
                     bool               ok = true;
                     for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++iter)
@@ -297,7 +323,8 @@ namespace b200wmma
                             if(!ok)
                                 break;
                             ptx::tc_fence_after_sync();
-                            const uint64_t b_desc = ptx::make_kmajor_sw128_desc(smem_b + stage * B_STAGE_BYTES);
+                            const uint64_t b_desc = B_MN ? ptx::make_mnmajor_sw128_desc(smem_b + stage * B_STAGE_BYTES, GROUP_B)
+                                                         : ptx::make_kmajor_sw128_desc(smem_b + stage * B_STAGE_BYTES);
 #pragma unroll
                             for(uint32_t j = 0; j < 2; ++j)
                             {
@@ -310,16 +337,17 @@ namespace b200wmma
                                         break;
                                     ptx::tc_fence_after_sync();
                                 }
-                                const uint64_t a_desc
-                                    = ptx::make_kmajor_sw128_desc(smem_a + stage * A_STAGE_BYTES + j * (SUB_M * BLOCK_K_BYTES));
+                                const uint32_t a_addr = smem_a + stage * A_STAGE_BYTES + j * (SUB_M * BLOCK_K_BYTES);
+                                const uint64_t a_desc = A_MN ? ptx::make_mnmajor_sw128_desc(a_addr, GROUP_B)
+                                                             : ptx::make_kmajor_sw128_desc(a_addr);
 #pragma unroll
                                 for(uint32_t ks = 0; ks < BLOCK_K_BYTES / 32; ++ks)
                                 {
                                     const uint32_t acc = (kb | ks) != 0u ? 1u : 0u;
                                     if constexpr(KIND == KIND_F16)
-                                        ptx::mma_f16_ss_pair(tmem_base + j * TILE_N, a_desc + 2 * ks, b_desc + 2 * ks, idesc, acc);
+                                        ptx::mma_f16_ss_pair(tmem_base + j * TILE_N, a_desc + A_STEP * ks, b_desc + B_STEP * ks, idesc, acc);
                                     else
-                                        ptx::mma_i8_ss_pair(tmem_base + j * TILE_N, a_desc + 2 * ks, b_desc + 2 * ks, idesc, acc);
+                                        ptx::mma_i8_ss_pair(tmem_base + j * TILE_N, a_desc + A_STEP * ks, b_desc + B_STEP * ks, idesc, acc);
                                 }
                             }
                             if(!ok)

@@ -451,5 +451,20 @@ namespace b200wmma
             desc |= static_cast<uint64_t>(2u) << 61; // SWIZZLE_128B
             return desc;
         }
+        // Descriptor for an MN-major operand tile (the M or N index is contiguous in memory, as in a
+        // column-major A or a row-major B).  The tile is stored as TMA SWIZZLE_128B boxes: each box
+        // holds one group of 128 bytes of MN (64 fp16 / 128 int8) for all K rows of the slab, one K row
+        // per 128-byte line.  8-K-row groups are 1024 bytes apart (SBO); consecutive MN groups are
+        // `group_bytes` apart (LBO).  Stepping along K adds (rows x 128 bytes) >> 4 to the start address.
+        __device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_addr, uint32_t group_bytes)
+        {
+            uint64_t desc = 0;
+            desc |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
+            desc |= static_cast<uint64_t>((group_bytes >> 4) & 0x3FFFu) << 16; // LBO
+            desc |= static_cast<uint64_t>(1024u >> 4) << 32; // SBO
+            desc |= static_cast<uint64_t>(1u) << 46; // descriptor version
+            desc |= static_cast<uint64_t>(2u) << 61; // SWIZZLE_128B
+            return desc;
+        }
     } // namespace ptx
 } // namespace b200wmma

@@ -1,17 +1,26 @@
 // Host driver of the tensor-core GEMM, mirroring gemm_test() of rocWMMA's samples/perf_hgemm.cpp:713-941:
 // fill, copy to the device, 2 warm-up + 5 timed launches, TFlops/s, spot validation.
-// Usage: perf_hgemm [m n k alpha beta]   (default 8192 8192 8192 1 1: A row-major, B col-major, C/D fp16)
+// Usage: perf_hgemm [m n k alpha beta [nt]]   (default 8192 8192 8192 1 1: A row-major, B col-major, C/D fp16;
+//        "nt" selects the layouts the reference sample ships with: A col-major, B row-major, samples/perf_hgemm.cpp:264-271)
 #include "common.hpp"
+
+#include <string>
 
 int main(int argc, char** argv)
 {
     const uint32_t m = argc > 3 ? std::atoi(argv[1]) : 8192, n = argc > 3 ? std::atoi(argv[2]) : 8192,
                    k = argc > 3 ? std::atoi(argv[3]) : 8192;
     const float alpha = argc > 5 ? std::atof(argv[4]) : 1.0f, beta = argc > 5 ? std::atof(argv[5]) : 1.0f;
+    const bool  nt    = argc > 6 && std::string(argv[6]) == "nt"; // A column-major (lda = m), B row-major (ldb = n)
     std::printf("Initializing host data...\n");
     std::vector<__half> a(size_t(m) * k), b(size_t(n) * k), c(size_t(m) * n), d(size_t(m) * n);
-    for(size_t i = 0; i < a.size(); ++i) a[i] = __float2half(float(sample::uniform(1, i)));
-    for(size_t i = 0; i < b.size(); ++i) b[i] = __float2half(float(sample::uniform(2, i))); // column-major: n rows of k
+    // logical A[i][h], B[h][j]; storage index depends on the layout
+    auto ai = [&](size_t i, size_t h) { return nt ? h * m + i : i * k + h; };
+    auto bi = [&](size_t h, size_t j) { return nt ? h * n + j : j * k + h; };
+    for(size_t i = 0; i < m; ++i)
+        for(size_t h = 0; h < k; ++h) a[ai(i, h)] = __float2half(float(sample::uniform(1, i * k + h)));
+    for(size_t h = 0; h < k; ++h)
+        for(size_t j = 0; j < n; ++j) b[bi(h, j)] = __float2half(float(sample::uniform(2, h * n + j)));
     for(size_t i = 0; i < c.size(); ++i) c[i] = __float2half(float(sample::uniform(3, i)));
     std::printf("Initializing device data...\n");
     __half *da = sample::to_device(a), *db = sample::to_device(b), *dc = sample::to_device(c), *dd = nullptr;
@@ -20,8 +29,10 @@ int main(int argc, char** argv)
     std::printf("Launching GEMM kernel...\n");
     const float ms = sample::time_launches(
         [&] {
-            CHECK_B200(b200wmma_gemm_f16(m, n, k, da, db, dc, dd, k, k, n, n, alpha, beta, B200WMMA_ROW_MAJOR,
-                                         B200WMMA_COL_MAJOR, B200WMMA_ROW_MAJOR, B200WMMA_OUT_F16, nullptr));
+            CHECK_B200(b200wmma_gemm_f16(m, n, k, da, db, dc, dd, nt ? m : k, nt ? n : k, n, n, alpha, beta,
+                                         nt ? B200WMMA_COL_MAJOR : B200WMMA_ROW_MAJOR,
+                                         nt ? B200WMMA_ROW_MAJOR : B200WMMA_COL_MAJOR, B200WMMA_ROW_MAJOR,
+                                         B200WMMA_OUT_F16, nullptr));
         },
         2, 5);
     std::printf("MatM, MatN, MatK, alpha, beta, elapsedMs, TFlops/s\n%u, %u, %u, %g, %g, %.4f, %.1f\n", m, n, k, alpha,
@@ -37,7 +48,7 @@ int main(int argc, char** argv)
             double acc = 0.0, mag = 0.0;
             for(uint32_t h = 0; h < k; ++h)
             {
-                const double av = __half2float(a[size_t(i) * k + h]), bv = __half2float(b[size_t(j) * k + h]);
+                const double av = __half2float(a[ai(i, h)]), bv = __half2float(b[bi(h, j)]);
                 acc += av * bv;
                 mag += std::fabs(av * bv);
             }

@@ -93,29 +93,68 @@ def test_gemm_f16_integer_inputs_exact():
     assert_status_ok()
 
 
+def _lds(m, n, k, la, lb, lcd):
+    return (m if la else k), (n if not lb else k), (m if lcd else n)
+
+
 def test_gemm_reference_fixtures():
-    """The committed outputs of the reference's own gemm_CPU (tests/golden/gemm_ref.npz)."""
+    """The committed outputs of the reference's own gemm_CPU (tests/golden/gemm_ref.npz), every layout case."""
     gold = np.load(os.path.join(GOLD, "gemm_ref.npz"))
     for case in GG.GEMM_CASES:
         name, m, n, k, it, ot, alpha, beta, la, lb, lc, ld = case
-        if (la, lb, lc, ld) != (0, 1, 0, 0) or it == np.float32:
+        if it == np.float32 or lc != ld:
             continue
         a, b, c, sa, sb, sc = GG.gemm_inputs(case)
-        ref = gold[name].reshape(m, n)
+        lda, ldb, ldcd = _lds(m, n, k, la, lb, lc)
+        ref = gold[name]
+        shape = (n, m) if lc else (m, n)
+        if it == np.float64 and (la, lb, lc) != (0, 1, 0):
+            continue
         if it == np.float16:
-            d = nan_filled((m, n), torch.float16 if ot == np.float16 else torch.float32)
-            api.gemm_f16(m, n, k, dev(sa), dev(sb), dev(sc), d, k, k, n, n, alpha, beta)
+            d = nan_filled(shape, torch.float16 if ot == np.float16 else torch.float32)
+            api.gemm_f16(m, n, k, dev(sa), dev(sb), dev(sc), d, lda, ldb, ldcd, ldcd, alpha, beta, la, lb, lc)
             bound = R.gemm_abs_bound(m, n, k, a, b, c, alpha, beta)
-            assert gemm_rel_err(d.cpu().numpy(), ref, bound) <= (TOL_F16_OUT if ot == np.float16 else TOL_F32_OUT), name
+            bound = np.ascontiguousarray(bound.T if lc else bound).ravel()
+            assert gemm_rel_err(d.cpu().numpy().ravel(), ref, bound) <= (TOL_F16_OUT if ot == np.float16 else TOL_F32_OUT), name
         elif it == np.int8:
-            d = nan_filled((m, n), torch.int32)
-            api.gemm_i8(m, n, k, dev(sa), dev(sb), dev(sc), d, k, k, n, n, alpha, beta)
-            assert np.array_equal(d.cpu().numpy(), ref), name
+            d = nan_filled(shape, torch.int32)
+            api.gemm_i8(m, n, k, dev(sa), dev(sb), dev(sc), d, lda, ldb, ldcd, ldcd, alpha, beta, la, lb, lc)
+            assert np.array_equal(d.cpu().numpy().ravel(), ref), name
         elif it == np.float64:
             d = nan_filled((m, n), torch.float64)
             api.gemm_f64(m, n, k, dev(sa), dev(sb), dev(sc), d, k, k, n, n, alpha, beta)
             bound = R.gemm_abs_bound(m, n, k, a, b, c, alpha, beta)
-            assert gemm_rel_err(d.cpu().numpy(), ref, bound) <= TOL_F64_OUT, name
+            assert gemm_rel_err(d.cpu().numpy(), ref.reshape(m, n), bound) <= TOL_F64_OUT, name
+    assert_status_ok()
+
+
+LAYOUTS = [(la, lb, lcd) for la in (0, 1) for lb in (0, 1) for lcd in (0, 1)]
+
+
+@pytest.mark.parametrize("la,lb,lcd", LAYOUTS, ids=["".join("RC"[x] for x in t) for t in LAYOUTS])
+@pytest.mark.parametrize("m,n,k", [(512, 256, 128), (608, 336, 208), (80, 1104, 272)])
+def test_gemm_all_layouts(la, lb, lcd, m, n, k):
+    """Every combination of row / column-major A, B and C/D (the reference sweeps NN/NT/TN/TT,
+    docs/api-reference/api-reference-guide.rst:169-187): fp16 within tolerance, int8 bit-exact.
+    Column-major A / row-major B go through MN-major tensor-core descriptors; column-major C/D through the
+    transposed problem."""
+    lda, ldb, ldcd = _lds(m, n, k, la, lb, lcd)
+    store = lambda x, col: np.ascontiguousarray(x.T if col else x)
+    # fp16
+    a = G.uniform_np(1, (m, k), np.float16); b = G.uniform_np(2, (k, n), np.float16); c = G.uniform_np(3, (m, n), np.float16)
+    sa, sb, sc = store(a, la), store(b, lb), store(c, lcd)
+    d = nan_filled(sc.shape, torch.float16)
+    api.gemm_f16(m, n, k, dev(sa), dev(sb), dev(sc), d, lda, ldb, ldcd, ldcd, 2.0, 0.5, la, lb, lcd)
+    ref = R.gemm(R.port(), m, n, k, sa.ravel(), sb.ravel(), sc.ravel(), 2.0, 0.5, np.float16, la, lb, lcd, lcd)
+    bound = store(R.gemm_abs_bound(m, n, k, a, b, c, 2.0, 0.5), lcd).ravel()
+    assert gemm_rel_err(d.cpu().numpy().ravel(), ref, bound) <= TOL_F16_OUT
+    # int8
+    ai = G.int8_np(1, (m, k)); bi = G.int8_np(2, (k, n)); ci = G.int8_np(3, (m, n)).astype(np.int32) * 1000
+    sa, sb, sc = store(ai, la), store(bi, lb), store(ci, lcd)
+    di = nan_filled(sc.shape, torch.int32)
+    api.gemm_i8(m, n, k, dev(sa), dev(sb), dev(sc), di, lda, ldb, ldcd, ldcd, 3, -1, la, lb, lcd)
+    refi = R.gemm(R.port(), m, n, k, sa.ravel(), sb.ravel(), sc.ravel(), 3, -1, np.int32, la, lb, lcd, lcd)
+    assert np.array_equal(di.cpu().numpy().ravel(), refi)
     assert_status_ok()
 
 
