@@ -75,10 +75,12 @@ def gemm_i8_sp24_workspace_bytes(m, n, k):
 
 def gemm_i8_sp24(m, n, k, a_vals, a_meta, b, c, d, lda_vals, ld_meta, ldb, ldc, ldd, alpha, beta, workspace):
     _need(a_vals, torch.int8, "a_vals"); _need(a_meta, torch.uint8, "a_meta")
-    _need(b, torch.int8, "b"); _need(d, torch.int32, "d"); _need(workspace, torch.uint8, "workspace")
+    _need(b, torch.int8, "b"); _need(d, torch.int32, "d")
+    if workspace is not None:          # needed only off the sparse tensor-core path (k % 128 != 0, unaligned rows)
+        _need(workspace, torch.uint8, "workspace")
     check(lib().b200wmma_gemm_i8_sp24(m, n, k, _ptr(a_vals), _ptr(a_meta), _ptr(b), _ptr(c), _ptr(d),
                                       lda_vals, ld_meta, ldb, ldc, ldd, alpha, beta,
-                                      _ptr(workspace), workspace.numel(), _stream()))
+                                      _ptr(workspace), 0 if workspace is None else workspace.numel(), _stream()))
 
 
 def gemm_i4_workspace_bytes(m, n, k):

@@ -74,4 +74,12 @@ namespace b200wmma
                             uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha,
                             int32_t beta, int layout_a, int layout_b, int layout_cd,
                             cudaStream_t stream);
+    // 2:4-sparse int8 GEMM on compressed A (values + metadata) without a densified copy.
+    // sp24_direct_ok() tells whether the operands meet its shape / alignment rules.
+    bool sp24_direct_ok(uint32_t k, const void* a_vals, const void* a_meta, const void* b, uint32_t lda_vals,
+                        uint32_t ld_meta, uint32_t ldb);
+    int  launch_gemm_tc05_i8_sp24(uint32_t m, uint32_t n, uint32_t k, const int8_t* a_vals, const uint8_t* a_meta,
+                                  const int8_t* b, const int32_t* c, int32_t* d, uint32_t lda_vals, uint32_t ld_meta,
+                                  uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha, int32_t beta,
+                                  cudaStream_t stream);
 } // namespace b200wmma

@@ -5,11 +5,16 @@
 // in test/gemm/gemm_common_test_params.hpp:51-147) applied to the densified / sign-extended
 // operands, bit-exact in int32.
 //
-// Both variants expand the compressed operand(s) to K-major int8 in a caller-provided device
-// workspace with one streaming pass (16-byte loads and stores), then run the tcgen05 int8
-// GEMM on the expanded operands.
+// The sparse GEMM runs on the sparse tensor-core path (gemm_tc05_sp.cuh: compressed values and
+// metadata straight into tcgen05.mma.sp) whenever k is a multiple of 128 and the rows are 16-byte
+// aligned.  Otherwise, and always for int4 (the sm_100 tensor cores have no 4-bit integer kind),
+// the compressed operand(s) are expanded to K-major int8 in a caller-provided device workspace
+// with one streaming pass (16-byte loads and stores) and the dense tcgen05 int8 GEMM runs on the
+// expanded operands.
 #include "common.cuh"
 
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 namespace b200wmma
@@ -94,6 +99,15 @@ namespace b200wmma
         {
             return (x + 255) & ~static_cast<size_t>(255);
         }
+        // B200WMMA_SP24_PATH=expand sends every sparse GEMM through the densifying pass (comparison aid).
+        static bool force_expansion()
+        {
+            static int v = []() {
+                const char* e = std::getenv("B200WMMA_SP24_PATH");
+                return (e && std::strcmp(e, "expand") == 0) ? 1 : 0;
+            }();
+            return v != 0;
+        }
     } // namespace i8var
 } // namespace b200wmma
 
@@ -118,11 +132,19 @@ extern "C" int b200wmma_gemm_i8_sp24(uint32_t m, uint32_t n, uint32_t k, const i
 {
     clear_error();
     B200_REQUIRE(m && n && k, B200WMMA_ERR_INVALID_ARG, "gemm_i8_sp24: m, n, k must be non-zero");
-    B200_REQUIRE(a_vals && a_meta && b && d && workspace, B200WMMA_ERR_INVALID_ARG,
-                 "gemm_i8_sp24: a_vals, a_meta, b, d, workspace must be non-null");
+    B200_REQUIRE(a_vals && a_meta && b && d, B200WMMA_ERR_INVALID_ARG,
+                 "gemm_i8_sp24: a_vals, a_meta, b, d must be non-null");
     B200_REQUIRE(k % 32 == 0, B200WMMA_ERR_UNSUPPORTED, "gemm_i8_sp24: k must be a multiple of 32");
     B200_REQUIRE(lda_vals >= k / 2 && ld_meta >= k / 8, B200WMMA_ERR_INVALID_ARG,
                  "gemm_i8_sp24: lda_vals / ld_meta smaller than k/2 / k/8");
+    // Sparse tensor-core path: compressed A goes to the tensor cores as it is, no scratch involved.
+    if(!i8var::force_expansion() && sp24_direct_ok(k, a_vals, a_meta, b, lda_vals, ld_meta, ldb))
+        return launch_gemm_tc05_i8_sp24(m, n, k, a_vals, a_meta, b, c, d, lda_vals, ld_meta, ldb, ldc, ldd, alpha, beta,
+                                        as_stream(stream));
+    // Otherwise (k not a multiple of 128, or rows that TMA cannot address): densify A into the
+    // workspace and run the dense int8 kernel.
+    B200_REQUIRE(workspace, B200WMMA_ERR_INVALID_ARG,
+                 "gemm_i8_sp24: this shape / alignment needs the workspace (k %% 128 != 0 or rows not 16-byte aligned)");
     B200_REQUIRE(aligned16(a_vals) && lda_vals % 16 == 0 && (reinterpret_cast<uintptr_t>(a_meta) & 3) == 0
                      && ld_meta % 4 == 0 && aligned16(workspace),
                  B200WMMA_ERR_ALIGNMENT,

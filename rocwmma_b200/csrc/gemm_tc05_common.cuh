@@ -286,6 +286,25 @@ namespace b200wmma
             return B200WMMA_OK;
         }
 
+        // Byte matrix (`rows` rows of `row_bytes` bytes, pitch `pitch_bytes`) tiled in boxes of
+        // box_bytes x box_rows with the given swizzle; zero fill out of bounds.
+        static int make_bytes_tmap(CUtensorMap* out, const void* ptr, uint32_t rows, uint32_t row_bytes,
+                                   uint64_t pitch_bytes, uint32_t box_bytes, uint32_t box_rows, CUtensorMapSwizzle swizzle)
+        {
+            EncodeTiledFn fn = get_encode_fn();
+            B200_REQUIRE(fn != nullptr, B200WMMA_ERR_CUDA, "cuTensorMapEncodeTiled not available");
+            cuuint64_t gdim[2]    = {row_bytes, rows};
+            cuuint64_t gstride[1] = {pitch_bytes};
+            cuuint32_t box[2]     = {box_bytes, box_rows};
+            cuuint32_t estr[2]    = {1, 1};
+            CUresult   r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            B200_REQUIRE(r == CUDA_SUCCESS, B200WMMA_ERR_CUDA,
+                         "cuTensorMapEncodeTiled (byte matrix) failed with CUresult %d", static_cast<int>(r));
+            return B200WMMA_OK;
+        }
+
         // MN-major operand: `k_extent` rows of `mn_extent` contiguous elements, row pitch ld elements
         // (a column-major A or a row-major B).  Box = 128 bytes of MN x one K slab of rows.
         static int make_mnmajor_tmap(CUtensorMap* out, CUtensorMapDataType dtype, uint32_t elem_bytes, const void* ptr,

@@ -51,11 +51,12 @@ namespace b200wmma
         // tile to a TMA store and request the C tile two steps ahead into the same buffer once the
         // store has read it.  TMA clips rows / columns outside the matrix, so ragged edges need no
         // special case.  All 32 lanes execute every step.
-        template <typename OutT, typename ScalarT>
+        // TN: columns of the accumulator being drained.
+        template <typename OutT, typename ScalarT, uint32_t TN = TILE_N>
         struct StagedDrain
         {
             static constexpr uint32_t STEP_COLS = 64 / sizeof(OutT);
-            static constexpr uint32_t STEPS     = TILE_N / STEP_COLS;
+            static constexpr uint32_t STEPS     = TN / STEP_COLS;
 
             // requests the C tiles of steps 0 and 1 (called while the tile is still being multiplied)
             __device__ static __forceinline__ void prefetch_c(const CUtensorMap* tmap_c, uint32_t buf0, uint32_t cbar0,

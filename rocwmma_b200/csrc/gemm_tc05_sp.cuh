@@ -1,0 +1,314 @@
+// 2:4 structured-sparse int8 GEMM on the sparse tensor-core path (tcgen05.mma.sp, kind::i8).
+//
+// rocWMMA v1.6.0 has no sparse GEMM; the semantics are the dense int8 GEMM of
+// gemm_rocwmma_d (samples/perf_hgemm.cpp:515-711 with the int8 / int32 types of
+// test/gemm/gemm_common_test_params.hpp:51-147) applied to the densified A, bit-exact in int32.
+//
+// A never exists in dense form on the device.  The kernel streams the compressed values
+// (m x k/2 bytes) and the position metadata (m x k/8 bytes) as they are:
+//   * values: TMA boxes of 64 bytes x 256 rows with the 64-byte swizzle (128 logical K per slab);
+//   * metadata: TMA boxes of 16 bytes x 256 rows, unswizzled (row r at r * 16 bytes).  One
+//     tcgen05.cp moves a 128-row sub-tile (2 KiB) into 4 tensor-memory columns, where the two MMAs
+//     of the slab read it (2 columns = 64 logical K each).  The byte format of the C interface - one
+//     nibble idx0 | idx1 << 2 per group of four K positions, low nibble = even group - is the
+//     hardware's own, so no repacking pass is needed;
+//   * B: TMA boxes of 128 bytes x 112 rows, 128-byte swizzle (each CTA of the pair loads half of N).
+// One tcgen05.mma.sp consumes 32 bytes per row of compressed A and 64 bytes per row of B: twice the
+// logical K of a dense int8 MMA per instruction.
+//
+// Tile: 512 x 224 per SM pair.  Each CTA owns 256 rows (two 128-lane accumulators of 224 columns =
+// 448 tensor-memory columns); the metadata needs 8 columns per pipeline stage (5 stages = 40),
+// which is why N is 224 and not 256: 2 x 256 accumulator columns would leave no room for it.  The
+// tall tile keeps the L2 -> shared-memory traffic at ~78 bytes per clock per SM at full sparse
+// rate (a 256 x 256 pair tile would need ~104).
+//
+// Roles and barrier protocol are those of gemm_tc05_pair512.cuh: warp 0 TMA producer (one lane,
+// both CTAs, loads counted on the leader's full[s]), warp 1 tensor-memory owner and MMA issuer (one
+// lane, leader only; commits signal both CTAs), warps 2-9 epilogue through TMA-staged C / D tiles.
+// Every wait is bounded.
+#pragma once
+#include "gemm_tc05_common.cuh"
+#include "gemm_tc05_pair512.cuh"
+
+namespace b200wmma
+{
+    namespace tc05s
+    {
+        using namespace tc05;
+
+        constexpr uint32_t SUB_M         = 128; // rows per MMA per CTA
+        constexpr uint32_t CTA_M         = 256; // rows of A / D per CTA (two accumulators)
+        constexpr uint32_t PAIR_M        = 512;
+        constexpr uint32_t TILE_N        = 224;
+        constexpr uint32_t HALF_N        = 112;
+        constexpr uint32_t SLAB_K        = 128; // logical K per pipeline stage
+        constexpr uint32_t STAGES        = 5;
+        constexpr uint32_t A_ROW_BYTES   = SLAB_K / 2; // 64: compressed values
+        constexpr uint32_t E_ROW_BYTES   = SLAB_K / 8; // 16: metadata
+        constexpr uint32_t A_STAGE_BYTES = CTA_M * A_ROW_BYTES; // 16 KiB
+        constexpr uint32_t E_STAGE_BYTES = CTA_M * E_ROW_BYTES; // 4 KiB
+        constexpr uint32_t B_STAGE_BYTES = HALF_N * SLAB_K; // 14 KiB
+        constexpr uint32_t STAGE_BYTES   = A_STAGE_BYTES + E_STAGE_BYTES + B_STAGE_BYTES;
+        constexpr uint32_t EPI_WARPS     = 8;
+        constexpr uint32_t NUM_THREADS   = 64 + EPI_WARPS * 32;
+        constexpr uint32_t TMEM_COLS     = 512;
+        constexpr uint32_t E_COL0        = 2 * TILE_N; // metadata columns: E_COL0 + 8 * stage + 4 * sub-tile
+        constexpr uint32_t GROUP_M       = 8;
+        constexpr uint32_t EPI_BUF_BYTES = tc05q::EPI_BUF_BYTES;
+        constexpr uint32_t EPI_BYTES     = EPI_WARPS * 2 * EPI_BUF_BYTES;
+        constexpr uint32_t MISC_BYTES    = 512;
+        constexpr uint32_t SMEM_BYTES    = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + MISC_BYTES;
+        static_assert(E_COL0 + 8 * STAGES <= TMEM_COLS, "metadata does not fit beside the accumulators");
+        static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+
+        __global__ void __launch_bounds__(NUM_THREADS, 1)
+            gemm_tc05_sp_kernel(const __grid_constant__ CUtensorMap tmap_a, // compressed values, 64 B x 256 rows, SW64
+                                const __grid_constant__ CUtensorMap tmap_e, // metadata, 16 B x 256 rows
+                                const __grid_constant__ CUtensorMap tmap_b, // B^T rows, 128 B x 112 rows, SW128
+                                const __grid_constant__ CUtensorMap tmap_c,
+                                const __grid_constant__ CUtensorMap tmap_d,
+                                const int32_t* __restrict__ c,
+                                int32_t* __restrict__ d,
+                                uint32_t  m,
+                                uint32_t  n,
+                                uint32_t  k, // logical K, a multiple of SLAB_K
+                                uint32_t  ldc,
+                                uint32_t  ldd,
+                                int32_t   alpha,
+                                int32_t   beta,
+                                uint32_t  tiles_m,
+                                uint32_t  tiles_n,
+                                int       vec_ok,
+                                uint32_t  group_m,
+                                unsigned* status)
+        {
+            extern __shared__ uint8_t smem_raw[];
+            const uint32_t            raw_addr = ptx::smem_u32(smem_raw);
+            const uint32_t            base     = (raw_addr + 1023u) & ~1023u;
+            uint8_t*                  smem     = smem_raw + (base - raw_addr);
+
+            // [A stages][B stages][E stages][epilogue staging tiles][barriers, tensor-memory slot, abort flag]
+            const uint32_t     smem_a     = base;
+            const uint32_t     smem_b     = smem_a + STAGES * A_STAGE_BYTES;
+            const uint32_t     smem_e     = smem_b + STAGES * B_STAGE_BYTES;
+            const uint32_t     epi_off    = STAGES * STAGE_BYTES;
+            const uint32_t     misc_off   = epi_off + EPI_BYTES;
+            const uint32_t     bar_base   = base + misc_off;
+            const uint32_t     full_bar   = bar_base; // STAGES x 8 (leader's copy in use)
+            const uint32_t     empty_bar  = bar_base + 64;
+            const uint32_t     tfull_bar  = bar_base + 128;
+            const uint32_t     tempty_bar = bar_base + 136; // 2 x 8, one per accumulator (leader's copy in use)
+            const uint32_t     cbar_base  = bar_base + 160; // EPI_WARPS x 2 x 8
+            uint32_t*          tmem_slot  = reinterpret_cast<uint32_t*>(smem + misc_off + 160 + EPI_WARPS * 16);
+            volatile uint32_t* cta_abort  = tmem_slot + 1;
+
+            const uint32_t warp      = threadIdx.x >> 5;
+            const uint32_t lane      = threadIdx.x & 31u;
+            const uint32_t rank      = ptx::cluster_ctarank();
+            const uint32_t pair      = blockIdx.x >> 1;
+            const uint32_t num_pairs = gridDim.x >> 1;
+            const uint32_t num_tiles = tiles_m * tiles_n;
+            const uint32_t num_kb    = k / SLAB_K;
+
+            if(threadIdx.x == 0)
+            {
+                ptx::prefetch_tensormap(&tmap_a);
+                ptx::prefetch_tensormap(&tmap_e);
+                ptx::prefetch_tensormap(&tmap_b);
+                ptx::prefetch_tensormap(&tmap_c);
+                ptx::prefetch_tensormap(&tmap_d);
+                for(uint32_t s = 0; s < STAGES; ++s)
+                {
+                    ptx::mbar_init(full_bar + 8 * s, 1);
+                    ptx::mbar_init(empty_bar + 8 * s, 1);
+                }
+                ptx::mbar_init(tfull_bar, 1);
+                ptx::mbar_init(tempty_bar, 8); // accumulator 0: 4 warps x 2 CTAs
+                ptx::mbar_init(tempty_bar + 8, 8); // accumulator 1
+                for(uint32_t i = 0; i < EPI_WARPS * 2; ++i)
+                    ptx::mbar_init(cbar_base + 8 * i, 1);
+                *cta_abort = 0u;
+                ptx::fence_barrier_init();
+                ptx::fence_proxy_async_smem();
+            }
+            if(warp == 1)
+            {
+                ptx::tmem_alloc_pair(ptx::smem_u32(tmem_slot), TMEM_COLS);
+                ptx::tmem_relinquish_pair();
+            }
+            ptx::tc_fence_before_sync();
+            ptx::cluster_sync();
+            ptx::tc_fence_after_sync();
+            const uint32_t tmem_base = *tmem_slot;
+
+            if(warp == 0)
+            {
+                // ------------------------------ TMA producer (both CTAs) ------------------------------
+                if(lane == 0)
+                {
+                    uint32_t stage = 0, phase = 0;
+                    bool     ok = true;
+                    for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs)
+                    {
+                        uint32_t m_idx, n_idx;
+                        tile_coords(tile, tiles_m, tiles_n, group_m, m_idx, n_idx);
+                        const int32_t row_a = static_cast<int32_t>(m_idx * PAIR_M + rank * CTA_M);
+                        const int32_t row_b = static_cast<int32_t>(n_idx * TILE_N + rank * HALF_N);
+                        for(uint32_t kb = 0; kb < num_kb; ++kb)
+                        {
+                            ok = ptx::mbar_wait_bounded(empty_bar + 8 * stage, phase ^ 1u, cta_abort, status,
+                                                        (ROLE_PRODUCER << 24) | blockIdx.x, WAIT_TIMEOUT_NS);
+                            if(!ok)
+                                break;
+                            if(rank == 0)
+                                ptx::mbar_arrive_expect_tx(full_bar + 8 * stage, 2u * STAGE_BYTES);
+                            const uint32_t leader_full = ptx::mapa(full_bar + 8 * stage, 0u);
+                            // inner coordinates are byte offsets into the value / metadata / B rows:
+                            // 64, 16 and 128 bytes per slab, all multiples of 16
+                            ptx::tma_load_2d_pair(smem_a + stage * A_STAGE_BYTES, &tmap_a,
+                                                  static_cast<int32_t>(kb * A_ROW_BYTES), row_a, leader_full);
+                            ptx::tma_load_2d_pair(smem_e + stage * E_STAGE_BYTES, &tmap_e,
+                                                  static_cast<int32_t>(kb * E_ROW_BYTES), row_a, leader_full);
+                            ptx::tma_load_2d_pair(smem_b + stage * B_STAGE_BYTES, &tmap_b,
+                                                  static_cast<int32_t>(kb * SLAB_K), row_b, leader_full);
+                            if(++stage == STAGES)
+                            {
+                                stage = 0;
+                                phase ^= 1u;
+                            }
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+            else if(warp == 1)
+            {
+                // ------------------------------- MMA issuer (leader only) -------------------------------
+                if(lane == 0 && rank == 0)
+                {
+                    // dense int8 descriptor with the sparsity flag (bit 2); metadata format id 0
+                    constexpr uint32_t idesc = make_idesc<KIND_I8, 2 * SUB_M, TILE_N>() | (1u << 2);
+                    uint32_t           stage = 0, phase = 0, iter = 0;
+                    bool               ok = true;
+                    for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++iter)
+                    {
+                        const uint32_t tphase = iter & 1u;
+                        for(uint32_t kb = 0; kb < num_kb && ok; ++kb)
+                        {
+                            ok = ptx::mbar_wait_bounded(full_bar + 8 * stage, phase, cta_abort, status,
+                                                        (ROLE_MMA << 24) | (1u << 20) | blockIdx.x, WAIT_TIMEOUT_NS);
+                            if(!ok)
+                                break;
+                            ptx::tc_fence_after_sync();
+                            const uint64_t b_desc = ptx::make_kmajor_sw128_desc(smem_b + stage * B_STAGE_BYTES);
+#pragma unroll
+                            for(uint32_t j = 0; j < 2; ++j)
+                            {
+                                if(kb == 0)
+                                {
+                                    // accumulator j of the previous tile must have been drained by both CTAs
+                                    ok = ptx::mbar_wait_bounded(tempty_bar + 8 * j, tphase ^ 1u, cta_abort, status,
+                                                                (ROLE_MMA << 24) | blockIdx.x, WAIT_TIMEOUT_NS);
+                                    if(!ok)
+                                        break;
+                                    ptx::tc_fence_after_sync();
+                                }
+                                // metadata of sub-tile j: 128 rows x 16 bytes -> 4 columns, in both CTAs
+                                const uint32_t e_tmem = tmem_base + E_COL0 + 8u * stage + 4u * j;
+                                ptx::tmem_cp_128x128b_pair(
+                                    e_tmem, ptx::make_rows16_desc(smem_e + stage * E_STAGE_BYTES + j * (SUB_M * E_ROW_BYTES)));
+                                const uint64_t a_desc
+                                    = ptx::make_kmajor_sw64_desc(smem_a + stage * A_STAGE_BYTES + j * (SUB_M * A_ROW_BYTES));
+#pragma unroll
+                                for(uint32_t ks = 0; ks < SLAB_K / 64; ++ks)
+                                {
+                                    // 64 logical K per MMA: 32 bytes of compressed A (+2), 64 bytes of B (+4),
+                                    // 2 metadata columns
+                                    const uint32_t acc = (kb | ks) != 0u ? 1u : 0u;
+                                    ptx::mma_i8_sp_ss_pair(tmem_base + j * TILE_N, a_desc + 2 * ks, b_desc + 4 * ks,
+                                                           e_tmem + 2 * ks, idesc, acc);
+                                }
+                            }
+                            if(!ok)
+                                break;
+                            ptx::tc_commit_pair(empty_bar + 8 * stage, 0x3);
+                            if(++stage == STAGES)
+                            {
+                                stage = 0;
+                                phase ^= 1u;
+                            }
+                        }
+                        if(ok)
+                            ptx::tc_commit_pair(tfull_bar, 0x3);
+                    }
+                }
+                __syncwarp();
+            }
+            else
+            {
+                // -------------------------------- epilogue (both CTAs) --------------------------------
+                const uint32_t e       = warp - 2u; // 0..7
+                const uint32_t quad    = warp & 3u; // lane quadrant this warp may read
+                const uint32_t j       = e >> 2; // accumulator: warps 2-5 -> 0, warps 6-9 -> 1
+                const bool     read_c  = (beta != 0) && (c != nullptr);
+                const uint32_t buf_off = epi_off + e * 2u * EPI_BUF_BYTES;
+                const uint32_t buf0    = base + buf_off;
+                const uint32_t cbar0   = cbar_base + e * 16u;
+                using Drain            = tc05q::StagedDrain<int32_t, int32_t, TILE_N>;
+                uint32_t iter = 0, cpar = 0;
+                bool     ok   = true;
+                for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++iter)
+                {
+                    uint32_t m_idx, n_idx;
+                    tile_coords(tile, tiles_m, tiles_n, group_m, m_idx, n_idx);
+                    const uint32_t row_base = m_idx * PAIR_M + rank * CTA_M + j * SUB_M;
+                    const uint32_t row0     = row_base + quad * 32u;
+                    const uint32_t col_base = n_idx * TILE_N;
+                    const bool     staged   = vec_ok != 0 && row0 < m && col_base < n;
+                    if(staged && read_c && lane == 0)
+                        Drain::prefetch_c(&tmap_c, buf0, cbar0, col_base, row0, n);
+                    ok = ptx::mbar_wait_bounded_warp(tfull_bar, iter & 1u, cta_abort, status,
+                                                     (ROLE_EPILOGUE << 24) | blockIdx.x, WAIT_TIMEOUT_NS, lane);
+                    if(!ok)
+                        break;
+                    ptx::tc_fence_after_sync();
+                    const uint32_t tmem_acc = tmem_base + j * TILE_N;
+                    if(staged)
+                        ok = Drain::run(tmem_acc, quad, lane, smem, buf_off, buf0, cbar0, &tmap_c, &tmap_d, col_base, row0, n,
+                                        alpha, beta, read_c, cpar, cta_abort, status,
+                                        (ROLE_EPILOGUE << 24) | (1u << 20) | blockIdx.x);
+                    else if(vec_ok == 0)
+                        drain_accumulator<int32_t, int32_t, TILE_N>(tmem_acc, quad, lane, row_base, col_base, m, n, c, d, ldc,
+                                                                    ldd, alpha, beta, read_c, 0);
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if(lane == 0)
+                        ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar + 8 * j, 0u));
+                }
+                if(lane == 0)
+                    ptx::bulk_wait_group<0>(); // the staging tiles must outlive the stores that read them
+                __syncwarp();
+            }
+
+            // ---------------------------------- teardown ----------------------------------
+            ptx::tc_fence_before_sync();
+            ptx::cluster_sync();
+            {
+                const uint32_t peer_abort = ptx::ld_shared_cluster_u32(
+                    ptx::mapa(ptx::smem_u32(const_cast<uint32_t*>(cta_abort)), rank ^ 1u));
+                if(*cta_abort || peer_abort)
+                {
+                    const uint64_t t0 = ptx::globaltimer_ns();
+                    while(ptx::globaltimer_ns() - t0 < 2000000ull)
+                        __nanosleep(1000);
+                }
+            }
+            ptx::cluster_sync();
+            if(warp == 1)
+            {
+                ptx::tc_fence_after_sync();
+                ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+            }
+        }
+    } // namespace tc05s
+} // namespace b200wmma

@@ -171,17 +171,71 @@ def test_gemm_i8_bit_exact(m, n, k, alpha, beta):
     assert np.array_equal(d.cpu().numpy(), ref)
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (200, 136, 512), (256, 256, 4096)])
-def test_gemm_i8_sparse24_bit_exact(m, n, k):
+# k % 128 == 0 with 16-byte aligned rows runs on the sparse tensor cores (512 x 224 pair tiles: the shapes
+# cross tile edges in M and N and include ragged ones); the other shapes take the densify-then-dense path.
+@pytest.mark.parametrize("m,n,k,alpha,beta", [(128, 256, 128, 1, 0), (200, 136, 512, 1, 0), (256, 256, 4096, 1, 0),
+                                              (1100, 500, 384, 3, -2), (513, 225, 256, 1, 1), (64, 1000, 128, -1, 1),
+                                              (300, 200, 96, 1, 0), (130, 72, 160, 2, 1)])
+def test_gemm_i8_sparse24_bit_exact(m, n, k, alpha, beta):
     dense = G.int8_np(G.SEED_A, (m, k)); b = G.int8_np(G.SEED_B, (k, n))
+    c = G.int8_np(G.SEED_C, (m, n)).astype(np.int32) * 54321
     vals, meta, densified = G.sparsify_24_np(dense)
     bs = np.ascontiguousarray(b.T)
     ws = torch.empty(api.gemm_i8_sp24_workspace_bytes(m, n, k), dtype=torch.uint8, device="cuda")
     d = nan_filled((m, n), torch.int32)
-    api.gemm_i8_sp24(m, n, k, dev(vals), dev(meta), dev(bs), None, d, k // 2, k // 8, k, n, n, 1, 0, ws)
+    api.gemm_i8_sp24(m, n, k, dev(vals), dev(meta), dev(bs), dev(c) if beta else None, d, k // 2, k // 8, k, n, n,
+                     alpha, beta, ws)
     assert_status_ok()
-    ref = oracle_gemm_rows(densified, bs, None, 1, 0, np.int32, n, k)
+    ref = oracle_gemm_rows(densified, bs, c if beta else None, alpha, beta, np.int32, n, k)
     assert np.array_equal(d.cpu().numpy(), ref)
+
+
+def test_gemm_i8_sparse24_padded_pitches_no_workspace():
+    """Row pitches larger than the rows (values, metadata, B, C, D), D rows not 16-byte aligned (element-wise
+    epilogue), and no workspace: the sparse tensor-core path needs none."""
+    m, n, k = 700, 451, 640
+    lda, ldm, ldb, ldc, ldd = k // 2 + 64, k // 8 + 16, k + 128, n + 5, n + 3
+    dense = G.int8_np(G.SEED_A, (m, k)); b = G.int8_np(G.SEED_B, (k, n))
+    c = G.int8_np(G.SEED_C, (m, n)).astype(np.int32) * 777
+    vals, meta, densified = G.sparsify_24_np(dense)
+    bs = np.ascontiguousarray(b.T)
+    pad = lambda x, ld, fill: np.concatenate([x, np.full((x.shape[0], ld - x.shape[1]), fill, x.dtype)], axis=1)
+    d = torch.full((m, ldd), -7, dtype=torch.int32, device="cuda")
+    api.gemm_i8_sp24(m, n, k, dev(pad(vals, lda, 99)), dev(pad(meta, ldm, 0xEE)), dev(pad(bs, ldb, 55)),
+                     dev(pad(c, ldc, 1 << 30)), d, lda, ldm, ldb, ldc, ldd, 2, 3, None)
+    assert_status_ok()
+    ref = oracle_gemm_rows(densified, bs, c, 2, 3, np.int32, n, k)
+    out = d.cpu().numpy()
+    assert np.array_equal(out[:, :n], ref)
+    assert np.all(out[:, n:] == -7)          # nothing written past the row ends
+
+
+def test_gemm_i8_sparse24_full_size_row_sample():
+    """M=N=8192, K=16384, 2:4-sparse A: 32 seeded-random rows bit-exact against the oracle on the densified
+    rows, and the exact column-sum checksum over the whole output."""
+    m, n, k = 8192, 8192, 16384
+    dense = G.fill_torch(torch.empty((m, k), dtype=torch.int8, device="cuda"), G.SEED_A, "int8")
+    vals = torch.empty((m, k // 2), dtype=torch.int8, device="cuda")
+    meta = torch.empty((m, k // 8), dtype=torch.uint8, device="cuda")
+    densified = torch.empty((m, k), dtype=torch.int8, device="cuda")
+    for r0 in range(0, m, 1024):                      # compress on the host in row chunks
+        v, md, dn = G.sparsify_24_np(dense[r0:r0 + 1024].cpu().numpy(), row_start=r0)
+        vals[r0:r0 + 1024] = torch.from_numpy(v).cuda()
+        meta[r0:r0 + 1024] = torch.from_numpy(md).cuda()
+        densified[r0:r0 + 1024] = torch.from_numpy(dn).cuda()
+    del dense
+    bs = G.fill_torch(torch.empty((n, k), dtype=torch.int8, device="cuda"), G.SEED_B, "int8")
+    d = nan_filled((m, n), torch.int32)
+    api.gemm_i8_sp24(m, n, k, vals, meta, bs, None, d, k // 2, k // 8, k, n, n, 1, 0, None)
+    assert_status_ok()
+    rows = _rows_sample(m, 32, 97)
+    idx = torch.from_numpy(rows).cuda()
+    ref = oracle_gemm_rows(densified[idx].cpu().numpy(), bs.cpu().numpy(), None, 1, 0, np.int32, n, k)
+    assert np.array_equal(d[idx].cpu().numpy(), ref)
+    col = d.to(torch.int64).sum(dim=0)
+    a_sum = densified.to(torch.float64).sum(dim=0)
+    expect = bs.to(torch.float64) @ a_sum
+    assert torch.equal(col.to(torch.float64), expect)
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 128), (200, 136, 512), (256, 256, 4096)])
