@@ -8,8 +8,8 @@
 // (m x k/2 bytes) and the position metadata (m x k/8 bytes) as they are:
 //   * values: TMA boxes of 64 bytes x 256 rows with the 64-byte swizzle (128 logical K per slab);
 //   * metadata: TMA boxes of 16 bytes x 256 rows, unswizzled (row r at r * 16 bytes).  One
-//     tcgen05.cp moves a 128-row sub-tile (2 KiB) into 4 tensor-memory columns, where the two MMAs
-//     of the slab read it (2 columns = 64 logical K each).  The byte format of the C interface - one
+//     tcgen05.cp per slab moves both 128-row sub-tiles (4 KiB) into 8 tensor-memory columns, 4 per
+//     sub-tile, where the two MMAs of each sub-tile read them (2 columns = 64 logical K each).  The byte format of the C interface - one
 //     nibble idx0 | idx1 << 2 per group of four K positions, low nibble = even group - is the
 //     hardware's own, so no repacking pass is needed;
 //   * B: TMA boxes of 128 bytes x 112 rows, 128-byte swizzle (each CTA of the pair loads half of N).
@@ -146,35 +146,42 @@ namespace b200wmma
                 // ------------------------------ TMA producer (both CTAs) ------------------------------
                 if(lane == 0)
                 {
-                    uint32_t stage = 0, phase = 0;
-                    bool     ok = true;
+                    // one slab every 448 clocks at full rate: the loop advances addresses by constant adds
+                    const uint32_t leader_full0 = ptx::mapa(full_bar, 0u);
+                    uint32_t       stage = 0, phase = 0;
+                    uint32_t       sa = smem_a, sb = smem_b, se = smem_e, eb = empty_bar, fb = full_bar, lf = leader_full0;
+                    bool           ok = true;
                     for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs)
                     {
                         uint32_t m_idx, n_idx;
                         tile_coords(tile, tiles_m, tiles_n, group_m, m_idx, n_idx);
                         const int32_t row_a = static_cast<int32_t>(m_idx * PAIR_M + rank * CTA_M);
                         const int32_t row_b = static_cast<int32_t>(n_idx * TILE_N + rank * HALF_N);
+                        // inner coordinates are byte offsets into the value / metadata / B rows: 64, 16 and
+                        // 128 bytes per slab, all multiples of 16
+                        int32_t ka = 0, ke = 0, kbb = 0;
                         for(uint32_t kb = 0; kb < num_kb; ++kb)
                         {
-                            ok = ptx::mbar_wait_bounded(empty_bar + 8 * stage, phase ^ 1u, cta_abort, status,
-                                                        (ROLE_PRODUCER << 24) | blockIdx.x, WAIT_TIMEOUT_NS);
+                            ok = ptx::mbar_wait_bounded(eb, phase ^ 1u, cta_abort, status, (ROLE_PRODUCER << 24) | blockIdx.x,
+                                                        WAIT_TIMEOUT_NS);
                             if(!ok)
                                 break;
                             if(rank == 0)
-                                ptx::mbar_arrive_expect_tx(full_bar + 8 * stage, 2u * STAGE_BYTES);
-                            const uint32_t leader_full = ptx::mapa(full_bar + 8 * stage, 0u);
-                            // inner coordinates are byte offsets into the value / metadata / B rows:
-                            // 64, 16 and 128 bytes per slab, all multiples of 16
-                            ptx::tma_load_2d_pair(smem_a + stage * A_STAGE_BYTES, &tmap_a,
-                                                  static_cast<int32_t>(kb * A_ROW_BYTES), row_a, leader_full);
-                            ptx::tma_load_2d_pair(smem_e + stage * E_STAGE_BYTES, &tmap_e,
-                                                  static_cast<int32_t>(kb * E_ROW_BYTES), row_a, leader_full);
-                            ptx::tma_load_2d_pair(smem_b + stage * B_STAGE_BYTES, &tmap_b,
-                                                  static_cast<int32_t>(kb * SLAB_K), row_b, leader_full);
+                                ptx::mbar_arrive_expect_tx(fb, 2u * STAGE_BYTES);
+                            ptx::tma_load_2d_pair(sb, &tmap_b, kbb, row_b, lf);
+                            ptx::tma_load_2d_pair(sa, &tmap_a, ka, row_a, lf);
+                            ptx::tma_load_2d_pair(se, &tmap_e, ke, row_a, lf);
+                            ka += static_cast<int32_t>(A_ROW_BYTES), ke += static_cast<int32_t>(E_ROW_BYTES),
+                                kbb += static_cast<int32_t>(SLAB_K);
                             if(++stage == STAGES)
                             {
                                 stage = 0;
                                 phase ^= 1u;
+                                sa = smem_a, sb = smem_b, se = smem_e, eb = empty_bar, fb = full_bar, lf = leader_full0;
+                            }
+                            else
+                            {
+                                sa += A_STAGE_BYTES, sb += B_STAGE_BYTES, se += E_STAGE_BYTES, eb += 8u, fb += 8u, lf += 8u;
                             }
                         }
                     }
@@ -186,60 +193,74 @@ namespace b200wmma
                 // ------------------------------- MMA issuer (leader only) -------------------------------
                 if(lane == 0 && rank == 0)
                 {
+                    // One thread feeds the tensor cores of both SMs, and a slab's four MMAs run for only 448
+                    // clocks: the instructions this thread executes per slab decide whether the tensor pipe
+                    // idles.  The ring is therefore walked by an unrolled loop over the stages, so that every
+                    // descriptor, metadata column and barrier address is a loop-invariant value (base plus a
+                    // compile-time offset) and a slab costs little more than its wait, copy, MMAs and commit.
                     // dense int8 descriptor with the sparsity flag (bit 2); metadata format id 0
-                    constexpr uint32_t idesc = make_idesc<KIND_I8, 2 * SUB_M, TILE_N>() | (1u << 2);
-                    uint32_t           stage = 0, phase = 0, iter = 0;
-                    bool               ok = true;
-                    for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++iter)
+                    constexpr uint32_t idesc  = make_idesc<KIND_I8, 2 * SUB_M, TILE_N>() | (1u << 2);
+                    constexpr uint64_t A_STEP = A_STAGE_BYTES >> 4, B_STEP = B_STAGE_BYTES >> 4, E_STEP = E_STAGE_BYTES >> 4;
+                    constexpr uint64_t A_SUB  = (SUB_M * A_ROW_BYTES) >> 4; // second 128-row sub-tile
+                    const uint64_t     a_desc0 = ptx::make_kmajor_sw64_desc(smem_a);
+                    const uint64_t     b_desc0 = ptx::make_kmajor_sw128_desc(smem_b);
+                    // metadata source: the two 128-row blocks of a stage (2 KiB apart) are the two 16-byte
+                    // column blocks of a 128 x 32-byte tile; one copy fills 8 columns (4 per sub-tile)
+                    const uint64_t e_desc0 = ptx::make_rows16_desc(smem_e, SUB_M * E_ROW_BYTES);
+                    const uint32_t e_tmem0 = tmem_base + E_COL0;
+                    const uint32_t acc0 = tmem_base, acc1 = tmem_base + TILE_N;
+                    const uint32_t my_tiles = pair < num_tiles ? (num_tiles - pair + num_pairs - 1) / num_pairs : 0u;
+                    uint32_t       left     = my_tiles * num_kb; // slabs this pair still has to multiply
+                    uint32_t       phase = 0, kb = 0, tphase = 0;
+                    bool           ok = true;
+                    while(ok && left != 0u)
                     {
-                        const uint32_t tphase = iter & 1u;
-                        for(uint32_t kb = 0; kb < num_kb && ok; ++kb)
+#pragma unroll
+                        for(uint32_t st = 0; st < STAGES; ++st)
                         {
-                            ok = ptx::mbar_wait_bounded(full_bar + 8 * stage, phase, cta_abort, status,
+                            if(left == 0u)
+                                break;
+                            ok = ptx::mbar_wait_bounded(full_bar + 8 * st, phase, cta_abort, status,
                                                         (ROLE_MMA << 24) | (1u << 20) | blockIdx.x, WAIT_TIMEOUT_NS);
                             if(!ok)
                                 break;
                             ptx::tc_fence_after_sync();
-                            const uint64_t b_desc = ptx::make_kmajor_sw128_desc(smem_b + stage * B_STAGE_BYTES);
-#pragma unroll
-                            for(uint32_t j = 0; j < 2; ++j)
+                            const uint32_t e_t = e_tmem0 + 8u * st;
+                            const uint64_t a_d = a_desc0 + st * A_STEP, b_d = b_desc0 + st * B_STEP;
+                            ptx::tmem_cp_128x256b_pair(e_t, e_desc0 + st * E_STEP);
+                            const uint32_t acc = kb != 0u ? 1u : 0u; // first slab of a tile overwrites
+                            if(kb == 0u)
                             {
-                                if(kb == 0)
-                                {
-                                    // accumulator j of the previous tile must have been drained by both CTAs
-                                    ok = ptx::mbar_wait_bounded(tempty_bar + 8 * j, tphase ^ 1u, cta_abort, status,
-                                                                (ROLE_MMA << 24) | blockIdx.x, WAIT_TIMEOUT_NS);
-                                    if(!ok)
-                                        break;
-                                    ptx::tc_fence_after_sync();
-                                }
-                                // metadata of sub-tile j: 128 rows x 16 bytes -> 4 columns, in both CTAs
-                                const uint32_t e_tmem = tmem_base + E_COL0 + 8u * stage + 4u * j;
-                                ptx::tmem_cp_128x128b_pair(
-                                    e_tmem, ptx::make_rows16_desc(smem_e + stage * E_STAGE_BYTES + j * (SUB_M * E_ROW_BYTES)));
-                                const uint64_t a_desc
-                                    = ptx::make_kmajor_sw64_desc(smem_a + stage * A_STAGE_BYTES + j * (SUB_M * A_ROW_BYTES));
-#pragma unroll
-                                for(uint32_t ks = 0; ks < SLAB_K / 64; ++ks)
-                                {
-                                    // 64 logical K per MMA: 32 bytes of compressed A (+2), 64 bytes of B (+4),
-                                    // 2 metadata columns
-                                    const uint32_t acc = (kb | ks) != 0u ? 1u : 0u;
-                                    ptx::mma_i8_sp_ss_pair(tmem_base + j * TILE_N, a_desc + 2 * ks, b_desc + 4 * ks,
-                                                           e_tmem + 2 * ks, idesc, acc);
-                                }
+                                // accumulator 0 of the previous tile must have been drained by both CTAs
+                                ok = ptx::mbar_wait_bounded(tempty_bar, tphase ^ 1u, cta_abort, status,
+                                                            (ROLE_MMA << 24) | blockIdx.x, WAIT_TIMEOUT_NS);
+                                if(!ok)
+                                    break;
+                                ptx::tc_fence_after_sync();
                             }
-                            if(!ok)
-                                break;
-                            ptx::tc_commit_pair(empty_bar + 8 * stage, 0x3);
-                            if(++stage == STAGES)
+                            // 64 logical K per MMA = 32 bytes of compressed A (+2), 64 bytes of B (+4), 2 metadata columns
+                            ptx::mma_i8_sp_ss_pair(acc0, a_d, b_d, e_t, idesc, acc);
+                            ptx::mma_i8_sp_ss_pair(acc0, a_d + 2, b_d + 4, e_t + 2, idesc, 1u);
+                            if(kb == 0u)
                             {
-                                stage = 0;
-                                phase ^= 1u;
+                                ok = ptx::mbar_wait_bounded(tempty_bar + 8, tphase ^ 1u, cta_abort, status,
+                                                            (ROLE_MMA << 24) | blockIdx.x, WAIT_TIMEOUT_NS);
+                                if(!ok)
+                                    break;
+                                ptx::tc_fence_after_sync();
+                            }
+                            ptx::mma_i8_sp_ss_pair(acc1, a_d + A_SUB, b_d, e_t + 4, idesc, acc);
+                            ptx::mma_i8_sp_ss_pair(acc1, a_d + A_SUB + 2, b_d + 4, e_t + 6, idesc, 1u);
+                            ptx::tc_commit_pair(empty_bar + 8 * st, 0x3); // the slot is free in both CTAs once these MMAs retire
+                            --left;
+                            if(++kb == num_kb)
+                            {
+                                kb = 0;
+                                tphase ^= 1u;
+                                ptx::tc_commit_pair(tfull_bar, 0x3); // accumulators complete
                             }
                         }
-                        if(ok)
-                            ptx::tc_commit_pair(tfull_bar, 0x3);
+                        phase ^= 1u;
                     }
                 }
                 __syncwarp();

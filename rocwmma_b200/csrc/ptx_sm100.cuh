@@ -474,6 +474,12 @@ namespace b200wmma
         {
             asm volatile("tcgen05.cp.cta_group::2.128x128b [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
         }
+        // 128 rows of 32 bytes -> 128 lanes x 8 columns.  The source is two 16-byte-wide column blocks
+        // (make_rows16_desc with the distance between the blocks as `lbo_bytes`).
+        __device__ __forceinline__ void tmem_cp_128x256b_pair(uint32_t taddr, uint64_t smem_desc)
+        {
+            asm volatile("tcgen05.cp.cta_group::2.128x256b [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+        }
         // K-major tile stored as rows of 64 bytes with the 64-byte swizzle (a TMA SWIZZLE_64B box):
         // 8-row groups are 512 bytes apart (SBO), layout type 4.  Base 512-byte aligned.
         __device__ __forceinline__ uint64_t make_kmajor_sw64_desc(uint32_t smem_addr)
@@ -487,12 +493,13 @@ namespace b200wmma
             return desc;
         }
         // Unswizzled tile of 16-byte rows stored back to back (row r at r * 16 bytes): 8-row core
-        // matrices of 128 bytes, 128 bytes apart (SBO); a single core matrix along K, so LBO is unused.
-        __device__ __forceinline__ uint64_t make_rows16_desc(uint32_t smem_addr)
+        // matrices of 128 bytes, 128 bytes apart (SBO).  A second 16-byte-wide column block, if the
+        // instruction reads one, lies `lbo_bytes` after the first (LBO).
+        __device__ __forceinline__ uint64_t make_rows16_desc(uint32_t smem_addr, uint32_t lbo_bytes = 128u)
         {
             uint64_t desc = 0;
             desc |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
-            desc |= static_cast<uint64_t>(128u >> 4) << 16; // LBO (unused)
+            desc |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16; // LBO
             desc |= static_cast<uint64_t>(128u >> 4) << 32; // SBO
             desc |= static_cast<uint64_t>(1u) << 46; // descriptor version; layout type 0 = no swizzle
             return desc;
