@@ -4,12 +4,12 @@
 
 namespace b200wmma
 {
-    // The kernel moves whole 128-wide K slabs with TMA: every row start and pitch a multiple of 16
+    // The kernel moves K in whole 128-wide boxes with TMA: every row start and pitch a multiple of 16
     // bytes, k a multiple of 128 (metadata rows are k/8 bytes: 16 bytes per slab).
     bool sp24_direct_ok(uint32_t k, const void* a_vals, const void* a_meta, const void* b, uint32_t lda_vals,
                         uint32_t ld_meta, uint32_t ldb)
     {
-        return k % tc05s::SLAB_K == 0 && aligned16(a_vals) && aligned16(a_meta) && aligned16(b) && lda_vals % 16 == 0
+        return k % tc05s::HALF_K == 0 && aligned16(a_vals) && aligned16(a_meta) && aligned16(b) && lda_vals % 16 == 0
                && ld_meta % 16 == 0 && ldb % 16 == 0;
     }
 
@@ -39,11 +39,11 @@ namespace b200wmma
         const int vec_ok = (row_align(d, ldd) && (!c || row_align(c, ldc))) ? 1 : 0;
 
         CUtensorMap tm_a, tm_e, tm_b;
-        if(int e = make_bytes_tmap(&tm_a, a_vals, m, k / 2, lda_vals, A_ROW_BYTES, CTA_M, CU_TENSOR_MAP_SWIZZLE_64B))
+        if(int e = make_bytes_tmap(&tm_a, a_vals, m, k / 2, lda_vals, A_ROW_BYTES, CTA_M, CU_TENSOR_MAP_SWIZZLE_128B))
             return e;
         if(int e = make_bytes_tmap(&tm_e, a_meta, m, k / 8, ld_meta, E_ROW_BYTES, CTA_M, CU_TENSOR_MAP_SWIZZLE_NONE))
             return e;
-        if(int e = make_bytes_tmap(&tm_b, b, n, k, ldb, SLAB_K, HALF_N, CU_TENSOR_MAP_SWIZZLE_128B))
+        if(int e = make_bytes_tmap(&tm_b, b, n, k, ldb, HALF_K, HALF_N, CU_TENSOR_MAP_SWIZZLE_128B))
             return e;
         CUtensorMap tm_c = tm_a, tm_d = tm_a; // placeholders, never dereferenced when vec_ok == 0
         if(vec_ok != 0)

@@ -5,22 +5,31 @@
 // test/gemm/gemm_common_test_params.hpp:51-147) applied to the densified A, bit-exact in int32.
 //
 // A never exists in dense form on the device.  The kernel streams the compressed values
-// (m x k/2 bytes) and the position metadata (m x k/8 bytes) as they are:
-//   * values: TMA boxes of 64 bytes x 256 rows with the 64-byte swizzle (128 logical K per slab);
-//   * metadata: TMA boxes of 16 bytes x 256 rows, unswizzled (row r at r * 16 bytes).  One
-//     tcgen05.cp per slab moves both 128-row sub-tiles (4 KiB) into 8 tensor-memory columns, 4 per
-//     sub-tile, where the two MMAs of each sub-tile read them (2 columns = 64 logical K each).  The byte format of the C interface - one
-//     nibble idx0 | idx1 << 2 per group of four K positions, low nibble = even group - is the
-//     hardware's own, so no repacking pass is needed;
-//   * B: TMA boxes of 128 bytes x 112 rows, 128-byte swizzle (each CTA of the pair loads half of N).
+// (m x k/2 bytes) and the position metadata (m x k/8 bytes) as they are, 256 logical K per slab:
+//   * values: one TMA box of 128 bytes x 256 rows, 128-byte swizzle;
+//   * metadata: two TMA boxes of 16 bytes x 256 rows (one per 128 K), unswizzled (row r at r * 16
+//     bytes).  A tcgen05.cp per box moves both 128-row sub-tiles (4 KiB) into 8 tensor-memory
+//     columns, 4 per sub-tile, where the MMAs read them (2 columns = 64 logical K each).  The byte
+//     format of the C interface - one nibble idx0 | idx1 << 2 per group of four K positions, low
+//     nibble = even group - is the hardware's own, so no repacking pass is needed;
+//   * B: two TMA boxes of 128 bytes x 112 rows, 128-byte swizzle (each CTA of the pair loads half of N).
 // One tcgen05.mma.sp consumes 32 bytes per row of compressed A and 64 bytes per row of B: twice the
-// logical K of a dense int8 MMA per instruction.
+// logical K of a dense int8 MMA per instruction, in the same 112 clocks (measured, N = 224, pair).
 //
 // Tile: 512 x 224 per SM pair.  Each CTA owns 256 rows (two 128-lane accumulators of 224 columns =
-// 448 tensor-memory columns); the metadata needs 8 columns per pipeline stage (5 stages = 40),
+// 448 tensor-memory columns); the metadata needs 16 columns per pipeline stage (3 stages = 48),
 // which is why N is 224 and not 256: 2 x 256 accumulator columns would leave no room for it.  The
-// tall tile keeps the L2 -> shared-memory traffic at ~78 bytes per clock per SM at full sparse
-// rate (a 256 x 256 pair tile would need ~104).
+// tall tile keeps the L2 -> shared-memory traffic at ~78 bytes per clock per SM at full sparse rate.
+//
+// Why 256 K per slab: the eight MMAs of a slab run for 896 clocks, and ONE thread issues them,
+// waits for the slab, copies its metadata and commits.  With 128 K per slab that thread needed
+// ~620 clocks of its own instruction latency per 448 clocks of tensor work and the tensor pipe
+// idled a quarter of the time; with 256 K the per-slab overhead is paid half as often.
+//
+// Shared memory: 3 stages x 68 KiB leave no room for the epilogue's staging tiles (32 KiB), so
+// those alias the A region of the last stage.  While a tile is drained that stage is not refilled:
+// the producer waits for a counter the epilogue warps bump once their TMA stores have read the
+// tiles (two stages = 136 KiB of the next tile are prefetched meanwhile).
 //
 // Roles and barrier protocol are those of gemm_tc05_pair512.cuh: warp 0 TMA producer (one lane,
 // both CTAs, loads counted on the leader's full[s]), warp 1 tensor-memory owner and MMA issuer (one
@@ -41,28 +50,33 @@ namespace b200wmma
         constexpr uint32_t PAIR_M        = 512;
         constexpr uint32_t TILE_N        = 224;
         constexpr uint32_t HALF_N        = 112;
-        constexpr uint32_t SLAB_K        = 128; // logical K per pipeline stage
-        constexpr uint32_t STAGES        = 5;
-        constexpr uint32_t A_ROW_BYTES   = SLAB_K / 2; // 64: compressed values
-        constexpr uint32_t E_ROW_BYTES   = SLAB_K / 8; // 16: metadata
-        constexpr uint32_t A_STAGE_BYTES = CTA_M * A_ROW_BYTES; // 16 KiB
-        constexpr uint32_t E_STAGE_BYTES = CTA_M * E_ROW_BYTES; // 4 KiB
-        constexpr uint32_t B_STAGE_BYTES = HALF_N * SLAB_K; // 14 KiB
-        constexpr uint32_t STAGE_BYTES   = A_STAGE_BYTES + E_STAGE_BYTES + B_STAGE_BYTES;
+        constexpr uint32_t SLAB_K        = 256; // logical K per pipeline stage
+        constexpr uint32_t HALF_K        = 128; // logical K per metadata / B box
+        constexpr uint32_t STAGES        = 3;
+        constexpr uint32_t A_ROW_BYTES   = SLAB_K / 2; // 128: compressed values
+        constexpr uint32_t E_ROW_BYTES   = HALF_K / 8; // 16: metadata of 128 K
+        constexpr uint32_t A_STAGE_BYTES = CTA_M * A_ROW_BYTES; // 32 KiB
+        constexpr uint32_t E_BOX_BYTES   = CTA_M * E_ROW_BYTES; // 4 KiB per 128 K
+        constexpr uint32_t E_STAGE_BYTES = 2 * E_BOX_BYTES; // 8 KiB
+        constexpr uint32_t B_BOX_BYTES   = HALF_N * HALF_K; // 14 KiB per 128 K
+        constexpr uint32_t B_STAGE_BYTES = 2 * B_BOX_BYTES; // 28 KiB
+        constexpr uint32_t STAGE_BYTES   = A_STAGE_BYTES + E_STAGE_BYTES + B_STAGE_BYTES; // 68 KiB
         constexpr uint32_t EPI_WARPS     = 8;
         constexpr uint32_t NUM_THREADS   = 64 + EPI_WARPS * 32;
         constexpr uint32_t TMEM_COLS     = 512;
-        constexpr uint32_t E_COL0        = 2 * TILE_N; // metadata columns: E_COL0 + 8 * stage + 4 * sub-tile
+        constexpr uint32_t E_COL0        = 2 * TILE_N; // metadata columns: E_COL0 + 16 * stage + 8 * K half + 4 * sub-tile
         constexpr uint32_t GROUP_M       = 8;
         constexpr uint32_t EPI_BUF_BYTES = tc05q::EPI_BUF_BYTES;
-        constexpr uint32_t EPI_BYTES     = EPI_WARPS * 2 * EPI_BUF_BYTES;
+        constexpr uint32_t EPI_BYTES     = EPI_WARPS * 2 * EPI_BUF_BYTES; // aliases the A region of the last stage
+        constexpr uint32_t EPI_STAGE     = STAGES - 1;
         constexpr uint32_t MISC_BYTES    = 512;
-        constexpr uint32_t SMEM_BYTES    = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + MISC_BYTES;
-        static_assert(E_COL0 + 8 * STAGES <= TMEM_COLS, "metadata does not fit beside the accumulators");
+        constexpr uint32_t SMEM_BYTES    = 1024 + STAGES * STAGE_BYTES + MISC_BYTES;
+        static_assert(E_COL0 + 16 * STAGES <= TMEM_COLS, "metadata does not fit beside the accumulators");
+        static_assert(EPI_BYTES <= A_STAGE_BYTES, "staging tiles must fit in one A stage");
         static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 
         __global__ void __launch_bounds__(NUM_THREADS, 1)
-            gemm_tc05_sp_kernel(const __grid_constant__ CUtensorMap tmap_a, // compressed values, 64 B x 256 rows, SW64
+            gemm_tc05_sp_kernel(const __grid_constant__ CUtensorMap tmap_a, // compressed values, 128 B x 256 rows, SW128
                                 const __grid_constant__ CUtensorMap tmap_e, // metadata, 16 B x 256 rows
                                 const __grid_constant__ CUtensorMap tmap_b, // B^T rows, 128 B x 112 rows, SW128
                                 const __grid_constant__ CUtensorMap tmap_c,
@@ -71,7 +85,7 @@ namespace b200wmma
                                 int32_t* __restrict__ d,
                                 uint32_t  m,
                                 uint32_t  n,
-                                uint32_t  k, // logical K, a multiple of SLAB_K
+                                uint32_t  k, // logical K, a multiple of HALF_K
                                 uint32_t  ldc,
                                 uint32_t  ldd,
                                 int32_t   alpha,
@@ -87,12 +101,13 @@ namespace b200wmma
             const uint32_t            base     = (raw_addr + 1023u) & ~1023u;
             uint8_t*                  smem     = smem_raw + (base - raw_addr);
 
-            // [A stages][B stages][E stages][epilogue staging tiles][barriers, tensor-memory slot, abort flag]
+            // [A stages][B stages][E stages][barriers, tensor-memory slot, abort flag, epilogue counter];
+            // the epilogue staging tiles alias A stage EPI_STAGE
             const uint32_t     smem_a     = base;
             const uint32_t     smem_b     = smem_a + STAGES * A_STAGE_BYTES;
             const uint32_t     smem_e     = smem_b + STAGES * B_STAGE_BYTES;
-            const uint32_t     epi_off    = STAGES * STAGE_BYTES;
-            const uint32_t     misc_off   = epi_off + EPI_BYTES;
+            const uint32_t     epi_off    = EPI_STAGE * A_STAGE_BYTES;
+            const uint32_t     misc_off   = STAGES * STAGE_BYTES;
             const uint32_t     bar_base   = base + misc_off;
             const uint32_t     full_bar   = bar_base; // STAGES x 8 (leader's copy in use)
             const uint32_t     empty_bar  = bar_base + 64;
@@ -101,6 +116,7 @@ namespace b200wmma
             const uint32_t     cbar_base  = bar_base + 160; // EPI_WARPS x 2 x 8
             uint32_t*          tmem_slot  = reinterpret_cast<uint32_t*>(smem + misc_off + 160 + EPI_WARPS * 16);
             volatile uint32_t* cta_abort  = tmem_slot + 1;
+            uint32_t*          epi_count  = tmem_slot + 2; // epilogue warps x tiles whose staging tiles are free again
 
             const uint32_t warp      = threadIdx.x >> 5;
             const uint32_t lane      = threadIdx.x & 31u;
@@ -108,7 +124,8 @@ namespace b200wmma
             const uint32_t pair      = blockIdx.x >> 1;
             const uint32_t num_pairs = gridDim.x >> 1;
             const uint32_t num_tiles = tiles_m * tiles_n;
-            const uint32_t num_kb    = k / SLAB_K;
+            const uint32_t num_kb    = (k + SLAB_K - 1) / SLAB_K; // the last slab may hold only 128 K
+            const bool     half_tail = (k % SLAB_K) != 0u;
 
             if(threadIdx.x == 0)
             {
@@ -128,6 +145,7 @@ namespace b200wmma
                 for(uint32_t i = 0; i < EPI_WARPS * 2; ++i)
                     ptx::mbar_init(cbar_base + 8 * i, 1);
                 *cta_abort = 0u;
+                *epi_count = 0u;
                 ptx::fence_barrier_init();
                 ptx::fence_proxy_async_smem();
             }
@@ -146,42 +164,68 @@ namespace b200wmma
                 // ------------------------------ TMA producer (both CTAs) ------------------------------
                 if(lane == 0)
                 {
-                    // one slab every 448 clocks at full rate: the loop advances addresses by constant adds
                     const uint32_t leader_full0 = ptx::mapa(full_bar, 0u);
-                    uint32_t       stage = 0, phase = 0;
-                    uint32_t       sa = smem_a, sb = smem_b, se = smem_e, eb = empty_bar, fb = full_bar, lf = leader_full0;
+                    uint32_t       stage = 0, phase = 0, iter = 0;
                     bool           ok = true;
-                    for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs)
+                    for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++iter)
                     {
                         uint32_t m_idx, n_idx;
                         tile_coords(tile, tiles_m, tiles_n, group_m, m_idx, n_idx);
                         const int32_t row_a = static_cast<int32_t>(m_idx * PAIR_M + rank * CTA_M);
                         const int32_t row_b = static_cast<int32_t>(n_idx * TILE_N + rank * HALF_N);
-                        // inner coordinates are byte offsets into the value / metadata / B rows: 64, 16 and
-                        // 128 bytes per slab, all multiples of 16
+                        // inner coordinates are byte offsets into the value / metadata / B rows: 128, 2 x 16 and
+                        // 2 x 128 bytes per slab, all multiples of 16
                         int32_t ka = 0, ke = 0, kbb = 0;
                         for(uint32_t kb = 0; kb < num_kb; ++kb)
                         {
-                            ok = ptx::mbar_wait_bounded(eb, phase ^ 1u, cta_abort, status, (ROLE_PRODUCER << 24) | blockIdx.x,
-                                                        WAIT_TIMEOUT_NS);
+                            ok = ptx::mbar_wait_bounded(empty_bar + 8 * stage, phase ^ 1u, cta_abort, status,
+                                                        (ROLE_PRODUCER << 24) | blockIdx.x, WAIT_TIMEOUT_NS);
                             if(!ok)
                                 break;
+                            if(stage == EPI_STAGE && iter != 0u)
+                            {
+                                // this stage's A region doubles as the epilogue's staging tiles: every epilogue
+                                // warp must have finished with them for all earlier tiles (bounded wait)
+                                const uint64_t t0 = ptx::globaltimer_ns();
+                                uint32_t       spins = 0;
+                                while(ptx::ld_acquire_shared_u32(epi_count) < EPI_WARPS * iter)
+                                {
+                                    if((++spins & 0xFFu) == 0u)
+                                    {
+                                        if(*cta_abort)
+                                        {
+                                            ok = false;
+                                            break;
+                                        }
+                                        if(ptx::globaltimer_ns() - t0 > WAIT_TIMEOUT_NS)
+                                        {
+                                            *cta_abort = 1u;
+                                            if(atomicCAS(status, 0u, ptx::STATUS_TIMEOUT_CODE) == 0u)
+                                                status[1] = (ROLE_PRODUCER << 24) | (2u << 20) | blockIdx.x;
+                                            ok = false;
+                                            break;
+                                        }
+                                    }
+                                }
+                                if(!ok)
+                                    break;
+                                ptx::fence_proxy_async_smem(); // generic writes of the staging tiles before the TMA overwrite
+                            }
+                            const uint32_t fb = full_bar + 8 * stage, lf = leader_full0 + 8 * stage;
                             if(rank == 0)
                                 ptx::mbar_arrive_expect_tx(fb, 2u * STAGE_BYTES);
+                            const uint32_t sb = smem_b + stage * B_STAGE_BYTES, se = smem_e + stage * E_STAGE_BYTES;
                             ptx::tma_load_2d_pair(sb, &tmap_b, kbb, row_b, lf);
-                            ptx::tma_load_2d_pair(sa, &tmap_a, ka, row_a, lf);
+                            ptx::tma_load_2d_pair(smem_a + stage * A_STAGE_BYTES, &tmap_a, ka, row_a, lf);
                             ptx::tma_load_2d_pair(se, &tmap_e, ke, row_a, lf);
-                            ka += static_cast<int32_t>(A_ROW_BYTES), ke += static_cast<int32_t>(E_ROW_BYTES),
+                            ptx::tma_load_2d_pair(sb + B_BOX_BYTES, &tmap_b, kbb + static_cast<int32_t>(HALF_K), row_b, lf);
+                            ptx::tma_load_2d_pair(se + E_BOX_BYTES, &tmap_e, ke + static_cast<int32_t>(E_ROW_BYTES), row_a, lf);
+                            ka += static_cast<int32_t>(A_ROW_BYTES), ke += static_cast<int32_t>(2 * E_ROW_BYTES),
                                 kbb += static_cast<int32_t>(SLAB_K);
                             if(++stage == STAGES)
                             {
                                 stage = 0;
                                 phase ^= 1u;
-                                sa = smem_a, sb = smem_b, se = smem_e, eb = empty_bar, fb = full_bar, lf = leader_full0;
-                            }
-                            else
-                            {
-                                sa += A_STAGE_BYTES, sb += B_STAGE_BYTES, se += E_STAGE_BYTES, eb += 8u, fb += 8u, lf += 8u;
                             }
                         }
                     }
@@ -193,18 +237,18 @@ namespace b200wmma
                 // ------------------------------- MMA issuer (leader only) -------------------------------
                 if(lane == 0 && rank == 0)
                 {
-                    // One thread feeds the tensor cores of both SMs, and a slab's four MMAs run for only 448
-                    // clocks: the instructions this thread executes per slab decide whether the tensor pipe
-                    // idles.  The ring is therefore walked by an unrolled loop over the stages, so that every
-                    // descriptor, metadata column and barrier address is a loop-invariant value (base plus a
-                    // compile-time offset) and a slab costs little more than its wait, copy, MMAs and commit.
+                    // One thread feeds the tensor cores of both SMs; what it executes per slab besides the MMAs
+                    // (wait, fence, two metadata copies, commit) has to hide behind 896 clocks of tensor work.
+                    // The ring is walked by an unrolled loop over the stages, so that every descriptor,
+                    // metadata column and barrier address is a loop-invariant value plus a compile-time offset.
                     // dense int8 descriptor with the sparsity flag (bit 2); metadata format id 0
                     constexpr uint32_t idesc  = make_idesc<KIND_I8, 2 * SUB_M, TILE_N>() | (1u << 2);
                     constexpr uint64_t A_STEP = A_STAGE_BYTES >> 4, B_STEP = B_STAGE_BYTES >> 4, E_STEP = E_STAGE_BYTES >> 4;
                     constexpr uint64_t A_SUB  = (SUB_M * A_ROW_BYTES) >> 4; // second 128-row sub-tile
-                    const uint64_t     a_desc0 = ptx::make_kmajor_sw64_desc(smem_a);
+                    constexpr uint64_t B_H1   = B_BOX_BYTES >> 4, E_H1 = E_BOX_BYTES >> 4; // second 128 K of the slab
+                    const uint64_t     a_desc0 = ptx::make_kmajor_sw128_desc(smem_a);
                     const uint64_t     b_desc0 = ptx::make_kmajor_sw128_desc(smem_b);
-                    // metadata source: the two 128-row blocks of a stage (2 KiB apart) are the two 16-byte
+                    // metadata source of one 128-K box: its two 128-row blocks (2 KiB apart) are the two 16-byte
                     // column blocks of a 128 x 32-byte tile; one copy fills 8 columns (4 per sub-tile)
                     const uint64_t e_desc0 = ptx::make_rows16_desc(smem_e, SUB_M * E_ROW_BYTES);
                     const uint32_t e_tmem0 = tmem_base + E_COL0;
@@ -225,9 +269,13 @@ namespace b200wmma
                             if(!ok)
                                 break;
                             ptx::tc_fence_after_sync();
-                            const uint32_t e_t = e_tmem0 + 8u * st;
+                            const uint32_t e_t = e_tmem0 + 16u * st;
                             const uint64_t a_d = a_desc0 + st * A_STEP, b_d = b_desc0 + st * B_STEP;
+                            // a slab that ends the K range with only 128 K (k % 256 == 128) runs its first half only
+                            const bool full_slab = !(half_tail && kb + 1u == num_kb);
                             ptx::tmem_cp_128x256b_pair(e_t, e_desc0 + st * E_STEP);
+                            if(full_slab)
+                                ptx::tmem_cp_128x256b_pair(e_t + 8u, e_desc0 + st * E_STEP + E_H1);
                             const uint32_t acc = kb != 0u ? 1u : 0u; // first slab of a tile overwrites
                             if(kb == 0u)
                             {
@@ -241,6 +289,11 @@ namespace b200wmma
                             // 64 logical K per MMA = 32 bytes of compressed A (+2), 64 bytes of B (+4), 2 metadata columns
                             ptx::mma_i8_sp_ss_pair(acc0, a_d, b_d, e_t, idesc, acc);
                             ptx::mma_i8_sp_ss_pair(acc0, a_d + 2, b_d + 4, e_t + 2, idesc, 1u);
+                            if(full_slab)
+                            {
+                                ptx::mma_i8_sp_ss_pair(acc0, a_d + 4, b_d + B_H1, e_t + 8, idesc, 1u);
+                                ptx::mma_i8_sp_ss_pair(acc0, a_d + 6, b_d + B_H1 + 4, e_t + 10, idesc, 1u);
+                            }
                             if(kb == 0u)
                             {
                                 ok = ptx::mbar_wait_bounded(tempty_bar + 8, tphase ^ 1u, cta_abort, status,
@@ -251,6 +304,11 @@ namespace b200wmma
                             }
                             ptx::mma_i8_sp_ss_pair(acc1, a_d + A_SUB, b_d, e_t + 4, idesc, acc);
                             ptx::mma_i8_sp_ss_pair(acc1, a_d + A_SUB + 2, b_d + 4, e_t + 6, idesc, 1u);
+                            if(full_slab)
+                            {
+                                ptx::mma_i8_sp_ss_pair(acc1, a_d + A_SUB + 4, b_d + B_H1, e_t + 12, idesc, 1u);
+                                ptx::mma_i8_sp_ss_pair(acc1, a_d + A_SUB + 6, b_d + B_H1 + 4, e_t + 14, idesc, 1u);
+                            }
                             ptx::tc_commit_pair(empty_bar + 8 * st, 0x3); // the slot is free in both CTAs once these MMAs retire
                             --left;
                             if(++kb == num_kb)
@@ -286,13 +344,15 @@ namespace b200wmma
                     const uint32_t row0     = row_base + quad * 32u;
                     const uint32_t col_base = n_idx * TILE_N;
                     const bool     staged   = vec_ok != 0 && row0 < m && col_base < n;
-                    if(staged && read_c && lane == 0)
-                        Drain::prefetch_c(&tmap_c, buf0, cbar0, col_base, row0, n);
                     ok = ptx::mbar_wait_bounded_warp(tfull_bar, iter & 1u, cta_abort, status,
                                                      (ROLE_EPILOGUE << 24) | blockIdx.x, WAIT_TIMEOUT_NS, lane);
                     if(!ok)
                         break;
                     ptx::tc_fence_after_sync();
+                    // the staging tiles share memory with an operand stage: only now, with every MMA of the
+                    // tile retired, may anything (the first C tiles included) be written there
+                    if(staged && read_c && lane == 0)
+                        Drain::prefetch_c(&tmap_c, buf0, cbar0, col_base, row0, n);
                     const uint32_t tmem_acc = tmem_base + j * TILE_N;
                     if(staged)
                         ok = Drain::run(tmem_acc, quad, lane, smem, buf_off, buf0, cbar0, &tmap_c, &tmap_d, col_base, row0, n,
@@ -304,10 +364,15 @@ namespace b200wmma
                     ptx::tc_fence_before_sync();
                     __syncwarp();
                     if(lane == 0)
+                    {
                         ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar + 8 * j, 0u));
+                        // hand the staging tiles back to the producer once this warp's stores have read them
+                        ptx::bulk_wait_group_read<0>();
+                        ptx::red_release_shared_add_u32(epi_count, 1u);
+                    }
                 }
                 if(lane == 0)
-                    ptx::bulk_wait_group<0>(); // the staging tiles must outlive the stores that read them
+                    ptx::bulk_wait_group<0>(); // the stores must have completed before the CTA exits
                 __syncwarp();
             }
 

@@ -163,6 +163,18 @@ namespace b200wmma
             return ok;
         }
 
+        // ---- counters in shared memory (release / acquire at CTA scope) ---------------------------
+        __device__ __forceinline__ uint32_t ld_acquire_shared_u32(const uint32_t* p)
+        {
+            uint32_t v;
+            asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+            return v;
+        }
+        __device__ __forceinline__ void red_release_shared_add_u32(uint32_t* p, uint32_t v)
+        {
+            asm volatile("red.release.cta.shared::cta.add.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+        }
+
         // ---- TMA ------------------------------------------------------------------------
         __device__ __forceinline__ void prefetch_tensormap(const void* tmap)
         {
