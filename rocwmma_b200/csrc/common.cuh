@@ -81,5 +81,7 @@ namespace b200wmma
     int  launch_gemm_tc05_i8_sp24(uint32_t m, uint32_t n, uint32_t k, const int8_t* a_vals, const uint8_t* a_meta,
                                   const int8_t* b, const int32_t* c, int32_t* d, uint32_t lda_vals, uint32_t ld_meta,
                                   uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha, int32_t beta,
-                                  cudaStream_t stream);
+                                  void* scratch, size_t scratch_bytes, cudaStream_t stream);
+    // bytes of scratch with which the kernel fetches the metadata in wide rows (a re-tiled copy)
+    size_t sp24_packed_meta_bytes(uint32_t m, uint32_t k);
 } // namespace b200wmma

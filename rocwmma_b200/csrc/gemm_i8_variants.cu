@@ -116,7 +116,9 @@ using namespace b200wmma;
 extern "C" size_t b200wmma_gemm_i8_sp24_workspace_bytes(uint32_t m, uint32_t n, uint32_t k)
 {
     (void)n;
-    return i8var::round256(static_cast<size_t>(m) * k);
+    // enough for either use: the densified A (m x k) or the re-tiled metadata of the sparse tensor-core path
+    const size_t dense = i8var::round256(static_cast<size_t>(m) * k), meta = i8var::round256(sp24_packed_meta_bytes(m, k));
+    return dense > meta ? dense : meta;
 }
 
 extern "C" size_t b200wmma_gemm_i4_workspace_bytes(uint32_t m, uint32_t n, uint32_t k)
@@ -140,7 +142,7 @@ extern "C" int b200wmma_gemm_i8_sp24(uint32_t m, uint32_t n, uint32_t k, const i
     // Sparse tensor-core path: compressed A goes to the tensor cores as it is, no scratch involved.
     if(!i8var::force_expansion() && sp24_direct_ok(k, a_vals, a_meta, b, lda_vals, ld_meta, ldb))
         return launch_gemm_tc05_i8_sp24(m, n, k, a_vals, a_meta, b, c, d, lda_vals, ld_meta, ldb, ldc, ldd, alpha, beta,
-                                        as_stream(stream));
+                                        workspace, workspace_bytes, as_stream(stream));
     // Otherwise (k not a multiple of 128, or rows that TMA cannot address): densify A into the
     // workspace and run the dense int8 kernel.
     B200_REQUIRE(workspace, B200WMMA_ERR_INVALID_ARG,

@@ -13,10 +13,15 @@ namespace b200wmma
                && ld_meta % 16 == 0 && ldb % 16 == 0;
     }
 
+    size_t sp24_packed_meta_bytes(uint32_t m, uint32_t k)
+    {
+        return static_cast<size_t>(ceil_div(m, tc05s::CTA_M)) * ceil_div(k, tc05s::SLAB_K) * tc05s::E_STAGE_BYTES;
+    }
+
     int launch_gemm_tc05_i8_sp24(uint32_t m, uint32_t n, uint32_t k, const int8_t* a_vals, const uint8_t* a_meta,
                                  const int8_t* b, const int32_t* c, int32_t* d, uint32_t lda_vals, uint32_t ld_meta,
                                  uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha, int32_t beta,
-                                 cudaStream_t stream)
+                                 void* scratch, size_t scratch_bytes, cudaStream_t stream)
     {
         using namespace tc05s;
         B200_REQUIRE(m && n && k, B200WMMA_ERR_INVALID_ARG, "gemm_i8_sp24: m, n, k must be non-zero");
@@ -38,10 +43,26 @@ namespace b200wmma
         };
         const int vec_ok = (row_align(d, ldd) && (!c || row_align(c, ldc))) ? 1 : 0;
 
+        // With scratch for a re-tiled copy of the metadata (1/8 byte per element of A) the kernel fetches it in
+        // 128-byte rows; without, in the 16-byte rows of the caller's array (8 x the requests).
+        const uint32_t num_kb   = ceil_div(k, SLAB_K);
+        const bool     e_packed = scratch != nullptr && aligned16(scratch) && scratch_bytes >= sp24_packed_meta_bytes(m, k);
+        if(e_packed)
+        {
+            repack_meta_kernel<<<dim3(num_kb, ceil_div(m, CTA_M)), 256, 0, stream>>>(
+                a_meta, static_cast<uint8_t*>(scratch), m, k, ld_meta, num_kb);
+            B200_CHECK_CUDA(cudaGetLastError());
+        }
         CUtensorMap tm_a, tm_e, tm_b;
         if(int e = make_bytes_tmap(&tm_a, a_vals, m, k / 2, lda_vals, A_ROW_BYTES, CTA_M, CU_TENSOR_MAP_SWIZZLE_128B))
             return e;
-        if(int e = make_bytes_tmap(&tm_e, a_meta, m, k / 8, ld_meta, E_ROW_BYTES, CTA_M, CU_TENSOR_MAP_SWIZZLE_NONE))
+        if(e_packed)
+        {
+            if(int e = make_bytes_tmap(&tm_e, scratch, ceil_div(m, CTA_M) * num_kb * E_PACKED_ROWS, 128, 128, 128, E_PACKED_ROWS,
+                                       CU_TENSOR_MAP_SWIZZLE_NONE))
+                return e;
+        }
+        else if(int e = make_bytes_tmap(&tm_e, a_meta, m, k / 8, ld_meta, E_ROW_BYTES, CTA_M, CU_TENSOR_MAP_SWIZZLE_NONE))
             return e;
         if(int e = make_bytes_tmap(&tm_b, b, n, k, ldb, HALF_K, HALF_N, CU_TENSOR_MAP_SWIZZLE_128B))
             return e;
@@ -59,8 +80,9 @@ namespace b200wmma
         int dev = 0, sms = 0;
         B200_CHECK_CUDA(cudaGetDevice(&dev));
         B200_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-        static int max_clusters_dev[MAX_DEVICES];
-        int&       max_clusters = max_clusters_dev[current_device_slot()];
+        auto kern = e_packed ? gemm_tc05_sp_kernel<true> : gemm_tc05_sp_kernel<false>;
+        static int max_clusters_dev[2][MAX_DEVICES];
+        int&       max_clusters = max_clusters_dev[e_packed ? 1 : 0][current_device_slot()];
         const uint32_t tiles_m = ceil_div(m, PAIR_M), tiles_n = ceil_div(n, TILE_N);
         cudaLaunchConfig_t  cfg = {};
         cudaLaunchAttribute attr[1];
@@ -76,16 +98,16 @@ namespace b200wmma
         if(max_clusters == 0)
         {
             B200_CHECK_CUDA(
-                cudaFuncSetAttribute(gemm_tc05_sp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+                cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
             cfg.gridDim = dim3(static_cast<unsigned>(sms) & ~1u);
             int nc      = 0;
-            B200_CHECK_CUDA(cudaOccupancyMaxActiveClusters(&nc, gemm_tc05_sp_kernel, &cfg));
+            B200_CHECK_CUDA(cudaOccupancyMaxActiveClusters(&nc, kern, &cfg));
             B200_REQUIRE(nc > 0, B200WMMA_ERR_CUDA, "no two-CTA cluster of the sparse GEMM kernel fits on this device");
             max_clusters = nc;
         }
         const uint32_t pairs = min(tiles_m * tiles_n, static_cast<uint32_t>(max_clusters));
         cfg.gridDim          = dim3(2 * pairs);
-        B200_CHECK_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc05_sp_kernel, tm_a, tm_e, tm_b, tm_c, tm_d, c, d, m, n, k, ldc, ldd,
+        B200_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, tm_a, tm_e, tm_b, tm_c, tm_d, c, d, m, n, k, ldc, ldd,
                                            alpha, beta, tiles_m, tiles_n, vec_ok, static_cast<uint32_t>(GROUP_M), status));
         return B200WMMA_OK;
     }

@@ -69,15 +69,19 @@ namespace b200wmma
         constexpr uint32_t EPI_BUF_BYTES = tc05q::EPI_BUF_BYTES;
         constexpr uint32_t EPI_BYTES     = EPI_WARPS * 2 * EPI_BUF_BYTES; // aliases the A region of the last stage
         constexpr uint32_t EPI_STAGE     = STAGES - 1;
+        constexpr uint32_t E_PACKED_ROWS = E_STAGE_BYTES / 128; // 128-byte rows of one re-tiled metadata block
         constexpr uint32_t MISC_BYTES    = 512;
         constexpr uint32_t SMEM_BYTES    = 1024 + STAGES * STAGE_BYTES + MISC_BYTES;
         static_assert(E_COL0 + 16 * STAGES <= TMEM_COLS, "metadata does not fit beside the accumulators");
         static_assert(EPI_BYTES <= A_STAGE_BYTES, "staging tiles must fit in one A stage");
         static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 
+        // E_PACKED: the metadata comes from a re-tiled copy (repack_meta_kernel) instead of the caller's
+        // row-major array: one box of 64 x 128 bytes per slab instead of two boxes of 256 x 16 bytes.
+        template <bool E_PACKED>
         __global__ void __launch_bounds__(NUM_THREADS, 1)
             gemm_tc05_sp_kernel(const __grid_constant__ CUtensorMap tmap_a, // compressed values, 128 B x 256 rows, SW128
-                                const __grid_constant__ CUtensorMap tmap_e, // metadata, 16 B x 256 rows
+                                const __grid_constant__ CUtensorMap tmap_e, // metadata: 16 B x 256 rows, or 128 B x 64 rows of the re-tiled copy
                                 const __grid_constant__ CUtensorMap tmap_b, // B^T rows, 128 B x 112 rows, SW128
                                 const __grid_constant__ CUtensorMap tmap_c,
                                 const __grid_constant__ CUtensorMap tmap_d,
@@ -176,6 +180,7 @@ namespace b200wmma
                         // inner coordinates are byte offsets into the value / metadata / B rows: 128, 2 x 16 and
                         // 2 x 128 bytes per slab, all multiples of 16
                         int32_t ka = 0, ke = 0, kbb = 0;
+                        const uint32_t e_blk0 = (m_idx * 2u + rank) * num_kb; // first re-tiled metadata block of this CTA's rows
                         for(uint32_t kb = 0; kb < num_kb; ++kb)
                         {
                             ok = ptx::mbar_wait_bounded(empty_bar + 8 * stage, phase ^ 1u, cta_abort, status,
@@ -217,9 +222,13 @@ namespace b200wmma
                             const uint32_t sb = smem_b + stage * B_STAGE_BYTES, se = smem_e + stage * E_STAGE_BYTES;
                             ptx::tma_load_2d_pair(sb, &tmap_b, kbb, row_b, lf);
                             ptx::tma_load_2d_pair(smem_a + stage * A_STAGE_BYTES, &tmap_a, ka, row_a, lf);
-                            ptx::tma_load_2d_pair(se, &tmap_e, ke, row_a, lf);
+                            if constexpr(E_PACKED)
+                                ptx::tma_load_2d_pair(se, &tmap_e, 0, static_cast<int32_t>((e_blk0 + kb) * E_PACKED_ROWS), lf);
+                            else
+                                ptx::tma_load_2d_pair(se, &tmap_e, ke, row_a, lf);
                             ptx::tma_load_2d_pair(sb + B_BOX_BYTES, &tmap_b, kbb + static_cast<int32_t>(HALF_K), row_b, lf);
-                            ptx::tma_load_2d_pair(se + E_BOX_BYTES, &tmap_e, ke + static_cast<int32_t>(E_ROW_BYTES), row_a, lf);
+                            if constexpr(!E_PACKED)
+                                ptx::tma_load_2d_pair(se + E_BOX_BYTES, &tmap_e, ke + static_cast<int32_t>(E_ROW_BYTES), row_a, lf);
                             ka += static_cast<int32_t>(A_ROW_BYTES), ke += static_cast<int32_t>(2 * E_ROW_BYTES),
                                 kbb += static_cast<int32_t>(SLAB_K);
                             if(++stage == STAGES)
@@ -395,6 +404,36 @@ namespace b200wmma
                 ptx::tc_fence_after_sync();
                 ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
             }
+        }
+
+        // Re-tiles the metadata for gemm_tc05_sp_kernel<true>: for every block of 256 rows x 256 K the 8 KiB
+        // image the kernel wants in shared memory - [K half][128-row sub-tile][row][16 bytes] - stored
+        // contiguously, blocks ordered (row block, slab).  The caller's array is read in full 32-byte
+        // sectors (both K halves of a row at once); rows >= m and bytes >= k/8 become zero (their products
+        // are never stored / never issued).  One thread per row of a block.
+        __global__ void __launch_bounds__(256)
+            repack_meta_kernel(const uint8_t* __restrict__ meta, uint8_t* __restrict__ packed, uint32_t m, uint32_t k,
+                               size_t ld_meta, uint32_t num_kb)
+        {
+            const uint32_t r      = threadIdx.x; // row inside the 256-row block
+            const uint32_t kb     = blockIdx.x;
+            const uint32_t rb     = blockIdx.y;
+            const uint32_t row    = rb * CTA_M + r;
+            const uint32_t col    = kb * (SLAB_K / 8); // byte offset in the metadata row
+            const uint32_t rowlen = k / 8;
+            uint4          h0 = make_uint4(0, 0, 0, 0), h1 = make_uint4(0, 0, 0, 0);
+            if(row < m)
+            {
+                const uint8_t* src = meta + static_cast<size_t>(row) * ld_meta + col;
+                if(col < rowlen)
+                    h0 = __ldcs(reinterpret_cast<const uint4*>(src));
+                if(col + 16u < rowlen)
+                    h1 = __ldcs(reinterpret_cast<const uint4*>(src + 16));
+            }
+            uint8_t* blk = packed + (static_cast<size_t>(rb) * num_kb + kb) * E_STAGE_BYTES;
+            const uint32_t sub = r >> 7, rr = r & 127u;
+            *reinterpret_cast<uint4*>(blk + sub * (SUB_M * E_ROW_BYTES) + rr * E_ROW_BYTES)               = h0;
+            *reinterpret_cast<uint4*>(blk + E_BOX_BYTES + sub * (SUB_M * E_ROW_BYTES) + rr * E_ROW_BYTES) = h1;
         }
     } // namespace tc05s
 } // namespace b200wmma

@@ -171,8 +171,10 @@ def test_gemm_i8_bit_exact(m, n, k, alpha, beta):
     assert np.array_equal(d.cpu().numpy(), ref)
 
 
-# k % 128 == 0 with 16-byte aligned rows runs on the sparse tensor cores (512 x 224 pair tiles: the shapes
-# cross tile edges in M and N and include ragged ones); the other shapes take the densify-then-dense path.
+# k % 128 == 0 with 16-byte aligned rows runs on the sparse tensor cores (512 x 224 pair tiles, 256 K per slab:
+# the shapes cross tile edges in M and N, include ragged ones and K tails of half a slab); with a workspace
+# the metadata is re-tiled first, without (next test) it is read as it is.  The other shapes take the
+# densify-then-dense path.
 @pytest.mark.parametrize("m,n,k,alpha,beta", [(128, 256, 128, 1, 0), (200, 136, 512, 1, 0), (256, 256, 4096, 1, 0),
                                               (1100, 500, 384, 3, -2), (513, 225, 256, 1, 1), (64, 1000, 128, -1, 1),
                                               (300, 200, 96, 1, 0), (130, 72, 160, 2, 1)])
@@ -226,7 +228,8 @@ def test_gemm_i8_sparse24_full_size_row_sample():
     del dense
     bs = G.fill_torch(torch.empty((n, k), dtype=torch.int8, device="cuda"), G.SEED_B, "int8")
     d = nan_filled((m, n), torch.int32)
-    api.gemm_i8_sp24(m, n, k, vals, meta, bs, None, d, k // 2, k // 8, k, n, n, 1, 0, None)
+    ws = torch.empty(api.gemm_i8_sp24_workspace_bytes(m, n, k), dtype=torch.uint8, device="cuda")
+    api.gemm_i8_sp24(m, n, k, vals, meta, bs, None, d, k // 2, k // 8, k, n, n, 1, 0, ws)
     assert_status_ok()
     rows = _rows_sample(m, 32, 97)
     idx = torch.from_numpy(rows).cuda()
