@@ -39,6 +39,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 NCU_TRAFFIC_BYTES = {
     "gemm_f16": 1.141e9,   # profiles/gemm_tc05_f16_8192.md: 1.020 GB read + 120.8 MB written (512x256 pair kernel)
     "gemm_i8": 1.416e9,    # profiles/gemm_tc05_i8_8192x8192x16384.md (256x256 pair kernel capture)
+    "gemm_i8_sp24": 8.595e8,  # profiles/gemm_tc05_sp24_8192x8192x16384.md (GEMM kernel; the re-tiling pre-pass adds ~33 MB)
     "dlrm_fwd": 119.5e6,   # profiles/dlrm_dot_B16384.md
     "dlrm_bwd": 195.8e6,   # profiles/dlrm_dot_B16384.md
     "sgemv": 4.299e9,      # profiles/gemv_32768.md
@@ -321,11 +322,13 @@ class GemmI8(GemmF16):
 
 class GemmI8Sp24(GemmI8):
     name, variant = "gemm_i8_sp24", "sp24"
+    launches_per_step = 2   # metadata re-tiling + sparse tensor-core GEMM
     metric = "2:4-sparse int8 GEMM dense-equivalent TOP/s at 8192x8192x16384"
 
 
 class GemmI4(GemmI8):
     name, variant = "gemm_i4", "i4"
+    launches_per_step = 3   # unpack A, unpack B, dense int8 GEMM
     metric = "int4-unpacked GEMM TOP/s at 8192x8192x16384"
 
 
@@ -671,7 +674,10 @@ def run_gpu_arm(args, wl):
         peaks = measured_peaks()
         if wl.bound == "tensor":
             peak = peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])
-            if wl.dtype == "i8":
+            if wl.dtype == "i8" and getattr(wl, "variant", "") == "sp24":
+                peak *= 4.0  # sparse int8: twice the dense int8 rate (measured: 112 clocks per 256x224x64 pair MMA)
+                peak_note = "4 x cuBLAS bf16 8192^3 burst, standing in for the 2:4-sparse int8 rate"
+            elif wl.dtype == "i8":
                 peak *= 2.0  # the dense int8 tensor rate is twice the 16-bit rate; no int8 figure is measured
                 peak_note = "2 x cuBLAS bf16 8192^3 burst, standing in for the dense int8 rate"
             elif wl.dtype == "f64":
@@ -693,7 +699,8 @@ def run_gpu_arm(args, wl):
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": wl.scaling,
             "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seeded counter-based generator)",
-            "config": wl.config(world), "roofline": roof, "clocks": sampler.summary(), "gpu_launches": args.steps,
+            "config": wl.config(world), "roofline": roof, "clocks": sampler.summary(),
+            "gpu_launches": args.steps * getattr(wl, "launches_per_step", 1),
             "a_broadcast_ms": wl.a_broadcast_ms,
         }
         if e2e:

@@ -106,6 +106,10 @@ int b200wmma_gemm_f64(uint32_t m, uint32_t n, uint32_t k,
  * i4: A (row major, m x k) and B (column major, k x n) hold int4 values in [-8,7], two per
  *   byte along K, low nibble = even k.  lda / ldb are in BYTES per row / column.
  * `workspace` is caller-owned device scratch of at least b200wmma_gemm_*_workspace_bytes().
+ *   sp24 with k a multiple of 128 and 16-byte aligned rows (a_vals, a_meta, b and their pitches) runs
+ *   on the sparse tensor cores straight from the compressed operands; the workspace is then optional
+ *   (NULL / 0 allowed) and only buys a faster metadata fetch.  Every other sp24 shape, and i4 always,
+ *   needs it.
  * ------------------------------------------------------------------------------------------ */
 size_t b200wmma_gemm_i8_sp24_workspace_bytes(uint32_t m, uint32_t n, uint32_t k);
 int b200wmma_gemm_i8_sp24(uint32_t m, uint32_t n, uint32_t k,

@@ -452,17 +452,6 @@ namespace b200wmma
         // One instruction covers 64 logical K: 32 bytes per row of compressed A, 64 bytes per row of
         // B, and 128 lanes x 2 columns of metadata at `e_tmem` (one bit per logical element: a byte
         // holds the two 4-bit position codes of 8 consecutive K positions).
-        __device__ __forceinline__ void mma_i8_sp_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                                     uint32_t e_tmem, uint32_t idesc, uint32_t accumulate)
-        {
-            asm volatile("{\n"
-                         ".reg .pred p;\n"
-                         "setp.ne.b32 p, %5, 0;\n"
-                         "tcgen05.mma.sp.cta_group::1.kind::i8 [%0], %1, %2, [%3], %4, p;\n"
-                         "}" ::"r"(d_tmem),
-                         "l"(a_desc), "l"(b_desc), "r"(e_tmem), "r"(idesc), "r"(accumulate)
-                         : "memory");
-        }
         __device__ __forceinline__ void mma_i8_sp_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                                           uint32_t e_tmem, uint32_t idesc, uint32_t accumulate)
         {
@@ -474,35 +463,13 @@ namespace b200wmma
                          "l"(a_desc), "l"(b_desc), "r"(e_tmem), "r"(idesc), "r"(accumulate)
                          : "memory");
         }
-        // Shared memory -> tensor memory: 128 rows of 16 bytes become 128 lanes x 4 columns.  Issued by
-        // the MMA thread; it executes in order with that thread's MMAs and is covered by its commits.
-        __device__ __forceinline__ void tmem_cp_128x128b(uint32_t taddr, uint64_t smem_desc)
-        {
-            asm volatile("tcgen05.cp.cta_group::1.128x128b [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
-        }
-        // Pair form: each CTA of the pair copies from its own shared memory (same offset) into its own
-        // tensor memory (same address).
-        __device__ __forceinline__ void tmem_cp_128x128b_pair(uint32_t taddr, uint64_t smem_desc)
-        {
-            asm volatile("tcgen05.cp.cta_group::2.128x128b [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
-        }
-        // 128 rows of 32 bytes -> 128 lanes x 8 columns.  The source is two 16-byte-wide column blocks
-        // (make_rows16_desc with the distance between the blocks as `lbo_bytes`).
+        // Shared memory -> tensor memory: 128 rows of 32 bytes become 128 lanes x 8 columns in each CTA of the
+        // pair (each copies from its own shared memory).  The source is two 16-byte-wide column blocks
+        // (make_rows16_desc with the distance between the blocks as `lbo_bytes`).  Issued by the MMA thread;
+        // it executes in order with that thread's MMAs and is covered by its commits.
         __device__ __forceinline__ void tmem_cp_128x256b_pair(uint32_t taddr, uint64_t smem_desc)
         {
             asm volatile("tcgen05.cp.cta_group::2.128x256b [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
-        }
-        // K-major tile stored as rows of 64 bytes with the 64-byte swizzle (a TMA SWIZZLE_64B box):
-        // 8-row groups are 512 bytes apart (SBO), layout type 4.  Base 512-byte aligned.
-        __device__ __forceinline__ uint64_t make_kmajor_sw64_desc(uint32_t smem_addr)
-        {
-            uint64_t desc = 0;
-            desc |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
-            desc |= static_cast<uint64_t>(1u) << 16; // LBO (ignored for swizzled K-major)
-            desc |= static_cast<uint64_t>(512u >> 4) << 32; // SBO
-            desc |= static_cast<uint64_t>(1u) << 46; // descriptor version
-            desc |= static_cast<uint64_t>(4u) << 61; // SWIZZLE_64B
-            return desc;
         }
         // Unswizzled tile of 16-byte rows stored back to back (row r at r * 16 bytes): 8-row core
         // matrices of 128 bytes, 128 bytes apart (SBO).  A second 16-byte-wide column block, if the
