@@ -120,6 +120,20 @@ int b200wmma_gemm_i8_sp24(uint32_t m, uint32_t n, uint32_t k,
                           int32_t alpha, int32_t beta,
                           void* workspace, size_t workspace_bytes, void* stream);
 
+/* The sparse tensor-core kernel fetches A's metadata fastest from a re-tiled copy (8 KiB blocks of 256 rows x
+ * 256 K).  b200wmma_gemm_i8_sp24 makes that copy in its workspace on every call; when A is reused (weights),
+ * make it once with b200wmma_sp24_repack_meta into a buffer of b200wmma_sp24_packed_meta_bytes(m, k) bytes and
+ * call b200wmma_gemm_i8_sp24_packed, which takes that buffer instead of a_meta and needs no workspace.
+ * k must be a multiple of 128; a_vals, b rows and `packed` 16-byte aligned. */
+size_t b200wmma_sp24_packed_meta_bytes(uint32_t m, uint32_t k);
+int b200wmma_sp24_repack_meta(uint32_t m, uint32_t k, const uint8_t* a_meta, uint32_t ld_meta,
+                              void* packed, size_t packed_bytes, void* stream);
+int b200wmma_gemm_i8_sp24_packed(uint32_t m, uint32_t n, uint32_t k,
+                                 const int8_t* a_vals, const void* a_meta_packed,
+                                 const int8_t* b, const int32_t* c, int32_t* d,
+                                 uint32_t lda_vals, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                                 int32_t alpha, int32_t beta, void* stream);
+
 /* No counterpart in the reference.  Same computation and arguments as b200wmma_gemm_i8_sp24 minus the
  * workspace: for callers that cannot provide scratch memory - code that launches through the plain
  * 13-argument GEMM kernel signature (which has no slot for a workspace), or that runs in a process whose

@@ -28,6 +28,9 @@ SIGNATURES = {
                                         i32, i32, vp, sz, vp]),
     "b200wmma_gemm_i8_sp24_static": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32,
                                                i32, i32, vp]),
+    "b200wmma_sp24_packed_meta_bytes": (sz, [u32, u32]),
+    "b200wmma_sp24_repack_meta": (C.c_int, [u32, u32, vp, u32, vp, sz, vp]),
+    "b200wmma_gemm_i8_sp24_packed": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, vp, u32, u32, u32, u32, i32, i32, vp]),
     "b200wmma_gemm_i4_workspace_bytes": (sz, [u32, u32, u32]),
     "b200wmma_gemm_i4": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32, i32, i32,
                                    vp, sz, vp]),

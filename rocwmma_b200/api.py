@@ -83,6 +83,23 @@ def gemm_i8_sp24(m, n, k, a_vals, a_meta, b, c, d, lda_vals, ld_meta, ldb, ldc, 
                                       _ptr(workspace), 0 if workspace is None else workspace.numel(), _stream()))
 
 
+def sp24_packed_meta_bytes(m, k):
+    return lib().b200wmma_sp24_packed_meta_bytes(m, k)
+
+
+def sp24_repack_meta(m, k, a_meta, ld_meta, packed):
+    """Re-tile the 2:4 metadata of A once (A reused across calls); feed `packed` to gemm_i8_sp24_packed."""
+    _need(a_meta, torch.uint8, "a_meta"); _need(packed, torch.uint8, "packed")
+    check(lib().b200wmma_sp24_repack_meta(m, k, _ptr(a_meta), ld_meta, _ptr(packed), packed.numel(), _stream()))
+
+
+def gemm_i8_sp24_packed(m, n, k, a_vals, a_meta_packed, b, c, d, lda_vals, ldb, ldc, ldd, alpha, beta):
+    _need(a_vals, torch.int8, "a_vals"); _need(a_meta_packed, torch.uint8, "a_meta_packed")
+    _need(b, torch.int8, "b"); _need(d, torch.int32, "d")
+    check(lib().b200wmma_gemm_i8_sp24_packed(m, n, k, _ptr(a_vals), _ptr(a_meta_packed), _ptr(b), _ptr(c), _ptr(d),
+                                             lda_vals, ldb, ldc, ldd, alpha, beta, _stream()))
+
+
 def gemm_i4_workspace_bytes(m, n, k):
     return lib().b200wmma_gemm_i4_workspace_bytes(m, n, k)
 

@@ -79,9 +79,11 @@ namespace b200wmma
     bool sp24_direct_ok(uint32_t k, const void* a_vals, const void* a_meta, const void* b, uint32_t lda_vals,
                         uint32_t ld_meta, uint32_t ldb);
     int  launch_gemm_tc05_i8_sp24(uint32_t m, uint32_t n, uint32_t k, const int8_t* a_vals, const uint8_t* a_meta,
-                                  const int8_t* b, const int32_t* c, int32_t* d, uint32_t lda_vals, uint32_t ld_meta,
-                                  uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha, int32_t beta,
+                                  bool meta_is_packed, const int8_t* b, const int32_t* c, int32_t* d, uint32_t lda_vals,
+                                  uint32_t ld_meta, uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha, int32_t beta,
                                   void* scratch, size_t scratch_bytes, cudaStream_t stream);
+    int  launch_sp24_repack_meta(uint32_t m, uint32_t k, const uint8_t* a_meta, uint32_t ld_meta, void* packed,
+                                 size_t packed_bytes, cudaStream_t stream);
     // bytes of scratch with which the kernel fetches the metadata in wide rows (a re-tiled copy)
     size_t sp24_packed_meta_bytes(uint32_t m, uint32_t k);
 } // namespace b200wmma

@@ -121,6 +121,29 @@ extern "C" size_t b200wmma_gemm_i8_sp24_workspace_bytes(uint32_t m, uint32_t n, 
     return dense > meta ? dense : meta;
 }
 
+extern "C" size_t b200wmma_sp24_packed_meta_bytes(uint32_t m, uint32_t k)
+{
+    return sp24_packed_meta_bytes(m, k);
+}
+
+extern "C" int b200wmma_sp24_repack_meta(uint32_t m, uint32_t k, const uint8_t* a_meta, uint32_t ld_meta, void* packed,
+                                         size_t packed_bytes, void* stream)
+{
+    clear_error();
+    return launch_sp24_repack_meta(m, k, a_meta, ld_meta, packed, packed_bytes, as_stream(stream));
+}
+
+extern "C" int b200wmma_gemm_i8_sp24_packed(uint32_t m, uint32_t n, uint32_t k, const int8_t* a_vals,
+                                            const void* a_meta_packed, const int8_t* b, const int32_t* c, int32_t* d,
+                                            uint32_t lda_vals, uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha,
+                                            int32_t beta, void* stream)
+{
+    clear_error();
+    B200_REQUIRE(k % 128 == 0, B200WMMA_ERR_UNSUPPORTED, "gemm_i8_sp24_packed: k must be a multiple of 128");
+    return launch_gemm_tc05_i8_sp24(m, n, k, a_vals, static_cast<const uint8_t*>(a_meta_packed), true, b, c, d, lda_vals, 0, ldb,
+                                    ldc, ldd, alpha, beta, nullptr, 0, as_stream(stream));
+}
+
 extern "C" size_t b200wmma_gemm_i4_workspace_bytes(uint32_t m, uint32_t n, uint32_t k)
 {
     return i8var::round256(static_cast<size_t>(m) * k) + i8var::round256(static_cast<size_t>(n) * k);
@@ -141,7 +164,7 @@ extern "C" int b200wmma_gemm_i8_sp24(uint32_t m, uint32_t n, uint32_t k, const i
                  "gemm_i8_sp24: lda_vals / ld_meta smaller than k/2 / k/8");
     // Sparse tensor-core path: compressed A goes to the tensor cores as it is, no scratch involved.
     if(!i8var::force_expansion() && sp24_direct_ok(k, a_vals, a_meta, b, lda_vals, ld_meta, ldb))
-        return launch_gemm_tc05_i8_sp24(m, n, k, a_vals, a_meta, b, c, d, lda_vals, ld_meta, ldb, ldc, ldd, alpha, beta,
+        return launch_gemm_tc05_i8_sp24(m, n, k, a_vals, a_meta, false, b, c, d, lda_vals, ld_meta, ldb, ldc, ldd, alpha, beta,
                                         workspace, workspace_bytes, as_stream(stream));
     // Otherwise (k not a multiple of 128, or rows that TMA cannot address): densify A into the
     // workspace and run the dense int8 kernel.

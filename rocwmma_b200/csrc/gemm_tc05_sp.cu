@@ -18,9 +18,32 @@ namespace b200wmma
         return static_cast<size_t>(ceil_div(m, tc05s::CTA_M)) * ceil_div(k, tc05s::SLAB_K) * tc05s::E_STAGE_BYTES;
     }
 
+    int launch_sp24_repack_meta(uint32_t m, uint32_t k, const uint8_t* a_meta, uint32_t ld_meta, void* packed,
+                                size_t packed_bytes, cudaStream_t stream)
+    {
+        using namespace tc05s;
+        B200_REQUIRE(m && k, B200WMMA_ERR_INVALID_ARG, "sp24_repack_meta: m, k must be non-zero");
+        B200_REQUIRE(a_meta && packed, B200WMMA_ERR_INVALID_ARG, "sp24_repack_meta: a_meta, packed must be non-null");
+        B200_REQUIRE(k % HALF_K == 0, B200WMMA_ERR_UNSUPPORTED, "sp24_repack_meta: k must be a multiple of 128");
+        B200_REQUIRE(ld_meta >= k / 8, B200WMMA_ERR_INVALID_ARG, "sp24_repack_meta: ld_meta smaller than k/8");
+        B200_REQUIRE(aligned16(a_meta) && ld_meta % 16 == 0 && aligned16(packed), B200WMMA_ERR_ALIGNMENT,
+                     "sp24_repack_meta: metadata rows and the destination must be 16-byte aligned");
+        B200_REQUIRE(packed_bytes >= sp24_packed_meta_bytes(m, k), B200WMMA_ERR_INVALID_ARG,
+                     "sp24_repack_meta: destination too small (%zu < %zu bytes)", packed_bytes, sp24_packed_meta_bytes(m, k));
+        if(int e = require_sm100())
+            return e;
+        const uint32_t num_kb = ceil_div(k, SLAB_K);
+        repack_meta_kernel<<<dim3(num_kb, ceil_div(m, CTA_M)), 256, 0, stream>>>(a_meta, static_cast<uint8_t*>(packed), m, k,
+                                                                                 ld_meta, num_kb);
+        B200_CHECK_CUDA(cudaGetLastError());
+        return B200WMMA_OK;
+    }
+
+    // meta_is_packed: `a_meta` is the re-tiled copy made by launch_sp24_repack_meta (ld_meta unused).  Otherwise
+    // it is the caller's row-major array; if `scratch` can hold the re-tiled copy it is made first.
     int launch_gemm_tc05_i8_sp24(uint32_t m, uint32_t n, uint32_t k, const int8_t* a_vals, const uint8_t* a_meta,
-                                 const int8_t* b, const int32_t* c, int32_t* d, uint32_t lda_vals, uint32_t ld_meta,
-                                 uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha, int32_t beta,
+                                 bool meta_is_packed, const int8_t* b, const int32_t* c, int32_t* d, uint32_t lda_vals,
+                                 uint32_t ld_meta, uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha, int32_t beta,
                                  void* scratch, size_t scratch_bytes, cudaStream_t stream)
     {
         using namespace tc05s;
@@ -28,6 +51,8 @@ namespace b200wmma
         B200_REQUIRE(a_vals && a_meta && b && d, B200WMMA_ERR_INVALID_ARG,
                      "gemm_i8_sp24: a_vals, a_meta, b, d must be non-null");
         B200_REQUIRE(c || beta == 0, B200WMMA_ERR_INVALID_ARG, "gemm_i8_sp24: c may be null only when beta == 0");
+        if(meta_is_packed)
+            ld_meta = (k / 8 + 15u) & ~15u; // not used for addressing; keeps the shared checks below meaningful
         B200_REQUIRE(lda_vals >= k / 2 && ld_meta >= k / 8 && ldb >= k && ldd >= n && (!c || ldc >= n),
                      B200WMMA_ERR_INVALID_ARG, "gemm_i8_sp24: leading dimension smaller than the row it strides");
         B200_REQUIRE(sp24_direct_ok(k, a_vals, a_meta, b, lda_vals, ld_meta, ldb), B200WMMA_ERR_ALIGNMENT,
@@ -46,19 +71,19 @@ namespace b200wmma
         // With scratch for a re-tiled copy of the metadata (1/8 byte per element of A) the kernel fetches it in
         // 128-byte rows; without, in the 16-byte rows of the caller's array (8 x the requests).
         const uint32_t num_kb   = ceil_div(k, SLAB_K);
-        const bool     e_packed = scratch != nullptr && aligned16(scratch) && scratch_bytes >= sp24_packed_meta_bytes(m, k);
-        if(e_packed)
-        {
-            repack_meta_kernel<<<dim3(num_kb, ceil_div(m, CTA_M)), 256, 0, stream>>>(
-                a_meta, static_cast<uint8_t*>(scratch), m, k, ld_meta, num_kb);
-            B200_CHECK_CUDA(cudaGetLastError());
-        }
+        const bool     retile   = !meta_is_packed && scratch != nullptr && aligned16(scratch)
+                            && scratch_bytes >= sp24_packed_meta_bytes(m, k);
+        const bool  e_packed = meta_is_packed || retile;
+        const void* e_src    = meta_is_packed ? static_cast<const void*>(a_meta) : scratch;
+        if(retile)
+            if(int e = launch_sp24_repack_meta(m, k, a_meta, ld_meta, scratch, scratch_bytes, stream))
+                return e;
         CUtensorMap tm_a, tm_e, tm_b;
         if(int e = make_bytes_tmap(&tm_a, a_vals, m, k / 2, lda_vals, A_ROW_BYTES, CTA_M, CU_TENSOR_MAP_SWIZZLE_128B))
             return e;
         if(e_packed)
         {
-            if(int e = make_bytes_tmap(&tm_e, scratch, ceil_div(m, CTA_M) * num_kb * E_PACKED_ROWS, 128, 128, 128, E_PACKED_ROWS,
+            if(int e = make_bytes_tmap(&tm_e, e_src, ceil_div(m, CTA_M) * num_kb * E_PACKED_ROWS, 128, 128, 128, E_PACKED_ROWS,
                                        CU_TENSOR_MAP_SWIZZLE_NONE))
                 return e;
         }

@@ -192,6 +192,21 @@ def test_gemm_i8_sparse24_bit_exact(m, n, k, alpha, beta):
     assert np.array_equal(d.cpu().numpy(), ref)
 
 
+@pytest.mark.parametrize("m,n,k", [(300, 260, 384), (1024, 448, 1024)])
+def test_gemm_i8_sparse24_metadata_retiled_once(m, n, k):
+    """Metadata re-tiled once (b200wmma_sp24_repack_meta), then two GEMMs with different B on the packed copy."""
+    dense = G.int8_np(G.SEED_A, (m, k))
+    vals, meta, densified = G.sparsify_24_np(dense)
+    packed = torch.empty(api.sp24_packed_meta_bytes(m, k), dtype=torch.uint8, device="cuda")
+    api.sp24_repack_meta(m, k, dev(meta), k // 8, packed)
+    for seed in (G.SEED_B, G.SEED_C):
+        bs = np.ascontiguousarray(G.int8_np(seed, (k, n)).T)
+        d = nan_filled((m, n), torch.int32)
+        api.gemm_i8_sp24_packed(m, n, k, dev(vals), packed, dev(bs), None, d, k // 2, k, n, n, 1, 0)
+        assert_status_ok()
+        assert np.array_equal(d.cpu().numpy(), oracle_gemm_rows(densified, bs, None, 1, 0, np.int32, n, k))
+
+
 def test_gemm_i8_sparse24_padded_pitches_no_workspace():
     """Row pitches larger than the rows (values, metadata, B, C, D), D rows not 16-byte aligned (element-wise
     epilogue), and no workspace: the sparse tensor-core path needs none."""
