@@ -11,7 +11,7 @@ N > 1: one process per GPU.  The problem is sharded by N-column blocks (B, C, D 
 over NCCL before the timed region and reported separately as `a_broadcast_ms`); there is no collective in
 the data path, total work is fixed (strong scaling), value = 2*M*N*K / max-over-ranks time.
 
-Other workloads (`--workload gemm_i8 | gemm_i8_sp24 | gemm_i4 | gemm_f64 | dlrm_fwd | dlrm_bwd | sgemv | dgemv`)
+Other workloads (`--workload gemm_bf16 | gemm_fp8 | gemm_i8 | gemm_i8_sp24 | gemm_i4 | gemm_f64 | dlrm_fwd | dlrm_bwd | sgemv | dgemv`)
 print the same line for the other configurations; they are not the default.
 
 `--impl reference` times the reference's own CPU implementation (oracle/_ref/libref.so, compiled from
@@ -233,6 +233,58 @@ class GemmF16(Workload):
         return work / seconds / 1e12
 
     cpu_rows = 64
+
+
+class GemmBF16(GemmF16):
+    """bfloat16 (or fp8) inputs, fp32 C / D: the same problem as gemm_f16 with the inputs rounded to the type."""
+    name, metric, dtype = "gemm_bf16", "bf16 GEMM TFLOP/s at 8192^3 (fp32 C/D)", "bf16"
+    has_host = False
+
+    def _in_dtype(self, torch):
+        return torch.bfloat16
+
+    def setup(self, torch, rank, world, dist):
+        super().setup(torch, rank, world, dist)
+        t = self._in_dtype(torch)
+        self.a, self.b = self.a.to(t), self.b.to(t)
+        self.c = self.c.to(torch.float32)
+        self.d = torch.empty_like(self.c)
+
+    def step(self):
+        from rocwmma_b200 import api
+        fn = api.gemm_bf16 if self.dtype == "bf16" else api.gemm_fp8
+        fn(self.M, self.nloc, self.K, self.a, self.b, self.c, self.d, self.K, self.K, self.nloc, self.nloc,
+           self.alpha, self.beta)
+
+    def config(self, world):
+        cfg = super().config(world)
+        cfg["workload"] = (f"dense {self.dtype} GEMM, M=N=K=8192, A row-major, B col-major, C/D row-major fp32, "
+                           "fp32 accumulate, alpha=beta=1")
+        cfg["l2"] = "inputs larger than L2"
+        return cfg
+
+    def cpu_sample(self, impl, rows):
+        import numpy as np
+        import torch
+        from oracle import cpu_ref as R
+        from rocwmma_b200 import datagen as G
+        K, N = self.K, self.N
+        if not hasattr(self, "_cpu"):
+            t = self._in_dtype(torch)
+            widen = lambda x: torch.from_numpy(x).to(t).to(torch.float32).numpy()
+            self._cpu = (widen(G.uniform_np(G.SEED_A, (rows, K), np.float32)), widen(G.uniform_np(G.SEED_B, (N, K), np.float32)),
+                         G.uniform_np(G.SEED_C, (rows, N), np.float32))
+        a, b, c = self._cpu
+        t0 = time.perf_counter()
+        R.gemm(impl, rows, N, K, a[:rows].ravel(), b.ravel(), c[:rows].ravel(), 1.0, 1.0, np.float32)
+        return 2.0 * rows * N * K, time.perf_counter() - t0
+
+
+class GemmFP8(GemmBF16):
+    name, metric, dtype = "gemm_fp8", "fp8 (e4m3) GEMM TFLOP/s at 8192^3 (fp32 C/D)", "fp8"
+
+    def _in_dtype(self, torch):
+        return torch.float8_e4m3fn
 
 
 class GemmI8(GemmF16):
@@ -538,7 +590,7 @@ class Dgemv(Gemv):
     double = True
 
 
-WORKLOADS = {w().name: w for w in (GemmF16, GemmI8, GemmI8Sp24, GemmI4, GemmF64, Dlrm, DlrmBwd, Gemv, Dgemv)}
+WORKLOADS = {w().name: w for w in (GemmF16, GemmBF16, GemmFP8, GemmI8, GemmI8Sp24, GemmI4, GemmF64, Dlrm, DlrmBwd, Gemv, Dgemv)}
 
 
 # ---------------------------------------------------------------------------------------- CPU arm
@@ -656,7 +708,7 @@ def run_gpu_arm(args, wl):
 
     # end to end: host buffers through the C ABI host drivers, copies inside the timed region
     e2e = None
-    if hasattr(wl, "setup_host") and not args.no_e2e:
+    if hasattr(wl, "setup_host") and getattr(wl, "has_host", True) and not args.no_e2e:
         wl.setup_host()
         for _ in range(2):
             wl.step_host()
@@ -674,7 +726,10 @@ def run_gpu_arm(args, wl):
         peaks = measured_peaks()
         if wl.bound == "tensor":
             peak = peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])
-            if wl.dtype == "i8" and getattr(wl, "variant", "") == "sp24":
+            if wl.dtype == "fp8":
+                peak *= 2.0  # the fp8 tensor rate is twice the 16-bit rate; no fp8 figure is measured
+                peak_note = "2 x cuBLAS bf16 8192^3 burst, standing in for the dense fp8 rate"
+            elif wl.dtype == "i8" and getattr(wl, "variant", "") == "sp24":
                 peak *= 4.0  # sparse int8: twice the dense int8 rate (measured: 112 clocks per 256x224x64 pair MMA)
                 peak_note = "4 x cuBLAS bf16 8192^3 burst, standing in for the 2:4-sparse int8 rate"
             elif wl.dtype == "i8":

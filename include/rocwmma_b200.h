@@ -43,6 +43,7 @@ typedef enum b200wmma_status
 
 enum { B200WMMA_ROW_MAJOR = 0, B200WMMA_COL_MAJOR = 1 };
 enum { B200WMMA_OUT_F16 = 0, B200WMMA_OUT_F32 = 1 };
+enum { B200WMMA_FP8_E4M3 = 0, B200WMMA_FP8_E5M2 = 1 }; /* OCP 8-bit float formats (finite-only e4m3, IEEE-like e5m2) */
 
 /* Human-readable text for the last error raised on the calling thread. */
 const char* b200wmma_last_error_string(void);
@@ -69,7 +70,9 @@ int b200wmma_device_status(void* stream, int* out_status, unsigned* out_detail);
  * f16: fp16 inputs, fp32 accumulate, D/C fp16 or fp32 (out_type).  tcgen05 tensor cores.
  * i8 : int8 inputs, int32 accumulate / scalars / outputs (wrap-around arithmetic).
  * f64: fp64 everywhere (DMMA).
- * f16 / i8 accept every combination of row / column major A, B and C/D (C and D share one layout), as
+ * bf16 / fp8: bfloat16 resp. OCP fp8 (both operands of one format) inputs, fp32 accumulate, C/D fp32 -
+ *   the reference's bfloat16_t and float8 / bfloat8 input types (docs/api-reference-guide.rst:84-143).
+ * f16 / i8 / bf16 / fp8 accept every combination of row / column major A, B and C/D (C and D share one layout), as
  * the reference's NN / NT / TN / TT sweeps do; f64 takes A row major, B column major, C/D row major.
  * A and B base pointers and leading dimensions (in bytes) must be multiples of 16 (TMA requirement);
  * C / D may be unaligned (slower element-wise epilogue).
@@ -85,6 +88,16 @@ int b200wmma_gemm_i8(uint32_t m, uint32_t n, uint32_t k,
                      uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
                      int32_t alpha, int32_t beta,
                      int layout_a, int layout_b, int layout_cd, void* stream);
+int b200wmma_gemm_bf16(uint32_t m, uint32_t n, uint32_t k,
+                       const void* a, const void* b, const float* c, float* d,
+                       uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                       float alpha, float beta,
+                       int layout_a, int layout_b, int layout_cd, void* stream);
+int b200wmma_gemm_fp8(uint32_t m, uint32_t n, uint32_t k,
+                      const void* a, const void* b, const float* c, float* d,
+                      uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                      float alpha, float beta,
+                      int layout_a, int layout_b, int layout_cd, int fp8_format, void* stream);
 
 /* Replaces gemm_rocwmma_d of samples/perf_dgemm.cpp:461 (same 13-argument signature). */
 int b200wmma_gemm_f64(uint32_t m, uint32_t n, uint32_t k,

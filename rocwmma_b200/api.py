@@ -50,6 +50,32 @@ def gemm_f16(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
                                   alpha, beta, layout_a, layout_b, layout_cd, out_type, _stream()))
 
 
+FP8_E4M3, FP8_E5M2 = 0, 1
+
+
+def gemm_bf16(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
+              layout_a=ROW_MAJOR, layout_b=COL_MAJOR, layout_cd=ROW_MAJOR):
+    """bfloat16 inputs, fp32 accumulate, fp32 C / D."""
+    _need(a, torch.bfloat16, "a"); _need(b, torch.bfloat16, "b"); _need(d, torch.float32, "d")
+    if c is not None:
+        _need(c, torch.float32, "c")
+    check(lib().b200wmma_gemm_bf16(m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc, ldd,
+                                   alpha, beta, layout_a, layout_b, layout_cd, _stream()))
+
+
+def gemm_fp8(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
+             layout_a=ROW_MAJOR, layout_b=COL_MAJOR, layout_cd=ROW_MAJOR):
+    """OCP fp8 inputs (both torch.float8_e4m3fn or both torch.float8_e5m2), fp32 accumulate, fp32 C / D."""
+    if a.dtype not in (torch.float8_e4m3fn, torch.float8_e5m2):
+        raise TypeError("a must be float8_e4m3fn or float8_e5m2")
+    _need(a, a.dtype, "a"); _need(b, a.dtype, "b"); _need(d, torch.float32, "d")
+    if c is not None:
+        _need(c, torch.float32, "c")
+    fmt = FP8_E4M3 if a.dtype == torch.float8_e4m3fn else FP8_E5M2
+    check(lib().b200wmma_gemm_fp8(m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc, ldd,
+                                  alpha, beta, layout_a, layout_b, layout_cd, fmt, _stream()))
+
+
 def gemm_i8(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
             layout_a=ROW_MAJOR, layout_b=COL_MAJOR, layout_cd=ROW_MAJOR):
     _need(a, torch.int8, "a"); _need(b, torch.int8, "b"); _need(d, torch.int32, "d")

@@ -121,6 +121,28 @@ extern "C" int b200wmma_gemm_f16(uint32_t m, uint32_t n, uint32_t k, const void*
                                 layout_cd, out_type, as_stream(stream));
 }
 
+extern "C" int b200wmma_gemm_bf16(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const float* c,
+                                  float* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, float alpha,
+                                  float beta, int layout_a, int layout_b, int layout_cd, void* stream)
+{
+    clear_error();
+    if(int e = check_layouts("gemm_bf16", layout_a, layout_b, layout_cd))
+        return e;
+    return launch_gemm_tc05_bf16(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, layout_a, layout_b, layout_cd,
+                                 as_stream(stream));
+}
+
+extern "C" int b200wmma_gemm_fp8(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const float* c,
+                                 float* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, float alpha,
+                                 float beta, int layout_a, int layout_b, int layout_cd, int fp8_format, void* stream)
+{
+    clear_error();
+    if(int e = check_layouts("gemm_fp8", layout_a, layout_b, layout_cd))
+        return e;
+    return launch_gemm_tc05_fp8(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, layout_a, layout_b, layout_cd,
+                                fp8_format, as_stream(stream));
+}
+
 extern "C" int b200wmma_gemm_i8(uint32_t m, uint32_t n, uint32_t k, const int8_t* a, const int8_t* b,
                                 const int32_t* c, int32_t* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
                                 uint32_t ldd, int32_t alpha, int32_t beta, int layout_a, int layout_b,

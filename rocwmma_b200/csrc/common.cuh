@@ -69,6 +69,12 @@ namespace b200wmma
                              const void* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
                              uint32_t ldd, float alpha, float beta, int layout_a, int layout_b,
                              int layout_cd, int out_type, cudaStream_t stream);
+    int launch_gemm_tc05_bf16(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const float* c, float* d,
+                              uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, float alpha, float beta, int layout_a,
+                              int layout_b, int layout_cd, cudaStream_t stream);
+    int launch_gemm_tc05_fp8(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const float* c, float* d,
+                             uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, float alpha, float beta, int layout_a,
+                             int layout_b, int layout_cd, int fp8_format, cudaStream_t stream);
     int launch_gemm_tc05_i8(uint32_t m, uint32_t n, uint32_t k, const int8_t* a,
                             const int8_t* b, const int32_t* c, int32_t* d, uint32_t lda,
                             uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha,

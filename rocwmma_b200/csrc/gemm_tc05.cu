@@ -302,7 +302,9 @@ namespace b200wmma
                           bool         b_mn, // B row-major (N contiguous) instead of column-major
                           cudaStream_t stream)
         {
-            constexpr uint32_t EB = (KIND == KIND_F16) ? 2u : 1u;
+            constexpr uint32_t EB = elem_bytes<KIND>();
+            // bf16 and fp8 inputs run on the 512 x 256 pair kernel only
+            constexpr bool ONLY_Q = KIND != KIND_F16 && KIND != KIND_I8;
             B200_REQUIRE(m && n && k, B200WMMA_ERR_INVALID_ARG, "gemm: m, n, k must be non-zero");
             B200_REQUIRE(a && b && d, B200WMMA_ERR_INVALID_ARG, "gemm: a, b, d must be non-null");
             B200_REQUIRE(c || beta == ScalarT(0),
@@ -323,7 +325,8 @@ namespace b200wmma
                 return e;
 
             const CUtensorMapDataType dt
-                = (KIND == KIND_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+                = (KIND == KIND_F16) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                     : (KIND == KIND_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8);
             // widest epilogue access every C / D row start allows: 32 bytes, 16 bytes, or element-wise
             auto row_align = [](const void* p, uint32_t ld, size_t es, uint64_t bytes) {
                 return (reinterpret_cast<uintptr_t>(p) % bytes) == 0 && (static_cast<uint64_t>(ld) * es) % bytes == 0;
@@ -342,7 +345,7 @@ namespace b200wmma
             // ceil(tiles / slots) rounds of one tile each; pick the shape with the smallest estimated
             // time = rounds x outputs per SM per tile / relative speed (measured at 8192^3: 1, 0.955, 0.91).
             // B200WMMA_GEMM_VARIANT=1cta|2cta|2cta512 forces one, for comparison.
-            const int forced = (a_mn || b_mn) ? 3 : forced_variant(); // MN-major operands: 512 x 256 kernel only
+            const int forced = (a_mn || b_mn || ONLY_Q) ? 3 : forced_variant(); // MN-major operands: 512 x 256 kernel only
             int       pick   = forced;
             if(pick == 0)
             {
@@ -418,6 +421,8 @@ namespace b200wmma
                 return B200WMMA_OK;
             }
 
+            if constexpr(!ONLY_Q)
+            {
             if(use_pair)
             {
                 auto        kern    = tc05p::gemm_tc05_pair_kernel<KIND, OutT, ScalarT>;
@@ -481,6 +486,9 @@ namespace b200wmma
                                                              status);
             B200_CHECK_CUDA(cudaGetLastError());
             return B200WMMA_OK;
+            }
+            else
+                return set_error(B200WMMA_ERR_UNSUPPORTED, "gemm: no kernel for this input type and shape");
         }
     } // namespace tc05
 
@@ -514,6 +522,27 @@ namespace b200wmma
                                                                    static_cast<float*>(d), lda, ldb, ldc, ldd, alpha, beta,
                                                                    layout_a, layout_b, layout_cd, stream);
         return set_error(B200WMMA_ERR_INVALID_ARG, "gemm_f16: out_type must be 0 (f16) or 1 (f32)");
+    }
+
+    int launch_gemm_tc05_bf16(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const float* c, float* d,
+                              uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, float alpha, float beta, int layout_a,
+                              int layout_b, int layout_cd, cudaStream_t stream)
+    {
+        return launch_any_layout<tc05::KIND_BF16, float, float>(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, layout_a,
+                                                                layout_b, layout_cd, stream);
+    }
+
+    int launch_gemm_tc05_fp8(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const float* c, float* d,
+                             uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, float alpha, float beta, int layout_a,
+                             int layout_b, int layout_cd, int fp8_format, cudaStream_t stream)
+    {
+        if(fp8_format == B200WMMA_FP8_E4M3)
+            return launch_any_layout<tc05::KIND_E4M3, float, float>(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
+                                                                    layout_a, layout_b, layout_cd, stream);
+        if(fp8_format == B200WMMA_FP8_E5M2)
+            return launch_any_layout<tc05::KIND_E5M2, float, float>(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
+                                                                    layout_a, layout_b, layout_cd, stream);
+        return set_error(B200WMMA_ERR_INVALID_ARG, "gemm_fp8: fp8_format must be 0 (e4m3) or 1 (e5m2)");
     }
 
     int launch_gemm_tc05_i8(uint32_t m, uint32_t n, uint32_t k, const int8_t* a,

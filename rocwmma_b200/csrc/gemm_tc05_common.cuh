@@ -16,9 +16,18 @@ namespace b200wmma
 
         enum Kind : int
         {
-            KIND_F16 = 0,
-            KIND_I8  = 1
+            KIND_F16  = 0, // fp16 x fp16 -> fp32
+            KIND_I8   = 1, // int8 x int8 -> int32
+            KIND_BF16 = 2, // bf16 x bf16 -> fp32
+            KIND_E4M3 = 3, // OCP fp8 e4m3 x e4m3 -> fp32
+            KIND_E5M2 = 4 // OCP fp8 e5m2 x e5m2 -> fp32
         };
+        // bytes per input element
+        template <int KIND>
+        __host__ __device__ constexpr uint32_t elem_bytes()
+        {
+            return (KIND == KIND_F16 || KIND == KIND_BF16) ? 2u : 1u;
+        }
         enum Role : uint32_t
         {
             ROLE_PRODUCER = 1,
@@ -35,6 +44,22 @@ namespace b200wmma
             if(KIND == KIND_F16)
             {
                 d |= 1u << 4; // D = F32;  A = B = F16 (format 0)
+            }
+            else if(KIND == KIND_BF16)
+            {
+                d |= 1u << 4; // D = F32
+                d |= 1u << 7; // A = BF16 (format 1 of kind::f16)
+                d |= 1u << 10; // B = BF16
+            }
+            else if(KIND == KIND_E4M3)
+            {
+                d |= 1u << 4; // D = F32;  A = B = E4M3 (format 0 of kind::f8f6f4)
+            }
+            else if(KIND == KIND_E5M2)
+            {
+                d |= 1u << 4; // D = F32
+                d |= 1u << 7; // A = E5M2 (format 1 of kind::f8f6f4)
+                d |= 1u << 10; // B = E5M2
             }
             else
             {

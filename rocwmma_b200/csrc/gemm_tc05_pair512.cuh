@@ -267,7 +267,7 @@ namespace b200wmma
                             if(rank == 0)
                                 ptx::mbar_arrive_expect_tx(full_bar + 8 * stage, 2u * STAGE_BYTES);
                             const uint32_t leader_full = ptx::mapa(full_bar + 8 * stage, 0u);
-                            constexpr uint32_t ES       = (KIND == KIND_F16) ? 2u : 1u;
+                            constexpr uint32_t ES       = elem_bytes<KIND>();
                             constexpr uint32_t SLAB_K   = BLOCK_K_BYTES / ES; // K elements per slab
                             constexpr uint32_t MN_GROUP = 128u / ES; // MN elements per 128-byte line
                             constexpr uint32_t GROUP_B  = SLAB_K * 128u; // bytes of one MN group over a slab
@@ -306,7 +306,7 @@ namespace b200wmma
                 if(lane == 0 && rank == 0)
                 {
                     constexpr uint32_t idesc = make_idesc<KIND, 2 * SUB_M, TILE_N, A_MN, B_MN>();
-                    constexpr uint32_t ES      = (KIND == KIND_F16) ? 2u : 1u;
+                    constexpr uint32_t ES      = elem_bytes<KIND>();
                     constexpr uint32_t GROUP_B = (BLOCK_K_BYTES / ES) * 128u; // one MN group over a slab
                     // descriptor start-address step per MMA (32 bytes of K): 32 bytes inside the K-major line,
                     // or (32 / ES) K rows of 128 bytes for an MN-major tile
@@ -345,10 +345,12 @@ namespace b200wmma
                                 for(uint32_t ks = 0; ks < BLOCK_K_BYTES / 32; ++ks)
                                 {
                                     const uint32_t acc = (kb | ks) != 0u ? 1u : 0u;
-                                    if constexpr(KIND == KIND_F16)
+                                    if constexpr(KIND == KIND_F16 || KIND == KIND_BF16)
                                         ptx::mma_f16_ss_pair(tmem_base + j * TILE_N, a_desc + A_STEP * ks, b_desc + B_STEP * ks, idesc, acc);
-                                    else
+                                    else if constexpr(KIND == KIND_I8)
                                         ptx::mma_i8_ss_pair(tmem_base + j * TILE_N, a_desc + A_STEP * ks, b_desc + B_STEP * ks, idesc, acc);
+                                    else
+                                        ptx::mma_f8_ss_pair(tmem_base + j * TILE_N, a_desc + A_STEP * ks, b_desc + B_STEP * ks, idesc, acc);
                                 }
                             }
                             if(!ok)

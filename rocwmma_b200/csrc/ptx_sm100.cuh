@@ -436,6 +436,22 @@ namespace b200wmma
                          "r"(accumulate)
                          : "memory");
         }
+        // 8-bit floating point inputs (e4m3 / e5m2 chosen in the instruction descriptor), fp32 accumulate;
+        // 32 bytes of K per instruction like the int8 form.
+        __device__ __forceinline__ void mma_f8_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                       uint32_t idesc, uint32_t accumulate)
+        {
+            asm volatile("{\n"
+                         ".reg .pred p;\n"
+                         "setp.ne.b32 p, %4, 0;\n"
+                         "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+                         "}" ::"r"(d_tmem),
+                         "l"(a_desc),
+                         "l"(b_desc),
+                         "r"(idesc),
+                         "r"(accumulate)
+                         : "memory");
+        }
         // Once every MMA issued so far by this thread has completed, arrive on the barrier at this
         // shared-memory offset in each CTA of the pair named by `cta_mask` (bit r = CTA rank r).
         // This is a barrier signal, not a data transfer: no operand is multicast.

@@ -158,6 +158,35 @@ def test_gemm_all_layouts(la, lb, lcd, m, n, k):
     assert_status_ok()
 
 
+_LOWP = {"bf16": torch.bfloat16, "e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
+
+
+@pytest.mark.parametrize("kind", sorted(_LOWP))
+@pytest.mark.parametrize("la,lb,lcd", [(0, 1, 0), (1, 0, 0), (0, 0, 1), (1, 1, 1)], ids=["RCR", "CRR", "RRC", "CCC"])
+@pytest.mark.parametrize("m,n,k", [(512, 256, 256), (608, 336, 208), (80, 1104, 272)])
+def test_gemm_bf16_fp8_inputs(kind, la, lb, lcd, m, n, k):
+    """bfloat16 / OCP fp8 inputs with fp32 accumulation and fp32 C / D (the reference's bfloat16_t, float8 and
+    bfloat8 input types, docs/api-reference/api-reference-guide.rst:84-143).  The oracle is the reference's
+    gemm_CPU arithmetic on the inputs widened exactly to fp32: acc += float(a) * float(b) in ascending k."""
+    tdt = _LOWP[kind]
+    lda, ldb, ldcd = _lds(m, n, k, la, lb, lcd)
+    store = lambda x, col: np.ascontiguousarray(x.T if col else x)
+    ta = torch.from_numpy(G.uniform_np(1, (m, k), np.float32)).to(tdt)       # rounded once; these ARE the inputs
+    tb = torch.from_numpy(G.uniform_np(2, (k, n), np.float32)).to(tdt)
+    a, b = ta.to(torch.float32).numpy(), tb.to(torch.float32).numpy()         # exact widening
+    c = G.uniform_np(3, (m, n), np.float32)
+    dev_lowp = lambda tt, col: (tt.t().contiguous() if col else tt.contiguous()).cuda()
+    sc = store(c, lcd)
+    d = nan_filled(sc.shape, torch.float32)
+    fn = api.gemm_bf16 if kind == "bf16" else api.gemm_fp8
+    fn(m, n, k, dev_lowp(ta, la), dev_lowp(tb, lb), dev(sc), d, lda, ldb, ldcd, ldcd, 2.0, 0.5, la, lb, lcd)
+    assert_status_ok()
+    ref = R.gemm(R.port(), m, n, k, store(a, la).ravel(), store(b, lb).ravel(), sc.ravel(), 2.0, 0.5, np.float32,
+                 la, lb, lcd, lcd)
+    bound = store(R.gemm_abs_bound(m, n, k, a, b, c, 2.0, 0.5), lcd).ravel()
+    assert gemm_rel_err(d.cpu().numpy().ravel(), ref, bound) <= TOL_F32_OUT
+
+
 @pytest.mark.parametrize("m,n,k,alpha,beta", [(128, 256, 128, 1, 0), (256, 256, 1024, 1, 0), (128, 512, 16384, 1, 0),
                                               (100, 72, 144, 3, -2), (513, 300, 272, 1, 1)])
 def test_gemm_i8_bit_exact(m, n, k, alpha, beta):
