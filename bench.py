@@ -11,7 +11,7 @@ N > 1: one process per GPU.  The problem is sharded by N-column blocks (B, C, D 
 over NCCL before the timed region and reported separately as `a_broadcast_ms`); there is no collective in
 the data path, total work is fixed (strong scaling), value = 2*M*N*K / max-over-ranks time.
 
-Other workloads (`--workload gemm_bf16 | gemm_fp8 | gemm_i8 | gemm_i8_sp24 | gemm_i4 | gemm_f64 | dlrm_fwd | dlrm_bwd | sgemv | dgemv`)
+Other workloads (`--workload gemm_bf16 | gemm_fp8 | gemm_f32 | gemm_i8 | gemm_i8_sp24 | gemm_i4 | gemm_f64 | dlrm_fwd | dlrm_bwd | sgemv | dgemv`)
 print the same line for the other configurations; they are not the default.
 
 `--impl reference` times the reference's own CPU implementation (oracle/_ref/libref.so, compiled from
@@ -278,6 +278,29 @@ class GemmBF16(GemmF16):
         t0 = time.perf_counter()
         R.gemm(impl, rows, N, K, a[:rows].ravel(), b.ravel(), c[:rows].ravel(), 1.0, 1.0, np.float32)
         return 2.0 * rows * N * K, time.perf_counter() - t0
+
+
+class GemmF32(GemmBF16):
+    name, metric, dtype = "gemm_f32", "fp32 GEMM (3 x TF32) TFLOP/s at 8192^3", "f32"
+    launches_per_step = 3   # split A, split B, GEMM
+
+    def _in_dtype(self, torch):
+        return torch.float32
+
+    def setup(self, torch, rank, world, dist):
+        super().setup(torch, rank, world, dist)
+        from rocwmma_b200 import api
+        from rocwmma_b200 import datagen as G
+        # full 24-bit mantissas (the inherited tensors hold fp16-rounded values, whose low TF32 terms would be zero)
+        col0, _ = _shard(self.N, world, rank)
+        G.fill_torch(self.a, G.SEED_A, "uniform")
+        G.fill_torch(self.b, G.SEED_B, "uniform", start=col0 * self.K)
+        self.ws = torch.empty(api.gemm_f32_workspace_bytes(self.M, self.nloc, self.K), dtype=torch.uint8, device="cuda")
+
+    def step(self):
+        from rocwmma_b200 import api
+        api.gemm_f32(self.M, self.nloc, self.K, self.a, self.b, self.c, self.d, self.K, self.K, self.nloc, self.nloc,
+                     self.alpha, self.beta, self.ws)
 
 
 class GemmFP8(GemmBF16):
@@ -590,7 +613,7 @@ class Dgemv(Gemv):
     double = True
 
 
-WORKLOADS = {w().name: w for w in (GemmF16, GemmBF16, GemmFP8, GemmI8, GemmI8Sp24, GemmI4, GemmF64, Dlrm, DlrmBwd, Gemv, Dgemv)}
+WORKLOADS = {w().name: w for w in (GemmF16, GemmBF16, GemmFP8, GemmF32, GemmI8, GemmI8Sp24, GemmI4, GemmF64, Dlrm, DlrmBwd, Gemv, Dgemv)}
 
 
 # ---------------------------------------------------------------------------------------- CPU arm
@@ -726,7 +749,10 @@ def run_gpu_arm(args, wl):
         peaks = measured_peaks()
         if wl.bound == "tensor":
             peak = peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])
-            if wl.dtype == "fp8":
+            if wl.dtype == "f32":
+                peak /= 6.0  # TF32 runs at half the 16-bit rate and every product takes three MMAs
+                peak_note = "cuBLAS bf16 8192^3 burst / 6: TF32 rate over three products"
+            elif wl.dtype == "fp8":
                 peak *= 2.0  # the fp8 tensor rate is twice the 16-bit rate; no fp8 figure is measured
                 peak_note = "2 x cuBLAS bf16 8192^3 burst, standing in for the dense fp8 rate"
             elif wl.dtype == "i8" and getattr(wl, "variant", "") == "sp24":

@@ -88,6 +88,18 @@ int b200wmma_gemm_i8(uint32_t m, uint32_t n, uint32_t k,
                      uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
                      int32_t alpha, int32_t beta,
                      int layout_a, int layout_b, int layout_cd, void* stream);
+/* fp32 inputs and outputs with fp32-class accuracy on the tensor cores (each operand split into two TF32
+ * terms, three products accumulated in fp32): the reference's fp32 GEMM samples sgemm_rocwmma_d
+ * (samples/simple_sgemm.cpp) and gemm_rocwmma_d of samples/perf_sgemm.cpp.  A row major, B column major,
+ * C/D row major; k a multiple of 4; A / B rows 16-byte aligned.  `workspace`: caller-owned device scratch of
+ * b200wmma_gemm_f32_workspace_bytes() bytes (the split copies of A and B). */
+size_t b200wmma_gemm_f32_workspace_bytes(uint32_t m, uint32_t n, uint32_t k);
+int b200wmma_gemm_f32(uint32_t m, uint32_t n, uint32_t k,
+                      const float* a, const float* b, const float* c, float* d,
+                      uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                      float alpha, float beta,
+                      int layout_a, int layout_b, int layout_cd,
+                      void* workspace, size_t workspace_bytes, void* stream);
 int b200wmma_gemm_bf16(uint32_t m, uint32_t n, uint32_t k,
                        const void* a, const void* b, const float* c, float* d,
                        uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,

@@ -50,6 +50,20 @@ def gemm_f16(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
                                   alpha, beta, layout_a, layout_b, layout_cd, out_type, _stream()))
 
 
+def gemm_f32_workspace_bytes(m, n, k):
+    return lib().b200wmma_gemm_f32_workspace_bytes(m, n, k)
+
+
+def gemm_f32(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, workspace):
+    """fp32 GEMM (3 x TF32 on the tensor cores); A row-major, B column-major, C/D row-major."""
+    _need(a, torch.float32, "a"); _need(b, torch.float32, "b"); _need(d, torch.float32, "d")
+    _need(workspace, torch.uint8, "workspace")
+    if c is not None:
+        _need(c, torch.float32, "c")
+    check(lib().b200wmma_gemm_f32(m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc, ldd, alpha, beta,
+                                  ROW_MAJOR, COL_MAJOR, ROW_MAJOR, _ptr(workspace), workspace.numel(), _stream()))
+
+
 FP8_E4M3, FP8_E5M2 = 0, 1
 
 

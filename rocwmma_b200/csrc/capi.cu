@@ -143,6 +143,25 @@ extern "C" int b200wmma_gemm_fp8(uint32_t m, uint32_t n, uint32_t k, const void*
                                 fp8_format, as_stream(stream));
 }
 
+extern "C" size_t b200wmma_gemm_f32_workspace_bytes(uint32_t m, uint32_t n, uint32_t k)
+{
+    return gemm_f32_workspace_bytes(m, n, k);
+}
+
+extern "C" int b200wmma_gemm_f32(uint32_t m, uint32_t n, uint32_t k, const float* a, const float* b, const float* c,
+                                 float* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, float alpha, float beta,
+                                 int layout_a, int layout_b, int layout_cd, void* workspace, size_t workspace_bytes,
+                                 void* stream)
+{
+    clear_error();
+    if(int e = check_layouts("gemm_f32", layout_a, layout_b, layout_cd))
+        return e;
+    B200_REQUIRE(layout_a == B200WMMA_ROW_MAJOR && layout_b == B200WMMA_COL_MAJOR && layout_cd == B200WMMA_ROW_MAJOR,
+                 B200WMMA_ERR_UNSUPPORTED, "gemm_f32: A row-major, B column-major, C/D row-major only");
+    return launch_gemm_tc05_f32(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, workspace, workspace_bytes,
+                                as_stream(stream));
+}
+
 extern "C" int b200wmma_gemm_i8(uint32_t m, uint32_t n, uint32_t k, const int8_t* a, const int8_t* b,
                                 const int32_t* c, int32_t* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
                                 uint32_t ldd, int32_t alpha, int32_t beta, int layout_a, int layout_b,

@@ -75,6 +75,11 @@ namespace b200wmma
     int launch_gemm_tc05_fp8(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const float* c, float* d,
                              uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, float alpha, float beta, int layout_a,
                              int layout_b, int layout_cd, int fp8_format, cudaStream_t stream);
+    // fp32 inputs, 3 x TF32 on the tensor cores (A row major, B column major, C / D row major)
+    size_t gemm_f32_workspace_bytes(uint32_t m, uint32_t n, uint32_t k);
+    int    launch_gemm_tc05_f32(uint32_t m, uint32_t n, uint32_t k, const float* a, const float* b, const float* c, float* d,
+                                uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, float alpha, float beta,
+                                void* workspace, size_t workspace_bytes, cudaStream_t stream);
     int launch_gemm_tc05_i8(uint32_t m, uint32_t n, uint32_t k, const int8_t* a,
                             const int8_t* b, const int32_t* c, int32_t* d, uint32_t lda,
                             uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha,

@@ -158,6 +158,27 @@ def test_gemm_all_layouts(la, lb, lcd, m, n, k):
     assert_status_ok()
 
 
+TOL_F32X3 = 5e-6   # three TF32 products: ~2^-21 per product; a single TF32 product (2^-11) would miss this by far
+
+
+@pytest.mark.parametrize("m,n,k,alpha,beta", [(512, 256, 256, 1.0, 0.0), (640, 300, 100, 2.0, 0.5), (200, 1000, 512, -1.5, 1.0),
+                                              (1024, 1024, 1024, 2.0, 2.0)])
+def test_gemm_f32_three_tf32(m, n, k, alpha, beta):
+    """fp32 GEMM of the sgemm samples (samples/simple_sgemm.cpp, samples/perf_sgemm.cpp) against the reference's
+    fp32 gemm_CPU arithmetic.  The tolerance is far tighter than BASELINE's 1e-3 so that a plain TF32 product,
+    which keeps 10 mantissa bits, could not pass."""
+    a = G.uniform_np(G.SEED_A, (m, k), np.float32); b = G.uniform_np(G.SEED_B, (k, n), np.float32)
+    c = G.uniform_np(G.SEED_C, (m, n), np.float32)
+    bs = np.ascontiguousarray(b.T)
+    ws = torch.empty(api.gemm_f32_workspace_bytes(m, n, k), dtype=torch.uint8, device="cuda")
+    d = nan_filled((m, n), torch.float32)
+    api.gemm_f32(m, n, k, dev(a), dev(bs), dev(c) if beta else None, d, k, k, n, n, alpha, beta, ws)
+    assert_status_ok()
+    ref = oracle_gemm_rows(a, bs, c if beta else None, alpha, beta, np.float32, n, k)
+    bound = R.gemm_abs_bound(m, n, k, a, b, c if beta else np.zeros_like(c), alpha, beta)
+    assert gemm_rel_err(d.cpu().numpy(), ref, bound) <= TOL_F32X3
+
+
 _LOWP = {"bf16": torch.bfloat16, "e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
 
 
