@@ -202,6 +202,18 @@ int b200wmma_simple_hgemm(uint32_t m, uint32_t n, uint32_t k,
                           uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
                           float alpha, float beta, int out_type, void* stream);
 
+/* The same naive kernel with the types of sgemm_rocwmma_d (samples/simple_sgemm.cpp:81-139: fp32 fragments,
+ * computed as three TF32 mma.sync products per fp32 product) and dgemm_rocwmma_d (samples/simple_dgemm.cpp:81-139:
+ * fp64 fragments, DMMA).  A row major, B column major, C/D row major; m, n, k multiples of 16. */
+int b200wmma_simple_sgemm(uint32_t m, uint32_t n, uint32_t k,
+                          const float* a, const float* b, const float* c, float* d,
+                          uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                          float alpha, float beta, void* stream);
+int b200wmma_simple_dgemm(uint32_t m, uint32_t n, uint32_t k,
+                          const double* a, const double* b, const double* c, double* d,
+                          uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                          double alpha, double beta, void* stream);
+
 /* perf_hgemm's kernel source pattern (cooperative global reads, shared-memory double buffer,
  * fragment transforms; samples/perf_hgemm.cpp:515-711) compiled against this repository's
  * fragment headers: 128x128 macro tile, A column major, B row major, C/D row major fp16 -

@@ -41,6 +41,8 @@ SIGNATURES = {
     "b200wmma_gemm_i4_workspace_bytes": (sz, [u32, u32, u32]),
     "b200wmma_gemm_i4": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32, i32, i32,
                                    vp, sz, vp]),
+    "b200wmma_simple_sgemm": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32, f32, f32, vp]),
+    "b200wmma_simple_dgemm": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32, f64, f64, vp]),
     "b200wmma_simple_hgemm": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32, f32, f32,
                                         C.c_int, vp]),
     "b200wmma_perf_hgemm_fragment": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32,

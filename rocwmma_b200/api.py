@@ -152,6 +152,22 @@ def gemm_i4(m, n, k, a_packed, b_packed, c, d, lda_bytes, ldb_bytes, ldc, ldd, a
                                  _ptr(workspace), workspace.numel(), _stream()))
 
 
+def simple_sgemm(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta):
+    """sgemm_rocwmma_d (samples/simple_sgemm.cpp:81-139) on this repo's fragment headers."""
+    for t, nm in ((a, "a"), (b, "b"), (c, "c"), (d, "d")):
+        _need(t, torch.float32, nm)
+    check(lib().b200wmma_simple_sgemm(m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc, ldd, alpha, beta,
+                                      _stream()))
+
+
+def simple_dgemm(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta):
+    """dgemm_rocwmma_d (samples/simple_dgemm.cpp:81-139) on this repo's fragment headers."""
+    for t, nm in ((a, "a"), (b, "b"), (c, "c"), (d, "d")):
+        _need(t, torch.float64, nm)
+    check(lib().b200wmma_simple_dgemm(m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc, ldd, alpha, beta,
+                                      _stream()))
+
+
 def simple_hgemm(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta):
     """hgemm_rocwmma_d (samples/simple_hgemm.cpp:81-139) on this repo's fragment headers."""
     _need(a, torch.float16, "a"); _need(b, torch.float16, "b")

@@ -27,17 +27,19 @@ namespace b200wmma
         constexpr uint32_t SB_M = 16, SB_N = 16, SB_K = 16;
         constexpr uint32_t S_TBLOCK_X = 4 * Constants::AMDGCN_WAVE_SIZE, S_TBLOCK_Y = 4;
 
-        template <typename OutT>
-        ROCWMMA_KERNEL void simple_hgemm_kernel(uint32_t m, uint32_t n, uint32_t k, float16_t const* a,
-                                                float16_t const* b, OutT const* c, OutT* d, uint32_t lda,
-                                                uint32_t ldb, uint32_t ldc, uint32_t ldd, float32_t alpha,
-                                                float32_t beta)
+        // The same kernel body serves hgemm_rocwmma_d (InT = float16_t, CmpT = float32_t), sgemm_rocwmma_d
+        // (samples/simple_sgemm.cpp:81-139, all float32_t) and dgemm_rocwmma_d (samples/simple_dgemm.cpp:81-139,
+        // all float64_t): the three samples differ in their types only.
+        template <typename InT, typename OutT, typename CmpT>
+        ROCWMMA_KERNEL void simple_gemm_kernel(uint32_t m, uint32_t n, uint32_t k, InT const* a, InT const* b,
+                                               OutT const* c, OutT* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
+                                               uint32_t ldd, CmpT alpha, CmpT beta)
         {
-            fragment<matrix_a, SB_M, SB_N, SB_K, float16_t, row_major> fragA;
-            fragment<matrix_b, SB_M, SB_N, SB_K, float16_t, col_major> fragB;
-            fragment<accumulator, SB_M, SB_N, SB_K, OutT>              fragC; // layout given at run time
-            fragment<accumulator, SB_M, SB_N, SB_K, float32_t>         fragAcc;
-            fill_fragment(fragAcc, 0.0f);
+            fragment<matrix_a, SB_M, SB_N, SB_K, InT, row_major> fragA;
+            fragment<matrix_b, SB_M, SB_N, SB_K, InT, col_major> fragB;
+            fragment<accumulator, SB_M, SB_N, SB_K, OutT>        fragC; // layout given at run time
+            fragment<accumulator, SB_M, SB_N, SB_K, CmpT>        fragAcc;
+            fill_fragment(fragAcc, CmpT(0));
 
             // one output block per wave: wave grid position -> block position
             const uint32_t waveRow = (blockIdx.x * blockDim.x + threadIdx.x) / Constants::AMDGCN_WAVE_SIZE;
@@ -231,14 +233,55 @@ extern "C" int b200wmma_simple_hgemm(uint32_t m, uint32_t n, uint32_t k, const v
     auto       A = static_cast<const rocwmma::float16_t*>(a);
     auto       B = static_cast<const rocwmma::float16_t*>(b);
     if(out_type == B200WMMA_OUT_F16)
-        fragk::simple_hgemm_kernel<rocwmma::float16_t><<<grid, block, 0, as_stream(stream)>>>(
+        fragk::simple_gemm_kernel<rocwmma::float16_t, rocwmma::float16_t, float><<<grid, block, 0, as_stream(stream)>>>(
             m, n, k, A, B, static_cast<const rocwmma::float16_t*>(c), static_cast<rocwmma::float16_t*>(d), lda, ldb,
             ldc, ldd, alpha, beta);
     else
-        fragk::simple_hgemm_kernel<float><<<grid, block, 0, as_stream(stream)>>>(
+        fragk::simple_gemm_kernel<rocwmma::float16_t, float, float><<<grid, block, 0, as_stream(stream)>>>(
             m, n, k, A, B, static_cast<const float*>(c), static_cast<float*>(d), lda, ldb, ldc, ldd, alpha, beta);
     B200_CHECK_CUDA(cudaGetLastError());
     return B200WMMA_OK;
+}
+
+namespace
+{
+    // shared by the fp32 / fp64 forms of the naive sample
+    template <typename T>
+    int simple_gemm_same_type(const char* who, uint32_t m, uint32_t n, uint32_t k, const T* a, const T* b, const T* c, T* d,
+                              uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, T alpha, T beta, void* stream)
+    {
+        clear_error();
+        B200_REQUIRE(a && b && c && d, B200WMMA_ERR_INVALID_ARG, "%s: a, b, c, d must be non-null", who);
+        B200_REQUIRE(m && n && k, B200WMMA_ERR_INVALID_ARG, "%s: m, n, k must be non-zero", who);
+        // same size rule as the samples' host check (samples/simple_sgemm.cpp:144-149)
+        B200_REQUIRE(m % fragk::SB_M == 0 && n % fragk::SB_N == 0 && k % fragk::SB_K == 0, B200WMMA_ERR_UNSUPPORTED,
+                     "%s: m, n, k must be multiples of 16", who);
+        B200_REQUIRE(lda >= k && ldb >= k && ldc >= n && ldd >= n, B200WMMA_ERR_INVALID_ARG,
+                     "%s: leading dimension too small", who);
+        if(int e = require_sm100())
+            return e;
+        const dim3 block(fragk::S_TBLOCK_X, fragk::S_TBLOCK_Y);
+        const dim3 grid(ceil_div(m, fragk::SB_M * fragk::S_TBLOCK_X / rocwmma::Constants::AMDGCN_WAVE_SIZE),
+                        ceil_div(n, fragk::SB_N * fragk::S_TBLOCK_Y));
+        fragk::simple_gemm_kernel<T, T, T><<<grid, block, 0, as_stream(stream)>>>(m, n, k, a, b, c, d, lda, ldb, ldc, ldd,
+                                                                                 alpha, beta);
+        B200_CHECK_CUDA(cudaGetLastError());
+        return B200WMMA_OK;
+    }
+} // namespace
+
+extern "C" int b200wmma_simple_sgemm(uint32_t m, uint32_t n, uint32_t k, const float* a, const float* b, const float* c,
+                                     float* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, float alpha,
+                                     float beta, void* stream)
+{
+    return simple_gemm_same_type<float>("simple_sgemm", m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, stream);
+}
+
+extern "C" int b200wmma_simple_dgemm(uint32_t m, uint32_t n, uint32_t k, const double* a, const double* b, const double* c,
+                                     double* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, double alpha,
+                                     double beta, void* stream)
+{
+    return simple_gemm_same_type<double>("simple_dgemm", m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, stream);
 }
 
 extern "C" int b200wmma_perf_hgemm_fragment(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b,

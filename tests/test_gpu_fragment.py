@@ -198,6 +198,22 @@ def test_simple_hgemm_config1(out_np):
     assert gemm_rel_err(d.cpu().numpy(), ref, bound) <= (TOL_F32_OUT if out_np == np.float32 else TOL_F16_OUT)
 
 
+@pytest.mark.parametrize("np_t", [np.float32, np.float64], ids=["sgemm", "dgemm"])
+@pytest.mark.parametrize("m,n,k", [(64, 64, 16), (256, 384, 208), (1024, 512, 512)])
+def test_simple_sgemm_dgemm(np_t, m, n, k):
+    """The fp32 / fp64 forms of the naive fragment GEMM (samples/simple_sgemm.cpp, samples/simple_dgemm.cpp):
+    fp32 fragments multiply through three TF32 products, so they are held to 5e-6, far inside BASELINE's 1e-3."""
+    a = G.uniform_np(G.SEED_A, (m, k), np_t); b = G.uniform_np(G.SEED_B, (k, n), np_t); c = G.uniform_np(G.SEED_C, (m, n), np_t)
+    bs = np.ascontiguousarray(b.T)
+    d = nan_filled((m, n), torch.float32 if np_t == np.float32 else torch.float64)
+    fn = api.simple_sgemm if np_t == np.float32 else api.simple_dgemm
+    fn(m, n, k, dev(a), dev(bs), dev(c), d, k, k, n, n, 2.0, 2.0)
+    assert_status_ok()
+    ref = R.gemm(R.port(), m, n, k, a.ravel(), bs.ravel(), c.ravel(), 2.0, 2.0, np_t).reshape(m, n)
+    bound = R.gemm_abs_bound(m, n, k, a, b, c, 2.0, 2.0)
+    assert gemm_rel_err(d.cpu().numpy(), ref, bound) <= (5e-6 if np_t == np.float32 else TOL_F64_OUT)
+
+
 @pytest.mark.parametrize("m,n,k", [(128, 128, 16), (256, 384, 512), (1024, 1024, 1024)])
 def test_perf_hgemm_fragment_pipeline(m, n, k):
     """perf_hgemm's cooperative / double-buffered pipeline on the fragment API: A col-major, B row-major."""
