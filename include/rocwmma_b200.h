@@ -235,7 +235,10 @@ int b200wmma_perf_hgemm_fragment(uint32_t m, uint32_t n, uint32_t k,
  * output : batch x out_stride fp16, out_stride >= k + m(m-1)/2; columns past the packed
  *          triangle are written as zero.
  * The reference's fp32 scratch `acc` is not needed and has no parameter.
- * Requires m <= 32, k a multiple of 16 with k <= 256, k % 8 == 0 and out_stride % 8 == 0.
+ * Requires k a multiple of 16 and out_stride % 8 == 0.  m <= 32 with k <= 256 (the DLRM benchmark shapes)
+ * runs on kernels tuned for them; anything larger (the reference test sweep's m = 128 and m = k = 1024
+ * among them) on general block-tiled kernels, which need m_stride >= m rounded up to 16 (they read, and
+ * discard, the padding rows of the last 16-row block) and batch <= 65535.
  *
  * Backward replaces trilReconstruct + dlrmDotBwd (samples/simple_dlrm.cpp:290-331, :349-441,
  * launched :535-584; test/dlrm/device/dlrm_dot_bwd.hpp:35-172):

@@ -382,17 +382,31 @@ namespace b200wmma
             }
         }
 
+        // Shapes beyond the one-warp-per-sample kernels (m <= 32, k <= 256, packed rows of at most 2048 values)
+        // go to the block-tiled kernels of dlrm_general.cu.
+        static bool needs_general(uint32_t m, uint32_t k, uint32_t packed_stride)
+        {
+            return m > static_cast<uint32_t>(MAX_M) || k > static_cast<uint32_t>(MAX_K) || packed_stride > 2048u;
+        }
+
         static int check_common(const void* input, uint32_t m, uint32_t m_stride, uint32_t k,
-                                uint32_t batch)
+                                uint32_t batch, bool general)
         {
             B200_REQUIRE(input, B200WMMA_ERR_INVALID_ARG, "dlrm: input must be non-null");
             B200_REQUIRE(m >= 1 && batch >= 1 && k >= 1, B200WMMA_ERR_INVALID_ARG,
                          "dlrm: m, k, batch must be non-zero");
             B200_REQUIRE(m_stride >= m, B200WMMA_ERR_INVALID_ARG, "dlrm: m_stride must be >= m");
-            B200_REQUIRE(m <= MAX_M, B200WMMA_ERR_UNSUPPORTED,
-                         "dlrm: m = %u not supported (this kernel handles m <= %d)", m, MAX_M);
-            B200_REQUIRE(k % 16 == 0 && k <= MAX_K, B200WMMA_ERR_UNSUPPORTED,
-                         "dlrm: k = %u not supported (multiple of 16, <= %d)", k, MAX_K);
+            B200_REQUIRE(k % 16 == 0, B200WMMA_ERR_UNSUPPORTED, "dlrm: k = %u not supported (multiple of 16)", k);
+            B200_REQUIRE(general || (m <= MAX_M && k <= MAX_K), B200WMMA_ERR_UNSUPPORTED, "dlrm: internal dispatch error");
+            if(general)
+            {
+                // the block-tiled kernels read whole 16-row blocks and index the batch with a grid dimension
+                B200_REQUIRE(m_stride >= ((m + 15u) & ~15u), B200WMMA_ERR_UNSUPPORTED,
+                             "dlrm: beyond m = 32 / k = 256 the row stride must cover m rounded up to 16 (%u < %u)", m_stride,
+                             (m + 15u) & ~15u);
+                B200_REQUIRE(batch <= 65535u && m <= 65535u * 16u, B200WMMA_ERR_UNSUPPORTED,
+                             "dlrm: batch above 65535 is not supported beyond m = 32 / k = 256");
+            }
             B200_REQUIRE(static_cast<uint64_t>(batch) * m_stride < (1ull << 31), B200WMMA_ERR_UNSUPPORTED,
                          "dlrm: batch * m_stride must stay below 2^31 rows");
             B200_REQUIRE(aligned16(input), B200WMMA_ERR_ALIGNMENT, "dlrm: input must be 16-byte aligned");
@@ -427,7 +441,8 @@ extern "C" int b200wmma_dlrm_fwd(const void* input, void* output, uint32_t m, ui
     using namespace b200wmma;
     using namespace b200wmma::dlrm;
     clear_error();
-    if(int e = check_common(input, m, m_stride, k, batch))
+    const bool general = needs_general(m, k, out_stride);
+    if(int e = check_common(input, m, m_stride, k, batch, general))
         return e;
     B200_REQUIRE(output, B200WMMA_ERR_INVALID_ARG, "dlrm_fwd: output must be non-null");
     B200_REQUIRE(out_stride >= k + m * (m - 1) / 2, B200WMMA_ERR_INVALID_ARG,
@@ -435,9 +450,10 @@ extern "C" int b200wmma_dlrm_fwd(const void* input, void* output, uint32_t m, ui
                  k + m * (m - 1) / 2);
     B200_REQUIRE(out_stride % 8 == 0 && aligned16(output), B200WMMA_ERR_ALIGNMENT,
                  "dlrm_fwd: output rows must be 16-byte aligned (out_stride %% 8 == 0)");
-    B200_REQUIRE(out_stride <= 2048, B200WMMA_ERR_UNSUPPORTED, "dlrm_fwd: out_stride too large");
     if(int e = require_sm100())
         return e;
+    if(general)
+        return launch_dlrm_fwd_general(input, output, m, m_stride, k, batch, out_stride, as_stream(stream));
     unsigned* status = nullptr;
     if(int e = status_word_ptr(&status))
         return e;
@@ -469,7 +485,8 @@ extern "C" int b200wmma_dlrm_bwd(const void* input, const void* upstream, void* 
     using namespace b200wmma;
     using namespace b200wmma::dlrm;
     clear_error();
-    if(int e = check_common(input, m, m_stride, k, batch))
+    const bool general = needs_general(m, k, upstream_stride);
+    if(int e = check_common(input, m, m_stride, k, batch, general))
         return e;
     B200_REQUIRE(upstream && grad, B200WMMA_ERR_INVALID_ARG, "dlrm_bwd: upstream and grad must be non-null");
     B200_REQUIRE(upstream_stride >= k + m * (m - 1) / 2, B200WMMA_ERR_INVALID_ARG,
@@ -479,9 +496,11 @@ extern "C" int b200wmma_dlrm_bwd(const void* input, const void* upstream, void* 
                      && (!bottom_mlp_grad || aligned16(bottom_mlp_grad)),
                  B200WMMA_ERR_ALIGNMENT,
                  "dlrm_bwd: buffers must be 16-byte aligned and upstream_stride %% 8 == 0");
-    B200_REQUIRE(upstream_stride <= 2048, B200WMMA_ERR_UNSUPPORTED, "dlrm_bwd: upstream_stride too large");
     if(int e = require_sm100())
         return e;
+    if(general)
+        return launch_dlrm_bwd_general(input, upstream, grad, bottom_mlp_grad, m, m_stride, k, batch, upstream_stride,
+                                       fuse_mlp_into_row0, as_stream(stream));
     unsigned* status = nullptr;
     if(int e = status_word_ptr(&status))
         return e;

@@ -61,7 +61,7 @@ def test_no_cpu_fallback_in_product_sources():
     (lambda L: L.b200wmma_gemm_i4(64, 64, 64, 16, 16, None, 16, 32, 32, 64, 64, 1, 0, 16, 16, None), 1),
     (lambda L: L.b200wmma_ctx_create(None), 1),
 ], ids=["bad_layout_flag", "col_major_a_lda_lt_m", "zero_m", "null_c_with_beta", "lda_too_small",
-        "lda_not_16B", "f64_odd_k", "gemv_zero_m", "gemv_lda_small", "dlrm_m_gt_32", "dlrm_k_not_16",
+        "lda_not_16B", "f64_odd_k", "gemv_zero_m", "gemv_lda_small", "dlrm_rows_beyond_stride", "dlrm_k_not_16",
         "dlrm_out_stride_small", "dlrm_bwd_null_upstream", "sp24_k_not_32", "i4_workspace_small", "ctx_null"])
 def test_argument_checks(call, code):
     L = _lib.lib()

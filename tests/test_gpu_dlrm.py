@@ -125,6 +125,22 @@ def test_dlrm_vs_oracle(b, m, k, m_stride):
         check_bwd(grad, mlp, x, up, rg, rm, fuse)
 
 
+@pytest.mark.parametrize("b,m,k,m_stride", [(64, 128, 128, 128), (4, 1024, 1024, 1024), (9, 100, 48, 112), (6, 40, 512, 48),
+                                            (3, 27, 1024, 32), (5, 33, 16, 48)])
+def test_dlrm_beyond_one_warp_per_sample(b, m, k, m_stride):
+    """Sizes of the reference's own sweep (test/dlrm/test/dlrm_test_params.hpp:55-58: m = 128 / k = 128 and
+    m = k = 1024) plus ragged ones: m > 32 or k > 256 run on the block-tiled kernels."""
+    x = G.normal_np(G.SEED_X, (b, m, k), 0.25, np.float16)
+    w = k + m * (m - 1) // 2
+    stride = (w + 7) // 8 * 8 + 8
+    up = G.normal_np(G.SEED_G, (b, w), 0.1, np.float16)
+    check_fwd(run_fwd(x, m_stride, stride), x, R.dlrm_fwd(R.port(), x, m, k, b))
+    rg, rm = R.dlrm_bwd(R.port(), x, up, m, k, b)
+    for fuse, want_mlp in ((False, True), (True, False)):
+        grad, mlp = run_bwd(x, up, m_stride, stride, fuse, want_mlp)
+        check_bwd(grad, mlp, x, up, rg, rm, fuse)
+
+
 def test_dlrm_full_size_config():
     """B=16384, F=27 padded to 32 rows, D=128, output width 480: sampled rows vs the oracle plus whole-batch
     properties (pass-through exact everywhere; Z symmetric => fwd(x) on a row-permuted sample permutes pairs)."""
