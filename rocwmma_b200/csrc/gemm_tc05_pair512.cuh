@@ -40,7 +40,8 @@ namespace b200wmma
         constexpr uint32_t GROUP_M       = 8; // rasterisation band: 8 pair-row tiles = 4096 rows
         constexpr uint32_t EPI_BUF_BYTES = 2048; // 32 rows x 64 bytes, TMA SWIZZLE_64B
         constexpr uint32_t EPI_BYTES     = EPI_WARPS * 2 * EPI_BUF_BYTES; // two staging tiles per epilogue warp
-        constexpr uint32_t MISC_BYTES    = 512; // barriers, tensor-memory slot, abort flag
+        constexpr uint32_t EPI_STAGE     = STAGES - 1; // operand stage whose A region doubles as two more staging tiles per warp
+        constexpr uint32_t MISC_BYTES    = 512; // barriers, tensor-memory slot, abort flag, epilogue counter
         constexpr uint32_t SMEM_BYTES    = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + MISC_BYTES;
 
         // Epilogue of one warp through shared-memory staging tiles.
@@ -166,6 +167,138 @@ namespace b200wmma
             }
         };
 
+        // The same epilogue with a ring of FOUR staging tiles per warp: two dedicated ones (buf0 ..) and two that
+        // alias an operand stage (alias0 ..), so that C tiles are requested three steps before they are needed
+        // and no step waits for the store it has just issued.  Buffers 0 / 1 may be filled before the tile's
+        // accumulators are complete (prefetch_early); buffers 2 / 3 only afterwards (prefetch_late), because until
+        // then the tensor cores may still be reading the operand stage they share memory with.
+        template <typename OutT, typename ScalarT, uint32_t TN = TILE_N>
+        struct StagedDrain4
+        {
+            static constexpr uint32_t NB        = 4;
+            static constexpr uint32_t STEP_COLS = 64 / sizeof(OutT);
+            static constexpr uint32_t STEPS     = TN / STEP_COLS;
+
+            __device__ static __forceinline__ uint32_t buf_addr(uint32_t i, uint32_t buf0, uint32_t alias0)
+            {
+                return i < 2u ? buf0 + i * EPI_BUF_BYTES : alias0 + (i - 2u) * EPI_BUF_BYTES;
+            }
+            __device__ static __forceinline__ void request_c(const CUtensorMap* tmap_c, uint32_t dst, uint32_t bar,
+                                                            uint32_t col, uint32_t row0)
+            {
+                ptx::mbar_arrive_expect_tx(bar, EPI_BUF_BYTES);
+                ptx::tma_load_2d(dst, tmap_c, static_cast<int32_t>(col), static_cast<int32_t>(row0), bar);
+            }
+            __device__ static __forceinline__ void prefetch_early(const CUtensorMap* tmap_c, uint32_t buf0, uint32_t cbar0,
+                                                                 uint32_t col_base, uint32_t row0, uint32_t n)
+            {
+                ptx::bulk_wait_group_read<0>(); // the previous tile's stores have read every buffer
+#pragma unroll
+                for(uint32_t s = 0; s < 2; ++s)
+                    if(col_base + s * STEP_COLS < n)
+                        request_c(tmap_c, buf0 + s * EPI_BUF_BYTES, cbar0 + 8 * s, col_base + s * STEP_COLS, row0);
+            }
+            __device__ static __forceinline__ void prefetch_late(const CUtensorMap* tmap_c, uint32_t alias0, uint32_t cbar0,
+                                                                uint32_t col_base, uint32_t row0, uint32_t n)
+            {
+#pragma unroll
+                for(uint32_t s = 2; s < NB; ++s)
+                    if(s < STEPS && col_base + s * STEP_COLS < n)
+                        request_c(tmap_c, alias0 + (s - 2u) * EPI_BUF_BYTES, cbar0 + 8 * s, col_base + s * STEP_COLS, row0);
+            }
+
+            __device__ static __forceinline__ bool run(uint32_t tmem_acc, uint32_t quad, uint32_t lane, uint8_t* smem,
+                                                       uint32_t buf_off, uint32_t buf0, uint32_t alias_off, uint32_t alias0,
+                                                       uint32_t cbar0, const CUtensorMap* tmap_c, const CUtensorMap* tmap_d,
+                                                       uint32_t col_base, uint32_t row0, uint32_t n, ScalarT alpha,
+                                                       ScalarT beta, bool read_c, uint32_t& cpar,
+                                                       volatile uint32_t* cta_abort, unsigned* status, uint32_t who)
+            {
+                // cpar: bit b = parity of the next completed C load into staging buffer b (kept across tiles)
+                const uint32_t row_sw = (lane >> 1) & 3u; // 64-byte swizzle phase of this lane's row
+#pragma unroll 2
+                for(uint32_t s = 0; s < STEPS; ++s)
+                {
+                    const uint32_t bi = s & (NB - 1u);
+                    uint32_t       v[STEP_COLS];
+                    if constexpr(STEP_COLS == 32)
+                        ptx::tmem_ld_32x32b_x32(tmem_acc + ((quad * 32u) << 16) + s * STEP_COLS, v);
+                    else
+                        ptx::tmem_ld_32x32b_x16(tmem_acc + ((quad * 32u) << 16) + s * STEP_COLS, v);
+                    if(col_base + s * STEP_COLS >= n)
+                    {
+                        ptx::tmem_ld_wait(); // right of the matrix (ragged N): nothing to load, combine or store
+                        continue;
+                    }
+                    if(read_c)
+                    {
+                        bool ok = ptx::mbar_wait_bounded(cbar0 + 8 * bi, (cpar >> bi) & 1u, cta_abort, status, who,
+                                                         WAIT_TIMEOUT_NS);
+                        if(!__all_sync(0xFFFFFFFFu, ok))
+                        {
+                            ptx::tmem_ld_wait();
+                            return false;
+                        }
+                        cpar ^= 1u << bi;
+                    }
+                    else
+                    {
+                        if(lane == 0)
+                            ptx::bulk_wait_group_read<NB - 1>(); // the store issued four steps ago has read this buffer
+                        __syncwarp();
+                    }
+                    ptx::tmem_ld_wait();
+                    const uint32_t off  = bi < 2u ? buf_off + bi * EPI_BUF_BYTES : alias_off + (bi - 2u) * EPI_BUF_BYTES;
+                    uint8_t*       rowp = smem + off + lane * 64u;
+#pragma unroll
+                    for(uint32_t q = 0; q < 4; ++q)
+                    {
+                        uint4* cell = reinterpret_cast<uint4*>(rowp + ((q ^ row_sw) << 4));
+                        uint4  cv   = make_uint4(0, 0, 0, 0);
+                        if(read_c)
+                            cv = *cell;
+                        const uint32_t cwv[4] = {cv.x, cv.y, cv.z, cv.w};
+                        uint32_t       ow[4];
+#pragma unroll
+                        for(uint32_t w = 0; w < 4; ++w)
+                        {
+                            if constexpr(sizeof(OutT) == 2)
+                            {
+                                const float2  cf = __half22float2(*reinterpret_cast<const __half2*>(&cwv[w]));
+                                const __half2 h  = __floats2half2_rn(
+                                    epi(__uint_as_float(v[8 * q + 2 * w]), cf.x, alpha, beta),
+                                    epi(__uint_as_float(v[8 * q + 2 * w + 1]), cf.y, alpha, beta));
+                                ow[w] = *reinterpret_cast<const uint32_t*>(&h);
+                            }
+                            else if constexpr(std::is_same<OutT, float>::value)
+                                ow[w] = __float_as_uint(epi(__uint_as_float(v[4 * q + w]), __uint_as_float(cwv[w]), alpha, beta));
+                            else
+                                ow[w] = static_cast<uint32_t>(
+                                    epi(static_cast<int32_t>(v[4 * q + w]), static_cast<int32_t>(cwv[w]), alpha, beta));
+                        }
+                        *cell = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+                    }
+                    ptx::fence_proxy_async_smem(); // the tile written above -> visible to the TMA store
+                    __syncwarp();
+                    if(lane == 0)
+                    {
+                        ptx::tma_store_2d(tmap_d, static_cast<int32_t>(col_base + s * STEP_COLS), static_cast<int32_t>(row0),
+                                          buf_addr(bi, buf0, alias0));
+                        ptx::bulk_commit_group();
+                        // refill the buffer of the PREVIOUS step: its store has had a whole step to read it
+                        const uint32_t nxt = s + NB - 1u;
+                        if(read_c && s >= 1u && nxt < STEPS && col_base + nxt * STEP_COLS < n)
+                        {
+                            ptx::bulk_wait_group_read<1>();
+                            const uint32_t pb = (s - 1u) & (NB - 1u);
+                            request_c(tmap_c, buf_addr(pb, buf0, alias0), cbar0 + 8 * pb, col_base + nxt * STEP_COLS, row0);
+                        }
+                    }
+                }
+                return true;
+            }
+        };
+
         // A_MN / B_MN: the operand is MN-major (column-major A / row-major B) instead of K-major.
         template <int KIND, typename OutT, typename ScalarT, bool A_MN = false, bool B_MN = false>
         __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -203,9 +336,12 @@ namespace b200wmma
             const uint32_t     empty_bar  = bar_base + 32;
             const uint32_t     tfull_bar  = bar_base + 64;
             const uint32_t     tempty_bar = bar_base + 72; // 2 x 8, one per accumulator (leader's copy in use)
-            const uint32_t     cbar_base  = bar_base + 96; // EPI_WARPS x 2 x 8: C tiles of the epilogue warps
-            uint32_t*          tmem_slot  = reinterpret_cast<uint32_t*>(smem + misc_off + 96 + EPI_WARPS * 16);
+            const uint32_t     cbar_base  = bar_base + 96; // EPI_WARPS x 4 x 8: C tiles of the epilogue warps
+            uint32_t*          tmem_slot  = reinterpret_cast<uint32_t*>(smem + misc_off + 96 + EPI_WARPS * 32);
             volatile uint32_t* cta_abort  = tmem_slot + 1;
+            uint32_t*          epi_count  = tmem_slot + 2; // epilogue warps x tiles whose aliased staging tiles are free again
+            // the A region of the last stage holds two more staging tiles per epilogue warp while a tile is drained
+            const uint32_t     alias_base_off = EPI_STAGE * A_STAGE_BYTES;
 
             const uint32_t warp      = threadIdx.x >> 5;
             const uint32_t lane      = threadIdx.x & 31u;
@@ -217,6 +353,7 @@ namespace b200wmma
 
             if(threadIdx.x == 0)
             {
+                *epi_count = 0u;
                 ptx::prefetch_tensormap(&tmap_a);
                 ptx::prefetch_tensormap(&tmap_b);
                 ptx::prefetch_tensormap(&tmap_c);
@@ -229,7 +366,7 @@ namespace b200wmma
                 ptx::mbar_init(tfull_bar, 1);
                 ptx::mbar_init(tempty_bar, 8); // accumulator 0: 4 warps x 2 CTAs
                 ptx::mbar_init(tempty_bar + 8, 8); // accumulator 1
-                for(uint32_t i = 0; i < EPI_WARPS * 2; ++i)
+                for(uint32_t i = 0; i < EPI_WARPS * 4; ++i)
                     ptx::mbar_init(cbar_base + 8 * i, 1);
                 *cta_abort = 0u;
                 ptx::fence_barrier_init();
@@ -250,9 +387,9 @@ namespace b200wmma
                 // ------------------------------ TMA producer (both CTAs) ------------------------------
                 if(lane == 0)
                 {
-                    uint32_t stage = 0, phase = 0;
+                    uint32_t stage = 0, phase = 0, iter = 0;
                     bool     ok = true;
-                    for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs)
+                    for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++iter)
                     {
                         uint32_t m_idx, n_idx;
                         tile_coords(tile, tiles_m, tiles_n, group_m, m_idx, n_idx);
@@ -264,6 +401,35 @@ namespace b200wmma
                                                         (ROLE_PRODUCER << 24) | blockIdx.x, WAIT_TIMEOUT_NS);
                             if(!ok)
                                 break;
+                            if(stage == EPI_STAGE && iter != 0u)
+                            {
+                                // this stage's A region doubles as staging tiles of the epilogue: every epilogue
+                                // warp must have finished with them for all earlier tiles (bounded wait)
+                                const uint64_t t0 = ptx::globaltimer_ns();
+                                uint32_t       spins = 0;
+                                while(ptx::ld_acquire_shared_u32(epi_count) < EPI_WARPS * iter)
+                                {
+                                    if((++spins & 0xFFu) == 0u)
+                                    {
+                                        if(*cta_abort)
+                                        {
+                                            ok = false;
+                                            break;
+                                        }
+                                        if(ptx::globaltimer_ns() - t0 > WAIT_TIMEOUT_NS)
+                                        {
+                                            *cta_abort = 1u;
+                                            if(atomicCAS(status, 0u, ptx::STATUS_TIMEOUT_CODE) == 0u)
+                                                status[1] = (ROLE_PRODUCER << 24) | (2u << 20) | blockIdx.x;
+                                            ok = false;
+                                            break;
+                                        }
+                                    }
+                                }
+                                if(!ok)
+                                    break;
+                                ptx::fence_proxy_async_smem(); // generic writes of the staging tiles before the TMA overwrite
+                            }
                             if(rank == 0)
                                 ptx::mbar_arrive_expect_tx(full_bar + 8 * stage, 2u * STAGE_BYTES);
                             const uint32_t leader_full = ptx::mapa(full_bar + 8 * stage, 0u);
@@ -375,10 +541,12 @@ namespace b200wmma
                 const uint32_t quad   = warp & 3u; // lane quadrant this warp may read
                 const uint32_t j      = e >> 2; // accumulator: warps 2-5 -> 0, warps 6-9 -> 1
                 const bool     read_c = (beta != ScalarT(0)) && (c != nullptr);
-                const uint32_t buf_off = epi_off + e * 2u * EPI_BUF_BYTES;
-                const uint32_t buf0    = base + buf_off;
-                const uint32_t cbar0   = cbar_base + e * 16u;
-                using Drain            = StagedDrain<OutT, ScalarT>;
+                const uint32_t buf_off   = epi_off + e * 2u * EPI_BUF_BYTES;
+                const uint32_t buf0      = base + buf_off;
+                const uint32_t alias_off = alias_base_off + e * 2u * EPI_BUF_BYTES;
+                const uint32_t alias0    = base + alias_off;
+                const uint32_t cbar0     = cbar_base + e * 32u;
+                using Drain              = StagedDrain4<OutT, ScalarT>;
                 uint32_t iter = 0, cpar = 0;
                 bool     ok   = true;
                 for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++iter)
@@ -392,16 +560,19 @@ namespace b200wmma
                     const bool staged = vec_ok != 0 && row0 < m && col_base < n;
                     // C does not depend on the accumulators: request its first two steps now
                     if(staged && read_c && lane == 0)
-                        Drain::prefetch_c(&tmap_c, buf0, cbar0, col_base, row0, n);
+                        Drain::prefetch_early(&tmap_c, buf0, cbar0, col_base, row0, n);
                     ok = ptx::mbar_wait_bounded_warp(tfull_bar, iter & 1u, cta_abort, status,
                                                      (ROLE_EPILOGUE << 24) | blockIdx.x, WAIT_TIMEOUT_NS, lane);
                     if(!ok)
                         break;
                     ptx::tc_fence_after_sync();
+                    // every MMA of the tile has retired: the aliased staging tiles may be written now
+                    if(staged && read_c && lane == 0)
+                        Drain::prefetch_late(&tmap_c, alias0, cbar0, col_base, row0, n);
                     const uint32_t tmem_acc = tmem_base + j * TILE_N;
                     if(staged)
-                        ok = Drain::run(tmem_acc, quad, lane, smem, buf_off, buf0, cbar0, &tmap_c, &tmap_d, col_base, row0, n,
-                                        alpha, beta, read_c, cpar, cta_abort, status,
+                        ok = Drain::run(tmem_acc, quad, lane, smem, buf_off, buf0, alias_off, alias0, cbar0, &tmap_c, &tmap_d,
+                                        col_base, row0, n, alpha, beta, read_c, cpar, cta_abort, status,
                                         (ROLE_EPILOGUE << 24) | (1u << 20) | blockIdx.x);
                     else if(vec_ok == 0)
                         drain_accumulator<OutT, ScalarT, TILE_N>(tmem_acc, quad, lane, row_base, col_base, m, n, c, d, ldc,
@@ -410,7 +581,12 @@ namespace b200wmma
                     ptx::tc_fence_before_sync();
                     __syncwarp();
                     if(lane == 0)
+                    {
                         ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar + 8 * j, 0u));
+                        // hand the aliased staging tiles back to the producer once this warp's stores have read them
+                        ptx::bulk_wait_group_read<0>();
+                        ptx::red_release_shared_add_u32(epi_count, 1u);
+                    }
                 }
                 if(lane == 0)
                     ptx::bulk_wait_group<0>(); // the staging tiles must outlive the stores that read them
