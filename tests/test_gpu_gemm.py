@@ -330,6 +330,36 @@ def test_gemm_f64(m, n, k):
     assert gemm_rel_err(d.cpu().numpy(), ref, bound) <= TOL_F64_OUT
 
 
+@pytest.mark.parametrize("k", [64, 128, 320])
+def test_gemm_many_tiles_per_sm_pair_short_k(k):
+    """More output tiles than SM pairs with only 1-5 K slabs per tile: the persistent kernels walk their operand
+    ring across tile boundaries while the epilogue of the previous tile still owns part of it (staging tiles that
+    alias an operand stage)."""
+    m, n = 4096, 4608
+    a = G.uniform_np(1, (m, k), np.float16); b = G.uniform_np(2, (k, n), np.float16); c = G.uniform_np(3, (m, n), np.float16)
+    bs = np.ascontiguousarray(b.T)
+    d = nan_filled((m, n), torch.float16)
+    api.gemm_f16(m, n, k, dev(a), dev(bs), dev(c), d, k, k, n, n, 1.0, 1.0)
+    assert_status_ok()
+    ref = oracle_gemm_rows(a, bs, c, 1.0, 1.0, np.float16, n, k)
+    assert gemm_rel_err(d.cpu().numpy(), ref, R.gemm_abs_bound(m, n, k, a, b, c, 1.0, 1.0)) <= TOL_F16_OUT
+    # int8 dense and 2:4 sparse (sparse needs k % 128 == 0)
+    ai = G.int8_np(1, (m, k)); bi = np.ascontiguousarray(G.int8_np(2, (k, n)).T)
+    ci = G.int8_np(3, (m, n)).astype(np.int32) * 321
+    di = nan_filled((m, n), torch.int32)
+    api.gemm_i8(m, n, k, dev(ai), dev(bi), dev(ci), di, k, k, n, n, 2, 1)
+    assert np.array_equal(di.cpu().numpy(), oracle_gemm_rows(ai, bi, ci, 2, 1, np.int32, n, k))
+    if k % 128 == 0:
+        vals, meta, densified = G.sparsify_24_np(ai)
+        ws = torch.empty(api.gemm_i8_sp24_workspace_bytes(m, n, k), dtype=torch.uint8, device="cuda")
+        ds = nan_filled((m, n), torch.int32)
+        for w in (ws, None):
+            ds.fill_(-1)
+            api.gemm_i8_sp24(m, n, k, dev(vals), dev(meta), dev(bi), dev(ci), ds, k // 2, k // 8, k, n, n, 2, 1, w)
+            assert np.array_equal(ds.cpu().numpy(), oracle_gemm_rows(densified, bi, ci, 2, 1, np.int32, n, k))
+    assert_status_ok()
+
+
 def _rows_sample(m, count, seed):
     rows = (G.raw_np(seed, count) % np.uint64(m)).astype(np.int64)
     rows[0], rows[-1] = 0, m - 1
