@@ -60,6 +60,27 @@ namespace rocwmma
     ROCWMMA_B200_COORD_OP(/)
     ROCWMMA_B200_COORD_OP(%)
 #undef ROCWMMA_B200_COORD_OP
+    // compound forms (the reference's vector type has them: matrixCoord *= make_coord2d(BlocksX, BlocksY),
+    // test/gemm/gemm_PGR0_LB0_MP0_MB_NC/device/kernel_device_func.hpp:110)
+#define ROCWMMA_B200_COORD_ASSIGN_OP(OP)                                                        \
+    ROCWMMA_HOST_DEVICE constexpr inline Coord2d& operator OP##=(Coord2d& a, Coord2d const& b) \
+    {                                                                                          \
+        a.v[0] OP## = b.v[0];                                                                  \
+        a.v[1] OP## = b.v[1];                                                                  \
+        return a;                                                                              \
+    }                                                                                          \
+    ROCWMMA_HOST_DEVICE constexpr inline Coord2d& operator OP##=(Coord2d& a, uint32_t s)       \
+    {                                                                                          \
+        a.v[0] OP## = s;                                                                       \
+        a.v[1] OP## = s;                                                                       \
+        return a;                                                                              \
+    }
+    ROCWMMA_B200_COORD_ASSIGN_OP(+)
+    ROCWMMA_B200_COORD_ASSIGN_OP(-)
+    ROCWMMA_B200_COORD_ASSIGN_OP(*)
+    ROCWMMA_B200_COORD_ASSIGN_OP(/)
+    ROCWMMA_B200_COORD_ASSIGN_OP(%)
+#undef ROCWMMA_B200_COORD_ASSIGN_OP
     ROCWMMA_HOST_DEVICE constexpr inline bool operator==(Coord2d const& a, Coord2d const& b)
     {
         return a.v[0] == b.v[0] && a.v[1] == b.v[1];

@@ -1,0 +1,70 @@
+"""rocWMMA's own test GEMM kernels (test/gemm/gemm_PGR0_LB0_MP0_{SB,MB}_NC/device/kernel_device_func.hpp),
+compiled unmodified against this repository's <rocwmma/rocwmma.hpp> (tests/csrc/ref_kernel_unit.cu, built by
+__graft_entry__.build() where the reference tree exists), run on the GPU and checked against the oracle.
+This is the header drop-in claim exercised on the reference's own source: fragment, fill_fragment,
+load / store_matrix_sync, mma_sync, synchronize_workgroup, MappingUtil and the Coord2d arithmetic."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import TOL_F16_OUT, TOL_F32_OUT, TOL_F64_OUT, gemm_rel_err
+from gpu_util import dev, nan_filled
+from oracle import cpu_ref as R
+from rocwmma_b200 import datagen as G
+
+pytestmark = pytest.mark.gpu
+LIB = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libref_kernel_unit.so")
+
+# variant -> (input dtype, output dtype, layout A, layout B, tolerance or None for exact)
+VARIANTS = {
+    0: (np.float16, np.float32, 0, 1, TOL_F32_OUT),
+    1: (np.float16, np.float16, 1, 0, TOL_F16_OUT),
+    2: (np.float32, np.float32, 0, 1, 5e-6),
+    3: (np.float64, np.float64, 0, 1, TOL_F64_OUT),
+    4: (np.int8, np.int32, 0, 1, None),
+    5: (np.float16, np.float32, 0, 1, TOL_F32_OUT),
+}
+
+
+def _lib():
+    if not os.path.exists(LIB):
+        pytest.skip("tests/libref_kernel_unit.so is built only where the reference tree is present")
+    lib = C.CDLL(LIB)
+    lib.ref_test_gemm.restype = C.c_int
+    lib.ref_test_gemm.argtypes = [C.c_int, C.c_int, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p,
+                                  C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_double, C.c_double]
+    return lib
+
+
+@pytest.mark.parametrize("multi", [0, 1], ids=["single_block", "multi_block"])
+@pytest.mark.parametrize("variant", sorted(VARIANTS))
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (512, 384, 208)])
+def test_reference_test_kernels_on_these_headers(variant, multi, m, n, k):
+    lib = _lib()
+    in_t, out_t, la, lb, tol = VARIANTS[variant]
+    if in_t == np.int8:
+        a, b = G.int8_np(1, (m, k)), G.int8_np(2, (k, n))
+        c = G.int8_np(3, (m, n)).astype(np.int32) * 100
+        alpha, beta = 2, -1
+    else:
+        a, b, c = G.uniform_np(1, (m, k), in_t), G.uniform_np(2, (k, n), in_t), G.uniform_np(3, (m, n), out_t)
+        alpha, beta = 2.0, 0.5
+    store = lambda x, col: np.ascontiguousarray(x.T if col else x)
+    sa, sb = store(a, la), store(b, lb)
+    lda, ldb = (m if la else k), (k if lb else n)
+    d = nan_filled((m, n), {np.float32: torch.float32, np.float16: torch.float16, np.float64: torch.float64,
+                            np.int32: torch.int32}[out_t])
+    da, db, dc = dev(sa), dev(sb), dev(c)
+    rc = lib.ref_test_gemm(variant, multi, m, n, k, da.data_ptr(), db.data_ptr(), dc.data_ptr(), d.data_ptr(), lda, ldb, n, n,
+                           float(alpha), float(beta))
+    torch.cuda.synchronize()
+    assert rc == 0
+    ref = R.gemm(R.port(), m, n, k, sa.ravel(), sb.ravel(), c.ravel(), alpha, beta, out_t, la, lb, 0, 0).reshape(m, n)
+    got = d.cpu().numpy()
+    if tol is None:
+        assert np.array_equal(got, ref)
+    else:
+        assert gemm_rel_err(got, ref, R.gemm_abs_bound(m, n, k, a, b, c, alpha, beta)) <= tol
