@@ -6,14 +6,16 @@
 // quarter less L2 -> SM traffic and fewer DRAM re-reads per flop.  On a power-capped part that is
 // clock speed.  The price: the two 128 x 256 fp32 accumulators fill all 512 tensor-memory columns,
 // so the accumulators are not double-buffered and the epilogue has to be short.  It is made short
-// by (a) eight epilogue warps (one lane quadrant of one accumulator each), (b) moving C and D
-// through small swizzled shared-memory tiles with TMA - a thread-per-row global access touches 32
-// different cache lines per warp instruction, which costs ~32 LSU cycles each and dominated the
-// drain - with the first C steps requested while the tile is still being multiplied, and
-// (c) releasing each accumulator to the MMA issuer separately.
+// by (a) sixteen epilogue warps - two per lane quadrant of each accumulator, taking alternate 64-byte column
+// steps, (b) moving C and D through small swizzled shared-memory tiles with TMA - a thread-per-row global
+// access touches 32 different cache lines per warp instruction, which costs ~32 LSU cycles each and dominated
+// the drain - and (c) releasing each accumulator to the MMA issuer separately.  Every warp has two staging
+// tiles: a dedicated one, whose C tile is requested while the tile is still being multiplied, and one inside the
+// A region of the last operand stage, which the producer refills only after a counter says every epilogue warp
+// has finished with the tile (bounded wait).
 //
-// Roles (320 threads): warp 0 TMA producer (one lane), warp 1 tensor-memory owner / MMA issuer
-// (one lane, leader CTA only), warps 2-9 epilogue.  Barrier protocol as in gemm_tc05_pair.cuh
+// Roles (576 threads): warp 0 TMA producer (one lane), warp 1 tensor-memory owner / MMA issuer
+// (one lane, leader CTA only), warps 2-17 epilogue.  Barrier protocol as in gemm_tc05_pair.cuh
 // (loads of both CTAs counted on the leader's full[s]; commits signal both CTAs), with one
 // tmem_full barrier per tile and one tmem_empty barrier per accumulator.
 #pragma once
@@ -34,13 +36,13 @@ namespace b200wmma
         constexpr uint32_t A_STAGE_BYTES = CTA_M * BLOCK_K_BYTES; // 32 KiB
         constexpr uint32_t B_STAGE_BYTES = HALF_N * BLOCK_K_BYTES; // 16 KiB
         constexpr uint32_t STAGE_BYTES   = A_STAGE_BYTES + B_STAGE_BYTES;
-        constexpr uint32_t EPI_WARPS     = 8;
+        constexpr uint32_t EPI_WARPS     = 16; // two per TMEM lane quadrant of each accumulator (alternate 64-byte column steps)
         constexpr uint32_t NUM_THREADS   = 64 + EPI_WARPS * 32;
         constexpr uint32_t TMEM_COLS     = 512;
         constexpr uint32_t GROUP_M       = 8; // rasterisation band: 8 pair-row tiles = 4096 rows
         constexpr uint32_t EPI_BUF_BYTES = 2048; // 32 rows x 64 bytes, TMA SWIZZLE_64B
-        constexpr uint32_t EPI_BYTES     = EPI_WARPS * 2 * EPI_BUF_BYTES; // two staging tiles per epilogue warp
-        constexpr uint32_t EPI_STAGE     = STAGES - 1; // operand stage whose A region doubles as two more staging tiles per warp
+        constexpr uint32_t EPI_BYTES     = EPI_WARPS * EPI_BUF_BYTES; // dedicated staging tiles: the first of each epilogue warp's two
+        constexpr uint32_t EPI_STAGE     = STAGES - 1; // operand stage whose A region holds every epilogue warp's second staging tile
         constexpr uint32_t MISC_BYTES    = 512; // barriers, tensor-memory slot, abort flag, epilogue counter
         constexpr uint32_t SMEM_BYTES    = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + MISC_BYTES;
 
@@ -52,26 +54,35 @@ namespace b200wmma
         // tile to a TMA store and request the C tile two steps ahead into the same buffer once the
         // store has read it.  TMA clips rows / columns outside the matrix, so ragged edges need no
         // special case.  All 32 lanes execute every step.
-        // TN: columns of the accumulator being drained.
-        template <typename OutT, typename ScalarT, uint32_t TN = TILE_N>
+        // TN: columns of the accumulator being drained.  STRIDE > 1 lets several warps share one lane quadrant of an
+        // accumulator: warp `first` (0 .. STRIDE-1) takes the steps first, first + STRIDE, ...
+        template <typename OutT, typename ScalarT, uint32_t TN = TILE_N, uint32_t STRIDE = 1>
         struct StagedDrain
         {
             static constexpr uint32_t STEP_COLS = 64 / sizeof(OutT);
-            static constexpr uint32_t STEPS     = TN / STEP_COLS;
+            static constexpr uint32_t STEPS     = TN / STEP_COLS; // of the whole accumulator
+            static constexpr uint32_t MY_STEPS  = STEPS / STRIDE; // of one warp
+            static_assert(STEPS % STRIDE == 0, "steps must divide evenly among the warps of a quadrant");
 
             // requests the C tiles of steps 0 and 1 (called while the tile is still being multiplied)
+            // ls_begin / ls_end: which of the warp's first two steps to request (both by default); buf1: address of the
+            // second staging tile when it does not follow the first one
             __device__ static __forceinline__ void prefetch_c(const CUtensorMap* tmap_c, uint32_t buf0, uint32_t cbar0,
-                                                             uint32_t col_base, uint32_t row0, uint32_t n)
+                                                             uint32_t col_base, uint32_t row0, uint32_t n, uint32_t first = 0,
+                                                             uint32_t ls_begin = 0, uint32_t ls_end = 2, uint32_t buf1 = 0)
             {
+                if(buf1 == 0u)
+                    buf1 = buf0 + EPI_BUF_BYTES;
                 ptx::bulk_wait_group_read<0>(); // the previous tile's last stores have read both buffers
 #pragma unroll
-                for(uint32_t s = 0; s < 2; ++s)
+                for(uint32_t ls = ls_begin; ls < ls_end && ls < MY_STEPS; ++ls)
                 {
+                    const uint32_t s = first + ls * STRIDE;
                     if(col_base + s * STEP_COLS >= n)
                         break; // steps that start right of the matrix are skipped everywhere
-                    ptx::mbar_arrive_expect_tx(cbar0 + 8 * s, EPI_BUF_BYTES);
-                    ptx::tma_load_2d(buf0 + s * EPI_BUF_BYTES, tmap_c, static_cast<int32_t>(col_base + s * STEP_COLS),
-                                     static_cast<int32_t>(row0), cbar0 + 8 * s);
+                    ptx::mbar_arrive_expect_tx(cbar0 + 8 * ls, EPI_BUF_BYTES);
+                    ptx::tma_load_2d(ls == 0u ? buf0 : buf1, tmap_c, static_cast<int32_t>(col_base + s * STEP_COLS),
+                                     static_cast<int32_t>(row0), cbar0 + 8 * ls);
                 }
             }
 
@@ -80,14 +91,21 @@ namespace b200wmma
                                                        const CUtensorMap* tmap_c, const CUtensorMap* tmap_d,
                                                        uint32_t col_base, uint32_t row0, uint32_t n, ScalarT alpha,
                                                        ScalarT beta, bool read_c, uint32_t& cpar,
-                                                       volatile uint32_t* cta_abort, unsigned* status, uint32_t who)
+                                                       volatile uint32_t* cta_abort, unsigned* status, uint32_t who,
+                                                       uint32_t first = 0, uint32_t buf1_off = 0, uint32_t buf1 = 0)
             {
+                if(buf1 == 0u)
+                {
+                    buf1_off = buf_off + EPI_BUF_BYTES;
+                    buf1     = buf0 + EPI_BUF_BYTES;
+                }
                 // cpar: bit b = parity of the next completed C load into staging buffer b (kept across tiles)
                 const uint32_t row_sw = (lane >> 1) & 3u; // 64-byte swizzle phase of this lane's row
 #pragma unroll 2
-                for(uint32_t s = 0; s < STEPS; ++s)
+                for(uint32_t ls = 0; ls < MY_STEPS; ++ls)
                 {
-                    const uint32_t bi = s & 1u;
+                    const uint32_t s  = first + ls * STRIDE;
+                    const uint32_t bi = ls & 1u;
                     uint32_t       v[STEP_COLS];
                     if constexpr(STEP_COLS == 32)
                         ptx::tmem_ld_32x32b_x32(tmem_acc + ((quad * 32u) << 16) + s * STEP_COLS, v);
@@ -117,7 +135,7 @@ namespace b200wmma
                         __syncwarp();
                     }
                     ptx::tmem_ld_wait();
-                    uint8_t* rowp = smem + buf_off + bi * EPI_BUF_BYTES + lane * 64u;
+                    uint8_t* rowp = smem + (bi == 0u ? buf_off : buf1_off) + lane * 64u;
 #pragma unroll
                     for(uint32_t q = 0; q < 4; ++q)
                     {
@@ -151,147 +169,15 @@ namespace b200wmma
                     if(lane == 0)
                     {
                         ptx::tma_store_2d(tmap_d, static_cast<int32_t>(col_base + s * STEP_COLS), static_cast<int32_t>(row0),
-                                          buf0 + bi * EPI_BUF_BYTES);
+                                          bi == 0u ? buf0 : buf1);
                         ptx::bulk_commit_group();
-                        if(read_c && s + 2 < STEPS && col_base + (s + 2) * STEP_COLS < n)
+                        if(read_c && ls + 2 < MY_STEPS && col_base + (s + 2 * STRIDE) * STEP_COLS < n)
                         {
                             ptx::bulk_wait_group_read<0>(); // the store has read the buffer: refill it with C
                             ptx::mbar_arrive_expect_tx(cbar0 + 8 * bi, EPI_BUF_BYTES);
-                            ptx::tma_load_2d(buf0 + bi * EPI_BUF_BYTES, tmap_c,
-                                             static_cast<int32_t>(col_base + (s + 2) * STEP_COLS), static_cast<int32_t>(row0),
-                                             cbar0 + 8 * bi);
-                        }
-                    }
-                }
-                return true;
-            }
-        };
-
-        // The same epilogue with a ring of FOUR staging tiles per warp: two dedicated ones (buf0 ..) and two that
-        // alias an operand stage (alias0 ..), so that C tiles are requested three steps before they are needed
-        // and no step waits for the store it has just issued.  Buffers 0 / 1 may be filled before the tile's
-        // accumulators are complete (prefetch_early); buffers 2 / 3 only afterwards (prefetch_late), because until
-        // then the tensor cores may still be reading the operand stage they share memory with.
-        template <typename OutT, typename ScalarT, uint32_t TN = TILE_N>
-        struct StagedDrain4
-        {
-            static constexpr uint32_t NB        = 4;
-            static constexpr uint32_t STEP_COLS = 64 / sizeof(OutT);
-            static constexpr uint32_t STEPS     = TN / STEP_COLS;
-
-            __device__ static __forceinline__ uint32_t buf_addr(uint32_t i, uint32_t buf0, uint32_t alias0)
-            {
-                return i < 2u ? buf0 + i * EPI_BUF_BYTES : alias0 + (i - 2u) * EPI_BUF_BYTES;
-            }
-            __device__ static __forceinline__ void request_c(const CUtensorMap* tmap_c, uint32_t dst, uint32_t bar,
-                                                            uint32_t col, uint32_t row0)
-            {
-                ptx::mbar_arrive_expect_tx(bar, EPI_BUF_BYTES);
-                ptx::tma_load_2d(dst, tmap_c, static_cast<int32_t>(col), static_cast<int32_t>(row0), bar);
-            }
-            __device__ static __forceinline__ void prefetch_early(const CUtensorMap* tmap_c, uint32_t buf0, uint32_t cbar0,
-                                                                 uint32_t col_base, uint32_t row0, uint32_t n)
-            {
-                ptx::bulk_wait_group_read<0>(); // the previous tile's stores have read every buffer
-#pragma unroll
-                for(uint32_t s = 0; s < 2; ++s)
-                    if(col_base + s * STEP_COLS < n)
-                        request_c(tmap_c, buf0 + s * EPI_BUF_BYTES, cbar0 + 8 * s, col_base + s * STEP_COLS, row0);
-            }
-            __device__ static __forceinline__ void prefetch_late(const CUtensorMap* tmap_c, uint32_t alias0, uint32_t cbar0,
-                                                                uint32_t col_base, uint32_t row0, uint32_t n)
-            {
-#pragma unroll
-                for(uint32_t s = 2; s < NB; ++s)
-                    if(s < STEPS && col_base + s * STEP_COLS < n)
-                        request_c(tmap_c, alias0 + (s - 2u) * EPI_BUF_BYTES, cbar0 + 8 * s, col_base + s * STEP_COLS, row0);
-            }
-
-            __device__ static __forceinline__ bool run(uint32_t tmem_acc, uint32_t quad, uint32_t lane, uint8_t* smem,
-                                                       uint32_t buf_off, uint32_t buf0, uint32_t alias_off, uint32_t alias0,
-                                                       uint32_t cbar0, const CUtensorMap* tmap_c, const CUtensorMap* tmap_d,
-                                                       uint32_t col_base, uint32_t row0, uint32_t n, ScalarT alpha,
-                                                       ScalarT beta, bool read_c, uint32_t& cpar,
-                                                       volatile uint32_t* cta_abort, unsigned* status, uint32_t who)
-            {
-                // cpar: bit b = parity of the next completed C load into staging buffer b (kept across tiles)
-                const uint32_t row_sw = (lane >> 1) & 3u; // 64-byte swizzle phase of this lane's row
-#pragma unroll 2
-                for(uint32_t s = 0; s < STEPS; ++s)
-                {
-                    const uint32_t bi = s & (NB - 1u);
-                    uint32_t       v[STEP_COLS];
-                    if constexpr(STEP_COLS == 32)
-                        ptx::tmem_ld_32x32b_x32(tmem_acc + ((quad * 32u) << 16) + s * STEP_COLS, v);
-                    else
-                        ptx::tmem_ld_32x32b_x16(tmem_acc + ((quad * 32u) << 16) + s * STEP_COLS, v);
-                    if(col_base + s * STEP_COLS >= n)
-                    {
-                        ptx::tmem_ld_wait(); // right of the matrix (ragged N): nothing to load, combine or store
-                        continue;
-                    }
-                    if(read_c)
-                    {
-                        bool ok = ptx::mbar_wait_bounded(cbar0 + 8 * bi, (cpar >> bi) & 1u, cta_abort, status, who,
-                                                         WAIT_TIMEOUT_NS);
-                        if(!__all_sync(0xFFFFFFFFu, ok))
-                        {
-                            ptx::tmem_ld_wait();
-                            return false;
-                        }
-                        cpar ^= 1u << bi;
-                    }
-                    else
-                    {
-                        if(lane == 0)
-                            ptx::bulk_wait_group_read<NB - 1>(); // the store issued four steps ago has read this buffer
-                        __syncwarp();
-                    }
-                    ptx::tmem_ld_wait();
-                    const uint32_t off  = bi < 2u ? buf_off + bi * EPI_BUF_BYTES : alias_off + (bi - 2u) * EPI_BUF_BYTES;
-                    uint8_t*       rowp = smem + off + lane * 64u;
-#pragma unroll
-                    for(uint32_t q = 0; q < 4; ++q)
-                    {
-                        uint4* cell = reinterpret_cast<uint4*>(rowp + ((q ^ row_sw) << 4));
-                        uint4  cv   = make_uint4(0, 0, 0, 0);
-                        if(read_c)
-                            cv = *cell;
-                        const uint32_t cwv[4] = {cv.x, cv.y, cv.z, cv.w};
-                        uint32_t       ow[4];
-#pragma unroll
-                        for(uint32_t w = 0; w < 4; ++w)
-                        {
-                            if constexpr(sizeof(OutT) == 2)
-                            {
-                                const float2  cf = __half22float2(*reinterpret_cast<const __half2*>(&cwv[w]));
-                                const __half2 h  = __floats2half2_rn(
-                                    epi(__uint_as_float(v[8 * q + 2 * w]), cf.x, alpha, beta),
-                                    epi(__uint_as_float(v[8 * q + 2 * w + 1]), cf.y, alpha, beta));
-                                ow[w] = *reinterpret_cast<const uint32_t*>(&h);
-                            }
-                            else if constexpr(std::is_same<OutT, float>::value)
-                                ow[w] = __float_as_uint(epi(__uint_as_float(v[4 * q + w]), __uint_as_float(cwv[w]), alpha, beta));
-                            else
-                                ow[w] = static_cast<uint32_t>(
-                                    epi(static_cast<int32_t>(v[4 * q + w]), static_cast<int32_t>(cwv[w]), alpha, beta));
-                        }
-                        *cell = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-                    }
-                    ptx::fence_proxy_async_smem(); // the tile written above -> visible to the TMA store
-                    __syncwarp();
-                    if(lane == 0)
-                    {
-                        ptx::tma_store_2d(tmap_d, static_cast<int32_t>(col_base + s * STEP_COLS), static_cast<int32_t>(row0),
-                                          buf_addr(bi, buf0, alias0));
-                        ptx::bulk_commit_group();
-                        // refill the buffer of the PREVIOUS step: its store has had a whole step to read it
-                        const uint32_t nxt = s + NB - 1u;
-                        if(read_c && s >= 1u && nxt < STEPS && col_base + nxt * STEP_COLS < n)
-                        {
-                            ptx::bulk_wait_group_read<1>();
-                            const uint32_t pb = (s - 1u) & (NB - 1u);
-                            request_c(tmap_c, buf_addr(pb, buf0, alias0), cbar0 + 8 * pb, col_base + nxt * STEP_COLS, row0);
+                            ptx::tma_load_2d(bi == 0u ? buf0 : buf1, tmap_c,
+                                             static_cast<int32_t>(col_base + (s + 2 * STRIDE) * STEP_COLS),
+                                             static_cast<int32_t>(row0), cbar0 + 8 * bi);
                         }
                     }
                 }
@@ -336,11 +222,11 @@ namespace b200wmma
             const uint32_t     empty_bar  = bar_base + 32;
             const uint32_t     tfull_bar  = bar_base + 64;
             const uint32_t     tempty_bar = bar_base + 72; // 2 x 8, one per accumulator (leader's copy in use)
-            const uint32_t     cbar_base  = bar_base + 96; // EPI_WARPS x 4 x 8: C tiles of the epilogue warps
-            uint32_t*          tmem_slot  = reinterpret_cast<uint32_t*>(smem + misc_off + 96 + EPI_WARPS * 32);
+            const uint32_t     cbar_base  = bar_base + 96; // EPI_WARPS x 2 x 8: C tiles of the epilogue warps
+            uint32_t*          tmem_slot  = reinterpret_cast<uint32_t*>(smem + misc_off + 96 + EPI_WARPS * 16);
             volatile uint32_t* cta_abort  = tmem_slot + 1;
             uint32_t*          epi_count  = tmem_slot + 2; // epilogue warps x tiles whose aliased staging tiles are free again
-            // the A region of the last stage holds two more staging tiles per epilogue warp while a tile is drained
+            // the A region of the last stage holds the second staging tile of every epilogue warp while a tile is drained
             const uint32_t     alias_base_off = EPI_STAGE * A_STAGE_BYTES;
 
             const uint32_t warp      = threadIdx.x >> 5;
@@ -364,9 +250,9 @@ namespace b200wmma
                     ptx::mbar_init(empty_bar + 8 * s, 1);
                 }
                 ptx::mbar_init(tfull_bar, 1);
-                ptx::mbar_init(tempty_bar, 8); // accumulator 0: 4 warps x 2 CTAs
-                ptx::mbar_init(tempty_bar + 8, 8); // accumulator 1
-                for(uint32_t i = 0; i < EPI_WARPS * 4; ++i)
+                ptx::mbar_init(tempty_bar, 16); // accumulator 0: 8 warps x 2 CTAs
+                ptx::mbar_init(tempty_bar + 8, 16); // accumulator 1
+                for(uint32_t i = 0; i < EPI_WARPS * 2; ++i)
                     ptx::mbar_init(cbar_base + 8 * i, 1);
                 *cta_abort = 0u;
                 ptx::fence_barrier_init();
@@ -537,16 +423,17 @@ namespace b200wmma
             else
             {
                 // -------------------------------- epilogue (both CTAs) --------------------------------
-                const uint32_t e      = warp - 2u; // 0..7
+                const uint32_t e      = warp - 2u; // 0..15
                 const uint32_t quad   = warp & 3u; // lane quadrant this warp may read
-                const uint32_t j      = e >> 2; // accumulator: warps 2-5 -> 0, warps 6-9 -> 1
+                const uint32_t j      = (e >> 2) & 1u; // accumulator: warps 2-5, 10-13 -> 0; warps 6-9, 14-17 -> 1
+                const uint32_t first  = e >> 3; // 0: even 64-byte column steps, 1: odd steps
                 const bool     read_c = (beta != ScalarT(0)) && (c != nullptr);
-                const uint32_t buf_off   = epi_off + e * 2u * EPI_BUF_BYTES;
-                const uint32_t buf0      = base + buf_off;
-                const uint32_t alias_off = alias_base_off + e * 2u * EPI_BUF_BYTES;
-                const uint32_t alias0    = base + alias_off;
-                const uint32_t cbar0     = cbar_base + e * 32u;
-                using Drain              = StagedDrain4<OutT, ScalarT>;
+                const uint32_t buf_off  = epi_off + e * EPI_BUF_BYTES; // first tile: dedicated
+                const uint32_t buf0     = base + buf_off;
+                const uint32_t buf1_off = alias_base_off + e * EPI_BUF_BYTES; // second tile: inside the last operand stage
+                const uint32_t buf1     = base + buf1_off;
+                const uint32_t cbar0   = cbar_base + e * 16u;
+                using Drain            = StagedDrain<OutT, ScalarT, TILE_N, 2>;
                 uint32_t iter = 0, cpar = 0;
                 bool     ok   = true;
                 for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++iter)
@@ -559,8 +446,9 @@ namespace b200wmma
                     // staged path: needs 16-byte aligned rows (TMA) and a tile that starts inside the matrix
                     const bool staged = vec_ok != 0 && row0 < m && col_base < n;
                     // C does not depend on the accumulators: request its first two steps now
+                    // C does not depend on the accumulators: the tile of the warp's first step is requested now
                     if(staged && read_c && lane == 0)
-                        Drain::prefetch_early(&tmap_c, buf0, cbar0, col_base, row0, n);
+                        Drain::prefetch_c(&tmap_c, buf0, cbar0, col_base, row0, n, first, 0, 1, buf1);
                     ok = ptx::mbar_wait_bounded_warp(tfull_bar, iter & 1u, cta_abort, status,
                                                      (ROLE_EPILOGUE << 24) | blockIdx.x, WAIT_TIMEOUT_NS, lane);
                     if(!ok)
@@ -568,13 +456,13 @@ namespace b200wmma
                     ptx::tc_fence_after_sync();
                     // every MMA of the tile has retired: the aliased staging tiles may be written now
                     if(staged && read_c && lane == 0)
-                        Drain::prefetch_late(&tmap_c, alias0, cbar0, col_base, row0, n);
+                        Drain::prefetch_c(&tmap_c, buf0, cbar0, col_base, row0, n, first, 1, 2, buf1);
                     const uint32_t tmem_acc = tmem_base + j * TILE_N;
                     if(staged)
-                        ok = Drain::run(tmem_acc, quad, lane, smem, buf_off, buf0, alias_off, alias0, cbar0, &tmap_c, &tmap_d,
-                                        col_base, row0, n, alpha, beta, read_c, cpar, cta_abort, status,
-                                        (ROLE_EPILOGUE << 24) | (1u << 20) | blockIdx.x);
-                    else if(vec_ok == 0)
+                        ok = Drain::run(tmem_acc, quad, lane, smem, buf_off, buf0, cbar0, &tmap_c, &tmap_d, col_base, row0, n,
+                                        alpha, beta, read_c, cpar, cta_abort, status,
+                                        (ROLE_EPILOGUE << 24) | (1u << 20) | blockIdx.x, first, buf1_off, buf1);
+                    else if(vec_ok == 0 && first == 0u)
                         drain_accumulator<OutT, ScalarT, TILE_N>(tmem_acc, quad, lane, row_base, col_base, m, n, c, d, ldc,
                                                                  ldd, alpha, beta, read_c, 0);
                     // (an aligned tile that lies wholly outside the matrix has nothing to store)
