@@ -16,6 +16,9 @@ BIN = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), 
     ("perf_hgemm", ["1536", "1024", "768", "2", "2", "nt"]),  # the reference sample's own layouts
     ("perf_sgemm", ["1024", "1536", "512", "2", "0.5"]),      # fp32 GEMM sample (3 x TF32)
     ("simple_hgemm", ["256", "512", "128"]),
+    ("simple_sgemm", ["256", "512", "128"]),
+    ("simple_dgemm", ["256", "384", "128"]),
+    ("perf_dgemm", ["1024", "768", "512", "2", "0.5"]),
     ("simple_dlrm", ["27", "128", "2048"]),
     ("simple_sgemv", ["2048", "4096"]),
     ("simple_dgemv", ["1024", "4096"]),
