@@ -255,6 +255,13 @@ int b200wmma_dlrm_fwd(const void* input, void* output,
 int b200wmma_dlrm_bwd(const void* input, const void* upstream, void* grad, void* bottom_mlp_grad,
                       uint32_t m, uint32_t m_stride, uint32_t k, uint32_t batch,
                       uint32_t upstream_stride, int fuse_mlp_into_row0, void* stream);
+/* fp32 data (the reference sweep's other data type): same contracts with 4-byte elements; always the general
+ * block-tiled kernels (m_stride >= m rounded up to 16, batch <= 65535, k a multiple of 16). */
+int b200wmma_dlrm_fwd_f32(const float* input, float* output, uint32_t m, uint32_t m_stride, uint32_t k,
+                          uint32_t batch, uint32_t out_stride, void* stream);
+int b200wmma_dlrm_bwd_f32(const float* input, const float* upstream, float* grad, float* bottom_mlp_grad,
+                          uint32_t m, uint32_t m_stride, uint32_t k, uint32_t batch, uint32_t upstream_stride,
+                          int fuse_mlp_into_row0, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * GEMV: y = alpha * A x + beta * y  (in place on y), A is m x n.

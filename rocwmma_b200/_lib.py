@@ -49,6 +49,8 @@ SIGNATURES = {
                                                f32, f32, vp]),
     "b200wmma_dlrm_fwd": (C.c_int, [vp, vp, u32, u32, u32, u32, u32, vp]),
     "b200wmma_dlrm_bwd": (C.c_int, [vp, vp, vp, vp, u32, u32, u32, u32, u32, C.c_int, vp]),
+    "b200wmma_dlrm_fwd_f32": (C.c_int, [vp, vp, u32, u32, u32, u32, u32, vp]),
+    "b200wmma_dlrm_bwd_f32": (C.c_int, [vp, vp, vp, vp, u32, u32, u32, u32, u32, C.c_int, vp]),
     "b200wmma_gemv_f32": (C.c_int, [u32, u32, vp, u32, C.c_int, vp, vp, f32, f32, vp]),
     "b200wmma_gemv_f64": (C.c_int, [u32, u32, vp, u32, C.c_int, vp, vp, f64, f64, vp]),
     "b200wmma_ctx_create": (C.c_int, [C.POINTER(vp)]),

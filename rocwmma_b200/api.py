@@ -185,18 +185,27 @@ def perf_hgemm_fragment(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta):
 
 
 def dlrm_dot_fwd(input, output, m, m_stride, k, batch, out_stride):
-    _need(input, torch.float16, "input"); _need(output, torch.float16, "output")
-    check(lib().b200wmma_dlrm_fwd(_ptr(input), _ptr(output), m, m_stride, k, batch, out_stride, _stream()))
+    """fp16 or fp32 data (by input.dtype)."""
+    dt = input.dtype
+    if dt not in (torch.float16, torch.float32):
+        raise TypeError("input must be float16 or float32")
+    _need(input, dt, "input"); _need(output, dt, "output")
+    fn = lib().b200wmma_dlrm_fwd if dt == torch.float16 else lib().b200wmma_dlrm_fwd_f32
+    check(fn(_ptr(input), _ptr(output), m, m_stride, k, batch, out_stride, _stream()))
 
 
 def dlrm_dot_bwd(input, upstream, grad, bottom_mlp_grad, m, m_stride, k, batch, upstream_stride,
                  fuse_mlp_into_row0=False):
-    _need(input, torch.float16, "input"); _need(upstream, torch.float16, "upstream")
-    _need(grad, torch.float16, "grad")
+    dt = input.dtype
+    if dt not in (torch.float16, torch.float32):
+        raise TypeError("input must be float16 or float32")
+    _need(input, dt, "input"); _need(upstream, dt, "upstream")
+    _need(grad, dt, "grad")
     if bottom_mlp_grad is not None:
-        _need(bottom_mlp_grad, torch.float16, "bottom_mlp_grad")
-    check(lib().b200wmma_dlrm_bwd(_ptr(input), _ptr(upstream), _ptr(grad), _ptr(bottom_mlp_grad),
-                                  m, m_stride, k, batch, upstream_stride, int(fuse_mlp_into_row0), _stream()))
+        _need(bottom_mlp_grad, dt, "bottom_mlp_grad")
+    fn = lib().b200wmma_dlrm_bwd if dt == torch.float16 else lib().b200wmma_dlrm_bwd_f32
+    check(fn(_ptr(input), _ptr(upstream), _ptr(grad), _ptr(bottom_mlp_grad),
+             m, m_stride, k, batch, upstream_stride, int(fuse_mlp_into_row0), _stream()))
 
 
 def gemv(m, n, a, lda, x, y, alpha, beta, layout_a=ROW_MAJOR):

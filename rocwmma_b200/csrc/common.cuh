@@ -87,9 +87,9 @@ namespace b200wmma
                             cudaStream_t stream);
     // DLRM dot interaction for shapes beyond the one-warp-per-sample kernels (dlrm_general.cu)
     int launch_dlrm_fwd_general(const void* input, void* output, uint32_t m, uint32_t m_stride, uint32_t k, uint32_t batch,
-                                uint32_t out_stride, cudaStream_t stream);
+                                uint32_t out_stride, bool f32, cudaStream_t stream);
     int launch_dlrm_bwd_general(const void* input, const void* upstream, void* grad, void* bottom_mlp_grad, uint32_t m,
-                                uint32_t m_stride, uint32_t k, uint32_t batch, uint32_t upstream_stride, int fuse,
+                                uint32_t m_stride, uint32_t k, uint32_t batch, uint32_t upstream_stride, int fuse, bool f32,
                                 cudaStream_t stream);
     // 2:4-sparse int8 GEMM on compressed A (values + metadata) without a densified copy.
     // sp24_direct_ok() tells whether the operands meet its shape / alignment rules.

@@ -453,7 +453,7 @@ extern "C" int b200wmma_dlrm_fwd(const void* input, void* output, uint32_t m, ui
     if(int e = require_sm100())
         return e;
     if(general)
-        return launch_dlrm_fwd_general(input, output, m, m_stride, k, batch, out_stride, as_stream(stream));
+        return launch_dlrm_fwd_general(input, output, m, m_stride, k, batch, out_stride, false, as_stream(stream));
     unsigned* status = nullptr;
     if(int e = status_word_ptr(&status))
         return e;
@@ -500,7 +500,7 @@ extern "C" int b200wmma_dlrm_bwd(const void* input, const void* upstream, void* 
         return e;
     if(general)
         return launch_dlrm_bwd_general(input, upstream, grad, bottom_mlp_grad, m, m_stride, k, batch, upstream_stride,
-                                       fuse_mlp_into_row0, as_stream(stream));
+                                       fuse_mlp_into_row0, false, as_stream(stream));
     unsigned* status = nullptr;
     if(int e = status_word_ptr(&status))
         return e;
@@ -528,4 +528,41 @@ extern "C" int b200wmma_dlrm_bwd(const void* input, const void* upstream, void* 
         upstream_stride, fuse_mlp_into_row0, status);
     B200_CHECK_CUDA(cudaGetLastError());
     return B200WMMA_OK;
+}
+
+// fp32 data (the second data type of the reference's DLRM sweep, test/dlrm/test/dlrm_test_params.hpp:51): always on the
+// block-tiled kernels of dlrm_general.cu.
+extern "C" int b200wmma_dlrm_fwd_f32(const float* input, float* output, uint32_t m, uint32_t m_stride, uint32_t k,
+                                     uint32_t batch, uint32_t out_stride, void* stream)
+{
+    using namespace b200wmma;
+    using namespace b200wmma::dlrm;
+    clear_error();
+    if(int e = check_common(input, m, m_stride, k, batch, true))
+        return e;
+    B200_REQUIRE(output, B200WMMA_ERR_INVALID_ARG, "dlrm_fwd_f32: output must be non-null");
+    B200_REQUIRE(out_stride >= k + m * (m - 1) / 2, B200WMMA_ERR_INVALID_ARG,
+                 "dlrm_fwd_f32: out_stride %u smaller than k + m(m-1)/2 = %u", out_stride, k + m * (m - 1) / 2);
+    if(int e = require_sm100())
+        return e;
+    return launch_dlrm_fwd_general(input, output, m, m_stride, k, batch, out_stride, true, as_stream(stream));
+}
+
+extern "C" int b200wmma_dlrm_bwd_f32(const float* input, const float* upstream, float* grad, float* bottom_mlp_grad, uint32_t m,
+                                     uint32_t m_stride, uint32_t k, uint32_t batch, uint32_t upstream_stride,
+                                     int fuse_mlp_into_row0, void* stream)
+{
+    using namespace b200wmma;
+    using namespace b200wmma::dlrm;
+    clear_error();
+    if(int e = check_common(input, m, m_stride, k, batch, true))
+        return e;
+    B200_REQUIRE(upstream && grad, B200WMMA_ERR_INVALID_ARG, "dlrm_bwd_f32: upstream and grad must be non-null");
+    B200_REQUIRE(upstream_stride >= k + m * (m - 1) / 2, B200WMMA_ERR_INVALID_ARG,
+                 "dlrm_bwd_f32: upstream_stride %u smaller than k + m(m-1)/2 = %u", upstream_stride, k + m * (m - 1) / 2);
+    B200_REQUIRE(aligned16(grad), B200WMMA_ERR_ALIGNMENT, "dlrm_bwd_f32: grad must be 16-byte aligned");
+    if(int e = require_sm100())
+        return e;
+    return launch_dlrm_bwd_general(input, upstream, grad, bottom_mlp_grad, m, m_stride, k, batch, upstream_stride,
+                                   fuse_mlp_into_row0, true, as_stream(stream));
 }

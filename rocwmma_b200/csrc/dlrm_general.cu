@@ -29,16 +29,19 @@ namespace b200wmma
             return i * (i - 1) / 2 + j;
         }
 
+        // DataT: float16_t, or float32_t (the reference sweep's second data type; fp32 fragments multiply through
+        // three TF32 products)
+        template <typename DataT>
         __global__ void __launch_bounds__(THREADS)
-            dlrm_fwd_general_kernel(const float16_t* __restrict__ x, float16_t* __restrict__ out, uint32_t m, uint32_t m_stride,
+            dlrm_fwd_general_kernel(const DataT* __restrict__ x, DataT* __restrict__ out, uint32_t m, uint32_t m_stride,
                                     uint32_t k, uint32_t out_stride, uint32_t nblk, uint32_t npairs)
         {
             __shared__ float tile[WARPS][T * T];
             const uint32_t   warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
             const uint32_t   b    = blockIdx.y;
             const uint32_t   p    = blockIdx.x * WARPS + warp; // index of the (bi, bj <= bi) block pair
-            const float16_t* xb   = x + static_cast<size_t>(b) * m_stride * k;
-            float16_t*       ob   = out + static_cast<size_t>(b) * out_stride;
+            const DataT*     xb   = x + static_cast<size_t>(b) * m_stride * k;
+            DataT*           ob   = out + static_cast<size_t>(b) * out_stride;
             if(p >= npairs)
                 return;
             // p = bi (bi + 1) / 2 + bj
@@ -50,12 +53,12 @@ namespace b200wmma
             const uint32_t bj = p - bi * (bi + 1) / 2;
             (void)nblk;
 
-            fragment<matrix_a, T, T, T, float16_t, row_major> fa;
-            fragment<matrix_b, T, T, T, float16_t, col_major> fb; // B = X^T: B[h][j] = X[j][h], K contiguous
-            fragment<accumulator, T, T, T, float32_t>         acc;
+            fragment<matrix_a, T, T, T, DataT, row_major> fa;
+            fragment<matrix_b, T, T, T, DataT, col_major> fb; // B = X^T: B[h][j] = X[j][h], K contiguous
+            fragment<accumulator, T, T, T, float32_t>     acc;
             fill_fragment(acc, 0.0f);
-            const float16_t* arow = xb + static_cast<size_t>(bi) * T * k;
-            const float16_t* brow = xb + static_cast<size_t>(bj) * T * k;
+            const DataT* arow = xb + static_cast<size_t>(bi) * T * k;
+            const DataT* brow = xb + static_cast<size_t>(bj) * T * k;
             for(uint32_t h = 0; h < k; h += T)
             {
                 load_matrix_sync(fa, arow + h, k);
@@ -68,7 +71,7 @@ namespace b200wmma
             {
                 const uint32_t i = bi * T + e / T, j = bj * T + e % T;
                 if(i < m && j < i)
-                    ob[k + tri(i, j)] = static_cast<float16_t>(tile[warp][e]);
+                    ob[k + tri(i, j)] = static_cast<DataT>(tile[warp][e]);
             }
             if(p == 0)
             {
@@ -76,29 +79,30 @@ namespace b200wmma
                 for(uint32_t h = lane; h < k; h += 32)
                     ob[h] = xb[h];
                 for(uint32_t h = k + m * (m - 1) / 2 + lane; h < out_stride; h += 32)
-                    ob[h] = static_cast<float16_t>(0.0f);
+                    ob[h] = static_cast<DataT>(0.0f);
             }
         }
 
+        template <typename DataT>
         __global__ void __launch_bounds__(THREADS)
-            dlrm_bwd_general_kernel(const float16_t* __restrict__ x, const float16_t* __restrict__ up,
-                                    float16_t* __restrict__ grad, float16_t* __restrict__ mlp, uint32_t m, uint32_t m_stride,
-                                    uint32_t k, uint32_t up_stride, int fuse)
+            dlrm_bwd_general_kernel(const DataT* __restrict__ x, const DataT* __restrict__ up, DataT* __restrict__ grad,
+                                    DataT* __restrict__ mlp, uint32_t m, uint32_t m_stride, uint32_t k, uint32_t up_stride,
+                                    int fuse)
         {
-            __shared__ __align__(16) float16_t tblk[T * T];
+            __shared__ __align__(16) DataT tblk[T * T];
             __shared__ float                   tile[WARPS][T * T];
             const uint32_t   warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
             const uint32_t   b    = blockIdx.z;
             const uint32_t   bi   = blockIdx.y; // 16 rows of grad
             const uint32_t   kc   = (blockIdx.x * WARPS + warp) * T; // this warp's 16 columns of k
             const bool       live = kc < k; // warps right of the matrix still help to build T and keep the barriers
-            const float16_t* xb   = x + static_cast<size_t>(b) * m_stride * k;
-            const float16_t* ub   = up + static_cast<size_t>(b) * up_stride;
-            float16_t*       gb   = grad + static_cast<size_t>(b) * m_stride * k;
+            const DataT*     xb   = x + static_cast<size_t>(b) * m_stride * k;
+            const DataT*     ub   = up + static_cast<size_t>(b) * up_stride;
+            DataT*           gb   = grad + static_cast<size_t>(b) * m_stride * k;
             const uint32_t   nblk = (m + T - 1) / T;
 
-            fragment<matrix_a, T, T, T, float16_t, row_major> fa;
-            fragment<matrix_b, T, T, T, float16_t, row_major> fb; // B[j][h] = X[j][h], N contiguous
+            fragment<matrix_a, T, T, T, DataT, row_major> fa;
+            fragment<matrix_b, T, T, T, DataT, row_major> fb; // B[j][h] = X[j][h], N contiguous
             fragment<accumulator, T, T, T, float32_t>         acc;
             fill_fragment(acc, 0.0f);
             for(uint32_t jb = 0; jb < nblk; ++jb)
@@ -107,7 +111,7 @@ namespace b200wmma
                 {
                     const uint32_t e = threadIdx.x;
                     const uint32_t i = bi * T + e / T, j = jb * T + e % T;
-                    float16_t      v = static_cast<float16_t>(0.0f);
+                    DataT          v = static_cast<DataT>(0.0f);
                     if(i < m && j < m && i != j)
                         v = ub[k + (i > j ? tri(i, j) : tri(j, i))];
                     tblk[e] = v;
@@ -132,8 +136,8 @@ namespace b200wmma
                 {
                     float v = tile[warp][e];
                     if(fuse && i == 0)
-                        v = static_cast<float>(static_cast<float16_t>(v)) + static_cast<float>(ub[h]);
-                    gb[static_cast<size_t>(i) * k + h] = static_cast<float16_t>(v);
+                        v = static_cast<float>(static_cast<DataT>(v)) + static_cast<float>(ub[h]);
+                    gb[static_cast<size_t>(i) * k + h] = static_cast<DataT>(v);
                 }
             }
             if(bi == 0 && mlp != nullptr && lane < T)
@@ -142,22 +146,27 @@ namespace b200wmma
     } // namespace dlrmg
 
     int launch_dlrm_fwd_general(const void* input, void* output, uint32_t m, uint32_t m_stride, uint32_t k, uint32_t batch,
-                                uint32_t out_stride, cudaStream_t stream)
+                                uint32_t out_stride, bool f32, cudaStream_t stream)
     {
         using namespace dlrmg;
         const uint32_t nblk = ceil_div(m, T), npairs = nblk * (nblk + 1) / 2;
         B200_REQUIRE(k % T == 0, B200WMMA_ERR_UNSUPPORTED, "dlrm_fwd: k must be a multiple of 16");
         // (row stride and batch limits are checked by the caller before any device is touched)
         dim3 grid(ceil_div(npairs, WARPS), batch);
-        dlrm_fwd_general_kernel<<<grid, THREADS, 0, stream>>>(static_cast<const rocwmma::float16_t*>(input),
-                                                              static_cast<rocwmma::float16_t*>(output), m, m_stride, k,
-                                                              out_stride, nblk, npairs);
+        if(f32)
+            dlrm_fwd_general_kernel<float><<<grid, THREADS, 0, stream>>>(static_cast<const float*>(input),
+                                                                         static_cast<float*>(output), m, m_stride, k,
+                                                                         out_stride, nblk, npairs);
+        else
+            dlrm_fwd_general_kernel<rocwmma::float16_t><<<grid, THREADS, 0, stream>>>(
+                static_cast<const rocwmma::float16_t*>(input), static_cast<rocwmma::float16_t*>(output), m, m_stride, k,
+                out_stride, nblk, npairs);
         B200_CHECK_CUDA(cudaGetLastError());
         return B200WMMA_OK;
     }
 
     int launch_dlrm_bwd_general(const void* input, const void* upstream, void* grad, void* bottom_mlp_grad, uint32_t m,
-                                uint32_t m_stride, uint32_t k, uint32_t batch, uint32_t upstream_stride, int fuse,
+                                uint32_t m_stride, uint32_t k, uint32_t batch, uint32_t upstream_stride, int fuse, bool f32,
                                 cudaStream_t stream)
     {
         using namespace dlrmg;
@@ -165,10 +174,15 @@ namespace b200wmma
         B200_REQUIRE(k % T == 0, B200WMMA_ERR_UNSUPPORTED, "dlrm_bwd: k must be a multiple of 16");
         // (row stride and batch limits are checked by the caller before any device is touched)
         dim3 grid(ceil_div(k, T * WARPS), nblk, batch);
-        dlrm_bwd_general_kernel<<<grid, THREADS, 0, stream>>>(
-            static_cast<const rocwmma::float16_t*>(input), static_cast<const rocwmma::float16_t*>(upstream),
-            static_cast<rocwmma::float16_t*>(grad), static_cast<rocwmma::float16_t*>(bottom_mlp_grad), m, m_stride, k,
-            upstream_stride, fuse);
+        if(f32)
+            dlrm_bwd_general_kernel<float><<<grid, THREADS, 0, stream>>>(
+                static_cast<const float*>(input), static_cast<const float*>(upstream), static_cast<float*>(grad),
+                static_cast<float*>(bottom_mlp_grad), m, m_stride, k, upstream_stride, fuse);
+        else
+            dlrm_bwd_general_kernel<rocwmma::float16_t><<<grid, THREADS, 0, stream>>>(
+                static_cast<const rocwmma::float16_t*>(input), static_cast<const rocwmma::float16_t*>(upstream),
+                static_cast<rocwmma::float16_t*>(grad), static_cast<rocwmma::float16_t*>(bottom_mlp_grad), m, m_stride, k,
+                upstream_stride, fuse);
         B200_CHECK_CUDA(cudaGetLastError());
         return B200WMMA_OK;
     }

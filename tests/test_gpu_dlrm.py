@@ -141,6 +141,50 @@ def test_dlrm_beyond_one_warp_per_sample(b, m, k, m_stride):
         check_bwd(grad, mlp, x, up, rg, rm, fuse)
 
 
+TOL_F32_DATA = 1e-5   # fp32 data: three TF32 products per multiply, fp32 accumulation (BASELINE asks 1e-3)
+
+
+@pytest.mark.parametrize("b,m,k,m_stride", [(4, 27, 128, 32), (64, 32, 32, 32), (8, 128, 128, 128), (2, 1024, 1024, 1024),
+                                            (5, 50, 48, 64)])
+def test_dlrm_fp32_data(b, m, k, m_stride):
+    """fp32 DLRM data, the second data type of the reference sweep (test/dlrm/test/dlrm_test_params.hpp:51-58): against
+    the oracle and, for the fixture case, against the committed output of the reference's own dlrm_*_CPU<float>."""
+    x = G.normal_np(G.SEED_X, (b, m, k), 0.25, np.float32)
+    w = k + m * (m - 1) // 2
+    stride = (w + 7) // 8 * 8 + 8
+    up = G.normal_np(G.SEED_G, (b, w), 0.1, np.float32)
+    ref_fwd = R.dlrm_fwd(R.port(), x, m, k, b)
+    rg, rm = R.dlrm_bwd(R.port(), x, up, m, k, b)
+    if (b, m, k) == (4, 27, 128):
+        gold = np.load(os.path.join(GOLD, "dlrm_ref.npz"))
+        assert np.array_equal(ref_fwd, gold["f32_m27_fwd"]) and np.array_equal(rg, gold["f32_m27_grad"])
+    xp = np.full((b, m_stride, k), np.float32(7.0)); xp[:, :m] = x
+    out = nan_filled((b, stride), torch.float32)
+    api.dlrm_dot_fwd(dev(xp), out, m, m_stride, k, b, stride)
+    assert_status_ok()
+    got = out.cpu().numpy()
+    assert np.array_equal(got[:, :k], x[:, 0, :]) and (got[:, w:] == 0).all()
+    if m > 1:
+        err = np.abs(got[:, k:w].astype(np.float64) - ref_fwd[:, k:].astype(np.float64)) / np.maximum(fwd_bound(x), 1e-30)
+        assert err.max() <= TOL_F32_DATA, err.max()
+    upp = np.zeros((b, stride), np.float32); upp[:, :w] = up
+    for fuse in (False, True):
+        grad = nan_filled((b, m_stride, k), torch.float32)
+        mlp = nan_filled((b, k), torch.float32)
+        api.dlrm_dot_bwd(dev(xp), dev(upp), grad, mlp, m, m_stride, k, b, stride, fuse)
+        assert_status_ok()
+        g = grad.cpu().numpy()
+        expect = rg.astype(np.float64).copy()
+        bound = bwd_bound(x, up, k)
+        if fuse:
+            expect[:, 0, :] += up[:, :k].astype(np.float64)
+            bound[:, 0, :] += np.abs(up[:, :k].astype(np.float64))
+        err = np.abs(g[:, :m].astype(np.float64) - expect) / np.maximum(bound, 1e-30)
+        assert err.max() <= TOL_F32_DATA * (2 if fuse else 1), err.max()
+        assert np.isnan(g[:, m:]).all()
+        assert np.array_equal(mlp.cpu().numpy(), rm)
+
+
 def test_dlrm_full_size_config():
     """B=16384, F=27 padded to 32 rows, D=128, output width 480: sampled rows vs the oracle plus whole-batch
     properties (pass-through exact everywhere; Z symmetric => fwd(x) on a row-permuted sample permutes pairs)."""
