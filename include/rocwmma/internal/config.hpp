@@ -25,4 +25,10 @@
 #define ROCWMMA_HOST_DEVICE __host__ __device__
 #define ROCWMMA_KERNEL __global__
 
+// HIP's spelling of the dynamic shared-memory array, used by kernels written for the reference
+// (samples/perf_hgemm.cpp:345, test/gemm/gemm_PGR1_LB2_MP0_MB_CP/device/kernel_device_func.hpp:191)
+#ifndef HIP_DYNAMIC_SHARED
+#define HIP_DYNAMIC_SHARED(type, var) extern __shared__ type var[];
+#endif
+
 #endif

@@ -51,6 +51,18 @@ namespace rocwmma
         mem_col_major
     };
 
+    // BLAS-style names of the data layouts (reference: internal/utils.hpp:312-323)
+    template <>
+    constexpr const char* dataTypeToString<row_major>()
+    {
+        return "T";
+    }
+    template <>
+    constexpr const char* dataTypeToString<col_major>()
+    {
+        return "N";
+    }
+
     namespace detail
     {
         // ---- 1-D data space (rocWMMA internal/mapping_util.hpp DataSpace) ---------------------
@@ -75,6 +87,19 @@ namespace rocwmma
         };
         template <>
         struct DataSpace<void>;
+    } // namespace detail
+
+    // 1-D array layouts by name (reference: internal/layout.hpp:36-44)
+    namespace DataLayout
+    {
+        template <typename DataLayoutT>
+        using Array1d = detail::DataSpace<DataLayoutT>;
+        using RowMajor = Array1d<row_major>;
+        using ColMajor = Array1d<col_major>;
+    } // namespace DataLayout
+
+    namespace detail
+    {
 
         template <typename L>
         struct OrthoLayout;

@@ -10,6 +10,72 @@
 
 namespace rocwmma
 {
+    namespace detail
+    {
+        // Warp ("wave") coordinates of the thread block.  TBlockX / TBlockY are the thread-block dimensions when
+        // they are known at compile time (workgroupDim() is then a constant expression), else 0 for a run-time
+        // query of blockDim (reference: internal/mapping_util.hpp:42-68, mapping_util_impl.hpp:70-121).
+        // The functions are callable in host code too, where the thread coordinates read as zero: user code
+        // declares `constexpr` helpers on top of them without a device qualifier.
+        template <uint32_t TBlockX = 0u, uint32_t TBlockY = 0u>
+        struct WaveSpace
+        {
+            using WaveCoordT      = Coord2d;
+            using WorkgroupCoordT = Coord2d;
+            using WorkgroupDimT   = Coord2d;
+
+            ROCWMMA_HOST_DEVICE static inline uint32_t localLaneId()
+            {
+#if defined(__CUDA_ARCH__)
+                return threadIdx.x & (Constants::AMDGCN_WAVE_SIZE - 1u);
+#else
+                return 0u;
+#endif
+            }
+            ROCWMMA_HOST_DEVICE static inline WaveCoordT localWaveCoord()
+            {
+#if defined(__CUDA_ARCH__)
+                return make_coord2d(threadIdx.x / Constants::AMDGCN_WAVE_SIZE, threadIdx.y);
+#else
+                return make_coord2d(0u, 0u);
+#endif
+            }
+            ROCWMMA_HOST_DEVICE static inline WaveCoordT globalWaveCoord()
+            {
+#if defined(__CUDA_ARCH__)
+                const uint32_t bx = TBlockX > 0u && TBlockY > 0u ? TBlockX : blockDim.x;
+                const uint32_t by = TBlockX > 0u && TBlockY > 0u ? TBlockY : blockDim.y;
+                return make_coord2d((blockIdx.x * bx + threadIdx.x) / Constants::AMDGCN_WAVE_SIZE,
+                                    blockIdx.y * by + threadIdx.y);
+#else
+                return make_coord2d(0u, 0u);
+#endif
+            }
+            ROCWMMA_HOST_DEVICE static inline WorkgroupCoordT workgroupCoord()
+            {
+#if defined(__CUDA_ARCH__)
+                return make_coord2d(blockIdx.x, blockIdx.y);
+#else
+                return make_coord2d(0u, 0u);
+#endif
+            }
+            template <bool IsConst = (TBlockX > 0u && TBlockY > 0u), std::enable_if_t<IsConst>* = nullptr>
+            ROCWMMA_HOST_DEVICE constexpr static inline WorkgroupDimT workgroupDim()
+            {
+                return make_coord2d(TBlockX / Constants::AMDGCN_WAVE_SIZE, TBlockY);
+            }
+            template <bool IsConst = (TBlockX > 0u && TBlockY > 0u), std::enable_if_t<!IsConst>* = nullptr>
+            ROCWMMA_HOST_DEVICE static inline WorkgroupDimT workgroupDim()
+            {
+#if defined(__CUDA_ARCH__)
+                return make_coord2d(blockDim.x / Constants::AMDGCN_WAVE_SIZE, blockDim.y);
+#else
+                return make_coord2d(0u, 0u);
+#endif
+            }
+        };
+    } // namespace detail
+
     template <uint32_t BlockHeight, uint32_t BlockWidth, typename DataT, typename DataLayout>
     struct MappingUtil
     {

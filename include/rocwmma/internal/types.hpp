@@ -63,6 +63,29 @@ namespace rocwmma
     using uint64_t   = ::uint64_t;
     using index_t    = ::int32_t;
 
+    // Printable names of the data types (reference: internal/utils.hpp:202-330); user code adds specialisations
+    // for its own tag types (test/gemm/gemm_config.hpp:435-475).
+    template <typename DataT>
+    constexpr const char* dataTypeToString();
+#define ROCWMMA_B200_TYPE_NAME(TYPE, NAME)                 \
+    template <>                                            \
+    constexpr const char* dataTypeToString<TYPE>()         \
+    {                                                      \
+        return NAME;                                       \
+    }
+    ROCWMMA_B200_TYPE_NAME(float16_t, "f16")
+    ROCWMMA_B200_TYPE_NAME(hfloat16_t, "h16")
+    ROCWMMA_B200_TYPE_NAME(float32_t, "f32")
+    ROCWMMA_B200_TYPE_NAME(float64_t, "f64")
+    ROCWMMA_B200_TYPE_NAME(int8_t, "i8")
+    ROCWMMA_B200_TYPE_NAME(uint8_t, "u8")
+    ROCWMMA_B200_TYPE_NAME(int16_t, "i16")
+    ROCWMMA_B200_TYPE_NAME(int32_t, "i32")
+    ROCWMMA_B200_TYPE_NAME(uint32_t, "u32")
+    ROCWMMA_B200_TYPE_NAME(int64_t, "i64")
+    ROCWMMA_B200_TYPE_NAME(uint64_t, "u64")
+#undef ROCWMMA_B200_TYPE_NAME
+
     // Minimal fixed-size vector used as fragment storage (`*frag`, `frag.x`).
     template <typename T, uint32_t N>
     struct VecT

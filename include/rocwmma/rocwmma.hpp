@@ -14,6 +14,7 @@
 #define ROCWMMA_B200_API_HPP
 
 #include "internal/config.hpp"
+#include "internal/flow_control.hpp"
 #include "internal/layout.hpp"
 #include "internal/mapping_util.hpp"
 #include "internal/mma_atoms.hpp"
@@ -124,6 +125,32 @@ namespace rocwmma
     using GetDataLayout_t = detail::DataSpace<typename detail::FragInfo<std::decay_t<FragT>>::Layout>;
     template <typename FragT>
     using GetDataType_t = typename detail::FragInfo<std::decay_t<FragT>>::Data;
+    // MappingUtil of a fragment's block shape, data type and data layout (reference: internal/accessors.hpp:89)
+    template <typename FragT>
+    using GetMappingUtil_t = MappingUtil<GetIOShape_t<FragT>::BlockHeight, GetIOShape_t<FragT>::BlockWidth,
+                                         GetDataType_t<FragT>, typename detail::FragInfo<std::decay_t<FragT>>::Layout>;
+
+    // Cooperative IO configuration of a fragment shared by WaveCount warps (reference: internal/accessors.hpp:59,
+    // internal/io_traits.hpp:61).  IOTraits::IOCount is the number of independent IO steps the whole fragment
+    // takes: here the number of 16-row atoms, the unit the cooperative loads and stores deal out to the warps.
+    // It does not depend on the data layout or on a transpose, so the IOCounts of a global-read fragment and of
+    // its shared-memory-write view always have a common divisor (what user code asserts on).
+    namespace detail
+    {
+        template <typename FragT, uint32_t WaveCount>
+        struct CoopIOConfig
+        {
+            struct IOTraits
+            {
+                enum : uint32_t
+                {
+                    IOCount = FragInfo<FragT>::Geometry::Atoms
+                };
+            };
+        };
+    }
+    template <typename FragT, uint32_t WaveCount = 1u>
+    using GetCoopIOConfig_t = detail::CoopIOConfig<std::decay_t<FragT>, WaveCount>;
 
     // ------------------------------------------------------------------------------------------
     // fill_fragment  (reference: rocwmma.hpp:217-219, rocwmma_impl.hpp:204-217)
