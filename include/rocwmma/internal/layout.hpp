@@ -204,6 +204,16 @@ namespace rocwmma
             }
         };
 
+        // Unit of a cooperative split: one 32-bit register's worth of elements (4 x 8-bit, 2 x 16-bit, 1 otherwise).
+        // Warps sharing a fragment each move a contiguous range of its elements, a whole number of these units;
+        // the rule depends only on the fragment's size and element type, so a fragment and any re-interpretation
+        // of its registers (transpose, data layout, register file) are split identically.
+        template <typename DataT>
+        struct CoopUnit
+        {
+            static constexpr uint32_t value = sizeof(DataT) >= 4 ? 1u : 4u / sizeof(DataT);
+        };
+
         // ---- whole-fragment geometry -----------------------------------------------------------
         // Gives, for each fragment kind: block height / width in matrix space, the atom grid and
         // the map  element index -> (row, col)  inside the block.  `RunAlongCol` says whether
@@ -254,6 +264,26 @@ namespace rocwmma
                 Atom::coord(lane >> 2, lane & 3u, i, d, k);
                 row = (atom % AtomsK) * KA + k;
                 col = (atom / AtomsK) * 16u + d;
+            }
+        };
+
+        // Register-file view: fragment<matrix_b, 1, warp size, R, DataT> is R registers of one warp seen as an
+        // R x 32 matrix, element i of lane l at (row i, col l) - the type ApplyRegisterFile_t produces
+        // (reference: rocwmma_transforms_impl.hpp:272-289).  It exists to park any fragment's registers in
+        // shared memory and to read them back into the same registers; BlockM = 1 marks it and it is not an
+        // mma_sync operand.  One "atom" is one register row.
+        template <uint32_t BN, uint32_t BK, typename DataT>
+        struct FragGeometry<matrix_b, 1u, BN, BK, DataT>
+        {
+            static_assert(BN == Constants::AMDGCN_WAVE_SIZE, "A register file is as wide as the warp");
+            static constexpr uint32_t BlockHeight = BK, BlockWidth = BN, BlockDim = BN, KDim = BK;
+            static constexpr uint32_t Atoms = BK, AtomElems = 1, Run = 1, Size = BK;
+            static constexpr bool     RunAlongCol = true;
+            ROCWMMA_DEVICE static inline void coord(uint32_t lane, uint32_t atom, uint32_t, uint32_t& row,
+                                                    uint32_t& col)
+            {
+                row = atom;
+                col = lane;
             }
         };
 

@@ -132,9 +132,10 @@ namespace rocwmma
 
     // Cooperative IO configuration of a fragment shared by WaveCount warps (reference: internal/accessors.hpp:59,
     // internal/io_traits.hpp:61).  IOTraits::IOCount is the number of independent IO steps the whole fragment
-    // takes: here the number of 16-row atoms, the unit the cooperative loads and stores deal out to the warps.
-    // It does not depend on the data layout or on a transpose, so the IOCounts of a global-read fragment and of
-    // its shared-memory-write view always have a common divisor (what user code asserts on).
+    // takes: here the number of 32-bit register units per lane, the unit the cooperative loads and stores deal out
+    // to the warps.  It depends only on the fragment's size and element type, so the IOCounts of a global-read
+    // fragment and of its shared-memory-write view (transposed, re-laid-out or as a register file) are equal and
+    // always have a common divisor (what user code asserts on).
     namespace detail
     {
         template <typename FragT, uint32_t WaveCount>
@@ -144,7 +145,7 @@ namespace rocwmma
             {
                 enum : uint32_t
                 {
-                    IOCount = FragInfo<FragT>::Geometry::Atoms
+                    IOCount = FragInfo<FragT>::Geometry::Size / CoopUnit<typename FragInfo<FragT>::Data>::value
                 };
             };
         };
@@ -194,9 +195,10 @@ namespace rocwmma
         // ColMajorMem selects the memory layout.  When consecutive register elements are adjacent
         // in memory (Run > 1 and the run direction is the contiguous memory direction) and the
         // addresses are suitably aligned, a run moves as one 2..16-byte access.
+        // Moves the elements [elemBegin, elemEnd) of a fragment.
         template <bool IsLoad, bool ColMajorMem, typename Geometry, typename DataT>
-        ROCWMMA_DEVICE inline void move_atoms(DataT* regs, DataT* mem, uint32_t ldm, uint32_t atomBegin,
-                                              uint32_t atomEnd)
+        ROCWMMA_DEVICE inline void move_atoms(DataT* regs, DataT* mem, uint32_t ldm, uint32_t elemBegin,
+                                              uint32_t elemEnd)
         {
             const uint32_t     lane       = threadIdx.x & 31u;
             constexpr uint32_t Run        = Geometry::Run;
@@ -210,19 +212,21 @@ namespace rocwmma
 #pragma unroll
             for(uint32_t atom = 0; atom < Geometry::Atoms; ++atom)
             {
-                if(atom < atomBegin || atom >= atomEnd)
-                    continue;
 #pragma unroll
                 for(uint32_t i = 0; i < Geometry::AtomElems; i += Run)
                 {
-                    uint32_t row, col;
+                    const uint32_t e = atom * Geometry::AtomElems + i; // first element of this run
+                    if(e + Run <= elemBegin || e >= elemEnd)
+                        continue;
+                    const bool whole = e >= elemBegin && e + Run <= elemEnd;
+                    uint32_t   row, col;
                     Geometry::coord(lane, atom, i, row, col);
-                    DataT* r = regs + atom * Geometry::AtomElems + i;
+                    DataT* r = regs + e;
                     if constexpr(contiguous)
                     {
                         const size_t off = ColMajorMem ? static_cast<size_t>(col) * ldm + row
                                                        : static_cast<size_t>(row) * ldm + col;
-                        if(vec_ok)
+                        if(vec_ok && whole)
                         {
                             // staged through a correctly aligned temporary: the fragment itself is
                             // only 4-byte aligned
@@ -249,6 +253,8 @@ namespace rocwmma
 #pragma unroll
                             for(uint32_t j = 0; j < Run; ++j)
                             {
+                                if(e + j < elemBegin || e + j >= elemEnd)
+                                    continue;
                                 if constexpr(IsLoad)
                                     r[j] = mem[off + j];
                                 else
@@ -261,6 +267,8 @@ namespace rocwmma
 #pragma unroll
                         for(uint32_t j = 0; j < Run; ++j)
                         {
+                            if(e + j < elemBegin || e + j >= elemEnd)
+                                continue;
                             uint32_t rr, cc;
                             Geometry::coord(lane, atom, i + j, rr, cc);
                             const size_t off = ColMajorMem ? static_cast<size_t>(cc) * ldm + rr
@@ -289,7 +297,7 @@ namespace rocwmma
                       "fragment declaration or use the run-time function overload.");
         using G = typename fragment<MatrixT, BlockM, BlockN, BlockK, DataT, DataLayoutT>::Geometry;
         detail::move_atoms<true, std::is_same<DataLayoutT, col_major>::value, G, DataT>(
-            frag.x, const_cast<DataT*>(data), ldm, 0u, G::Atoms);
+            frag.x, const_cast<DataT*>(data), ldm, 0u, G::Size);
     }
 
     template <typename MatrixT, uint32_t BlockM, uint32_t BlockN, uint32_t BlockK, typename DataT>
@@ -298,9 +306,9 @@ namespace rocwmma
     {
         using G = typename fragment<MatrixT, BlockM, BlockN, BlockK, DataT>::Geometry;
         if(layout == layout_t::mem_row_major)
-            detail::move_atoms<true, false, G, DataT>(frag.x, const_cast<DataT*>(data), ldm, 0u, G::Atoms);
+            detail::move_atoms<true, false, G, DataT>(frag.x, const_cast<DataT*>(data), ldm, 0u, G::Size);
         else
-            detail::move_atoms<true, true, G, DataT>(frag.x, const_cast<DataT*>(data), ldm, 0u, G::Atoms);
+            detail::move_atoms<true, true, G, DataT>(frag.x, const_cast<DataT*>(data), ldm, 0u, G::Size);
     }
 
     // ------------------------------------------------------------------------------------------
@@ -318,7 +326,7 @@ namespace rocwmma
                       "fragment declaration or use the run-time function overload.");
         using G = typename fragment<MatrixT, BlockM, BlockN, BlockK, DataT, DataLayoutT>::Geometry;
         detail::move_atoms<false, std::is_same<DataLayoutT, col_major>::value, G, DataT>(
-            const_cast<DataT*>(frag.x), data, ldm, 0u, G::Atoms);
+            const_cast<DataT*>(frag.x), data, ldm, 0u, G::Size);
     }
 
     template <typename MatrixT, uint32_t BlockM, uint32_t BlockN, uint32_t BlockK, typename DataT>
@@ -328,9 +336,9 @@ namespace rocwmma
     {
         using G = typename fragment<MatrixT, BlockM, BlockN, BlockK, DataT>::Geometry;
         if(layout == layout_t::mem_row_major)
-            detail::move_atoms<false, false, G, DataT>(const_cast<DataT*>(frag.x), data, ldm, 0u, G::Atoms);
+            detail::move_atoms<false, false, G, DataT>(const_cast<DataT*>(frag.x), data, ldm, 0u, G::Size);
         else
-            detail::move_atoms<false, true, G, DataT>(const_cast<DataT*>(frag.x), data, ldm, 0u, G::Atoms);
+            detail::move_atoms<false, true, G, DataT>(const_cast<DataT*>(frag.x), data, ldm, 0u, G::Size);
     }
 
     // ------------------------------------------------------------------------------------------

@@ -6,9 +6,12 @@
 // participating warp moves the whole block collectively (global -> registers -> shared memory in
 // perf_hgemm, samples/perf_hgemm.cpp:329-362).
 //
-// The unit of splitting here is the fragment's 16-row atom (see internal/layout.hpp): the atoms
-// are dealt out in contiguous, equally sized groups; when there are more warps than atoms the
-// surplus warps do nothing, like the reference's waves beyond `maxWaves`
+// The unit of splitting here is one 32-bit register per lane (4 / 2 / 1 elements of 8- / 16- / 32-and-64-bit
+// types): the fragment's elements are dealt out in contiguous, equally sized ranges of such units, identically for
+// a fragment and for any re-interpretation of its registers (applyTranspose, applyDataLayout, the register-file
+// view), so a cooperative load of one view followed by a cooperative store of another moves exactly the
+// registers each warp holds.  When there are more warps than units the surplus warps do nothing, like the
+// reference's waves beyond `maxWaves`
 // (internal/coop_load.hpp:101-135).  The deprecated splitCount forms are accepted and ignore the
 // split count, as the reference does (rocwmma_coop_impl.hpp:51-53).
 #ifndef ROCWMMA_B200_COOP_API_HPP
@@ -20,13 +23,18 @@ namespace rocwmma
 {
     namespace detail
     {
-        template <typename Geometry>
+        // Element range [begin, end) of the fragment that warp `waveIndex` of `waveCount` moves.
+        template <typename Geometry, typename DataT>
         ROCWMMA_DEVICE inline void coop_range(uint32_t waveIndex, uint32_t waveCount, uint32_t& begin,
                                               uint32_t& end)
         {
-            const uint32_t per = (Geometry::Atoms + waveCount - 1u) / waveCount;
-            begin              = min(waveIndex * per, Geometry::Atoms);
-            end                = min(begin + per, Geometry::Atoms);
+            constexpr uint32_t U     = CoopUnit<DataT>::value;
+            constexpr uint32_t units = Geometry::Size / U;
+            static_assert(Geometry::Size % U == 0, "fragments hold whole 32-bit registers");
+            const uint32_t per = (units + waveCount - 1u) / waveCount;
+            const uint32_t b   = min(waveIndex * per, units);
+            begin              = b * U;
+            end                = min(b + per, units) * U;
         }
         // Default wave index / count: all warps of the thread block, row-major warp order
         // (reference: rocwmma_coop_impl.hpp:101-107).
@@ -48,7 +56,7 @@ namespace rocwmma
         static_assert(!std::is_same<DataLayoutT, void>::value, "Cooperative loads need a static data layout");
         using G = typename fragment<MatrixT, BlockM, BlockN, BlockK, DataT, DataLayoutT>::Geometry;
         uint32_t begin, end;
-        detail::coop_range<G>(waveIndex, waveCount, begin, end);
+        detail::coop_range<G, DataT>(waveIndex, waveCount, begin, end);
         detail::move_atoms<true, std::is_same<DataLayoutT, col_major>::value, G, DataT>(
             frag.x, const_cast<DataT*>(data), ldm, begin, end);
     }
@@ -102,7 +110,7 @@ namespace rocwmma
         static_assert(!std::is_same<DataLayoutT, void>::value, "Cooperative stores need a static data layout");
         using G = typename fragment<MatrixT, BlockM, BlockN, BlockK, DataT, DataLayoutT>::Geometry;
         uint32_t begin, end;
-        detail::coop_range<G>(waveIndex, waveCount, begin, end);
+        detail::coop_range<G, DataT>(waveIndex, waveCount, begin, end);
         detail::move_atoms<false, std::is_same<DataLayoutT, col_major>::value, G, DataT>(
             const_cast<DataT*>(frag.x), data, ldm, begin, end);
     }

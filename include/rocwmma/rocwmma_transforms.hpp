@@ -6,7 +6,8 @@
 // only the memory layout tag.  Both are re-interpretations here because a fragment's register
 // layout is independent of its data layout and matrix_b is laid out as the transpose of matrix_a
 // (internal/layout.hpp); the WaveCount template argument of applyDataLayout is accepted for
-// source compatibility and has no effect.
+// source compatibility and has no effect.  ApplyRegisterFile_t is the one transform that changes the shape: it
+// names the raw register file of a fragment as a matrix of its own.
 #ifndef ROCWMMA_B200_TRANSFORMS_API_HPP
 #define ROCWMMA_B200_TRANSFORMS_API_HPP
 
@@ -43,9 +44,13 @@ namespace rocwmma
     using ApplyTranspose_t = typename detail::TransposeOf<std::decay_t<FragT>>::type;
     template <typename FragT, typename DataLayoutT>
     using ApplyDataLayout_t = typename detail::WithLayout<std::decay_t<FragT>, DataLayoutT>::type;
-    // Register-file view of a fragment: identical here, since fragments already are the MMA operands.
+    // Register-file view of a fragment: its registers as a (registers per lane) x (warp size) matrix_b block, for
+    // parking them in shared memory as they are (reference: rocwmma_transforms_impl.hpp:272-289).  Obtained by
+    // reinterpret_cast of the fragment, as the reference's users do (test/gemm/gemm_local_mapping.hpp:417-434).
     template <typename FragT>
-    using ApplyRegisterFile_t = std::decay_t<FragT>;
+    using ApplyRegisterFile_t
+        = fragment<matrix_b, 1u, Constants::AMDGCN_WAVE_SIZE, std::decay_t<FragT>::num_elements,
+                   typename detail::FragInfo<std::decay_t<FragT>>::Data, typename detail::FragInfo<std::decay_t<FragT>>::Layout>;
 
     template <typename FragT>
     ROCWMMA_DEVICE inline ApplyTranspose_t<FragT> const& applyTranspose(FragT const& frag)

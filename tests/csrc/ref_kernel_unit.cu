@@ -177,7 +177,8 @@ namespace
 } // namespace
 
 // config : 0 block-level / 1 wave-level / 2 workgroup-level cooperation (test/gemm/gemm_config.hpp), each with the
-//          inputs kept as A | B^T (+0, "LdsNT") or A^T | B (+3, "LdsTN") in shared memory
+//          inputs kept as A | B^T (+0, "LdsNT") or A^T | B (+3, "LdsTN") in shared memory; 6 block-level with the
+//          fragments' raw register files in shared memory ("LdsRF")
 // lds_col: shared-memory data layout row_major (0) or col_major (1)
 // variant: 0 f16->f32 (A row, B col)  1 f16->f16 compute f32 (A col, B row)  2 f32 (A row, B col)  3 f64 (A row, B col)
 //          4 i8->i32, BlockK 32 (A row, B col)  5 f16->f32, 32x32x16 blocks (A col, B col);  C / D row-major
@@ -198,6 +199,7 @@ extern "C" int ref_test_gemm_coop(int config, int lds_col, int variant, uint32_t
         COOP_CASE(3, CG::BlockLevel::LdsTN)
         COOP_CASE(4, CG::WaveLevel::LdsTN)
         COOP_CASE(5, CG::WorkgroupLevel::LdsTN)
+        COOP_CASE(6, CG::BlockLevel::LdsRF)
     default:
         return -1;
     }

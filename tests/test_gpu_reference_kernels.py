@@ -75,15 +75,15 @@ def _check(got, case, m, n, k):
 # the cooperative kernel's variants: as above except 4 (BlockK 32) and 5 (both inputs column-major)
 COOP_VARIANTS = dict(VARIANTS)
 COOP_VARIANTS[5] = (np.float16, np.float32, 1, 1, TOL_F32_OUT)
-COOP_CONFIGS = ["block_LdsNT", "wave_LdsNT", "workgroup_LdsNT", "block_LdsTN", "wave_LdsTN", "workgroup_LdsTN"]
+COOP_CONFIGS = ["block_LdsNT", "wave_LdsNT", "workgroup_LdsNT", "block_LdsTN", "wave_LdsTN", "workgroup_LdsTN", "block_LdsRF"]
 
 
 @pytest.mark.parametrize("lds_col", [0, 1], ids=["lds_row_major", "lds_col_major"])
-@pytest.mark.parametrize("config", range(6), ids=COOP_CONFIGS)
+@pytest.mark.parametrize("config", range(7), ids=COOP_CONFIGS)
 @pytest.mark.parametrize("variant", sorted(COOP_VARIANTS))
 def test_reference_cooperative_kernel_on_these_headers(variant, config, lds_col):
     """gemm_PGR1_LB2_MP0_MB_CP: global prefetch, two shared-memory buffers, cooperative loads - in each of the
-    reference's six cooperation / shared-memory configurations and both shared-memory data layouts."""
+    reference's seven cooperation / shared-memory configurations and both shared-memory data layouts."""
     lib = _lib()
     m, n, k = 256, 512, 96  # multiples of every variant's macro tile (at most 128 x 256) and K step
     case = _case(COOP_VARIANTS, variant, m, n, k)
