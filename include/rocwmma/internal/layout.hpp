@@ -15,10 +15,13 @@
 // mma.sync instructions, so that mma_sync needs no shuffles:
 //   element size   A atom (M x K)   instruction            per-lane elements
 //   1 byte         16 x 16          m16n8k16 (s8)          (row g + 8*(i>>2),      col 4t + (i&3))
-//   2 bytes        16 x 16          m16n8k16 (f16)         (row g + 8*((i>>1)&1),  col 2t + (i&1) + 8*(i>>2))
+//   2 bytes        16 x 16          m16n8k16 (f16, bf16)   (row g + 8*((i>>1)&1),  col 2t + (i&1) + 8*(i>>2))
+//                  16 x 8           m16n8k8  (f16, bf16)   (row g + 8*(i>>1),      col 2t + (i&1))
 //   4 bytes        16 x 8           m16n8k8  (tf32)        (row g + 8*(i&1),       col t + 4*(i>>1))
+//                  16 x 4           m16n8k4  (tf32)        (row g + 8*i,           col t)
 //   8 bytes        16 x 4           m16n8k4  (f64)         (row g + 8*i,           col t)
-// with g = lane / 4, t = lane % 4.  B atoms are the transposes (k takes the role of col, n of
+// with g = lane / 4, t = lane % 4.  The deeper atom is used when BlockK is a multiple of it, the
+// shallower one otherwise (BlockK = 8 for 16-bit types, 4 for fp32: the reference's minimum K).  B atoms are the transposes (k takes the role of col, n of
 // row).  Accumulator atoms are 16 x 16 = two m16n8 result tiles:
 //   (row g + 8*((i>>1)&1), col 2t + (i&1) + 8*(i>>2)).
 #ifndef ROCWMMA_B200_LAYOUT_HPP
@@ -119,37 +122,38 @@ namespace rocwmma
             using type = void;
         };
 
-        // ---- atom geometry by element size --------------------------------------------------
-        template <uint32_t ElemBytes>
+        // ---- atom geometry by element size and BlockK -----------------------------------------
+        // Depth of one input atom: the deepest mma.sync K that divides BlockK (0: shape not offered).
+        template <uint32_t ElemBytes, uint32_t BK>
         struct AtomK;
-        template <>
-        struct AtomK<1>
+        template <uint32_t BK>
+        struct AtomK<1, BK>
         {
-            static constexpr uint32_t value = 16;
+            static constexpr uint32_t value = BK % 16 == 0 ? 16 : 0;
         };
-        template <>
-        struct AtomK<2>
+        template <uint32_t BK>
+        struct AtomK<2, BK>
         {
-            static constexpr uint32_t value = 16;
+            static constexpr uint32_t value = BK % 16 == 0 ? 16 : (BK % 8 == 0 ? 8 : 0);
         };
-        template <>
-        struct AtomK<4>
+        template <uint32_t BK>
+        struct AtomK<4, BK>
         {
-            static constexpr uint32_t value = 8;
+            static constexpr uint32_t value = BK % 8 == 0 ? 8 : (BK % 4 == 0 ? 4 : 0);
         };
-        template <>
-        struct AtomK<8>
+        template <uint32_t BK>
+        struct AtomK<8, BK>
         {
-            static constexpr uint32_t value = 4;
+            static constexpr uint32_t value = BK % 4 == 0 ? 4 : 0;
         };
 
         // Coordinates (dim, k) of element `i` of one input atom for lane (g, t); `dim` runs along
         // the 16-wide block dimension (rows of A / columns of B), `k` along the reduction.
         // `Run` = number of consecutive elements that are adjacent along k.
-        template <uint32_t ElemBytes>
+        template <uint32_t ElemBytes, uint32_t KA>
         struct InputAtom;
         template <>
-        struct InputAtom<1>
+        struct InputAtom<1, 16>
         {
             static constexpr uint32_t Elems = 8, Run = 4;
             ROCWMMA_DEVICE static inline void coord(uint32_t g, uint32_t t, uint32_t i, uint32_t& dim,
@@ -160,7 +164,7 @@ namespace rocwmma
             }
         };
         template <>
-        struct InputAtom<2>
+        struct InputAtom<2, 16>
         {
             static constexpr uint32_t Elems = 8, Run = 2;
             ROCWMMA_DEVICE static inline void coord(uint32_t g, uint32_t t, uint32_t i, uint32_t& dim,
@@ -171,7 +175,18 @@ namespace rocwmma
             }
         };
         template <>
-        struct InputAtom<4>
+        struct InputAtom<2, 8>
+        {
+            static constexpr uint32_t Elems = 4, Run = 2;
+            ROCWMMA_DEVICE static inline void coord(uint32_t g, uint32_t t, uint32_t i, uint32_t& dim,
+                                                    uint32_t& k)
+            {
+                dim = g + 8u * (i >> 1);
+                k   = 2u * t + (i & 1u);
+            }
+        };
+        template <>
+        struct InputAtom<4, 8>
         {
             static constexpr uint32_t Elems = 4, Run = 1;
             ROCWMMA_DEVICE static inline void coord(uint32_t g, uint32_t t, uint32_t i, uint32_t& dim,
@@ -182,7 +197,18 @@ namespace rocwmma
             }
         };
         template <>
-        struct InputAtom<8>
+        struct InputAtom<4, 4>
+        {
+            static constexpr uint32_t Elems = 2, Run = 1;
+            ROCWMMA_DEVICE static inline void coord(uint32_t g, uint32_t t, uint32_t i, uint32_t& dim,
+                                                    uint32_t& k)
+            {
+                dim = g + 8u * i;
+                k   = t;
+            }
+        };
+        template <>
+        struct InputAtom<8, 4>
         {
             static constexpr uint32_t Elems = 2, Run = 1;
             ROCWMMA_DEVICE static inline void coord(uint32_t g, uint32_t t, uint32_t i, uint32_t& dim,
@@ -224,12 +250,12 @@ namespace rocwmma
         template <uint32_t BM, uint32_t BN, uint32_t BK, typename DataT>
         struct FragGeometry<matrix_a, BM, BN, BK, DataT>
         {
-            using Atom = InputAtom<sizeof(DataT)>;
-            static constexpr uint32_t KA = AtomK<sizeof(DataT)>::value;
+            static constexpr uint32_t KA = AtomK<sizeof(DataT), BK>::value;
+            static_assert(KA != 0, "BlockK must be a multiple of the smallest instruction K "
+                                   "(16 for 8-bit types, 8 for 16-bit, 4 for 32- and 64-bit)");
+            using Atom = InputAtom<sizeof(DataT), KA>;
             static constexpr uint32_t BlockHeight = BM, BlockWidth = BK, BlockDim = BM, KDim = BK;
             static_assert(BM % 16 == 0, "matrix_a fragments need BlockM to be a multiple of 16");
-            static_assert(BK % KA == 0, "BlockK must be a multiple of the instruction K "
-                                        "(16 for 8/16-bit types, 8 for 32-bit, 4 for 64-bit)");
             static constexpr uint32_t AtomsDim = BM / 16, AtomsK = BK / KA;
             static constexpr uint32_t Atoms = AtomsDim * AtomsK, AtomElems = Atom::Elems, Run = Atom::Run;
             static constexpr uint32_t Size = Atoms * AtomElems;
@@ -247,12 +273,12 @@ namespace rocwmma
         template <uint32_t BM, uint32_t BN, uint32_t BK, typename DataT>
         struct FragGeometry<matrix_b, BM, BN, BK, DataT>
         {
-            using Atom = InputAtom<sizeof(DataT)>;
-            static constexpr uint32_t KA = AtomK<sizeof(DataT)>::value;
+            static constexpr uint32_t KA = AtomK<sizeof(DataT), BK>::value;
+            static_assert(KA != 0, "BlockK must be a multiple of the smallest instruction K "
+                                   "(16 for 8-bit types, 8 for 16-bit, 4 for 32- and 64-bit)");
+            using Atom = InputAtom<sizeof(DataT), KA>;
             static constexpr uint32_t BlockHeight = BK, BlockWidth = BN, BlockDim = BN, KDim = BK;
             static_assert(BN % 16 == 0, "matrix_b fragments need BlockN to be a multiple of 16");
-            static_assert(BK % KA == 0, "BlockK must be a multiple of the instruction K "
-                                        "(16 for 8/16-bit types, 8 for 32-bit, 4 for 64-bit)");
             static constexpr uint32_t AtomsDim = BN / 16, AtomsK = BK / KA;
             static constexpr uint32_t Atoms = AtomsDim * AtomsK, AtomElems = Atom::Elems, Run = Atom::Run;
             static constexpr uint32_t Size = Atoms * AtomElems;

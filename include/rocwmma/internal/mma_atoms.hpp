@@ -25,6 +25,43 @@ namespace rocwmma
                          : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[1]), "r"(b[3]));
         }
 
+        // fp16, 8 deep (m16n8k8): a = 2 x b32, b = 2 x b32 [n-half 0, n-half 1]
+        ROCWMMA_DEVICE inline void mma_atom_f16_f32_k8(float (&acc)[8], const uint32_t (&a)[2], const uint32_t (&b)[2])
+        {
+            asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 "
+                         "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                         : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])
+                         : "r"(a[0]), "r"(a[1]), "r"(b[0]));
+            asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 "
+                         "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                         : "+f"(acc[4]), "+f"(acc[5]), "+f"(acc[6]), "+f"(acc[7])
+                         : "r"(a[0]), "r"(a[1]), "r"(b[1]));
+        }
+
+        // bf16 x bf16 -> fp32, same register orders as fp16
+        ROCWMMA_DEVICE inline void mma_atom_bf16_f32(float (&acc)[8], const uint32_t (&a)[4], const uint32_t (&b)[4])
+        {
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+                         "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                         : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])
+                         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[2]));
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+                         "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                         : "+f"(acc[4]), "+f"(acc[5]), "+f"(acc[6]), "+f"(acc[7])
+                         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[1]), "r"(b[3]));
+        }
+        ROCWMMA_DEVICE inline void mma_atom_bf16_f32_k8(float (&acc)[8], const uint32_t (&a)[2], const uint32_t (&b)[2])
+        {
+            asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 "
+                         "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                         : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])
+                         : "r"(a[0]), "r"(a[1]), "r"(b[0]));
+            asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 "
+                         "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                         : "+f"(acc[4]), "+f"(acc[5]), "+f"(acc[6]), "+f"(acc[7])
+                         : "r"(a[0]), "r"(a[1]), "r"(b[1]));
+        }
+
         // int8 x int8 -> int32 (m16n8k16): a = 2 x b32, b = 2 x b32 [n-half 0, n-half 1]
         ROCWMMA_DEVICE inline void mma_atom_i8_i32(int32_t (&acc)[8], const uint32_t (&a)[2],
                                                    const uint32_t (&b)[2])
@@ -86,6 +123,32 @@ namespace rocwmma
             mma_tf32_1688(acc + 4, al, bh[1], bh[3]);
             mma_tf32_1688(acc + 4, ah, bl[1], bl[3]);
             mma_tf32_1688(acc + 4, ah, bh[1], bh[3]);
+        }
+        // 4 deep (m16n8k4): a = 2 floats (rows g, g + 8 at k = t), b = 2 floats [n-half 0, n-half 1]
+        ROCWMMA_DEVICE inline void mma_tf32_1684(float* acc, const uint32_t (&a)[2], uint32_t b0)
+        {
+            asm volatile("mma.sync.aligned.m16n8k4.row.col.f32.tf32.tf32.f32 "
+                         "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                         : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])
+                         : "r"(a[0]), "r"(a[1]), "r"(b0));
+        }
+        ROCWMMA_DEVICE inline void mma_atom_f32_k4(float (&acc)[8], const float (&a)[2], const float (&b)[2])
+        {
+            uint32_t ah[2], al[2], bh[2], bl[2];
+#pragma unroll
+            for(int i = 0; i < 2; ++i)
+            {
+                ah[i] = to_tf32(a[i]);
+                al[i] = to_tf32(a[i] - __uint_as_float(ah[i]));
+                bh[i] = to_tf32(b[i]);
+                bl[i] = to_tf32(b[i] - __uint_as_float(bh[i]));
+            }
+            mma_tf32_1684(acc, al, bh[0]);
+            mma_tf32_1684(acc, ah, bl[0]);
+            mma_tf32_1684(acc, ah, bh[0]);
+            mma_tf32_1684(acc + 4, al, bh[1]);
+            mma_tf32_1684(acc + 4, ah, bl[1]);
+            mma_tf32_1684(acc + 4, ah, bh[1]);
         }
     } // namespace detail
 } // namespace rocwmma

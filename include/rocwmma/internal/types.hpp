@@ -8,6 +8,7 @@
 #ifndef ROCWMMA_B200_TYPES_HPP
 #define ROCWMMA_B200_TYPES_HPP
 
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cstdint>
 
@@ -51,6 +52,36 @@ namespace rocwmma
     };
     static_assert(sizeof(float16_t) == 2, "float16_t must be two bytes");
 
+    // bfloat16_t: the same kind of wrapper around the bf16 bits (the reference's is hip_bfloat16, a class with
+    // float conversions, internal/types.hpp:52)
+    struct __align__(2) bfloat16_t
+    {
+        unsigned short bits;
+
+        bfloat16_t() = default;
+        ROCWMMA_HOST_DEVICE bfloat16_t(float f)
+        {
+            bits = __bfloat16_as_ushort(__float2bfloat16_rn(f));
+        }
+        ROCWMMA_HOST_DEVICE bfloat16_t(double f)
+            : bfloat16_t(static_cast<float>(f))
+        {
+        }
+        ROCWMMA_HOST_DEVICE bfloat16_t(int v)
+            : bfloat16_t(static_cast<float>(v))
+        {
+        }
+        ROCWMMA_HOST_DEVICE bfloat16_t(unsigned v)
+            : bfloat16_t(static_cast<float>(v))
+        {
+        }
+        ROCWMMA_HOST_DEVICE operator float() const
+        {
+            return __bfloat162float(__ushort_as_bfloat16(bits));
+        }
+    };
+    static_assert(sizeof(bfloat16_t) == 2, "bfloat16_t must be two bytes");
+
     using hfloat16_t = __half;
     using float32_t  = float;
     using float64_t  = double;
@@ -75,6 +106,7 @@ namespace rocwmma
     }
     ROCWMMA_B200_TYPE_NAME(float16_t, "f16")
     ROCWMMA_B200_TYPE_NAME(hfloat16_t, "h16")
+    ROCWMMA_B200_TYPE_NAME(bfloat16_t, "bf16")
     ROCWMMA_B200_TYPE_NAME(float32_t, "f32")
     ROCWMMA_B200_TYPE_NAME(float64_t, "f64")
     ROCWMMA_B200_TYPE_NAME(int8_t, "i8")

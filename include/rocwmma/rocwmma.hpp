@@ -6,10 +6,10 @@
 // that header compiles against this one with nvcc for sm_100a; the "wave" is the CUDA warp
 // (Constants::AMDGCN_WAVE_SIZE == 32) and blockDim.x must be a multiple of 32.
 //
-// Supported block shapes: BlockM, BlockN multiples of 16; BlockK a multiple of 16 for 8- and
-// 16-bit inputs, 8 for fp32, 4 for fp64.  Supported mma_sync type pairs (input -> compute):
-// float16_t/hfloat16_t -> float32_t or float16_t, int8_t -> int32_t, float32_t -> float32_t
-// (3xTF32), float64_t -> float64_t.
+// Supported block shapes: BlockM, BlockN multiples of 16; BlockK a multiple of 16 for 8-bit
+// inputs, 8 for 16-bit, 4 for fp32 and fp64.  Supported mma_sync type pairs (input -> compute):
+// float16_t/hfloat16_t -> float32_t or the input type, bfloat16_t -> float32_t or bfloat16_t,
+// int8_t -> int32_t, float32_t -> float32_t (3xTF32), float64_t -> float64_t.
 #ifndef ROCWMMA_B200_API_HPP
 #define ROCWMMA_B200_API_HPP
 
@@ -352,15 +352,20 @@ namespace rocwmma
         template <typename InputT, typename ComputeT>
         struct MmaAtomOp;
 
+        // exec<KA>: one input atom of depth KA (the fragment geometry's choice for its BlockK)
         template <typename InputT>
         struct MmaF16Common
         {
             using AccT = float;
-            static constexpr uint32_t AElems = 8, BElems = 8;
+            template <uint32_t KA>
             ROCWMMA_DEVICE static inline void exec(float (&acc)[8], const InputT* a, const InputT* b)
             {
-                mma_atom_f16_f32(acc, *reinterpret_cast<const uint32_t(*)[4]>(a),
-                                 *reinterpret_cast<const uint32_t(*)[4]>(b));
+                if constexpr(KA == 16)
+                    mma_atom_f16_f32(acc, *reinterpret_cast<const uint32_t(*)[4]>(a),
+                                     *reinterpret_cast<const uint32_t(*)[4]>(b));
+                else
+                    mma_atom_f16_f32_k8(acc, *reinterpret_cast<const uint32_t(*)[2]>(a),
+                                        *reinterpret_cast<const uint32_t(*)[2]>(b));
             }
         };
         template <>
@@ -379,10 +384,33 @@ namespace rocwmma
         struct MmaAtomOp<hfloat16_t, hfloat16_t> : MmaF16Common<hfloat16_t>
         {
         };
+        struct MmaBf16Common
+        {
+            using AccT = float;
+            template <uint32_t KA>
+            ROCWMMA_DEVICE static inline void exec(float (&acc)[8], const bfloat16_t* a, const bfloat16_t* b)
+            {
+                if constexpr(KA == 16)
+                    mma_atom_bf16_f32(acc, *reinterpret_cast<const uint32_t(*)[4]>(a),
+                                      *reinterpret_cast<const uint32_t(*)[4]>(b));
+                else
+                    mma_atom_bf16_f32_k8(acc, *reinterpret_cast<const uint32_t(*)[2]>(a),
+                                         *reinterpret_cast<const uint32_t(*)[2]>(b));
+            }
+        };
+        template <>
+        struct MmaAtomOp<bfloat16_t, float32_t> : MmaBf16Common
+        {
+        };
+        template <>
+        struct MmaAtomOp<bfloat16_t, bfloat16_t> : MmaBf16Common
+        {
+        };
         template <>
         struct MmaAtomOp<int8_t, int32_t>
         {
             using AccT = int32_t;
+            template <uint32_t KA>
             ROCWMMA_DEVICE static inline void exec(int32_t (&acc)[8], const int8_t* a, const int8_t* b)
             {
                 mma_atom_i8_i32(acc, *reinterpret_cast<const uint32_t(*)[2]>(a),
@@ -393,6 +421,7 @@ namespace rocwmma
         struct MmaAtomOp<float64_t, float64_t>
         {
             using AccT = double;
+            template <uint32_t KA>
             ROCWMMA_DEVICE static inline void exec(double (&acc)[8], const double* a, const double* b)
             {
                 mma_atom_f64(acc, *reinterpret_cast<const double(*)[2]>(a),
@@ -403,10 +432,15 @@ namespace rocwmma
         struct MmaAtomOp<float32_t, float32_t>
         {
             using AccT = float;
+            template <uint32_t KA>
             ROCWMMA_DEVICE static inline void exec(float (&acc)[8], const float* a, const float* b)
             {
-                mma_atom_f32(acc, *reinterpret_cast<const float(*)[4]>(a),
-                             *reinterpret_cast<const float(*)[4]>(b));
+                if constexpr(KA == 8)
+                    mma_atom_f32(acc, *reinterpret_cast<const float(*)[4]>(a),
+                                 *reinterpret_cast<const float(*)[4]>(b));
+                else
+                    mma_atom_f32_k4(acc, *reinterpret_cast<const float(*)[2]>(a),
+                                    *reinterpret_cast<const float(*)[2]>(b));
             }
         };
     } // namespace detail
@@ -438,7 +472,7 @@ namespace rocwmma
                     acc[e] = static_cast<AccT>(c.x[cbase + e]);
 #pragma unroll
                 for(uint32_t ki = 0; ki < GA::AtomsK; ++ki)
-                    Op::exec(acc, a.x + (mi * GA::AtomsK + ki) * GA::AtomElems,
+                    Op::template exec<GA::KA>(acc, a.x + (mi * GA::AtomsK + ki) * GA::AtomElems,
                              b.x + (ni * GB::AtomsK + ki) * GB::AtomElems);
 #pragma unroll
                 for(uint32_t e = 0; e < 8; ++e)

@@ -5,8 +5,8 @@
 //   matrix_a    : fragment<matrix_a, BlockDim, 16, BlockK>       (BlockDim x BlockK in memory)
 //   matrix_b    : fragment<matrix_b, 16, BlockDim, BlockK>       (BlockK x BlockDim in memory)
 //   accumulator : fragment<accumulator, BlockDim, BlockK, 16>    (BlockDim x BlockK in memory)
-// Points this implementation does not offer return -3: BlockK = 8 with 8- and 16-bit inputs (the fragments are
-// made of whole mma.sync operands, 16 deep for those types) and accumulator blocks narrower than 16.
+// Points this implementation does not offer return -3: BlockK = 8 with 8-bit inputs (the fragments are made of
+// whole mma.sync operands, at least 16 deep for that type) and accumulator blocks narrower than 16.
 //
 // The file is compiled once per (fragment kind, element type) with -DSWEEP_KIND=0..2 -DSWEEP_TYPE=0..3, so that the
 // pieces build in parallel, and once without them for the dispatcher frag_sweep(); all objects are linked into one
@@ -41,14 +41,14 @@ namespace
     template <uint32_t BD, uint32_t BK, typename T, typename L>
     struct FragOf<matrix_a, BD, BK, T, L>
     {
-        static constexpr bool supported = BK % detail::AtomK<sizeof(T)>::value == 0;
+        static constexpr bool supported = detail::AtomK<sizeof(T), BK>::value != 0;
         template <typename = void>
         using type = fragment<matrix_a, BD, 16, BK, T, L>;
     };
     template <uint32_t BD, uint32_t BK, typename T, typename L>
     struct FragOf<matrix_b, BD, BK, T, L>
     {
-        static constexpr bool supported = BK % detail::AtomK<sizeof(T)>::value == 0;
+        static constexpr bool supported = detail::AtomK<sizeof(T), BK>::value != 0;
         template <typename = void>
         using type = fragment<matrix_b, 16, BD, BK, T, L>;
     };

@@ -262,7 +262,15 @@ extern "C" int frag_unit_transpose(int case_id, const void* src, void* dst, uint
     X(10, 16, 16, 8, float32_t, float32_t, float32_t, row_major, col_major)                   \
     X(11, 32, 32, 16, float32_t, float32_t, float32_t, col_major, row_major)                  \
     X(12, 32, 16, 16, float16_t, float32_t, float32_t, row_major, col_major)                  \
-    X(13, 16, 16, 16, hfloat16_t, float32_t, float32_t, row_major, col_major)
+    X(13, 16, 16, 16, hfloat16_t, float32_t, float32_t, row_major, col_major)                 \
+    X(14, 32, 32, 8, float16_t, float32_t, float32_t, row_major, col_major)                   \
+    X(15, 16, 16, 8, float16_t, float32_t, float16_t, col_major, row_major)                   \
+    X(16, 16, 16, 4, float32_t, float32_t, float32_t, row_major, col_major)                   \
+    X(17, 32, 32, 4, float32_t, float32_t, float32_t, col_major, row_major)                   \
+    X(18, 16, 16, 16, bfloat16_t, float32_t, float32_t, row_major, col_major)                 \
+    X(19, 32, 32, 8, bfloat16_t, float32_t, float32_t, col_major, row_major)                  \
+    X(20, 16, 16, 16, bfloat16_t, bfloat16_t, float32_t, row_major, row_major)                \
+    X(21, 32, 16, 24, float16_t, float32_t, float32_t, row_major, col_major)
 
 extern "C" int frag_unit_gemm(int case_id, uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b,
                               const void* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,

@@ -38,6 +38,12 @@ GEMM_CASES = {
     8: (np.float64, np.float64, 0, 1, TOL_F64_OUT), 9: (np.float64, np.float64, 1, 0, TOL_F64_OUT),
     10: (np.float32, np.float32, 0, 1, 1e-5), 11: (np.float32, np.float32, 1, 0, 1e-5),
     12: (np.float16, np.float32, 0, 1, TOL_F32_OUT), 13: (np.float16, np.float32, 0, 1, TOL_F32_OUT),
+    # the reference's minimum BlockK (8 for 16-bit inputs, 4 for fp32), bfloat16 inputs, a BlockK that is not a multiple of 16
+    14: (np.float16, np.float32, 0, 1, TOL_F32_OUT), 15: (np.float16, np.float16, 1, 0, TOL_F16_OUT),
+    16: (np.float32, np.float32, 0, 1, 1e-5), 17: (np.float32, np.float32, 1, 0, 1e-5),
+    18: ("bf16", np.float32, 0, 1, TOL_F32_OUT), 19: ("bf16", np.float32, 1, 0, TOL_F32_OUT),
+    20: ("bf16", np.float32, 0, 0, 2e-2),  # bf16 compute: the accumulator is rounded to bf16 after every K step
+    21: (np.float16, np.float32, 0, 1, TOL_F32_OUT),
 }
 
 
@@ -165,13 +171,21 @@ def test_naive_fragment_gemm(unit, cid):
     if it == np.int8:
         a = G.int8_np(1, (m, k)); b = G.int8_np(2, (k, n)); c = G.int8_np(3, (m, n)).astype(np.int32) * 7
         alpha, beta = 2, 3
+    elif it == "bf16":
+        # rounded once to bfloat16: these ARE the inputs; the oracle gets them widened exactly to fp32
+        a = torch.from_numpy(G.uniform_np(1, (m, k), np.float32)).to(torch.bfloat16).to(torch.float32).numpy()
+        b = torch.from_numpy(G.uniform_np(2, (k, n), np.float32)).to(torch.bfloat16).to(torch.float32).numpy()
+        c = G.uniform_np(3, (m, n), ot)
+        alpha, beta = 2.0, 0.5
     else:
         a = G.uniform_np(1, (m, k), it); b = G.uniform_np(2, (k, n), it); c = G.uniform_np(3, (m, n), ot)
         alpha, beta = 2.0, 0.5
     sa = np.ascontiguousarray(a.T if acol else a)
     sb = np.ascontiguousarray(b.T if bcol else b)
     d = dev(np.full((m, n), MARK[ot], dtype=ot))
-    assert unit.frag_unit_gemm(cid, m, n, k, dev(sa).data_ptr(), dev(sb).data_ptr(), dev(c).data_ptr(), d.data_ptr(),
+    dev_in = (lambda x: dev(x).to(torch.bfloat16)) if it == "bf16" else dev
+    da, db = dev_in(sa), dev_in(sb)
+    assert unit.frag_unit_gemm(cid, m, n, k, da.data_ptr(), db.data_ptr(), dev(c).data_ptr(), d.data_ptr(),
                                sa.shape[1], sb.shape[1], n, n, alpha, beta, 2, 2) == 0
     ref = R.gemm(R.port(), m, n, k, sa.ravel(), sb.ravel(), c.ravel(), alpha, beta, ot, acol, bcol).reshape(m, n)
     got = d.cpu().numpy()

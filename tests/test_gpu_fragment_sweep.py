@@ -35,10 +35,11 @@ def sweep():
 
 
 def offered(kind, bk, dt):
-    """Fragments are whole mma.sync operands: 16 deep for 8- / 16-bit inputs; accumulator blocks at least 16 wide."""
+    """Fragments are whole mma.sync operands: at least 16 deep for 8-bit inputs, 8 for 16-bit, 4 for 32- / 64-bit;
+    accumulator blocks at least 16 wide."""
     if kind == 2:
         return bk % 16 == 0
-    return bk % {1: 16, 2: 16, 4: 8, 8: 4}[np.dtype(dt).itemsize] == 0
+    return bk % {1: 16, 2: 8, 4: 4, 8: 4}[np.dtype(dt).itemsize] == 0
 
 
 def rand_matrix(rows, cols, dt, seed):
