@@ -37,7 +37,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
 # (None where no capture exists yet).
 NCU_TRAFFIC_BYTES = {
-    "gemm_f16": 1.141e9,   # profiles/gemm_tc05_f16_8192.md: 1.020 GB read + 120.8 MB written (512x256 pair kernel)
+    "gemm_f16": 1.144e9,   # profiles/gemm_tc05_f16_8192.md: 1.022 GB read + 122.4 MB written (512x256 pair kernel)
     "gemm_i8": 1.416e9,    # profiles/gemm_tc05_i8_8192x8192x16384.md (256x256 pair kernel capture)
     "gemm_i8_sp24": 8.595e8,  # profiles/gemm_tc05_sp24_8192x8192x16384.md (GEMM kernel; the re-tiling pre-pass adds ~33 MB)
     "dlrm_fwd": 119.5e6,   # profiles/dlrm_dot_B16384.md
