@@ -729,6 +729,30 @@ def run_gpu_arm(args, wl):
     ms_step = ms_total / args.steps
     value = wl.value(wl.work_total, ms_step * 1e-3)
 
+    # HBM-bound workloads: a plain device-to-device copy moving the same number of bytes per launch, timed the same
+    # way (sources and destinations rotate through sets larger than L2).  The measured copy peak is a large-transfer figure; at these launch
+    # sizes a copy does not reach it either, and this figure says what does.
+    copy_same = None
+    if wl.bound == "hbm" and not args.no_copy_ref:
+        nbytes_launch = wl.bytes_per_sample * wl.work_local if hasattr(wl, "bytes_per_sample") else wl.work_local
+        half = max(int(nbytes_launch) // 2 // 4 * 4, 4)
+        if half <= (6 << 30):
+            nbuf = max(2, int((300 << 20) // half) + 1)
+            srcs = [torch.empty(half, dtype=torch.uint8, device="cuda") for _ in range(nbuf)]
+            dsts = [torch.empty(half, dtype=torch.uint8, device="cuda") for _ in range(nbuf)]
+            state = {"i": 0}
+
+            def copy_step():
+                i = state["i"]
+                dsts[i % nbuf].copy_(srcs[i % nbuf])
+                state["i"] = i + 1
+
+            for _ in range(3):
+                copy_step()
+            ms_copy, _ = timed(copy_step, args.steps)
+            copy_same = 2.0 * half / (ms_copy / args.steps * 1e-3) / 1e9
+            del srcs, dsts
+
     # end to end: host buffers through the C ABI host drivers, copies inside the timed region
     e2e = None
     if hasattr(wl, "setup_host") and getattr(wl, "has_host", True) and not args.no_e2e:
@@ -776,6 +800,9 @@ def run_gpu_arm(args, wl):
             achieved = nbytes / (ms_step * 1e-3) / 1e9
             roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                     "traffic": NCU_TRAFFIC_BYTES.get(wl.name), "peak_source": f"{peaks['_source']} (copy bandwidth)"}
+            if copy_same:
+                roof["copy_same_bytes"] = copy_same  # GB/s of torch copy_ moving the same bytes per launch
+                roof["frac_of_copy_same_bytes"] = achieved / copy_same
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": wl.scaling,
@@ -802,6 +829,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gemm_f16", choices=sorted(WORKLOADS))
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end measurement")
+    ap.add_argument("--no-copy-ref", action="store_true",
+                    help="HBM-bound workloads: skip timing a plain device copy of the same byte count")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]()

@@ -112,6 +112,11 @@ namespace b200wmma
             }
             ptx::fence_proxy_async_smem(); // the zero fills above precede any TMA write to the same tiles
             __syncthreads();
+            // Everything above touched shared memory only and may have run while the previous kernel of the stream
+            // was finishing (programmatic dependent launch); global memory is touched from here on.  This grid is
+            // fully resident, so the next kernel's CTAs may take over each SM as soon as this grid's CTAs leave it.
+            ptx::grid_dep_launch_dependents();
+            ptx::grid_dep_wait();
 
             const uint32_t stride = gridDim.x * WARPS;
             const uint32_t first  = blockIdx.x * WARPS + warp;
@@ -274,6 +279,9 @@ namespace b200wmma
                 clear_pad_rows(s);
             ptx::fence_proxy_async_smem();
             __syncwarp();
+            // shared memory only up to here (see the forward kernel): global memory is touched from here on
+            ptx::grid_dep_launch_dependents();
+            ptx::grid_dep_wait();
             if(lane == 0)
                 for(uint32_t s = 0; s < BWD_STAGES; ++s)
                     if(first + s * stride < batch)
@@ -426,6 +434,23 @@ namespace b200wmma
             return want < cap ? want : cap;
         }
 
+        // Launch with programmatic stream serialization: the kernel's prologue (barrier set-up, pad rows) may overlap
+        // the tail of the preceding kernel in the stream; the kernel itself waits for that kernel's completion
+        // (grid_dep_wait) before it touches global memory, so stream order is kept.
+        static cudaLaunchConfig_t pdl_config(cudaLaunchAttribute (&attr)[1], uint32_t grid, size_t smem, cudaStream_t stream)
+        {
+            attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cudaLaunchConfig_t cfg                             = {};
+            cfg.gridDim                                        = dim3(grid);
+            cfg.blockDim                                       = dim3(WARPS * 32);
+            cfg.dynamicSmemBytes                               = smem;
+            cfg.stream                                         = stream;
+            cfg.attrs                                          = attr;
+            cfg.numAttrs                                       = 1;
+            return cfg;
+        }
+
         // 2-D view [(batch-1)*m_stride + m rows, k columns] of a sample buffer: only real rows are covered.
         static int sample_tmap(CUtensorMap* out, const void* ptr, uint32_t m, uint32_t m_stride, uint32_t k,
                                uint32_t batch)
@@ -471,9 +496,10 @@ extern "C" int b200wmma_dlrm_fwd(const void* input, void* output, uint32_t m, ui
         attr_set = smem;
     }
     const uint32_t grid = grid_for(batch, reinterpret_cast<const void*>(dlrm_fwd_kernel), smem);
-    dlrm_fwd_kernel<<<grid, WARPS * 32, smem, as_stream(stream)>>>(tm_x, static_cast<__half*>(output), m, m_stride, k,
-                                                                    batch, out_stride, status);
-    B200_CHECK_CUDA(cudaGetLastError());
+    cudaLaunchAttribute attr[1];
+    cudaLaunchConfig_t  cfg = pdl_config(attr, grid, smem, as_stream(stream));
+    B200_CHECK_CUDA(cudaLaunchKernelEx(&cfg, dlrm_fwd_kernel, tm_x, static_cast<__half*>(output), m, m_stride, k, batch,
+                                       out_stride, status));
     return B200WMMA_OK;
 }
 
@@ -523,10 +549,11 @@ extern "C" int b200wmma_dlrm_bwd(const void* input, const void* upstream, void* 
         attr_set = smem;
     }
     const uint32_t grid = grid_for(batch, reinterpret_cast<const void*>(dlrm_bwd_kernel), smem);
-    dlrm_bwd_kernel<<<grid, WARPS * 32, smem, as_stream(stream)>>>(
-        tm_x, tm_g, static_cast<const __half*>(upstream), static_cast<__half*>(bottom_mlp_grad), m, m_stride, k, batch,
-        upstream_stride, fuse_mlp_into_row0, status);
-    B200_CHECK_CUDA(cudaGetLastError());
+    cudaLaunchAttribute attr[1];
+    cudaLaunchConfig_t  cfg = pdl_config(attr, grid, smem, as_stream(stream));
+    B200_CHECK_CUDA(cudaLaunchKernelEx(&cfg, dlrm_bwd_kernel, tm_x, tm_g, static_cast<const __half*>(upstream),
+                                       static_cast<__half*>(bottom_mlp_grad), m, m_stride, k, batch, upstream_stride,
+                                       fuse_mlp_into_row0, status));
     return B200WMMA_OK;
 }
 

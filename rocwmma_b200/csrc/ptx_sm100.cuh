@@ -43,6 +43,20 @@ namespace b200wmma
         {
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
         }
+        // Programmatic dependent launch.  launch_dependents: the next kernel of the stream, if it was launched with
+        // programmatic stream serialization, may start its CTAs once every CTA of this grid has passed this point
+        // (or exited).  grid_dep_wait: returns when the preceding grid has completed and its memory operations are
+        // visible; a no-op when the kernel was launched the ordinary way.  Everything a kernel does before
+        // grid_dep_wait overlaps the tail of its predecessor, so it must touch no global memory there.
+        __device__ __forceinline__ void grid_dep_launch_dependents()
+        {
+            asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        }
+        __device__ __forceinline__ void grid_dep_wait()
+        {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+        }
+
         __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         {
             uint32_t ok;
