@@ -76,6 +76,30 @@ namespace rocwmma
                          : "r"(a[0]), "r"(a[1]), "r"(b[1]));
         }
 
+        // OCP fp8 x fp8 -> fp32 (m16n8k16), same register orders as int8
+        ROCWMMA_DEVICE inline void mma_atom_e4m3_f32(float (&acc)[8], const uint32_t (&a)[2], const uint32_t (&b)[2])
+        {
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.e4m3.e4m3.f32 "
+                         "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                         : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])
+                         : "r"(a[0]), "r"(a[1]), "r"(b[0]));
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.e4m3.e4m3.f32 "
+                         "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                         : "+f"(acc[4]), "+f"(acc[5]), "+f"(acc[6]), "+f"(acc[7])
+                         : "r"(a[0]), "r"(a[1]), "r"(b[1]));
+        }
+        ROCWMMA_DEVICE inline void mma_atom_e5m2_f32(float (&acc)[8], const uint32_t (&a)[2], const uint32_t (&b)[2])
+        {
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.e5m2.e5m2.f32 "
+                         "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                         : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])
+                         : "r"(a[0]), "r"(a[1]), "r"(b[0]));
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.e5m2.e5m2.f32 "
+                         "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                         : "+f"(acc[4]), "+f"(acc[5]), "+f"(acc[6]), "+f"(acc[7])
+                         : "r"(a[0]), "r"(a[1]), "r"(b[1]));
+        }
+
         // fp64 (m16n8k4): a = 2 doubles, b = 2 doubles [n-half 0, n-half 1]
         ROCWMMA_DEVICE inline void mma_atom_f64(double (&acc)[8], const double (&a)[2], const double (&b)[2])
         {
@@ -124,6 +148,20 @@ namespace rocwmma
             mma_tf32_1688(acc + 4, ah, bl[1], bl[3]);
             mma_tf32_1688(acc + 4, ah, bh[1], bh[3]);
         }
+        // xfloat32: one TF32 product per atom (inputs rounded to TF32, fp32 accumulate)
+        ROCWMMA_DEVICE inline void mma_atom_xf32(float (&acc)[8], const float (&a)[4], const float (&b)[4])
+        {
+            uint32_t ah[4], bh[4];
+#pragma unroll
+            for(int i = 0; i < 4; ++i)
+            {
+                ah[i] = to_tf32(a[i]);
+                bh[i] = to_tf32(b[i]);
+            }
+            mma_tf32_1688(acc, ah, bh[0], bh[2]);
+            mma_tf32_1688(acc + 4, ah, bh[1], bh[3]);
+        }
+
         // 4 deep (m16n8k4): a = 2 floats (rows g, g + 8 at k = t), b = 2 floats [n-half 0, n-half 1]
         ROCWMMA_DEVICE inline void mma_tf32_1684(float* acc, const uint32_t (&a)[2], uint32_t b0)
         {
@@ -149,6 +187,12 @@ namespace rocwmma
             mma_tf32_1684(acc + 4, al, bh[1]);
             mma_tf32_1684(acc + 4, ah, bl[1]);
             mma_tf32_1684(acc + 4, ah, bh[1]);
+        }
+        ROCWMMA_DEVICE inline void mma_atom_xf32_k4(float (&acc)[8], const float (&a)[2], const float (&b)[2])
+        {
+            const uint32_t ah[2] = {to_tf32(a[0]), to_tf32(a[1])};
+            mma_tf32_1684(acc, ah, to_tf32(b[0]));
+            mma_tf32_1684(acc + 4, ah, to_tf32(b[1]));
         }
     } // namespace detail
 } // namespace rocwmma

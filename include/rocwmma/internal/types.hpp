@@ -9,6 +9,7 @@
 #define ROCWMMA_B200_TYPES_HPP
 
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cuda_fp16.h>
 #include <cstdint>
 
@@ -82,6 +83,54 @@ namespace rocwmma
     };
     static_assert(sizeof(bfloat16_t) == 2, "bfloat16_t must be two bytes");
 
+    // 8-bit floats in the OCP formats the tensor cores take: float8_t = e4m3, bfloat8_t = e5m2 (the reference's
+    // float8_t / bfloat8_t on its OCP targets, internal/types.hpp:48-50).  Conversions saturate to the largest
+    // finite value, like the hardware's.
+    template <__nv_fp8_interpretation_t Format>
+    struct __align__(1) fp8_base
+    {
+        unsigned char bits;
+
+        fp8_base() = default;
+        ROCWMMA_HOST_DEVICE fp8_base(float f)
+        {
+            bits = static_cast<unsigned char>(__nv_cvt_float_to_fp8(f, __NV_SATFINITE, Format));
+        }
+        ROCWMMA_HOST_DEVICE fp8_base(double f)
+            : fp8_base(static_cast<float>(f))
+        {
+        }
+        ROCWMMA_HOST_DEVICE fp8_base(int v)
+            : fp8_base(static_cast<float>(v))
+        {
+        }
+        ROCWMMA_HOST_DEVICE operator float() const
+        {
+            return __half2float(__half(__nv_cvt_fp8_to_halfraw(bits, Format)));
+        }
+    };
+    using float8_t  = fp8_base<__NV_E4M3>;
+    using bfloat8_t = fp8_base<__NV_E5M2>;
+    static_assert(sizeof(float8_t) == 1 && sizeof(bfloat8_t) == 1, "8-bit floats must be one byte");
+
+    // xfloat32_t: fp32 storage multiplied at TF32 precision (one tensor-core product instead of the three that
+    // float32_t inputs take); the reference's xfloat32_t (internal/types.hpp:62).
+    struct xfloat32_t
+    {
+        float value;
+
+        xfloat32_t() = default;
+        ROCWMMA_HOST_DEVICE xfloat32_t(float f)
+            : value(f)
+        {
+        }
+        ROCWMMA_HOST_DEVICE operator float() const
+        {
+            return value;
+        }
+    };
+    static_assert(sizeof(xfloat32_t) == 4, "xfloat32_t must be four bytes");
+
     using hfloat16_t = __half;
     using float32_t  = float;
     using float64_t  = double;
@@ -107,6 +156,9 @@ namespace rocwmma
     ROCWMMA_B200_TYPE_NAME(float16_t, "f16")
     ROCWMMA_B200_TYPE_NAME(hfloat16_t, "h16")
     ROCWMMA_B200_TYPE_NAME(bfloat16_t, "bf16")
+    ROCWMMA_B200_TYPE_NAME(float8_t, "f8")
+    ROCWMMA_B200_TYPE_NAME(bfloat8_t, "bf8")
+    ROCWMMA_B200_TYPE_NAME(xfloat32_t, "xf32")
     ROCWMMA_B200_TYPE_NAME(float32_t, "f32")
     ROCWMMA_B200_TYPE_NAME(float64_t, "f64")
     ROCWMMA_B200_TYPE_NAME(int8_t, "i8")

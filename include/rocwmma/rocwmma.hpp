@@ -9,7 +9,8 @@
 // Supported block shapes: BlockM, BlockN multiples of 16; BlockK a multiple of 16 for 8-bit
 // inputs, 8 for 16-bit, 4 for fp32 and fp64.  Supported mma_sync type pairs (input -> compute):
 // float16_t/hfloat16_t -> float32_t or the input type, bfloat16_t -> float32_t or bfloat16_t,
-// int8_t -> int32_t, float32_t -> float32_t (3xTF32), float64_t -> float64_t.
+// float8_t / bfloat8_t (OCP e4m3 / e5m2) -> float32_t, int8_t -> int32_t, xfloat32_t -> float32_t (one TF32
+// product), float32_t -> float32_t (3xTF32), float64_t -> float64_t.
 #ifndef ROCWMMA_B200_API_HPP
 #define ROCWMMA_B200_API_HPP
 
@@ -415,6 +416,42 @@ namespace rocwmma
             {
                 mma_atom_i8_i32(acc, *reinterpret_cast<const uint32_t(*)[2]>(a),
                                 *reinterpret_cast<const uint32_t(*)[2]>(b));
+            }
+        };
+        template <>
+        struct MmaAtomOp<float8_t, float32_t>
+        {
+            using AccT = float;
+            template <uint32_t KA>
+            ROCWMMA_DEVICE static inline void exec(float (&acc)[8], const float8_t* a, const float8_t* b)
+            {
+                mma_atom_e4m3_f32(acc, *reinterpret_cast<const uint32_t(*)[2]>(a),
+                                  *reinterpret_cast<const uint32_t(*)[2]>(b));
+            }
+        };
+        template <>
+        struct MmaAtomOp<bfloat8_t, float32_t>
+        {
+            using AccT = float;
+            template <uint32_t KA>
+            ROCWMMA_DEVICE static inline void exec(float (&acc)[8], const bfloat8_t* a, const bfloat8_t* b)
+            {
+                mma_atom_e5m2_f32(acc, *reinterpret_cast<const uint32_t(*)[2]>(a),
+                                  *reinterpret_cast<const uint32_t(*)[2]>(b));
+            }
+        };
+        template <>
+        struct MmaAtomOp<xfloat32_t, float32_t>
+        {
+            using AccT = float;
+            template <uint32_t KA>
+            ROCWMMA_DEVICE static inline void exec(float (&acc)[8], const xfloat32_t* a, const xfloat32_t* b)
+            {
+                if constexpr(KA == 8)
+                    mma_atom_xf32(acc, *reinterpret_cast<const float(*)[4]>(a), *reinterpret_cast<const float(*)[4]>(b));
+                else
+                    mma_atom_xf32_k4(acc, *reinterpret_cast<const float(*)[2]>(a),
+                                     *reinterpret_cast<const float(*)[2]>(b));
             }
         };
         template <>

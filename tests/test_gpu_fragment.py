@@ -44,7 +44,11 @@ GEMM_CASES = {
     18: ("bf16", np.float32, 0, 1, TOL_F32_OUT), 19: ("bf16", np.float32, 1, 0, TOL_F32_OUT),
     20: ("bf16", np.float32, 0, 0, 2e-2),  # bf16 compute: the accumulator is rounded to bf16 after every K step
     21: (np.float16, np.float32, 0, 1, TOL_F32_OUT),
+    # OCP fp8 inputs (exact products, fp32 accumulation) and xfloat32 (inputs rounded to TF32: 2^-11 relative each)
+    22: ("e4m3", np.float32, 0, 1, TOL_F32_OUT), 23: ("e5m2", np.float32, 1, 0, TOL_F32_OUT),
+    24: ("xf32", np.float32, 0, 1, 2e-3), 25: ("xf32", np.float32, 1, 0, 2e-3),
 }
+_TORCH_LOWP = {"bf16": torch.bfloat16, "e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
 
 
 @pytest.fixture(scope="module")
@@ -171,11 +175,14 @@ def test_naive_fragment_gemm(unit, cid):
     if it == np.int8:
         a = G.int8_np(1, (m, k)); b = G.int8_np(2, (k, n)); c = G.int8_np(3, (m, n)).astype(np.int32) * 7
         alpha, beta = 2, 3
-    elif it == "bf16":
-        # rounded once to bfloat16: these ARE the inputs; the oracle gets them widened exactly to fp32
-        a = torch.from_numpy(G.uniform_np(1, (m, k), np.float32)).to(torch.bfloat16).to(torch.float32).numpy()
-        b = torch.from_numpy(G.uniform_np(2, (k, n), np.float32)).to(torch.bfloat16).to(torch.float32).numpy()
+    elif it in _TORCH_LOWP:
+        # rounded once to the narrow type: these ARE the inputs; the oracle gets them widened exactly to fp32
+        a = torch.from_numpy(G.uniform_np(1, (m, k), np.float32)).to(_TORCH_LOWP[it]).to(torch.float32).numpy()
+        b = torch.from_numpy(G.uniform_np(2, (k, n), np.float32)).to(_TORCH_LOWP[it]).to(torch.float32).numpy()
         c = G.uniform_np(3, (m, n), ot)
+        alpha, beta = 2.0, 0.5
+    elif it == "xf32":
+        a = G.uniform_np(1, (m, k), np.float32); b = G.uniform_np(2, (k, n), np.float32); c = G.uniform_np(3, (m, n), ot)
         alpha, beta = 2.0, 0.5
     else:
         a = G.uniform_np(1, (m, k), it); b = G.uniform_np(2, (k, n), it); c = G.uniform_np(3, (m, n), ot)
@@ -183,7 +190,7 @@ def test_naive_fragment_gemm(unit, cid):
     sa = np.ascontiguousarray(a.T if acol else a)
     sb = np.ascontiguousarray(b.T if bcol else b)
     d = dev(np.full((m, n), MARK[ot], dtype=ot))
-    dev_in = (lambda x: dev(x).to(torch.bfloat16)) if it == "bf16" else dev
+    dev_in = (lambda x: dev(x).to(_TORCH_LOWP[it])) if it in _TORCH_LOWP else dev
     da, db = dev_in(sa), dev_in(sb)
     assert unit.frag_unit_gemm(cid, m, n, k, da.data_ptr(), db.data_ptr(), dev(c).data_ptr(), d.data_ptr(),
                                sa.shape[1], sb.shape[1], n, n, alpha, beta, 2, 2) == 0
