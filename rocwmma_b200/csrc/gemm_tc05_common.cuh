@@ -351,8 +351,9 @@ namespace b200wmma
 
         // Row-major output matrix (rows x cols, pitch ld elements) tiled in boxes of 64 bytes x 32 rows
         // with the 64-byte swizzle: the staging tiles of the TMA epilogue.
+        // row_bytes: 64 (default), or 128 with the 128-byte swizzle.
         static int make_rowbox_tmap(CUtensorMap* out, uint32_t elem_bytes, const void* ptr, uint32_t rows,
-                                    uint32_t cols, uint32_t ld)
+                                    uint32_t cols, uint32_t ld, uint32_t row_bytes = 64)
         {
             EncodeTiledFn fn = get_encode_fn();
             B200_REQUIRE(fn != nullptr, B200WMMA_ERR_CUDA, "cuTensorMapEncodeTiled not available");
@@ -360,10 +361,11 @@ namespace b200wmma
                 = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
             cuuint64_t gdim[2]    = {cols, rows};
             cuuint64_t gstride[1] = {static_cast<cuuint64_t>(ld) * elem_bytes};
-            cuuint32_t box[2]     = {64u / elem_bytes, 32u};
+            cuuint32_t box[2]     = {row_bytes / elem_bytes, 32u};
             cuuint32_t estr[2]    = {1, 1};
             CUresult   r          = fn(out, dt, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                             CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             B200_REQUIRE(r == CUDA_SUCCESS, B200WMMA_ERR_CUDA,
                          "cuTensorMapEncodeTiled (output boxes) failed with CUresult %d", static_cast<int>(r));

@@ -56,10 +56,15 @@ namespace b200wmma
         // special case.  All 32 lanes execute every step.
         // TN: columns of the accumulator being drained.  STRIDE > 1 lets several warps share one lane quadrant of an
         // accumulator: warp `first` (0 .. STRIDE-1) takes the steps first, first + STRIDE, ...
-        template <typename OutT, typename ScalarT, uint32_t TN = TILE_N, uint32_t STRIDE = 1>
+        // ROW_BYTES: bytes per row of a staging tile, 64 (TMA SWIZZLE_64B) or, for 32-bit outputs, 128 (SWIZZLE_128B:
+        // half as many row requests per byte moved).
+        template <typename OutT, typename ScalarT, uint32_t TN = TILE_N, uint32_t STRIDE = 1, uint32_t ROW_BYTES = 64>
         struct StagedDrain
         {
-            static constexpr uint32_t STEP_COLS = 64 / sizeof(OutT);
+            static constexpr uint32_t BUF_BYTES = 32 * ROW_BYTES; // one staging tile: 32 rows
+            static constexpr uint32_t CELLS     = ROW_BYTES / 16; // 16-byte cells per row
+            static_assert(ROW_BYTES == 64 || (ROW_BYTES == 128 && sizeof(OutT) == 4), "staging rows: 64 bytes, or 128 for 32-bit outputs");
+            static constexpr uint32_t STEP_COLS = ROW_BYTES / sizeof(OutT);
             static constexpr uint32_t STEPS     = TN / STEP_COLS; // of the whole accumulator
             static constexpr uint32_t MY_STEPS  = STEPS / STRIDE; // of one warp
             static_assert(STEPS % STRIDE == 0, "steps must divide evenly among the warps of a quadrant");
@@ -72,7 +77,7 @@ namespace b200wmma
                                                              uint32_t ls_begin = 0, uint32_t ls_end = 2, uint32_t buf1 = 0)
             {
                 if(buf1 == 0u)
-                    buf1 = buf0 + EPI_BUF_BYTES;
+                    buf1 = buf0 + BUF_BYTES;
                 ptx::bulk_wait_group_read<0>(); // the previous tile's last stores have read both buffers
 #pragma unroll
                 for(uint32_t ls = ls_begin; ls < ls_end && ls < MY_STEPS; ++ls)
@@ -80,7 +85,7 @@ namespace b200wmma
                     const uint32_t s = first + ls * STRIDE;
                     if(col_base + s * STEP_COLS >= n)
                         break; // steps that start right of the matrix are skipped everywhere
-                    ptx::mbar_arrive_expect_tx(cbar0 + 8 * ls, EPI_BUF_BYTES);
+                    ptx::mbar_arrive_expect_tx(cbar0 + 8 * ls, BUF_BYTES);
                     ptx::tma_load_2d(ls == 0u ? buf0 : buf1, tmap_c, static_cast<int32_t>(col_base + s * STEP_COLS),
                                      static_cast<int32_t>(row0), cbar0 + 8 * ls);
                 }
@@ -96,17 +101,19 @@ namespace b200wmma
             {
                 if(buf1 == 0u)
                 {
-                    buf1_off = buf_off + EPI_BUF_BYTES;
-                    buf1     = buf0 + EPI_BUF_BYTES;
+                    buf1_off = buf_off + BUF_BYTES;
+                    buf1     = buf0 + BUF_BYTES;
                 }
                 // cpar: bit b = parity of the next completed C load into staging buffer b (kept across tiles)
-                const uint32_t row_sw = (lane >> 1) & 3u; // 64-byte swizzle phase of this lane's row
+                // swizzle phase of this lane's row: 16-byte cell index XOR (128-byte line index mod 4 or 8)
+                const uint32_t row_sw = ROW_BYTES == 64 ? ((lane >> 1) & 3u) : (lane & 7u);
 #pragma unroll 2
                 for(uint32_t ls = 0; ls < MY_STEPS; ++ls)
                 {
                     const uint32_t s  = first + ls * STRIDE;
                     const uint32_t bi = ls & 1u;
                     uint32_t       v[STEP_COLS];
+                    static_assert(STEP_COLS == 32 || STEP_COLS == 16, "one tensor-memory load per step");
                     if constexpr(STEP_COLS == 32)
                         ptx::tmem_ld_32x32b_x32(tmem_acc + ((quad * 32u) << 16) + s * STEP_COLS, v);
                     else
@@ -135,9 +142,9 @@ namespace b200wmma
                         __syncwarp();
                     }
                     ptx::tmem_ld_wait();
-                    uint8_t* rowp = smem + (bi == 0u ? buf_off : buf1_off) + lane * 64u;
+                    uint8_t* rowp = smem + (bi == 0u ? buf_off : buf1_off) + lane * ROW_BYTES;
 #pragma unroll
-                    for(uint32_t q = 0; q < 4; ++q)
+                    for(uint32_t q = 0; q < CELLS; ++q)
                     {
                         uint4* cell = reinterpret_cast<uint4*>(rowp + ((q ^ row_sw) << 4));
                         uint4  cv   = make_uint4(0, 0, 0, 0);
@@ -174,7 +181,7 @@ namespace b200wmma
                         if(read_c && ls + 2 < MY_STEPS && col_base + (s + 2 * STRIDE) * STEP_COLS < n)
                         {
                             ptx::bulk_wait_group_read<0>(); // the store has read the buffer: refill it with C
-                            ptx::mbar_arrive_expect_tx(cbar0 + 8 * bi, EPI_BUF_BYTES);
+                            ptx::mbar_arrive_expect_tx(cbar0 + 8 * bi, BUF_BYTES);
                             ptx::tma_load_2d(bi == 0u ? buf0 : buf1, tmap_c,
                                              static_cast<int32_t>(col_base + (s + 2 * STRIDE) * STEP_COLS),
                                              static_cast<int32_t>(row0), cbar0 + 8 * bi);

@@ -94,11 +94,11 @@ namespace b200wmma
         CUtensorMap tm_c = tm_a, tm_d = tm_a; // placeholders, never dereferenced when vec_ok == 0
         if(vec_ok != 0)
         {
-            if(int e = make_rowbox_tmap(&tm_d, 4, d, m, n, ldd))
+            if(int e = make_rowbox_tmap(&tm_d, 4, d, m, n, ldd, EPI_ROW_BYTES))
                 return e;
             tm_c = tm_d;
             if(c)
-                if(int e = make_rowbox_tmap(&tm_c, 4, c, m, n, ldc))
+                if(int e = make_rowbox_tmap(&tm_c, 4, c, m, n, ldc, EPI_ROW_BYTES))
                     return e;
         }
 

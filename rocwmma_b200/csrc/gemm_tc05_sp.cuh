@@ -26,8 +26,9 @@
 // ~620 clocks of its own instruction latency per 448 clocks of tensor work and the tensor pipe
 // idled a quarter of the time; with 256 K the per-slab overhead is paid half as often.
 //
-// Shared memory: 3 stages x 68 KiB leave no room for the epilogue's staging tiles (32 KiB), so
-// those alias the A region of the last stage.  While a tile is drained that stage is not refilled:
+// Shared memory: 3 stages x 68 KiB leave no room for the epilogue's staging tiles (eight warps x two tiles
+// of 32 rows x 128 bytes), so those alias the A and B regions of the last stage (the last warp's second tile
+// has 4 KiB of its own).  While a tile is drained that stage is not refilled:
 // the producer waits for a counter the epilogue warps bump once their TMA stores have read the
 // tiles (two stages = 136 KiB of the next tile are prefetched meanwhile).
 //
@@ -66,14 +67,17 @@ namespace b200wmma
         constexpr uint32_t TMEM_COLS     = 512;
         constexpr uint32_t E_COL0        = 2 * TILE_N; // metadata columns: E_COL0 + 16 * stage + 8 * K half + 4 * sub-tile
         constexpr uint32_t GROUP_M       = 8;
-        constexpr uint32_t EPI_BUF_BYTES = tc05q::EPI_BUF_BYTES;
-        constexpr uint32_t EPI_BYTES     = EPI_WARPS * 2 * EPI_BUF_BYTES; // aliases the A region of the last stage
+        constexpr uint32_t EPI_ROW_BYTES = 128; // staging tiles: 32 rows x 128 bytes, TMA SWIZZLE_128B
+        constexpr uint32_t EPI_BUF_BYTES = 32 * EPI_ROW_BYTES;
+        constexpr uint32_t EPI_BYTES     = EPI_WARPS * EPI_BUF_BYTES; // first staging tiles: alias the A region of the last stage
+        constexpr uint32_t EPI_IN_B      = B_STAGE_BYTES / EPI_BUF_BYTES; // second staging tiles that fit in its B region
+        constexpr uint32_t EPI_EXTRA     = (EPI_WARPS - EPI_IN_B) * EPI_BUF_BYTES; // the rest have memory of their own
         constexpr uint32_t EPI_STAGE     = STAGES - 1;
         constexpr uint32_t E_PACKED_ROWS = E_STAGE_BYTES / 128; // 128-byte rows of one re-tiled metadata block
-        constexpr uint32_t MISC_BYTES    = 512;
-        constexpr uint32_t SMEM_BYTES    = 1024 + STAGES * STAGE_BYTES + MISC_BYTES;
+        constexpr uint32_t MISC_BYTES    = 1024;
+        constexpr uint32_t SMEM_BYTES    = 1024 + STAGES * STAGE_BYTES + MISC_BYTES + EPI_EXTRA;
         static_assert(E_COL0 + 16 * STAGES <= TMEM_COLS, "metadata does not fit beside the accumulators");
-        static_assert(EPI_BYTES <= A_STAGE_BYTES, "staging tiles must fit in one A stage");
+        static_assert(EPI_BYTES <= A_STAGE_BYTES && EPI_IN_B <= EPI_WARPS, "staging tiles must fit in one A stage");
         static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 
         // E_PACKED: the metadata comes from a re-tiled copy (repack_meta_kernel) instead of the caller's
@@ -111,6 +115,8 @@ namespace b200wmma
             const uint32_t     smem_b     = smem_a + STAGES * A_STAGE_BYTES;
             const uint32_t     smem_e     = smem_b + STAGES * B_STAGE_BYTES;
             const uint32_t     epi_off    = EPI_STAGE * A_STAGE_BYTES;
+            const uint32_t     epi_b_off  = STAGES * A_STAGE_BYTES + EPI_STAGE * B_STAGE_BYTES; // B region of the same stage
+            const uint32_t     epi_x_off  = STAGES * STAGE_BYTES + MISC_BYTES; // staging tiles that alias nothing
             const uint32_t     misc_off   = STAGES * STAGE_BYTES;
             const uint32_t     bar_base   = base + misc_off;
             const uint32_t     full_bar   = bar_base; // STAGES x 8 (leader's copy in use)
@@ -189,7 +195,7 @@ namespace b200wmma
                                 break;
                             if(stage == EPI_STAGE && iter != 0u)
                             {
-                                // this stage's A region doubles as the epilogue's staging tiles: every epilogue
+                                // this stage's A and B regions double as the epilogue's staging tiles: every epilogue
                                 // warp must have finished with them for all earlier tiles (bounded wait)
                                 const uint64_t t0 = ptx::globaltimer_ns();
                                 uint32_t       spins = 0;
@@ -339,10 +345,14 @@ namespace b200wmma
                 const uint32_t quad    = warp & 3u; // lane quadrant this warp may read
                 const uint32_t j       = e >> 2; // accumulator: warps 2-5 -> 0, warps 6-9 -> 1
                 const bool     read_c  = (beta != 0) && (c != nullptr);
-                const uint32_t buf_off = epi_off + e * 2u * EPI_BUF_BYTES;
+                const uint32_t buf_off = epi_off + e * EPI_BUF_BYTES; // first tile: in the A region of the last stage
                 const uint32_t buf0    = base + buf_off;
+                // second tile: in the B region of that stage, or (the last warp) in memory of its own
+                const uint32_t buf1_off
+                    = e < EPI_IN_B ? epi_b_off + e * EPI_BUF_BYTES : epi_x_off + (e - EPI_IN_B) * EPI_BUF_BYTES;
+                const uint32_t buf1    = base + buf1_off;
                 const uint32_t cbar0   = cbar_base + e * 16u;
-                using Drain            = tc05q::StagedDrain<int32_t, int32_t, TILE_N>;
+                using Drain            = tc05q::StagedDrain<int32_t, int32_t, TILE_N, 1, EPI_ROW_BYTES>;
                 uint32_t iter = 0, cpar = 0;
                 bool     ok   = true;
                 for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++iter)
@@ -361,12 +371,12 @@ namespace b200wmma
                     // the staging tiles share memory with an operand stage: only now, with every MMA of the
                     // tile retired, may anything (the first C tiles included) be written there
                     if(staged && read_c && lane == 0)
-                        Drain::prefetch_c(&tmap_c, buf0, cbar0, col_base, row0, n);
+                        Drain::prefetch_c(&tmap_c, buf0, cbar0, col_base, row0, n, 0, 0, 2, buf1);
                     const uint32_t tmem_acc = tmem_base + j * TILE_N;
                     if(staged)
                         ok = Drain::run(tmem_acc, quad, lane, smem, buf_off, buf0, cbar0, &tmap_c, &tmap_d, col_base, row0, n,
                                         alpha, beta, read_c, cpar, cta_abort, status,
-                                        (ROLE_EPILOGUE << 24) | (1u << 20) | blockIdx.x);
+                                        (ROLE_EPILOGUE << 24) | (1u << 20) | blockIdx.x, 0, buf1_off, buf1);
                     else if(vec_ok == 0)
                         drain_accumulator<int32_t, int32_t, TILE_N>(tmem_acc, quad, lane, row_base, col_base, m, n, c, d, ldc,
                                                                     ldd, alpha, beta, read_c, 0);
