@@ -312,6 +312,28 @@ int b200wmma_gemv_f64_host(b200wmma_ctx* ctx, uint32_t m, uint32_t n, const doub
                            uint32_t lda, int layout_a, const double* x, double* y,
                            double alpha, double beta);
 
+/* ------------------------------------------------------------------------------------------
+ * Multi-GPU plumbing: one process per GPU.  The reference is single-GPU; its paths shard with no
+ * exchange after the kernel - GEMM by blocks of N columns (B column-major and C / D are split, A is
+ * needed whole by every rank), DLRM by batch, GEMV by rows of A (x is needed whole) - so the only
+ * communication is one broadcast before the kernels, done here with NCCL.
+ *
+ * Rank 0 calls b200wmma_mg_unique_id and ships the B200WMMA_MG_ID_BYTES bytes to the other ranks by any
+ * means (a file, MPI, a socket); every rank then calls b200wmma_mg_create with the device it will use
+ * current.  b200wmma_mg_broadcast works in place on device memory, asynchronously on `stream`.
+ * NCCL is opened at run time (libnccl.so.2); without it these calls return B200WMMA_ERR_UNSUPPORTED.
+ * b200wmma_shard_range gives rank `index` of `parts` its contiguous share of `total` units, which
+ * must split into whole granules (e.g. 16 columns, one sample, one row).
+ * ------------------------------------------------------------------------------------------ */
+#define B200WMMA_MG_ID_BYTES 128
+typedef struct b200wmma_mg b200wmma_mg;
+int b200wmma_mg_unique_id(void* id_out);
+int b200wmma_mg_create(b200wmma_mg** out_mg, const void* id, int rank, int nranks);
+int b200wmma_mg_broadcast(b200wmma_mg* mg, void* buf, size_t bytes, int root, void* stream);
+int b200wmma_mg_destroy(b200wmma_mg* mg);
+int b200wmma_shard_range(uint64_t total, uint32_t parts, uint32_t index, uint32_t granule,
+                         uint64_t* begin, uint64_t* count);
+
 #ifdef __cplusplus
 }
 #endif

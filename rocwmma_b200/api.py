@@ -266,3 +266,49 @@ class HostContext:
     def gemv(self, m, n, a, lda, x, y, alpha, beta, layout_a=ROW_MAJOR, double=False):
         fn = lib().b200wmma_gemv_f64_host if double else lib().b200wmma_gemv_f32_host
         check(fn(self._h, m, n, self._hp(a), lda, layout_a, self._hp(x), self._hp(y), alpha, beta))
+
+
+def shard_range(total, parts, index, granule=1):
+    """(begin, count) of part `index` of `parts` over `total` units (b200wmma_shard_range)."""
+    begin, count = C.c_uint64(), C.c_uint64()
+    check(lib().b200wmma_shard_range(total, parts, index, granule, C.byref(begin), C.byref(count)))
+    return begin.value, count.value
+
+
+class MultiGpu:
+    """One rank of a one-process-per-GPU group on the library's own NCCL plumbing (b200wmma_mg_*).
+
+    Rank 0 calls MultiGpu.unique_id() and ships the bytes to the other ranks by any means; every rank then
+    constructs MultiGpu(id_bytes, rank, nranks) with its device current."""
+
+    ID_BYTES = 128
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = C.create_string_buffer(MultiGpu.ID_BYTES)
+        check(lib().b200wmma_mg_unique_id(buf))
+        return buf.raw
+
+    def __init__(self, id_bytes: bytes, rank: int, nranks: int):
+        if len(id_bytes) != self.ID_BYTES:
+            raise ValueError("id_bytes must be the 128 bytes of MultiGpu.unique_id()")
+        self._h = C.c_void_p()
+        check(lib().b200wmma_mg_create(C.byref(self._h), id_bytes, rank, nranks))
+        self.rank, self.nranks = rank, nranks
+
+    def broadcast(self, t, root=0):
+        """In place, on the current torch stream."""
+        if not t.is_cuda or not t.is_contiguous():
+            raise ValueError("broadcast needs a contiguous CUDA tensor")
+        check(lib().b200wmma_mg_broadcast(self._h, _ptr(t), t.numel() * t.element_size(), root, _stream()))
+
+    def close(self):
+        if self._h:
+            check(lib().b200wmma_mg_destroy(self._h))
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -72,13 +72,27 @@ def test_no_cpu_fallback_in_product_sources():
     (lambda L: L.b200wmma_gemm_i8_sp24_packed(256, 256, 256, 16, None, 16, None, 16, 128, 256, 256, 256, 1, 0, None), 1),
     (lambda L: L.b200wmma_simple_sgemm(100, 64, 64, 16, 16, 16, 16, 64, 64, 64, 64, 1.0, 1.0, None), 2),
     (lambda L: L.b200wmma_simple_dgemm(64, 64, 64, 16, 16, None, 16, 64, 64, 64, 64, 1.0, 1.0, None), 1),
+    (lambda L: L.b200wmma_mg_unique_id(None), 1),
+    (lambda L: L.b200wmma_mg_create(None, None, 0, 1), 1),
+    (lambda L: L.b200wmma_mg_broadcast(None, 16, 16, 0, None), 1),
+    (lambda L: L.b200wmma_shard_range(1000, 8, 0, 16, C.byref(C.c_uint64()), C.byref(C.c_uint64())), 2),
+    (lambda L: L.b200wmma_shard_range(1024, 8, 8, 16, C.byref(C.c_uint64()), C.byref(C.c_uint64())), 1),
 ], ids=["bad_layout_flag", "col_major_a_lda_lt_m", "zero_m", "null_c_with_beta", "lda_too_small",
         "lda_not_16B", "f64_odd_k", "gemv_zero_m", "gemv_lda_small", "dlrm_rows_beyond_stride", "dlrm_k_not_16",
         "dlrm_out_stride_small", "dlrm_bwd_null_upstream", "sp24_k_not_32", "i4_workspace_small", "ctx_null",
         "bf16_bad_layout_flag", "fp8_lda_too_small", "fp8_bad_format", "f32_layout_unsupported", "f32_workspace_small",
         "f32_k_not_4", "repack_k_not_128", "repack_dest_small", "sp24_packed_k_not_128", "sp24_packed_null_meta",
-        "simple_sgemm_m_not_16", "simple_dgemm_null_c"])
+        "simple_sgemm_m_not_16", "simple_dgemm_null_c", "mg_id_null", "mg_create_null", "mg_broadcast_null_handle",
+        "shard_uneven", "shard_bad_index"])
 def test_argument_checks(call, code):
     L = _lib.lib()
     assert call(L) == code
     assert L.b200wmma_last_error_string()  # a message is always recorded
+
+
+def test_shard_range_and_destroy_of_null():
+    L = _lib.lib()
+    begin, count = C.c_uint64(), C.c_uint64()
+    assert L.b200wmma_shard_range(8192, 8, 3, 16, C.byref(begin), C.byref(count)) == 0
+    assert (begin.value, count.value) == (3072, 1024)
+    assert L.b200wmma_mg_destroy(None) == 0  # like free(NULL)
