@@ -729,6 +729,21 @@ def run_gpu_arm(args, wl):
     ms_step = ms_total / args.steps
     value = wl.value(wl.work_total, ms_step * 1e-3)
 
+    # Tensor-bound workloads: the same step repeated for a few seconds.  The timed K steps above are a burst (the part
+    # has not settled under its power cap yet); this is the rate it holds, to set beside the sustained library figure.
+    sustained = None
+    if wl.bound == "tensor" and args.sustained_seconds > 0:
+        per_batch = max(10, int(0.25 / max(ms_step * 1e-3, 1e-6)))
+        done, ms_acc = 0, 0.0
+        # the batch count comes from the (rank-reduced) step time, so every rank runs the same number of batches
+        batches = max(1, int(args.sustained_seconds / (per_batch * ms_step * 1e-3) + 0.5))
+        for _ in range(batches):
+            ms_b, _ = timed(wl.step, per_batch)
+            ms_acc += ms_b
+            done += per_batch
+        sustained = {"value": wl.value(wl.work_total, ms_acc / done * 1e-3), "unit": wl.unit, "launches": done,
+                     "seconds": ms_acc * 1e-3}
+
     # HBM-bound workloads: a plain device-to-device copy moving the same number of bytes per launch, timed the same
     # way (sources and destinations rotate through sets larger than L2).  The measured copy peak is a large-transfer figure; at these launch
     # sizes a copy does not reach it either, and this figure says what does.
@@ -813,6 +828,11 @@ def run_gpu_arm(args, wl):
         }
         if e2e:
             line["e2e"] = e2e
+        if sustained:
+            ref = peaks.get("bf16_tflops_sustained")
+            if ref and wl.dtype == "f16":
+                sustained["frac_of_sustained_peak"] = sustained["value"] / ref  # measured cuBLAS bf16 sustained loop
+            line["sustained"] = sustained
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(wl)
         print(json.dumps(line), flush=True)
@@ -829,6 +849,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gemm_f16", choices=sorted(WORKLOADS))
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end measurement")
+    ap.add_argument("--sustained-seconds", type=float, default=3.0,
+                    help="tensor-bound workloads: also report the rate held over this many seconds of back-to-back steps (0 = skip)")
     ap.add_argument("--no-copy-ref", action="store_true",
                     help="HBM-bound workloads: skip timing a plain device copy of the same byte count")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
