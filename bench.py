@@ -809,6 +809,14 @@ def run_gpu_arm(args, wl):
             roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s" if wl.dtype != "i8" else "TOP/s",
                     "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(wl.name),
                     "peak_source": f"{peaks['_source']} ({peak_note})"}
+            # the vendor's dense figures, for context: 2250 TFLOP/s 16-bit, 4500 fp8 / int8, 9000 for 2:4-sparse int8,
+            # 1125 / 3 for fp32 through three TF32 products, 40 fp64
+            nominal = {"f16": 2250.0, "bf16": 2250.0, "fp8": 4500.0, "i4": 4500.0, "f32": 375.0, "f64": 40.0}.get(wl.dtype)
+            if wl.dtype == "i8":
+                nominal = 9000.0 if getattr(wl, "variant", "") == "sp24" else 4500.0
+            if nominal:
+                roof["nominal_peak"] = nominal
+                roof["frac_of_nominal"] = achieved / nominal
         else:
             peak = peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"])
             nbytes = wl.bytes_per_sample * wl.work_local if hasattr(wl, "bytes_per_sample") else wl.work_local
@@ -818,6 +826,8 @@ def run_gpu_arm(args, wl):
             if copy_same:
                 roof["copy_same_bytes"] = copy_same  # GB/s of torch copy_ moving the same bytes per launch
                 roof["frac_of_copy_same_bytes"] = achieved / copy_same
+            roof["nominal_peak"] = 8000.0  # GB/s, the vendor's HBM3e figure
+            roof["frac_of_nominal"] = achieved / 8000.0
         line = {
             "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": wl.scaling,
