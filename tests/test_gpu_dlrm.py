@@ -209,3 +209,43 @@ def test_dlrm_full_size_config():
     g = grad[sel].cpu().numpy()
     g[:, m:] = np.nan
     check_bwd(g, None, xs, ups, rg, rm, True)
+
+
+def test_dlrm_back_to_back_launches_keep_stream_order():
+    """The kernels are launched with programmatic stream serialization: a launch may start while its predecessor
+    in the stream is finishing, but must not touch global memory before that kernel has completed.  A chain with
+    write-after-write (two forwards into one output) and read-after-write (a backward fed by the forward's output,
+    a forward fed by the backward's gradient) hazards, issued without any host synchronisation in between and
+    repeated, must give what the same calls give one at a time."""
+    b, m, k, ms = 4096, 27, 128, 32
+    w = k + m * (m - 1) // 2
+    stride = 480
+    x1 = G.normal_np(11, (b, m, k), 0.25, np.float16)
+    x2 = G.normal_np(12, (b, m, k), 0.25, np.float16)
+    d1, d2 = dev(pad_rows(x1, ms)), dev(pad_rows(x2, ms))
+    out = nan_filled((b, stride), torch.float16)
+    grad = torch.zeros((b, ms, k), dtype=torch.float16, device="cuda")
+    out2 = nan_filled((b, stride), torch.float16)
+
+    def chain():
+        api.dlrm_dot_fwd(d1, out, m, ms, k, b, stride)                       # out = f(x1)
+        api.dlrm_dot_fwd(d2, out, m, ms, k, b, stride)                       # WAW: out = f(x2)
+        api.dlrm_dot_bwd(d2, out, grad, None, m, ms, k, b, stride, False)    # RAW: upstream = out
+        api.dlrm_dot_fwd(grad, out2, m, ms, k, b, stride)                    # RAW: input = grad (pad rows stay zero)
+
+    for _ in range(5):
+        chain()
+    torch.cuda.synchronize()
+    assert_status_ok()
+    got_out, got_grad, got_out2 = out.cpu().numpy(), grad.cpu().numpy(), out2.cpu().numpy()
+    # the same calls, each followed by a synchronisation
+    out_s = nan_filled((b, stride), torch.float16)
+    grad_s = torch.zeros((b, ms, k), dtype=torch.float16, device="cuda")
+    out2_s = nan_filled((b, stride), torch.float16)
+    api.dlrm_dot_fwd(d2, out_s, m, ms, k, b, stride); torch.cuda.synchronize()
+    api.dlrm_dot_bwd(d2, out_s, grad_s, None, m, ms, k, b, stride, False); torch.cuda.synchronize()
+    api.dlrm_dot_fwd(grad_s, out2_s, m, ms, k, b, stride); torch.cuda.synchronize()
+    assert np.array_equal(got_out, out_s.cpu().numpy())
+    assert np.array_equal(got_grad, grad_s.cpu().numpy())
+    assert np.array_equal(got_out2, out2_s.cpu().numpy(), equal_nan=True)
+    check_fwd(got_out, x2, R.dlrm_fwd(R.port(), x2, m, k, b))
