@@ -331,6 +331,17 @@ int b200wmma_mg_unique_id(void* id_out);
 int b200wmma_mg_create(b200wmma_mg** out_mg, const void* id, int rank, int nranks);
 int b200wmma_mg_broadcast(b200wmma_mg* mg, void* buf, size_t bytes, int root, void* stream);
 int b200wmma_mg_destroy(b200wmma_mg* mg);
+int b200wmma_mg_rank(const b200wmma_mg* mg); /* -1 for a null handle */
+int b200wmma_mg_size(const b200wmma_mg* mg); /*  0 for a null handle */
+/* b200wmma_gemm_f16_host for a column-sharded GEMM (A row-major, B column-major, C / D row-major): n, b, c, d are this
+ * rank's block of columns; A is needed whole by every rank, so only rank `root` reads its host copy `a` (ignored
+ * elsewhere) and each row block is broadcast over NCCL inside the copy / compute pipeline.  root = -1: every rank
+ * holds A on the host; row block i (1024 rows) is uploaded and broadcast by rank i mod nranks, which shares out the
+ * upload too.  Collective: every rank of `mg` makes the call with the same m, k, lda, root. */
+int b200wmma_gemm_f16_host_mg(b200wmma_ctx* ctx, b200wmma_mg* mg, int root, uint32_t m, uint32_t n, uint32_t k,
+                              const void* a, const void* b, const void* c, void* d,
+                              uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                              float alpha, float beta, int out_type);
 int b200wmma_shard_range(uint64_t total, uint32_t parts, uint32_t index, uint32_t granule,
                          uint64_t* begin, uint64_t* count);
 

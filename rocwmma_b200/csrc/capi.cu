@@ -182,6 +182,7 @@ struct b200wmma_ctx
     static constexpr int NBUF = 4;
     cudaStream_t         stream    = nullptr; // compute stream (and the only one for the small drivers)
     cudaStream_t         s_in = nullptr, s_out = nullptr; // copy-in / copy-out streams of the pipelined GEMM driver
+    cudaStream_t         s_bc = nullptr; // broadcasts of the multi-GPU GEMM driver (created on first use)
     std::vector<cudaEvent_t> events;      // reusable, timing disabled
     void*                buf[NBUF] = {nullptr, nullptr, nullptr, nullptr};
     size_t               cap[NBUF] = {0, 0, 0, 0};
@@ -246,11 +247,17 @@ namespace
     // (copy-out stream).  Row blocks of a row-major A / C / D are contiguous, and rows of a GEMM are
     // independent, so the copies of block i+1 and of block i-1 overlap the kernel of block i and the two
     // copy directions overlap each other.  `launch(rows, a_dev, c_dev, d_dev)` enqueues one block.
+    // With a multi-GPU handle (`mg`), A is the operand every rank needs whole: only rank `root` uploads it from its
+    // host copy, block by block, and each block is broadcast to the other ranks over NCCL on the copy-in stream
+    // (NVLink instead of one PCIe upload per rank); `a` is ignored on the other ranks.  root = -1: every rank holds A
+    // on the host, and row block i is uploaded and broadcast by rank i mod nranks, so the upload is shared out as well.
+    // Every rank must make the call.
     template <typename Launch>
     int gemm_host_pipeline(b200wmma_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b,
                            const void* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
-                           size_t in_es, size_t out_es, bool use_c, Launch launch)
+                           size_t in_es, size_t out_es, bool use_c, Launch launch, b200wmma_mg* mg = nullptr, int root = 0)
     {
+        const int my_rank = mg ? b200wmma_mg_rank(mg) : 0, nranks = mg ? b200wmma_mg_size(mg) : 1;
         const size_t ba = extent(m, k, lda) * in_es, bb = extent(n, k, ldb) * in_es;
         const size_t bc = extent(m, n, ldc) * out_es, bd = extent(m, n, ldd) * out_es;
         if(int e = ctx_reserve(ctx, 0, ba)) return e;
@@ -259,7 +266,9 @@ namespace
         if(int e = ctx_reserve(ctx, 3, bd)) return e;
         const uint32_t block_rows = 1024; // 64 pair tiles of 512 x 256 at n = 8192: one round of the GEMM kernel
         const uint32_t blocks     = (m + block_rows - 1) / block_rows;
-        if(int e = ctx_events(ctx, 2 * static_cast<size_t>(blocks) + 1)) return e;
+        if(int e = ctx_events(ctx, 3 * static_cast<size_t>(blocks) + 1)) return e;
+        if(mg && !ctx->s_bc)
+            B200_CHECK_CUDA(cudaStreamCreateWithFlags(&ctx->s_bc, cudaStreamNonBlocking));
         char*       da = static_cast<char*>(ctx->buf[0]);
         char*       dc = static_cast<char*>(ctx->buf[2]);
         char*       dd = static_cast<char*>(ctx->buf[3]);
@@ -273,7 +282,24 @@ namespace
             const uint32_t r0 = i * block_rows, rows = (m - r0 < block_rows) ? m - r0 : block_rows;
             const size_t   oa = static_cast<size_t>(r0) * lda * in_es, oc = static_cast<size_t>(r0) * ldc * out_es,
                          od = static_cast<size_t>(r0) * ldd * out_es;
-            B200_CHECK_CUDA(cudaMemcpyAsync(da + oa, ha + oa, extent(rows, k, lda) * in_es, cudaMemcpyHostToDevice, ctx->s_in));
+            const int blk_root = root >= 0 ? root : static_cast<int>(i % static_cast<uint32_t>(nranks));
+            if(mg == nullptr || my_rank == blk_root)
+                B200_CHECK_CUDA(cudaMemcpyAsync(da + oa, ha + oa, extent(rows, k, lda) * in_es, cudaMemcpyHostToDevice, ctx->s_in));
+            if(mg)
+            {
+                // the broadcasts run on a stream of their own, so that this rank's later uploads do not queue behind
+                // a broadcast that waits for another rank's upload
+                cudaEvent_t ev_up = ctx->events[2 * static_cast<size_t>(blocks) + 1 + i];
+                if(my_rank == blk_root)
+                {
+                    B200_CHECK_CUDA(cudaEventRecord(ev_up, ctx->s_in));
+                    B200_CHECK_CUDA(cudaStreamWaitEvent(ctx->s_bc, ev_up, 0));
+                }
+                if(int e = b200wmma_mg_broadcast(mg, da + oa, extent(rows, k, lda) * in_es, blk_root, ctx->s_bc))
+                    return e;
+                B200_CHECK_CUDA(cudaEventRecord(ev_up, ctx->s_bc)); // reused: now "block i of A is on this device"
+                B200_CHECK_CUDA(cudaStreamWaitEvent(ctx->stream, ev_up, 0));
+            }
             if(use_c)
                 B200_CHECK_CUDA(cudaMemcpyAsync(dc + oc, hc + oc, extent(rows, n, ldc) * out_es, cudaMemcpyHostToDevice, ctx->s_in));
             cudaEvent_t ev_in = ctx->events[2 * i], ev_done = ctx->events[2 * i + 1];
@@ -287,6 +313,8 @@ namespace
         }
         B200_CHECK_CUDA(cudaStreamSynchronize(ctx->s_out));
         B200_CHECK_CUDA(cudaStreamSynchronize(ctx->s_in));
+        if(mg)
+            B200_CHECK_CUDA(cudaStreamSynchronize(ctx->s_bc));
         return finish(ctx);
     }
 }
@@ -332,6 +360,8 @@ extern "C" int b200wmma_ctx_destroy(b200wmma_ctx* ctx)
         cudaStreamDestroy(ctx->stream);
     if(ctx->s_in)
         cudaStreamDestroy(ctx->s_in);
+    if(ctx->s_bc)
+        cudaStreamDestroy(ctx->s_bc);
     if(ctx->s_out)
         cudaStreamDestroy(ctx->s_out);
     delete ctx;
@@ -365,6 +395,33 @@ extern "C" int b200wmma_gemm_f16_host(b200wmma_ctx* ctx, uint32_t m, uint32_t n,
                                                               use_c ? beta : 0.0f, B200WMMA_ROW_MAJOR, B200WMMA_COL_MAJOR,
                                                               B200WMMA_ROW_MAJOR, out_type, ctx->stream);
                               });
+}
+
+extern "C" int b200wmma_gemm_f16_host_mg(b200wmma_ctx* ctx, b200wmma_mg* mg, int root, uint32_t m, uint32_t n, uint32_t k,
+                                         const void* a, const void* b, const void* c, void* d, uint32_t lda, uint32_t ldb,
+                                         uint32_t ldc, uint32_t ldd, float alpha, float beta, int out_type)
+{
+    clear_error();
+    if(int e = ctx_check(ctx))
+        return e;
+    B200_REQUIRE(mg, B200WMMA_ERR_INVALID_ARG, "gemm_f16_host_mg: mg must be a live handle");
+    B200_REQUIRE(root >= -1 && root < b200wmma_mg_size(mg), B200WMMA_ERR_INVALID_ARG, "gemm_f16_host_mg: bad root %d", root);
+    const bool needs_a = root < 0 || b200wmma_mg_rank(mg) == root;
+    B200_REQUIRE((a || !needs_a) && b && d && m && n && k, B200WMMA_ERR_INVALID_ARG,
+                 "gemm_f16_host_mg: null pointer or zero size");
+    B200_REQUIRE(out_type == 0 || out_type == 1, B200WMMA_ERR_INVALID_ARG, "gemm_f16_host_mg: bad out_type");
+    B200_REQUIRE(lda >= k && ldb >= k && ldd >= n && ldc >= n, B200WMMA_ERR_INVALID_ARG,
+                 "gemm_f16_host_mg: leading dimension too small");
+    const size_t osz   = out_type == B200WMMA_OUT_F16 ? 2 : 4;
+    const bool   use_c = c != nullptr && beta != 0.0f;
+    B200_REQUIRE(c || beta == 0.0f, B200WMMA_ERR_INVALID_ARG, "gemm_f16_host_mg: c may be null only when beta == 0");
+    return gemm_host_pipeline(
+        ctx, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, 2, osz, use_c,
+        [&](uint32_t rows, const void* da, const void* dc, void* dd) {
+            return launch_gemm_tc05_f16(rows, n, k, da, ctx->buf[1], dc, dd, lda, ldb, ldc, ldd, alpha, use_c ? beta : 0.0f,
+                                        B200WMMA_ROW_MAJOR, B200WMMA_COL_MAJOR, B200WMMA_ROW_MAJOR, out_type, ctx->stream);
+        },
+        mg, root);
 }
 
 extern "C" int b200wmma_gemm_i8_host(b200wmma_ctx* ctx, uint32_t m, uint32_t n, uint32_t k,

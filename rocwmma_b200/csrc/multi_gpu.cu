@@ -153,6 +153,16 @@ extern "C" int b200wmma_mg_destroy(b200wmma_mg* mg)
     return B200WMMA_OK;
 }
 
+extern "C" int b200wmma_mg_rank(const b200wmma_mg* mg)
+{
+    return mg ? mg->rank : -1;
+}
+
+extern "C" int b200wmma_mg_size(const b200wmma_mg* mg)
+{
+    return mg ? mg->nranks : 0;
+}
+
 // Contiguous, equally sized share [begin, begin + count) of `total` units for part `index` of `parts`; `total` must be
 // a multiple of parts * granule (granule: the unit the kernels want whole, e.g. 16 columns).
 extern "C" int b200wmma_shard_range(uint64_t total, uint32_t parts, uint32_t index, uint32_t granule, uint64_t* begin,

@@ -96,3 +96,4 @@ def test_shard_range_and_destroy_of_null():
     assert L.b200wmma_shard_range(8192, 8, 3, 16, C.byref(begin), C.byref(count)) == 0
     assert (begin.value, count.value) == (3072, 1024)
     assert L.b200wmma_mg_destroy(None) == 0  # like free(NULL)
+    assert L.b200wmma_mg_rank(None) == -1 and L.b200wmma_mg_size(None) == 0

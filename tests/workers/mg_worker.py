@@ -42,6 +42,23 @@ def main():
     torch.cuda.synchronize()
     st, detail = api.device_status()
     assert st == 0, (st, detail)
+    # the host-buffer driver of the same shard: only rank 0 hands over A, the library ships it inside its pipeline
+    ctx = api.HostContext()
+    hb = np.ascontiguousarray(b.T[col0:col0 + ncols]); hc = np.ascontiguousarray(c[:, col0:col0 + ncols])
+    hd = np.full((m, ncols), np.float16(np.nan))
+    for _ in range(2):  # twice: the cached device buffers and events are reused
+        ctx.gemm_f16_mg(mg, 0, m, ncols, k, a if rank == 0 else None, hb, hc, hd, k, k, ncols, ncols, 1.0, 1.0, 0)
+    assert np.array_equal(hd, ds.cpu().numpy()), "host-buffer multi-GPU driver differs from the device-pointer call"
+    # rotating root: every rank holds A; with 2048 rows there are two row blocks, one uploaded by each rank
+    m2 = 2048
+    a2 = G.uniform_np(21, (m2, k), np.float16); c2 = G.uniform_np(23, (m2, n), np.float16)
+    hc2 = np.ascontiguousarray(c2[:, col0:col0 + ncols]); hd2 = np.full((m2, ncols), np.float16(np.nan))
+    ctx.gemm_f16_mg(mg, -1, m2, ncols, k, a2, hb, hc2, hd2, k, k, ncols, ncols, 1.0, 1.0, 0)
+    ref2 = R.gemm(R.port(), m2, ncols, k, a2.ravel(), hb.ravel(), hc2.ravel(), 1.0, 1.0, np.float16).reshape(m2, ncols)
+    bound2 = R.gemm_abs_bound(m2, ncols, k, a2, b[:, col0:col0 + ncols], hc2, 1.0, 1.0)
+    err2 = float(np.max(np.abs(hd2.astype(np.float64) - ref2.astype(np.float64)) / bound2))
+    assert err2 <= 2e-3, err2
+    ctx.close()
     parts = [None] * world
     dist.all_gather_object(parts, (col0, ds.cpu().numpy()))
     if rank == 0:
