@@ -385,9 +385,22 @@ class GemmI8(GemmF16):
         self.ctx = api.HostContext()
         self.h2d = self.h_a.numel() + self.h_b.numel()
         self.d2h = self.h_d.numel() * 4
+        self.mg = None
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            # as for the fp16 GEMM: each row block of A is uploaded by one rank and broadcast inside the timed call
+            ident = [api.MultiGpu.unique_id() if dist.get_rank() == 0 else None]
+            dist.broadcast_object_list(ident, src=0)
+            self.mg = api.MultiGpu(ident[0], dist.get_rank(), dist.get_world_size())
+            blocks = (self.M + 1023) // 1024
+            mine = len(range(dist.get_rank(), blocks, dist.get_world_size()))
+            self.h2d -= (blocks - mine) * 1024 * self.K
 
     def step_host(self):
         n = self.nloc
+        if self.mg is not None:
+            self.ctx.gemm_i8_mg(self.mg, -1, self.M, n, self.K, self.h_a, self.h_b, None, self.h_d, self.K, self.K, n, n, 1, 0)
+            return
         self.ctx.gemm_i8(self.M, n, self.K, self.h_a, self.h_b, None, self.h_d, self.K, self.K, n, n, 1, 0)
 
     def config(self, world):

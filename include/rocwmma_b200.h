@@ -342,6 +342,11 @@ int b200wmma_gemm_f16_host_mg(b200wmma_ctx* ctx, b200wmma_mg* mg, int root, uint
                               const void* a, const void* b, const void* c, void* d,
                               uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
                               float alpha, float beta, int out_type);
+/* the same for b200wmma_gemm_i8_host */
+int b200wmma_gemm_i8_host_mg(b200wmma_ctx* ctx, b200wmma_mg* mg, int root, uint32_t m, uint32_t n, uint32_t k,
+                             const int8_t* a, const int8_t* b, const int32_t* c, int32_t* d,
+                             uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                             int32_t alpha, int32_t beta);
 int b200wmma_shard_range(uint64_t total, uint32_t parts, uint32_t index, uint32_t granule,
                          uint64_t* begin, uint64_t* count);
 

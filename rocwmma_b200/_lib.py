@@ -61,6 +61,7 @@ SIGNATURES = {
     "b200wmma_mg_size": (C.c_int, [vp]),
     "b200wmma_gemm_f16_host_mg": (C.c_int, [vp, vp, C.c_int, u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32, f32, f32,
                                             C.c_int]),
+    "b200wmma_gemm_i8_host_mg": (C.c_int, [vp, vp, C.c_int, u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32, i32, i32]),
     "b200wmma_shard_range": (C.c_int, [C.c_uint64, u32, u32, u32, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "b200wmma_ctx_create": (C.c_int, [C.POINTER(vp)]),
     "b200wmma_ctx_destroy": (C.c_int, [vp]),

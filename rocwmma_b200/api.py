@@ -258,6 +258,11 @@ class HostContext:
         check(lib().b200wmma_gemm_f16_host_mg(self._h, mg._h, root, m, n, k, self._hp(a), self._hp(b), self._hp(c),
                                               self._hp(d), lda, ldb, ldc, ldd, alpha, beta, out_type))
 
+    def gemm_i8_mg(self, mg, root, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta):
+        """Column-sharded int8 form of gemm_f16_mg."""
+        check(lib().b200wmma_gemm_i8_host_mg(self._h, mg._h, root, m, n, k, self._hp(a), self._hp(b), self._hp(c),
+                                             self._hp(d), lda, ldb, ldc, ldd, alpha, beta))
+
     def gemm_i8(self, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta):
         check(lib().b200wmma_gemm_i8_host(self._h, m, n, k, self._hp(a), self._hp(b), self._hp(c), self._hp(d),
                                           lda, ldb, ldc, ldd, alpha, beta, ROW_MAJOR, COL_MAJOR, ROW_MAJOR))

@@ -453,6 +453,33 @@ extern "C" int b200wmma_gemm_i8_host(b200wmma_ctx* ctx, uint32_t m, uint32_t n, 
                               });
 }
 
+extern "C" int b200wmma_gemm_i8_host_mg(b200wmma_ctx* ctx, b200wmma_mg* mg, int root, uint32_t m, uint32_t n, uint32_t k,
+                                        const int8_t* a, const int8_t* b, const int32_t* c, int32_t* d, uint32_t lda,
+                                        uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha, int32_t beta)
+{
+    clear_error();
+    if(int e = ctx_check(ctx))
+        return e;
+    B200_REQUIRE(mg, B200WMMA_ERR_INVALID_ARG, "gemm_i8_host_mg: mg must be a live handle");
+    B200_REQUIRE(root >= -1 && root < b200wmma_mg_size(mg), B200WMMA_ERR_INVALID_ARG, "gemm_i8_host_mg: bad root %d", root);
+    const bool needs_a = root < 0 || b200wmma_mg_rank(mg) == root;
+    B200_REQUIRE((a || !needs_a) && b && d && m && n && k, B200WMMA_ERR_INVALID_ARG,
+                 "gemm_i8_host_mg: null pointer or zero size");
+    B200_REQUIRE(lda >= k && ldb >= k && ldd >= n && ldc >= n, B200WMMA_ERR_INVALID_ARG,
+                 "gemm_i8_host_mg: leading dimension too small");
+    const bool use_c = c != nullptr && beta != 0;
+    B200_REQUIRE(c || beta == 0, B200WMMA_ERR_INVALID_ARG, "gemm_i8_host_mg: c may be null only when beta == 0");
+    return gemm_host_pipeline(
+        ctx, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, 1, 4, use_c,
+        [&](uint32_t rows, const void* da, const void* dc, void* dd) {
+            return launch_gemm_tc05_i8(rows, n, k, static_cast<const int8_t*>(da), static_cast<const int8_t*>(ctx->buf[1]),
+                                       static_cast<const int32_t*>(dc), static_cast<int32_t*>(dd), lda, ldb, ldc, ldd, alpha,
+                                       use_c ? beta : 0, B200WMMA_ROW_MAJOR, B200WMMA_COL_MAJOR, B200WMMA_ROW_MAJOR,
+                                       ctx->stream);
+        },
+        mg, root);
+}
+
 extern "C" int b200wmma_dlrm_fwd_host(b200wmma_ctx* ctx, const void* input, void* output, uint32_t m,
                                       uint32_t m_stride, uint32_t k, uint32_t batch, uint32_t out_stride)
 {

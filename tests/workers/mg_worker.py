@@ -58,6 +58,11 @@ def main():
     bound2 = R.gemm_abs_bound(m2, ncols, k, a2, b[:, col0:col0 + ncols], hc2, 1.0, 1.0)
     err2 = float(np.max(np.abs(hd2.astype(np.float64) - ref2.astype(np.float64)) / bound2))
     assert err2 <= 2e-3, err2
+    # int8 form, bit-exact
+    a8 = G.int8_np(31, (m2, k)); b8 = G.int8_np(32, (k, n))
+    hb8 = np.ascontiguousarray(b8.T[col0:col0 + ncols]); hd8 = np.zeros((m2, ncols), np.int32)
+    ctx.gemm_i8_mg(mg, -1, m2, ncols, k, a8, hb8, None, hd8, k, k, ncols, ncols, 1, 0)
+    assert np.array_equal(hd8, a8.astype(np.int32) @ b8[:, col0:col0 + ncols].astype(np.int32)), "int8 multi-GPU driver"
     ctx.close()
     parts = [None] * world
     dist.all_gather_object(parts, (col0, ds.cpu().numpy()))
