@@ -11,8 +11,16 @@ N > 1: one process per GPU.  The problem is sharded by N-column blocks (B, C, D 
 over NCCL before the timed region and reported separately as `a_broadcast_ms`); there is no collective in
 the data path, total work is fixed (strong scaling), value = 2*M*N*K / max-over-ranks time.
 
-Other workloads (`--workload gemm_bf16 | gemm_fp8 | gemm_f32 | gemm_i8 | gemm_i8_sp24 | gemm_i4 | gemm_f64 | dlrm_fwd | dlrm_bwd | sgemv | dgemv`)
-print the same line for the other configurations; they are not the default.
+The line also carries `"also"`: every other component of the metric (int8 / 2:4-sparse / int4 / bf16 / fp8 / fp64 GEMM,
+DLRM forward and backward, sgemv / dgemv, the fragment-API GEMMs) measured in the same process the same way, each with
+its own ms_per_step, roofline, clocks, parity_check and (where a host driver exists) e2e; at N > 1 each is sharded its own
+way (GEMM by N-column blocks, DLRM by batch, GEMV by rows).  `--no-also` skips them, `--workload NAME` makes one of
+them the headline instead (`gemm_bf16 | gemm_fp8 | gemm_f32 | gemm_i8 | gemm_i8_sp24 | gemm_i4 | gemm_f64 | dlrm_fwd |
+dlrm_bwd | sgemv | dgemv | frag_simple_hgemm | frag_perf_hgemm`).
+
+`"parity_check"`: after the timed region and outside it, every rank compares a seeded sample of rows / samples of its own
+result (device-pointer path, and the host-driver result where there is one) with the CPU oracle; the run exits non-zero
+when a check fails.
 
 `--impl reference` times the reference's own CPU implementation (oracle/_ref/libref.so, compiled from
 rocWMMA's test/reference_impl.hpp; the port oracle/libref_port.so if that is absent) on the host cores,
@@ -147,6 +155,67 @@ def _shard(n, world, rank):
     return shard_range(n, world, rank)
 
 
+def _timed_broadcast(torch, dist, t):
+    """A is needed whole by every rank: one NCCL broadcast from rank 0 before the timed region.  Returns
+    (ms of that first call, which includes NCCL's channel set-up; ms of a second, warmed call of the same size)."""
+    out = []
+    for _ in range(2):
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        dist.broadcast(t, src=0)
+        e1.record()
+        torch.cuda.synchronize()
+        out.append(e0.elapsed_time(e1))
+    return out[0], out[1]
+
+
+def _sample_rows(total, count, seed):
+    """Seeded sample of row / sample indices, always with the first and the last one."""
+    import numpy as np
+    from rocwmma_b200 import datagen as G
+    rows = (G.raw_np(seed, count) % np.uint64(total)).astype(np.int64)
+    rows[0], rows[-1] = 0, total - 1
+    return np.unique(rows)
+
+
+def _parity_result(rows, err, tol, exact=None, what=""):
+    """`err`: max |got - ref| / bound (floating point); `exact`: number of mismatching elements (integer paths)."""
+    if exact is not None:
+        return {"rows": int(rows), "max_rel_err": 0.0 if exact == 0 else float("inf"), "mismatches": int(exact),
+                "tol": 0.0, "ok": exact == 0, "what": what}
+    ok = bool(err == err and err <= tol)
+    return {"rows": int(rows), "max_rel_err": float(err), "tol": tol, "ok": ok, "what": what}
+
+
+def _gemm_rows_parity(wl, torch, a_rows, b_store, c_rows, got, alpha, beta, out_np, tol, what):
+    """Rows of D = alpha*A*B + beta*C against the oracle.  a_rows [r, k] and b_store [n, k] (column-major B) are
+    numpy arrays in the oracle's input type; the error bound |alpha| sum|a||b| + |beta||c| is formed on the device
+    in fp64 (plumbing for the tolerance only)."""
+    import numpy as np
+    from oracle import cpu_ref as R
+    r, k = a_rows.shape
+    n = b_store.shape[0]
+    ref = R.gemm(R.port(), r, n, k, np.ascontiguousarray(a_rows).ravel(), np.ascontiguousarray(b_store).ravel(),
+                 None if c_rows is None else np.ascontiguousarray(c_rows).ravel(), alpha, beta, out_np).reshape(r, n)
+    if np.issubdtype(np.dtype(out_np), np.integer):
+        return _parity_result(r, 0.0, 0.0, exact=int(np.count_nonzero(got != ref)), what=what)
+    ta = torch.from_numpy(np.abs(a_rows.astype(np.float64))).cuda()
+    bound = torch.zeros((r, n), dtype=torch.float64, device="cuda")
+    for c0 in range(0, n, 2048):   # column chunks keep the fp64 copy of B small
+        tb = torch.from_numpy(np.abs(b_store[c0:c0 + 2048].astype(np.float64))).cuda()
+        bound[:, c0:c0 + 2048] = abs(alpha) * (ta @ tb.t())
+    bound = bound.cpu().numpy()
+    if c_rows is not None:
+        bound += abs(beta) * np.abs(c_rows.astype(np.float64))
+    g64 = got.astype(np.float64)
+    if not np.isfinite(g64).all():
+        return _parity_result(r, float("nan"), tol, what=what)
+    err = float(np.max(np.abs(g64 - ref.astype(np.float64)) / np.maximum(bound, 1e-300)))
+    return _parity_result(r, err, tol, what=what)
+
+
 class GemmF16(Workload):
     name, metric, unit, dtype, bound = "gemm_f16", "fp16 GEMM TFLOP/s at 8192^3", "TFLOP/s", "f16", "tensor"
     M = N = K = 8192
@@ -176,12 +245,7 @@ class GemmF16(Workload):
         if world > 1:
             torch.cuda.synchronize()
             dist.barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            dist.broadcast(self.a, src=0)  # A is needed whole by every rank: one NCCL broadcast, untimed
-            e1.record()
-            torch.cuda.synchronize()
-            self.a_broadcast_ms = e0.elapsed_time(e1)
+            self.a_broadcast_ms, self.a_broadcast_warm_ms = _timed_broadcast(torch, dist, self.a)
         self.work_total = 2.0 * M * N * K
         self.work_local = 2.0 * M * self.nloc * K
 
@@ -249,12 +313,42 @@ class GemmF16(Workload):
         return work / seconds / 1e12
 
     cpu_rows = 64
+    parity_rows = 16
+    parity_tol = 2e-3     # fp16 outputs: |d - ref| / (|alpha| sum|a||b| + |beta||c|)
+
+    def _oracle_np(self, t):
+        """Device tensor -> numpy array in the oracle's input type (exact widening for bf16 / fp8)."""
+        torch = self.torch
+        if t.dtype in (torch.float16, torch.float32, torch.float64, torch.int8, torch.int32):
+            return t.cpu().numpy()
+        return t.to(torch.float32).cpu().numpy()
+
+    def parity(self, host=False):
+        """Seeded rows of this rank's block of D (device path: self.d after the last step; host path: h_d)."""
+        import numpy as np
+        torch = self.torch
+        rows = _sample_rows(self.M, self.parity_rows, 4321 + self.rank)
+        idx = torch.from_numpy(rows).cuda()
+        out_np = {torch.float16: np.float16, torch.float32: np.float32, torch.int32: np.int32,
+                  torch.float64: np.float64}[self.d.dtype]
+        got = self.h_d[torch.from_numpy(rows)].numpy() if host else self.d[idx].cpu().numpy()
+        c = getattr(self, "c", None)
+        beta = getattr(self, "beta", 0)
+        return _gemm_rows_parity(self, torch, self._oracle_np(self._a_for_oracle()[idx]), self._oracle_np(self.b),
+                                 None if (c is None or not beta) else c[idx].cpu().numpy(), got,
+                                 getattr(self, "alpha", 1), beta, out_np, self.parity_tol,
+                                 f"{len(rows)} seeded rows x this rank's {self.nloc} columns vs the CPU oracle"
+                                 + (" (host-buffer driver result)" if host else ""))
+
+    def _a_for_oracle(self):
+        return self.a
 
 
 class GemmBF16(GemmF16):
     """bfloat16 (or fp8) inputs, fp32 C / D: the same problem as gemm_f16 with the inputs rounded to the type."""
     name, metric, dtype = "gemm_bf16", "bf16 GEMM TFLOP/s at 8192^3 (fp32 C/D)", "bf16"
     has_host = False
+    parity_tol = 1e-3     # fp32 outputs
 
     def _in_dtype(self, torch):
         return torch.bfloat16
@@ -345,25 +439,26 @@ class GemmI8(GemmF16):
         self.a_broadcast_ms = 0.0
         if world > 1:
             torch.cuda.synchronize(); dist.barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(); dist.broadcast(self.a, src=0); e1.record(); torch.cuda.synchronize()
-            self.a_broadcast_ms = e0.elapsed_time(e1)
+            self.a_broadcast_ms, self.a_broadcast_warm_ms = _timed_broadcast(torch, dist, self.a)
         self.d = torch.empty((M, self.nloc), dtype=torch.int32, device="cuda")
         if self.variant == "sp24":
             import numpy as np
             # compress on the host in row chunks (format definition lives in datagen.sparsify_24_np)
             vals = torch.empty((M, K // 2), dtype=torch.int8, device="cuda")
             meta = torch.empty((M, K // 8), dtype=torch.uint8, device="cuda")
+            self.a_dense = torch.empty_like(self.a)   # the densified operand, kept for the parity check only
             for r0 in range(0, M, 1024):
-                v, md, _ = G.sparsify_24_np(self.a[r0:r0 + 1024].cpu().numpy(), row_start=r0)
+                v, md, dn = G.sparsify_24_np(self.a[r0:r0 + 1024].cpu().numpy(), row_start=r0)
                 vals[r0:r0 + 1024] = torch.from_numpy(v).cuda()
                 meta[r0:r0 + 1024] = torch.from_numpy(md).cuda()
+                self.a_dense[r0:r0 + 1024] = torch.from_numpy(dn).cuda()
             self.vals, self.meta = vals, meta
             self.ws = torch.empty(api.gemm_i8_sp24_workspace_bytes(M, self.nloc, K), dtype=torch.uint8, device="cuda")
         elif self.variant == "i4":
             pack = lambda t: ((t[:, 0::2].to(torch.uint8) & 0xF) | ((t[:, 1::2].to(torch.uint8) & 0xF) << 4)).contiguous()
             self.ap, self.bp = pack(self.a), pack(self.b)
-            self.ws = torch.empty(api.gemm_i4_workspace_bytes(M, self.nloc, K), dtype=torch.uint8, device="cuda")
+            nws = api.gemm_i4_workspace_bytes(M, self.nloc, K)
+            self.ws = torch.empty(nws, dtype=torch.uint8, device="cuda") if nws else None
         self.work_total = 2.0 * M * N * K
         self.work_local = 2.0 * M * self.nloc * K
 
@@ -422,16 +517,22 @@ class GemmI8(GemmF16):
         return 2.0 * rows * N * K, time.perf_counter() - t0
 
     cpu_rows = 64
+    alpha, beta = 1, 0
+
+    def _a_for_oracle(self):
+        return self.a_dense if self.variant == "sp24" else self.a
 
 
 class GemmI8Sp24(GemmI8):
     name, variant = "gemm_i8_sp24", "sp24"
+    has_host = False   # the host-buffer driver exists for the dense int8 form only
     launches_per_step = 2   # metadata re-tiling + sparse tensor-core GEMM
     metric = "2:4-sparse int8 GEMM dense-equivalent TOP/s at 8192x8192x16384"
 
 
 class GemmI4(GemmI8):
     name, variant = "gemm_i4", "i4"
+    has_host = False
     launches_per_step = 3   # unpack A, unpack B, dense int8 GEMM
     metric = "int4-unpacked GEMM TOP/s at 8192x8192x16384"
 
@@ -442,10 +543,11 @@ class GemmF64(Workload):
 
     def setup(self, torch, rank, world, dist):
         from rocwmma_b200 import datagen as G
-        self.torch = torch
+        self.torch, self.rank = torch, rank
         col0, self.nloc = _shard(self.N, world, rank)
-        f = lambda shape, seed: G.fill_torch(torch.empty(shape, dtype=torch.float64, device="cuda"), seed, "uniform")
-        self.a, self.b, self.c = f((self.M, self.K), 1), f((self.nloc, self.K), 2), f((self.M, self.nloc), 3)
+        f = lambda shape, seed, start=0: G.fill_torch(torch.empty(shape, dtype=torch.float64, device="cuda"), seed, "uniform", start=start)
+        self.a, self.b = f((self.M, self.K), 1), f((self.nloc, self.K), 2, col0 * self.K)
+        self.c = f((self.M, self.nloc), 3 + 10 * rank)
         self.d = torch.empty_like(self.c)
         self.a_broadcast_ms = 0.0
         self.work_total = 2.0 * self.M * self.N * self.K
@@ -457,6 +559,12 @@ class GemmF64(Workload):
 
     def config(self, world):
         return {"workload": "fp64 GEMM (DMMA), M=N=K=4096, A row-major, B col-major, alpha=beta=1", "l2": "inputs larger than L2"}
+
+    alpha = beta = 1.0
+    parity_rows, parity_tol = 32, 1e-12
+    _oracle_np = GemmF16._oracle_np
+    _a_for_oracle = GemmF16._a_for_oracle
+    parity = GemmF16.parity
 
     def value(self, work, seconds):
         return work / seconds / 1e12
@@ -491,7 +599,7 @@ class Dlrm(Workload):
 
     def setup(self, torch, rank, world, dist):
         from rocwmma_b200 import datagen as G
-        self.torch = torch
+        self.torch, self.rank = torch, rank
         b0, self.bloc = _shard(self.B, world, rank)
         ms, k, w = self.m_stride, self.k, self.width
         # L2 is 126 MB and one batch is ~134 MB of X: rotate over 4 independent batches so no step finds its input cached
@@ -547,6 +655,48 @@ class Dlrm(Workload):
     def value(self, work, seconds):
         return work / seconds
 
+    def parity(self, host=False):
+        """64 seeded samples of this rank's shard against the oracle: pass-through columns exact, the packed triangle /
+        the gradient within 2e-3 of sum|a||b| (fp16 outputs; twice that on the fused row 0, which is rounded once
+        more in the oracle), padding columns zero."""
+        import numpy as np
+        from oracle import cpu_ref as R
+        from rocwmma_b200 import api
+        torch, m, k, w = self.torch, self.m, self.k, self.width
+        rows = _sample_rows(self.bloc, 64, 977 + self.rank)
+        idx = torch.from_numpy(rows).cuda()
+        if not host:
+            if self.backward:
+                api.dlrm_dot_bwd(self.x[0], self.up[0], self.grad, None, m, self.m_stride, k, self.bloc, w, True)
+            else:
+                api.dlrm_dot_fwd(self.x[0], self.out, m, self.m_stride, k, self.bloc, w)
+            torch.cuda.synchronize()
+        x = np.ascontiguousarray(self.x[0][idx][:, :m].cpu().numpy())
+        x64 = np.abs(x.astype(np.float64))
+        il, jl = np.tril_indices(m, -1)
+        what = f"{len(rows)} seeded samples of this rank's shard vs the CPU oracle" + (" (host-buffer driver result)" if host else "")
+        if not self.backward:
+            got = (self.h_out[torch.from_numpy(rows)] if host else self.out[idx].cpu()).numpy()
+            ref = R.dlrm_fwd(R.port(), x, m, k, len(rows))
+            wreal = k + len(il)
+            bound = np.einsum("bik,bjk->bij", x64, x64)[:, il, jl]
+            err = float(np.max(np.abs(got[:, k:wreal].astype(np.float64) - ref[:, k:].astype(np.float64)) / np.maximum(bound, 1e-30)))
+            exact = np.array_equal(got[:, :k], x[:, 0, :]) and bool((got[:, wreal:] == 0).all())
+            res = _parity_result(len(rows), err if exact else float("inf"), 2e-3, what=what)
+            return res
+        up = self.up[0][idx].cpu().numpy()
+        got = (self.h_grad[torch.from_numpy(rows)] if host else self.grad[idx].cpu()).numpy()[:, :m]
+        ref_grad, _ = R.dlrm_bwd(R.port(), x, np.ascontiguousarray(up[:, :k + len(il)]), m, k, len(rows))
+        expect = ref_grad.astype(np.float64)
+        expect[:, 0, :] += up[:, :k].astype(np.float64)
+        T = np.zeros((len(rows), m, m))
+        T[:, il, jl] = np.abs(up[:, k:k + len(il)].astype(np.float64))
+        T = T + T.transpose(0, 2, 1)
+        bound = np.einsum("bih,bhj->bij", T, x64)
+        bound[:, 0, :] += np.abs(up[:, :k].astype(np.float64))
+        err = float(np.max(np.abs(got.astype(np.float64) - expect) / np.maximum(bound, 1e-30)))
+        return _parity_result(len(rows), err, 4e-3, what=what)
+
     def cpu_sample(self, impl, rows):
         import numpy as np
         from oracle import cpu_ref as R
@@ -588,12 +738,13 @@ class Gemv(Workload):
 
     def setup(self, torch, rank, world, dist):
         from rocwmma_b200 import datagen as G
-        self.torch = torch
+        self.torch, self.rank = torch, rank
         dt = torch.float64 if self.double else torch.float32
         r0, self.mloc = _shard(self.M, world, rank)
         self.a = G.fill_torch(torch.empty((self.mloc, self.N), dtype=dt, device="cuda"), G.SEED_GEMV_A, "uniform", start=r0 * self.N)
         self.x = G.fill_torch(torch.empty(self.N, dtype=dt, device="cuda"), G.SEED_GEMV_X, "uniform")
         self.y = G.fill_torch(torch.empty(self.mloc, dtype=dt, device="cuda"), G.SEED_GEMV_Y, "uniform", start=r0)
+        self.y0 = self.y.clone()   # y is updated in place by every step; the parity check starts from this copy
         es = 8 if self.double else 4
         self.a_broadcast_ms = 0.0
         self.work_total = float(es * (self.M * self.N + self.N + 2 * self.M))
@@ -605,7 +756,8 @@ class Gemv(Workload):
 
     def setup_host(self):
         from rocwmma_b200 import api
-        self.h_a = self.a.cpu().pin_memory(); self.h_x = self.x.cpu().pin_memory(); self.h_y = self.y.cpu().pin_memory()
+        self.h_a = self.a.cpu().pin_memory(); self.h_x = self.x.cpu().pin_memory(); self.h_y = self.y0.cpu().pin_memory()
+        self.h_y0 = self.y0.cpu()
         self.ctx = api.HostContext()
         es = 8 if self.double else 4
         self.h2d = (self.h_a.numel() + self.h_x.numel() + self.h_y.numel()) * es
@@ -614,6 +766,10 @@ class Gemv(Workload):
     def step_host(self):
         self.ctx.gemv(self.mloc, self.N, self.h_a, self.N, self.h_x, self.h_y, 1.5, 0.5, double=self.double)
 
+    def host_parity_prepare(self):
+        self.h_y.copy_(self.h_y0)   # y is updated in place: one call on the original vector
+        self.step_host()
+
     def config(self, world):
         return {"workload": f"{'dgemv' if self.double else 'sgemv'} y = 1.5*A*x + 0.5*y, A row-major 32768 x 32768",
                 "sharding": "single GPU" if world == 1 else f"rows split over {world} ranks, x replicated",
@@ -621,6 +777,30 @@ class Gemv(Workload):
 
     def value(self, work, seconds):
         return work / seconds / 1e9
+
+    def parity(self, host=False):
+        """64 seeded rows of this rank's shard, one call on a fresh copy of y, against the oracle:
+        |y - ref| / (|alpha| sum|a||x| + |beta||y0|) <= 1e-3 (fp32) / 1e-12 (fp64)."""
+        import numpy as np
+        from oracle import cpu_ref as R
+        from rocwmma_b200 import api
+        torch = self.torch
+        dt = np.float64 if self.double else np.float32
+        rows = _sample_rows(self.mloc, 64, 611 + self.rank)
+        idx = torch.from_numpy(rows).cuda()
+        if host:
+            y0, got = self.h_y0[torch.from_numpy(rows)].numpy(), self.h_y[torch.from_numpy(rows)].numpy()
+        else:
+            y = self.y0.clone()
+            api.gemv(self.mloc, self.N, self.a, self.N, self.x, y, 1.5, 0.5)
+            torch.cuda.synchronize()
+            y0, got = self.y0[idx].cpu().numpy(), y[idx].cpu().numpy()
+        ah, xh = self.a[idx].cpu().numpy(), self.x.cpu().numpy()
+        ref = R.gemv(R.port(), len(rows), self.N, np.ascontiguousarray(ah).ravel(), xh, y0, dt(1.5), dt(0.5))
+        bound = 1.5 * (np.abs(ah.astype(np.float64)) @ np.abs(xh.astype(np.float64))) + 0.5 * np.abs(y0.astype(np.float64))
+        err = float(np.max(np.abs(got.astype(np.float64) - ref.astype(np.float64)) / np.maximum(bound, 1e-300)))
+        return _parity_result(len(rows), err, 1e-12 if self.double else 1e-3,
+                              what=f"{len(rows)} seeded rows of this rank's shard vs the CPU oracle" + (" (host-buffer driver result)" if host else ""))
 
     def cpu_sample(self, impl, rows):
         import numpy as np
@@ -642,7 +822,85 @@ class Dgemv(Gemv):
     double = True
 
 
-WORKLOADS = {w().name: w for w in (GemmF16, GemmBF16, GemmFP8, GemmF32, GemmI8, GemmI8Sp24, GemmI4, GemmF64, Dlrm, DlrmBwd, Gemv, Dgemv)}
+class FragSimpleHgemm(GemmF16):
+    """hgemm_rocwmma_d of samples/simple_hgemm.cpp on this repository's fragment headers: the 1024^3 correctness-gate
+    configuration (A row-major, B column-major fp16, C / D fp32, alpha = beta = 2), one 16x16 block per warp."""
+    name, metric, dtype = "frag_simple_hgemm", "fragment-API simple_hgemm TFLOP/s at 1024^3 (fp32 C/D, alpha=beta=2)", "f16"
+    M = N = K = 1024
+    alpha = beta = 2.0
+    has_host = False
+    legacy_mma = True
+    parity_rows, parity_tol = 64, 1e-3
+
+    def setup(self, torch, rank, world, dist):
+        from rocwmma_b200 import datagen as G
+        self.torch, self.rank, self.world = torch, rank, world
+        M, N, K = self.M, self.N, self.K
+        col0, self.nloc = _shard(N, world, rank)
+        self.a = G.fill_torch(torch.empty((M, K), dtype=torch.float16, device="cuda"), G.SEED_A, "uniform")
+        self.b = G.fill_torch(torch.empty((self.nloc, K), dtype=torch.float16, device="cuda"), G.SEED_B, "uniform", start=col0 * K)
+        self.c = G.fill_torch(torch.empty((M, self.nloc), dtype=torch.float32, device="cuda"), G.SEED_C + 10 * rank, "uniform")
+        self.d = torch.empty_like(self.c)
+        self.a_broadcast_ms = 0.0
+        self.work_total, self.work_local = 2.0 * M * N * K, 2.0 * M * self.nloc * K
+
+    def step(self):
+        from rocwmma_b200 import api
+        api.simple_hgemm(self.M, self.nloc, self.K, self.a, self.b, self.c, self.d, self.K, self.K, self.nloc, self.nloc,
+                         self.alpha, self.beta)
+
+    def config(self, world):
+        return {"workload": "simple_hgemm on the fragment API (mma.sync), M=N=K=1024, A row-major / B col-major fp16, C/D fp32, "
+                            "alpha=beta=2", "M": self.M, "N": self.N, "K": self.K,
+                "sharding": "single GPU" if world == 1 else f"N split into {world} column blocks",
+                "l2": "problem fits L2 (correctness-gate size)"}
+
+
+class FragPerfHgemm(FragSimpleHgemm):
+    """perf_hgemm's kernel pattern (cooperative global reads, shared-memory double buffer, fragment transforms) on the
+    fragment headers, in the layouts the sample ships with: A column-major, B row-major, C / D row-major fp16."""
+    name, metric = "frag_perf_hgemm", "fragment-API perf_hgemm TFLOP/s at 8192^3 (A col-major, B row-major, fp16 C/D)"
+    M = N = K = 8192
+    alpha = beta = 1.0
+    parity_rows, parity_tol = 16, 2e-3
+
+    def setup(self, torch, rank, world, dist):
+        from rocwmma_b200 import datagen as G
+        self.torch, self.rank, self.world = torch, rank, world
+        M, N, K = self.M, self.N, self.K
+        col0, self.nloc = _shard(N, world, rank)
+        f16 = torch.float16
+        self.a_t = G.fill_torch(torch.empty((K, M), dtype=f16, device="cuda"), G.SEED_A, "uniform")            # A column-major
+        self.b_kn = G.fill_torch(torch.empty((K, self.nloc), dtype=f16, device="cuda"), G.SEED_B + 10 * rank, "uniform")  # B row-major
+        self.c = G.fill_torch(torch.empty((M, self.nloc), dtype=f16, device="cuda"), G.SEED_C + 10 * rank, "uniform")
+        self.d = torch.empty_like(self.c)
+        self.a_broadcast_ms = 0.0
+        self.work_total, self.work_local = 2.0 * M * N * K, 2.0 * M * self.nloc * K
+
+    def step(self):
+        from rocwmma_b200 import api
+        api.perf_hgemm_fragment(self.M, self.nloc, self.K, self.a_t, self.b_kn, self.c, self.d, self.M, self.nloc,
+                                self.nloc, self.nloc, self.alpha, self.beta)
+
+    def parity(self, host=False):
+        import numpy as np
+        torch = self.torch
+        rows = _sample_rows(self.M, self.parity_rows, 4321 + self.rank)
+        idx = torch.from_numpy(rows).cuda()
+        a_rows = self.a_t[:, idx].t().contiguous().cpu().numpy()
+        b_store = self.b_kn.t().contiguous().cpu().numpy()   # [n, k]: the oracle helper takes column-major B
+        return _gemm_rows_parity(self, torch, a_rows, b_store, self.c[idx].cpu().numpy(), self.d[idx].cpu().numpy(),
+                                 self.alpha, self.beta, np.float16, self.parity_tol,
+                                 f"{len(rows)} seeded rows x this rank's {self.nloc} columns vs the CPU oracle")
+
+    def config(self, world):
+        return {"workload": "perf_hgemm kernel pattern on the fragment API (mma.sync), M=N=K=8192, A col-major / B row-major fp16, "
+                            "C/D row-major fp16, alpha=beta=1", "M": self.M, "N": self.N, "K": self.K,
+                "sharding": "single GPU" if world == 1 else f"N split into {world} column blocks",
+                "l2": "inputs larger than L2"}
+
+
+WORKLOADS = {w().name: w for w in (FragSimpleHgemm, FragPerfHgemm, GemmF16, GemmBF16, GemmFP8, GemmF32, GemmI8, GemmI8Sp24, GemmI4, GemmF64, Dlrm, DlrmBwd, Gemv, Dgemv)}
 
 
 # ---------------------------------------------------------------------------------------- CPU arm
@@ -695,31 +953,92 @@ def run_reference_arm(args, wl):
 
 
 # ---------------------------------------------------------------------------------------- GPU arm
-def run_gpu_arm(args, wl):
-    import torch
-    import torch.distributed as dist
+def roofline_of(wl, ms_step, peaks, copy_same):
+    """roofline object of one workload from its measured step time (this rank's share of the work / this GPU's peak)."""
+    if wl.bound == "tensor":
+        peak = peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])
+        variant = getattr(wl, "variant", "")
+        if wl.dtype == "f32":
+            peak /= 6.0  # TF32 runs at half the 16-bit rate and every product takes three MMAs
+            peak_note = "cuBLAS bf16 8192^3 burst / 6: TF32 rate over three products"
+        elif wl.dtype == "fp8":
+            peak *= 2.0  # the fp8 tensor rate is twice the 16-bit rate; no fp8 figure is measured
+            peak_note = "2 x cuBLAS bf16 8192^3 burst, standing in for the dense fp8 rate"
+        elif wl.dtype == "i8" and variant == "sp24":
+            peak *= 4.0  # sparse int8: twice the dense int8 rate (measured: 112 clocks per 256x224x64 pair MMA)
+            peak_note = "4 x cuBLAS bf16 8192^3 burst, standing in for the 2:4-sparse int8 rate"
+        elif wl.dtype == "i8":
+            peak *= 2.0  # the dense int8 tensor rate is twice the 16-bit rate; no int8 figure is measured
+            peak_note = "2 x cuBLAS bf16 8192^3 burst, standing in for the dense int8 rate"
+        elif wl.dtype == "f64":
+            peak = 40.0
+            peak_note = "nominal B200 fp64 tensor rate; no measured figure"
+        elif getattr(wl, "legacy_mma", False):
+            peak_note = "cuBLAS bf16 8192^3 burst (tcgen05); this workload runs on the warp-level mma.sync path of the fragment API"
+        else:
+            peak_note = "cuBLAS bf16 8192^3 burst"
+        achieved = wl.work_local / (ms_step * 1e-3) / 1e12
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s" if wl.dtype != "i8" else "TOP/s",
+                "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(wl.name),
+                "peak_source": f"{peaks['_source']} ({peak_note})"}
+        # the vendor's dense figures, for context: 2250 TFLOP/s 16-bit, 4500 fp8 / int8, 9000 for 2:4-sparse int8,
+        # 1125 / 3 for fp32 through three TF32 products, 40 fp64
+        nominal = {"f16": 2250.0, "bf16": 2250.0, "fp8": 4500.0, "f32": 375.0, "f64": 40.0}.get(wl.dtype)
+        if wl.dtype == "i8":
+            nominal = 9000.0 if variant == "sp24" else 4500.0
+        if nominal:
+            roof["nominal_peak"] = nominal
+            roof["frac_of_nominal"] = achieved / nominal
+        return roof
+    peak = peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"])
+    nbytes = wl.bytes_per_sample * wl.work_local if hasattr(wl, "bytes_per_sample") else wl.work_local
+    achieved = nbytes / (ms_step * 1e-3) / 1e9
+    roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "traffic": NCU_TRAFFIC_BYTES.get(wl.name), "peak_source": f"{peaks['_source']} (copy bandwidth)"}
+    if copy_same:
+        roof["copy_same_bytes"] = copy_same  # GB/s of torch copy_ moving the same bytes per launch
+        roof["frac_of_copy_same_bytes"] = achieved / copy_same
+    roof["nominal_peak"] = 8000.0  # GB/s, the vendor's HBM3e figure
+    roof["frac_of_nominal"] = achieved / 8000.0
+    return roof
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device; rocwmma_b200 has no CPU fallback (use --impl reference for the CPU arm)")
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    assert world == args.gpus or world == 1, f"--gpus {args.gpus} but WORLD_SIZE={world}"
 
-    from rocwmma_b200 import api
-    wl.setup(torch, rank, world, dist)
+class Harness:
+    """Device timing shared by the headline workload and the `also` workloads of one process."""
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist, self.args = torch, dist, args
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py: no CUDA device; rocwmma_b200 has no CPU fallback (use --impl reference for the CPU arm)")
+        torch.cuda.set_device(self.local_rank)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
+        assert self.world == args.gpus or self.world == 1, f"--gpus {args.gpus} but WORLD_SIZE={self.world}"
+        self.peaks = measured_peaks()
 
-    def timed(fn, steps, sampler=None):
-        barrier()
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+            self.torch.cuda.synchronize()
+
+    def reduce_max(self, x):
+        if self.world == 1:
+            return float(x)
+        t = self.torch.tensor([x], dtype=self.torch.float64, device="cuda")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(self, fn, steps, sampler=None):
+        """K back-to-back calls between two CUDA events on the launching stream, barrier + synchronize on both sides;
+        returns (device ms, max over ranks; host wall seconds of this rank)."""
+        torch = self.torch
+        self.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         if sampler:
             sampler.start()
@@ -732,152 +1051,177 @@ def run_gpu_arm(args, wl):
         wall = time.perf_counter() - t0
         if sampler:
             sampler.stop()
-        barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms, wall
+        self.barrier()
+        return self.reduce_max(e0.elapsed_time(e1)), wall
 
-    for _ in range(max(args.warmup, 3)):
-        wl.step()
-    sampler = ClockSampler(local_rank)
-    ms_total, _ = timed(wl.step, args.steps, sampler)
-    if len(sampler.samples) < 5:
-        # the timed region was too short for the sampling period: extend the same loop (untimed) under the sampler
-        sampler.start()
-        t_end = time.perf_counter() + 0.4
-        while time.perf_counter() < t_end:
-            for _ in range(20):
-                wl.step()
-            torch.cuda.synchronize()
-        sampler.stop()
-    st, detail = api.device_status()
-    assert st == 0, f"device status {st} (detail {detail:#x})"
-    ms_step = ms_total / args.steps
-    value = wl.value(wl.work_total, ms_step * 1e-3)
+    def merge_parity(self, res):
+        """Combine the per-rank parity results: rows summed, error maximised, ok only if every rank is ok."""
+        if self.world == 1:
+            return res
+        torch, dist = self.torch, self.dist
+        err = res["max_rel_err"] if res["max_rel_err"] == res["max_rel_err"] else float("inf")
+        t = torch.tensor([err, 0.0 if res["ok"] else 1.0], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        r = torch.tensor([res["rows"]], dtype=torch.int64, device="cuda")
+        dist.all_reduce(r)
+        out = dict(res)
+        out.update(rows=int(r.item()), max_rel_err=float(t[0].item()), ok=bool(t[1].item() == 0.0), ranks=self.world)
+        return out
 
-    # Tensor-bound workloads: the same step repeated for a few seconds.  The timed K steps above are a burst (the part
-    # has not settled under its power cap yet); this is the rate it holds, to set beside the sustained library figure.
-    sustained = None
-    if wl.bound == "tensor" and args.sustained_seconds > 0:
-        per_batch = max(10, int(0.25 / max(ms_step * 1e-3, 1e-6)))
-        done, ms_acc = 0, 0.0
-        # the batch count comes from the (rank-reduced) step time, so every rank runs the same number of batches
-        batches = max(1, int(args.sustained_seconds / (per_batch * ms_step * 1e-3) + 0.5))
-        for _ in range(batches):
-            ms_b, _ = timed(wl.step, per_batch)
-            ms_acc += ms_b
-            done += per_batch
-        sustained = {"value": wl.value(wl.work_total, ms_acc / done * 1e-3), "unit": wl.unit, "launches": done,
-                     "seconds": ms_acc * 1e-3}
+    def measure(self, wl, steps, warmup, headline):
+        """Times one workload; returns its part of the JSON line (rank 0 uses it; every rank must call)."""
+        torch, args, world = self.torch, self.args, self.world
+        from rocwmma_b200 import api
+        wl.setup(torch, self.rank, world, self.dist)
+        for _ in range(max(warmup, 3)):
+            wl.step()
+        sampler = ClockSampler(self.local_rank)
+        ms_total, _ = self.timed(wl.step, steps, sampler)
+        if len(sampler.samples) < 5:
+            # the timed region was too short for the sampling period: extend the same loop (untimed) under the sampler
+            sampler.start()
+            t_end = time.perf_counter() + 0.4
+            while time.perf_counter() < t_end:
+                for _ in range(20):
+                    wl.step()
+                torch.cuda.synchronize()
+            sampler.stop()
+        st, detail = api.device_status()
+        assert st == 0, f"device status {st} (detail {detail:#x})"
+        ms_step = ms_total / steps
+        value = wl.value(wl.work_total, ms_step * 1e-3)
+        parity = self.merge_parity(wl.parity())   # outside the timed region, every rank on its own block
 
-    # HBM-bound workloads: a plain device-to-device copy moving the same number of bytes per launch, timed the same
-    # way (sources and destinations rotate through sets larger than L2).  The measured copy peak is a large-transfer figure; at these launch
-    # sizes a copy does not reach it either, and this figure says what does.
-    copy_same = None
-    if wl.bound == "hbm" and not args.no_copy_ref:
-        nbytes_launch = wl.bytes_per_sample * wl.work_local if hasattr(wl, "bytes_per_sample") else wl.work_local
-        half = max(int(nbytes_launch) // 2 // 4 * 4, 4)
-        if half <= (6 << 30):
-            nbuf = max(2, int((300 << 20) // half) + 1)
-            srcs = [torch.empty(half, dtype=torch.uint8, device="cuda") for _ in range(nbuf)]
-            dsts = [torch.empty(half, dtype=torch.uint8, device="cuda") for _ in range(nbuf)]
-            state = {"i": 0}
-
-            def copy_step():
-                i = state["i"]
-                dsts[i % nbuf].copy_(srcs[i % nbuf])
-                state["i"] = i + 1
-
-            for _ in range(3):
-                copy_step()
-            ms_copy, _ = timed(copy_step, args.steps)
-            copy_same = 2.0 * half / (ms_copy / args.steps * 1e-3) / 1e9
-            del srcs, dsts
-
-    # end to end: host buffers through the C ABI host drivers, copies inside the timed region
-    e2e = None
-    if hasattr(wl, "setup_host") and getattr(wl, "has_host", True) and not args.no_e2e:
-        wl.setup_host()
-        for _ in range(2):
-            wl.step_host()
-        e2e_steps = max(2, min(args.steps, 5))
-        _, wall = timed(wl.step_host, e2e_steps)
-        if world > 1:
-            t = torch.tensor([wall], dtype=torch.float64, device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            wall = float(t.item())
-        e2e = {"value": wl.value(wl.work_total, wall / e2e_steps), "unit": wl.unit,
-               "h2d_bytes_per_step": int(wl.h2d), "d2h_bytes_per_step": int(wl.d2h), "steps": e2e_steps,
-               "timing": "host wall clock around synchronous C-ABI host calls (pinned host buffers), max over ranks"}
-
-    if rank == 0:
-        peaks = measured_peaks()
-        if wl.bound == "tensor":
-            peak = peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])
-            if wl.dtype == "f32":
-                peak /= 6.0  # TF32 runs at half the 16-bit rate and every product takes three MMAs
-                peak_note = "cuBLAS bf16 8192^3 burst / 6: TF32 rate over three products"
-            elif wl.dtype == "fp8":
-                peak *= 2.0  # the fp8 tensor rate is twice the 16-bit rate; no fp8 figure is measured
-                peak_note = "2 x cuBLAS bf16 8192^3 burst, standing in for the dense fp8 rate"
-            elif wl.dtype == "i8" and getattr(wl, "variant", "") == "sp24":
-                peak *= 4.0  # sparse int8: twice the dense int8 rate (measured: 112 clocks per 256x224x64 pair MMA)
-                peak_note = "4 x cuBLAS bf16 8192^3 burst, standing in for the 2:4-sparse int8 rate"
-            elif wl.dtype == "i8":
-                peak *= 2.0  # the dense int8 tensor rate is twice the 16-bit rate; no int8 figure is measured
-                peak_note = "2 x cuBLAS bf16 8192^3 burst, standing in for the dense int8 rate"
-            elif wl.dtype == "f64":
-                peak = 40.0
-                peak_note = "nominal B200 fp64 tensor rate; no measured figure"
-            else:
-                peak_note = "cuBLAS bf16 8192^3 burst"
-            achieved = wl.work_local / (ms_step * 1e-3) / 1e12
-            roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s" if wl.dtype != "i8" else "TOP/s",
-                    "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(wl.name),
-                    "peak_source": f"{peaks['_source']} ({peak_note})"}
-            # the vendor's dense figures, for context: 2250 TFLOP/s 16-bit, 4500 fp8 / int8, 9000 for 2:4-sparse int8,
-            # 1125 / 3 for fp32 through three TF32 products, 40 fp64
-            nominal = {"f16": 2250.0, "bf16": 2250.0, "fp8": 4500.0, "i4": 4500.0, "f32": 375.0, "f64": 40.0}.get(wl.dtype)
-            if wl.dtype == "i8":
-                nominal = 9000.0 if getattr(wl, "variant", "") == "sp24" else 4500.0
-            if nominal:
-                roof["nominal_peak"] = nominal
-                roof["frac_of_nominal"] = achieved / nominal
-        else:
-            peak = peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"])
-            nbytes = wl.bytes_per_sample * wl.work_local if hasattr(wl, "bytes_per_sample") else wl.work_local
-            achieved = nbytes / (ms_step * 1e-3) / 1e9
-            roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                    "traffic": NCU_TRAFFIC_BYTES.get(wl.name), "peak_source": f"{peaks['_source']} (copy bandwidth)"}
-            if copy_same:
-                roof["copy_same_bytes"] = copy_same  # GB/s of torch copy_ moving the same bytes per launch
-                roof["frac_of_copy_same_bytes"] = achieved / copy_same
-            roof["nominal_peak"] = 8000.0  # GB/s, the vendor's HBM3e figure
-            roof["frac_of_nominal"] = achieved / 8000.0
-        line = {
-            "metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": wl.scaling,
-            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seeded counter-based generator)",
-            "config": wl.config(world), "roofline": roof, "clocks": sampler.summary(),
-            "gpu_launches": args.steps * getattr(wl, "launches_per_step", 1),
-            "a_broadcast_ms": wl.a_broadcast_ms,
-        }
-        if e2e:
-            line["e2e"] = e2e
-        if sustained:
-            ref = peaks.get("bf16_tflops_sustained")
+        # Tensor-bound workloads: the same step repeated for a few seconds.  The timed K steps above are a burst (the part
+        # has not settled under its power cap yet); this is the rate it holds, to set beside the sustained library figure.
+        sustained = None
+        if headline and wl.bound == "tensor" and args.sustained_seconds > 0:
+            per_batch = max(10, int(0.25 / max(ms_step * 1e-3, 1e-6)))
+            done, ms_acc = 0, 0.0
+            # the batch count comes from the (rank-reduced) step time, so every rank runs the same number of batches
+            batches = max(1, int(args.sustained_seconds / (per_batch * ms_step * 1e-3) + 0.5))
+            for _ in range(batches):
+                ms_b, _ = self.timed(wl.step, per_batch)
+                ms_acc += ms_b
+                done += per_batch
+            sustained = {"value": wl.value(wl.work_total, ms_acc / done * 1e-3), "unit": wl.unit, "launches": done,
+                         "seconds": ms_acc * 1e-3}
+            ref = self.peaks.get("bf16_tflops_sustained")
             if ref and wl.dtype == "f16":
-                sustained["frac_of_sustained_peak"] = sustained["value"] / ref  # measured cuBLAS bf16 sustained loop
-            line["sustained"] = sustained
-        if world == 1 and not args.no_cpu:
-            line["cpu_baseline"] = cpu_baseline(wl)
+                # the aggregate over all ranks against as many GPUs' worth of the measured one-GPU cuBLAS bf16 loop
+                sustained["frac_of_sustained_peak"] = sustained["value"] / (ref * world)
+
+        # HBM-bound workloads: a plain device-to-device copy moving the same number of bytes per launch, timed the same
+        # way (sources and destinations rotate through sets larger than L2).  The measured copy peak is a large-transfer
+        # figure; at these launch sizes a copy does not reach it either, and this figure says what does.
+        copy_same = None
+        if wl.bound == "hbm" and not args.no_copy_ref:
+            nbytes_launch = wl.bytes_per_sample * wl.work_local if hasattr(wl, "bytes_per_sample") else wl.work_local
+            half = max(int(nbytes_launch) // 2 // 4 * 4, 4)
+            if half <= (6 << 30):
+                nbuf = max(2, int((300 << 20) // half) + 1)
+                srcs = [torch.empty(half, dtype=torch.uint8, device="cuda") for _ in range(nbuf)]
+                dsts = [torch.empty(half, dtype=torch.uint8, device="cuda") for _ in range(nbuf)]
+                state = {"i": 0}
+
+                def copy_step():
+                    i = state["i"]
+                    dsts[i % nbuf].copy_(srcs[i % nbuf])
+                    state["i"] = i + 1
+
+                for _ in range(3):
+                    copy_step()
+                ms_copy, _ = self.timed(copy_step, steps)
+                copy_same = 2.0 * half / (ms_copy / steps * 1e-3) / 1e9
+                del srcs, dsts
+
+        # end to end: host buffers through the C ABI host drivers, copies inside the timed region
+        e2e = None
+        if hasattr(wl, "setup_host") and getattr(wl, "has_host", True) and not args.no_e2e:
+            wl.setup_host()
+            for _ in range(2):
+                wl.step_host()
+            e2e_steps = max(2, min(steps, 5)) if headline else 3
+            _, wall = self.timed(wl.step_host, e2e_steps)
+            wall = self.reduce_max(wall)
+            e2e = {"value": wl.value(wl.work_total, wall / e2e_steps), "unit": wl.unit,
+                   "h2d_bytes_per_step": int(wl.h2d), "d2h_bytes_per_step": int(wl.d2h), "steps": e2e_steps,
+                   "timing": "host wall clock around synchronous C-ABI host calls (pinned host buffers), max over ranks"}
+            if hasattr(wl, "host_parity_prepare"):
+                wl.host_parity_prepare()
+            e2e["parity_check"] = self.merge_parity(wl.parity(host=True))
+            stages = getattr(wl, "host_stage_ms", None)
+            if stages:
+                e2e["stage_ms"] = stages()
+
+        out = {
+            "metric": wl.metric, "value": value, "unit": wl.unit, "steps": steps, "warmup": max(warmup, 3),
+            "ms_per_step": ms_step, "dtype": wl.dtype, "config": wl.config(world),
+            "roofline": roofline_of(wl, ms_step, self.peaks, copy_same), "clocks": sampler.summary(),
+            "gpu_launches": steps * getattr(wl, "launches_per_step", 1), "parity_check": parity,
+        }
+        if getattr(wl, "a_broadcast_ms", 0.0):
+            out["a_broadcast_ms"] = wl.a_broadcast_ms
+            if getattr(wl, "a_broadcast_warm_ms", None) is not None:
+                out["a_broadcast_warm_ms"] = wl.a_broadcast_warm_ms
+        if e2e:
+            out["e2e"] = e2e
+        if sustained:
+            out["sustained"] = sustained
+        return out
+
+
+# the other components of the metric, measured after the headline workload in the same process
+ALSO = ["gemm_i8", "gemm_i8_sp24", "gemm_i4", "gemm_bf16", "gemm_fp8", "gemm_f64", "dlrm_fwd", "dlrm_bwd", "sgemv", "dgemv",
+        "frag_simple_hgemm", "frag_perf_hgemm"]
+
+
+def run_gpu_arm(args, wl):
+    import gc
+    H = Harness(args)
+    torch = H.torch
+    main = H.measure(wl, args.steps, args.warmup, headline=True)
+    failed = [] if main["parity_check"]["ok"] else [wl.name]
+    if "e2e" in main and not main["e2e"]["parity_check"]["ok"]:
+        failed.append(wl.name + " (host driver)")
+    cpu = cpu_baseline(wl) if (H.rank == 0 and H.world == 1 and not args.no_cpu) else None
+    also = {}
+    if not args.no_also:
+        for name in ALSO:
+            if name == wl.name:
+                continue
+            del wl
+            gc.collect()
+            torch.cuda.empty_cache()
+            wl = WORKLOADS[name]()
+            r = H.measure(wl, max(args.also_steps, 20), 3, headline=False)
+            if not r["parity_check"]["ok"]:
+                failed.append(name)
+            if "e2e" in r and not r["e2e"]["parity_check"]["ok"]:
+                failed.append(name + " (host driver)")
+            also[name] = r
+    if H.rank == 0:
+        line = {
+            "metric": main["metric"], "value": main["value"], "unit": main["unit"], "n_gpus": H.world, "steps": args.steps,
+            "warmup": main["warmup"], "ms_per_step": main["ms_per_step"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": main["dtype"],
+            "data": "synthetic (seeded counter-based generator)", "config": main["config"],
+            "roofline": main["roofline"], "clocks": main["clocks"], "gpu_launches": main["gpu_launches"],
+            "a_broadcast_ms": main.get("a_broadcast_ms", 0.0), "parity_check": main["parity_check"],
+        }
+        for key in ("a_broadcast_warm_ms", "e2e", "sustained"):
+            if key in main:
+                line[key] = main[key]
+        if cpu:
+            line["cpu_baseline"] = cpu
+        if also:
+            line["also"] = also
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    if H.world > 1:
+        H.dist.barrier()
+        H.dist.destroy_process_group()
+    if failed:
+        raise SystemExit(f"bench.py: parity check failed for {failed}")
 
 
 def main():
@@ -893,6 +1237,8 @@ def main():
     ap.add_argument("--no-copy-ref", action="store_true",
                     help="HBM-bound workloads: skip timing a plain device copy of the same byte count")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
+    ap.add_argument("--no-also", action="store_true", help="measure the headline workload only")
+    ap.add_argument("--also-steps", type=int, default=20, help="timed steps of each `also` workload (at least 20)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]()
     if args.impl == "reference":

@@ -50,6 +50,15 @@ const char* b200wmma_last_error_string(void);
 /* Library version as major*10000 + minor*100 + patch. */
 int b200wmma_version(void);
 
+/* Overrides of the library's own kernel selection, process wide; for A/B measurements and for tests that have to reach
+ * every kernel.  value 0 restores the built-in choice.  Keys:
+ *   "gemm_tile_variant"  dense tcgen05 GEMM tile shape: 1 = 128x256 per SM, 2 = 256x256 per SM pair, 3 = 512x256 per pair
+ *   "gemm_group_m"       rasterisation band height of that GEMM, in row tiles
+ *   "sp24_force_expand"  1: b200wmma_gemm_i8_sp24 always densifies A into the workspace and runs the dense kernel
+ * Unknown keys and out-of-range values return B200WMMA_ERR_INVALID_ARG.  The library reads no environment variable
+ * except B200WMMA_NCCL_LIBRARY (see the multi-GPU section). */
+int b200wmma_set_tuning(const char* key, int value);
+
 /* Synchronises `stream`, then reads and clears the current device's status word.
  * *out_status is B200WMMA_OK or B200WMMA_ERR_DEVICE_TIMEOUT; *out_detail (may be NULL)
  * identifies the wait that gave up (role << 24 | block index). */
@@ -169,7 +178,10 @@ int b200wmma_gemm_i8_sp24_packed(uint32_t m, uint32_t n, uint32_t k,
  *   - Problems with m * k above B200WMMA_SP24_STATIC_SCRATCH_BYTES are refused with
  *     B200WMMA_ERR_UNSUPPORTED; use b200wmma_gemm_i8_sp24 for those.
  *   - The first call on each device looks up the array's device address (once, cached afterwards);
- *     make that first call before starting any stream capture.
+ *     make that first call before starting any stream capture (a first call on a capturing stream is
+ *     refused with B200WMMA_ERR_INVALID_ARG).
+ *   - The array of the device that is current in the calling thread is used; `stream` must belong to
+ *     that device (checked).
  *   - All calls on a device use the same array.  Calls whose GPU work can overlap (different streams,
  *     or different host threads without ordering between them) overwrite each other's data: keep
  *     them ordered on one stream or separate them with events.  Nothing has to be cleared between
@@ -287,6 +299,13 @@ int b200wmma_gemv_f64(uint32_t m, uint32_t n, const double* a, uint32_t lda, int
 typedef struct b200wmma_ctx b200wmma_ctx;
 int b200wmma_ctx_create(b200wmma_ctx** out_ctx);
 int b200wmma_ctx_destroy(b200wmma_ctx* ctx);
+/* Device times (ms, CUDA events) of the stages of the last successful b200wmma_gemm_*_host / _host_mg call on `ctx`:
+ * out_ms5[0] span of the host -> device copies, [1] exchange of A between the GPUs (sum over chunks; 0 on one GPU),
+ * [2] GEMM kernels (sum), [3] device -> host copies (sum), [4] first copy in to last copy out.  The stages overlap,
+ * so [0..3] do not add up to [4].  The GEMM host drivers check every argument before they queue any work; should a
+ * CUDA call fail later, they drain their streams before returning, so the caller's buffers are never in use after
+ * the call returns. */
+int b200wmma_ctx_last_stage_ms(b200wmma_ctx* ctx, float* out_ms5);
 
 int b200wmma_gemm_f16_host(b200wmma_ctx* ctx, uint32_t m, uint32_t n, uint32_t k,
                            const void* a, const void* b, const void* c, void* d,
@@ -321,7 +340,13 @@ int b200wmma_gemv_f64_host(b200wmma_ctx* ctx, uint32_t m, uint32_t n, const doub
  * Rank 0 calls b200wmma_mg_unique_id and ships the B200WMMA_MG_ID_BYTES bytes to the other ranks by any
  * means (a file, MPI, a socket); every rank then calls b200wmma_mg_create with the device it will use
  * current.  b200wmma_mg_broadcast works in place on device memory, asynchronously on `stream`.
- * NCCL is opened at run time (libnccl.so.2); without it these calls return B200WMMA_ERR_UNSUPPORTED.
+ * NCCL is opened at run time (the copy already loaded in the process, else libnccl.so.2; the environment variable
+ * B200WMMA_NCCL_LIBRARY, read at the first of these calls, names another file).  When it cannot be opened, lacks a
+ * needed symbol, or ncclGetUniqueId / ncclCommInitRank fails, these calls return B200WMMA_ERR_UNSUPPORTED with the
+ * reason in b200wmma_last_error_string(); nothing else in the library depends on NCCL.  b200wmma_mg_create is
+ * collective and runs one small broadcast and all-gather, so that NCCL's channel set-up is not left for the first
+ * timed call.  b200wmma_mg_allgather works in place: rank r contributes the bytes_per_rank bytes at
+ * buf + r * bytes_per_rank and afterwards every rank holds all nranks pieces.
  * b200wmma_shard_range gives rank `index` of `parts` its contiguous share of `total` units, which
  * must split into whole granules (e.g. 16 columns, one sample, one row).
  * ------------------------------------------------------------------------------------------ */
@@ -330,14 +355,17 @@ typedef struct b200wmma_mg b200wmma_mg;
 int b200wmma_mg_unique_id(void* id_out);
 int b200wmma_mg_create(b200wmma_mg** out_mg, const void* id, int rank, int nranks);
 int b200wmma_mg_broadcast(b200wmma_mg* mg, void* buf, size_t bytes, int root, void* stream);
+int b200wmma_mg_allgather(b200wmma_mg* mg, void* buf, size_t bytes_per_rank, void* stream);
 int b200wmma_mg_destroy(b200wmma_mg* mg);
 int b200wmma_mg_rank(const b200wmma_mg* mg); /* -1 for a null handle */
 int b200wmma_mg_size(const b200wmma_mg* mg); /*  0 for a null handle */
 /* b200wmma_gemm_f16_host for a column-sharded GEMM (A row-major, B column-major, C / D row-major): n, b, c, d are this
- * rank's block of columns; A is needed whole by every rank, so only rank `root` reads its host copy `a` (ignored
- * elsewhere) and each row block is broadcast over NCCL inside the copy / compute pipeline.  root = -1: every rank
- * holds A on the host; row block i (1024 rows) is uploaded and broadcast by rank i mod nranks, which shares out the
- * upload too.  Collective: every rank of `mg` makes the call with the same m, k, lda, root. */
+ * rank's block of columns; A is needed whole by every rank.  root >= 0: only rank `root` reads its host copy `a`
+ * (ignored elsewhere) and each chunk of rows is broadcast over NCCL inside the copy / compute pipeline.  root = -1:
+ * every rank holds A on the host; the rows are cut into up to four chunks, of each chunk every rank uploads one
+ * equal slice, and one all-gather per chunk assembles it on every GPU (a rank moves A / nranks over PCIe).
+ * Collective: every rank of `mg` makes the call with the same m, k, lda, root, on the device `mg` was created on.
+ * If the call fails on one rank only, the others may be left inside a collective: destroy the handle on every rank. */
 int b200wmma_gemm_f16_host_mg(b200wmma_ctx* ctx, b200wmma_mg* mg, int root, uint32_t m, uint32_t n, uint32_t k,
                               const void* a, const void* b, const void* c, void* d,
                               uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,

@@ -16,6 +16,7 @@ u32, i32, f32, f64, vp, sz = C.c_uint32, C.c_int32, C.c_float, C.c_double, C.c_v
 SIGNATURES = {
     "b200wmma_last_error_string": (C.c_char_p, []),
     "b200wmma_version": (C.c_int, []),
+    "b200wmma_set_tuning": (C.c_int, [C.c_char_p, C.c_int]),
     "b200wmma_device_status": (C.c_int, [vp, C.POINTER(C.c_int), C.POINTER(C.c_uint)]),
     "b200wmma_gemm_f16": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32, f32, f32,
                                     C.c_int, C.c_int, C.c_int, C.c_int, vp]),
@@ -56,6 +57,7 @@ SIGNATURES = {
     "b200wmma_mg_unique_id": (C.c_int, [vp]),
     "b200wmma_mg_create": (C.c_int, [C.POINTER(vp), vp, C.c_int, C.c_int]),
     "b200wmma_mg_broadcast": (C.c_int, [vp, vp, C.c_size_t, C.c_int, vp]),
+    "b200wmma_mg_allgather": (C.c_int, [vp, vp, C.c_size_t, vp]),
     "b200wmma_mg_destroy": (C.c_int, [vp]),
     "b200wmma_mg_rank": (C.c_int, [vp]),
     "b200wmma_mg_size": (C.c_int, [vp]),
@@ -65,6 +67,7 @@ SIGNATURES = {
     "b200wmma_shard_range": (C.c_int, [C.c_uint64, u32, u32, u32, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "b200wmma_ctx_create": (C.c_int, [C.POINTER(vp)]),
     "b200wmma_ctx_destroy": (C.c_int, [vp]),
+    "b200wmma_ctx_last_stage_ms": (C.c_int, [vp, C.POINTER(C.c_float)]),
     "b200wmma_gemm_f16_host": (C.c_int, [vp, u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32, f32, f32,
                                          C.c_int, C.c_int, C.c_int, C.c_int]),
     "b200wmma_gemm_i8_host": (C.c_int, [vp, u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32, i32, i32,

@@ -31,6 +31,11 @@ def _need(t, dtype, name):
         raise TypeError(f"{name} must be a CUDA tensor of dtype {dtype}")
 
 
+def set_tuning(key: str, value: int):
+    """b200wmma_set_tuning: override the library's kernel selection (0 = built-in choice)."""
+    check(lib().b200wmma_set_tuning(key.encode(), int(value)))
+
+
 def device_status():
     """Synchronise the current stream and return (status, detail) of the device status word."""
     st, detail = C.c_int(0), C.c_uint(0)
@@ -144,12 +149,14 @@ def gemm_i4_workspace_bytes(m, n, k):
     return lib().b200wmma_gemm_i4_workspace_bytes(m, n, k)
 
 
-def gemm_i4(m, n, k, a_packed, b_packed, c, d, lda_bytes, ldb_bytes, ldc, ldd, alpha, beta, workspace):
+def gemm_i4(m, n, k, a_packed, b_packed, c, d, lda_bytes, ldb_bytes, ldc, ldd, alpha, beta, workspace=None):
     _need(a_packed, torch.uint8, "a_packed"); _need(b_packed, torch.uint8, "b_packed")
-    _need(d, torch.int32, "d"); _need(workspace, torch.uint8, "workspace")
+    _need(d, torch.int32, "d")
+    if workspace is not None:
+        _need(workspace, torch.uint8, "workspace")
     check(lib().b200wmma_gemm_i4(m, n, k, _ptr(a_packed), _ptr(b_packed), _ptr(c), _ptr(d),
                                  lda_bytes, ldb_bytes, ldc, ldd, alpha, beta,
-                                 _ptr(workspace), workspace.numel(), _stream()))
+                                 _ptr(workspace), 0 if workspace is None else workspace.numel(), _stream()))
 
 
 def simple_sgemm(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta):
@@ -248,6 +255,12 @@ class HostContext:
             return C.c_void_p(t.data_ptr())
         return C.c_void_p(t.ctypes.data)
 
+    def last_stage_ms(self):
+        """Device times of the last GEMM host call: dict of upload / exchange / compute / download / total ms."""
+        out = (C.c_float * 5)()
+        check(lib().b200wmma_ctx_last_stage_ms(self._h, out))
+        return dict(zip(("upload", "exchange", "compute", "download", "total"), (float(x) for x in out)))
+
     def gemm_f16(self, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, out_type):
         check(lib().b200wmma_gemm_f16_host(self._h, m, n, k, self._hp(a), self._hp(b), self._hp(c), self._hp(d),
                                            lda, ldb, ldc, ldd, alpha, beta, ROW_MAJOR, COL_MAJOR, ROW_MAJOR, out_type))
@@ -312,6 +325,15 @@ class MultiGpu:
         if not t.is_cuda or not t.is_contiguous():
             raise ValueError("broadcast needs a contiguous CUDA tensor")
         check(lib().b200wmma_mg_broadcast(self._h, _ptr(t), t.numel() * t.element_size(), root, _stream()))
+
+    def allgather(self, t):
+        """In place, on the current torch stream: rank r contributes the r-th of nranks equal pieces of `t`."""
+        if not t.is_cuda or not t.is_contiguous():
+            raise ValueError("allgather needs a contiguous CUDA tensor")
+        nbytes = t.numel() * t.element_size()
+        if nbytes % self.nranks:
+            raise ValueError("allgather: the buffer does not split into nranks equal pieces")
+        check(lib().b200wmma_mg_allgather(self._h, _ptr(t), nbytes // self.nranks, _stream()))
 
     def close(self):
         if self._h:

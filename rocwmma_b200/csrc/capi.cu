@@ -2,6 +2,7 @@
 // the dense GEMM entry points, and the host-buffer drivers that mirror the reference samples'
 // host functions (allocate / copy in / launch / copy out).
 #include "common.cuh"
+#include "tuning.cuh"
 
 #include <cstring>
 #include <mutex>
@@ -34,16 +35,21 @@ namespace b200wmma
         cudaError_t e   = cudaGetDevice(&dev);
         if(e != cudaSuccess)
             return set_error(B200WMMA_ERR_NO_DEVICE, "no CUDA device: %s", cudaGetErrorString(e));
-        static int cached_major[64];
-        if(dev >= 0 && dev < 64 && cached_major[dev] == 0)
+        static int        cached_major[64];
+        static std::mutex mu;
+        int               major = 0;
         {
-            int major = 0;
-            e         = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
-            if(e != cudaSuccess)
-                return set_error(B200WMMA_ERR_CUDA, "cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
-            cached_major[dev] = major;
+            std::lock_guard<std::mutex> lock(mu);
+            if(dev >= 0 && dev < 64 && cached_major[dev] == 0)
+            {
+                int v = 0;
+                e     = cudaDeviceGetAttribute(&v, cudaDevAttrComputeCapabilityMajor, dev);
+                if(e != cudaSuccess)
+                    return set_error(B200WMMA_ERR_CUDA, "cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
+                cached_major[dev] = v;
+            }
+            major = (dev >= 0 && dev < 64) ? cached_major[dev] : 0;
         }
-        const int major = (dev >= 0 && dev < 64) ? cached_major[dev] : 0;
         if(major != 10)
             return set_error(B200WMMA_ERR_NO_DEVICE,
                              "device %d has compute capability major %d; this library contains "
@@ -52,11 +58,23 @@ namespace b200wmma
         return B200WMMA_OK;
     }
 
+    static unsigned*  g_status_cache[64];
+    static std::mutex g_status_mu;
+
+    bool status_word_ready()
+    {
+        int dev = 0;
+        if(cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+            return false;
+        std::lock_guard<std::mutex> lock(g_status_mu);
+        return g_status_cache[dev] != nullptr;
+    }
+
     int status_word_ptr(unsigned** out)
     {
-        static unsigned*  cache[64];
-        static std::mutex mu;
-        int               dev = 0;
+        unsigned**  cache = g_status_cache;
+        std::mutex& mu    = g_status_mu;
+        int         dev   = 0;
         B200_CHECK_CUDA(cudaGetDevice(&dev));
         B200_REQUIRE(dev >= 0 && dev < 64, B200WMMA_ERR_UNSUPPORTED, "device index %d out of range", dev);
         std::lock_guard<std::mutex> lock(mu);
@@ -70,6 +88,19 @@ namespace b200wmma
         *out = cache[dev];
         return B200WMMA_OK;
     }
+
+    namespace tuning
+    {
+        static std::atomic<int> g_values[NUM_KEYS];
+        int get(Key k)
+        {
+            return g_values[k].load(std::memory_order_relaxed);
+        }
+        void set(Key k, int value)
+        {
+            g_values[k].store(value, std::memory_order_relaxed);
+        }
+    } // namespace tuning
 
     static int check_layouts(const char* who, int la, int lb, int lcd)
     {
@@ -89,6 +120,29 @@ extern "C" const char* b200wmma_last_error_string(void)
 extern "C" int b200wmma_version(void)
 {
     return 100; // 0.1.0
+}
+
+extern "C" int b200wmma_set_tuning(const char* key, int value)
+{
+    clear_error();
+    B200_REQUIRE(key, B200WMMA_ERR_INVALID_ARG, "set_tuning: key must be non-null");
+    static const struct
+    {
+        const char*  name;
+        tuning::Key  key;
+        int          lo, hi;
+    } table[] = {{"gemm_tile_variant", tuning::GEMM_TILE_VARIANT, 0, 3},
+                 {"gemm_group_m", tuning::GEMM_GROUP_M, 0, 1024},
+                 {"sp24_force_expand", tuning::SP24_FORCE_EXPAND, 0, 1}};
+    for(const auto& t : table)
+        if(std::strcmp(key, t.name) == 0)
+        {
+            B200_REQUIRE(value >= t.lo && value <= t.hi, B200WMMA_ERR_INVALID_ARG, "set_tuning: %s takes %d..%d, got %d", key,
+                         t.lo, t.hi, value);
+            tuning::set(t.key, value);
+            return B200WMMA_OK;
+        }
+    return set_error(B200WMMA_ERR_INVALID_ARG, "set_tuning: unknown key '%s'", key);
 }
 
 extern "C" int b200wmma_device_status(void* stream, int* out_status, unsigned* out_detail)
@@ -183,10 +237,12 @@ struct b200wmma_ctx
     cudaStream_t         stream    = nullptr; // compute stream (and the only one for the small drivers)
     cudaStream_t         s_in = nullptr, s_out = nullptr; // copy-in / copy-out streams of the pipelined GEMM driver
     cudaStream_t         s_bc = nullptr; // broadcasts of the multi-GPU GEMM driver (created on first use)
-    std::vector<cudaEvent_t> events;      // reusable, timing disabled
+    std::vector<cudaEvent_t> events;      // reusable
     void*                buf[NBUF] = {nullptr, nullptr, nullptr, nullptr};
     size_t               cap[NBUF] = {0, 0, 0, 0};
     int                  device    = 0;
+    float                stage_ms[5] = {0, 0, 0, 0, 0}; // upload span, exchange, compute, copy-out, total of the last GEMM host call
+    bool                 stage_valid = false;
 };
 
 namespace
@@ -236,37 +292,72 @@ namespace
         while(ctx->events.size() < count)
         {
             cudaEvent_t ev = nullptr;
-            B200_CHECK_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+            B200_CHECK_CUDA(cudaEventCreate(&ev)); // timing enabled: the drivers report per-stage times from them
             ctx->events.push_back(ev);
         }
         return B200WMMA_OK;
     }
 
-    // Host-buffer GEMM as a three-stream pipeline over blocks of rows.  B is copied once; then for each
-    // block of rows: copy A / C rows in (copy-in stream), multiply (compute stream), copy the D rows out
-    // (copy-out stream).  Row blocks of a row-major A / C / D are contiguous, and rows of a GEMM are
-    // independent, so the copies of block i+1 and of block i-1 overlap the kernel of block i and the two
-    // copy directions overlap each other.  `launch(rows, a_dev, c_dev, d_dev)` enqueues one block.
-    // With a multi-GPU handle (`mg`), A is the operand every rank needs whole: only rank `root` uploads it from its
-    // host copy, block by block, and each block is broadcast to the other ranks over NCCL on the copy-in stream
-    // (NVLink instead of one PCIe upload per rank); `a` is ignored on the other ranks.  root = -1: every rank holds A
-    // on the host, and row block i is uploaded and broadcast by rank i mod nranks, so the upload is shared out as well.
-    // Every rank must make the call.
+    // Host-buffer GEMM as a pipeline over chunks of rows on three (multi-GPU: four) streams.  B is copied once; then
+    // for each chunk of rows: copy A / C rows in (copy-in stream), multiply (compute stream), copy the D rows out
+    // (copy-out stream).  Row chunks of a row-major A / C / D are contiguous, and rows of a GEMM are independent, so the
+    // copies of chunk i+1 and of chunk i-1 overlap the kernel of chunk i and the two copy directions overlap each other.
+    // `launch(rows, a_dev, c_dev, d_dev)` enqueues one chunk.
+    //
+    // With a multi-GPU handle (`mg`), A is the operand every rank needs whole.
+    //   root = -1: every rank holds A on the host.  The rows are cut into a few chunks; of each chunk every rank uploads
+    //     one equal slice (1 / nranks of the rows) and one all-gather per chunk, on a stream of its own, assembles the
+    //     chunk on every GPU over NVLink: a rank moves A / nranks over PCIe, and the first multiply starts after the
+    //     first chunk instead of after all of A.
+    //   root >= 0: only rank `root` reads its host copy, chunk by chunk, and broadcasts each chunk; `a` is ignored on
+    //     the other ranks.
+    // Every rank must make the call with the same m, k, lda and root.
+    //
+    // Everything that can be rejected is checked before the first copy is queued.  If a CUDA or NCCL call fails after
+    // that, the streams are drained before the error is returned, so no copy is still reading or writing the caller's
+    // host buffers when the call returns; in the multi-GPU form the other ranks may then be left waiting inside a
+    // collective, and every rank has to destroy the handle (b200wmma_mg_destroy) to recover.
     template <typename Launch>
     int gemm_host_pipeline(b200wmma_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b,
                            const void* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
                            size_t in_es, size_t out_es, bool use_c, Launch launch, b200wmma_mg* mg = nullptr, int root = 0)
     {
         const int my_rank = mg ? b200wmma_mg_rank(mg) : 0, nranks = mg ? b200wmma_mg_size(mg) : 1;
-        const size_t ba = extent(m, k, lda) * in_es, bb = extent(n, k, ldb) * in_es;
+        // ---- checks that precede any queued work (the kernels' own launch checks repeat some of these) ----
+        B200_REQUIRE((static_cast<uint64_t>(lda) * in_es) % 16 == 0 && (static_cast<uint64_t>(ldb) * in_es) % 16 == 0,
+                     B200WMMA_ERR_ALIGNMENT,
+                     "gemm host driver: the row pitches of A and B must be multiples of 16 bytes (TMA requirement)");
+        if(mg)
+            B200_REQUIRE(mg_device(mg) == ctx->device, B200WMMA_ERR_INVALID_ARG,
+                         "gemm host driver: the context was created on device %d, the multi-GPU handle on device %d",
+                         ctx->device, mg_device(mg));
+        if(int e = require_sm100())
+            return e;
+
+        // ---- row chunks ----
+        // single GPU: 1024 rows (64 pair tiles of 512 x 256 at n = 8192: one round of the GEMM kernel).
+        // multi GPU : up to 4 chunks, each nranks equal slices of whole rows (a multiple of 128 rows per slice).
+        uint32_t chunk_rows = 1024, slice_rows = 0;
+        if(mg && nranks > 1)
+        {
+            uint32_t nchunk = m / (static_cast<uint32_t>(nranks) * 256u);
+            nchunk          = nchunk < 1 ? 1 : (nchunk > 4 ? 4 : nchunk);
+            slice_rows      = (m + nchunk * nranks - 1) / (nchunk * nranks);
+            slice_rows      = (slice_rows + 127u) & ~127u;
+            chunk_rows      = slice_rows * static_cast<uint32_t>(nranks);
+        }
+        const uint32_t chunks = (m + chunk_rows - 1) / chunk_rows;
+        // A on the device is sized in whole chunks: the last all-gather may move (never-read) rows past m
+        const size_t ba = mg && nranks > 1 ? static_cast<size_t>(chunks) * chunk_rows * lda * in_es : extent(m, k, lda) * in_es;
+        const size_t bb = extent(n, k, ldb) * in_es;
         const size_t bc = extent(m, n, ldc) * out_es, bd = extent(m, n, ldd) * out_es;
         if(int e = ctx_reserve(ctx, 0, ba)) return e;
         if(int e = ctx_reserve(ctx, 1, bb)) return e;
         if(int e = ctx_reserve(ctx, 2, use_c ? bc : 16)) return e;
         if(int e = ctx_reserve(ctx, 3, bd)) return e;
-        const uint32_t block_rows = 1024; // 64 pair tiles of 512 x 256 at n = 8192: one round of the GEMM kernel
-        const uint32_t blocks     = (m + block_rows - 1) / block_rows;
-        if(int e = ctx_events(ctx, 3 * static_cast<size_t>(blocks) + 1)) return e;
+        // events per chunk: A in, exchange begin, exchange end, C in, compute begin, compute end, copy-out end; +3 overall
+        constexpr size_t PER = 7;
+        if(int e = ctx_events(ctx, PER * static_cast<size_t>(chunks) + 3)) return e;
         if(mg && !ctx->s_bc)
             B200_CHECK_CUDA(cudaStreamCreateWithFlags(&ctx->s_bc, cudaStreamNonBlocking));
         char*       da = static_cast<char*>(ctx->buf[0]);
@@ -275,48 +366,138 @@ namespace
         const char* ha = static_cast<const char*>(a);
         const char* hc = static_cast<const char*>(c);
         char*       hd = static_cast<char*>(d);
+        cudaEvent_t ev_start = ctx->events[PER * chunks], ev_b = ctx->events[PER * chunks + 1],
+                    ev_in_end = ctx->events[PER * chunks + 2];
+        ctx->stage_valid = false;
 
-        B200_CHECK_CUDA(cudaMemcpyAsync(ctx->buf[1], b, bb, cudaMemcpyHostToDevice, ctx->s_in));
-        for(uint32_t i = 0; i < blocks; ++i)
+        int         rc   = B200WMMA_OK;
+        cudaError_t cerr = cudaSuccess;
+#define PIPE_CUDA(expr)                                                                                     \
+    do                                                                                                      \
+    {                                                                                                       \
+        cerr = (expr);                                                                                      \
+        if(cerr != cudaSuccess)                                                                             \
+        {                                                                                                   \
+            rc = set_error(B200WMMA_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(cerr),     \
+                           __FILE__, __LINE__);                                                             \
+            goto drain;                                                                                     \
+        }                                                                                                   \
+    } while(0)
+
+        PIPE_CUDA(cudaEventRecord(ev_start, ctx->s_in));
+        for(uint32_t i = 0; i < chunks; ++i)
         {
-            const uint32_t r0 = i * block_rows, rows = (m - r0 < block_rows) ? m - r0 : block_rows;
+            const uint32_t r0 = i * chunk_rows, rows = (m - r0 < chunk_rows) ? m - r0 : chunk_rows;
             const size_t   oa = static_cast<size_t>(r0) * lda * in_es, oc = static_cast<size_t>(r0) * ldc * out_es,
                          od = static_cast<size_t>(r0) * ldd * out_es;
-            const int blk_root = root >= 0 ? root : static_cast<int>(i % static_cast<uint32_t>(nranks));
-            if(mg == nullptr || my_rank == blk_root)
-                B200_CHECK_CUDA(cudaMemcpyAsync(da + oa, ha + oa, extent(rows, k, lda) * in_es, cudaMemcpyHostToDevice, ctx->s_in));
-            if(mg)
+            cudaEvent_t* ev = &ctx->events[PER * i]; // [0] A in, [1] exch begin, [2] exch end, [3] C in, [4] / [5] compute, [6] out
+            // ---- A rows of the chunk: the whole chunk (single GPU / the root), or this rank's slice of it ----
+            if(!mg || nranks == 1)
+                PIPE_CUDA(cudaMemcpyAsync(da + oa, ha + oa, extent(rows, k, lda) * in_es, cudaMemcpyHostToDevice, ctx->s_in));
+            else if(root >= 0)
             {
-                // the broadcasts run on a stream of their own, so that this rank's later uploads do not queue behind
-                // a broadcast that waits for another rank's upload
-                cudaEvent_t ev_up = ctx->events[2 * static_cast<size_t>(blocks) + 1 + i];
-                if(my_rank == blk_root)
-                {
-                    B200_CHECK_CUDA(cudaEventRecord(ev_up, ctx->s_in));
-                    B200_CHECK_CUDA(cudaStreamWaitEvent(ctx->s_bc, ev_up, 0));
-                }
-                if(int e = b200wmma_mg_broadcast(mg, da + oa, extent(rows, k, lda) * in_es, blk_root, ctx->s_bc))
-                    return e;
-                B200_CHECK_CUDA(cudaEventRecord(ev_up, ctx->s_bc)); // reused: now "block i of A is on this device"
-                B200_CHECK_CUDA(cudaStreamWaitEvent(ctx->stream, ev_up, 0));
+                if(my_rank == root)
+                    PIPE_CUDA(cudaMemcpyAsync(da + oa, ha + oa, extent(rows, k, lda) * in_es, cudaMemcpyHostToDevice, ctx->s_in));
             }
+            else
+            {
+                const uint32_t s0 = r0 + static_cast<uint32_t>(my_rank) * slice_rows; // first row of this rank's slice
+                if(s0 < m)
+                {
+                    const uint32_t srows = (m - s0 < slice_rows) ? m - s0 : slice_rows;
+                    const size_t   os    = static_cast<size_t>(s0) * lda * in_es;
+                    PIPE_CUDA(cudaMemcpyAsync(da + os, ha + os, extent(srows, k, lda) * in_es, cudaMemcpyHostToDevice, ctx->s_in));
+                }
+            }
+            PIPE_CUDA(cudaEventRecord(ev[0], ctx->s_in));
+            if(i == 0)
+            {
+                PIPE_CUDA(cudaMemcpyAsync(ctx->buf[1], b, bb, cudaMemcpyHostToDevice, ctx->s_in));
+                PIPE_CUDA(cudaEventRecord(ev_b, ctx->s_in));
+                PIPE_CUDA(cudaStreamWaitEvent(ctx->stream, ev_b, 0));
+            }
+            // ---- exchange: the chunk reaches every rank over NVLink, on a stream of its own so that this rank's later
+            //      uploads do not queue behind a collective that waits for another rank ----
+            if(mg && nranks > 1)
+            {
+                PIPE_CUDA(cudaStreamWaitEvent(ctx->s_bc, ev[0], 0));
+                PIPE_CUDA(cudaEventRecord(ev[1], ctx->s_bc));
+                if(root >= 0)
+                    rc = mg_broadcast_here(mg, da + oa, extent(rows, k, lda) * in_es, root, ctx->s_bc);
+                else
+                    rc = mg_allgather_here(mg, da + oa, static_cast<size_t>(slice_rows) * lda * in_es, ctx->s_bc);
+                if(rc != B200WMMA_OK)
+                    goto drain;
+                PIPE_CUDA(cudaEventRecord(ev[2], ctx->s_bc)); // "chunk i of A is on this device"
+                PIPE_CUDA(cudaStreamWaitEvent(ctx->stream, ev[2], 0));
+            }
+            else
+                PIPE_CUDA(cudaStreamWaitEvent(ctx->stream, ev[0], 0));
             if(use_c)
-                B200_CHECK_CUDA(cudaMemcpyAsync(dc + oc, hc + oc, extent(rows, n, ldc) * out_es, cudaMemcpyHostToDevice, ctx->s_in));
-            cudaEvent_t ev_in = ctx->events[2 * i], ev_done = ctx->events[2 * i + 1];
-            B200_CHECK_CUDA(cudaEventRecord(ev_in, ctx->s_in)); // B (first block) and this block's rows are on the device
-            B200_CHECK_CUDA(cudaStreamWaitEvent(ctx->stream, ev_in, 0));
-            if(int e = launch(rows, da + oa, use_c ? dc + oc : nullptr, dd + od))
-                return e;
-            B200_CHECK_CUDA(cudaEventRecord(ev_done, ctx->stream));
-            B200_CHECK_CUDA(cudaStreamWaitEvent(ctx->s_out, ev_done, 0));
-            B200_CHECK_CUDA(cudaMemcpyAsync(hd + od, dd + od, extent(rows, n, ldd) * out_es, cudaMemcpyDeviceToHost, ctx->s_out));
+                PIPE_CUDA(cudaMemcpyAsync(dc + oc, hc + oc, extent(rows, n, ldc) * out_es, cudaMemcpyHostToDevice, ctx->s_in));
+            PIPE_CUDA(cudaEventRecord(ev[3], ctx->s_in));
+            PIPE_CUDA(cudaStreamWaitEvent(ctx->stream, ev[3], 0));
+            PIPE_CUDA(cudaEventRecord(ev[4], ctx->stream));
+            rc = launch(rows, da + oa, use_c ? dc + oc : nullptr, dd + od);
+            if(rc != B200WMMA_OK)
+                goto drain;
+            PIPE_CUDA(cudaEventRecord(ev[5], ctx->stream));
+            PIPE_CUDA(cudaStreamWaitEvent(ctx->s_out, ev[5], 0));
+            PIPE_CUDA(cudaMemcpyAsync(hd + od, dd + od, extent(rows, n, ldd) * out_es, cudaMemcpyDeviceToHost, ctx->s_out));
+            PIPE_CUDA(cudaEventRecord(ev[6], ctx->s_out));
         }
-        B200_CHECK_CUDA(cudaStreamSynchronize(ctx->s_out));
-        B200_CHECK_CUDA(cudaStreamSynchronize(ctx->s_in));
-        if(mg)
-            B200_CHECK_CUDA(cudaStreamSynchronize(ctx->s_bc));
+        PIPE_CUDA(cudaEventRecord(ev_in_end, ctx->s_in));
+#undef PIPE_CUDA
+    drain:
+        // both exits: nothing of this call may still be in flight when it returns
+        {
+            cudaError_t e1 = cudaStreamSynchronize(ctx->s_out), e2 = cudaStreamSynchronize(ctx->s_in),
+                        e3 = mg && ctx->s_bc ? cudaStreamSynchronize(ctx->s_bc) : cudaSuccess,
+                        e4 = cudaStreamSynchronize(ctx->stream);
+            if(rc == B200WMMA_OK)
+                for(cudaError_t e : {e1, e2, e3, e4})
+                    if(e != cudaSuccess)
+                    {
+                        rc = set_error(B200WMMA_ERR_CUDA, "gemm host driver: %s", cudaGetErrorString(e));
+                        break;
+                    }
+        }
+        if(rc != B200WMMA_OK)
+            return rc;
+        // ---- per-stage device times of this call (ms): upload span, exchange, compute, copy-out (sums), total span ----
+        {
+            float up = 0, ex = 0, cp = 0, out = 0, total = 0, t = 0;
+            bool  ok = cudaEventElapsedTime(&up, ev_start, ev_in_end) == cudaSuccess;
+            for(uint32_t i = 0; ok && i < chunks; ++i)
+            {
+                cudaEvent_t* ev = &ctx->events[PER * i];
+                if(mg && nranks > 1)
+                {
+                    ok = cudaEventElapsedTime(&t, ev[1], ev[2]) == cudaSuccess;
+                    ex += t;
+                }
+                ok = ok && cudaEventElapsedTime(&t, ev[4], ev[5]) == cudaSuccess;
+                cp += t;
+                ok = ok && cudaEventElapsedTime(&t, ev[5], ev[6]) == cudaSuccess;
+                out += t;
+            }
+            ok = ok && cudaEventElapsedTime(&total, ev_start, ctx->events[PER * (chunks - 1) + 6]) == cudaSuccess;
+            ctx->stage_ms[0] = up, ctx->stage_ms[1] = ex, ctx->stage_ms[2] = cp, ctx->stage_ms[3] = out, ctx->stage_ms[4] = total;
+            ctx->stage_valid = ok;
+        }
         return finish(ctx);
     }
+}
+
+extern "C" int b200wmma_ctx_last_stage_ms(b200wmma_ctx* ctx, float* out_ms5)
+{
+    clear_error();
+    B200_REQUIRE(ctx && out_ms5, B200WMMA_ERR_INVALID_ARG, "ctx_last_stage_ms: ctx and out_ms5 must be non-null");
+    B200_REQUIRE(ctx->stage_valid, B200WMMA_ERR_UNSUPPORTED,
+                 "ctx_last_stage_ms: no stage times (the last call on this context was not a GEMM host driver, or it failed)");
+    for(int i = 0; i < 5; ++i)
+        out_ms5[i] = ctx->stage_ms[i];
+    return B200WMMA_OK;
 }
 
 extern "C" int b200wmma_ctx_create(b200wmma_ctx** out_ctx)
@@ -480,6 +661,20 @@ extern "C" int b200wmma_gemm_i8_host_mg(b200wmma_ctx* ctx, b200wmma_mg* mg, int 
         mg, root);
 }
 
+// A failed call inside a host driver, after copies from / to the caller's buffers may already be queued: drain the
+// stream first, so that nothing of the call is still in flight when the error is returned.
+#define HOST_CHECK_CUDA(ctx, expr)                                                                          \
+    do                                                                                                      \
+    {                                                                                                       \
+        cudaError_t _e = (expr);                                                                            \
+        if(_e != cudaSuccess)                                                                               \
+        {                                                                                                   \
+            cudaStreamSynchronize((ctx)->stream);                                                           \
+            return ::b200wmma::set_error(B200WMMA_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                 \
+                                         cudaGetErrorString(_e), __FILE__, __LINE__);                       \
+        }                                                                                                   \
+    } while(0)
+
 extern "C" int b200wmma_dlrm_fwd_host(b200wmma_ctx* ctx, const void* input, void* output, uint32_t m,
                                       uint32_t m_stride, uint32_t k, uint32_t batch, uint32_t out_stride)
 {
@@ -492,10 +687,13 @@ extern "C" int b200wmma_dlrm_fwd_host(b200wmma_ctx* ctx, const void* input, void
     const size_t bo = static_cast<size_t>(batch) * out_stride * 2;
     if(int e = ctx_reserve(ctx, 0, bi)) return e;
     if(int e = ctx_reserve(ctx, 3, bo)) return e;
-    B200_CHECK_CUDA(cudaMemcpyAsync(ctx->buf[0], input, bi, cudaMemcpyHostToDevice, ctx->stream));
+    HOST_CHECK_CUDA(ctx, cudaMemcpyAsync(ctx->buf[0], input, bi, cudaMemcpyHostToDevice, ctx->stream));
     if(int e = b200wmma_dlrm_fwd(ctx->buf[0], ctx->buf[3], m, m_stride, k, batch, out_stride, ctx->stream))
+    {
+        cudaStreamSynchronize(ctx->stream); // the input copy must not outlive the call
         return e;
-    B200_CHECK_CUDA(cudaMemcpyAsync(output, ctx->buf[3], bo, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    HOST_CHECK_CUDA(ctx, cudaMemcpyAsync(output, ctx->buf[3], bo, cudaMemcpyDeviceToHost, ctx->stream));
     return finish(ctx);
 }
 
@@ -516,17 +714,20 @@ extern "C" int b200wmma_dlrm_bwd_host(b200wmma_ctx* ctx, const void* input, cons
     if(int e = ctx_reserve(ctx, 1, bu)) return e;
     if(int e = ctx_reserve(ctx, 2, bm)) return e;
     if(int e = ctx_reserve(ctx, 3, bi)) return e;
-    B200_CHECK_CUDA(cudaMemcpyAsync(ctx->buf[0], input, bi, cudaMemcpyHostToDevice, ctx->stream));
-    B200_CHECK_CUDA(cudaMemcpyAsync(ctx->buf[1], upstream, bu, cudaMemcpyHostToDevice, ctx->stream));
+    HOST_CHECK_CUDA(ctx, cudaMemcpyAsync(ctx->buf[0], input, bi, cudaMemcpyHostToDevice, ctx->stream));
+    HOST_CHECK_CUDA(ctx, cudaMemcpyAsync(ctx->buf[1], upstream, bu, cudaMemcpyHostToDevice, ctx->stream));
     // rows m..m_stride-1 of grad are not written by the kernel: keep what the host passed in
     if(m_stride != m)
-        B200_CHECK_CUDA(cudaMemcpyAsync(ctx->buf[3], grad, bi, cudaMemcpyHostToDevice, ctx->stream));
+        HOST_CHECK_CUDA(ctx, cudaMemcpyAsync(ctx->buf[3], grad, bi, cudaMemcpyHostToDevice, ctx->stream));
     if(int e = b200wmma_dlrm_bwd(ctx->buf[0], ctx->buf[1], ctx->buf[3], bottom_mlp_grad ? ctx->buf[2] : nullptr,
                                  m, m_stride, k, batch, upstream_stride, fuse_mlp_into_row0, ctx->stream))
+    {
+        cudaStreamSynchronize(ctx->stream);
         return e;
-    B200_CHECK_CUDA(cudaMemcpyAsync(grad, ctx->buf[3], bi, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    HOST_CHECK_CUDA(ctx, cudaMemcpyAsync(grad, ctx->buf[3], bi, cudaMemcpyDeviceToHost, ctx->stream));
     if(bottom_mlp_grad)
-        B200_CHECK_CUDA(cudaMemcpyAsync(bottom_mlp_grad, ctx->buf[2], bm, cudaMemcpyDeviceToHost, ctx->stream));
+        HOST_CHECK_CUDA(ctx, cudaMemcpyAsync(bottom_mlp_grad, ctx->buf[2], bm, cudaMemcpyDeviceToHost, ctx->stream));
     return finish(ctx);
 }
 
@@ -543,14 +744,17 @@ static int gemv_host(b200wmma_ctx* ctx, uint32_t m, uint32_t n, const T* a, uint
     if(int e = ctx_reserve(ctx, 0, ba)) return e;
     if(int e = ctx_reserve(ctx, 1, n * sizeof(T))) return e;
     if(int e = ctx_reserve(ctx, 3, m * sizeof(T))) return e;
-    B200_CHECK_CUDA(cudaMemcpyAsync(ctx->buf[0], a, ba, cudaMemcpyHostToDevice, ctx->stream));
-    B200_CHECK_CUDA(cudaMemcpyAsync(ctx->buf[1], x, n * sizeof(T), cudaMemcpyHostToDevice, ctx->stream));
-    B200_CHECK_CUDA(cudaMemcpyAsync(ctx->buf[3], y, m * sizeof(T), cudaMemcpyHostToDevice, ctx->stream));
+    HOST_CHECK_CUDA(ctx, cudaMemcpyAsync(ctx->buf[0], a, ba, cudaMemcpyHostToDevice, ctx->stream));
+    HOST_CHECK_CUDA(ctx, cudaMemcpyAsync(ctx->buf[1], x, n * sizeof(T), cudaMemcpyHostToDevice, ctx->stream));
+    HOST_CHECK_CUDA(ctx, cudaMemcpyAsync(ctx->buf[3], y, m * sizeof(T), cudaMemcpyHostToDevice, ctx->stream));
     if(int e = launch(m, n, static_cast<const T*>(ctx->buf[0]), lda, layout_a,
                       static_cast<const T*>(ctx->buf[1]), static_cast<T*>(ctx->buf[3]), alpha, beta,
                       ctx->stream))
+    {
+        cudaStreamSynchronize(ctx->stream);
         return e;
-    B200_CHECK_CUDA(cudaMemcpyAsync(y, ctx->buf[3], m * sizeof(T), cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    HOST_CHECK_CUDA(ctx, cudaMemcpyAsync(y, ctx->buf[3], m * sizeof(T), cudaMemcpyDeviceToHost, ctx->stream));
     return finish(ctx);
 }
 

@@ -41,6 +41,8 @@ namespace b200wmma
     // Device-resident status word {code, detail}; one copy per device (module global).
     // Kernels with bounded waits get its device address from here.
     int status_word_ptr(unsigned** out_dev_ptr);
+    // true once status_word_ptr has resolved (and cleared) the word of the current device
+    bool status_word_ready();
 
     static inline bool aligned16(const void* p)
     {
@@ -103,4 +105,9 @@ namespace b200wmma
                                  size_t packed_bytes, cudaStream_t stream);
     // bytes of scratch with which the kernel fetches the metadata in wide rows (a re-tiled copy)
     size_t sp24_packed_meta_bytes(uint32_t m, uint32_t k);
+    // multi-GPU handle internals for the host-buffer drivers (multi_gpu.cu); the *_here forms assume that the handle's
+    // device is already current.  mg_allgather_here: rank r's bytes_per_rank bytes lie at buf + r * bytes_per_rank.
+    int mg_device(const b200wmma_mg* mg);
+    int mg_broadcast_here(b200wmma_mg* mg, void* buf, size_t bytes, int root, cudaStream_t stream);
+    int mg_allgather_here(b200wmma_mg* mg, void* buf, size_t bytes_per_rank, cudaStream_t stream);
 } // namespace b200wmma

@@ -12,9 +12,8 @@
 // with one streaming pass (16-byte loads and stores) and the dense tcgen05 int8 GEMM runs on the
 // expanded operands.
 #include "common.cuh"
+#include "tuning.cuh"
 
-#include <cstdlib>
-#include <cstring>
 #include <mutex>
 
 namespace b200wmma
@@ -99,14 +98,10 @@ namespace b200wmma
         {
             return (x + 255) & ~static_cast<size_t>(255);
         }
-        // B200WMMA_SP24_PATH=expand sends every sparse GEMM through the densifying pass (comparison aid).
+        // b200wmma_set_tuning("sp24_force_expand", 1) sends every sparse GEMM through the densifying pass (comparison aid).
         static bool force_expansion()
         {
-            static int v = []() {
-                const char* e = std::getenv("B200WMMA_SP24_PATH");
-                return (e && std::strcmp(e, "expand") == 0) ? 1 : 0;
-            }();
-            return v != 0;
+            return tuning::get(tuning::SP24_FORCE_EXPAND) != 0;
         }
     } // namespace i8var
 } // namespace b200wmma
@@ -239,14 +234,37 @@ namespace b200wmma
         // Device address of the array for the current device.  In host code the array's name is only a
         // handle for the runtime, never an address a kernel may use: it is resolved once per device,
         // with that device current, and cached.
-        static int static_scratch_address(int8_t** out)
+        static int static_scratch_address(int8_t** out, cudaStream_t stream)
         {
             static int8_t*    cache[64];
             static std::mutex mu;
             int               dev = 0;
             B200_CHECK_CUDA(cudaGetDevice(&dev));
             B200_REQUIRE(dev >= 0 && dev < 64, B200WMMA_ERR_UNSUPPORTED, "device index %d out of range", dev);
+            // The array of the CURRENT device is used: a stream of another device would run the kernels there with
+            // this device's address.
+            if(stream != nullptr)
+            {
+                int sdev = dev;
+                if(cudaStreamGetDevice(stream, &sdev) == cudaSuccess)
+                    B200_REQUIRE(sdev == dev, B200WMMA_ERR_INVALID_ARG,
+                                 "gemm_i8_sp24_static: the stream belongs to device %d but device %d is current", sdev, dev);
+                else
+                    (void)cudaGetLastError();
+            }
             std::lock_guard<std::mutex> lock(mu);
+            if(!cache[dev] || !status_word_ready())
+            {
+                // first call on this device: the look-ups below (and the status word's, inside the GEMM launch) are
+                // not stream operations and must not happen while the stream is being captured
+                cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+                if(cudaStreamIsCapturing(stream, &cap) == cudaSuccess)
+                    B200_REQUIRE(cap == cudaStreamCaptureStatusNone, B200WMMA_ERR_INVALID_ARG,
+                                 "gemm_i8_sp24_static: the first call on a device sets the library up and cannot be part of a "
+                                 "stream capture; call it once before capturing");
+                else
+                    (void)cudaGetLastError();
+            }
             if(!cache[dev])
             {
                 void* p = nullptr;
@@ -286,7 +304,7 @@ extern "C" int b200wmma_gemm_i8_sp24_static(uint32_t m, uint32_t n, uint32_t k, 
     if(int e = require_sm100())
         return e;
     int8_t* dense = nullptr;
-    if(int e = i8var::static_scratch_address(&dense))
+    if(int e = i8var::static_scratch_address(&dense, as_stream(stream)))
         return e;
     // The expansion writes all m * k bytes it later reads (zeros included), so nothing left in the array
     // by an earlier call can leak into this one and nothing needs clearing first.

@@ -21,9 +21,7 @@
 #include "gemm_tc05_common.cuh"
 #include "gemm_tc05_pair.cuh"
 #include "gemm_tc05_pair512.cuh"
-
-#include <cstdlib>
-#include <cstring>
+#include "tuning.cuh"
 
 namespace b200wmma
 {
@@ -257,31 +255,17 @@ namespace b200wmma
             }
         }
 
-        // Rasterisation band height; B200WMMA_GROUP_M overrides the built-in value (tuning aid).
+        // Tuning overrides set through b200wmma_set_tuning (0 = built-in choice): see tuning.cuh.
         static uint32_t group_override(uint32_t dflt)
         {
-            static int v = []() {
-                const char* e = std::getenv("B200WMMA_GROUP_M");
-                return e ? std::atoi(e) : 0;
-            }();
+            const int v = tuning::get(tuning::GEMM_GROUP_M);
             return v > 0 ? static_cast<uint32_t>(v) : dflt;
         }
-
         // 0 = automatic, 1 = one-CTA tiles, 2 = two-CTA 256x256 pair tiles, 3 = two-CTA 512x256 pair tiles
-        // (environment override for A/B comparisons)
         static int forced_variant()
         {
-            static int v = []() {
-                const char* e = std::getenv("B200WMMA_GEMM_VARIANT");
-                if(e && std::strcmp(e, "1cta") == 0)
-                    return 1;
-                if(e && std::strcmp(e, "2cta") == 0)
-                    return 2;
-                if(e && std::strcmp(e, "2cta512") == 0)
-                    return 3;
-                return 0;
-            }();
-            return v;
+            const int v = tuning::get(tuning::GEMM_TILE_VARIANT);
+            return (v >= 1 && v <= 3) ? v : 0;
         }
 
         template <int KIND, typename OutT, typename ScalarT>
@@ -344,7 +328,7 @@ namespace b200wmma
             // flop), 256 x 256 per pair and 128 x 256 per SM.  All are persistent, so a problem costs
             // ceil(tiles / slots) rounds of one tile each; pick the shape with the smallest estimated
             // time = rounds x outputs per SM per tile / relative speed (measured at 8192^3: 1, 0.955, 0.91).
-            // B200WMMA_GEMM_VARIANT=1cta|2cta|2cta512 forces one, for comparison.
+            // b200wmma_set_tuning("gemm_tile_variant", 1 | 2 | 3) forces one, for comparison.
             const int forced = (a_mn || b_mn || ONLY_Q) ? 3 : forced_variant(); // MN-major operands: 512 x 256 kernel only
             int       pick   = forced;
             if(pick == 0)

@@ -92,6 +92,10 @@ namespace b200wmma
         // device status word {code, detail}) or another thread of the CTA already aborted.
         // No trap, no unbounded loop: the caller unwinds to the kernel's common exit.
         constexpr unsigned STATUS_TIMEOUT_CODE = 5u; // == B200WMMA_ERR_DEVICE_TIMEOUT
+        // Suspend-time hint (ns) of the waits below; 0 = poll with plain try_wait.
+#ifndef B200WMMA_WAIT_HINT_NS
+#define B200WMMA_WAIT_HINT_NS 4000
+#endif
         __device__ __forceinline__ bool mbar_wait_bounded(uint32_t           bar,
                                                           uint32_t           parity,
                                                           volatile uint32_t* cta_abort,
@@ -105,9 +109,17 @@ namespace b200wmma
             uint32_t       spins = 0;
             while(true)
             {
+#if B200WMMA_WAIT_HINT_NS > 0
+                // parked in hardware until the phase completes or the hint runs out: a waiting thread issues a
+                // handful of instructions per wake-up instead of polling
+                if(mbar_try_wait_hint(bar, parity, B200WMMA_WAIT_HINT_NS))
+                    return true;
+                if((++spins & 0x7u) == 0u)
+#else
                 if(mbar_try_wait(bar, parity))
                     return true;
                 if((++spins & 0xFFu) == 0u)
+#endif
                 {
                     if(*cta_abort)
                         return false;

@@ -1,0 +1,20 @@
+// Process-wide tuning overrides of the kernel selection, set through b200wmma_set_tuning() (capi.cu).  They exist for
+// A/B comparisons and for tests that must reach every kernel; 0 always means "the library's own choice".
+#pragma once
+#include <atomic>
+
+namespace b200wmma
+{
+    namespace tuning
+    {
+        enum Key : int
+        {
+            GEMM_TILE_VARIANT = 0, // dense tcgen05 GEMM tile shape: 1 = 128x256 per SM, 2 = 256x256 per SM pair, 3 = 512x256 per pair
+            GEMM_GROUP_M      = 1, // rasterisation band height in row tiles
+            SP24_FORCE_EXPAND = 2, // 1: the 2:4-sparse GEMM always densifies A into the workspace and runs the dense kernel
+            NUM_KEYS
+        };
+        int  get(Key k);
+        void set(Key k, int value);
+    } // namespace tuning
+} // namespace b200wmma

@@ -75,6 +75,10 @@ def test_no_cpu_fallback_in_product_sources():
     (lambda L: L.b200wmma_mg_unique_id(None), 1),
     (lambda L: L.b200wmma_mg_create(None, None, 0, 1), 1),
     (lambda L: L.b200wmma_mg_broadcast(None, 16, 16, 0, None), 1),
+    (lambda L: L.b200wmma_mg_allgather(None, 16, 16, None), 1),
+    (lambda L: L.b200wmma_set_tuning(b"no_such_key", 1), 1),
+    (lambda L: L.b200wmma_set_tuning(b"gemm_tile_variant", 9), 1),
+    (lambda L: L.b200wmma_ctx_last_stage_ms(None, None), 1),
     (lambda L: L.b200wmma_shard_range(1000, 8, 0, 16, C.byref(C.c_uint64()), C.byref(C.c_uint64())), 2),
     (lambda L: L.b200wmma_shard_range(1024, 8, 8, 16, C.byref(C.c_uint64()), C.byref(C.c_uint64())), 1),
 ], ids=["bad_layout_flag", "col_major_a_lda_lt_m", "zero_m", "null_c_with_beta", "lda_too_small",
@@ -83,11 +87,19 @@ def test_no_cpu_fallback_in_product_sources():
         "bf16_bad_layout_flag", "fp8_lda_too_small", "fp8_bad_format", "f32_layout_unsupported", "f32_workspace_small",
         "f32_k_not_4", "repack_k_not_128", "repack_dest_small", "sp24_packed_k_not_128", "sp24_packed_null_meta",
         "simple_sgemm_m_not_16", "simple_dgemm_null_c", "mg_id_null", "mg_create_null", "mg_broadcast_null_handle",
+        "mg_allgather_null_handle", "tuning_unknown_key", "tuning_out_of_range", "stage_ms_null",
         "shard_uneven", "shard_bad_index"])
 def test_argument_checks(call, code):
     L = _lib.lib()
     assert call(L) == code
     assert L.b200wmma_last_error_string()  # a message is always recorded
+
+
+def test_set_tuning_round_trip():
+    L = _lib.lib()
+    for key in (b"gemm_tile_variant", b"gemm_group_m", b"sp24_force_expand"):
+        assert L.b200wmma_set_tuning(key, 1) == 0
+        assert L.b200wmma_set_tuning(key, 0) == 0
 
 
 def test_shard_range_and_destroy_of_null():

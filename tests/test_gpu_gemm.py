@@ -406,40 +406,62 @@ def test_gemm_i8_full_size_row_sample():
     assert torch.equal(col.to(torch.float64), expect)
 
 
-_VARIANT_SCRIPT = r"""
-import sys, numpy as np, torch
-sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[1] + "/tests")
-from oracle import cpu_ref as R
-from rocwmma_b200 import api, datagen as G
-ok = True
-for (m, n, k) in [(640, 768, 320), (1100, 300, 144), (128, 256, 64)]:
-    a = G.uniform_np(1, (m, k), np.float16); b = G.uniform_np(2, (k, n), np.float16); c = G.uniform_np(3, (m, n), np.float16)
-    bs = np.ascontiguousarray(b.T)
-    d = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
-    dev = lambda x: torch.from_numpy(np.ascontiguousarray(x)).cuda()
-    api.gemm_f16(m, n, k, dev(a), dev(bs), dev(c), d, k, k, n, n, 1.0, 1.0)
-    ref = R.gemm(R.port(), m, n, k, a.ravel(), bs.ravel(), c.ravel(), 1.0, 1.0, np.float16).reshape(m, n)
-    bound = R.gemm_abs_bound(m, n, k, a, b, c, 1.0, 1.0)
-    err = np.max(np.abs(d.cpu().numpy().astype(np.float64) - ref.astype(np.float64)) / bound)
-    ok &= bool(np.isfinite(err) and err <= 2e-3)
-    ai = G.int8_np(1, (m, k)); bi = np.ascontiguousarray(G.int8_np(2, (k, n)).T)
-    di = torch.zeros((m, n), dtype=torch.int32, device="cuda")
-    api.gemm_i8(m, n, k, dev(ai), dev(bi), None, di, k, k, n, n, 1, 0)
-    ok &= bool(np.array_equal(di.cpu().numpy(), R.gemm(R.port(), m, n, k, ai.ravel(), bi.ravel(), None, 1, 0, np.int32).reshape(m, n)))
-st, detail = api.device_status()
-print("VARIANT_OK" if ok and st == 0 else f"VARIANT_FAIL status={st}")
-"""
+def test_gemm_i4_full_size_row_sample():
+    """M=N=8192, K=16384 with both operands int4 in [-8, 7], packed two per byte (low nibble = even k): 32
+    seeded-random rows bit-exact against the oracle on the sign-extended operands, and the exact column-sum
+    checksum over the whole output (no element can be missing from it)."""
+    m, n, k = 8192, 8192, 16384
+    a = G.fill_torch(torch.empty((m, k), dtype=torch.int8, device="cuda"), G.SEED_A, "int4")
+    bs = G.fill_torch(torch.empty((n, k), dtype=torch.int8, device="cuda"), G.SEED_B, "int4")
+    assert int(a.min()) >= -8 and int(a.max()) <= 7
+    pack = lambda t: ((t[:, 0::2].to(torch.uint8) & 0xF) | ((t[:, 1::2].to(torch.uint8) & 0xF) << 4)).contiguous()
+    ap, bp = pack(a), pack(bs)
+    ws_bytes = api.gemm_i4_workspace_bytes(m, n, k)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda") if ws_bytes else None
+    d = nan_filled((m, n), torch.int32)
+    api.gemm_i4(m, n, k, ap, bp, None, d, k // 2, k // 2, n, n, 1, 0, ws)
+    assert_status_ok()
+    rows = _rows_sample(m, 32, 96)
+    idx = torch.from_numpy(rows).cuda()
+    ref = oracle_gemm_rows(a[idx].cpu().numpy(), bs.cpu().numpy(), None, 1, 0, np.int32, n, k)
+    assert np.array_equal(d[idx].cpu().numpy(), ref)
+    col = d.to(torch.int64).sum(dim=0)
+    a_sum = a.to(torch.float64).sum(dim=0)
+    expect = bs.to(torch.float64) @ a_sum
+    assert torch.equal(col.to(torch.float64), expect)
 
 
-@pytest.mark.parametrize("variant", ["1cta", "2cta", "2cta512"])
-def test_gemm_every_tile_variant(variant, tmp_path):
+def test_gemm_f64_bench_size_row_sample():
+    """M=N=K=4096 fp64 (the size bench.py measures), alpha=beta=1: all columns of 64 seeded-random rows within
+    1e-12 of the oracle, and the whole output finite."""
+    m = n = k = 4096
+    f = lambda shape, seed: G.fill_torch(torch.empty(shape, dtype=torch.float64, device="cuda"), seed, "uniform")
+    a, bs, c = f((m, k), G.SEED_A), f((n, k), G.SEED_B), f((m, n), G.SEED_C)
+    d = nan_filled((m, n), torch.float64)
+    api.gemm_f64(m, n, k, a, bs, c, d, k, k, n, n, 1.0, 1.0)
+    assert_status_ok()
+    assert bool(torch.isfinite(d).all())
+    rows = _rows_sample(m, 64, 95)
+    idx = torch.from_numpy(rows).cuda()
+    a_r, c_r, d_r = a[idx].cpu().numpy(), c[idx].cpu().numpy(), d[idx].cpu().numpy()
+    b_h = bs.cpu().numpy()
+    ref = oracle_gemm_rows(a_r, b_h, c_r, 1.0, 1.0, np.float64, n, k)
+    bound = R.gemm_abs_bound(len(rows), n, k, a_r, b_h.T, c_r, 1.0, 1.0)
+    assert gemm_rel_err(d_r, ref, bound) <= TOL_F64_OUT
+
+
+@pytest.mark.parametrize("variant", [1, 2, 3], ids=["1cta", "2cta", "2cta512"])
+def test_gemm_every_tile_variant(variant):
     """Each tile shape of the tcgen05 GEMM (one-CTA 128x256, pair 256x256, pair 512x256), forced through
-    B200WMMA_GEMM_VARIANT in a fresh process, on shapes with ragged edges; fp16 within tolerance, int8 exact."""
-    import subprocess
-    import sys
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    script = tmp_path / "variant_check.py"
-    script.write_text(_VARIANT_SCRIPT)
-    env = dict(os.environ, B200WMMA_GEMM_VARIANT=variant)
-    res = subprocess.run([sys.executable, str(script), root], capture_output=True, text=True, env=env, timeout=600)
-    assert "VARIANT_OK" in res.stdout, res.stdout + res.stderr
+    b200wmma_set_tuning, on shapes with ragged edges; fp16 within tolerance, int8 exact."""
+    api.set_tuning("gemm_tile_variant", variant)
+    try:
+        for (m, n, k) in [(640, 768, 320), (1100, 300, 144), (128, 256, 64)]:
+            run_f16(m, n, k, 1.0, 1.0, np.float16)
+            ai = G.int8_np(1, (m, k)); bi = np.ascontiguousarray(G.int8_np(2, (k, n)).T)
+            di = nan_filled((m, n), torch.int32)
+            api.gemm_i8(m, n, k, dev(ai), dev(bi), None, di, k, k, n, n, 1, 0)
+            assert np.array_equal(di.cpu().numpy(), oracle_gemm_rows(ai, bi, None, 1, 0, np.int32, n, k))
+        assert_status_ok()
+    finally:
+        api.set_tuning("gemm_tile_variant", 0)
