@@ -55,6 +55,8 @@ int b200wmma_version(void);
  *   "gemm_tile_variant"  dense tcgen05 GEMM tile shape: 1 = 128x256 per SM, 2 = 256x256 per SM pair, 3 = 512x256 per pair
  *   "gemm_group_m"       rasterisation band height of that GEMM, in row tiles
  *   "sp24_force_expand"  1: b200wmma_gemm_i8_sp24 always densifies A into the workspace and runs the dense kernel
+ *   "gemm_mma_order"     512x256 kernel, MMAs of a tile's first and last K slabs: 1 = accumulator by accumulator (so each
+ *                        accumulator's drain overlaps the other's MMAs), 2 = slab by slab
  * Unknown keys and out-of-range values return B200WMMA_ERR_INVALID_ARG.  The library reads no environment variable
  * except B200WMMA_NCCL_LIBRARY (see the multi-GPU section). */
 int b200wmma_set_tuning(const char* key, int value);
@@ -138,12 +140,15 @@ int b200wmma_gemm_f64(uint32_t m, uint32_t n, uint32_t k,
  *   idx0 | (idx1 << 2) with idx0 < idx1 the kept positions, two groups per byte, low nibble =
  *   even group.  B column major int8, C/D row major int32.
  * i4: A (row major, m x k) and B (column major, k x n) hold int4 values in [-8,7], two per
- *   byte along K, low nibble = even k.  lda / ldb are in BYTES per row / column.
+ *   byte along K, low nibble = even k.  lda / ldb are in BYTES per row / column; k a multiple of 32, packed rows
+ *   16-byte aligned.  The nibbles are sign-extended to int8 inside the kernel (TMA brings the packed bytes to shared
+ *   memory, converter warps rewrite them as the int8 tile the tensor core reads): no int8 copy of the operands ever
+ *   exists in device memory, so `workspace` is not used - NULL / 0 are accepted, and
+ *   b200wmma_gemm_i4_workspace_bytes() returns 0.
  * `workspace` is caller-owned device scratch of at least b200wmma_gemm_*_workspace_bytes().
  *   sp24 with k a multiple of 128 and 16-byte aligned rows (a_vals, a_meta, b and their pitches) runs
  *   on the sparse tensor cores straight from the compressed operands; the workspace is then optional
- *   (NULL / 0 allowed) and only buys a faster metadata fetch.  Every other sp24 shape, and i4 always,
- *   needs it.
+ *   (NULL / 0 allowed) and only buys a faster metadata fetch.  Every other sp24 shape needs it.
  * ------------------------------------------------------------------------------------------ */
 size_t b200wmma_gemm_i8_sp24_workspace_bytes(uint32_t m, uint32_t n, uint32_t k);
 int b200wmma_gemm_i8_sp24(uint32_t m, uint32_t n, uint32_t k,

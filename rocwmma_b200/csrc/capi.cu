@@ -133,7 +133,8 @@ extern "C" int b200wmma_set_tuning(const char* key, int value)
         int          lo, hi;
     } table[] = {{"gemm_tile_variant", tuning::GEMM_TILE_VARIANT, 0, 3},
                  {"gemm_group_m", tuning::GEMM_GROUP_M, 0, 1024},
-                 {"sp24_force_expand", tuning::SP24_FORCE_EXPAND, 0, 1}};
+                 {"sp24_force_expand", tuning::SP24_FORCE_EXPAND, 0, 1},
+                 {"gemm_mma_order", tuning::GEMM_MMA_ORDER, 0, 2}};
     for(const auto& t : table)
         if(std::strcmp(key, t.name) == 0)
         {

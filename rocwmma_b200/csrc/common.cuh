@@ -87,6 +87,10 @@ namespace b200wmma
                             uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha,
                             int32_t beta, int layout_a, int layout_b, int layout_cd,
                             cudaStream_t stream);
+    // packed int4 operands (two per byte along K), unpacked to int8 in the kernel's load path
+    int launch_gemm_tc05_i4(uint32_t m, uint32_t n, uint32_t k, const uint8_t* a_packed, const uint8_t* b_packed,
+                            const int32_t* c, int32_t* d, uint32_t lda_bytes, uint32_t ldb_bytes, uint32_t ldc, uint32_t ldd,
+                            int32_t alpha, int32_t beta, cudaStream_t stream);
     // DLRM dot interaction for shapes beyond the one-warp-per-sample kernels (dlrm_general.cu)
     int launch_dlrm_fwd_general(const void* input, void* output, uint32_t m, uint32_t m_stride, uint32_t k, uint32_t batch,
                                 uint32_t out_stride, bool f32, cudaStream_t stream);

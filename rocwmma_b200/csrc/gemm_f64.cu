@@ -4,7 +4,11 @@
 // 16x16x16 fp64 blocks).  tcgen05 has no fp64 kind, so the math is warp-level
 // mma.sync.m16n8k8.f64 fed from a 3-stage cp.async shared-memory ring:
 //   CTA tile 128x128, K slab 32, 16 warps as 4 (M) x 4 (N), warp tile 32x32.
-// A row major (K contiguous), B column major (K contiguous), C / D row major.
+// Native layouts: A row major (K contiguous), B column major (K contiguous), C / D row major.  A column-major A or a
+// row-major B (M / N contiguous, the reference's other NN / NT / TN / TT cases,
+// docs/api-reference/api-reference-guide.rst:169-187) is loaded into a shared-memory tile that is transposed
+// ([k][m] with a padded pitch), from which the same fragments are read; column-major C / D is the transposed problem
+// D^T = alpha * B^T A^T + beta * C^T with the operands swapped on the host.
 // Measured: the DMMA pipe is ~84 % busy for every variant tried (K slab 16 / 32, 3-5 stages, m16n8k4 / k8 /
 // k16 shapes, 8 or 16 warps: 30.8-31.6 TFLOP/s at 4096^3, 1.96 GHz, no throttling); this is the best of them.
 #include "common.cuh"
@@ -18,16 +22,18 @@ namespace b200wmma
         struct Cfg
         {
             static constexpr int PITCH       = BK + 4; // doubles per shared row: pad -> conflict-free 8-byte reads
-            static constexpr int TILE_ELEMS  = BM * PITCH;
+            static constexpr int PITCH_MN    = BM + 4; // the transposed tile of an M / N-contiguous operand: [k][m]
+            // a tile holds 128 x BK values either as 128 rows of PITCH or as BK rows of PITCH_MN
+            static constexpr int TILE_ELEMS  = (BM * PITCH > BK * PITCH_MN) ? BM * PITCH : BK * PITCH_MN;
             static constexpr int STAGE_ELEMS = 2 * TILE_ELEMS;
             static constexpr size_t SMEM_BYTES = static_cast<size_t>(STAGES) * STAGE_ELEMS * sizeof(double);
         };
 
-        __device__ __forceinline__ void cp_async16_zfill(double* dst, const double* src, bool valid)
+        // 16-byte async copy of which the first `bytes` (16, 8 or 0) come from src; the rest is zero-filled
+        __device__ __forceinline__ void cp_async16_zfill(double* dst, const double* src, int bytes)
         {
-            const uint32_t d  = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
-            const int      sz = valid ? 16 : 0; // src-size 0 -> the 16 bytes are zero-filled
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(sz)
+            const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes)
                          : "memory");
         }
         __device__ __forceinline__ void cp_async_commit()
@@ -63,11 +69,29 @@ namespace b200wmma
                 const uint32_t gr = row0 + r, gk = k0 + ch * 2;
                 const bool     ok = gr < rows && gk < kdim; // kdim is even: a chunk is all in or out
                 const double*  s  = ok ? src + static_cast<size_t>(gr) * ld + gk : src;
-                cp_async16_zfill(dst + r * PITCH + ch * 2, s, ok);
+                cp_async16_zfill(dst + r * PITCH + ch * 2, s, ok ? 16 : 0);
+            }
+        }
+        // The same slab of an operand whose M / N index is the contiguous one (element (row, kk) at src[kk * ld + row]):
+        // chunks of two consecutive rows at one K position land in the transposed tile dst[kk][row].
+        template <int BK, int THREADS>
+        __device__ __forceinline__ void load_slab_mn(double* dst, const double* src, size_t ld, uint32_t rows,
+                                                     uint32_t kdim, uint32_t row0, uint32_t k0)
+        {
+            constexpr int PITCH_MN = BM + 4, CH = BM / 2; // chunks of 2 rows per K position
+#pragma unroll
+            for(int i = 0; i < BK * CH / THREADS; ++i)
+            {
+                const uint32_t idx = threadIdx.x + i * THREADS;
+                const uint32_t kk = idx / CH, ch = idx % CH;
+                const uint32_t gk = k0 + kk, gr = row0 + ch * 2;
+                const int      bytes = (gk < kdim && gr < rows) ? (gr + 1 < rows ? 16 : 8) : 0;
+                const double*  s     = bytes ? src + static_cast<size_t>(gk) * ld + gr : src;
+                cp_async16_zfill(dst + kk * PITCH_MN + ch * 2, s, bytes);
             }
         }
 
-        template <int BK, int STAGES, int WARPS_M, int WARPS_N>
+        template <int BK, int STAGES, int WARPS_M, int WARPS_N, bool A_MN, bool B_MN>
         __global__ void __launch_bounds__(32 * WARPS_M * WARPS_N, 1)
             gemm_f64_kernel(uint32_t m, uint32_t n, uint32_t k, const double* __restrict__ a,
                             const double* __restrict__ b, const double* __restrict__ c,
@@ -75,8 +99,8 @@ namespace b200wmma
                             double alpha, double beta, int vec_ok)
         {
             constexpr int THREADS = 32 * WARPS_M * WARPS_N, WM = BM / WARPS_M, WN = BN / WARPS_N, MI = WM / 16, NJ = WN / 8;
-            constexpr int PITCH = Cfg<BK, STAGES>::PITCH, TILE_ELEMS = Cfg<BK, STAGES>::TILE_ELEMS,
-                          STAGE_ELEMS = Cfg<BK, STAGES>::STAGE_ELEMS;
+            constexpr int PITCH = Cfg<BK, STAGES>::PITCH, PITCH_MN = Cfg<BK, STAGES>::PITCH_MN,
+                          TILE_ELEMS = Cfg<BK, STAGES>::TILE_ELEMS, STAGE_ELEMS = Cfg<BK, STAGES>::STAGE_ELEMS;
             extern __shared__ __align__(16) uint8_t smem_raw[];
             double*        smem = reinterpret_cast<double*>(smem_raw);
             const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -84,6 +108,19 @@ namespace b200wmma
             const uint32_t wm = warp / WARPS_N, wn = warp % WARPS_N;
             const uint32_t row0 = blockIdx.y * BM, col0 = blockIdx.x * BN;
             const uint32_t num_kb = (k + BK - 1) / BK;
+            const auto     row0_of = [](uint32_t block) { return block * static_cast<uint32_t>(BM); }; // BM == BN
+            const auto load_a = [&](double* dst, uint32_t k0) {
+                if constexpr(A_MN)
+                    load_slab_mn<BK, THREADS>(dst, a, lda, m, k, row0_of(blockIdx.y), k0);
+                else
+                    load_slab<BK, THREADS>(dst, a, lda, m, k, row0_of(blockIdx.y), k0);
+            };
+            const auto load_b = [&](double* dst, uint32_t k0) {
+                if constexpr(B_MN)
+                    load_slab_mn<BK, THREADS>(dst, b, ldb, n, k, row0_of(blockIdx.x), k0);
+                else
+                    load_slab<BK, THREADS>(dst, b, ldb, n, k, row0_of(blockIdx.x), k0);
+            };
 
             double acc[MI][NJ][4]; // [m16 tile][n8 tile][c0..c3]
 #pragma unroll
@@ -100,8 +137,8 @@ namespace b200wmma
             {
                 if(static_cast<uint32_t>(s) < num_kb)
                 {
-                    load_slab<BK, THREADS>(smem + s * STAGE_ELEMS, a, lda, m, k, row0, s * BK);
-                    load_slab<BK, THREADS>(smem + s * STAGE_ELEMS + TILE_ELEMS, b, ldb, n, k, col0, s * BK);
+                    load_a(smem + s * STAGE_ELEMS, s * BK);
+                    load_b(smem + s * STAGE_ELEMS + TILE_ELEMS, s * BK);
                 }
                 cp_async_commit();
             }
@@ -115,13 +152,16 @@ namespace b200wmma
                     if(nxt < num_kb)
                     {
                         double* st = smem + (nxt % STAGES) * STAGE_ELEMS;
-                        load_slab<BK, THREADS>(st, a, lda, m, k, row0, nxt * BK);
-                        load_slab<BK, THREADS>(st + TILE_ELEMS, b, ldb, n, k, col0, nxt * BK);
+                        load_a(st, nxt * BK);
+                        load_b(st + TILE_ELEMS, nxt * BK);
                     }
                     cp_async_commit();
                 }
-                const double* as = smem + (kb % STAGES) * STAGE_ELEMS + (wm * WM) * PITCH;
-                const double* bs = smem + (kb % STAGES) * STAGE_ELEMS + TILE_ELEMS + (wn * WN) * PITCH;
+                // element (r, kk) of the warp's part of the tile: K-major tile[r][kk], transposed tile[kk][r]
+                const double* as = smem + (kb % STAGES) * STAGE_ELEMS + (A_MN ? wm * WM : (wm * WM) * PITCH);
+                const double* bs = smem + (kb % STAGES) * STAGE_ELEMS + TILE_ELEMS + (B_MN ? wn * WN : (wn * WN) * PITCH);
+                const auto a_at = [&](int r, int kk) { return A_MN ? as[kk * PITCH_MN + r] : as[r * PITCH + kk]; };
+                const auto b_at = [&](int r, int kk) { return B_MN ? bs[kk * PITCH_MN + r] : bs[r * PITCH + kk]; };
                 {
 #pragma unroll
                     for(int ks = 0; ks < BK; ks += 8)
@@ -131,12 +171,12 @@ namespace b200wmma
                         for(int i = 0; i < MI; ++i)
 #pragma unroll
                             for(int q = 0; q < 4; ++q)
-                                af[i][q] = as[(i * 16 + g + 8 * (q & 1)) * PITCH + ks + 4 * (q >> 1) + t];
+                                af[i][q] = a_at(i * 16 + g + 8 * (q & 1), ks + 4 * (q >> 1) + t);
 #pragma unroll
                         for(int j = 0; j < NJ; ++j)
 #pragma unroll
                             for(int q = 0; q < 2; ++q)
-                                bf[j][q] = bs[(j * 8 + g) * PITCH + ks + 4 * q + t];
+                                bf[j][q] = b_at(j * 8 + g, ks + 4 * q + t);
 #pragma unroll
                         for(int i = 0; i < MI; ++i)
 #pragma unroll
@@ -185,6 +225,51 @@ namespace b200wmma
     } // namespace f64
 } // namespace b200wmma
 
+namespace b200wmma
+{
+    namespace f64
+    {
+        // A is m x k with element (i, h) at a[i * lda + h] (a_mn false) or a[h * lda + i] (a_mn true); B likewise as
+        // n x k; C / D row major.
+        static int launch(uint32_t m, uint32_t n, uint32_t k, const double* a, const double* b, const double* c, double* d,
+                          uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, double alpha, double beta, bool a_mn,
+                          bool b_mn, cudaStream_t stream)
+        {
+            B200_REQUIRE(lda >= (a_mn ? m : k) && ldb >= (b_mn ? n : k) && ldd >= n && (!c || ldc >= n),
+                         B200WMMA_ERR_INVALID_ARG, "gemm_f64: leading dimension smaller than the row/column it strides");
+            B200_REQUIRE(lda % 2 == 0 && ldb % 2 == 0 && aligned16(a) && aligned16(b) && (a_mn || k % 2 == 0)
+                             && (b_mn || k % 2 == 0),
+                         B200WMMA_ERR_ALIGNMENT,
+                         "gemm_f64: lda, ldb (and k, for an operand stored with K contiguous) must be even and A, B 16-byte "
+                         "aligned (16-byte async copies)");
+            if(int e = require_sm100())
+                return e;
+            const int vec_ok = aligned16(d) && ldd % 2 == 0 && (!c || (aligned16(c) && ldc % 2 == 0));
+            dim3      grid(ceil_div(n, BN), ceil_div(m, BM));
+            constexpr int BK = 32, STAGES = 3, WARPS_M = 4, WARPS_N = 4;
+            using KernT = decltype(&gemm_f64_kernel<BK, STAGES, WARPS_M, WARPS_N, false, false>);
+            const KernT kerns[4] = {gemm_f64_kernel<BK, STAGES, WARPS_M, WARPS_N, false, false>,
+                                    gemm_f64_kernel<BK, STAGES, WARPS_M, WARPS_N, false, true>,
+                                    gemm_f64_kernel<BK, STAGES, WARPS_M, WARPS_N, true, false>,
+                                    gemm_f64_kernel<BK, STAGES, WARPS_M, WARPS_N, true, true>};
+            const int   id   = (a_mn ? 2 : 0) + (b_mn ? 1 : 0);
+            KernT       kern = kerns[id];
+            static bool attr_ok_dev[4][MAX_DEVICES];
+            bool&       attr_ok = attr_ok_dev[id][current_device_slot()];
+            if(!attr_ok)
+            {
+                B200_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     static_cast<int>(Cfg<BK, STAGES>::SMEM_BYTES)));
+                attr_ok = true;
+            }
+            kern<<<grid, 32 * WARPS_M * WARPS_N, Cfg<BK, STAGES>::SMEM_BYTES, stream>>>(m, n, k, a, b, c, d, lda, ldb, ldc, ldd,
+                                                                                      alpha, beta, vec_ok);
+            B200_CHECK_CUDA(cudaGetLastError());
+            return B200WMMA_OK;
+        }
+    } // namespace f64
+} // namespace b200wmma
+
 extern "C" int b200wmma_gemm_f64(uint32_t m, uint32_t n, uint32_t k, const double* a, const double* b,
                                  const double* c, double* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
                                  uint32_t ldd, double alpha, double beta, int layout_a, int layout_b,
@@ -195,34 +280,12 @@ extern "C" int b200wmma_gemm_f64(uint32_t m, uint32_t n, uint32_t k, const doubl
     B200_REQUIRE((layout_a == 0 || layout_a == 1) && (layout_b == 0 || layout_b == 1)
                      && (layout_cd == 0 || layout_cd == 1),
                  B200WMMA_ERR_INVALID_ARG, "gemm_f64: layout flags must be 0 (row) or 1 (col)");
-    B200_REQUIRE(layout_a == B200WMMA_ROW_MAJOR && layout_b == B200WMMA_COL_MAJOR
-                     && layout_cd == B200WMMA_ROW_MAJOR,
-                 B200WMMA_ERR_UNSUPPORTED,
-                 "gemm_f64: only A row-major, B column-major, C/D row-major is implemented");
     B200_REQUIRE(m && n && k, B200WMMA_ERR_INVALID_ARG, "gemm_f64: m, n, k must be non-zero");
     B200_REQUIRE(a && b && d, B200WMMA_ERR_INVALID_ARG, "gemm_f64: a, b, d must be non-null");
     B200_REQUIRE(c || beta == 0.0, B200WMMA_ERR_INVALID_ARG, "gemm_f64: c may be null only when beta == 0");
-    B200_REQUIRE(lda >= k && ldb >= k && ldd >= n && (!c || ldc >= n), B200WMMA_ERR_INVALID_ARG,
-                 "gemm_f64: leading dimension smaller than the row/column it strides");
-    B200_REQUIRE(k % 2 == 0 && lda % 2 == 0 && ldb % 2 == 0 && aligned16(a) && aligned16(b),
-                 B200WMMA_ERR_ALIGNMENT,
-                 "gemm_f64: k, lda, ldb must be even and A, B 16-byte aligned (16-byte async copies)");
-    if(int e = require_sm100())
-        return e;
-    const int vec_ok = aligned16(d) && ldd % 2 == 0 && (!c || (aligned16(c) && ldc % 2 == 0));
-    dim3      grid(ceil_div(n, f64::BN), ceil_div(m, f64::BM));
-    constexpr int BK = 32, STAGES = 3, WARPS_M = 4, WARPS_N = 4;
-    auto          kern = f64::gemm_f64_kernel<BK, STAGES, WARPS_M, WARPS_N>;
-    static bool   attr_ok_dev[MAX_DEVICES];
-    bool&         attr_ok = attr_ok_dev[current_device_slot()];
-    if(!attr_ok)
-    {
-        B200_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(f64::Cfg<BK, STAGES>::SMEM_BYTES)));
-        attr_ok = true;
-    }
-    kern<<<grid, 32 * WARPS_M * WARPS_N, f64::Cfg<BK, STAGES>::SMEM_BYTES, as_stream(stream)>>>(m, n, k, a, b, c, d, lda, ldb,
-                                                                                              ldc, ldd, alpha, beta, vec_ok);
-    B200_CHECK_CUDA(cudaGetLastError());
-    return B200WMMA_OK;
+    const bool a_mn = layout_a == B200WMMA_COL_MAJOR, b_mn = layout_b == B200WMMA_ROW_MAJOR;
+    if(layout_cd == B200WMMA_ROW_MAJOR)
+        return f64::launch(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, a_mn, b_mn, as_stream(stream));
+    // column-major C / D: the transposed problem; B^T (n x k) takes A's role and is K-contiguous exactly when B was
+    return f64::launch(n, m, k, b, a, c, d, ldb, lda, ldc, ldd, alpha, beta, b_mn, a_mn, as_stream(stream));
 }

@@ -7,10 +7,10 @@
 //
 // The sparse GEMM runs on the sparse tensor-core path (gemm_tc05_sp.cuh: compressed values and
 // metadata straight into tcgen05.mma.sp) whenever k is a multiple of 128 and the rows are 16-byte
-// aligned.  Otherwise, and always for int4 (the sm_100 tensor cores have no 4-bit integer kind),
-// the compressed operand(s) are expanded to K-major int8 in a caller-provided device workspace
-// with one streaming pass (16-byte loads and stores) and the dense tcgen05 int8 GEMM runs on the
-// expanded operands.
+// aligned.  Otherwise the compressed operand is expanded to K-major int8 in a caller-provided device
+// workspace with one streaming pass (16-byte loads and stores) and the dense tcgen05 int8 GEMM runs on
+// the expanded operand.  The int4 GEMM (the sm_100 tensor cores have no 4-bit integer kind) unpacks to
+// int8 inside its own kernel, between the TMA load and the MMA (gemm_tc05_i4.cuh).
 #include "common.cuh"
 #include "tuning.cuh"
 
@@ -48,40 +48,6 @@ namespace b200wmma
                     const uint32_t nib  = (md >> (4 * gi)) & 0xFu;
                     const uint32_t i0 = nib & 3u, i1 = nib >> 2;
                     out[gi] = ((pair & 0xFFu) << (8 * i0)) | ((pair >> 8) << (8 * i1));
-                }
-                uint4* dst = reinterpret_cast<uint4*>(dense + static_cast<size_t>(row) * k + unit * 32);
-                dst[0]     = make_uint4(out[0], out[1], out[2], out[3]);
-                dst[1]     = make_uint4(out[4], out[5], out[6], out[7]);
-            }
-        }
-
-        // One thread sign-extends 16 packed bytes (32 int4 values, low nibble first) to 32 int8.
-        __global__ void __launch_bounds__(THREADS)
-            unpack_i4_kernel(const uint8_t* __restrict__ packed, int8_t* __restrict__ dense,
-                             uint32_t rows, uint32_t k, size_t ld_bytes)
-        {
-            const uint32_t units_per_row = k >> 5;
-            const size_t   total         = static_cast<size_t>(rows) * units_per_row;
-            for(size_t u = static_cast<size_t>(blockIdx.x) * THREADS + threadIdx.x; u < total;
-                u += static_cast<size_t>(gridDim.x) * THREADS)
-            {
-                const uint32_t row  = static_cast<uint32_t>(u / units_per_row);
-                const uint32_t unit = static_cast<uint32_t>(u - static_cast<size_t>(row) * units_per_row);
-                const uint4    p = __ldcs(reinterpret_cast<const uint4*>(packed + row * ld_bytes + unit * 16));
-                const uint32_t pw[4] = {p.x, p.y, p.z, p.w};
-                uint32_t       out[8];
-#pragma unroll
-                for(int w = 0; w < 4; ++w)
-                {
-                    // bytes b0..b3 of the word -> values (lo0,hi0,lo1,hi1) and (lo2,hi2,lo3,hi3)
-                    const uint32_t x  = pw[w];
-                    const uint32_t lo = x & 0x0F0F0F0Fu, hi = (x >> 4) & 0x0F0F0F0Fu;
-                    // sign-extend each 4-bit field held in its own byte: (v ^ 8) - 8
-                    const uint32_t los = __vsub4(lo ^ 0x08080808u, 0x08080808u);
-                    const uint32_t his = __vsub4(hi ^ 0x08080808u, 0x08080808u);
-                    // interleave bytes: out = lo0 hi0 lo1 hi1 | lo2 hi2 lo3 hi3
-                    out[2 * w]     = __byte_perm(los, his, 0x5140);
-                    out[2 * w + 1] = __byte_perm(los, his, 0x7362);
                 }
                 uint4* dst = reinterpret_cast<uint4*>(dense + static_cast<size_t>(row) * k + unit * 32);
                 dst[0]     = make_uint4(out[0], out[1], out[2], out[3]);
@@ -141,7 +107,8 @@ extern "C" int b200wmma_gemm_i8_sp24_packed(uint32_t m, uint32_t n, uint32_t k, 
 
 extern "C" size_t b200wmma_gemm_i4_workspace_bytes(uint32_t m, uint32_t n, uint32_t k)
 {
-    return i8var::round256(static_cast<size_t>(m) * k) + i8var::round256(static_cast<size_t>(n) * k);
+    (void)m, (void)n, (void)k;
+    return 0; // the int4 GEMM unpacks inside the kernel: no scratch
 }
 
 extern "C" int b200wmma_gemm_i8_sp24(uint32_t m, uint32_t n, uint32_t k, const int8_t* a_vals,
@@ -190,29 +157,9 @@ extern "C" int b200wmma_gemm_i4(uint32_t m, uint32_t n, uint32_t k, const uint8_
                                 void* stream)
 {
     clear_error();
-    B200_REQUIRE(m && n && k, B200WMMA_ERR_INVALID_ARG, "gemm_i4: m, n, k must be non-zero");
-    B200_REQUIRE(a_packed && b_packed && d && workspace, B200WMMA_ERR_INVALID_ARG,
-                 "gemm_i4: a_packed, b_packed, d, workspace must be non-null");
-    B200_REQUIRE(k % 32 == 0, B200WMMA_ERR_UNSUPPORTED, "gemm_i4: k must be a multiple of 32");
-    B200_REQUIRE(lda_bytes >= k / 2 && ldb_bytes >= k / 2, B200WMMA_ERR_INVALID_ARG,
-                 "gemm_i4: lda_bytes / ldb_bytes smaller than k/2");
-    B200_REQUIRE(aligned16(a_packed) && aligned16(b_packed) && lda_bytes % 16 == 0 && ldb_bytes % 16 == 0
-                     && aligned16(workspace),
-                 B200WMMA_ERR_ALIGNMENT, "gemm_i4: packed rows must be 16-byte aligned");
-    B200_REQUIRE(workspace_bytes >= b200wmma_gemm_i4_workspace_bytes(m, n, k), B200WMMA_ERR_INVALID_ARG,
-                 "gemm_i4: workspace too small (%zu < %zu bytes)", workspace_bytes,
-                 b200wmma_gemm_i4_workspace_bytes(m, n, k));
-    if(int e = require_sm100())
-        return e;
-    int8_t* dense_a = static_cast<int8_t*>(workspace);
-    int8_t* dense_b = dense_a + i8var::round256(static_cast<size_t>(m) * k);
-    i8var::unpack_i4_kernel<<<i8var::grid_for(static_cast<size_t>(m) * (k / 32)), i8var::THREADS, 0,
-                              as_stream(stream)>>>(a_packed, dense_a, m, k, lda_bytes);
-    i8var::unpack_i4_kernel<<<i8var::grid_for(static_cast<size_t>(n) * (k / 32)), i8var::THREADS, 0,
-                              as_stream(stream)>>>(b_packed, dense_b, n, k, ldb_bytes);
-    B200_CHECK_CUDA(cudaGetLastError());
-    return launch_gemm_tc05_i8(m, n, k, dense_a, dense_b, c, d, k, k, ldc, ldd, alpha, beta, B200WMMA_ROW_MAJOR,
-                               B200WMMA_COL_MAJOR, B200WMMA_ROW_MAJOR, as_stream(stream));
+    (void)workspace, (void)workspace_bytes; // kept in the signature; the kernel unpacks in its load path and needs none
+    return launch_gemm_tc05_i4(m, n, k, a_packed, b_packed, c, d, lda_bytes, ldb_bytes, ldc, ldd, alpha, beta,
+                               as_stream(stream));
 }
 
 // ---------------------------------------------------------------------------------------------

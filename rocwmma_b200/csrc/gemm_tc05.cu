@@ -356,14 +356,20 @@ namespace b200wmma
 
             if(use_q)
             {
-                using KernT = decltype(&tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT, false, false>);
-                const KernT kerns[4] = {tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT, false, false>,
-                                        tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT, false, true>,
-                                        tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT, true, false>,
-                                        tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT, true, true>};
-                const int   layout_id = (a_mn ? 2 : 0) + (b_mn ? 1 : 0);
+                using KernT = decltype(&tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT, false, false, false>);
+                const KernT kerns[8] = {tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT, false, false, false>,
+                                        tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT, false, true, false>,
+                                        tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT, true, false, false>,
+                                        tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT, true, true, false>,
+                                        tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT, false, false, true>,
+                                        tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT, false, true, true>,
+                                        tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT, true, false, true>,
+                                        tc05q::gemm_tc05_pair512_kernel<KIND, OutT, ScalarT, true, true, true>};
+                // MMA order of a tile's first and last slabs: by accumulator (1, default) or by slab (2)
+                const bool  split     = tuning::get(tuning::GEMM_MMA_ORDER) != 2;
+                const int   layout_id = (a_mn ? 2 : 0) + (b_mn ? 1 : 0) + (split ? 4 : 0);
                 KernT       kern      = kerns[layout_id];
-                static int  max_clusters_dev[4][MAX_DEVICES]; // per template instantiation, layout and device
+                static int  max_clusters_dev[8][MAX_DEVICES]; // per template instantiation, layout and device
                 int&        max_clusters = max_clusters_dev[layout_id][current_device_slot()];
                 const uint32_t tiles_m = ceil_div(m, tc05q::PAIR_M), tiles_n = ceil_div(n, tc05q::TILE_N);
                 cudaLaunchConfig_t  cfg = {};

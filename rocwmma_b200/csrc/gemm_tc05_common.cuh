@@ -220,7 +220,7 @@ namespace b200wmma
         // applies alpha / beta and stores D.  `tmem_acc` is the accumulator's tensor-memory address
         // (lane 0, first column); row_base / col_base locate the CTA's 128 x TILE_N block in D.
         // All 32 lanes must call it together (tcgen05.ld is warp-collective).
-        template <typename OutT, typename ScalarT, uint32_t TILE_N>
+        template <typename OutT, typename ScalarT, uint32_t TILE_N, int ACC_SHIFT = 0>
         __device__ __forceinline__ void drain_accumulator(uint32_t tmem_acc, uint32_t quad, uint32_t lane,
                                                           uint32_t row_base, uint32_t col_base, uint32_t m,
                                                           uint32_t n, const OutT* __restrict__ c,
@@ -237,6 +237,12 @@ namespace b200wmma
                 uint32_t v[32];
                 ptx::tmem_ld_32x32b_x32(tmem_acc + ((quad * 32u) << 16) + ch * 32u, v);
                 ptx::tmem_ld_wait();
+                if constexpr(ACC_SHIFT != 0) // integer accumulators of operands that carry a power-of-two scale
+                {
+#pragma unroll
+                    for(int i = 0; i < 32; ++i)
+                        v[i] = static_cast<uint32_t>(static_cast<int32_t>(v[i]) >> ACC_SHIFT);
+                }
                 const uint32_t col0 = col_base + ch * 32u;
                 if(row_ok && col0 < n)
                 {

@@ -58,9 +58,13 @@ namespace b200wmma
         // accumulator: warp `first` (0 .. STRIDE-1) takes the steps first, first + STRIDE, ...
         // ROW_BYTES: bytes per row of a staging tile, 64 (TMA SWIZZLE_64B) or, for 32-bit outputs, 128 (SWIZZLE_128B:
         // half as many row requests per byte moved).
-        template <typename OutT, typename ScalarT, uint32_t TN = TILE_N, uint32_t STRIDE = 1, uint32_t ROW_BYTES = 64>
+        // ACC_SHIFT (integer accumulators): the accumulator is shifted right by that many bits (arithmetic) before alpha /
+        // beta are applied, for kernels whose operands carry a power-of-two scale.
+        template <typename OutT, typename ScalarT, uint32_t TN = TILE_N, uint32_t STRIDE = 1, uint32_t ROW_BYTES = 64,
+                  int ACC_SHIFT = 0>
         struct StagedDrain
         {
+            static_assert(ACC_SHIFT == 0 || std::is_same<ScalarT, int32_t>::value, "accumulator shift: integer paths only");
             static constexpr uint32_t BUF_BYTES = 32 * ROW_BYTES; // one staging tile: 32 rows
             static constexpr uint32_t CELLS     = ROW_BYTES / 16; // 16-byte cells per row
             static_assert(ROW_BYTES == 64 || (ROW_BYTES == 128 && sizeof(OutT) == 4), "staging rows: 64 bytes, or 128 for 32-bit outputs");
@@ -143,34 +147,62 @@ namespace b200wmma
                     }
                     ptx::tmem_ld_wait();
                     uint8_t* rowp = smem + (bi == 0u ? buf_off : buf1_off) + lane * ROW_BYTES;
-#pragma unroll
-                    for(uint32_t q = 0; q < CELLS; ++q)
-                    {
-                        uint4* cell = reinterpret_cast<uint4*>(rowp + ((q ^ row_sw) << 4));
-                        uint4  cv   = make_uint4(0, 0, 0, 0);
-                        if(read_c)
-                            cv = *cell;
-                        const uint32_t cwv[4] = {cv.x, cv.y, cv.z, cv.w};
-                        uint32_t       ow[4];
-#pragma unroll
-                        for(uint32_t w = 0; w < 4; ++w)
-                        {
-                            if constexpr(sizeof(OutT) == 2)
+                    // The epilogue warps share four issue ports, so the drain's length is close to its instruction count:
+                    // the common scalars get their own code (alpha == 1: one fused multiply-add per element; no C: none).
+                    const auto combine = [&](auto mode_tag) {
+                        constexpr int MODE = decltype(mode_tag)::value; // 0 general, 1 alpha == 1 with C, 2 alpha == 1 without C
+                        const auto one = [&](uint32_t accbits, auto cval) {
+                            if constexpr(std::is_same<ScalarT, float>::value)
                             {
-                                const float2  cf = __half22float2(*reinterpret_cast<const __half2*>(&cwv[w]));
-                                const __half2 h  = __floats2half2_rn(
-                                    epi(__uint_as_float(v[8 * q + 2 * w]), cf.x, alpha, beta),
-                                    epi(__uint_as_float(v[8 * q + 2 * w + 1]), cf.y, alpha, beta));
-                                ow[w] = *reinterpret_cast<const uint32_t*>(&h);
+                                const float acc = __uint_as_float(accbits);
+                                if constexpr(MODE == 2)
+                                    return acc;
+                                else if constexpr(MODE == 1)
+                                    return fmaf(beta, static_cast<float>(cval), acc);
+                                else
+                                    return epi(acc, static_cast<float>(cval), alpha, beta);
                             }
-                            else if constexpr(std::is_same<OutT, float>::value)
-                                ow[w] = __float_as_uint(epi(__uint_as_float(v[4 * q + w]), __uint_as_float(cwv[w]), alpha, beta));
                             else
-                                ow[w] = static_cast<uint32_t>(
-                                    epi(static_cast<int32_t>(v[4 * q + w]), static_cast<int32_t>(cwv[w]), alpha, beta));
+                            {
+                                const int32_t acc = static_cast<int32_t>(accbits) >> ACC_SHIFT;
+                                if constexpr(MODE == 2)
+                                    return acc;
+                                else
+                                    return epi(acc, static_cast<int32_t>(cval), MODE == 1 ? ScalarT(1) : alpha, beta);
+                            }
+                        };
+#pragma unroll
+                        for(uint32_t q = 0; q < CELLS; ++q)
+                        {
+                            uint4* cell = reinterpret_cast<uint4*>(rowp + ((q ^ row_sw) << 4));
+                            uint4  cv   = make_uint4(0, 0, 0, 0);
+                            if(MODE != 2 && read_c)
+                                cv = *cell;
+                            const uint32_t cwv[4] = {cv.x, cv.y, cv.z, cv.w};
+                            uint32_t       ow[4];
+#pragma unroll
+                            for(uint32_t w = 0; w < 4; ++w)
+                            {
+                                if constexpr(sizeof(OutT) == 2)
+                                {
+                                    const float2  cf = __half22float2(*reinterpret_cast<const __half2*>(&cwv[w]));
+                                    const __half2 h  = __floats2half2_rn(one(v[8 * q + 2 * w], cf.x), one(v[8 * q + 2 * w + 1], cf.y));
+                                    ow[w]            = *reinterpret_cast<const uint32_t*>(&h);
+                                }
+                                else if constexpr(std::is_same<OutT, float>::value)
+                                    ow[w] = __float_as_uint(one(v[4 * q + w], __uint_as_float(cwv[w])));
+                                else
+                                    ow[w] = static_cast<uint32_t>(one(v[4 * q + w], static_cast<int32_t>(cwv[w])));
+                            }
+                            *cell = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                         }
-                        *cell = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-                    }
+                    };
+                    if(alpha == ScalarT(1) && !read_c)
+                        combine(std::integral_constant<int, 2>{});
+                    else if(alpha == ScalarT(1))
+                        combine(std::integral_constant<int, 1>{});
+                    else
+                        combine(std::integral_constant<int, 0>{});
                     ptx::fence_proxy_async_smem(); // the tile written above -> visible to the TMA store
                     __syncwarp();
                     if(lane == 0)
@@ -193,7 +225,14 @@ namespace b200wmma
         };
 
         // A_MN / B_MN: the operand is MN-major (column-major A / row-major B) instead of K-major.
-        template <int KIND, typename OutT, typename ScalarT, bool A_MN = false, bool B_MN = false>
+        // SPLIT: order the MMAs of a tile's first HEAD_KB and last TAIL_KB K slabs by accumulator instead of by slab
+        // (accumulator 0 over those slabs, then accumulator 1), with one tmem_full barrier per accumulator.  The two
+        // accumulators fill tensor memory, so a tile's drain cannot overlap the next tile's MMAs on the same accumulator;
+        // ordered this way accumulator 0 is drained while accumulator 1 still multiplies the tile's last slabs, and
+        // accumulator 1 while accumulator 0 already multiplies the next tile's first slabs.
+        constexpr uint32_t HEAD_KB = STAGES - 1; // the next tile's slab in the stage that holds staging tiles is not among them
+        constexpr uint32_t TAIL_KB = STAGES; // every stage: all slabs of the block are resident at once
+        template <int KIND, typename OutT, typename ScalarT, bool A_MN = false, bool B_MN = false, bool SPLIT = false>
         __global__ void __launch_bounds__(NUM_THREADS, 1)
             gemm_tc05_pair512_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                      const __grid_constant__ CUtensorMap tmap_b,
@@ -227,8 +266,8 @@ namespace b200wmma
             const uint32_t     bar_base   = base + misc_off;
             const uint32_t     full_bar   = bar_base; // STAGES x 8 (leader's copy in use)
             const uint32_t     empty_bar  = bar_base + 32;
-            const uint32_t     tfull_bar  = bar_base + 64;
-            const uint32_t     tempty_bar = bar_base + 72; // 2 x 8, one per accumulator (leader's copy in use)
+            const uint32_t     tfull_bar  = bar_base + 64; // 2 x 8, one per accumulator
+            const uint32_t     tempty_bar = bar_base + 80; // 2 x 8, one per accumulator (leader's copy in use)
             const uint32_t     cbar_base  = bar_base + 96; // EPI_WARPS x 2 x 8: C tiles of the epilogue warps
             uint32_t*          tmem_slot  = reinterpret_cast<uint32_t*>(smem + misc_off + 96 + EPI_WARPS * 16);
             volatile uint32_t* cta_abort  = tmem_slot + 1;
@@ -257,6 +296,7 @@ namespace b200wmma
                     ptx::mbar_init(empty_bar + 8 * s, 1);
                 }
                 ptx::mbar_init(tfull_bar, 1);
+                ptx::mbar_init(tfull_bar + 8, 1);
                 ptx::mbar_init(tempty_bar, 16); // accumulator 0: 8 warps x 2 CTAs
                 ptx::mbar_init(tempty_bar + 8, 16); // accumulator 1
                 for(uint32_t i = 0; i < EPI_WARPS * 2; ++i)
@@ -373,56 +413,118 @@ namespace b200wmma
                     constexpr uint32_t B_STEP = B_MN ? ((32u / ES) * 128u) >> 4 : 2u;
                     uint32_t           stage = 0, phase = 0, iter = 0;
                     bool               ok = true;
+                    const auto advance = [](uint32_t& st, uint32_t& ph) {
+                        if(++st == STAGES)
+                        {
+                            st = 0;
+                            ph ^= 1u;
+                        }
+                    };
+                    // the slab in stage `st` has arrived (both CTAs' loads are counted on this barrier)
+                    const auto wait_slab = [&](uint32_t st, uint32_t ph) {
+                        const bool got = ptx::mbar_wait_bounded(full_bar + 8 * st, ph, cta_abort, status,
+                                                                (ROLE_MMA << 24) | (1u << 20) | blockIdx.x, WAIT_TIMEOUT_NS);
+                        ptx::tc_fence_after_sync();
+                        return got;
+                    };
+                    // accumulator j of the previous tile has been drained by both CTAs
+                    const auto wait_drained = [&](uint32_t j, uint32_t tphase) {
+                        const bool got = ptx::mbar_wait_bounded(tempty_bar + 8 * j, tphase ^ 1u, cta_abort, status,
+                                                                (ROLE_MMA << 24) | blockIdx.x, WAIT_TIMEOUT_NS);
+                        ptx::tc_fence_after_sync();
+                        return got;
+                    };
+                    // the MMAs of one K slab (stage st) into accumulator j; `fresh`: the slab is the tile's first
+                    const auto mma_slab = [&](uint32_t j, uint32_t st, bool fresh) {
+                        const uint64_t b_desc = B_MN ? ptx::make_mnmajor_sw128_desc(smem_b + st * B_STAGE_BYTES, GROUP_B)
+                                                     : ptx::make_kmajor_sw128_desc(smem_b + st * B_STAGE_BYTES);
+                        const uint32_t a_addr = smem_a + st * A_STAGE_BYTES + j * (SUB_M * BLOCK_K_BYTES);
+                        const uint64_t a_desc = A_MN ? ptx::make_mnmajor_sw128_desc(a_addr, GROUP_B)
+                                                     : ptx::make_kmajor_sw128_desc(a_addr);
+#pragma unroll
+                        for(uint32_t ks = 0; ks < BLOCK_K_BYTES / 32; ++ks)
+                        {
+                            const uint32_t acc = (fresh && ks == 0u) ? 0u : 1u;
+                            if constexpr(KIND == KIND_F16 || KIND == KIND_BF16)
+                                ptx::mma_f16_ss_pair(tmem_base + j * TILE_N, a_desc + A_STEP * ks, b_desc + B_STEP * ks, idesc, acc);
+                            else if constexpr(KIND == KIND_I8)
+                                ptx::mma_i8_ss_pair(tmem_base + j * TILE_N, a_desc + A_STEP * ks, b_desc + B_STEP * ks, idesc, acc);
+                            else
+                                ptx::mma_f8_ss_pair(tmem_base + j * TILE_N, a_desc + A_STEP * ks, b_desc + B_STEP * ks, idesc, acc);
+                        }
+                    };
                     for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++iter)
                     {
                         const uint32_t tphase = iter & 1u;
-                        for(uint32_t kb = 0; kb < num_kb && ok; ++kb)
+                        const bool     split  = SPLIT && num_kb >= HEAD_KB + TAIL_KB;
+                        uint32_t       kb     = 0;
+                        if(split)
                         {
-                            ok = ptx::mbar_wait_bounded(full_bar + 8 * stage, phase, cta_abort, status,
-                                                        (ROLE_MMA << 24) | (1u << 20) | blockIdx.x, WAIT_TIMEOUT_NS);
-                            if(!ok)
-                                break;
-                            ptx::tc_fence_after_sync();
-                            const uint64_t b_desc = B_MN ? ptx::make_mnmajor_sw128_desc(smem_b + stage * B_STAGE_BYTES, GROUP_B)
-                                                         : ptx::make_kmajor_sw128_desc(smem_b + stage * B_STAGE_BYTES);
+                            // head: accumulator 0 over the first slabs (accumulator 1 of the previous tile may still be
+                            // draining), then accumulator 1 over the same slabs, releasing each stage
+                            uint32_t st = stage, ph = phase;
+                            ok = wait_drained(0, tphase);
+                            for(uint32_t i = 0; ok && i < HEAD_KB; ++i)
+                            {
+                                ok = wait_slab(st, ph);
+                                if(ok)
+                                    mma_slab(0, st, i == 0u);
+                                advance(st, ph);
+                            }
+                            if(ok)
+                                ok = wait_drained(1, tphase);
+                            for(uint32_t i = 0; ok && i < HEAD_KB; ++i)
+                            {
+                                mma_slab(1, stage, i == 0u);
+                                ptx::tc_commit_pair(empty_bar + 8 * stage, 0x3);
+                                advance(stage, phase);
+                            }
+                            kb = HEAD_KB;
+                        }
+                        const uint32_t mid_end = split ? num_kb - TAIL_KB : num_kb;
+                        for(; ok && kb < mid_end; ++kb)
+                        {
+                            ok = wait_slab(stage, phase);
 #pragma unroll
                             for(uint32_t j = 0; j < 2; ++j)
                             {
-                                if(kb == 0)
-                                {
-                                    // accumulator j of the previous tile must have been drained by both CTAs
-                                    ok = ptx::mbar_wait_bounded(tempty_bar + 8 * j, tphase ^ 1u, cta_abort, status,
-                                                                (ROLE_MMA << 24) | blockIdx.x, WAIT_TIMEOUT_NS);
-                                    if(!ok)
-                                        break;
-                                    ptx::tc_fence_after_sync();
-                                }
-                                const uint32_t a_addr = smem_a + stage * A_STAGE_BYTES + j * (SUB_M * BLOCK_K_BYTES);
-                                const uint64_t a_desc = A_MN ? ptx::make_mnmajor_sw128_desc(a_addr, GROUP_B)
-                                                             : ptx::make_kmajor_sw128_desc(a_addr);
-#pragma unroll
-                                for(uint32_t ks = 0; ks < BLOCK_K_BYTES / 32; ++ks)
-                                {
-                                    const uint32_t acc = (kb | ks) != 0u ? 1u : 0u;
-                                    if constexpr(KIND == KIND_F16 || KIND == KIND_BF16)
-                                        ptx::mma_f16_ss_pair(tmem_base + j * TILE_N, a_desc + A_STEP * ks, b_desc + B_STEP * ks, idesc, acc);
-                                    else if constexpr(KIND == KIND_I8)
-                                        ptx::mma_i8_ss_pair(tmem_base + j * TILE_N, a_desc + A_STEP * ks, b_desc + B_STEP * ks, idesc, acc);
-                                    else
-                                        ptx::mma_f8_ss_pair(tmem_base + j * TILE_N, a_desc + A_STEP * ks, b_desc + B_STEP * ks, idesc, acc);
-                                }
+                                if(ok && kb == 0u)
+                                    ok = wait_drained(j, tphase);
+                                if(ok)
+                                    mma_slab(j, stage, kb == 0u);
                             }
                             if(!ok)
                                 break;
                             ptx::tc_commit_pair(empty_bar + 8 * stage, 0x3);
-                            if(++stage == STAGES)
-                            {
-                                stage = 0;
-                                phase ^= 1u;
-                            }
+                            advance(stage, phase);
                         }
-                        if(ok)
+                        if(split && ok)
+                        {
+                            // tail: accumulator 0 over the last slabs and its tmem_full, then accumulator 1
+                            uint32_t st = stage, ph = phase;
+                            for(uint32_t i = 0; ok && i < TAIL_KB; ++i)
+                            {
+                                ok = wait_slab(st, ph);
+                                if(ok)
+                                    mma_slab(0, st, false);
+                                advance(st, ph);
+                            }
+                            if(ok)
+                                ptx::tc_commit_pair(tfull_bar, 0x3);
+                            for(uint32_t i = 0; ok && i < TAIL_KB; ++i)
+                            {
+                                mma_slab(1, stage, false);
+                                ptx::tc_commit_pair(empty_bar + 8 * stage, 0x3);
+                                advance(stage, phase);
+                            }
+                            if(ok)
+                                ptx::tc_commit_pair(tfull_bar + 8, 0x3);
+                        }
+                        else if(ok)
+                        {
                             ptx::tc_commit_pair(tfull_bar, 0x3);
+                            ptx::tc_commit_pair(tfull_bar + 8, 0x3);
+                        }
                     }
                 }
                 __syncwarp();
@@ -437,7 +539,9 @@ namespace b200wmma
                 const bool     read_c = (beta != ScalarT(0)) && (c != nullptr);
                 const uint32_t buf_off  = epi_off + e * EPI_BUF_BYTES; // first tile: dedicated
                 const uint32_t buf0     = base + buf_off;
-                const uint32_t buf1_off = alias_base_off + e * EPI_BUF_BYTES; // second tile: inside the last operand stage
+                // second tile: inside the A region of the last operand stage, accumulator 0's warps in the half that holds
+                // rows 0-127 (which only accumulator 0's MMAs read), accumulator 1's in the other half
+                const uint32_t buf1_off = alias_base_off + (j * 8u + (e & 3u) + 4u * first) * EPI_BUF_BYTES;
                 const uint32_t buf1     = base + buf1_off;
                 const uint32_t cbar0   = cbar_base + e * 16u;
                 using Drain            = StagedDrain<OutT, ScalarT, TILE_N, 2>;
@@ -456,12 +560,13 @@ namespace b200wmma
                     // C does not depend on the accumulators: the tile of the warp's first step is requested now
                     if(staged && read_c && lane == 0)
                         Drain::prefetch_c(&tmap_c, buf0, cbar0, col_base, row0, n, first, 0, 1, buf1);
-                    ok = ptx::mbar_wait_bounded_warp(tfull_bar, iter & 1u, cta_abort, status,
+                    ok = ptx::mbar_wait_bounded_warp(tfull_bar + 8 * j, iter & 1u, cta_abort, status,
                                                      (ROLE_EPILOGUE << 24) | blockIdx.x, WAIT_TIMEOUT_NS, lane);
                     if(!ok)
                         break;
                     ptx::tc_fence_after_sync();
-                    // every MMA of the tile has retired: the aliased staging tiles may be written now
+                    // every MMA of the tile into this accumulator has retired: its half of the aliased staging tiles may be
+                    // written now
                     if(staged && read_c && lane == 0)
                         Drain::prefetch_c(&tmap_c, buf0, cbar0, col_base, row0, n, first, 1, 2, buf1);
                     const uint32_t tmem_acc = tmem_base + j * TILE_N;

@@ -392,10 +392,13 @@ namespace b200wmma
             asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
             return r;
         }
+        // Arrive on a barrier that may live in the peer CTA (`cluster_addr` from mapa).  Default semantics (release at
+        // CTA scope): what the arrival publishes has already been made visible to its consumer by other means - tensor
+        // memory reads by tcgen05.wait::ld + tcgen05.fence, shared-memory tiles for the tensor core by
+        // fence.proxy.async - so the cluster-scope release, a fence that costs ~1000 cycles per arrival, is not needed.
         __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
         {
-            asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
-                         : "memory");
+            asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
         }
         __device__ __forceinline__ uint32_t ld_shared_cluster_u32(uint32_t cluster_addr)
         {

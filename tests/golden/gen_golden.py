@@ -1,6 +1,6 @@
 """Generates the committed parity fixtures.  Run where the rocWMMA reference tree is mounted:
 
-    make -C oracle && python tests/golden/gen_golden.py [--ref-root /root/reference]
+    make -C oracle && python tests/golden/gen_golden.py [--ref-root <rocWMMA checkout>]
 
 Writes into tests/golden/:
   gemm_ref.npz    outputs of the reference's OWN gemm_CPU (test/reference_impl.hpp:36-81, compiled
@@ -21,7 +21,8 @@ import sys
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
 
 from oracle import cpu_ref as R  # noqa: E402
 from rocwmma_b200 import datagen as G  # noqa: E402
@@ -79,7 +80,8 @@ def gemv_inputs(case):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref-root", default="/root/reference")
+    ap.add_argument("--ref-root", default=os.environ.get("ROCWMMA_REFERENCE_ROOT") or os.path.join(os.path.dirname(ROOT), "reference"),
+                    help="rocWMMA checkout (default: $ROCWMMA_REFERENCE_ROOT, else a directory `reference` beside this repository)")
     args = ap.parse_args()
     ref = R.reference()
 

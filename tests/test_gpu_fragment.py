@@ -223,7 +223,7 @@ def test_simple_hgemm_config1(out_np):
 @pytest.mark.parametrize("m,n,k", [(64, 64, 16), (256, 384, 208), (1024, 512, 512)])
 def test_simple_sgemm_dgemm(np_t, m, n, k):
     """The fp32 / fp64 forms of the naive fragment GEMM (samples/simple_sgemm.cpp, samples/simple_dgemm.cpp):
-    fp32 fragments multiply through three TF32 products, so they are held to 5e-6, far inside BASELINE's 1e-3."""
+    fp32 fragments multiply through three TF32 products, so they are held to 5e-6, far inside the 1e-3 acceptance bound for fp32 outputs."""
     a = G.uniform_np(G.SEED_A, (m, k), np_t); b = G.uniform_np(G.SEED_B, (k, n), np_t); c = G.uniform_np(G.SEED_C, (m, n), np_t)
     bs = np.ascontiguousarray(b.T)
     d = nan_filled((m, n), torch.float32 if np_t == np.float32 else torch.float64)

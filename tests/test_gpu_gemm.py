@@ -165,7 +165,7 @@ TOL_F32X3 = 5e-6   # three TF32 products: ~2^-21 per product; a single TF32 prod
                                               (1024, 1024, 1024, 2.0, 2.0)])
 def test_gemm_f32_three_tf32(m, n, k, alpha, beta):
     """fp32 GEMM of the sgemm samples (samples/simple_sgemm.cpp, samples/perf_sgemm.cpp) against the reference's
-    fp32 gemm_CPU arithmetic.  The tolerance is far tighter than BASELINE's 1e-3 so that a plain TF32 product,
+    fp32 gemm_CPU arithmetic.  The tolerance is far tighter than the 1e-3 acceptance bound for fp32 outputs so that a plain TF32 product,
     which keeps 10 mantissa bits, could not pass."""
     a = G.uniform_np(G.SEED_A, (m, k), np.float32); b = G.uniform_np(G.SEED_B, (k, n), np.float32)
     c = G.uniform_np(G.SEED_C, (m, n), np.float32)
@@ -306,16 +306,38 @@ def test_gemm_i8_sparse24_full_size_row_sample():
     assert torch.equal(col.to(torch.float64), expect)
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (200, 136, 512), (256, 256, 4096)])
-def test_gemm_i4_bit_exact(m, n, k):
+@pytest.mark.parametrize("m,n,k,alpha,beta", [(128, 256, 128, 1, 0), (200, 136, 512, 1, 0), (256, 256, 4096, 1, 0),
+                                              (700, 300, 96, 3, -2), (513, 520, 1056, 1, 1), (40, 24, 32, -1, 5),
+                                              (96, 256, 131072, 1, 0), (64, 128, 131072 + 64, 2, 1)])
+def test_gemm_i4_bit_exact(m, n, k, alpha, beta):
+    """Packed int4 operands, unpacked inside the kernel (no workspace): ragged M / N, K that is a multiple of 32 only,
+    alpha / beta with C, and K of 131072 and more, where the kernel sign-extends the nibbles instead of scaling them."""
+    assert api.gemm_i4_workspace_bytes(m, n, k) == 0
     a = G.int4_np(G.SEED_A, (m, k)); b = G.int4_np(G.SEED_B, (k, n))
+    c = G.int8_np(G.SEED_C, (m, n)).astype(np.int32) * 4321
     bs = np.ascontiguousarray(b.T)
-    ws = torch.empty(api.gemm_i4_workspace_bytes(m, n, k), dtype=torch.uint8, device="cuda")
     d = nan_filled((m, n), torch.int32)
-    api.gemm_i4(m, n, k, dev(G.pack_int4_np(a)), dev(G.pack_int4_np(bs)), None, d, k // 2, k // 2, n, n, 1, 0, ws)
+    api.gemm_i4(m, n, k, dev(G.pack_int4_np(a)), dev(G.pack_int4_np(bs)), dev(c) if beta else None, d, k // 2, k // 2, n, n,
+                alpha, beta, None)
     assert_status_ok()
-    ref = oracle_gemm_rows(a, bs, None, 1, 0, np.int32, n, k)
+    ref = oracle_gemm_rows(a, bs, c if beta else None, alpha, beta, np.int32, n, k)
     assert np.array_equal(d.cpu().numpy(), ref)
+
+
+def test_gemm_i4_extreme_values_and_padded_pitches():
+    """Every value -8 (the case in which 256 * sum is largest) at K = 65536, row pitches larger than the rows, and D
+    rows that are not 16-byte aligned (element-wise drain)."""
+    m, n, k = 130, 70, 65536
+    a = np.full((m, k), -8, np.int8); bs = np.full((n, k), -8, np.int8)
+    a[::3, ::5] = 7; bs[1::2, ::7] = 7
+    lda, ldb, ldd = k // 2 + 32, k // 2 + 16, n + 3
+    pad = lambda x, ld: np.concatenate([x, np.full((x.shape[0], ld - x.shape[1]), 0x5A, x.dtype)], axis=1)
+    d = torch.full((m, ldd), -7, dtype=torch.int32, device="cuda")
+    api.gemm_i4(m, n, k, dev(pad(G.pack_int4_np(a), lda)), dev(pad(G.pack_int4_np(bs), ldb)), None, d, lda, ldb, n, ldd, 1, 0)
+    assert_status_ok()
+    out = d.cpu().numpy()
+    assert np.array_equal(out[:, :n], oracle_gemm_rows(a, bs, None, 1, 0, np.int32, n, k))
+    assert (out[:, n:] == -7).all()
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 136, 72), (512, 384, 256)])
