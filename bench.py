@@ -285,6 +285,10 @@ class GemmF16(Workload):
         self.ctx.gemm_f16(self.M, self.nloc, self.K, self.h_a, self.h_b, self.h_c, self.h_d,
                           self.K, self.K, self.nloc, self.nloc, self.alpha, self.beta, 0)
 
+    def host_stage_ms(self):
+        """Device times of the stages of the last host-driver call (upload span, exchange of A, GEMM, download, total)."""
+        return self.ctx.last_stage_ms()
+
     def config(self, world):
         return {"workload": "perf_hgemm-form dense fp16 GEMM, M=N=K=8192, A row-major fp16, B col-major fp16, "
                             "C/D row-major fp16, fp32 accumulate, alpha=beta=1",

@@ -83,10 +83,10 @@ int b200wmma_device_status(void* stream, int* out_status, unsigned* out_detail);
  * f64: fp64 everywhere (DMMA).
  * bf16 / fp8: bfloat16 resp. OCP fp8 (both operands of one format) inputs, fp32 accumulate, C/D fp32 -
  *   the reference's bfloat16_t and float8 / bfloat8 input types (docs/api-reference-guide.rst:84-143).
- * f16 / i8 / bf16 / fp8 accept every combination of row / column major A, B and C/D (C and D share one layout), as
- * the reference's NN / NT / TN / TT sweeps do; f64 takes A row major, B column major, C/D row major.
- * A and B base pointers and leading dimensions (in bytes) must be multiples of 16 (TMA requirement);
- * C / D may be unaligned (slower element-wise epilogue).
+ * f16 / i8 / bf16 / fp8 / f64 accept every combination of row / column major A, B and C/D (C and D share one layout),
+ * as the reference's NN / NT / TN / TT sweeps do.
+ * A and B base pointers and leading dimensions (in bytes) must be multiples of 16 (TMA / 16-byte async copies; for
+ * f64 also k even when an operand is stored with K contiguous); C / D may be unaligned (slower element-wise epilogue).
  * ------------------------------------------------------------------------------------------ */
 int b200wmma_gemm_f16(uint32_t m, uint32_t n, uint32_t k,
                       const void* a, const void* b, const void* c, void* d,

@@ -271,7 +271,7 @@ namespace b200wmma
             const uint32_t     cbar_base  = bar_base + 96; // EPI_WARPS x 2 x 8: C tiles of the epilogue warps
             uint32_t*          tmem_slot  = reinterpret_cast<uint32_t*>(smem + misc_off + 96 + EPI_WARPS * 16);
             volatile uint32_t* cta_abort  = tmem_slot + 1;
-            uint32_t*          epi_count  = tmem_slot + 2; // epilogue warps x tiles whose aliased staging tiles are free again
+            const uint32_t     drained_bar = bar_base + 96 + EPI_WARPS * 16 + 16; // every epilogue warp is done with a tile's staging tiles
             // the A region of the last stage holds the second staging tile of every epilogue warp while a tile is drained
             const uint32_t     alias_base_off = EPI_STAGE * A_STAGE_BYTES;
 
@@ -285,7 +285,6 @@ namespace b200wmma
 
             if(threadIdx.x == 0)
             {
-                *epi_count = 0u;
                 ptx::prefetch_tensormap(&tmap_a);
                 ptx::prefetch_tensormap(&tmap_b);
                 ptx::prefetch_tensormap(&tmap_c);
@@ -297,6 +296,7 @@ namespace b200wmma
                 }
                 ptx::mbar_init(tfull_bar, 1);
                 ptx::mbar_init(tfull_bar + 8, 1);
+                ptx::mbar_init(drained_bar, EPI_WARPS);
                 ptx::mbar_init(tempty_bar, 16); // accumulator 0: 8 warps x 2 CTAs
                 ptx::mbar_init(tempty_bar + 8, 16); // accumulator 1
                 for(uint32_t i = 0; i < EPI_WARPS * 2; ++i)
@@ -337,28 +337,9 @@ namespace b200wmma
                             if(stage == EPI_STAGE && iter != 0u)
                             {
                                 // this stage's A region doubles as staging tiles of the epilogue: every epilogue
-                                // warp must have finished with them for all earlier tiles (bounded wait)
-                                const uint64_t t0 = ptx::globaltimer_ns();
-                                uint32_t       spins = 0;
-                                while(ptx::ld_acquire_shared_u32(epi_count) < EPI_WARPS * iter)
-                                {
-                                    if((++spins & 0xFFu) == 0u)
-                                    {
-                                        if(*cta_abort)
-                                        {
-                                            ok = false;
-                                            break;
-                                        }
-                                        if(ptx::globaltimer_ns() - t0 > WAIT_TIMEOUT_NS)
-                                        {
-                                            *cta_abort = 1u;
-                                            if(atomicCAS(status, 0u, ptx::STATUS_TIMEOUT_CODE) == 0u)
-                                                status[1] = (ROLE_PRODUCER << 24) | (2u << 20) | blockIdx.x;
-                                            ok = false;
-                                            break;
-                                        }
-                                    }
-                                }
+                                // warp must have finished with them for the previous tile (bounded wait)
+                                ok = ptx::mbar_wait_bounded(drained_bar, (iter - 1u) & 1u, cta_abort, status,
+                                                            (ROLE_PRODUCER << 24) | (2u << 20) | blockIdx.x, WAIT_TIMEOUT_NS);
                                 if(!ok)
                                     break;
                                 ptx::fence_proxy_async_smem(); // generic writes of the staging tiles before the TMA overwrite
@@ -545,9 +526,15 @@ namespace b200wmma
                 const uint32_t buf1     = base + buf1_off;
                 const uint32_t cbar0   = cbar_base + e * 16u;
                 using Drain            = StagedDrain<OutT, ScalarT, TILE_N, 2>;
-                uint32_t iter = 0, cpar = 0;
-                bool     ok   = true;
-                for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++iter)
+                // The eight warps of an accumulator wait for it together: one of them (the leader) watches the tmem_full
+                // barrier, the others park on a named hardware barrier and issue nothing meanwhile - sixteen warps polling
+                // through every tile's main loop were most of the kernel's instructions.  A warp that gives up (a bounded
+                // wait ran out, the CTA is aborting) keeps going round the loop without working, so that the named
+                // barrier always sees all of its warps.
+                const bool leader = (e & 11u) == 0u; // e == 0 (accumulator 0), e == 4 (accumulator 1)
+                uint32_t   iter = 0, cpar = 0;
+                bool       dead = false;
+                for(uint32_t tile = pair; tile < num_tiles; tile += num_pairs, ++iter)
                 {
                     uint32_t m_idx, n_idx;
                     tile_coords(tile, tiles_m, tiles_n, group_m, m_idx, n_idx);
@@ -556,14 +543,18 @@ namespace b200wmma
                     const uint32_t col_base = n_idx * TILE_N;
                     // staged path: needs 16-byte aligned rows (TMA) and a tile that starts inside the matrix
                     const bool staged = vec_ok != 0 && row0 < m && col_base < n;
-                    // C does not depend on the accumulators: request its first two steps now
                     // C does not depend on the accumulators: the tile of the warp's first step is requested now
-                    if(staged && read_c && lane == 0)
+                    if(!dead && staged && read_c && lane == 0)
                         Drain::prefetch_c(&tmap_c, buf0, cbar0, col_base, row0, n, first, 0, 1, buf1);
-                    ok = ptx::mbar_wait_bounded_warp(tfull_bar + 8 * j, iter & 1u, cta_abort, status,
-                                                     (ROLE_EPILOGUE << 24) | blockIdx.x, WAIT_TIMEOUT_NS, lane);
-                    if(!ok)
-                        break;
+                    if(leader && !dead)
+                        dead = !ptx::mbar_wait_bounded_warp(tfull_bar + 8 * j, iter & 1u, cta_abort, status,
+                                                            (ROLE_EPILOGUE << 24) | blockIdx.x, WAIT_TIMEOUT_NS, lane);
+                    ptx::named_bar_sync(1u + j, 8u * 32u);
+                    if(!dead && !leader)
+                        // the leader saw the phase complete (or gave up and raised the abort flag): confirm it here
+                        dead = (*cta_abort != 0u) || !ptx::mbar_try_wait(tfull_bar + 8 * j, iter & 1u);
+                    if(dead)
+                        continue;
                     ptx::tc_fence_after_sync();
                     // every MMA of the tile into this accumulator has retired: its half of the aliased staging tiles may be
                     // written now
@@ -571,13 +562,15 @@ namespace b200wmma
                         Drain::prefetch_c(&tmap_c, buf0, cbar0, col_base, row0, n, first, 1, 2, buf1);
                     const uint32_t tmem_acc = tmem_base + j * TILE_N;
                     if(staged)
-                        ok = Drain::run(tmem_acc, quad, lane, smem, buf_off, buf0, cbar0, &tmap_c, &tmap_d, col_base, row0, n,
-                                        alpha, beta, read_c, cpar, cta_abort, status,
-                                        (ROLE_EPILOGUE << 24) | (1u << 20) | blockIdx.x, first, buf1_off, buf1);
+                        dead = !Drain::run(tmem_acc, quad, lane, smem, buf_off, buf0, cbar0, &tmap_c, &tmap_d, col_base, row0, n,
+                                           alpha, beta, read_c, cpar, cta_abort, status,
+                                           (ROLE_EPILOGUE << 24) | (1u << 20) | blockIdx.x, first, buf1_off, buf1);
                     else if(vec_ok == 0 && first == 0u)
                         drain_accumulator<OutT, ScalarT, TILE_N>(tmem_acc, quad, lane, row_base, col_base, m, n, c, d, ldc,
                                                                  ldd, alpha, beta, read_c, 0);
                     // (an aligned tile that lies wholly outside the matrix has nothing to store)
+                    if(dead)
+                        continue;
                     ptx::tc_fence_before_sync();
                     __syncwarp();
                     if(lane == 0)
@@ -585,7 +578,7 @@ namespace b200wmma
                         ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar + 8 * j, 0u));
                         // hand the aliased staging tiles back to the producer once this warp's stores have read them
                         ptx::bulk_wait_group_read<0>();
-                        ptx::red_release_shared_add_u32(epi_count, 1u);
+                        ptx::mbar_arrive(drained_bar);
                     }
                 }
                 if(lane == 0)

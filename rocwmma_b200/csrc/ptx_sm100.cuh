@@ -189,6 +189,13 @@ namespace b200wmma
             return ok;
         }
 
+        // Named hardware barrier `id` (1..15) over `threads` threads (a multiple of 32): the waiting warps issue no
+        // instructions until the last one arrives.
+        __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t threads)
+        {
+            asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+        }
+
         // ---- counters in shared memory (release / acquire at CTA scope) ---------------------------
         __device__ __forceinline__ uint32_t ld_acquire_shared_u32(const uint32_t* p)
         {

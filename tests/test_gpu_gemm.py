@@ -352,6 +352,34 @@ def test_gemm_f64(m, n, k):
     assert gemm_rel_err(d.cpu().numpy(), ref, bound) <= TOL_F64_OUT
 
 
+@pytest.mark.parametrize("la,lb,lcd", LAYOUTS, ids=["".join("RC"[x] for x in t) for t in LAYOUTS])
+@pytest.mark.parametrize("m,n,k", [(256, 128, 64), (301, 202, 100), (64, 390, 34)])
+def test_gemm_f64_all_layouts(la, lb, lcd, m, n, k):
+    """fp64 GEMM in every combination of row / column-major A, B and C/D (the reference's NN / NT / TN / TT sweep,
+    docs/api-reference/api-reference-guide.rst:169-187), odd extents included, against the oracle in the same layouts.
+    Leading dimensions are padded to even values where the extent is odd (16-byte async copies)."""
+    even = lambda x: x + (x & 1)
+    a = G.uniform_np(G.SEED_A, (m, k), np.float64); b = G.uniform_np(G.SEED_B, (k, n), np.float64)
+    c = G.uniform_np(G.SEED_C, (m, n), np.float64)
+    def store(x, col):   # (storage with an even pitch, pitch)
+        t = np.ascontiguousarray(x.T if col else x)
+        ld = even(t.shape[1])
+        out = np.full((t.shape[0], ld), np.nan)
+        out[:, :t.shape[1]] = t
+        return out, ld
+    (sa, lda), (sb, ldb), (sc, ldc) = store(a, la), store(b, lb), store(c, lcd)
+    d = nan_filled(sc.shape, torch.float64)
+    api.gemm_f64(m, n, k, dev(sa), dev(sb), dev(sc), d, lda, ldb, ldc, ldc, 1.5, 0.5, la, lb, lcd)
+    assert_status_ok()
+    nat = lambda x, col: np.ascontiguousarray(x.T if col else x)
+    ref = R.gemm(R.port(), m, n, k, nat(a, la).ravel(), nat(b, lb).ravel(), nat(c, lcd).ravel(), 1.5, 0.5, np.float64, la, lb, lcd, lcd)
+    ref = ref.reshape(nat(c, lcd).shape)
+    bound = nat(R.gemm_abs_bound(m, n, k, a, b, c, 1.5, 0.5), lcd)
+    got = d.cpu().numpy()[:, :ref.shape[1]]
+    assert gemm_rel_err(got, ref, bound) <= TOL_F64_OUT
+    assert np.isnan(d.cpu().numpy()[:, ref.shape[1]:]).all()   # pitch padding untouched
+
+
 @pytest.mark.parametrize("k", [64, 128, 320])
 def test_gemm_many_tiles_per_sm_pair_short_k(k):
     """More output tiles than SM pairs with only 1-5 K slabs per tile: the persistent kernels walk their operand
