@@ -252,7 +252,15 @@ class GemmF16(Workload):
     def step(self):
         from rocwmma_b200 import api
         api.gemm_f16(self.M, self.nloc, self.K, self.a, self.b, self.c, self.d,
-                     self.K, self.K, self.nloc, self.nloc, self.alpha, self.beta)
+                     self.K, self.K, self.nloc, self.nloc, self.alpha, self.beta, workspace=self._split_ws())
+
+    def _split_ws(self):
+        """Caller-owned scratch of the split-K tail (b200wmma_gemm_*_ws): lets a shard whose tiles do not fill a whole
+        number of rounds (64 tiles on 74 SM pairs at 8 GPUs) use every pair; the library itself allocates nothing."""
+        if not hasattr(self, "_ws"):
+            from rocwmma_b200 import api
+            self._ws = self.torch.empty(api.gemm_split_workspace_bytes(), dtype=self.torch.uint8, device="cuda")
+        return self._ws
 
     def setup_host(self):
         from rocwmma_b200 import api
@@ -470,7 +478,7 @@ class GemmI8(GemmF16):
         from rocwmma_b200 import api
         M, K, n = self.M, self.K, self.nloc
         if self.variant == "dense":
-            api.gemm_i8(M, n, K, self.a, self.b, None, self.d, K, K, n, n, 1, 0)
+            api.gemm_i8(M, n, K, self.a, self.b, None, self.d, K, K, n, n, 1, 0, workspace=self._split_ws())
         elif self.variant == "sp24":
             api.gemm_i8_sp24(M, n, K, self.vals, self.meta, self.b, None, self.d, K // 2, K // 8, K, n, n, 1, 0, self.ws)
         else:

@@ -55,6 +55,10 @@ int b200wmma_version(void);
  *   "gemm_tile_variant"  dense tcgen05 GEMM tile shape: 1 = 128x256 per SM, 2 = 256x256 per SM pair, 3 = 512x256 per pair
  *   "gemm_group_m"       rasterisation band height of that GEMM, in row tiles
  *   "sp24_force_expand"  1: b200wmma_gemm_i8_sp24 always densifies A into the workspace and runs the dense kernel
+ *   "gemm_split_tail"    512x256 kernel given a workspace (b200wmma_gemm_*_ws, the host drivers): 2 = never split the last
+ *                        round along K
+ *   "gemm_split_fixup"   cost of that split's exchange as the planner counts it, in K slabs (0 = built-in estimate); the
+ *                        split is used when slabs per pair + this < slabs of a whole tile
  *   "gemm_mma_order"     512x256 kernel, MMAs of a tile's first and last K slabs: 1 = accumulator by accumulator (so each
  *                        accumulator's drain overlaps the other's MMAs), 2 = slab by slab
  * Unknown keys and out-of-range values return B200WMMA_ERR_INVALID_ARG.  The library reads no environment variable
@@ -99,6 +103,28 @@ int b200wmma_gemm_i8(uint32_t m, uint32_t n, uint32_t k,
                      uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
                      int32_t alpha, int32_t beta,
                      int layout_a, int layout_b, int layout_cd, void* stream);
+/* The same two GEMMs with an optional caller-owned scratch buffer of b200wmma_gemm_split_workspace_bytes() bytes (for the
+ * current device; 16-byte aligned).  The kernels are persistent: a problem whose tiles do not fill a whole number of
+ * rounds over the SM pairs leaves pairs idle in the last round (64 tiles on 74 pairs, say, when a GEMM is sharded over
+ * 8 GPUs).  With the scratch the tiles of that last round are cut along K into equal ranges, one per pair; the partial
+ * accumulators (fp32 / int32) meet in the scratch and the pair that holds a tile's last K range applies alpha / beta.
+ * int8 stays bit-exact (integer addition is associative); fp16 results differ from the unsplit ones by fp32
+ * summation order only.  workspace == NULL, a buffer that is too small, unaligned C / D rows, or a problem for which
+ * the split would not pay give the unsplit schedule.  The library allocates nothing; calls that may overlap on
+ * the GPU must not share one workspace.  No counterpart in the reference (its kernels are not persistent). */
+size_t b200wmma_gemm_split_workspace_bytes(void);
+int b200wmma_gemm_f16_ws(uint32_t m, uint32_t n, uint32_t k,
+                         const void* a, const void* b, const void* c, void* d,
+                         uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                         float alpha, float beta,
+                         int layout_a, int layout_b, int layout_cd, int out_type,
+                         void* workspace, size_t workspace_bytes, void* stream);
+int b200wmma_gemm_i8_ws(uint32_t m, uint32_t n, uint32_t k,
+                        const int8_t* a, const int8_t* b, const int32_t* c, int32_t* d,
+                        uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                        int32_t alpha, int32_t beta,
+                        int layout_a, int layout_b, int layout_cd,
+                        void* workspace, size_t workspace_bytes, void* stream);
 /* fp32 inputs and outputs with fp32-class accuracy on the tensor cores (each operand split into two TF32
  * terms, three products accumulated in fp32): the reference's fp32 GEMM samples sgemm_rocwmma_d
  * (samples/simple_sgemm.cpp) and gemm_rocwmma_d of samples/perf_sgemm.cpp.  A row major, B column major,

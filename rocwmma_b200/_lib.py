@@ -22,6 +22,11 @@ SIGNATURES = {
                                     C.c_int, C.c_int, C.c_int, C.c_int, vp]),
     "b200wmma_gemm_i8": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32, i32, i32,
                                    C.c_int, C.c_int, C.c_int, vp]),
+    "b200wmma_gemm_split_workspace_bytes": (sz, []),
+    "b200wmma_gemm_f16_ws": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32, f32, f32,
+                                       C.c_int, C.c_int, C.c_int, C.c_int, vp, sz, vp]),
+    "b200wmma_gemm_i8_ws": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32, i32, i32,
+                                      C.c_int, C.c_int, C.c_int, vp, sz, vp]),
     "b200wmma_gemm_f32_workspace_bytes": (sz, [u32, u32, u32]),
     "b200wmma_gemm_f32": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32, f32, f32,
                                     C.c_int, C.c_int, C.c_int, vp, sz, vp]),

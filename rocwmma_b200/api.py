@@ -43,14 +43,25 @@ def device_status():
     return st.value, detail.value
 
 
+def gemm_split_workspace_bytes():
+    """Bytes of scratch with which gemm_f16 / gemm_i8 may split the tiles of a partial last round along K."""
+    return lib().b200wmma_gemm_split_workspace_bytes()
+
+
 def gemm_f16(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
-             layout_a=ROW_MAJOR, layout_b=COL_MAJOR, layout_cd=ROW_MAJOR):
-    """D = alpha * A x B + beta * C; fp16 inputs, fp32 accumulate, D/C fp16 or fp32 (by d.dtype)."""
+             layout_a=ROW_MAJOR, layout_b=COL_MAJOR, layout_cd=ROW_MAJOR, workspace=None):
+    """D = alpha * A x B + beta * C; fp16 inputs, fp32 accumulate, D/C fp16 or fp32 (by d.dtype).
+    workspace: optional uint8 CUDA tensor of gemm_split_workspace_bytes() bytes (b200wmma_gemm_f16_ws)."""
     _need(a, torch.float16, "a"); _need(b, torch.float16, "b")
     out_type = OUT_F16 if d.dtype == torch.float16 else OUT_F32
     _need(d, torch.float16 if out_type == OUT_F16 else torch.float32, "d")
     if c is not None:
         _need(c, d.dtype, "c")
+    if workspace is not None:
+        _need(workspace, torch.uint8, "workspace")
+        check(lib().b200wmma_gemm_f16_ws(m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc, ldd, alpha, beta,
+                                         layout_a, layout_b, layout_cd, out_type, _ptr(workspace), workspace.numel(), _stream()))
+        return
     check(lib().b200wmma_gemm_f16(m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc, ldd,
                                   alpha, beta, layout_a, layout_b, layout_cd, out_type, _stream()))
 
@@ -96,10 +107,15 @@ def gemm_fp8(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
 
 
 def gemm_i8(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
-            layout_a=ROW_MAJOR, layout_b=COL_MAJOR, layout_cd=ROW_MAJOR):
+            layout_a=ROW_MAJOR, layout_b=COL_MAJOR, layout_cd=ROW_MAJOR, workspace=None):
     _need(a, torch.int8, "a"); _need(b, torch.int8, "b"); _need(d, torch.int32, "d")
     if c is not None:
         _need(c, torch.int32, "c")
+    if workspace is not None:
+        _need(workspace, torch.uint8, "workspace")
+        check(lib().b200wmma_gemm_i8_ws(m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc, ldd, alpha, beta,
+                                        layout_a, layout_b, layout_cd, _ptr(workspace), workspace.numel(), _stream()))
+        return
     check(lib().b200wmma_gemm_i8(m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc, ldd,
                                  alpha, beta, layout_a, layout_b, layout_cd, _stream()))
 

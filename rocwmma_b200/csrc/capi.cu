@@ -134,7 +134,9 @@ extern "C" int b200wmma_set_tuning(const char* key, int value)
     } table[] = {{"gemm_tile_variant", tuning::GEMM_TILE_VARIANT, 0, 3},
                  {"gemm_group_m", tuning::GEMM_GROUP_M, 0, 1024},
                  {"sp24_force_expand", tuning::SP24_FORCE_EXPAND, 0, 1},
-                 {"gemm_mma_order", tuning::GEMM_MMA_ORDER, 0, 2}};
+                 {"gemm_mma_order", tuning::GEMM_MMA_ORDER, 0, 2},
+                 {"gemm_split_tail", tuning::GEMM_SPLIT_TAIL, 0, 2},
+                 {"gemm_split_fixup", tuning::GEMM_SPLIT_FIXUP, 0, 4096}};
     for(const auto& t : table)
         if(std::strcmp(key, t.name) == 0)
         {
@@ -174,6 +176,35 @@ extern "C" int b200wmma_gemm_f16(uint32_t m, uint32_t n, uint32_t k, const void*
         return e;
     return launch_gemm_tc05_f16(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, layout_a, layout_b,
                                 layout_cd, out_type, as_stream(stream));
+}
+
+extern "C" size_t b200wmma_gemm_split_workspace_bytes(void)
+{
+    return gemm_split_workspace_bytes();
+}
+
+extern "C" int b200wmma_gemm_f16_ws(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const void* c, void* d,
+                                    uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, float alpha, float beta,
+                                    int layout_a, int layout_b, int layout_cd, int out_type, void* workspace,
+                                    size_t workspace_bytes, void* stream)
+{
+    clear_error();
+    if(int e = check_layouts("gemm_f16_ws", layout_a, layout_b, layout_cd))
+        return e;
+    return launch_gemm_tc05_f16(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, layout_a, layout_b, layout_cd, out_type,
+                                as_stream(stream), workspace, workspace_bytes);
+}
+
+extern "C" int b200wmma_gemm_i8_ws(uint32_t m, uint32_t n, uint32_t k, const int8_t* a, const int8_t* b, const int32_t* c,
+                                   int32_t* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha,
+                                   int32_t beta, int layout_a, int layout_b, int layout_cd, void* workspace,
+                                   size_t workspace_bytes, void* stream)
+{
+    clear_error();
+    if(int e = check_layouts("gemm_i8_ws", layout_a, layout_b, layout_cd))
+        return e;
+    return launch_gemm_tc05_i8(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, layout_a, layout_b, layout_cd,
+                               as_stream(stream), workspace, workspace_bytes);
 }
 
 extern "C" int b200wmma_gemm_bf16(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const float* c,
@@ -234,13 +265,13 @@ extern "C" int b200wmma_gemm_i8(uint32_t m, uint32_t n, uint32_t k, const int8_t
 // ---------------------------------------------------------------------------------------------
 struct b200wmma_ctx
 {
-    static constexpr int NBUF = 4;
+    static constexpr int NBUF = 5; // A, B, C, D, split-K scratch of the GEMM kernel
     cudaStream_t         stream    = nullptr; // compute stream (and the only one for the small drivers)
     cudaStream_t         s_in = nullptr, s_out = nullptr; // copy-in / copy-out streams of the pipelined GEMM driver
     cudaStream_t         s_bc = nullptr; // broadcasts of the multi-GPU GEMM driver (created on first use)
     std::vector<cudaEvent_t> events;      // reusable
-    void*                buf[NBUF] = {nullptr, nullptr, nullptr, nullptr};
-    size_t               cap[NBUF] = {0, 0, 0, 0};
+    void*                buf[NBUF] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    size_t               cap[NBUF] = {0, 0, 0, 0, 0};
     int                  device    = 0;
     float                stage_ms[5] = {0, 0, 0, 0, 0}; // upload span, exchange, compute, copy-out, total of the last GEMM host call
     bool                 stage_valid = false;
@@ -356,6 +387,7 @@ namespace
         if(int e = ctx_reserve(ctx, 1, bb)) return e;
         if(int e = ctx_reserve(ctx, 2, use_c ? bc : 16)) return e;
         if(int e = ctx_reserve(ctx, 3, bd)) return e;
+        if(int e = ctx_reserve(ctx, 4, gemm_split_workspace_bytes())) return e;
         // events per chunk: A in, exchange begin, exchange end, C in, compute begin, compute end, copy-out end; +3 overall
         constexpr size_t PER = 7;
         if(int e = ctx_events(ctx, PER * static_cast<size_t>(chunks) + 3)) return e;
@@ -575,7 +607,7 @@ extern "C" int b200wmma_gemm_f16_host(b200wmma_ctx* ctx, uint32_t m, uint32_t n,
                               [&](uint32_t rows, const void* da, const void* dc, void* dd) {
                                   return launch_gemm_tc05_f16(rows, n, k, da, ctx->buf[1], dc, dd, lda, ldb, ldc, ldd, alpha,
                                                               use_c ? beta : 0.0f, B200WMMA_ROW_MAJOR, B200WMMA_COL_MAJOR,
-                                                              B200WMMA_ROW_MAJOR, out_type, ctx->stream);
+                                                              B200WMMA_ROW_MAJOR, out_type, ctx->stream, ctx->buf[4], ctx->cap[4]);
                               });
 }
 
@@ -601,7 +633,7 @@ extern "C" int b200wmma_gemm_f16_host_mg(b200wmma_ctx* ctx, b200wmma_mg* mg, int
         ctx, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, 2, osz, use_c,
         [&](uint32_t rows, const void* da, const void* dc, void* dd) {
             return launch_gemm_tc05_f16(rows, n, k, da, ctx->buf[1], dc, dd, lda, ldb, ldc, ldd, alpha, use_c ? beta : 0.0f,
-                                        B200WMMA_ROW_MAJOR, B200WMMA_COL_MAJOR, B200WMMA_ROW_MAJOR, out_type, ctx->stream);
+                                        B200WMMA_ROW_MAJOR, B200WMMA_COL_MAJOR, B200WMMA_ROW_MAJOR, out_type, ctx->stream, ctx->buf[4], ctx->cap[4]);
         },
         mg, root);
 }
@@ -631,7 +663,8 @@ extern "C" int b200wmma_gemm_i8_host(b200wmma_ctx* ctx, uint32_t m, uint32_t n, 
                                                              static_cast<const int8_t*>(ctx->buf[1]),
                                                              static_cast<const int32_t*>(dc), static_cast<int32_t*>(dd), lda,
                                                              ldb, ldc, ldd, alpha, use_c ? beta : 0, B200WMMA_ROW_MAJOR,
-                                                             B200WMMA_COL_MAJOR, B200WMMA_ROW_MAJOR, ctx->stream);
+                                                             B200WMMA_COL_MAJOR, B200WMMA_ROW_MAJOR, ctx->stream, ctx->buf[4],
+                                                             ctx->cap[4]);
                               });
 }
 
@@ -657,7 +690,7 @@ extern "C" int b200wmma_gemm_i8_host_mg(b200wmma_ctx* ctx, b200wmma_mg* mg, int 
             return launch_gemm_tc05_i8(rows, n, k, static_cast<const int8_t*>(da), static_cast<const int8_t*>(ctx->buf[1]),
                                        static_cast<const int32_t*>(dc), static_cast<int32_t*>(dd), lda, ldb, ldc, ldd, alpha,
                                        use_c ? beta : 0, B200WMMA_ROW_MAJOR, B200WMMA_COL_MAJOR, B200WMMA_ROW_MAJOR,
-                                       ctx->stream);
+                                       ctx->stream, ctx->buf[4], ctx->cap[4]);
         },
         mg, root);
 }

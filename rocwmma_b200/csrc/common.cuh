@@ -70,7 +70,10 @@ namespace b200wmma
     int launch_gemm_tc05_f16(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b,
                              const void* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
                              uint32_t ldd, float alpha, float beta, int layout_a, int layout_b,
-                             int layout_cd, int out_type, cudaStream_t stream);
+                             int layout_cd, int out_type, cudaStream_t stream, void* split_ws = nullptr,
+                             size_t split_ws_bytes = 0);
+    // bytes of scratch with which the 512 x 256 GEMM kernel may split the tiles of its last, partial round along K
+    size_t gemm_split_workspace_bytes();
     int launch_gemm_tc05_bf16(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const float* c, float* d,
                               uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, float alpha, float beta, int layout_a,
                               int layout_b, int layout_cd, cudaStream_t stream);
@@ -86,7 +89,7 @@ namespace b200wmma
                             const int8_t* b, const int32_t* c, int32_t* d, uint32_t lda,
                             uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha,
                             int32_t beta, int layout_a, int layout_b, int layout_cd,
-                            cudaStream_t stream);
+                            cudaStream_t stream, void* split_ws = nullptr, size_t split_ws_bytes = 0);
     // packed int4 operands (two per byte along K), unpacked to int8 in the kernel's load path
     int launch_gemm_tc05_i4(uint32_t m, uint32_t n, uint32_t k, const uint8_t* a_packed, const uint8_t* b_packed,
                             const int32_t* c, int32_t* d, uint32_t lda_bytes, uint32_t ldb_bytes, uint32_t ldc, uint32_t ldd,

@@ -284,7 +284,9 @@ namespace b200wmma
                           ScalarT      beta,
                           bool         a_mn, // A column-major (M contiguous) instead of row-major
                           bool         b_mn, // B row-major (N contiguous) instead of column-major
-                          cudaStream_t stream)
+                          cudaStream_t stream,
+                          void*        split_ws       = nullptr, // optional scratch for the split-K tail (512 x 256 kernel)
+                          size_t       split_ws_bytes = 0)
         {
             constexpr uint32_t EB = elem_bytes<KIND>();
             // bf16 and fp8 inputs run on the 512 x 256 pair kernel only
@@ -339,6 +341,8 @@ namespace b200wmma
                 const double t256 = rounds(static_cast<uint64_t>(ceil_div(m, 256)) * ceil_div(n, 256), slots2) * 32768.0 / 0.955;
                 const double t128 = rounds(static_cast<uint64_t>(ceil_div(m, 128)) * ceil_div(n, 256), slots1) * 32768.0 / 0.91;
                 pick              = (t512 <= t256 && t512 <= t128) ? 3 : (t256 <= t128 ? 2 : 1);
+                if(split_ws != nullptr && m > tc05p::PAIR_M)
+                    pick = 3; // with a split-K tail the 512 x 256 kernel has no partial round to lose
                 if(m <= BLOCK_M)
                     pick = 1; // a single 128-row band: pairing would multiply zeros
                 else if(m <= tc05p::PAIR_M && pick == 3)
@@ -393,8 +397,44 @@ namespace b200wmma
                     B200_REQUIRE(nc > 0, B200WMMA_ERR_CUDA, "no two-CTA cluster of the GEMM kernel fits on this device");
                     max_clusters = nc;
                 }
-                const uint32_t pairs = min(tiles_m * tiles_n, static_cast<uint32_t>(max_clusters));
-                cfg.gridDim          = dim3(2 * pairs);
+                uint32_t pairs = min(tiles_m * tiles_n, static_cast<uint32_t>(max_clusters));
+                // Split-K tail: when the tiles do not fill a whole number of rounds, the tiles of the last, partial round
+                // are cut along K into equal slab ranges, one per SM pair, so that every pair works to the end; the
+                // partial accumulators meet in the caller's workspace.  Worth it when the slabs saved exceed the cost of
+                // the exchange (about FIXUP_SLABS slabs' worth of time); needs the TMA epilogue.
+                tc05q::SplitPlan plan = {0u, 0u, 0u};
+                if(split_ws != nullptr && vec_ok != 0 && tuning::get(tuning::GEMM_SPLIT_TAIL) != 2)
+                {
+                    // The exchange costs a pair about as much time as FIXUP_SLABS K slabs.  Measured (fp16, 64-wide slabs, 74
+                    // pairs): writing a partial 6 k + 2 k cycles (stores, fence), adding one 8.5 k on top of the 6 k drain, a
+                    // second pipeline ramp and the flag reset; in all 33 slabs' worth at 8192 x 1024 x 8192 (two pieces per
+                    // tile) and about 75 at 8192 x 4096 x 8192 (three pieces per tile after three whole rounds).  With 80
+                    // the split is taken where a few left-over tiles would otherwise cost a whole round.
+                    constexpr uint32_t MIN_SLABS   = 16;
+                    const uint32_t     fix_tuned   = static_cast<uint32_t>(tuning::get(tuning::GEMM_SPLIT_FIXUP));
+                    const uint32_t     FIXUP_SLABS = fix_tuned ? fix_tuned : 80u;
+                    const uint32_t pmax = static_cast<uint32_t>(max_clusters), tiles = tiles_m * tiles_n;
+                    const uint32_t num_kb = ceil_div(k * EB, BLOCK_K_BYTES);
+                    const uint32_t full = tiles / pmax, rem = tiles % pmax;
+                    const uint64_t slabs = static_cast<uint64_t>(rem) * num_kb;
+                    uint32_t       sk_pairs = static_cast<uint32_t>(slabs / MIN_SLABS < pmax ? slabs / MIN_SLABS : pmax);
+                    const uint32_t used = full > 0 ? pmax : sk_pairs;
+                    const size_t   need = static_cast<size_t>(used) * (tc05q::SLOT_WORDS * 4u + 4u);
+                    if(rem > 0 && sk_pairs > rem && slabs < (1ull << 31) && split_ws_bytes >= need && aligned16(split_ws))
+                    {
+                        const uint64_t per_pair = (slabs + sk_pairs - 1) / sk_pairs;
+                        if(per_pair + FIXUP_SLABS < num_kb)
+                        {
+                            plan.dp_rounds = full, plan.sk_tiles = rem, plan.sk_pairs = sk_pairs;
+                            pairs = used;
+                            uint32_t* flags = static_cast<uint32_t*>(split_ws) + static_cast<size_t>(pairs) * tc05q::SLOT_WORDS;
+#ifndef B200WMMA_SK_NO_MEMSET // (timing experiments only: results are wrong without the reset)
+                            B200_CHECK_CUDA(cudaMemsetAsync(flags, 0, sizeof(uint32_t) * pairs, stream));
+#endif
+                        }
+                    }
+                }
+                cfg.gridDim = dim3(2 * pairs);
                 // C / D staging boxes for the TMA epilogue (used when the rows are 16-byte aligned)
                 CUtensorMap tm_c = tm_a, tm_d = tm_a; // placeholders, never dereferenced when vec_ok == 0
                 if(vec_ok != 0)
@@ -407,7 +447,8 @@ namespace b200wmma
                             return e;
                 }
                 B200_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, tm_c, tm_d, c, d, m, n, k * EB, ldc, ldd, alpha,
-                                                   beta, tiles_m, tiles_n, vec_ok, group_override(tc05q::GROUP_M), status));
+                                                   beta, tiles_m, tiles_n, vec_ok, group_override(tc05q::GROUP_M), status, plan,
+                                                   static_cast<uint32_t*>(split_ws)));
                 return B200WMMA_OK;
             }
 
@@ -488,29 +529,41 @@ namespace b200wmma
     template <int KIND, typename OutT, typename ScalarT>
     static int launch_any_layout(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const OutT* c,
                                  OutT* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, ScalarT alpha,
-                                 ScalarT beta, int layout_a, int layout_b, int layout_cd, cudaStream_t stream)
+                                 ScalarT beta, int layout_a, int layout_b, int layout_cd, cudaStream_t stream,
+                                 void* split_ws = nullptr, size_t split_ws_bytes = 0)
     {
         const bool a_mn = layout_a == B200WMMA_COL_MAJOR, b_mn = layout_b == B200WMMA_ROW_MAJOR;
         if(layout_cd == B200WMMA_ROW_MAJOR)
             return tc05::launch<KIND, OutT, ScalarT>(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, a_mn, b_mn,
-                                                     stream);
+                                                     stream, split_ws, split_ws_bytes);
         // B^T (n x k) takes the role of A: it is K-major exactly when B was; likewise A^T for B
-        return tc05::launch<KIND, OutT, ScalarT>(n, m, k, b, a, c, d, ldb, lda, ldc, ldd, alpha, beta, b_mn, a_mn, stream);
+        return tc05::launch<KIND, OutT, ScalarT>(n, m, k, b, a, c, d, ldb, lda, ldc, ldd, alpha, beta, b_mn, a_mn, stream,
+                                                 split_ws, split_ws_bytes);
+    }
+
+    size_t gemm_split_workspace_bytes()
+    {
+        int dev = 0, sms = 0;
+        if(cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            return 0;
+        return static_cast<size_t>(sms / 2) * (tc05q::SLOT_WORDS * 4u + 4u);
     }
 
     int launch_gemm_tc05_f16(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b,
                              const void* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
                              uint32_t ldd, float alpha, float beta, int layout_a, int layout_b, int layout_cd,
-                             int out_type, cudaStream_t stream)
+                             int out_type, cudaStream_t stream, void* split_ws, size_t split_ws_bytes)
     {
         if(out_type == B200WMMA_OUT_F16)
             return launch_any_layout<tc05::KIND_F16, __half, float>(m, n, k, a, b, static_cast<const __half*>(c),
                                                                     static_cast<__half*>(d), lda, ldb, ldc, ldd, alpha,
-                                                                    beta, layout_a, layout_b, layout_cd, stream);
+                                                                    beta, layout_a, layout_b, layout_cd, stream, split_ws,
+                                                                    split_ws_bytes);
         if(out_type == B200WMMA_OUT_F32)
             return launch_any_layout<tc05::KIND_F16, float, float>(m, n, k, a, b, static_cast<const float*>(c),
                                                                    static_cast<float*>(d), lda, ldb, ldc, ldd, alpha, beta,
-                                                                   layout_a, layout_b, layout_cd, stream);
+                                                                   layout_a, layout_b, layout_cd, stream, split_ws,
+                                                                   split_ws_bytes);
         return set_error(B200WMMA_ERR_INVALID_ARG, "gemm_f16: out_type must be 0 (f16) or 1 (f32)");
     }
 
@@ -538,9 +591,11 @@ namespace b200wmma
     int launch_gemm_tc05_i8(uint32_t m, uint32_t n, uint32_t k, const int8_t* a,
                             const int8_t* b, const int32_t* c, int32_t* d, uint32_t lda,
                             uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha,
-                            int32_t beta, int layout_a, int layout_b, int layout_cd, cudaStream_t stream)
+                            int32_t beta, int layout_a, int layout_b, int layout_cd, cudaStream_t stream, void* split_ws,
+                            size_t split_ws_bytes)
     {
         return launch_any_layout<tc05::KIND_I8, int32_t, int32_t>(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
-                                                                  layout_a, layout_b, layout_cd, stream);
+                                                                  layout_a, layout_b, layout_cd, stream, split_ws,
+                                                                  split_ws_bytes);
     }
 } // namespace b200wmma

@@ -46,6 +46,109 @@ namespace b200wmma
         constexpr uint32_t MISC_BYTES    = 512; // barriers, tensor-memory slot, abort flag, epilogue counter
         constexpr uint32_t SMEM_BYTES    = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + MISC_BYTES;
 
+        // ---- work schedule ------------------------------------------------------------------------------------------
+        // A persistent pair walks "units".  Without a split-K tail every unit is a whole tile: pair p takes tiles
+        // p, p + P, ...  With one (stream-K over the last, partial round): the first `dp_rounds` units of every pair are
+        // whole tiles as before, and the remaining `sk_tiles` tiles, seen as sk_tiles * num_kb K slabs in a row, are cut
+        // into `sk_pairs` equal ranges, one per pair.  A range covers at most two tiles: the tail of one and the head of
+        // the next.  A unit that does not end its tile (PARTIAL) writes its raw accumulators to the pair's slot of a
+        // workspace and raises the slot's flag; the unit that ends a tile (FINISH) adds the other units' partials to its
+        // own accumulators and runs the alpha / beta epilogue.  Every pair works its PARTIAL unit first and its FINISH
+        // unit last, so a FINISH unit never waits for work that has not been started before it.
+        struct SplitPlan
+        {
+            uint32_t dp_rounds; // whole-tile units per pair (split mode); unused otherwise
+            uint32_t sk_tiles; // tiles of the split round (0 = no split round)
+            uint32_t sk_pairs; // pairs that take part in it
+        };
+        enum UnitKind : uint32_t
+        {
+            UNIT_FULL    = 0,
+            UNIT_PARTIAL = 1,
+            UNIT_FINISH  = 2
+        };
+        struct Unit
+        {
+            uint32_t tile, kb0, kb1, kind;
+        };
+        constexpr uint32_t SLOT_WORDS = 2u * 2u * TILE_N * SUB_M; // one pair's accumulators: [CTA][accumulator][column][row]
+
+        // slab range [u0, u1) of pair q in the split round
+        __device__ __forceinline__ void split_range(uint32_t q, const SplitPlan& plan, uint32_t num_kb, uint32_t& u0, uint32_t& u1)
+        {
+            const uint64_t total = static_cast<uint64_t>(plan.sk_tiles) * num_kb;
+            u0 = static_cast<uint32_t>(total * q / plan.sk_pairs);
+            u1 = static_cast<uint32_t>(total * (q + 1u) / plan.sk_pairs);
+        }
+        // the idx-th unit of `pair`; false when the pair has no more units
+        __device__ __forceinline__ bool unit_at(uint32_t idx, uint32_t pair, uint32_t num_pairs, uint32_t num_tiles,
+                                                uint32_t num_kb, const SplitPlan& plan, Unit& u)
+        {
+            if(plan.sk_tiles == 0u)
+            {
+                u.tile = pair + idx * num_pairs;
+                u.kb0 = 0u, u.kb1 = num_kb, u.kind = UNIT_FULL;
+                return u.tile < num_tiles;
+            }
+            if(idx < plan.dp_rounds)
+            {
+                u.tile = pair + idx * num_pairs;
+                u.kb0 = 0u, u.kb1 = num_kb, u.kind = UNIT_FULL;
+                return true;
+            }
+            const uint32_t sidx = idx - plan.dp_rounds;
+            if(pair >= plan.sk_pairs || sidx > 1u)
+                return false;
+            uint32_t u0, u1;
+            split_range(pair, plan, num_kb, u0, u1);
+            if(u0 >= u1)
+                return false;
+            const uint32_t first_tile = plan.dp_rounds * num_pairs;
+            const uint32_t ta = u0 / num_kb, tb = (u1 - 1u) / num_kb;
+            if(ta == tb)
+            {
+                if(sidx != 0u)
+                    return false;
+                u.tile = first_tile + ta, u.kb0 = u0 - ta * num_kb, u.kb1 = u1 - ta * num_kb;
+            }
+            else if(sidx == 0u) // the head of the later tile first: it only produces a partial
+                u.tile = first_tile + tb, u.kb0 = 0u, u.kb1 = u1 - tb * num_kb;
+            else
+                u.tile = first_tile + ta, u.kb0 = u0 - ta * num_kb, u.kb1 = num_kb;
+            u.kind = (u.kb1 == num_kb) ? (u.kb0 == 0u ? UNIT_FULL : UNIT_FINISH) : UNIT_PARTIAL;
+            return true;
+        }
+        // How many pairs before `pair` hold partials of the tile whose FINISH unit starts at slab kb0 (they are the pairs
+        // pair-1, pair-2, ...: ranges are laid out in pair order).
+        __device__ __forceinline__ uint32_t finish_contributors(uint32_t pair, uint32_t tile, uint32_t num_pairs, uint32_t num_kb,
+                                                                const SplitPlan& plan)
+        {
+            const uint32_t tile_first_unit = (tile - plan.dp_rounds * num_pairs) * num_kb;
+            uint32_t       count           = 0;
+            for(uint32_t q = pair; q-- > 0u;)
+            {
+                uint32_t u0, u1;
+                split_range(q, plan, num_kb, u0, u1);
+                if(u1 <= tile_first_unit)
+                    break;
+                if(u0 < u1)
+                    ++count;
+                else
+                    break; // (an empty range cannot lie between non-empty ones of equal size; defensive)
+            }
+            return count;
+        }
+        __device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p)
+        {
+            uint32_t v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+            return v;
+        }
+        __device__ __forceinline__ void red_release_gpu_add_u32(uint32_t* p, uint32_t v)
+        {
+            asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+        }
+
         // Epilogue of one warp through shared-memory staging tiles.
         // A step covers 64 bytes of each of the warp's 32 rows (32 columns of 2-byte outputs, 16
         // columns of 4-byte outputs).  Per step: tcgen05.ld the accumulator columns, wait for the C
@@ -101,8 +204,12 @@ namespace b200wmma
                                                        uint32_t col_base, uint32_t row0, uint32_t n, ScalarT alpha,
                                                        ScalarT beta, bool read_c, uint32_t& cpar,
                                                        volatile uint32_t* cta_abort, unsigned* status, uint32_t who,
-                                                       uint32_t first = 0, uint32_t buf1_off = 0, uint32_t buf1 = 0)
+                                                       uint32_t first = 0, uint32_t buf1_off = 0, uint32_t buf1 = 0,
+                                                       const uint32_t* partials = nullptr, uint32_t npartials = 0)
             {
+                // partials: this thread's row in the accumulator copy that the nearest contributing pair left in the split-K
+                // workspace ([column][row] words); further contributors lie SLOT_WORDS lower each.  Their sum is added to
+                // the accumulator before alpha / beta.
                 if(buf1 == 0u)
                 {
                     buf1_off = buf_off + BUF_BYTES;
@@ -146,6 +253,29 @@ namespace b200wmma
                         __syncwarp();
                     }
                     ptx::tmem_ld_wait();
+                    for(uint32_t pi = 0; pi < npartials; ++pi)
+                    {
+                        const uint32_t* src = partials - static_cast<size_t>(pi) * SLOT_WORDS + (s * STEP_COLS) * SUB_M;
+                        // sixteen loads in flight at a time (each a coalesced 128-byte row of the warp), then the adds
+#pragma unroll
+                        for(uint32_t h = 0; h < STEP_COLS; h += 16)
+                        {
+                            uint32_t w[16];
+#pragma unroll
+                            for(uint32_t i = 0; i < 16; ++i)
+                                asm volatile("ld.global.cg.u32 %0, [%1];" // written by another SM: read through L2
+                                             : "=r"(w[i])
+                                             : "l"(src + (h + i) * SUB_M));
+#pragma unroll
+                            for(uint32_t i = 0; i < 16; ++i)
+                            {
+                                if constexpr(std::is_same<ScalarT, float>::value)
+                                    v[h + i] = __float_as_uint(__uint_as_float(v[h + i]) + __uint_as_float(w[i]));
+                                else
+                                    v[h + i] += w[i];
+                            }
+                        }
+                    }
                     uint8_t* rowp = smem + (bi == 0u ? buf_off : buf1_off) + lane * ROW_BYTES;
                     // The epilogue warps share four issue ports, so the drain's length is close to its instruction count:
                     // the common scalars get their own code (alpha == 1: one fused multiply-add per element; no C: none).
@@ -222,6 +352,26 @@ namespace b200wmma
                 }
                 return true;
             }
+
+            // A unit that does not end its tile: the warp's share of the raw accumulator goes to the workspace
+            // (dst: this thread's row of the pair's slot, [column][row] words - consecutive lanes, consecutive addresses).
+            __device__ static __forceinline__ void store_partial(uint32_t tmem_acc, uint32_t quad, uint32_t* dst, uint32_t first)
+            {
+#pragma unroll 2
+                for(uint32_t ls = 0; ls < MY_STEPS; ++ls)
+                {
+                    const uint32_t s = first + ls * STRIDE;
+                    uint32_t       v[STEP_COLS];
+                    if constexpr(STEP_COLS == 32)
+                        ptx::tmem_ld_32x32b_x32(tmem_acc + ((quad * 32u) << 16) + s * STEP_COLS, v);
+                    else
+                        ptx::tmem_ld_32x32b_x16(tmem_acc + ((quad * 32u) << 16) + s * STEP_COLS, v);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for(uint32_t i = 0; i < STEP_COLS; ++i)
+                        __stcg(dst + (s * STEP_COLS + i) * SUB_M, v[i]);
+                }
+            }
         };
 
         // A_MN / B_MN: the operand is MN-major (column-major A / row-major B) instead of K-major.
@@ -251,7 +401,9 @@ namespace b200wmma
                                      uint32_t  tiles_n,
                                      int       vec_ok,
                                      uint32_t  group_m,
-                                     unsigned* status)
+                                     unsigned* status,
+                                     SplitPlan plan, // sk_tiles == 0: every unit is a whole tile
+                                     uint32_t* split_ws) // split round: num_pairs slots of SLOT_WORDS words, then one flag per pair
         {
             extern __shared__ uint8_t smem_raw[];
             const uint32_t            raw_addr = ptx::smem_u32(smem_raw);
@@ -320,15 +472,16 @@ namespace b200wmma
                 // ------------------------------ TMA producer (both CTAs) ------------------------------
                 if(lane == 0)
                 {
-                    uint32_t stage = 0, phase = 0, iter = 0;
+                    uint32_t stage = 0, phase = 0, iter = 0, drained_seen = 0;
                     bool     ok = true;
-                    for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++iter)
+                    Unit     unit;
+                    for(; ok && unit_at(iter, pair, num_pairs, num_tiles, num_kb, plan, unit); ++iter)
                     {
                         uint32_t m_idx, n_idx;
-                        tile_coords(tile, tiles_m, tiles_n, group_m, m_idx, n_idx);
+                        tile_coords(unit.tile, tiles_m, tiles_n, group_m, m_idx, n_idx);
                         const int32_t row_a = static_cast<int32_t>(m_idx * PAIR_M + rank * CTA_M);
                         const int32_t row_b = static_cast<int32_t>(n_idx * TILE_N + rank * HALF_N);
-                        for(uint32_t kb = 0; kb < num_kb; ++kb)
+                        for(uint32_t kb = unit.kb0; kb < unit.kb1; ++kb)
                         {
                             ok = ptx::mbar_wait_bounded(empty_bar + 8 * stage, phase ^ 1u, cta_abort, status,
                                                         (ROLE_PRODUCER << 24) | blockIdx.x, WAIT_TIMEOUT_NS);
@@ -337,9 +490,15 @@ namespace b200wmma
                             if(stage == EPI_STAGE && iter != 0u)
                             {
                                 // this stage's A region doubles as staging tiles of the epilogue: every epilogue
-                                // warp must have finished with them for the previous tile (bounded wait)
-                                ok = ptx::mbar_wait_bounded(drained_bar, (iter - 1u) & 1u, cta_abort, status,
-                                                            (ROLE_PRODUCER << 24) | (2u << 20) | blockIdx.x, WAIT_TIMEOUT_NS);
+                                // warp must have finished with them for all earlier units (bounded wait).  The phases of
+                                // the barrier are consumed one by one: a unit with fewer slabs than stages may never come
+                                // here, and a parity wait that skipped a phase would be satisfied by the wrong one.
+                                while(ok && drained_seen < iter)
+                                {
+                                    ok = ptx::mbar_wait_bounded(drained_bar, drained_seen & 1u, cta_abort, status,
+                                                                (ROLE_PRODUCER << 24) | (2u << 20) | blockIdx.x, WAIT_TIMEOUT_NS);
+                                    ++drained_seen;
+                                }
                                 if(!ok)
                                     break;
                                 ptx::fence_proxy_async_smem(); // generic writes of the staging tiles before the TMA overwrite
@@ -434,10 +593,12 @@ namespace b200wmma
                                 ptx::mma_f8_ss_pair(tmem_base + j * TILE_N, a_desc + A_STEP * ks, b_desc + B_STEP * ks, idesc, acc);
                         }
                     };
-                    for(uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++iter)
+                    Unit unit;
+                    for(; ok && unit_at(iter, pair, num_pairs, num_tiles, num_kb, plan, unit); ++iter)
                     {
                         const uint32_t tphase = iter & 1u;
-                        const bool     split  = SPLIT && num_kb >= HEAD_KB + TAIL_KB;
+                        const uint32_t nslab  = unit.kb1 - unit.kb0; // slabs of this unit; kb counts them from 0
+                        const bool     split  = SPLIT && nslab >= HEAD_KB + TAIL_KB;
                         uint32_t       kb     = 0;
                         if(split)
                         {
@@ -462,7 +623,7 @@ namespace b200wmma
                             }
                             kb = HEAD_KB;
                         }
-                        const uint32_t mid_end = split ? num_kb - TAIL_KB : num_kb;
+                        const uint32_t mid_end = split ? nslab - TAIL_KB : nslab;
                         for(; ok && kb < mid_end; ++kb)
                         {
                             ok = wait_slab(stage, phase);
@@ -534,15 +695,21 @@ namespace b200wmma
                 const bool leader = (e & 11u) == 0u; // e == 0 (accumulator 0), e == 4 (accumulator 1)
                 uint32_t   iter = 0, cpar = 0;
                 bool       dead = false;
-                for(uint32_t tile = pair; tile < num_tiles; tile += num_pairs, ++iter)
+                // split round: this thread's row in its pair's workspace slot, and the flags
+                uint32_t* const slot_row = split_ws + static_cast<size_t>(pair) * SLOT_WORDS
+                                           + static_cast<size_t>(rank * 2u + j) * (TILE_N * SUB_M) + quad * 32u + lane;
+                uint32_t* const flags = split_ws + static_cast<size_t>(num_pairs) * SLOT_WORDS;
+                Unit            unit;
+                for(; unit_at(iter, pair, num_pairs, num_tiles, num_kb, plan, unit); ++iter)
                 {
                     uint32_t m_idx, n_idx;
-                    tile_coords(tile, tiles_m, tiles_n, group_m, m_idx, n_idx);
+                    tile_coords(unit.tile, tiles_m, tiles_n, group_m, m_idx, n_idx);
                     const uint32_t row_base = m_idx * PAIR_M + rank * CTA_M + j * SUB_M; // this accumulator's first row
                     const uint32_t row0     = row_base + quad * 32u; // this warp's first row
                     const uint32_t col_base = n_idx * TILE_N;
                     // staged path: needs 16-byte aligned rows (TMA) and a tile that starts inside the matrix
-                    const bool staged = vec_ok != 0 && row0 < m && col_base < n;
+                    const bool partial = unit.kind == UNIT_PARTIAL; // no C, no D: the raw accumulators go to the workspace
+                    const bool staged  = !partial && vec_ok != 0 && row0 < m && col_base < n;
                     // C does not depend on the accumulators: the tile of the warp's first step is requested now
                     if(!dead && staged && read_c && lane == 0)
                         Drain::prefetch_c(&tmap_c, buf0, cbar0, col_base, row0, n, first, 0, 1, buf1);
@@ -561,10 +728,49 @@ namespace b200wmma
                     if(staged && read_c && lane == 0)
                         Drain::prefetch_c(&tmap_c, buf0, cbar0, col_base, row0, n, first, 1, 2, buf1);
                     const uint32_t tmem_acc = tmem_base + j * TILE_N;
-                    if(staged)
-                        dead = !Drain::run(tmem_acc, quad, lane, smem, buf_off, buf0, cbar0, &tmap_c, &tmap_d, col_base, row0, n,
-                                           alpha, beta, read_c, cpar, cta_abort, status,
-                                           (ROLE_EPILOGUE << 24) | (1u << 20) | blockIdx.x, first, buf1_off, buf1);
+                    if(partial)
+                    {
+                        Drain::store_partial(tmem_acc, quad, slot_row, first);
+                        __threadfence(); // this thread's partial sums before the flag
+                        __syncwarp();
+                        if(lane == 0)
+                            red_release_gpu_add_u32(flags + pair, 1u); // complete at 2 CTAs x EPI_WARPS
+                    }
+                    else if(staged)
+                    {
+                        uint32_t npart = 0;
+                        if(unit.kind == UNIT_FINISH)
+                        {
+                            // the pairs before this one hold the rest of the tile's K range: wait for their partials
+                            npart = finish_contributors(pair, unit.tile, num_pairs, num_kb, plan);
+                            const uint64_t t0 = ptx::globaltimer_ns();
+                            for(uint32_t pi = 0; pi < npart && !dead; ++pi)
+                            {
+                                uint32_t spins = 0;
+                                while(ld_acquire_gpu_u32(flags + pair - 1u - pi) < 2u * EPI_WARPS)
+                                {
+                                    __nanosleep(64);
+                                    if((++spins & 0x3Fu) == 0u && (*cta_abort || ptx::globaltimer_ns() - t0 > WAIT_TIMEOUT_NS))
+                                    {
+                                        if(!*cta_abort)
+                                        {
+                                            *cta_abort = 1u;
+                                            if(atomicCAS(status, 0u, ptx::STATUS_TIMEOUT_CODE) == 0u)
+                                                status[1] = (ROLE_EPILOGUE << 24) | (6u << 20) | blockIdx.x;
+                                        }
+                                        dead = true;
+                                        break;
+                                    }
+                                }
+                            }
+                            dead = __any_sync(0xFFFFFFFFu, dead);
+                        }
+                        if(!dead)
+                            dead = !Drain::run(tmem_acc, quad, lane, smem, buf_off, buf0, cbar0, &tmap_c, &tmap_d, col_base, row0,
+                                               n, alpha, beta, read_c, cpar, cta_abort, status,
+                                               (ROLE_EPILOGUE << 24) | (1u << 20) | blockIdx.x, first, buf1_off, buf1,
+                                               slot_row - SLOT_WORDS, npart);
+                    }
                     else if(vec_ok == 0 && first == 0u)
                         drain_accumulator<OutT, ScalarT, TILE_N>(tmem_acc, quad, lane, row_base, col_base, m, n, c, d, ldc,
                                                                  ldd, alpha, beta, read_c, 0);

@@ -12,6 +12,8 @@ namespace b200wmma
             GEMM_TILE_VARIANT = 0, // dense tcgen05 GEMM tile shape: 1 = 128x256 per SM, 2 = 256x256 per SM pair, 3 = 512x256 per pair
             GEMM_GROUP_M      = 1, // rasterisation band height in row tiles
             SP24_FORCE_EXPAND = 2, // 1: the 2:4-sparse GEMM always densifies A into the workspace and runs the dense kernel
+            GEMM_SPLIT_TAIL   = 4, // 512x256 kernel given a workspace: 1 = split the last partial round along K when it pays, 2 = never
+            GEMM_SPLIT_FIXUP  = 5, // cost of the split-K exchange the planner assumes, in K slabs (0 = built-in)
             GEMM_MMA_ORDER    = 3, // 512x256 kernel, first / last K slabs of a tile: 1 = by accumulator, 2 = by slab
             NUM_KEYS
         };

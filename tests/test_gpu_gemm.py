@@ -500,6 +500,85 @@ def test_gemm_f64_bench_size_row_sample():
     assert gemm_rel_err(d_r, ref, bound) <= TOL_F64_OUT
 
 
+# Shapes whose tile count is not a whole number of rounds over the SM pairs, so that with a workspace the last round is
+# split along K (stream-K): a few tiles over many pairs, whole rounds followed by a split round, ragged M / N / K,
+# the per-GPU problem of an 8192^3 GEMM sharded 8 ways.
+SPLIT_SHAPES = [(1024, 1024, 8192), (2560, 7680, 2048), (1100, 900, 4160), (8192, 1024, 8192), (600, 256, 1024),
+                (8192, 2048, 8192), (3584, 3072, 4096), (2048, 4864, 4096)]
+
+
+@pytest.fixture(autouse=True)
+def _split_whenever_possible():
+    """The planner only splits when it expects a gain; these tests are about correctness, so they make it split whenever
+    the schedule allows (exchange cost counted as one slab)."""
+    api.set_tuning("gemm_split_fixup", 1)
+    yield
+    api.set_tuning("gemm_split_fixup", 0)
+
+
+@pytest.mark.parametrize("m,n,k", SPLIT_SHAPES)
+def test_gemm_split_tail_int8_bit_exact(m, n, k):
+    """int8 with the split-K workspace: bit-identical to the unsplit call (integer addition is associative) and to the
+    oracle on a row sample; alpha / beta with C included."""
+    a = G.fill_torch(torch.empty((m, k), dtype=torch.int8, device="cuda"), G.SEED_A, "int8")
+    bs = G.fill_torch(torch.empty((n, k), dtype=torch.int8, device="cuda"), G.SEED_B, "int8")
+    c = (G.fill_torch(torch.empty((m, n), dtype=torch.int8, device="cuda"), G.SEED_C, "int8").to(torch.int32) * 1000).contiguous()
+    ws = torch.empty(api.gemm_split_workspace_bytes(), dtype=torch.uint8, device="cuda")
+    for alpha, beta in ((1, 0), (3, -2)):
+        plain, split = nan_filled((m, n), torch.int32), nan_filled((m, n), torch.int32)
+        api.gemm_i8(m, n, k, a, bs, c if beta else None, plain, k, k, n, n, alpha, beta)
+        for _ in range(2):   # twice: the flags in the workspace are reset by every call
+            split.fill_(-5)
+            api.gemm_i8(m, n, k, a, bs, c if beta else None, split, k, k, n, n, alpha, beta, workspace=ws)
+            assert_status_ok()
+            assert torch.equal(plain, split)
+        rows = _rows_sample(m, 12, 91)
+        idx = torch.from_numpy(rows).cuda()
+        ref = oracle_gemm_rows(a[idx].cpu().numpy(), bs.cpu().numpy(), c[idx].cpu().numpy() if beta else None, alpha, beta,
+                               np.int32, n, k)
+        assert np.array_equal(split[idx].cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("m,n,k", SPLIT_SHAPES)
+@pytest.mark.parametrize("out_np", [np.float16, np.float32], ids=["f16out", "f32out"])
+def test_gemm_split_tail_f16(m, n, k, out_np):
+    """fp16 with the split-K workspace against the oracle on a row sample (the partial sums are fp32)."""
+    tdt = torch.float16 if out_np == np.float16 else torch.float32
+    a = G.fill_torch(torch.empty((m, k), dtype=torch.float16, device="cuda"), G.SEED_A, "uniform")
+    bs = G.fill_torch(torch.empty((n, k), dtype=torch.float16, device="cuda"), G.SEED_B, "uniform")
+    c = G.fill_torch(torch.empty((m, n), dtype=tdt, device="cuda"), G.SEED_C, "uniform")
+    ws = torch.empty(api.gemm_split_workspace_bytes(), dtype=torch.uint8, device="cuda")
+    d = nan_filled((m, n), tdt)
+    api.gemm_f16(m, n, k, a, bs, c, d, k, k, n, n, 1.0, 1.0, workspace=ws)
+    assert_status_ok()
+    assert bool(torch.isfinite(d).all())
+    rows = _rows_sample(m, 12, 92)
+    idx = torch.from_numpy(rows).cuda()
+    a_r, c_r, b_h = a[idx].cpu().numpy(), c[idx].cpu().numpy(), bs.cpu().numpy()
+    ref = oracle_gemm_rows(a_r, b_h, c_r, 1.0, 1.0, out_np, n, k)
+    bound = R.gemm_abs_bound(len(rows), n, k, a_r, b_h.T, c_r, 1.0, 1.0)
+    assert gemm_rel_err(d[idx].cpu().numpy(), ref, bound) <= (TOL_F16_OUT if out_np == np.float16 else TOL_F32_OUT)
+
+
+def test_gemm_split_tail_declined_cases():
+    """A workspace that is too small, and C / D rows that are not 16-byte aligned: the unsplit schedule runs, results
+    unchanged."""
+    m, n, k = 1024, 1024, 2048
+    a = G.fill_torch(torch.empty((m, k), dtype=torch.int8, device="cuda"), 1, "int8")
+    bs = G.fill_torch(torch.empty((n, k), dtype=torch.int8, device="cuda"), 2, "int8")
+    want = nan_filled((m, n), torch.int32)
+    api.gemm_i8(m, n, k, a, bs, None, want, k, k, n, n, 1, 0)
+    small = torch.empty(4096, dtype=torch.uint8, device="cuda")
+    got = nan_filled((m, n), torch.int32)
+    api.gemm_i8(m, n, k, a, bs, None, got, k, k, n, n, 1, 0, workspace=small)
+    assert torch.equal(got, want)
+    ws = torch.empty(api.gemm_split_workspace_bytes(), dtype=torch.uint8, device="cuda")
+    odd = torch.full((m, n + 3), -9, dtype=torch.int32, device="cuda")
+    api.gemm_i8(m, n, k, a, bs, None, odd, k, k, n, n + 3, 1, 0, workspace=ws)
+    assert_status_ok()
+    assert torch.equal(odd[:, :n], want) and bool((odd[:, n:] == -9).all())
+
+
 @pytest.mark.parametrize("variant", [1, 2, 3], ids=["1cta", "2cta", "2cta512"])
 def test_gemm_every_tile_variant(variant):
     """Each tile shape of the tcgen05 GEMM (one-CTA 128x256, pair 256x256, pair 512x256), forced through
