@@ -42,7 +42,7 @@ typedef enum b200wmma_status
 } b200wmma_status;
 
 enum { B200WMMA_ROW_MAJOR = 0, B200WMMA_COL_MAJOR = 1 };
-enum { B200WMMA_OUT_F16 = 0, B200WMMA_OUT_F32 = 1 };
+enum { B200WMMA_OUT_F16 = 0, B200WMMA_OUT_F32 = 1, B200WMMA_OUT_BF16 = 2 };
 enum { B200WMMA_FP8_E4M3 = 0, B200WMMA_FP8_E5M2 = 1 }; /* OCP 8-bit float formats (finite-only e4m3, IEEE-like e5m2) */
 
 /* Human-readable text for the last error raised on the calling thread. */
@@ -127,9 +127,10 @@ int b200wmma_gemm_i8_ws(uint32_t m, uint32_t n, uint32_t k,
                         void* workspace, size_t workspace_bytes, void* stream);
 /* fp32 inputs and outputs with fp32-class accuracy on the tensor cores (each operand split into two TF32
  * terms, three products accumulated in fp32): the reference's fp32 GEMM samples sgemm_rocwmma_d
- * (samples/simple_sgemm.cpp) and gemm_rocwmma_d of samples/perf_sgemm.cpp.  A row major, B column major,
- * C/D row major; k a multiple of 4; A / B rows 16-byte aligned.  `workspace`: caller-owned device scratch of
- * b200wmma_gemm_f32_workspace_bytes() bytes (the split copies of A and B). */
+ * (samples/simple_sgemm.cpp) and gemm_rocwmma_d of samples/perf_sgemm.cpp.  Every combination of row / column major
+ * A, B and C/D; k a multiple of 4; the rows of an operand stored with K contiguous 16-byte aligned.  `workspace`:
+ * caller-owned device scratch of b200wmma_gemm_f32_workspace_bytes() bytes (the split copies of A and B, always
+ * written K-contiguous, which is where the other layouts are absorbed). */
 size_t b200wmma_gemm_f32_workspace_bytes(uint32_t m, uint32_t n, uint32_t k);
 int b200wmma_gemm_f32(uint32_t m, uint32_t n, uint32_t k,
                       const float* a, const float* b, const float* c, float* d,
@@ -142,6 +143,21 @@ int b200wmma_gemm_bf16(uint32_t m, uint32_t n, uint32_t k,
                        uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
                        float alpha, float beta,
                        int layout_a, int layout_b, int layout_cd, void* stream);
+/* The other (InputT, OutputT, ComputeT) sets of the reference's GEMM sweep (test/gemm/gemm_common_test_params.hpp:51-147):
+ * bfloat16 inputs with bfloat16 C / D and fp32 compute (out_type B200WMMA_OUT_BF16; B200WMMA_OUT_F32 is
+ * b200wmma_gemm_bf16), and int8 inputs with int8 C / D and int32 compute: d = int8(alpha * acc + beta * int32(c)), the
+ * int32 value cast as the reference's static_cast<OutputT> does (test/reference_impl.hpp:77-78: the low 8 bits).
+ * All layout combinations.  The int8-output form drains element-wise (one byte per store). */
+int b200wmma_gemm_bf16_out(uint32_t m, uint32_t n, uint32_t k,
+                           const void* a, const void* b, const void* c, void* d,
+                           uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                           float alpha, float beta,
+                           int layout_a, int layout_b, int layout_cd, int out_type, void* stream);
+int b200wmma_gemm_i8_i8(uint32_t m, uint32_t n, uint32_t k,
+                        const int8_t* a, const int8_t* b, const int8_t* c, int8_t* d,
+                        uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
+                        int32_t alpha, int32_t beta,
+                        int layout_a, int layout_b, int layout_cd, void* stream);
 int b200wmma_gemm_fp8(uint32_t m, uint32_t n, uint32_t k,
                       const void* a, const void* b, const float* c, float* d,
                       uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,

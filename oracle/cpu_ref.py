@@ -21,7 +21,7 @@ REF_PATH = os.path.join(_HERE, "_ref", "libref.so")
 
 _u32, _vp = C.c_uint32, C.c_void_p
 _GEMM_SCALARS = {
-    "oracle_gemm_f16_f32": C.c_float, "oracle_gemm_f16_f16": C.c_float, "oracle_gemm_i8_i32": C.c_int32,
+    "oracle_gemm_f16_f32": C.c_float, "oracle_gemm_f16_f16": C.c_float, "oracle_gemm_i8_i32": C.c_int32, "oracle_gemm_i8_i8": C.c_int32,
     "oracle_gemm_f32": C.c_float, "oracle_gemm_f64": C.c_double,
 }
 
@@ -91,7 +91,7 @@ def _c(a):
 
 _GEMM_FN = {
     (np.float16, np.float32): "oracle_gemm_f16_f32", (np.float16, np.float16): "oracle_gemm_f16_f16",
-    (np.int8, np.int32): "oracle_gemm_i8_i32", (np.float32, np.float32): "oracle_gemm_f32",
+    (np.int8, np.int32): "oracle_gemm_i8_i32", (np.int8, np.int8): "oracle_gemm_i8_i8", (np.float32, np.float32): "oracle_gemm_f32",
     (np.float64, np.float64): "oracle_gemm_f64",
 }
 

@@ -68,6 +68,7 @@ static inline size_t idx2(uint32_t row, uint32_t col, uint32_t ld, int col_major
 DEFINE_GEMM(oracle_gemm_f16_f32, f16, float, float)
 DEFINE_GEMM(oracle_gemm_f16_f16, f16, f16, float)
 DEFINE_GEMM(oracle_gemm_i8_i32, int8_t, int32_t, int32_t)
+DEFINE_GEMM(oracle_gemm_i8_i8, int8_t, int8_t, int32_t) /* the reference's <int8_t, int8_t, int32_t> set (test/gemm/gemm_common_test_params.hpp:53) */
 DEFINE_GEMM(oracle_gemm_f32, float, float, float)
 DEFINE_GEMM(oracle_gemm_f64, double, double, double)
 

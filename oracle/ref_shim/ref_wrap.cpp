@@ -106,6 +106,7 @@ namespace
 GEMM_ENTRY(oracle_gemm_f16_f32, _Float16, float, float)
 GEMM_ENTRY(oracle_gemm_f16_f16, _Float16, _Float16, float)
 GEMM_ENTRY(oracle_gemm_i8_i32, int8_t, int32_t, int32_t)
+GEMM_ENTRY(oracle_gemm_i8_i8, int8_t, int8_t, int32_t)
 GEMM_ENTRY(oracle_gemm_f32, float, float, float)
 GEMM_ENTRY(oracle_gemm_f64, double, double, double)
 

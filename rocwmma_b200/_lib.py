@@ -32,6 +32,10 @@ SIGNATURES = {
                                     C.c_int, C.c_int, C.c_int, vp, sz, vp]),
     "b200wmma_gemm_bf16": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32, f32, f32,
                                      C.c_int, C.c_int, C.c_int, vp]),
+    "b200wmma_gemm_bf16_out": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32, f32, f32,
+                                         C.c_int, C.c_int, C.c_int, C.c_int, vp]),
+    "b200wmma_gemm_i8_i8": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32, i32, i32,
+                                      C.c_int, C.c_int, C.c_int, vp]),
     "b200wmma_gemm_fp8": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32, f32, f32,
                                     C.c_int, C.c_int, C.c_int, C.c_int, vp]),
     "b200wmma_gemm_f64": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32, f64, f64,

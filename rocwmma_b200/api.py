@@ -70,27 +70,48 @@ def gemm_f32_workspace_bytes(m, n, k):
     return lib().b200wmma_gemm_f32_workspace_bytes(m, n, k)
 
 
-def gemm_f32(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, workspace):
-    """fp32 GEMM (3 x TF32 on the tensor cores); A row-major, B column-major, C/D row-major."""
+def gemm_f32(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, workspace,
+             layout_a=ROW_MAJOR, layout_b=COL_MAJOR, layout_cd=ROW_MAJOR):
+    """fp32 GEMM (3 x TF32 on the tensor cores), every layout combination."""
     _need(a, torch.float32, "a"); _need(b, torch.float32, "b"); _need(d, torch.float32, "d")
     _need(workspace, torch.uint8, "workspace")
     if c is not None:
         _need(c, torch.float32, "c")
     check(lib().b200wmma_gemm_f32(m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc, ldd, alpha, beta,
-                                  ROW_MAJOR, COL_MAJOR, ROW_MAJOR, _ptr(workspace), workspace.numel(), _stream()))
+                                  layout_a, layout_b, layout_cd, _ptr(workspace), workspace.numel(), _stream()))
 
 
 FP8_E4M3, FP8_E5M2 = 0, 1
 
 
+OUT_BF16 = 2
+
+
 def gemm_bf16(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
               layout_a=ROW_MAJOR, layout_b=COL_MAJOR, layout_cd=ROW_MAJOR):
-    """bfloat16 inputs, fp32 accumulate, fp32 C / D."""
-    _need(a, torch.bfloat16, "a"); _need(b, torch.bfloat16, "b"); _need(d, torch.float32, "d")
+    """bfloat16 inputs, fp32 accumulate, C / D fp32 or bfloat16 (by d.dtype)."""
+    _need(a, torch.bfloat16, "a"); _need(b, torch.bfloat16, "b")
+    if d.dtype not in (torch.float32, torch.bfloat16):
+        raise TypeError("d must be float32 or bfloat16")
+    _need(d, d.dtype, "d")
     if c is not None:
-        _need(c, torch.float32, "c")
-    check(lib().b200wmma_gemm_bf16(m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc, ldd,
-                                   alpha, beta, layout_a, layout_b, layout_cd, _stream()))
+        _need(c, d.dtype, "c")
+    if d.dtype == torch.float32:
+        check(lib().b200wmma_gemm_bf16(m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc, ldd,
+                                       alpha, beta, layout_a, layout_b, layout_cd, _stream()))
+    else:
+        check(lib().b200wmma_gemm_bf16_out(m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc, ldd,
+                                           alpha, beta, layout_a, layout_b, layout_cd, OUT_BF16, _stream()))
+
+
+def gemm_i8_i8(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
+               layout_a=ROW_MAJOR, layout_b=COL_MAJOR, layout_cd=ROW_MAJOR):
+    """int8 inputs, int32 compute, int8 C / D (the int32 result cast to int8)."""
+    _need(a, torch.int8, "a"); _need(b, torch.int8, "b"); _need(d, torch.int8, "d")
+    if c is not None:
+        _need(c, torch.int8, "c")
+    check(lib().b200wmma_gemm_i8_i8(m, n, k, _ptr(a), _ptr(b), _ptr(c), _ptr(d), lda, ldb, ldc, ldd,
+                                    alpha, beta, layout_a, layout_b, layout_cd, _stream()))
 
 
 def gemm_fp8(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,

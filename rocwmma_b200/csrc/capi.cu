@@ -215,7 +215,29 @@ extern "C" int b200wmma_gemm_bf16(uint32_t m, uint32_t n, uint32_t k, const void
     if(int e = check_layouts("gemm_bf16", layout_a, layout_b, layout_cd))
         return e;
     return launch_gemm_tc05_bf16(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, layout_a, layout_b, layout_cd,
+                                 B200WMMA_OUT_F32, as_stream(stream));
+}
+
+extern "C" int b200wmma_gemm_bf16_out(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const void* c, void* d,
+                                      uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, float alpha, float beta,
+                                      int layout_a, int layout_b, int layout_cd, int out_type, void* stream)
+{
+    clear_error();
+    if(int e = check_layouts("gemm_bf16_out", layout_a, layout_b, layout_cd))
+        return e;
+    return launch_gemm_tc05_bf16(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, layout_a, layout_b, layout_cd, out_type,
                                  as_stream(stream));
+}
+
+extern "C" int b200wmma_gemm_i8_i8(uint32_t m, uint32_t n, uint32_t k, const int8_t* a, const int8_t* b, const int8_t* c,
+                                   int8_t* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha,
+                                   int32_t beta, int layout_a, int layout_b, int layout_cd, void* stream)
+{
+    clear_error();
+    if(int e = check_layouts("gemm_i8_i8", layout_a, layout_b, layout_cd))
+        return e;
+    return launch_gemm_tc05_i8_i8(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, layout_a, layout_b, layout_cd,
+                                  as_stream(stream));
 }
 
 extern "C" int b200wmma_gemm_fp8(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const float* c,
@@ -242,10 +264,13 @@ extern "C" int b200wmma_gemm_f32(uint32_t m, uint32_t n, uint32_t k, const float
     clear_error();
     if(int e = check_layouts("gemm_f32", layout_a, layout_b, layout_cd))
         return e;
-    B200_REQUIRE(layout_a == B200WMMA_ROW_MAJOR && layout_b == B200WMMA_COL_MAJOR && layout_cd == B200WMMA_ROW_MAJOR,
-                 B200WMMA_ERR_UNSUPPORTED, "gemm_f32: A row-major, B column-major, C/D row-major only");
-    return launch_gemm_tc05_f32(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, workspace, workspace_bytes,
-                                as_stream(stream));
+    const bool a_mn = layout_a == B200WMMA_COL_MAJOR, b_mn = layout_b == B200WMMA_ROW_MAJOR;
+    if(layout_cd == B200WMMA_ROW_MAJOR)
+        return launch_gemm_tc05_f32(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, workspace, workspace_bytes,
+                                    as_stream(stream), a_mn, b_mn);
+    // column-major C / D: the transposed problem D^T = alpha * B^T A^T + beta * C^T (B^T is K-contiguous exactly when B was)
+    return launch_gemm_tc05_f32(n, m, k, b, a, c, d, ldb, lda, ldc, ldd, alpha, beta, workspace, workspace_bytes,
+                                as_stream(stream), b_mn, a_mn);
 }
 
 extern "C" int b200wmma_gemm_i8(uint32_t m, uint32_t n, uint32_t k, const int8_t* a, const int8_t* b,

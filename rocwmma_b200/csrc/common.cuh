@@ -74,17 +74,22 @@ namespace b200wmma
                              size_t split_ws_bytes = 0);
     // bytes of scratch with which the 512 x 256 GEMM kernel may split the tiles of its last, partial round along K
     size_t gemm_split_workspace_bytes();
-    int launch_gemm_tc05_bf16(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const float* c, float* d,
+    int launch_gemm_tc05_bf16(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const void* c, void* d,
                               uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, float alpha, float beta, int layout_a,
-                              int layout_b, int layout_cd, cudaStream_t stream);
+                              int layout_b, int layout_cd, int out_type, cudaStream_t stream);
+    // int8 inputs, int32 compute, int8 C / D (the int32 result cast to int8)
+    int launch_gemm_tc05_i8_i8(uint32_t m, uint32_t n, uint32_t k, const int8_t* a, const int8_t* b, const int8_t* c, int8_t* d,
+                               uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha, int32_t beta, int layout_a,
+                               int layout_b, int layout_cd, cudaStream_t stream);
     int launch_gemm_tc05_fp8(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const float* c, float* d,
                              uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, float alpha, float beta, int layout_a,
                              int layout_b, int layout_cd, int fp8_format, cudaStream_t stream);
-    // fp32 inputs, 3 x TF32 on the tensor cores (A row major, B column major, C / D row major)
+    // fp32 inputs, 3 x TF32 on the tensor cores; C / D row major, a_mn / b_mn: operand stored with M / N contiguous
     size_t gemm_f32_workspace_bytes(uint32_t m, uint32_t n, uint32_t k);
     int    launch_gemm_tc05_f32(uint32_t m, uint32_t n, uint32_t k, const float* a, const float* b, const float* c, float* d,
                                 uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, float alpha, float beta,
-                                void* workspace, size_t workspace_bytes, cudaStream_t stream);
+                                void* workspace, size_t workspace_bytes, cudaStream_t stream, bool a_mn = false,
+                                bool b_mn = false);
     int launch_gemm_tc05_i8(uint32_t m, uint32_t n, uint32_t k, const int8_t* a,
                             const int8_t* b, const int32_t* c, int32_t* d, uint32_t lda,
                             uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha,

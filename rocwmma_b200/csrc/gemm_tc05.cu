@@ -290,7 +290,8 @@ namespace b200wmma
         {
             constexpr uint32_t EB = elem_bytes<KIND>();
             // bf16 and fp8 inputs run on the 512 x 256 pair kernel only
-            constexpr bool ONLY_Q = KIND != KIND_F16 && KIND != KIND_I8;
+            // ... and so do the extra output types (bf16 outputs, int8 outputs of the int8 GEMM)
+            constexpr bool ONLY_Q = (KIND != KIND_F16 && KIND != KIND_I8) || sizeof(OutT) == 1;
             B200_REQUIRE(m && n && k, B200WMMA_ERR_INVALID_ARG, "gemm: m, n, k must be non-zero");
             B200_REQUIRE(a && b && d, B200WMMA_ERR_INVALID_ARG, "gemm: a, b, d must be non-null");
             B200_REQUIRE(c || beta == ScalarT(0),
@@ -318,7 +319,9 @@ namespace b200wmma
                 return (reinterpret_cast<uintptr_t>(p) % bytes) == 0 && (static_cast<uint64_t>(ld) * es) % bytes == 0;
             };
             int vec_ok = 0;
-            if(row_align(d, ldd, sizeof(OutT), 32) && (!c || row_align(c, ldc, sizeof(OutT), 32)))
+            if(sizeof(OutT) == 1)
+                vec_ok = 0; // one-byte outputs: element-wise drain
+            else if(row_align(d, ldd, sizeof(OutT), 32) && (!c || row_align(c, ldc, sizeof(OutT), 32)))
                 vec_ok = 2;
             else if(row_align(d, ldd, sizeof(OutT), 16) && (!c || row_align(c, ldc, sizeof(OutT), 16)))
                 vec_ok = 1;
@@ -567,12 +570,27 @@ namespace b200wmma
         return set_error(B200WMMA_ERR_INVALID_ARG, "gemm_f16: out_type must be 0 (f16) or 1 (f32)");
     }
 
-    int launch_gemm_tc05_bf16(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const float* c, float* d,
+    int launch_gemm_tc05_bf16(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const void* c, void* d,
                               uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, float alpha, float beta, int layout_a,
-                              int layout_b, int layout_cd, cudaStream_t stream)
+                              int layout_b, int layout_cd, int out_type, cudaStream_t stream)
     {
-        return launch_any_layout<tc05::KIND_BF16, float, float>(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, layout_a,
-                                                                layout_b, layout_cd, stream);
+        if(out_type == B200WMMA_OUT_F32)
+            return launch_any_layout<tc05::KIND_BF16, float, float>(m, n, k, a, b, static_cast<const float*>(c),
+                                                                    static_cast<float*>(d), lda, ldb, ldc, ldd, alpha, beta,
+                                                                    layout_a, layout_b, layout_cd, stream);
+        if(out_type == B200WMMA_OUT_BF16)
+            return launch_any_layout<tc05::KIND_BF16, __nv_bfloat16, float>(m, n, k, a, b, static_cast<const __nv_bfloat16*>(c),
+                                                                            static_cast<__nv_bfloat16*>(d), lda, ldb, ldc, ldd,
+                                                                            alpha, beta, layout_a, layout_b, layout_cd, stream);
+        return set_error(B200WMMA_ERR_INVALID_ARG, "gemm_bf16: out_type must be B200WMMA_OUT_F32 or B200WMMA_OUT_BF16");
+    }
+
+    int launch_gemm_tc05_i8_i8(uint32_t m, uint32_t n, uint32_t k, const int8_t* a, const int8_t* b, const int8_t* c, int8_t* d,
+                               uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, int32_t alpha, int32_t beta, int layout_a,
+                               int layout_b, int layout_cd, cudaStream_t stream)
+    {
+        return launch_any_layout<tc05::KIND_I8, int8_t, int32_t>(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, layout_a,
+                                                                 layout_b, layout_cd, stream);
     }
 
     int launch_gemm_tc05_fp8(uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b, const float* c, float* d,

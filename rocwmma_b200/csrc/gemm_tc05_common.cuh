@@ -5,6 +5,7 @@
 #include "common.cuh"
 #include "ptx_sm100.cuh"
 
+#include <cuda_bf16.h>
 #include <type_traits>
 
 namespace b200wmma
@@ -105,6 +106,36 @@ namespace b200wmma
                                         + static_cast<uint32_t>(beta) * static_cast<uint32_t>(c));
         }
 
+        // Two 16-bit outputs in one 32-bit word: widening of a C word and rounding of a D pair, for fp16 and bf16.
+        template <typename T>
+        struct Pack16;
+        template <>
+        struct Pack16<__half>
+        {
+            __device__ static __forceinline__ float2 widen(uint32_t w)
+            {
+                return __half22float2(*reinterpret_cast<const __half2*>(&w));
+            }
+            __device__ static __forceinline__ uint32_t narrow(float x, float y)
+            {
+                const __half2 h = __floats2half2_rn(x, y);
+                return *reinterpret_cast<const uint32_t*>(&h);
+            }
+        };
+        template <>
+        struct Pack16<__nv_bfloat16>
+        {
+            __device__ static __forceinline__ float2 widen(uint32_t w)
+            {
+                return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+            }
+            __device__ static __forceinline__ uint32_t narrow(float x, float y)
+            {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+                return *reinterpret_cast<const uint32_t*>(&h);
+            }
+        };
+
         // 16- or 32-byte global accesses of VW 32-bit words.  C is read once and D written once,
         // so both use the streaming (evict-first) policy and leave L2 to the A / B slabs.
         template <int VW>
@@ -159,11 +190,10 @@ namespace b200wmma
                     const int w = g * VW + j;
                     if constexpr(EPW == 2)
                     {
-                        const float2 cf = __half22float2(*reinterpret_cast<const __half2*>(&cw[j]));
+                        const float2 cf = Pack16<OutT>::widen(cw[j]);
                         const float  x0 = epi(__uint_as_float(v[2 * w]), cf.x, alpha, beta);
                         const float  x1 = epi(__uint_as_float(v[2 * w + 1]), cf.y, alpha, beta);
-                        const __half2 h = __floats2half2_rn(x0, x1);
-                        ow[j]           = *reinterpret_cast<const uint32_t*>(&h);
+                        ow[j]           = Pack16<OutT>::narrow(x0, x1);
                     }
                     else if constexpr(std::is_same<OutT, float>::value)
                         ow[j] = __float_as_uint(epi(__uint_as_float(v[w]), __uint_as_float(cw[j]), alpha, beta));
@@ -188,9 +218,10 @@ namespace b200wmma
                                                            bool     read_c,
                                                            int      vec)
         {
-            if(ncols == 32 && vec == 2)
+            // (one-byte outputs always take the element-wise path)
+            if(sizeof(OutT) >= 2 && ncols == 32 && vec == 2)
                 epilogue_row_chunk_vec<OutT, ScalarT, 8>(v, c_row, d_row, alpha, beta, read_c);
-            else if(ncols == 32 && vec == 1)
+            else if(sizeof(OutT) >= 2 && ncols == 32 && vec == 1)
                 epilogue_row_chunk_vec<OutT, ScalarT, 4>(v, c_row, d_row, alpha, beta, read_c);
             else
             {
@@ -199,10 +230,12 @@ namespace b200wmma
                 {
                     if(static_cast<uint32_t>(j) < ncols)
                     {
-                        if constexpr(std::is_same<OutT, int32_t>::value)
+                        if constexpr(std::is_integral<OutT>::value)
                         {
-                            const int32_t cvv = read_c ? c_row[j] : 0;
-                            d_row[j] = epi(static_cast<int32_t>(v[j]), cvv, alpha, beta);
+                            // int32 compute; a narrower output type keeps the low bits, as the reference's
+                            // static_cast<OutputT> does (test/reference_impl.hpp:77-78)
+                            const int32_t cvv = read_c ? static_cast<int32_t>(c_row[j]) : 0;
+                            d_row[j] = static_cast<OutT>(epi(static_cast<int32_t>(v[j]), cvv, alpha, beta));
                         }
                         else
                         {

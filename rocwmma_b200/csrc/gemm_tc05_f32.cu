@@ -311,6 +311,48 @@ namespace b200wmma
             }
         }
 
+        // The same split for an operand whose M / N index is the contiguous one (element (row, kk) at src[kk * ld + row],
+        // a column-major A or a row-major B): 32 x 32 tiles are transposed through shared memory, so that reads and
+        // writes are both coalesced and the outputs are K-major like the other kernel's.
+        __global__ void __launch_bounds__(256)
+            split_tf32_transposed_kernel(const float* __restrict__ src, float* __restrict__ hi, float* __restrict__ lo, uint32_t rows,
+                                         uint32_t k, size_t ld)
+        {
+            __shared__ float th[32][33], tl[32][33];
+            const uint32_t   tx = threadIdx.x & 31u, ty = threadIdx.x >> 5; // 32 x 8
+            const uint32_t   tiles_r = (rows + 31u) / 32u, tiles_k = (k + 31u) / 32u;
+            for(uint32_t t = blockIdx.x; t < tiles_r * tiles_k; t += gridDim.x)
+            {
+                const uint32_t r0 = (t % tiles_r) * 32u, k0 = (t / tiles_r) * 32u;
+#pragma unroll
+                for(uint32_t i = 0; i < 4; ++i)
+                {
+                    const uint32_t kk = k0 + ty + 8u * i, r = r0 + tx;
+                    float          x  = 0.0f;
+                    if(kk < k && r < rows)
+                        x = __ldcs(src + static_cast<size_t>(kk) * ld + r);
+                    uint32_t hb, lb;
+                    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(x));
+                    const float h = __uint_as_float(hb);
+                    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lb) : "f"(x - h));
+                    th[ty + 8u * i][tx] = h;
+                    tl[ty + 8u * i][tx] = __uint_as_float(lb);
+                }
+                __syncthreads();
+#pragma unroll
+                for(uint32_t i = 0; i < 4; ++i)
+                {
+                    const uint32_t r = r0 + ty + 8u * i, kk = k0 + tx;
+                    if(r < rows && kk < k)
+                    {
+                        hi[static_cast<size_t>(r) * k + kk] = th[tx][ty + 8u * i];
+                        lo[static_cast<size_t>(r) * k + kk] = tl[tx][ty + 8u * i];
+                    }
+                }
+                __syncthreads();
+            }
+        }
+
         static size_t round256(size_t x)
         {
             return (x + 255) & ~static_cast<size_t>(255);
@@ -324,17 +366,20 @@ namespace b200wmma
 
     int launch_gemm_tc05_f32(uint32_t m, uint32_t n, uint32_t k, const float* a, const float* b, const float* c, float* d,
                              uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd, float alpha, float beta, void* workspace,
-                             size_t workspace_bytes, cudaStream_t stream)
+                             size_t workspace_bytes, cudaStream_t stream, bool a_mn, bool b_mn)
     {
+        // a_mn: A is column-major (element (i, h) at a[h * lda + i]); b_mn: B is row-major (element (h, j) at b[h * ldb + j]).
+        // Either way the split pre-pass leaves K-major hi / lo copies, so the GEMM kernel itself knows one layout only.
         using namespace tc05t;
         B200_REQUIRE(m && n && k, B200WMMA_ERR_INVALID_ARG, "gemm_f32: m, n, k must be non-zero");
         B200_REQUIRE(a && b && d && workspace, B200WMMA_ERR_INVALID_ARG, "gemm_f32: a, b, d, workspace must be non-null");
         B200_REQUIRE(c || beta == 0.0f, B200WMMA_ERR_INVALID_ARG, "gemm_f32: c may be null only when beta == 0");
-        B200_REQUIRE(lda >= k && ldb >= k && ldd >= n && (!c || ldc >= n), B200WMMA_ERR_INVALID_ARG,
-                     "gemm_f32: leading dimension smaller than the row it strides");
+        B200_REQUIRE(lda >= (a_mn ? m : k) && ldb >= (b_mn ? n : k) && ldd >= n && (!c || ldc >= n), B200WMMA_ERR_INVALID_ARG,
+                     "gemm_f32: leading dimension smaller than the row / column it strides");
         B200_REQUIRE(k % 4 == 0, B200WMMA_ERR_UNSUPPORTED, "gemm_f32: k must be a multiple of 4");
-        B200_REQUIRE(aligned16(a) && aligned16(b) && lda % 4 == 0 && ldb % 4 == 0 && aligned16(workspace), B200WMMA_ERR_ALIGNMENT,
-                     "gemm_f32: A / B rows and the workspace must be 16-byte aligned");
+        B200_REQUIRE((a_mn || (aligned16(a) && lda % 4 == 0)) && (b_mn || (aligned16(b) && ldb % 4 == 0)) && aligned16(workspace),
+                     B200WMMA_ERR_ALIGNMENT,
+                     "gemm_f32: the rows of an operand stored with K contiguous, and the workspace, must be 16-byte aligned");
         B200_REQUIRE(workspace_bytes >= gemm_f32_workspace_bytes(m, n, k), B200WMMA_ERR_INVALID_ARG,
                      "gemm_f32: workspace too small (%zu < %zu bytes)", workspace_bytes, gemm_f32_workspace_bytes(m, n, k));
         if(int e = require_sm100())
@@ -353,8 +398,15 @@ namespace b200wmma
             const size_t want = (units + 255) / 256;
             return static_cast<uint32_t>(want < 148u * 16u ? (want ? want : 1) : 148u * 16u);
         };
-        split_tf32_kernel<<<grid_for(static_cast<size_t>(m) * (k / 4)), 256, 0, stream>>>(a, a_hi, a_lo, m, k, lda);
-        split_tf32_kernel<<<grid_for(static_cast<size_t>(n) * (k / 4)), 256, 0, stream>>>(b, b_hi, b_lo, n, k, ldb);
+        const auto tiles32 = [](uint32_t rows, uint32_t kk) { return static_cast<size_t>((rows + 31) / 32) * ((kk + 31) / 32) * 256; };
+        if(a_mn)
+            split_tf32_transposed_kernel<<<grid_for(tiles32(m, k)), 256, 0, stream>>>(a, a_hi, a_lo, m, k, lda);
+        else
+            split_tf32_kernel<<<grid_for(static_cast<size_t>(m) * (k / 4)), 256, 0, stream>>>(a, a_hi, a_lo, m, k, lda);
+        if(b_mn)
+            split_tf32_transposed_kernel<<<grid_for(tiles32(n, k)), 256, 0, stream>>>(b, b_hi, b_lo, n, k, ldb);
+        else
+            split_tf32_kernel<<<grid_for(static_cast<size_t>(n) * (k / 4)), 256, 0, stream>>>(b, b_hi, b_lo, n, k, ldb);
         B200_CHECK_CUDA(cudaGetLastError());
 
         auto row_align = [](const void* p, uint32_t ld) {

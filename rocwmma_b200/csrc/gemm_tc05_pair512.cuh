@@ -171,6 +171,7 @@ namespace b200wmma
             static constexpr uint32_t BUF_BYTES = 32 * ROW_BYTES; // one staging tile: 32 rows
             static constexpr uint32_t CELLS     = ROW_BYTES / 16; // 16-byte cells per row
             static_assert(ROW_BYTES == 64 || (ROW_BYTES == 128 && sizeof(OutT) == 4), "staging rows: 64 bytes, or 128 for 32-bit outputs");
+            static_assert(sizeof(OutT) >= 2, "one-byte outputs are drained element-wise, not through staging tiles");
             static constexpr uint32_t STEP_COLS = ROW_BYTES / sizeof(OutT);
             static constexpr uint32_t STEPS     = TN / STEP_COLS; // of the whole accumulator
             static constexpr uint32_t MY_STEPS  = STEPS / STRIDE; // of one warp
@@ -315,9 +316,8 @@ namespace b200wmma
                             {
                                 if constexpr(sizeof(OutT) == 2)
                                 {
-                                    const float2  cf = __half22float2(*reinterpret_cast<const __half2*>(&cwv[w]));
-                                    const __half2 h  = __floats2half2_rn(one(v[8 * q + 2 * w], cf.x), one(v[8 * q + 2 * w + 1], cf.y));
-                                    ow[w]            = *reinterpret_cast<const uint32_t*>(&h);
+                                    const float2 cf = Pack16<OutT>::widen(cwv[w]);
+                                    ow[w] = Pack16<OutT>::narrow(one(v[8 * q + 2 * w], cf.x), one(v[8 * q + 2 * w + 1], cf.y));
                                 }
                                 else if constexpr(std::is_same<OutT, float>::value)
                                     ow[w] = __float_as_uint(one(v[4 * q + w], __uint_as_float(cwv[w])));
@@ -686,7 +686,9 @@ namespace b200wmma
                 const uint32_t buf1_off = alias_base_off + (j * 8u + (e & 3u) + 4u * first) * EPI_BUF_BYTES;
                 const uint32_t buf1     = base + buf1_off;
                 const uint32_t cbar0   = cbar_base + e * 16u;
-                using Drain            = StagedDrain<OutT, ScalarT, TILE_N, 2>;
+                // one-byte outputs have no staged path (the host passes vec_ok == 0 for them)
+                using StageT           = typename std::conditional<sizeof(OutT) >= 2, OutT, int32_t>::type;
+                using Drain            = StagedDrain<StageT, ScalarT, TILE_N, 2>;
                 // The eight warps of an accumulator wait for it together: one of them (the leader) watches the tmem_full
                 // barrier, the others park on a named hardware barrier and issue nothing meanwhile - sixteen warps polling
                 // through every tile's main loop were most of the kernel's instructions.  A warp that gives up (a bounded

@@ -35,6 +35,8 @@ GEMM_CASES = [
     ("f16_f32_nn_colout", 32, 16, 48, np.float16, np.float32, 0.5, -1.5, 0, 0, 1, 1),
     ("i8_i32_tn", 48, 64, 160, np.int8, np.int32, 1, 0, 0, 1, 0, 0),
     ("i8_i32_tn_ab", 32, 32, 64, np.int8, np.int32, 3, -2, 0, 1, 0, 0),
+    ("i8_i8_tn", 48, 64, 160, np.int8, np.int8, 1, 1, 0, 1, 0, 0),      # int8 outputs: the int32 result cast (wraps)
+    ("i8_i8_nt_ab", 32, 48, 64, np.int8, np.int8, 3, -2, 1, 0, 0, 0),
     ("f64_tn", 40, 56, 72, np.float64, np.float64, 1.5, 0.5, 0, 1, 0, 0),
     ("f32_tn", 24, 40, 56, np.float32, np.float32, 1.5, 0.5, 0, 1, 0, 0),
 ]
@@ -45,7 +47,7 @@ def gemm_inputs(case):
     name, m, n, k, it, ot, alpha, beta, la, lb, lc, ld = case
     if it == np.int8:
         a = G.int8_np(G.SEED_A, (m, k)); b = G.int8_np(G.SEED_B, (k, n))
-        c = (G.int8_np(G.SEED_C, (m, n)).astype(np.int32) * 1000)
+        c = G.int8_np(G.SEED_C, (m, n)) if ot == np.int8 else (G.int8_np(G.SEED_C, (m, n)).astype(np.int32) * 1000)
     else:
         a = G.uniform_np(G.SEED_A, (m, k), it); b = G.uniform_np(G.SEED_B, (k, n), it)
         c = G.uniform_np(G.SEED_C, (m, n), ot)

@@ -63,7 +63,7 @@ def test_no_cpu_fallback_in_product_sources():
     (lambda L: L.b200wmma_gemm_bf16(128, 128, 64, 16, 16, None, 16, 64, 64, 128, 128, 1.0, 0.0, 0, 3, 0, None), 1),
     (lambda L: L.b200wmma_gemm_fp8(128, 128, 64, 16, 16, None, 16, 60, 64, 128, 128, 1.0, 0.0, 0, 1, 0, 0, None), 1),
     (lambda L: L.b200wmma_gemm_fp8(128, 128, 64, 16, 16, None, 16, 64, 64, 128, 128, 1.0, 0.0, 0, 1, 0, 7, None), 1),
-    (lambda L: L.b200wmma_gemm_f32(128, 128, 64, 16, 16, None, 16, 64, 64, 128, 128, 1.0, 0.0, 1, 1, 0, 16, 1 << 30, None), 2),
+    (lambda L: L.b200wmma_gemm_f32(128, 128, 64, 16, 16, None, 16, 64, 64, 128, 128, 1.0, 0.0, 1, 1, 0, 16, 1 << 30, None), 1),
     (lambda L: L.b200wmma_gemm_f32(128, 128, 64, 16, 16, None, 16, 64, 64, 128, 128, 1.0, 0.0, 0, 1, 0, 16, 1024, None), 1),
     (lambda L: L.b200wmma_gemm_f32(128, 128, 62, 16, 16, None, 16, 64, 64, 128, 128, 1.0, 0.0, 0, 1, 0, 16, 1 << 30, None), 2),
     (lambda L: L.b200wmma_sp24_repack_meta(256, 192, 16, 32, 16, 1 << 20, None), 2),
@@ -84,7 +84,7 @@ def test_no_cpu_fallback_in_product_sources():
 ], ids=["bad_layout_flag", "col_major_a_lda_lt_m", "zero_m", "null_c_with_beta", "lda_too_small",
         "lda_not_16B", "f64_odd_k", "gemv_zero_m", "gemv_lda_small", "dlrm_rows_beyond_stride", "dlrm_k_not_16",
         "dlrm_out_stride_small", "dlrm_bwd_null_upstream", "sp24_k_not_32", "i4_k_not_32", "ctx_null",
-        "bf16_bad_layout_flag", "fp8_lda_too_small", "fp8_bad_format", "f32_layout_unsupported", "f32_workspace_small",
+        "bf16_bad_layout_flag", "fp8_lda_too_small", "fp8_bad_format", "f32_col_major_a_lda_lt_m", "f32_workspace_small",
         "f32_k_not_4", "repack_k_not_128", "repack_dest_small", "sp24_packed_k_not_128", "sp24_packed_null_meta",
         "simple_sgemm_m_not_16", "simple_dgemm_null_c", "mg_id_null", "mg_create_null", "mg_broadcast_null_handle",
         "mg_allgather_null_handle", "tuning_unknown_key", "tuning_out_of_range", "stage_ms_null",

@@ -116,6 +116,10 @@ def test_gemm_reference_fixtures():
             bound = R.gemm_abs_bound(m, n, k, a, b, c, alpha, beta)
             bound = np.ascontiguousarray(bound.T if lc else bound).ravel()
             assert gemm_rel_err(d.cpu().numpy().ravel(), ref, bound) <= (TOL_F16_OUT if ot == np.float16 else TOL_F32_OUT), name
+        elif it == np.int8 and ot == np.int8:
+            d = nan_filled(shape, torch.int8)
+            api.gemm_i8_i8(m, n, k, dev(sa), dev(sb), dev(sc), d, lda, ldb, ldcd, ldcd, alpha, beta, la, lb, lc)
+            assert np.array_equal(d.cpu().numpy().ravel(), ref), name
         elif it == np.int8:
             d = nan_filled(shape, torch.int32)
             api.gemm_i8(m, n, k, dev(sa), dev(sb), dev(sc), d, lda, ldb, ldcd, ldcd, alpha, beta, la, lb, lc)
@@ -177,6 +181,75 @@ def test_gemm_f32_three_tf32(m, n, k, alpha, beta):
     ref = oracle_gemm_rows(a, bs, c if beta else None, alpha, beta, np.float32, n, k)
     bound = R.gemm_abs_bound(m, n, k, a, b, c if beta else np.zeros_like(c), alpha, beta)
     assert gemm_rel_err(d.cpu().numpy(), ref, bound) <= TOL_F32X3
+
+
+@pytest.mark.parametrize("la,lb,lcd", LAYOUTS, ids=["".join("RC"[x] for x in t) for t in LAYOUTS])
+@pytest.mark.parametrize("m,n,k", [(512, 256, 128), (301, 203, 100)])
+def test_gemm_f32_all_layouts(la, lb, lcd, m, n, k):
+    """fp32 GEMM in every layout combination (the split pre-pass absorbs column-major A / row-major B; column-major
+    C / D is the transposed problem), ragged extents included, at the fp32-class tolerance."""
+    a = G.uniform_np(G.SEED_A, (m, k), np.float32); b = G.uniform_np(G.SEED_B, (k, n), np.float32)
+    c = G.uniform_np(G.SEED_C, (m, n), np.float32)
+    def store(x, col, mult):   # natural storage, pitch rounded up to `mult` elements
+        t = np.ascontiguousarray(x.T if col else x)
+        ld = (t.shape[1] + mult - 1) // mult * mult
+        out = np.full((t.shape[0], ld), np.nan, np.float32)
+        out[:, :t.shape[1]] = t
+        return out, ld
+    (sa, lda), (sb, ldb), (sc, ldc) = store(a, la, 4), store(b, lb, 4), store(c, lcd, 1)
+    ws = torch.empty(api.gemm_f32_workspace_bytes(m, n, k), dtype=torch.uint8, device="cuda")
+    d = nan_filled(sc.shape, torch.float32)
+    api.gemm_f32(m, n, k, dev(sa), dev(sb), dev(sc), d, lda, ldb, ldc, ldc, 1.5, 0.5, ws, la, lb, lcd)
+    assert_status_ok()
+    nat = lambda x, col: np.ascontiguousarray(x.T if col else x)
+    ref = R.gemm(R.port(), m, n, k, nat(a, la).ravel(), nat(b, lb).ravel(), nat(c, lcd).ravel(), 1.5, 0.5, np.float32,
+                 la, lb, lcd, lcd).reshape(nat(c, lcd).shape)
+    bound = nat(R.gemm_abs_bound(m, n, k, a, b, c, 1.5, 0.5), lcd)
+    assert gemm_rel_err(d.cpu().numpy()[:, :ref.shape[1]], ref, bound) <= TOL_F32X3
+
+
+@pytest.mark.parametrize("la,lb,lcd", [(0, 1, 0), (1, 0, 0), (0, 0, 1), (1, 1, 1)], ids=["RCR", "CRR", "RRC", "CCC"])
+@pytest.mark.parametrize("m,n,k,alpha,beta", [(512, 256, 256, 1, 0), (608, 336, 208, 3, -2), (144, 80, 96, 1, 1)])
+def test_gemm_i8_int8_outputs(la, lb, lcd, m, n, k, alpha, beta):
+    """The reference's <int8_t, int8_t, int32_t> set (test/gemm/gemm_common_test_params.hpp:53): int32 compute, the
+    result cast to int8 as gemm_CPU's static_cast does.  Bit-exact against the oracle in the same layouts."""
+    lda, ldb, ldcd = _lds(m, n, k, la, lb, lcd)
+    store = lambda x, col: np.ascontiguousarray(x.T if col else x)
+    a = G.int8_np(G.SEED_A, (m, k)); b = G.int8_np(G.SEED_B, (k, n)); c = G.int8_np(G.SEED_C, (m, n))
+    sa, sb, sc = store(a, la), store(b, lb), store(c, lcd)
+    d = nan_filled(sc.shape, torch.int8)
+    api.gemm_i8_i8(m, n, k, dev(sa), dev(sb), dev(sc) if beta else None, d, lda, ldb, ldcd, ldcd, alpha, beta, la, lb, lcd)
+    assert_status_ok()
+    ref = R.gemm(R.port(), m, n, k, sa.ravel(), sb.ravel(), sc.ravel() if beta else None, alpha, beta, np.int8, la, lb, lcd, lcd)
+    assert np.array_equal(d.cpu().numpy().ravel(), ref)
+
+
+TOL_BF16_OUT = 4e-3   # bf16 keeps 8 significant bits: one rounding of the result is up to 2^-9 of its magnitude
+
+
+@pytest.mark.parametrize("la,lb,lcd", [(0, 1, 0), (1, 0, 0), (0, 0, 1), (1, 1, 1)], ids=["RCR", "CRR", "RRC", "CCC"])
+@pytest.mark.parametrize("m,n,k", [(512, 256, 256), (608, 336, 208), (80, 1104, 272)])
+def test_gemm_bf16_bf16_outputs(la, lb, lcd, m, n, k):
+    """The reference's <bfloat16_t, bfloat16_t, float32_t> set (test/gemm/gemm_common_test_params.hpp:89-94): bf16 C and
+    D, fp32 compute.  The reference build here has no bfloat16 type, so the oracle is gemm_CPU's fp32 arithmetic on the
+    exactly widened inputs, with its final cast to bf16 applied by torch (round to nearest even, like the type's own)."""
+    lda, ldb, ldcd = _lds(m, n, k, la, lb, lcd)
+    store = lambda x, col: np.ascontiguousarray(x.T if col else x)
+    bf = torch.bfloat16
+    ta = torch.from_numpy(G.uniform_np(1, (m, k), np.float32)).to(bf)
+    tb = torch.from_numpy(G.uniform_np(2, (k, n), np.float32)).to(bf)
+    tc = torch.from_numpy(G.uniform_np(3, (m, n), np.float32)).to(bf)
+    a, b, c = (t.to(torch.float32).numpy() for t in (ta, tb, tc))
+    lay = lambda tt, col: (tt.t().contiguous() if col else tt.contiguous()).cuda()
+    dc = lay(tc, lcd)
+    d = torch.full(dc.shape, float("nan"), dtype=bf, device="cuda")
+    api.gemm_bf16(m, n, k, lay(ta, la), lay(tb, lb), dc, d, lda, ldb, ldcd, ldcd, 2.0, 0.5, la, lb, lcd)
+    assert_status_ok()
+    ref32 = R.gemm(R.port(), m, n, k, store(a, la).ravel(), store(b, lb).ravel(), store(c, lcd).ravel(), 2.0, 0.5, np.float32,
+                   la, lb, lcd, lcd)
+    ref = torch.from_numpy(ref32).to(bf).to(torch.float32).numpy()
+    bound = store(R.gemm_abs_bound(m, n, k, a, b, c, 2.0, 0.5), lcd).ravel()
+    assert gemm_rel_err(d.to(torch.float32).cpu().numpy().ravel(), ref, bound) <= TOL_BF16_OUT
 
 
 _LOWP = {"bf16": torch.bfloat16, "e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
