@@ -342,6 +342,9 @@ int b200wmma_gemv_f64(uint32_t m, uint32_t n, const double* a, uint32_t lda, int
  * A b200wmma_ctx caches the device buffers (grown on demand) and one stream, so repeated
  * calls do not allocate.  All pointers in *_host calls are host pointers; pinned host
  * memory gives the fastest copies but pageable memory works.
+ * The GEMM drivers take every layout combination: with a row-major A, C and D (either layout of B) the copies and the
+ * kernels are pipelined over chunks of rows; with a column-major A or C / D, whose row chunks are not contiguous, the
+ * whole matrices go up, one GEMM runs and D comes back.
  * ------------------------------------------------------------------------------------------ */
 typedef struct b200wmma_ctx b200wmma_ctx;
 int b200wmma_ctx_create(b200wmma_ctx** out_ctx);

@@ -298,9 +298,10 @@ class HostContext:
         check(lib().b200wmma_ctx_last_stage_ms(self._h, out))
         return dict(zip(("upload", "exchange", "compute", "download", "total"), (float(x) for x in out)))
 
-    def gemm_f16(self, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, out_type):
+    def gemm_f16(self, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, out_type,
+                 layout_a=ROW_MAJOR, layout_b=COL_MAJOR, layout_cd=ROW_MAJOR):
         check(lib().b200wmma_gemm_f16_host(self._h, m, n, k, self._hp(a), self._hp(b), self._hp(c), self._hp(d),
-                                           lda, ldb, ldc, ldd, alpha, beta, ROW_MAJOR, COL_MAJOR, ROW_MAJOR, out_type))
+                                           lda, ldb, ldc, ldd, alpha, beta, layout_a, layout_b, layout_cd, out_type))
 
     def gemm_f16_mg(self, mg, root, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta, out_type):
         """Column-sharded form: n, b, c, d are this rank's block; only rank `root` reads `a` (may be None elsewhere);
@@ -313,9 +314,10 @@ class HostContext:
         check(lib().b200wmma_gemm_i8_host_mg(self._h, mg._h, root, m, n, k, self._hp(a), self._hp(b), self._hp(c),
                                              self._hp(d), lda, ldb, ldc, ldd, alpha, beta))
 
-    def gemm_i8(self, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta):
+    def gemm_i8(self, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta,
+                layout_a=ROW_MAJOR, layout_b=COL_MAJOR, layout_cd=ROW_MAJOR):
         check(lib().b200wmma_gemm_i8_host(self._h, m, n, k, self._hp(a), self._hp(b), self._hp(c), self._hp(d),
-                                          lda, ldb, ldc, ldd, alpha, beta, ROW_MAJOR, COL_MAJOR, ROW_MAJOR))
+                                          lda, ldb, ldc, ldd, alpha, beta, layout_a, layout_b, layout_cd))
 
     def dlrm_fwd(self, input, output, m, m_stride, k, batch, out_stride):
         check(lib().b200wmma_dlrm_fwd_host(self._h, self._hp(input), self._hp(output), m, m_stride, k, batch, out_stride))

@@ -288,6 +288,20 @@ extern "C" int b200wmma_gemm_i8(uint32_t m, uint32_t n, uint32_t k, const int8_t
 // ---------------------------------------------------------------------------------------------
 // Host-buffer drivers
 // ---------------------------------------------------------------------------------------------
+// A failed call inside a host driver, after copies from / to the caller's buffers may already be queued: drain the
+// stream first, so that nothing of the call is still in flight when the error is returned.
+#define HOST_CHECK_CUDA(ctx, expr)                                                                          \
+    do                                                                                                      \
+    {                                                                                                       \
+        cudaError_t _e = (expr);                                                                            \
+        if(_e != cudaSuccess)                                                                               \
+        {                                                                                                   \
+            cudaStreamSynchronize((ctx)->stream);                                                           \
+            return ::b200wmma::set_error(B200WMMA_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                 \
+                                         cudaGetErrorString(_e), __FILE__, __LINE__);                       \
+        }                                                                                                   \
+    } while(0)
+
 struct b200wmma_ctx
 {
     static constexpr int NBUF = 5; // A, B, C, D, split-K scratch of the GEMM kernel
@@ -377,8 +391,12 @@ namespace
     template <typename Launch>
     int gemm_host_pipeline(b200wmma_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b,
                            const void* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
-                           size_t in_es, size_t out_es, bool use_c, Launch launch, b200wmma_mg* mg = nullptr, int root = 0)
+                           size_t in_es, size_t out_es, bool use_c, Launch launch, b200wmma_mg* mg = nullptr, int root = 0,
+                           uint32_t b_outer = 0, uint32_t b_inner = 0)
     {
+        // b_outer x b_inner: the stored shape of B when it is not the column-major n x k (a row-major B is k x n)
+        if(b_outer == 0)
+            b_outer = n, b_inner = k;
         const int my_rank = mg ? b200wmma_mg_rank(mg) : 0, nranks = mg ? b200wmma_mg_size(mg) : 1;
         // ---- checks that precede any queued work (the kernels' own launch checks repeat some of these) ----
         B200_REQUIRE((static_cast<uint64_t>(lda) * in_es) % 16 == 0 && (static_cast<uint64_t>(ldb) * in_es) % 16 == 0,
@@ -406,7 +424,7 @@ namespace
         const uint32_t chunks = (m + chunk_rows - 1) / chunk_rows;
         // A on the device is sized in whole chunks: the last all-gather may move (never-read) rows past m
         const size_t ba = mg && nranks > 1 ? static_cast<size_t>(chunks) * chunk_rows * lda * in_es : extent(m, k, lda) * in_es;
-        const size_t bb = extent(n, k, ldb) * in_es;
+        const size_t bb = extent(b_outer, b_inner, ldb) * in_es;
         const size_t bc = extent(m, n, ldc) * out_es, bd = extent(m, n, ldd) * out_es;
         if(int e = ctx_reserve(ctx, 0, ba)) return e;
         if(int e = ctx_reserve(ctx, 1, bb)) return e;
@@ -547,6 +565,37 @@ namespace
     }
 }
 
+namespace
+{
+    // Host-buffer GEMM for the layouts in which a chunk of rows is not contiguous in every matrix (column-major A, C or D):
+    // all of A, B and C go up, one GEMM runs, D comes back.  `launch(a_dev, b_dev, c_dev, d_dev)` enqueues the GEMM.
+    // ea, eb, ec, ed: element counts of the stored matrices.
+    template <typename Launch>
+    int gemm_host_whole(b200wmma_ctx* ctx, const void* a, const void* b, const void* c, void* d, size_t ba, size_t bb, size_t bc,
+                        size_t bd, bool use_c, Launch launch)
+    {
+        if(int e = require_sm100())
+            return e;
+        if(int e = ctx_reserve(ctx, 0, ba)) return e;
+        if(int e = ctx_reserve(ctx, 1, bb)) return e;
+        if(int e = ctx_reserve(ctx, 2, use_c ? bc : 16)) return e;
+        if(int e = ctx_reserve(ctx, 3, bd)) return e;
+        if(int e = ctx_reserve(ctx, 4, gemm_split_workspace_bytes())) return e;
+        ctx->stage_valid = false;
+        HOST_CHECK_CUDA(ctx, cudaMemcpyAsync(ctx->buf[0], a, ba, cudaMemcpyHostToDevice, ctx->stream));
+        HOST_CHECK_CUDA(ctx, cudaMemcpyAsync(ctx->buf[1], b, bb, cudaMemcpyHostToDevice, ctx->stream));
+        if(use_c)
+            HOST_CHECK_CUDA(ctx, cudaMemcpyAsync(ctx->buf[2], c, bc, cudaMemcpyHostToDevice, ctx->stream));
+        if(int e = launch(ctx->buf[0], ctx->buf[1], use_c ? ctx->buf[2] : nullptr, ctx->buf[3]))
+        {
+            cudaStreamSynchronize(ctx->stream);
+            return e;
+        }
+        HOST_CHECK_CUDA(ctx, cudaMemcpyAsync(d, ctx->buf[3], bd, cudaMemcpyDeviceToHost, ctx->stream));
+        return finish(ctx);
+    }
+}
+
 extern "C" int b200wmma_ctx_last_stage_ms(b200wmma_ctx* ctx, float* out_ms5)
 {
     clear_error();
@@ -618,22 +667,30 @@ extern "C" int b200wmma_gemm_f16_host(b200wmma_ctx* ctx, uint32_t m, uint32_t n,
         return e;
     if(int e = check_layouts("gemm_f16_host", layout_a, layout_b, layout_cd))
         return e;
-    B200_REQUIRE(layout_a == B200WMMA_ROW_MAJOR && layout_b == B200WMMA_COL_MAJOR && layout_cd == B200WMMA_ROW_MAJOR,
-                 B200WMMA_ERR_UNSUPPORTED,
-                 "gemm_f16_host: the row-block pipeline needs A row-major, B column-major, C/D row-major");
     B200_REQUIRE(a && b && d && m && n && k, B200WMMA_ERR_INVALID_ARG, "gemm_f16_host: null pointer or zero size");
     B200_REQUIRE(out_type == 0 || out_type == 1, B200WMMA_ERR_INVALID_ARG, "gemm_f16_host: bad out_type");
-    B200_REQUIRE(lda >= k && ldb >= k && ldd >= n && ldc >= n, B200WMMA_ERR_INVALID_ARG,
-                 "gemm_f16_host: leading dimension too small");
     const size_t osz   = out_type == B200WMMA_OUT_F16 ? 2 : 4;
     const bool   use_c = c != nullptr && beta != 0.0f;
     B200_REQUIRE(c || beta == 0.0f, B200WMMA_ERR_INVALID_ARG, "gemm_f16_host: c may be null only when beta == 0");
+    const bool a_col = layout_a == B200WMMA_COL_MAJOR, b_col = layout_b == B200WMMA_COL_MAJOR, cd_col = layout_cd == B200WMMA_COL_MAJOR;
+    B200_REQUIRE(lda >= (a_col ? m : k) && ldb >= (b_col ? k : n) && ldd >= (cd_col ? m : n) && (!c || ldc >= (cd_col ? m : n)),
+                 B200WMMA_ERR_INVALID_ARG, "gemm_f16_host: leading dimension too small");
+    if(a_col || cd_col)
+        // a chunk of rows is not contiguous in these layouts: whole matrices up, one GEMM, D back
+        return gemm_host_whole(ctx, a, b, c, d, extent(a_col ? k : m, a_col ? m : k, lda) * 2, extent(b_col ? n : k, b_col ? k : n, ldb) * 2,
+                               extent(cd_col ? n : m, cd_col ? m : n, ldc) * osz, extent(cd_col ? n : m, cd_col ? m : n, ldd) * osz, use_c,
+                               [&](const void* da, const void* db, const void* dc, void* dd) {
+                                   return launch_gemm_tc05_f16(m, n, k, da, db, dc, dd, lda, ldb, ldc, ldd, alpha, use_c ? beta : 0.0f,
+                                                               layout_a, layout_b, layout_cd, out_type, ctx->stream, ctx->buf[4],
+                                                               ctx->cap[4]);
+                               });
     return gemm_host_pipeline(ctx, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, 2, osz, use_c,
                               [&](uint32_t rows, const void* da, const void* dc, void* dd) {
                                   return launch_gemm_tc05_f16(rows, n, k, da, ctx->buf[1], dc, dd, lda, ldb, ldc, ldd, alpha,
-                                                              use_c ? beta : 0.0f, B200WMMA_ROW_MAJOR, B200WMMA_COL_MAJOR,
+                                                              use_c ? beta : 0.0f, B200WMMA_ROW_MAJOR, layout_b,
                                                               B200WMMA_ROW_MAJOR, out_type, ctx->stream, ctx->buf[4], ctx->cap[4]);
-                              });
+                              },
+                              nullptr, 0, b_col ? n : k, b_col ? k : n);
 }
 
 extern "C" int b200wmma_gemm_f16_host_mg(b200wmma_ctx* ctx, b200wmma_mg* mg, int root, uint32_t m, uint32_t n, uint32_t k,
@@ -674,23 +731,31 @@ extern "C" int b200wmma_gemm_i8_host(b200wmma_ctx* ctx, uint32_t m, uint32_t n, 
         return e;
     if(int e = check_layouts("gemm_i8_host", layout_a, layout_b, layout_cd))
         return e;
-    B200_REQUIRE(layout_a == B200WMMA_ROW_MAJOR && layout_b == B200WMMA_COL_MAJOR && layout_cd == B200WMMA_ROW_MAJOR,
-                 B200WMMA_ERR_UNSUPPORTED,
-                 "gemm_i8_host: the row-block pipeline needs A row-major, B column-major, C/D row-major");
     B200_REQUIRE(a && b && d && m && n && k, B200WMMA_ERR_INVALID_ARG, "gemm_i8_host: null pointer or zero size");
-    B200_REQUIRE(lda >= k && ldb >= k && ldd >= n && ldc >= n, B200WMMA_ERR_INVALID_ARG,
-                 "gemm_i8_host: leading dimension too small");
     const bool use_c = c != nullptr && beta != 0;
     B200_REQUIRE(c || beta == 0, B200WMMA_ERR_INVALID_ARG, "gemm_i8_host: c may be null only when beta == 0");
+    const bool a_col = layout_a == B200WMMA_COL_MAJOR, b_col = layout_b == B200WMMA_COL_MAJOR, cd_col = layout_cd == B200WMMA_COL_MAJOR;
+    B200_REQUIRE(lda >= (a_col ? m : k) && ldb >= (b_col ? k : n) && ldd >= (cd_col ? m : n) && (!c || ldc >= (cd_col ? m : n)),
+                 B200WMMA_ERR_INVALID_ARG, "gemm_i8_host: leading dimension too small");
+    if(a_col || cd_col)
+        return gemm_host_whole(ctx, a, b, c, d, extent(a_col ? k : m, a_col ? m : k, lda), extent(b_col ? n : k, b_col ? k : n, ldb),
+                               extent(cd_col ? n : m, cd_col ? m : n, ldc) * 4, extent(cd_col ? n : m, cd_col ? m : n, ldd) * 4, use_c,
+                               [&](const void* da, const void* db, const void* dc, void* dd) {
+                                   return launch_gemm_tc05_i8(m, n, k, static_cast<const int8_t*>(da), static_cast<const int8_t*>(db),
+                                                              static_cast<const int32_t*>(dc), static_cast<int32_t*>(dd), lda, ldb, ldc,
+                                                              ldd, alpha, use_c ? beta : 0, layout_a, layout_b, layout_cd, ctx->stream,
+                                                              ctx->buf[4], ctx->cap[4]);
+                               });
     return gemm_host_pipeline(ctx, m, n, k, a, b, c, d, lda, ldb, ldc, ldd, 1, 4, use_c,
                               [&](uint32_t rows, const void* da, const void* dc, void* dd) {
                                   return launch_gemm_tc05_i8(rows, n, k, static_cast<const int8_t*>(da),
                                                              static_cast<const int8_t*>(ctx->buf[1]),
                                                              static_cast<const int32_t*>(dc), static_cast<int32_t*>(dd), lda,
                                                              ldb, ldc, ldd, alpha, use_c ? beta : 0, B200WMMA_ROW_MAJOR,
-                                                             B200WMMA_COL_MAJOR, B200WMMA_ROW_MAJOR, ctx->stream, ctx->buf[4],
+                                                             layout_b, B200WMMA_ROW_MAJOR, ctx->stream, ctx->buf[4],
                                                              ctx->cap[4]);
-                              });
+                              },
+                              nullptr, 0, b_col ? n : k, b_col ? k : n);
 }
 
 extern "C" int b200wmma_gemm_i8_host_mg(b200wmma_ctx* ctx, b200wmma_mg* mg, int root, uint32_t m, uint32_t n, uint32_t k,
@@ -719,20 +784,6 @@ extern "C" int b200wmma_gemm_i8_host_mg(b200wmma_ctx* ctx, b200wmma_mg* mg, int 
         },
         mg, root);
 }
-
-// A failed call inside a host driver, after copies from / to the caller's buffers may already be queued: drain the
-// stream first, so that nothing of the call is still in flight when the error is returned.
-#define HOST_CHECK_CUDA(ctx, expr)                                                                          \
-    do                                                                                                      \
-    {                                                                                                       \
-        cudaError_t _e = (expr);                                                                            \
-        if(_e != cudaSuccess)                                                                               \
-        {                                                                                                   \
-            cudaStreamSynchronize((ctx)->stream);                                                           \
-            return ::b200wmma::set_error(B200WMMA_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                 \
-                                         cudaGetErrorString(_e), __FILE__, __LINE__);                       \
-        }                                                                                                   \
-    } while(0)
 
 extern "C" int b200wmma_dlrm_fwd_host(b200wmma_ctx* ctx, const void* input, void* output, uint32_t m,
                                       uint32_t m_stride, uint32_t k, uint32_t batch, uint32_t out_stride)

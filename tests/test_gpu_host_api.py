@@ -34,6 +34,30 @@ def test_gemm_f16_host_row_block_pipeline(ctx, m, n, k, out_np, beta):
         assert gemm_rel_err(d, ref, bound) <= (TOL_F16_OUT if out_np == np.float16 else TOL_F32_OUT)
 
 
+_HOST_LAYOUTS = [(la, lb, lcd) for la in (0, 1) for lb in (0, 1) for lcd in (0, 1)]
+
+
+@pytest.mark.parametrize("la,lb,lcd", _HOST_LAYOUTS, ids=["".join("RC"[x] for x in t) for t in _HOST_LAYOUTS])
+def test_gemm_host_all_layouts(ctx, la, lb, lcd):
+    """Every layout combination through the host-buffer drivers (the reference's NN / NT / TN / TT sweep): row-major
+    A / C / D are pipelined over row chunks (m spans several), the other layouts go whole; fp16 and int8."""
+    m, n, k = 2304, 320, 256
+    store = lambda x, col: np.ascontiguousarray(x.T if col else x)
+    lda, ldb, ldcd = (m if la else k), (k if lb else n), (m if lcd else n)
+    a = G.uniform_np(1, (m, k), np.float16); b = G.uniform_np(2, (k, n), np.float16); c = G.uniform_np(3, (m, n), np.float16)
+    sa, sb, sc = store(a, la), store(b, lb), store(c, lcd)
+    d = np.full(sc.shape, np.nan, np.float16)
+    ctx.gemm_f16(m, n, k, sa, sb, sc, d, lda, ldb, ldcd, ldcd, 1.5, 0.5, 0, la, lb, lcd)
+    ref = R.gemm(R.port(), m, n, k, sa.ravel(), sb.ravel(), sc.ravel(), 1.5, 0.5, np.float16, la, lb, lcd, lcd)
+    bound = store(R.gemm_abs_bound(m, n, k, a, b, c, 1.5, 0.5), lcd).ravel()
+    assert gemm_rel_err(d.ravel(), ref, bound) <= TOL_F16_OUT
+    ai = G.int8_np(1, (m, k)); bi = G.int8_np(2, (k, n)); ci = G.int8_np(3, (m, n)).astype(np.int32) * 77
+    sa, sb, sc = store(ai, la), store(bi, lb), store(ci, lcd)
+    di = np.zeros(sc.shape, np.int32)
+    ctx.gemm_i8(m, n, k, sa, sb, sc, di, lda, ldb, ldcd, ldcd, 2, -1, la, lb, lcd)
+    assert np.array_equal(di.ravel(), R.gemm(R.port(), m, n, k, sa.ravel(), sb.ravel(), sc.ravel(), 2, -1, np.int32, la, lb, lcd, lcd))
+
+
 def test_gemm_f16_host_in_place(ctx):
     m, n, k = 2100, 256, 128
     a = G.uniform_np(1, (m, k), np.float16); b = G.uniform_np(2, (k, n), np.float16); c = G.uniform_np(3, (m, n), np.float16)
@@ -76,12 +100,14 @@ def test_dlrm_and_gemv_host(ctx):
         assert np.max(np.abs(y.astype(np.float64) - ref) / bound) <= tol
 
 
-def test_host_driver_rejects_other_layouts(ctx):
-    """The row-block pipeline of the host drivers is defined for A row-major / B column-major / C,D row-major only."""
+def test_host_driver_rejects_bad_layout_flags_and_pitches(ctx):
+    """Layout flags outside {0, 1} and a leading dimension smaller than the column it strides are argument errors."""
     from rocwmma_b200 import _lib
     import ctypes as C
     L = _lib.lib()
     a = np.zeros((128, 64), np.float16); d = np.zeros((128, 128), np.float16)
     p = lambda x: C.c_void_p(x.ctypes.data)
-    rc = L.b200wmma_gemm_f16_host(ctx._h, 128, 128, 64, p(a), p(a), None, p(d), 128, 64, 128, 128, 1.0, 0.0, 1, 1, 0, 0)
-    assert rc == 2 and b"row-block pipeline" in L.b200wmma_last_error_string()
+    assert L.b200wmma_gemm_f16_host(ctx._h, 128, 128, 64, p(a), p(a), None, p(d), 128, 64, 128, 128, 1.0, 0.0, 2, 1, 0, 0) == 1
+    # column-major A needs lda >= m
+    assert L.b200wmma_gemm_f16_host(ctx._h, 128, 128, 64, p(a), p(a), None, p(d), 64, 64, 128, 128, 1.0, 0.0, 1, 1, 0, 0) == 1
+    assert b"leading dimension" in L.b200wmma_last_error_string()
