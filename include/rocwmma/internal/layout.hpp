@@ -15,13 +15,17 @@
 // mma.sync instructions, so that mma_sync needs no shuffles:
 //   element size   A atom (M x K)   instruction            per-lane elements
 //   1 byte         16 x 16          m16n8k16 (s8)          (row g + 8*(i>>2),      col 4t + (i&3))
+//                  16 x 8           m16n8k8 on fp16 copies (row g + 8*(i>>1),      col 2t + (i&1))   [int8, BlockK = 8]
 //   2 bytes        16 x 16          m16n8k16 (f16, bf16)   (row g + 8*((i>>1)&1),  col 2t + (i&1) + 8*(i>>2))
 //                  16 x 8           m16n8k8  (f16, bf16)   (row g + 8*(i>>1),      col 2t + (i&1))
 //   4 bytes        16 x 8           m16n8k8  (tf32)        (row g + 8*(i&1),       col t + 4*(i>>1))
 //                  16 x 4           m16n8k4  (tf32)        (row g + 8*i,           col t)
+//                  16 x 2           shuffles + FMA         (row lane / 2,          col lane % 2)     [fp32, BlockK = 2]
 //   8 bytes        16 x 4           m16n8k4  (f64)         (row g + 8*i,           col t)
 // with g = lane / 4, t = lane % 4.  The deeper atom is used when BlockK is a multiple of it, the
-// shallower one otherwise (BlockK = 8 for 16-bit types, 4 for fp32: the reference's minimum K).  B atoms are the transposes (k takes the role of col, n of
+// shallower one otherwise (BlockK = 8 for 8- and 16-bit types, 4 and 2 for fp32: the reference's minimum K of 32 x 32
+// blocks, docs/api-reference/api-reference-guide.rst:100-146; there is no 8-deep int8 or 2-deep fp32 mma.sync shape, so
+// those two multiply through exact fp16 copies on m16n8k8 resp. through shuffles and FMAs).  B atoms are the transposes (k takes the role of col, n of
 // row).  Accumulator atoms are 16 x 16 = two m16n8 result tiles:
 //   (row g + 8*((i>>1)&1), col 2t + (i&1) + 8*(i>>2)).
 #ifndef ROCWMMA_B200_LAYOUT_HPP
@@ -129,7 +133,7 @@ namespace rocwmma
         template <uint32_t BK>
         struct AtomK<1, BK>
         {
-            static constexpr uint32_t value = BK % 16 == 0 ? 16 : 0;
+            static constexpr uint32_t value = BK % 16 == 0 ? 16 : (BK % 8 == 0 ? 8 : 0);
         };
         template <uint32_t BK>
         struct AtomK<2, BK>
@@ -139,7 +143,7 @@ namespace rocwmma
         template <uint32_t BK>
         struct AtomK<4, BK>
         {
-            static constexpr uint32_t value = BK % 8 == 0 ? 8 : (BK % 4 == 0 ? 4 : 0);
+            static constexpr uint32_t value = BK % 8 == 0 ? 8 : (BK % 4 == 0 ? 4 : (BK % 2 == 0 ? 2 : 0));
         };
         template <uint32_t BK>
         struct AtomK<8, BK>
@@ -161,6 +165,17 @@ namespace rocwmma
             {
                 dim = g + 8u * (i >> 2);
                 k   = 4u * t + (i & 3u);
+            }
+        };
+        template <>
+        struct InputAtom<1, 8>
+        {
+            static constexpr uint32_t Elems = 4, Run = 2;
+            ROCWMMA_DEVICE static inline void coord(uint32_t g, uint32_t t, uint32_t i, uint32_t& dim,
+                                                    uint32_t& k)
+            {
+                dim = g + 8u * (i >> 1);
+                k   = 2u * t + (i & 1u);
             }
         };
         template <>
@@ -208,6 +223,17 @@ namespace rocwmma
             }
         };
         template <>
+        struct InputAtom<4, 2>
+        {
+            static constexpr uint32_t Elems = 1, Run = 1;
+            ROCWMMA_DEVICE static inline void coord(uint32_t g, uint32_t t, uint32_t, uint32_t& dim, uint32_t& k)
+            {
+                const uint32_t lane = 4u * g + t;
+                dim = lane >> 1;
+                k   = lane & 1u;
+            }
+        };
+        template <>
         struct InputAtom<8, 4>
         {
             static constexpr uint32_t Elems = 2, Run = 1;
@@ -251,8 +277,8 @@ namespace rocwmma
         struct FragGeometry<matrix_a, BM, BN, BK, DataT>
         {
             static constexpr uint32_t KA = AtomK<sizeof(DataT), BK>::value;
-            static_assert(KA != 0, "BlockK must be a multiple of the smallest instruction K "
-                                   "(16 for 8-bit types, 8 for 16-bit, 4 for 32- and 64-bit)");
+            static_assert(KA != 0, "BlockK must be a multiple of the smallest atom depth "
+                                   "(8 for 8- and 16-bit types, 2 for 32-bit, 4 for 64-bit)");
             using Atom = InputAtom<sizeof(DataT), KA>;
             static constexpr uint32_t BlockHeight = BM, BlockWidth = BK, BlockDim = BM, KDim = BK;
             static_assert(BM % 16 == 0, "matrix_a fragments need BlockM to be a multiple of 16");
@@ -274,8 +300,8 @@ namespace rocwmma
         struct FragGeometry<matrix_b, BM, BN, BK, DataT>
         {
             static constexpr uint32_t KA = AtomK<sizeof(DataT), BK>::value;
-            static_assert(KA != 0, "BlockK must be a multiple of the smallest instruction K "
-                                   "(16 for 8-bit types, 8 for 16-bit, 4 for 32- and 64-bit)");
+            static_assert(KA != 0, "BlockK must be a multiple of the smallest atom depth "
+                                   "(8 for 8- and 16-bit types, 2 for 32-bit, 4 for 64-bit)");
             using Atom = InputAtom<sizeof(DataT), KA>;
             static constexpr uint32_t BlockHeight = BK, BlockWidth = BN, BlockDim = BN, KDim = BK;
             static_assert(BN % 16 == 0, "matrix_b fragments need BlockN to be a multiple of 16");

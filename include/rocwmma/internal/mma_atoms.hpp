@@ -76,6 +76,33 @@ namespace rocwmma
                          : "r"(a[0]), "r"(a[1]), "r"(b[1]));
         }
 
+        // int8, 8 deep: no such integer mma.sync shape.  The products are formed on m16n8k8 with exact fp16 copies of the
+        // operands (|v| <= 128) and fp32 accumulation from zero - eight products of at most 2^14 each, exact - and added
+        // to the int32 accumulator as integers.  a = 4 int8 (one register), b = 4 int8 [n-half 0 pair, n-half 1 pair].
+        ROCWMMA_DEVICE inline uint32_t i8pair_to_half2(uint32_t word, uint32_t shift)
+        {
+            const int     lo = static_cast<int8_t>((word >> shift) & 0xFFu), hi = static_cast<int8_t>((word >> (shift + 8u)) & 0xFFu);
+            const __half2 h  = __halves2half2(__int2half_rn(lo), __int2half_rn(hi));
+            return *reinterpret_cast<const uint32_t*>(&h);
+        }
+        ROCWMMA_DEVICE inline void mma_atom_i8_i32_k8(int32_t (&acc)[8], uint32_t a, uint32_t b)
+        {
+            const uint32_t ah[2] = {i8pair_to_half2(a, 0), i8pair_to_half2(a, 16)};
+            const uint32_t bh[2] = {i8pair_to_half2(b, 0), i8pair_to_half2(b, 16)};
+            float          p[8]  = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 "
+                         "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                         : "+f"(p[0]), "+f"(p[1]), "+f"(p[2]), "+f"(p[3])
+                         : "r"(ah[0]), "r"(ah[1]), "r"(bh[0]));
+            asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 "
+                         "{%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                         : "+f"(p[4]), "+f"(p[5]), "+f"(p[6]), "+f"(p[7])
+                         : "r"(ah[0]), "r"(ah[1]), "r"(bh[1]));
+#pragma unroll
+            for(int e = 0; e < 8; ++e)
+                acc[e] += __float2int_rn(p[e]);
+        }
+
         // OCP fp8 x fp8 -> fp32 (m16n8k16), same register orders as int8
         ROCWMMA_DEVICE inline void mma_atom_e4m3_f32(float (&acc)[8], const uint32_t (&a)[2], const uint32_t (&b)[2])
         {
@@ -187,6 +214,27 @@ namespace rocwmma
             mma_tf32_1684(acc + 4, al, bh[1]);
             mma_tf32_1684(acc + 4, ah, bl[1]);
             mma_tf32_1684(acc + 4, ah, bh[1]);
+        }
+        // fp32, 2 deep: no such mma.sync shape.  A atom 16 x 2 and B atom 2 x 16 hold one element per lane (lane l: block
+        // index l / 2, k = l % 2); every accumulator element fetches its two products' operands by shuffle and adds them
+        // with FMAs in ascending k.  ROUND_TF32: the xfloat32_t form (inputs rounded to TF32 first).
+        template <bool ROUND_TF32>
+        ROCWMMA_DEVICE inline void mma_atom_f32_k2(float (&acc)[8], float a, float b)
+        {
+            if constexpr(ROUND_TF32)
+            {
+                a = __uint_as_float(to_tf32(a));
+                b = __uint_as_float(to_tf32(b));
+            }
+            const uint32_t lane = threadIdx.x & 31u, g = lane >> 2, t = lane & 3u;
+#pragma unroll
+            for(uint32_t e = 0; e < 8; ++e)
+            {
+                const uint32_t row = g + 8u * ((e >> 1) & 1u), col = 2u * t + (e & 1u) + 8u * (e >> 2);
+                const float    a0 = __shfl_sync(0xFFFFFFFFu, a, 2u * row), a1 = __shfl_sync(0xFFFFFFFFu, a, 2u * row + 1u);
+                const float    b0 = __shfl_sync(0xFFFFFFFFu, b, 2u * col), b1 = __shfl_sync(0xFFFFFFFFu, b, 2u * col + 1u);
+                acc[e]            = fmaf(a1, b1, fmaf(a0, b0, acc[e]));
+            }
         }
         ROCWMMA_DEVICE inline void mma_atom_xf32_k4(float (&acc)[8], const float (&a)[2], const float (&b)[2])
         {

@@ -6,8 +6,8 @@
 // that header compiles against this one with nvcc for sm_100a; the "wave" is the CUDA warp
 // (Constants::AMDGCN_WAVE_SIZE == 32) and blockDim.x must be a multiple of 32.
 //
-// Supported block shapes: BlockM, BlockN multiples of 16; BlockK a multiple of 16 for 8-bit
-// inputs, 8 for 16-bit, 4 for fp32 and fp64.  Supported mma_sync type pairs (input -> compute):
+// Supported block shapes: BlockM, BlockN multiples of 16; BlockK a multiple of 8 for 8- and 16-bit
+// inputs (OCP fp8: 16), 2 for fp32, 4 for fp64 - the reference's minimum K per type.  Supported mma_sync type pairs (input -> compute):
 // float16_t/hfloat16_t -> float32_t or the input type, bfloat16_t -> float32_t or bfloat16_t,
 // float8_t / bfloat8_t (OCP e4m3 / e5m2) -> float32_t, int8_t -> int32_t, xfloat32_t -> float32_t (one TF32
 // product), float32_t -> float32_t (3xTF32), float64_t -> float64_t.
@@ -192,17 +192,128 @@ namespace rocwmma
             using type = uint4;
         };
 
-        // Moves the atoms [atomBegin, atomEnd) of a fragment between registers and memory.
-        // ColMajorMem selects the memory layout.  When consecutive register elements are adjacent
-        // in memory (Run > 1 and the run direction is the contiguous memory direction) and the
-        // addresses are suitably aligned, a run moves as one 2..16-byte access.
-        // Moves the elements [elemBegin, elemEnd) of a fragment.
+        // ---- whole-matrix moves of 16-bit atoms ------------------------------------------------
+        // A 16-bit atom is two (16 x 8) or four (16 x 16, accumulators included) 8 x 8 matrices in exactly the
+        // register order of ldmatrix / stmatrix: matrix j is the atom's elements 2j, 2j + 1 of every lane, thread
+        // (g, t) holding its entries (g, 2t) and (g, 2t + 1) with rows along the atom's block dimension and columns
+        // along k.  So an atom moves to or from SHARED memory in one instruction: plain when memory is contiguous
+        // along k, .trans when it is contiguous along the block dimension (the stored 8 x 8 tiles then have their
+        // rows along k).  In GLOBAL memory the second case is the expensive one for per-lane accesses (eight
+        // 2-byte accesses per atom); there each lane moves the 32-bit word it would own in the transposed tile
+        // and movmatrix swaps the tile across the warp.
+        template <typename Geometry, typename DataT>
+        struct MatrixAtoms
+        {
+            static constexpr uint32_t Mats = (sizeof(DataT) == 2 && Geometry::Run == 2)
+                                                 ? (Geometry::AtomElems == 8 ? 4u : (Geometry::AtomElems == 4 ? 2u : 0u))
+                                                 : 0u;
+        };
+        ROCWMMA_DEVICE inline uint32_t movmatrix_trans(uint32_t w)
+        {
+            uint32_t r;
+            asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(w));
+            return r;
+        }
+        template <uint32_t Mats, bool Trans>
+        ROCWMMA_DEVICE inline void ldmatrix_atom(uint32_t* r, uint32_t saddr)
+        {
+            if constexpr(Mats == 4 && !Trans)
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr) : "memory");
+            else if constexpr(Mats == 4)
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr) : "memory");
+            else if constexpr(!Trans)
+                asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
+                             : "=r"(r[0]), "=r"(r[1]) : "r"(saddr) : "memory");
+            else
+                asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];"
+                             : "=r"(r[0]), "=r"(r[1]) : "r"(saddr) : "memory");
+        }
+        template <uint32_t Mats, bool Trans>
+        ROCWMMA_DEVICE inline void stmatrix_atom(const uint32_t* r, uint32_t saddr)
+        {
+            if constexpr(Mats == 4 && !Trans)
+                asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%4], {%0,%1,%2,%3};" ::"r"(r[0]), "r"(r[1]), "r"(r[2]),
+                             "r"(r[3]), "r"(saddr) : "memory");
+            else if constexpr(Mats == 4)
+                asm volatile("stmatrix.sync.aligned.m8n8.x4.trans.shared.b16 [%4], {%0,%1,%2,%3};" ::"r"(r[0]), "r"(r[1]),
+                             "r"(r[2]), "r"(r[3]), "r"(saddr) : "memory");
+            else if constexpr(!Trans)
+                asm volatile("stmatrix.sync.aligned.m8n8.x2.shared.b16 [%2], {%0,%1};" ::"r"(r[0]), "r"(r[1]), "r"(saddr) : "memory");
+            else
+                asm volatile("stmatrix.sync.aligned.m8n8.x2.trans.shared.b16 [%2], {%0,%1};" ::"r"(r[0]), "r"(r[1]), "r"(saddr)
+                             : "memory");
+        }
+
+        // One whole 16-bit atom between registers and memory through the instructions above.  Returns false (and moves
+        // nothing) when the addresses do not allow it; every lane of the warp takes the same branch (mem, ldm are
+        // warp-uniform arguments of the *_sync functions).
         template <bool IsLoad, bool ColMajorMem, typename Geometry, typename DataT>
-        ROCWMMA_DEVICE inline void move_atoms(DataT* regs, DataT* mem, uint32_t ldm, uint32_t elemBegin,
-                                              uint32_t elemEnd)
+        ROCWMMA_DEVICE inline bool move_matrix_atom(DataT* atom_regs, DataT* mem, uint32_t ldm, uint32_t atom, uint32_t lane)
+        {
+            // atom_regs: the AtomElems registers that hold (or receive) atom `atom` of the fragment
+            constexpr uint32_t Mats  = MatrixAtoms<Geometry, DataT>::Mats;
+            constexpr bool     Trans = Geometry::RunAlongCol == ColMajorMem; // memory is contiguous along the block dimension
+            const uintptr_t    base  = reinterpret_cast<uintptr_t>(mem);
+            const uintptr_t    pitch = static_cast<uintptr_t>(ldm) * sizeof(DataT);
+            uint32_t*          r32   = reinterpret_cast<uint32_t*>(atom_regs);
+            const auto offset_of = [&](uint32_t syn_lane, uint32_t syn_elem) {
+                uint32_t row, col;
+                Geometry::coord(syn_lane, atom, syn_elem, row, col);
+                return ColMajorMem ? static_cast<size_t>(col) * ldm + row : static_cast<size_t>(row) * ldm + col;
+            };
+            if(__isShared(mem) && ((base | pitch) & 15u) == 0u)
+            {
+                // lane l gives the address of row (l % 8) of matrix (l / 8); lanes beyond the last matrix repeat valid ones
+                const uint32_t j = (lane >> 3) % Mats, rr = lane & 7u;
+                // plain: row rr = (block-dimension index rr, k 0..7) of the matrix; .trans: stored row rr = (k index rr)
+                const size_t off = Trans ? offset_of(rr >> 1, 2u * j + (rr & 1u)) : offset_of(rr << 2, 2u * j);
+                const uint32_t saddr = static_cast<uint32_t>(__cvta_generic_to_shared(mem + off));
+                if constexpr(IsLoad)
+                    ldmatrix_atom<Mats, Trans>(r32, saddr);
+                else
+                    stmatrix_atom<Mats, Trans>(r32, saddr);
+                return true;
+            }
+            if constexpr(Trans)
+            {
+                if(((base | pitch) & 3u) == 0u)
+                {
+                    // the word this lane owns in the transposed tile: (k index g, block-dimension indices 2t, 2t + 1)
+                    const uint32_t g = lane >> 2, t = lane & 3u;
+#pragma unroll
+                    for(uint32_t j = 0; j < Mats; ++j)
+                    {
+                        uint32_t* word = reinterpret_cast<uint32_t*>(mem + offset_of(((2u * t) << 2) | (g >> 1), 2u * j + (g & 1u)));
+                        if constexpr(IsLoad)
+                            r32[j] = movmatrix_trans(*word);
+                        else
+                            *word = movmatrix_trans(r32[j]);
+                    }
+                    return true;
+                }
+            }
+            return false;
+        }
+
+        // Moves the elements [elemBegin, elemBegin + count) of a fragment between memory and the registers
+        // regs[0 .. count): register r holds element elemBegin + r.  A whole-fragment move has elemBegin = 0 and
+        // count = Size (constants: the loops below then fold to straight-line code with constant register numbers and
+        // atom coordinates); a cooperative move passes the warp's slice, which therefore always sits in the FIRST
+        // registers of the warp's fragment whatever the wave index - only addresses depend on it.
+        // ColMajorMem selects the memory layout.  When consecutive register elements are adjacent in memory (Run > 1
+        // and the run direction is the contiguous memory direction) and the addresses are suitably aligned, a run
+        // moves as one 2..16-byte access; 16-bit atoms that lie wholly inside the range move as 8 x 8 matrices.
+        // RunAligned: elemBegin and count are multiples of the run length.  Cooperative slices are whole 32-bit register
+        // units, which is a whole run for 8- and 16-bit types; a slice of a 32- or 64-bit accumulator (runs of two) may
+        // start or end inside a run, and is then moved element by element.
+        template <bool IsLoad, bool ColMajorMem, typename Geometry, typename DataT, bool RunAligned = true>
+        ROCWMMA_DEVICE inline void move_atoms(DataT* regs, DataT* mem, uint32_t ldm, uint32_t elemBegin, uint32_t count)
         {
             const uint32_t     lane       = threadIdx.x & 31u;
-            constexpr uint32_t Run        = Geometry::Run;
+            constexpr uint32_t Run        = RunAligned ? Geometry::Run : 1u;
+            constexpr uint32_t AE         = Geometry::AtomElems;
             constexpr bool     contiguous = (Run > 1) && (Geometry::RunAlongCol != ColMajorMem);
             constexpr uint32_t VecBytes   = contiguous ? Run * sizeof(DataT) : sizeof(DataT);
             bool               vec_ok     = false;
@@ -211,23 +322,34 @@ namespace rocwmma
                           % VecBytes)
                          == 0;
 #pragma unroll
-            for(uint32_t atom = 0; atom < Geometry::Atoms; ++atom)
+            for(uint32_t chunk = 0; chunk < Geometry::Atoms; ++chunk) // registers [chunk * AE, (chunk + 1) * AE)
             {
-#pragma unroll
-                for(uint32_t i = 0; i < Geometry::AtomElems; i += Run)
+                const uint32_t r0 = chunk * AE;
+                if(r0 >= count)
+                    continue; // (no early exit: the loops must stay fully unrolled for the registers to stay registers)
+                if constexpr(MatrixAtoms<Geometry, DataT>::Mats != 0)
                 {
-                    const uint32_t e = atom * Geometry::AtomElems + i; // first element of this run
-                    if(e + Run <= elemBegin || e >= elemEnd)
+                    // a 16-bit atom wholly inside the range: one matrix instruction (or word moves + movmatrix)
+                    const uint32_t e0 = elemBegin + r0;
+                    if(e0 % AE == 0u && r0 + AE <= count)
+                        if(move_matrix_atom<IsLoad, ColMajorMem, Geometry, DataT>(regs + r0, mem, ldm, e0 / AE, lane))
+                            continue;
+                }
+#pragma unroll
+                for(uint32_t ri = 0; ri < AE; ri += Run)
+                {
+                    const uint32_t r = r0 + ri; // first register of this run
+                    if(r >= count)
                         continue;
-                    const bool whole = e >= elemBegin && e + Run <= elemEnd;
-                    uint32_t   row, col;
-                    Geometry::coord(lane, atom, i, row, col);
-                    DataT* r = regs + e;
+                    const uint32_t e = elemBegin + r, atom = e / AE, i = e % AE;
+                    DataT*         rp = regs + r;
                     if constexpr(contiguous)
                     {
+                        uint32_t row, col;
+                        Geometry::coord(lane, atom, i, row, col);
                         const size_t off = ColMajorMem ? static_cast<size_t>(col) * ldm + row
                                                        : static_cast<size_t>(row) * ldm + col;
-                        if(vec_ok && whole)
+                        if(vec_ok)
                         {
                             // staged through a correctly aligned temporary: the fragment itself is
                             // only 4-byte aligned
@@ -239,13 +361,13 @@ namespace rocwmma
                                 tmp = *reinterpret_cast<const V*>(mem + off);
 #pragma unroll
                                 for(uint32_t j = 0; j < Run; ++j)
-                                    r[j] = tp[j];
+                                    rp[j] = tp[j];
                             }
                             else
                             {
 #pragma unroll
                                 for(uint32_t j = 0; j < Run; ++j)
-                                    tp[j] = r[j];
+                                    tp[j] = rp[j];
                                 *reinterpret_cast<V*>(mem + off) = tmp;
                             }
                         }
@@ -254,12 +376,10 @@ namespace rocwmma
 #pragma unroll
                             for(uint32_t j = 0; j < Run; ++j)
                             {
-                                if(e + j < elemBegin || e + j >= elemEnd)
-                                    continue;
                                 if constexpr(IsLoad)
-                                    r[j] = mem[off + j];
+                                    rp[j] = mem[off + j];
                                 else
-                                    mem[off + j] = r[j];
+                                    mem[off + j] = rp[j];
                             }
                         }
                     }
@@ -268,16 +388,14 @@ namespace rocwmma
 #pragma unroll
                         for(uint32_t j = 0; j < Run; ++j)
                         {
-                            if(e + j < elemBegin || e + j >= elemEnd)
-                                continue;
                             uint32_t rr, cc;
                             Geometry::coord(lane, atom, i + j, rr, cc);
                             const size_t off = ColMajorMem ? static_cast<size_t>(cc) * ldm + rr
                                                            : static_cast<size_t>(rr) * ldm + cc;
                             if constexpr(IsLoad)
-                                r[j] = mem[off];
+                                rp[j] = mem[off];
                             else
-                                mem[off] = r[j];
+                                mem[off] = rp[j];
                         }
                     }
                 }
@@ -414,8 +532,11 @@ namespace rocwmma
             template <uint32_t KA>
             ROCWMMA_DEVICE static inline void exec(int32_t (&acc)[8], const int8_t* a, const int8_t* b)
             {
-                mma_atom_i8_i32(acc, *reinterpret_cast<const uint32_t(*)[2]>(a),
-                                *reinterpret_cast<const uint32_t(*)[2]>(b));
+                if constexpr(KA == 16)
+                    mma_atom_i8_i32(acc, *reinterpret_cast<const uint32_t(*)[2]>(a),
+                                    *reinterpret_cast<const uint32_t(*)[2]>(b));
+                else
+                    mma_atom_i8_i32_k8(acc, *reinterpret_cast<const uint32_t*>(a), *reinterpret_cast<const uint32_t*>(b));
             }
         };
         template <>
@@ -449,9 +570,11 @@ namespace rocwmma
             {
                 if constexpr(KA == 8)
                     mma_atom_xf32(acc, *reinterpret_cast<const float(*)[4]>(a), *reinterpret_cast<const float(*)[4]>(b));
-                else
+                else if constexpr(KA == 4)
                     mma_atom_xf32_k4(acc, *reinterpret_cast<const float(*)[2]>(a),
                                      *reinterpret_cast<const float(*)[2]>(b));
+                else
+                    mma_atom_f32_k2<true>(acc, *reinterpret_cast<const float*>(a), *reinterpret_cast<const float*>(b));
             }
         };
         template <>
@@ -475,9 +598,11 @@ namespace rocwmma
                 if constexpr(KA == 8)
                     mma_atom_f32(acc, *reinterpret_cast<const float(*)[4]>(a),
                                  *reinterpret_cast<const float(*)[4]>(b));
-                else
+                else if constexpr(KA == 4)
                     mma_atom_f32_k4(acc, *reinterpret_cast<const float(*)[2]>(a),
                                     *reinterpret_cast<const float(*)[2]>(b));
+                else
+                    mma_atom_f32_k2<false>(acc, *a, *b);
             }
         };
     } // namespace detail

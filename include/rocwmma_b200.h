@@ -61,6 +61,8 @@ int b200wmma_version(void);
  *                        split is used when slabs per pair + this < slabs of a whole tile
  *   "gemm_mma_order"     512x256 kernel, MMAs of a tile's first and last K slabs: 1 = accumulator by accumulator (so each
  *                        accumulator's drain overlaps the other's MMAs), 2 = slab by slab
+ *   "dlrm_bwd_stages"    one-warp-per-sample DLRM backward kernel: depth of each warp's sample ring, 2 or 3
+ *   "dlrm_bwd_warps"     ... and warps per CTA, 1..12 (clipped to what fits in shared memory)
  * Unknown keys and out-of-range values return B200WMMA_ERR_INVALID_ARG.  The library reads no environment variable
  * except B200WMMA_NCCL_LIBRARY (see the multi-GPU section). */
 int b200wmma_set_tuning(const char* key, int value);

@@ -136,7 +136,9 @@ extern "C" int b200wmma_set_tuning(const char* key, int value)
                  {"sp24_force_expand", tuning::SP24_FORCE_EXPAND, 0, 1},
                  {"gemm_mma_order", tuning::GEMM_MMA_ORDER, 0, 2},
                  {"gemm_split_tail", tuning::GEMM_SPLIT_TAIL, 0, 2},
-                 {"gemm_split_fixup", tuning::GEMM_SPLIT_FIXUP, 0, 4096}};
+                 {"gemm_split_fixup", tuning::GEMM_SPLIT_FIXUP, 0, 4096},
+                 {"dlrm_bwd_stages", tuning::DLRM_BWD_STAGES, 0, 3},
+                 {"dlrm_bwd_warps", tuning::DLRM_BWD_WARPS, 0, 12}};
     for(const auto& t : table)
         if(std::strcmp(key, t.name) == 0)
         {

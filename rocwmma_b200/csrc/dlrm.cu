@@ -20,8 +20,11 @@
 // optionally with the bottom-MLP pass-through gradient added to row 0.
 //
 // Both are HBM-bound: the arithmetic is 2*m*m*k flop per sample against ~8-15 KB of traffic.
+#include <algorithm>
+
 #include "gemm_tc05_common.cuh" // make_kmajor_tmap: 64-column, 128-byte-swizzled box maps
 #include "ptx_sm100.cuh"
+#include "tuning.cuh"
 
 namespace b200wmma
 {
@@ -31,7 +34,8 @@ namespace b200wmma
         constexpr int      MAX_M       = 32;
         constexpr int      MAX_K       = 256;
         constexpr int      FWD_STAGES  = 3;
-        constexpr int      BWD_STAGES  = 2;
+        constexpr int      BWD_MAX_WARPS = 12; // the backward kernel takes its warp count from the launch
+        constexpr int      BWD_BATCH     = 4; // 16-column slabs of dX in flight per warp
         constexpr int      TPITCH      = 40; // halfs per row of the 32x32 symmetric matrix (+8 pad)
         constexpr uint32_t BOX_BYTES   = MAX_M * 128; // one 64-column box: 32 rows of 128 bytes
         constexpr uint64_t WAIT_NS     = 2000000000ull;
@@ -223,8 +227,12 @@ namespace b200wmma
 
         // ---------------------------------- backward ---------------------------------------
         // Shared memory per warp: BWD_STAGES x (sample tile + upstream row), the symmetric matrix,
-        // BWD_STAGES mbarriers.
-        __global__ void __launch_bounds__(WARPS * 32)
+        // BWD_STAGES mbarriers.  The launch picks the warp count (blockDim.x / 32) and the ring depth from what
+        // fits in shared memory: three stages where at least four warps fit (two samples' loads in flight behind the
+        // one a warp works on, and a stage is only handed back to the loader after the NEXT sample's stores were
+        // issued, so no warp waits for its own stores to be read), two stages otherwise.
+        template <int BWD_STAGES>
+        __global__ void __launch_bounds__(BWD_MAX_WARPS * 32)
             dlrm_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_g,
                             const __half* __restrict__ upstream, __half* __restrict__ bottom_mlp_grad,
                             uint32_t m, uint32_t m_stride, uint32_t k, uint32_t batch, uint32_t up_stride,
@@ -235,6 +243,7 @@ namespace b200wmma
             const uint32_t base  = (raw + 1023u) & ~1023u;
             uint8_t*       smem  = smem_raw + (base - raw);
             const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+            const uint32_t WARPS    = blockDim.x >> 5;
             const uint32_t nbox     = (k + 63u) >> 6;
             const uint32_t tile_b   = nbox * BOX_BYTES;
             const uint32_t up_b     = up_stride * 2u; // multiple of 16
@@ -323,42 +332,59 @@ namespace b200wmma
                         ldmatrix_x4(af[rb][ks][0], af[rb][ks][1], af[rb][ks][2], af[rb][ks][3],
                                     ts_addr + ((16 * rb + (lane & 15)) * TPITCH + 16 * ks + (lane >> 4) * 8) * 2u);
 
-                // dX[:, n0:n0+16] depends only on X[:, n0:n0+16]: compute a 16-column slab,
-                // then overwrite those columns of the shared tile with the result.
-                for(uint32_t n0 = 0; n0 < k; n0 += 16)
+                // dX[:, n0:n0+16] depends only on X[:, n0:n0+16]: compute 16-column slabs, then overwrite those
+                // columns of the shared tile with the result.  BWD_BATCH slabs go through together so that their
+                // loads, MMAs and stores overlap (one warp has nothing else to hide their latencies with).
+                for(uint32_t n0 = 0; n0 < k; n0 += 16u * BWD_BATCH)
                 {
-                    float    acc[2][2][4] = {};
-                    uint32_t bf[2][4];
+                    float    acc[BWD_BATCH][2][2][4] = {};
+                    uint32_t bf[BWD_BATCH][2][4];
 #pragma unroll
-                    for(int ks = 0; ks < 2; ++ks)
-                        ldmatrix_x4_trans(bf[ks][0], bf[ks][1], bf[ks][2], bf[ks][3],
-                                          xs + tile_off(16 * ks + (lane & 7) + ((lane >> 3) & 1) * 8, n0 + (lane >> 4) * 8));
-#pragma unroll
-                    for(int rb = 0; rb < 2; ++rb)
-#pragma unroll
-                        for(int ks = 0; ks < 2; ++ks)
+                    for(int s = 0; s < BWD_BATCH; ++s)
+                        if(n0 + 16u * s < k)
                         {
-                            mma_16816(acc[rb][0], af[rb][ks], bf[ks][0], bf[ks][1]);
-                            mma_16816(acc[rb][1], af[rb][ks], bf[ks][2], bf[ks][3]);
+#pragma unroll
+                            for(int ks = 0; ks < 2; ++ks)
+                                ldmatrix_x4_trans(bf[s][ks][0], bf[s][ks][1], bf[s][ks][2], bf[s][ks][3],
+                                                  xs + tile_off(16 * ks + (lane & 7) + ((lane >> 3) & 1) * 8,
+                                                                n0 + 16u * s + (lane >> 4) * 8));
                         }
-                    __syncwarp(); // every lane has read this slab of X
 #pragma unroll
-                    for(int rb = 0; rb < 2; ++rb)
+                    for(int s = 0; s < BWD_BATCH; ++s)
+                        if(n0 + 16u * s < k)
+                        {
 #pragma unroll
-                        for(int nt = 0; nt < 2; ++nt)
+                            for(int rb = 0; rb < 2; ++rb)
 #pragma unroll
-                            for(int h = 0; h < 2; ++h)
-                            {
-                                const uint32_t r = 16 * rb + g + 8 * h, c = n0 + 8 * nt + 2 * t;
-                                float          v0 = acc[rb][nt][2 * h], v1 = acc[rb][nt][2 * h + 1];
-                                if(fuse_mlp && r == 0)
+                                for(int ks = 0; ks < 2; ++ks)
                                 {
-                                    v0 += __half2float(gs[c]);
-                                    v1 += __half2float(gs[c + 1]);
+                                    mma_16816(acc[s][rb][0], af[rb][ks], bf[s][ks][0], bf[s][ks][1]);
+                                    mma_16816(acc[s][rb][1], af[rb][ks], bf[s][ks][2], bf[s][ks][3]);
                                 }
-                                *reinterpret_cast<__half2*>(smem + xs_off + tile_off(r, c) + (c & 7u) * 2u)
-                                    = __floats2half2_rn(v0, v1);
-                            }
+                        }
+                    __syncwarp(); // every lane has read these slabs of X
+#pragma unroll
+                    for(int s = 0; s < BWD_BATCH; ++s)
+                        if(n0 + 16u * s < k)
+                        {
+#pragma unroll
+                            for(int rb = 0; rb < 2; ++rb)
+#pragma unroll
+                                for(int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                                    for(int h = 0; h < 2; ++h)
+                                    {
+                                        const uint32_t r = 16 * rb + g + 8 * h, c = n0 + 16u * s + 8 * nt + 2 * t;
+                                        float          v0 = acc[s][rb][nt][2 * h], v1 = acc[s][rb][nt][2 * h + 1];
+                                        if(fuse_mlp && r == 0)
+                                        {
+                                            v0 += __half2float(gs[c]);
+                                            v1 += __half2float(gs[c + 1]);
+                                        }
+                                        *reinterpret_cast<__half2*>(smem + xs_off + tile_off(r, c) + (c & 7u) * 2u)
+                                            = __floats2half2_rn(v0, v1);
+                                    }
+                        }
                 }
                 ptx::fence_proxy_async_smem(); // generic writes of dX -> visible to the TMA stores
                 __syncwarp();
@@ -370,14 +396,24 @@ namespace b200wmma
                     if(bottom_mlp_grad)
                         ptx::bulk_store_1d(bottom_mlp_grad + static_cast<size_t>(b) * k, base + up_off + stage * up_slot, k * 2u);
                     ptx::bulk_commit_group();
-                    // the stage is reloaded as soon as the stores above have read it
-                    ptx::bulk_wait_group_read<0>();
+                    // Rows m..31 of a tile still hold zeros after a pass: the product of the zero rows of the
+                    // symmetric matrix was written over them.
+                    if constexpr(BWD_STAGES >= 3)
+                    {
+                        // hand the PREVIOUS sample's stage to the loader: its stores have been read by now or
+                        // nearly so, and this sample's stores stay in flight
+                        ptx::bulk_wait_group_read<1>();
+                        if(it > 0 && b + (BWD_STAGES - 1) * stride < batch)
+                            issue_load(b + (BWD_STAGES - 1) * stride, (it - 1) % BWD_STAGES);
+                    }
+                    else
+                    {
+                        ptx::bulk_wait_group_read<0>();
+                        if(b + BWD_STAGES * stride < batch)
+                            issue_load(b + BWD_STAGES * stride, stage);
+                    }
                 }
                 __syncwarp();
-                // rows m..31 of the tile still hold zeros: the product of the zero rows of the
-                // symmetric matrix was written over them
-                if(lane == 0 && b + BWD_STAGES * stride < batch)
-                    issue_load(b + BWD_STAGES * stride, stage);
             }
             if(lane == 0)
                 ptx::bulk_wait_group<0>();
@@ -421,15 +457,15 @@ namespace b200wmma
             return B200WMMA_OK;
         }
 
-        static uint32_t grid_for(uint32_t batch, const void* kernel, size_t smem_bytes)
+        static uint32_t grid_for(uint32_t batch, const void* kernel, size_t smem_bytes, uint32_t warps = WARPS)
         {
             int dev = 0, sms = 148, per_sm = 1;
             cudaGetDevice(&dev);
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, WARPS * 32, smem_bytes);
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, warps * 32, smem_bytes);
             if(per_sm < 1)
                 per_sm = 1;
-            const uint32_t want = ceil_div(batch, WARPS);
+            const uint32_t want = ceil_div(batch, warps);
             const uint32_t cap  = static_cast<uint32_t>(sms) * per_sm;
             return want < cap ? want : cap;
         }
@@ -437,13 +473,14 @@ namespace b200wmma
         // Launch with programmatic stream serialization: the kernel's prologue (barrier set-up, pad rows) may overlap
         // the tail of the preceding kernel in the stream; the kernel itself waits for that kernel's completion
         // (grid_dep_wait) before it touches global memory, so stream order is kept.
-        static cudaLaunchConfig_t pdl_config(cudaLaunchAttribute (&attr)[1], uint32_t grid, size_t smem, cudaStream_t stream)
+        static cudaLaunchConfig_t pdl_config(cudaLaunchAttribute (&attr)[1], uint32_t grid, size_t smem, cudaStream_t stream,
+                                             uint32_t warps = WARPS)
         {
             attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
             attr[0].val.programmaticStreamSerializationAllowed = 1;
             cudaLaunchConfig_t cfg                             = {};
             cfg.gridDim                                        = dim3(grid);
-            cfg.blockDim                                       = dim3(WARPS * 32);
+            cfg.blockDim                                       = dim3(warps * 32);
             cfg.dynamicSmemBytes                               = smem;
             cfg.stream                                         = stream;
             cfg.attrs                                          = attr;
@@ -537,21 +574,38 @@ extern "C" int b200wmma_dlrm_bwd(const void* input, const void* upstream, void* 
         return e;
     const uint32_t nbox    = (k + 63) / 64;
     const uint32_t up_slot = (upstream_stride * 2 + 127) & ~127u;
-    const size_t   smem    = 1024
-                        + static_cast<size_t>(WARPS) * (BWD_STAGES * (nbox * BOX_BYTES + up_slot) + MAX_M * TPITCH * 2 + BWD_STAGES * 8)
-                        + 16;
-    static size_t attr_set_dev[MAX_DEVICES];
-    size_t&       attr_set = attr_set_dev[current_device_slot()];
+    auto per_warp = [&](uint32_t stages) -> size_t {
+        return static_cast<size_t>(stages) * (nbox * BOX_BYTES + up_slot) + MAX_M * TPITCH * 2 + stages * 8;
+    };
+    // ring depth and warps per CTA from what one SM's shared memory holds (see the kernel's header comment)
+    const size_t budget = 227 * 1024 - 1024 - 16;
+    uint32_t     stages = 3, warps = static_cast<uint32_t>(std::min<size_t>(8, budget / per_warp(3)));
+    if(warps < 4)
+    {
+        stages = 2;
+        warps  = static_cast<uint32_t>(std::min<size_t>(8, budget / per_warp(2)));
+    }
+    if(const int forced = tuning::get(tuning::DLRM_BWD_STAGES); forced == 2 || forced == 3)
+    {
+        stages = static_cast<uint32_t>(forced);
+        warps  = static_cast<uint32_t>(std::min<size_t>(8, budget / per_warp(stages)));
+    }
+    if(const int forced = tuning::get(tuning::DLRM_BWD_WARPS); forced > 0)
+        warps = static_cast<uint32_t>(std::min<size_t>(std::min<int>(forced, BWD_MAX_WARPS), budget / per_warp(stages)));
+    B200_REQUIRE(warps >= 1, B200WMMA_ERR_INVALID_ARG, "dlrm_bwd: one sample's tiles do not fit in shared memory");
+    auto* const  kernel = stages == 3 ? dlrm_bwd_kernel<3> : dlrm_bwd_kernel<2>;
+    const size_t smem   = 1024 + warps * per_warp(stages) + 16;
+    static size_t attr_set_dev[MAX_DEVICES][2];
+    size_t&       attr_set = attr_set_dev[current_device_slot()][stages - 2];
     if(smem > 48 * 1024 && smem > attr_set)
     {
-        B200_CHECK_CUDA(cudaFuncSetAttribute(dlrm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(smem)));
+        B200_CHECK_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         attr_set = smem;
     }
-    const uint32_t grid = grid_for(batch, reinterpret_cast<const void*>(dlrm_bwd_kernel), smem);
+    const uint32_t grid = grid_for(batch, reinterpret_cast<const void*>(kernel), smem, warps);
     cudaLaunchAttribute attr[1];
-    cudaLaunchConfig_t  cfg = pdl_config(attr, grid, smem, as_stream(stream));
-    B200_CHECK_CUDA(cudaLaunchKernelEx(&cfg, dlrm_bwd_kernel, tm_x, tm_g, static_cast<const __half*>(upstream),
+    cudaLaunchConfig_t  cfg = pdl_config(attr, grid, smem, as_stream(stream), warps);
+    B200_CHECK_CUDA(cudaLaunchKernelEx(&cfg, kernel, tm_x, tm_g, static_cast<const __half*>(upstream),
                                        static_cast<__half*>(bottom_mlp_grad), m, m_stride, k, batch, upstream_stride,
                                        fuse_mlp_into_row0, status));
     return B200WMMA_OK;

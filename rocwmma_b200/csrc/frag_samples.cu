@@ -95,7 +95,11 @@ namespace b200wmma
         constexpr uint32_t P_LDS_HEIGHT = GetIOShape_t<LdsWriteA>::BlockHeight + GetIOShape_t<LdsWriteB>::BlockHeight;
         constexpr uint32_t P_LDS_WIDTH  = P_K;
         constexpr uint32_t P_LDS_ELEMS  = P_LDS_HEIGHT * P_LDS_WIDTH;
-        constexpr uint32_t P_LDS_LD     = std::is_same<PLayoutLds, row_major>::value ? P_LDS_WIDTH : P_LDS_HEIGHT;
+        // leading dimension of the shared-memory block, padded by 16 bytes: consecutive K rows then start in different
+        // banks, which the 8 x 8 matrix loads and stores (eight 16-byte rows per instruction phase) need to be conflict-free
+        constexpr uint32_t P_LDS_PAD    = 16 / sizeof(PIn);
+        constexpr uint32_t P_LDS_LD     = (std::is_same<PLayoutLds, row_major>::value ? P_LDS_WIDTH : P_LDS_HEIGHT) + P_LDS_PAD;
+        constexpr uint32_t P_LDS_ALLOC  = P_LDS_LD * (std::is_same<PLayoutLds, row_major>::value ? P_LDS_HEIGHT : P_LDS_WIDTH);
 
         ROCWMMA_KERNEL void __launch_bounds__(P_TBLOCK_X* P_TBLOCK_Y)
             perf_hgemm_fragment_kernel(uint32_t m, uint32_t n, uint32_t k, PIn const* a, PIn const* b,
@@ -104,7 +108,7 @@ namespace b200wmma
         {
             extern __shared__ __align__(16) unsigned char lds_raw[];
             PIn* ldsLo = reinterpret_cast<PIn*>(lds_raw);
-            PIn* ldsHi = ldsLo + P_LDS_ELEMS;
+            PIn* ldsHi = ldsLo + P_LDS_ALLOC;
 
             const auto warpCoord  = make_coord2d(threadIdx.x / Constants::AMDGCN_WAVE_SIZE, threadIdx.y);
             const auto warpOffset = warpCoord * make_coord2d(P_WARP_TILE_X, P_WARP_TILE_Y);
@@ -300,7 +304,7 @@ extern "C" int b200wmma_perf_hgemm_fragment(uint32_t m, uint32_t n, uint32_t k, 
         return e;
     const dim3   block(fragk::P_TBLOCK_X, fragk::P_TBLOCK_Y);
     const dim3   grid(m / fragk::P_MACRO_X, n / fragk::P_MACRO_Y);
-    const size_t lds = 2 * fragk::P_LDS_ELEMS * sizeof(fragk::PIn);
+    const size_t lds = 2 * fragk::P_LDS_ALLOC * sizeof(fragk::PIn);
     fragk::perf_hgemm_fragment_kernel<<<grid, block, lds, as_stream(stream)>>>(
         m, n, k, static_cast<const fragk::PIn*>(a), static_cast<const fragk::PIn*>(b),
         static_cast<const fragk::POut*>(c), static_cast<fragk::POut*>(d), lda, ldb, ldc, ldd, alpha, beta);

@@ -15,6 +15,8 @@ namespace b200wmma
             GEMM_SPLIT_TAIL   = 4, // 512x256 kernel given a workspace: 1 = split the last partial round along K when it pays, 2 = never
             GEMM_SPLIT_FIXUP  = 5, // cost of the split-K exchange the planner assumes, in K slabs (0 = built-in)
             GEMM_MMA_ORDER    = 3, // 512x256 kernel, first / last K slabs of a tile: 1 = by accumulator, 2 = by slab
+            DLRM_BWD_STAGES   = 6, // one-warp-per-sample DLRM backward kernel: ring depth 2 or 3
+            DLRM_BWD_WARPS    = 7, // ... and warps per CTA (1..12, clipped to what fits in shared memory)
             NUM_KEYS
         };
         int  get(Key k);

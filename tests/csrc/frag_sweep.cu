@@ -1,12 +1,13 @@
 // Systematic sweep of fragment shapes for the load / store / cooperative / contamination checks, built into
 // tests/libfrag_sweep.so.  It follows the parameter space of the reference's unit suites
-// (test/unit/unit_test_params.hpp:86-141: BlockDim 16..256 x BlockK 8..64 x {i8, f16, f32, f64} x {row, col}
-// major, for matrix_a, matrix_b and accumulator fragments), one template instantiation per point:
+// (test/unit/unit_test_params.hpp:86-141: BlockDim 16..256 x BlockK 8..64, and 128 / 256 of its extended set, x
+// {i8, f16, f32, f64} x {row, col} major, for matrix_a, matrix_b and accumulator fragments), one template
+// instantiation per point:
 //   matrix_a    : fragment<matrix_a, BlockDim, 16, BlockK>       (BlockDim x BlockK in memory)
 //   matrix_b    : fragment<matrix_b, 16, BlockDim, BlockK>       (BlockK x BlockDim in memory)
 //   accumulator : fragment<accumulator, BlockDim, BlockK, 16>    (BlockDim x BlockK in memory)
-// Points this implementation does not offer return -3: BlockK = 8 with 8-bit inputs (the fragments are made of
-// whole mma.sync operands, at least 16 deep for that type) and accumulator blocks narrower than 16.
+// Points this implementation does not offer return -3: accumulator blocks narrower than 16, and blocks of more than
+// 32 KB (1 KB = 256 registers per lane: a fragment lives in registers, and a thread has 255).
 //
 // The file is compiled once per (fragment kind, element type) with -DSWEEP_KIND=0..2 -DSWEEP_TYPE=0..3, so that the
 // pieces build in parallel, and once without them for the dispatcher frag_sweep(); all objects are linked into one
@@ -41,21 +42,21 @@ namespace
     template <uint32_t BD, uint32_t BK, typename T, typename L>
     struct FragOf<matrix_a, BD, BK, T, L>
     {
-        static constexpr bool supported = detail::AtomK<sizeof(T), BK>::value != 0;
+        static constexpr bool supported = detail::AtomK<sizeof(T), BK>::value != 0 && BD * BK * sizeof(T) <= 32768;
         template <typename = void>
         using type = fragment<matrix_a, BD, 16, BK, T, L>;
     };
     template <uint32_t BD, uint32_t BK, typename T, typename L>
     struct FragOf<matrix_b, BD, BK, T, L>
     {
-        static constexpr bool supported = detail::AtomK<sizeof(T), BK>::value != 0;
+        static constexpr bool supported = detail::AtomK<sizeof(T), BK>::value != 0 && BD * BK * sizeof(T) <= 32768;
         template <typename = void>
         using type = fragment<matrix_b, 16, BD, BK, T, L>;
     };
     template <uint32_t BD, uint32_t BK, typename T, typename L>
     struct FragOf<accumulator, BD, BK, T, L>
     {
-        static constexpr bool supported = BK % 16 == 0;
+        static constexpr bool supported = BK % 16 == 0 && BD * BK * sizeof(T) <= 32768;
         template <typename = void>
         using type = fragment<accumulator, BD, BK, 16, T, L>;
     };
@@ -143,6 +144,10 @@ namespace
             return by_layout<MatrixT, BD, 32, SweepT>(col, mode, a);
         case 64:
             return by_layout<MatrixT, BD, 64, SweepT>(col, mode, a);
+        case 128:
+            return by_layout<MatrixT, BD, 128, SweepT>(col, mode, a);
+        case 256:
+            return by_layout<MatrixT, BD, 256, SweepT>(col, mode, a);
         default:
             return -1;
         }

@@ -274,7 +274,13 @@ extern "C" int frag_unit_transpose(int case_id, const void* src, void* dst, uint
     X(22, 16, 16, 32, float8_t, float32_t, float32_t, row_major, col_major)                   \
     X(23, 32, 32, 16, bfloat8_t, float32_t, float32_t, col_major, row_major)                  \
     X(24, 16, 16, 8, xfloat32_t, float32_t, float32_t, row_major, col_major)                  \
-    X(25, 32, 32, 4, xfloat32_t, float32_t, float32_t, col_major, row_major)
+    X(25, 32, 32, 4, xfloat32_t, float32_t, float32_t, col_major, row_major)                  \
+    X(26, 32, 32, 8, int8_t, int32_t, int32_t, row_major, col_major)                          \
+    X(27, 32, 32, 8, int8_t, int32_t, int32_t, col_major, row_major)                          \
+    X(28, 32, 32, 2, float32_t, float32_t, float32_t, row_major, col_major)                   \
+    X(29, 32, 32, 2, float32_t, float32_t, float32_t, col_major, row_major)                   \
+    X(30, 32, 32, 2, xfloat32_t, float32_t, float32_t, row_major, row_major)                  \
+    X(31, 16, 16, 24, int8_t, int32_t, int32_t, row_major, row_major)
 
 extern "C" int frag_unit_gemm(int case_id, uint32_t m, uint32_t n, uint32_t k, const void* a, const void* b,
                               const void* c, void* d, uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,

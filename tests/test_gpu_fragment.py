@@ -47,6 +47,10 @@ GEMM_CASES = {
     # OCP fp8 inputs (exact products, fp32 accumulation) and xfloat32 (inputs rounded to TF32: 2^-11 relative each)
     22: ("e4m3", np.float32, 0, 1, TOL_F32_OUT), 23: ("e5m2", np.float32, 1, 0, TOL_F32_OUT),
     24: ("xf32", np.float32, 0, 1, 2e-3), 25: ("xf32", np.float32, 1, 0, 2e-3),
+    # the reference's minimum K of 32 x 32 blocks for int8 (8) and fp32 (2): atoms without an mma.sync shape of their own
+    26: (np.int8, np.int32, 0, 1, None), 27: (np.int8, np.int32, 1, 0, None),
+    28: (np.float32, np.float32, 0, 1, 1e-5), 29: (np.float32, np.float32, 1, 0, 1e-5),
+    30: ("xf32", np.float32, 0, 0, 2e-3), 31: (np.int8, np.int32, 0, 0, None),
 }
 _TORCH_LOWP = {"bf16": torch.bfloat16, "e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
 

@@ -1,6 +1,6 @@
 """Systematic fragment-shape sweep (tests/csrc/frag_sweep.cu): for every point of the reference unit suites'
-parameter space (test/unit/unit_test_params.hpp:86-141: BlockDim 16..256 x BlockK 8..64 x {i8, f16, f32, f64} x
-{row, col} major, matrix_a / matrix_b / accumulator) a load -> store round trip must reproduce the block exactly,
+parameter space (test/unit/unit_test_params.hpp:86-141: BlockDim 16..256 x BlockK 8..64, plus 128 and 256 of its
+extended set, x {i8, f16, f32, f64} x {row, col} major, matrix_a / matrix_b / accumulator) a load -> store round trip must reproduce the block exactly,
 leave every padding and guard element untouched (the contamination test), and the cooperative forms with 1, 4 and
 6 waves must move the same block collectively."""
 import ctypes as C
@@ -18,7 +18,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 KINDS = ["matrix_a", "matrix_b", "accumulator"]
 TYPES = [np.int8, np.float16, np.float32, np.float64]
 DIMS = [16, 32, 64, 128, 256]
-KS = [8, 16, 32, 64]
+KS = [8, 16, 32, 64, 128, 256]
 MARK = {np.int8: 99, np.float16: 777.0, np.float32: 777.0, np.float64: 777.0}
 
 
@@ -34,12 +34,11 @@ def sweep():
     return h
 
 
-def offered(kind, bk, dt):
-    """Fragments are whole mma.sync operands: at least 16 deep for 8-bit inputs, 8 for 16-bit, 4 for 32- / 64-bit;
-    accumulator blocks at least 16 wide."""
-    if kind == 2:
-        return bk % 16 == 0
-    return bk % {1: 16, 2: 8, 4: 4, 8: 4}[np.dtype(dt).itemsize] == 0
+def offered(kind, bd, bk, dt):
+    """Accumulator blocks are at least 16 wide; a block is at most 32 KB (256 registers per lane)."""
+    if bd * bk * np.dtype(dt).itemsize > 32768:
+        return False
+    return bk % 16 == 0 if kind == 2 else True
 
 
 def rand_matrix(rows, cols, dt, seed):
@@ -65,8 +64,8 @@ def test_fragment_shape_sweep(sweep, kind, bd, bk, ti):
     dt = TYPES[ti]
     shape = (C.c_uint32 * 4)()
     rc = sweep.frag_sweep(kind, bd, bk, ti, 0, 0, None, None, 0, 0, 0, 0, 1, 1, 1, shape)
-    if not offered(kind, bk, dt):
-        assert rc == -3  # documented gap: no half-operand fragments
+    if not offered(kind, bd, bk, dt):
+        assert rc == -3  # documented limits
         return
     assert rc == 0
     bh, bw, eb, ne = list(shape)
