@@ -63,6 +63,9 @@ int b200wmma_version(void);
  *                        accumulator's drain overlaps the other's MMAs), 2 = slab by slab
  *   "dlrm_bwd_stages"    one-warp-per-sample DLRM backward kernel: depth of each warp's sample ring, 2 or 3
  *   "dlrm_bwd_warps"     ... and warps per CTA, 1..12 (clipped to what fits in shared memory)
+ *   "dlrm_fwd_stages", "dlrm_fwd_warps"   the same two for the forward kernel
+ *   "gemm_f64_kernel"    b200wmma_gemm_f64: 1 = the cp.async-fed kernel (the one ragged shapes always get), 2 = the TMA-fed
+ *                        kernel, B200WMMA_ERR_UNSUPPORTED where it cannot run (a contiguous extent that is no multiple of 4)
  * Unknown keys and out-of-range values return B200WMMA_ERR_INVALID_ARG.  The library reads no environment variable
  * except B200WMMA_NCCL_LIBRARY (see the multi-GPU section). */
 int b200wmma_set_tuning(const char* key, int value);

@@ -138,7 +138,10 @@ extern "C" int b200wmma_set_tuning(const char* key, int value)
                  {"gemm_split_tail", tuning::GEMM_SPLIT_TAIL, 0, 2},
                  {"gemm_split_fixup", tuning::GEMM_SPLIT_FIXUP, 0, 4096},
                  {"dlrm_bwd_stages", tuning::DLRM_BWD_STAGES, 0, 3},
-                 {"dlrm_bwd_warps", tuning::DLRM_BWD_WARPS, 0, 12}};
+                 {"dlrm_bwd_warps", tuning::DLRM_BWD_WARPS, 0, 12},
+                 {"dlrm_fwd_stages", tuning::DLRM_FWD_STAGES, 0, 3},
+                 {"dlrm_fwd_warps", tuning::DLRM_FWD_WARPS, 0, 12},
+                 {"gemm_f64_kernel", tuning::GEMM_F64_KERNEL, 0, 2}};
     for(const auto& t : table)
         if(std::strcmp(key, t.name) == 0)
         {

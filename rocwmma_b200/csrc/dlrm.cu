@@ -30,10 +30,9 @@ namespace b200wmma
 {
     namespace dlrm
     {
-        constexpr int      WARPS       = 4;
         constexpr int      MAX_M       = 32;
         constexpr int      MAX_K       = 256;
-        constexpr int      FWD_STAGES  = 3;
+        constexpr int      FWD_MAX_WARPS = 12; // both kernels take their warp count from the launch
         constexpr int      BWD_MAX_WARPS = 12; // the backward kernel takes its warp count from the launch
         constexpr int      BWD_BATCH     = 4; // 16-column slabs of dX in flight per warp
         constexpr int      TPITCH      = 40; // halfs per row of the 32x32 symmetric matrix (+8 pad)
@@ -74,8 +73,9 @@ namespace b200wmma
 
         // ---------------------------------- forward ----------------------------------------
         // Shared memory per warp: FWD_STAGES sample tiles, two output rows (double-buffered bulk
-        // stores), FWD_STAGES mbarriers.
-        __global__ void __launch_bounds__(WARPS * 32)
+        // stores), FWD_STAGES mbarriers.  Warps per CTA = blockDim.x / 32, chosen by the launch.
+        template <int FWD_STAGES>
+        __global__ void __launch_bounds__(FWD_MAX_WARPS * 32)
             dlrm_fwd_kernel(const __grid_constant__ CUtensorMap tmap_x, __half* __restrict__ output,
                             uint32_t m, uint32_t m_stride, uint32_t k, uint32_t batch,
                             uint32_t out_stride, unsigned* status)
@@ -85,6 +85,7 @@ namespace b200wmma
             const uint32_t base  = (raw + 1023u) & ~1023u;
             uint8_t*       smem  = smem_raw + (base - raw);
             const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+            const uint32_t WARPS     = blockDim.x >> 5;
             const uint32_t nbox      = (k + 63u) >> 6;
             const uint32_t tile_b    = nbox * BOX_BYTES;
             const uint32_t orow_b    = out_stride * 2u; // multiple of 16
@@ -227,10 +228,12 @@ namespace b200wmma
 
         // ---------------------------------- backward ---------------------------------------
         // Shared memory per warp: BWD_STAGES x (sample tile + upstream row), the symmetric matrix,
-        // BWD_STAGES mbarriers.  The launch picks the warp count (blockDim.x / 32) and the ring depth from what
-        // fits in shared memory: three stages where at least four warps fit (two samples' loads in flight behind the
-        // one a warp works on, and a stage is only handed back to the loader after the NEXT sample's stores were
-        // issued, so no warp waits for its own stores to be read), two stages otherwise.
+        // BWD_STAGES mbarriers.  The launch picks the warp count (blockDim.x / 32): as many as shared memory holds
+        // with two stages each.  Measured at B = 16384, k = 128 on one B200, per launch: 6 / 8 / 10 / 11 warps per SM
+        // with two stages 66.5 / 55.3 / 48.9 / 46.4 us (a device copy of the same bytes: 44.3 us); three stages (the
+        // previous sample's stage is handed back to the loader after this sample's stores were issued, so no warp
+        // waits for its own stores to be read) fit 7 warps and take 58.7 us.  A warp works through its samples one
+        // after the other, so the number of warps, not the depth of each warp's ring, hides the latencies.
         template <int BWD_STAGES>
         __global__ void __launch_bounds__(BWD_MAX_WARPS * 32)
             dlrm_bwd_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_g,
@@ -457,7 +460,19 @@ namespace b200wmma
             return B200WMMA_OK;
         }
 
-        static uint32_t grid_for(uint32_t batch, const void* kernel, size_t smem_bytes, uint32_t warps = WARPS)
+        // Warps per CTA: as many as fit (`fit`), but no more than spreads a small batch over every SM.
+        static uint32_t warps_for(uint32_t batch, size_t fit, int max_warps, int forced)
+        {
+            int dev = 0, sms = 148;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            uint32_t warps = static_cast<uint32_t>(std::min<size_t>(max_warps, fit));
+            if(forced > 0)
+                return std::min<uint32_t>(static_cast<uint32_t>(forced), warps);
+            return std::min<uint32_t>(warps, std::max<uint32_t>(4u, ceil_div(batch, static_cast<uint32_t>(sms))));
+        }
+
+        static uint32_t grid_for(uint32_t batch, const void* kernel, size_t smem_bytes, uint32_t warps)
         {
             int dev = 0, sms = 148, per_sm = 1;
             cudaGetDevice(&dev);
@@ -474,7 +489,7 @@ namespace b200wmma
         // the tail of the preceding kernel in the stream; the kernel itself waits for that kernel's completion
         // (grid_dep_wait) before it touches global memory, so stream order is kept.
         static cudaLaunchConfig_t pdl_config(cudaLaunchAttribute (&attr)[1], uint32_t grid, size_t smem, cudaStream_t stream,
-                                             uint32_t warps = WARPS)
+                                             uint32_t warps)
         {
             attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
             attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -523,18 +538,30 @@ extern "C" int b200wmma_dlrm_fwd(const void* input, void* output, uint32_t m, ui
     if(int e = sample_tmap(&tm_x, input, m, m_stride, k, batch))
         return e;
     const uint32_t nbox = (k + 63) / 64;
-    const size_t   smem = 1024 + static_cast<size_t>(WARPS) * (FWD_STAGES * nbox * BOX_BYTES + 2 * out_stride * 2 + FWD_STAGES * 8) + 16;
-    static size_t attr_set_dev[MAX_DEVICES];
-    size_t&       attr_set = attr_set_dev[current_device_slot()];
+    auto per_warp = [&](uint32_t stages) -> size_t {
+        return static_cast<size_t>(stages) * nbox * BOX_BYTES + 2 * out_stride * 2 + stages * 8;
+    };
+    // A warp's samples go through one after the other, so what keeps the memory system busy is the number of warps
+    // per SM: two stages per warp and as many warps as shared memory holds.
+    const size_t budget = 227 * 1024 - 1024 - 16;
+    uint32_t     stages = 2;
+    if(const int forced = tuning::get(tuning::DLRM_FWD_STAGES); forced == 2 || forced == 3)
+        stages = static_cast<uint32_t>(forced);
+    const uint32_t warps = warps_for(batch, budget / per_warp(stages), FWD_MAX_WARPS, tuning::get(tuning::DLRM_FWD_WARPS));
+    B200_REQUIRE(warps >= 1, B200WMMA_ERR_INVALID_ARG, "dlrm_fwd: one sample's tiles do not fit in shared memory");
+    auto* const  dlrm_fwd_kernel = stages == 3 ? dlrm::dlrm_fwd_kernel<3> : dlrm::dlrm_fwd_kernel<2>;
+    const size_t smem            = 1024 + warps * per_warp(stages) + 16;
+    static size_t attr_set_dev[MAX_DEVICES][2];
+    size_t&       attr_set = attr_set_dev[current_device_slot()][stages - 2];
     if(smem > 48 * 1024 && smem > attr_set)
     {
         B200_CHECK_CUDA(cudaFuncSetAttribute(dlrm_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(smem)));
         attr_set = smem;
     }
-    const uint32_t grid = grid_for(batch, reinterpret_cast<const void*>(dlrm_fwd_kernel), smem);
+    const uint32_t grid = grid_for(batch, reinterpret_cast<const void*>(dlrm_fwd_kernel), smem, warps);
     cudaLaunchAttribute attr[1];
-    cudaLaunchConfig_t  cfg = pdl_config(attr, grid, smem, as_stream(stream));
+    cudaLaunchConfig_t  cfg = pdl_config(attr, grid, smem, as_stream(stream), warps);
     B200_CHECK_CUDA(cudaLaunchKernelEx(&cfg, dlrm_fwd_kernel, tm_x, static_cast<__half*>(output), m, m_stride, k, batch,
                                        out_stride, status));
     return B200WMMA_OK;
@@ -577,21 +604,12 @@ extern "C" int b200wmma_dlrm_bwd(const void* input, const void* upstream, void* 
     auto per_warp = [&](uint32_t stages) -> size_t {
         return static_cast<size_t>(stages) * (nbox * BOX_BYTES + up_slot) + MAX_M * TPITCH * 2 + stages * 8;
     };
-    // ring depth and warps per CTA from what one SM's shared memory holds (see the kernel's header comment)
+    // warps per CTA from what one SM's shared memory holds (see the kernel's header comment)
     const size_t budget = 227 * 1024 - 1024 - 16;
-    uint32_t     stages = 3, warps = static_cast<uint32_t>(std::min<size_t>(8, budget / per_warp(3)));
-    if(warps < 4)
-    {
-        stages = 2;
-        warps  = static_cast<uint32_t>(std::min<size_t>(8, budget / per_warp(2)));
-    }
+    uint32_t     stages = 2;
     if(const int forced = tuning::get(tuning::DLRM_BWD_STAGES); forced == 2 || forced == 3)
-    {
         stages = static_cast<uint32_t>(forced);
-        warps  = static_cast<uint32_t>(std::min<size_t>(8, budget / per_warp(stages)));
-    }
-    if(const int forced = tuning::get(tuning::DLRM_BWD_WARPS); forced > 0)
-        warps = static_cast<uint32_t>(std::min<size_t>(std::min<int>(forced, BWD_MAX_WARPS), budget / per_warp(stages)));
+    const uint32_t warps = warps_for(batch, budget / per_warp(stages), BWD_MAX_WARPS, tuning::get(tuning::DLRM_BWD_WARPS));
     B200_REQUIRE(warps >= 1, B200WMMA_ERR_INVALID_ARG, "dlrm_bwd: one sample's tiles do not fit in shared memory");
     auto* const  kernel = stages == 3 ? dlrm_bwd_kernel<3> : dlrm_bwd_kernel<2>;
     const size_t smem   = 1024 + warps * per_warp(stages) + 16;

@@ -228,6 +228,19 @@ namespace b200wmma
                          : "memory");
         }
 
+        __device__ __forceinline__ void
+            tma_load_3d(uint32_t dst_smem, const void* tmap, int32_t c0, int32_t c1, int32_t c2, uint32_t bar)
+        {
+            asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+                         " [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst_smem),
+                         "l"(reinterpret_cast<uint64_t>(tmap)),
+                         "r"(c0),
+                         "r"(c1),
+                         "r"(c2),
+                         "r"(bar)
+                         : "memory");
+        }
+
         // 1-D bulk copy global -> shared (this CTA); both addresses 16-byte aligned, size a multiple of 16.
         __device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar)
         {

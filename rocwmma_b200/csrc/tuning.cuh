@@ -17,6 +17,9 @@ namespace b200wmma
             GEMM_MMA_ORDER    = 3, // 512x256 kernel, first / last K slabs of a tile: 1 = by accumulator, 2 = by slab
             DLRM_BWD_STAGES   = 6, // one-warp-per-sample DLRM backward kernel: ring depth 2 or 3
             DLRM_BWD_WARPS    = 7, // ... and warps per CTA (1..12, clipped to what fits in shared memory)
+            DLRM_FWD_STAGES   = 8, // the same two for the forward kernel
+            DLRM_FWD_WARPS    = 9,
+            GEMM_F64_KERNEL   = 10, // fp64 GEMM: 1 = the cp.async kernel, 2 = the TMA-fed kernel or an error where it cannot run
             NUM_KEYS
         };
         int  get(Key k);

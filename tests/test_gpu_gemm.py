@@ -453,6 +453,36 @@ def test_gemm_f64_all_layouts(la, lb, lcd, m, n, k):
     assert np.isnan(d.cpu().numpy()[:, ref.shape[1]:]).all()   # pitch padding untouched
 
 
+@pytest.mark.parametrize("which", [1, 2], ids=["cp_async", "tma"])
+@pytest.mark.parametrize("la,lb", [(0, 1), (1, 0), (0, 0), (1, 1)], ids=["RC", "CR", "RR", "CC"])
+def test_gemm_f64_both_kernels(la, lb, which):
+    """The fp64 GEMM has a TMA-fed kernel (contiguous extents that are multiples of 4) and a cp.async-fed one (everything
+    else); both on one shape that is a multiple of 4 but of no tile size, K spanning several slabs with a ragged last
+    one, padded pitches.  `gemm_f64_kernel` = 2 fails instead of falling back, so the TMA-fed kernel provably ran."""
+    m, n, k = 300, 204, 100
+    a = G.uniform_np(G.SEED_A, (m, k), np.float64); b = G.uniform_np(G.SEED_B, (k, n), np.float64)
+    c = G.uniform_np(G.SEED_C, (m, n), np.float64)
+    def store(x, col, pad):
+        t = np.ascontiguousarray(x.T if col else x)
+        out = np.full((t.shape[0], t.shape[1] + pad), np.nan)
+        out[:, :t.shape[1]] = t
+        return out, t.shape[1] + pad
+    (sa, lda), (sb, ldb) = store(a, la, 6), store(b, lb, 2)
+    d = nan_filled((m, n), torch.float64)
+    api.set_tuning("gemm_f64_kernel", which)
+    try:
+        api.gemm_f64(m, n, k, dev(sa), dev(sb), dev(c), d, lda, ldb, n, n, 1.5, 0.5, la, lb, 0)
+        assert_status_ok()
+        if which == 2:   # a shape without the 3-D views is refused, not silently given the other kernel
+            with pytest.raises(api.B200WmmaError):
+                api.gemm_f64(m, n, 98, dev(sa), dev(sb), dev(c), d, lda, ldb, n, n, 1.5, 0.5, 0, 1, 0)
+    finally:
+        api.set_tuning("gemm_f64_kernel", 0)
+    nat = lambda x, col: np.ascontiguousarray(x.T if col else x)
+    ref = R.gemm(R.port(), m, n, k, nat(a, la).ravel(), nat(b, lb).ravel(), c.ravel(), 1.5, 0.5, np.float64, la, lb, 0, 0).reshape(m, n)
+    assert gemm_rel_err(d.cpu().numpy(), ref, R.gemm_abs_bound(m, n, k, a, b, c, 1.5, 0.5)) <= TOL_F64_OUT
+
+
 @pytest.mark.parametrize("k", [64, 128, 320])
 def test_gemm_many_tiles_per_sm_pair_short_k(k):
     """More output tiles than SM pairs with only 1-5 K slabs per tile: the persistent kernels walk their operand
