@@ -965,6 +965,20 @@ def run_reference_arm(args, wl):
 
 
 # ---------------------------------------------------------------------------------------- GPU arm
+_MMA_SYNC_RATE = {}
+
+
+def mma_sync_rate(kind):
+    """Measured issue rate (TFLOP/s) of mma.sync m16n8k16 f16->f32 (kind 0) / m16n8k8 f64 (kind 1) on this GPU; cached."""
+    if kind not in _MMA_SYNC_RATE:
+        try:
+            from rocwmma_b200 import api
+            _MMA_SYNC_RATE[kind] = api.measure_mma_sync_rate(kind)
+        except Exception:
+            _MMA_SYNC_RATE[kind] = None
+    return _MMA_SYNC_RATE[kind]
+
+
 def roofline_of(wl, ms_step, peaks, copy_same):
     """roofline object of one workload from its measured step time (this rank's share of the work / this GPU's peak)."""
     if wl.bound == "tensor":
@@ -984,7 +998,7 @@ def roofline_of(wl, ms_step, peaks, copy_same):
             peak_note = "2 x cuBLAS bf16 8192^3 burst, standing in for the dense int8 rate"
         elif wl.dtype == "f64":
             peak = 40.0
-            peak_note = "nominal B200 fp64 tensor rate; no measured figure"
+            peak_note = "nominal B200 fp64 tensor rate"
         elif getattr(wl, "legacy_mma", False):
             peak_note = "cuBLAS bf16 8192^3 burst (tcgen05); this workload runs on the warp-level mma.sync path of the fragment API"
         else:
@@ -1001,6 +1015,14 @@ def roofline_of(wl, ms_step, peaks, copy_same):
         if nominal:
             roof["nominal_peak"] = nominal
             roof["frac_of_nominal"] = achieved / nominal
+        # kernels built on warp-level mma.sync: the rate at which this GPU issues that instruction from registers,
+        # measured just now (b200wmma_measure_mma_sync_rate), is the bound that applies to them
+        kind = 1 if wl.dtype == "f64" else (0 if getattr(wl, "legacy_mma", False) else None)
+        if kind is not None:
+            rate = mma_sync_rate(kind)
+            if rate:
+                roof["mma_sync_rate"] = rate
+                roof["frac_of_mma_sync_rate"] = achieved / rate
         return roof
     peak = peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"])
     nbytes = wl.bytes_per_sample * wl.work_local if hasattr(wl, "bytes_per_sample") else wl.work_local

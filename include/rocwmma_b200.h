@@ -66,6 +66,8 @@ int b200wmma_version(void);
  *   "dlrm_fwd_stages", "dlrm_fwd_warps"   the same two for the forward kernel
  *   "gemm_f64_kernel"    b200wmma_gemm_f64: 1 = the cp.async-fed kernel (the one ragged shapes always get), 2 = the TMA-fed
  *                        kernel, B200WMMA_ERR_UNSUPPORTED where it cannot run (a contiguous extent that is no multiple of 4)
+ *   "frag_perf_slab_k"   b200wmma_perf_hgemm_fragment: K depth of one shared-memory slab, 16 (the default), 32 or 64
+ *                        (used when it divides k)
  * Unknown keys and out-of-range values return B200WMMA_ERR_INVALID_ARG.  The library reads no environment variable
  * except B200WMMA_NCCL_LIBRARY (see the multi-GPU section). */
 int b200wmma_set_tuning(const char* key, int value);
@@ -286,6 +288,13 @@ int b200wmma_perf_hgemm_fragment(uint32_t m, uint32_t n, uint32_t k,
                                  const void* a, const void* b, const void* c, void* d,
                                  uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,
                                  float alpha, float beta, void* stream);
+
+/* Measures, on the current device, the rate at which the SMs issue the warp-level tensor-core instruction the
+ * fragment API's 16-bit multiplies (kind 0: mma.sync m16n8k16, fp16 inputs, fp32 accumulate) or the fp64 GEMM
+ * (kind 1: mma.sync m16n8k8, fp64) are built on: every SM runs 16 warps that issue it back to back from registers.
+ * *tflops receives the rate; it is the denominator for those kernels' throughput.  Synchronises `stream`; allocates
+ * and frees a small device buffer.  No reference counterpart (a measurement aid). */
+int b200wmma_measure_mma_sync_rate(int kind, double* tflops, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * DLRM dot interaction.

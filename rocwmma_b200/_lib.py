@@ -57,6 +57,7 @@ SIGNATURES = {
                                         C.c_int, vp]),
     "b200wmma_perf_hgemm_fragment": (C.c_int, [u32, u32, u32, vp, vp, vp, vp, u32, u32, u32, u32,
                                                f32, f32, vp]),
+    "b200wmma_measure_mma_sync_rate": (C.c_int, [C.c_int, C.POINTER(C.c_double), vp]),
     "b200wmma_dlrm_fwd": (C.c_int, [vp, vp, u32, u32, u32, u32, u32, vp]),
     "b200wmma_dlrm_bwd": (C.c_int, [vp, vp, vp, vp, u32, u32, u32, u32, u32, C.c_int, vp]),
     "b200wmma_dlrm_fwd_f32": (C.c_int, [vp, vp, u32, u32, u32, u32, u32, vp]),

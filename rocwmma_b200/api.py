@@ -221,6 +221,13 @@ def simple_hgemm(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta):
                                       alpha, beta, out_type, _stream()))
 
 
+def measure_mma_sync_rate(kind):
+    """TFLOP/s at which the device issues mma.sync from registers: kind 0 = m16n8k16 fp16 -> fp32, 1 = m16n8k8 fp64."""
+    out = C.c_double(0.0)
+    check(lib().b200wmma_measure_mma_sync_rate(int(kind), C.byref(out), _stream()))
+    return out.value
+
+
 def perf_hgemm_fragment(m, n, k, a, b, c, d, lda, ldb, ldc, ldd, alpha, beta):
     for t, nm in ((a, "a"), (b, "b"), (c, "c"), (d, "d")):
         _need(t, torch.float16, nm)

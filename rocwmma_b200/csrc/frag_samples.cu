@@ -12,6 +12,7 @@
 // The fast GEMM of this library is the tcgen05 kernel (gemm_tc05.cu); these two go through
 // warp-level mma.sync fragments like any user kernel would.
 #include "common.cuh"
+#include "tuning.cuh"
 
 #include <rocwmma/rocwmma.hpp>
 #include <rocwmma/rocwmma_coop.hpp>
@@ -62,7 +63,10 @@ namespace b200wmma
 
         // ------------------------------ perf_hgemm on fragments --------------------------------
         // 8 warps as 4 (x) by 2 (y); each warp owns a 32 x 64 tile = 2 x 4 blocks of 16 x 16;
-        // the thread block owns a 128 x 128 macro tile and walks K in steps of 16.
+        // the thread block owns a 128 x 128 macro tile and walks K in slabs of SLAB_K (a multiple of the blocks' K = 16):
+        // one cooperative global read, one shared-memory write and one barrier per slab, SLAB_K / 16 rounds of block
+        // multiplies on it.  The sample's own slab is one block deep (samples/perf_hgemm.cpp:264-271), and so is the
+        // default here; deeper slabs are selectable for measurement (see the launch code for what they cost).
         constexpr uint32_t P_M = 16, P_N = 16, P_K = 16;
         constexpr uint32_t P_BLOCKS_X = 2, P_BLOCKS_Y = 4;
         constexpr uint32_t P_TBLOCK_X = 128, P_TBLOCK_Y = 2;
@@ -83,32 +87,42 @@ namespace b200wmma
         using MmaB   = fragment<matrix_b, P_M, P_N, P_K, PIn, PLayoutB>;
         using MmaC   = fragment<accumulator, P_M, P_N, P_K, POut, PLayoutC>;
         using MmaAcc = fragment<accumulator, P_M, P_N, P_K, PCmp>;
-        // whole-macro-tile K slabs read cooperatively from global memory
-        using GlobalA = fragment<matrix_a, P_MACRO_X, P_N, P_K, PIn, PLayoutA>;
-        using GlobalB = fragment<matrix_b, P_M, P_MACRO_Y, P_K, PIn, PLayoutB>;
-        // shared memory holds A and B^T stacked, both as "matrix_a"-shaped column-major blocks
-        using LdsWriteA = ApplyDataLayout_t<GlobalA, PLayoutLds>;
-        using LdsWriteB = ApplyDataLayout_t<ApplyTranspose_t<GlobalB>, PLayoutLds>;
-        using LdsReadA  = ApplyDataLayout_t<MmaA, PLayoutLds>;
-        using LdsReadB  = ApplyDataLayout_t<ApplyTranspose_t<MmaB>, PLayoutLds>;
+        using LdsReadA = ApplyDataLayout_t<MmaA, PLayoutLds>;
+        using LdsReadB = ApplyDataLayout_t<ApplyTranspose_t<MmaB>, PLayoutLds>;
+        template <uint32_t SLAB_K>
+        struct PSlab
+        {
+            // whole-macro-tile K slabs read cooperatively from global memory
+            using GlobalA = fragment<matrix_a, P_MACRO_X, P_N, SLAB_K, PIn, PLayoutA>;
+            using GlobalB = fragment<matrix_b, P_M, P_MACRO_Y, SLAB_K, PIn, PLayoutB>;
+            // shared memory holds A and B^T stacked, both as "matrix_a"-shaped column-major blocks
+            using LdsWriteA = ApplyDataLayout_t<GlobalA, PLayoutLds>;
+            using LdsWriteB = ApplyDataLayout_t<ApplyTranspose_t<GlobalB>, PLayoutLds>;
+            static constexpr uint32_t LDS_HEIGHT = GetIOShape_t<LdsWriteA>::BlockHeight + GetIOShape_t<LdsWriteB>::BlockHeight;
+            static constexpr uint32_t LDS_WIDTH  = SLAB_K;
+            // leading dimension of the shared-memory block, padded by 16 bytes: consecutive K rows then start in
+            // different banks, which the 8 x 8 matrix loads and stores (eight 16-byte rows per instruction phase) need
+            // to be conflict-free
+            static constexpr uint32_t LDS_PAD   = 16 / sizeof(PIn);
+            static constexpr uint32_t LDS_LD    = (std::is_same<PLayoutLds, row_major>::value ? LDS_WIDTH : LDS_HEIGHT) + LDS_PAD;
+            static constexpr uint32_t LDS_ALLOC = LDS_LD * (std::is_same<PLayoutLds, row_major>::value ? LDS_HEIGHT : LDS_WIDTH);
+        };
 
-        constexpr uint32_t P_LDS_HEIGHT = GetIOShape_t<LdsWriteA>::BlockHeight + GetIOShape_t<LdsWriteB>::BlockHeight;
-        constexpr uint32_t P_LDS_WIDTH  = P_K;
-        constexpr uint32_t P_LDS_ELEMS  = P_LDS_HEIGHT * P_LDS_WIDTH;
-        // leading dimension of the shared-memory block, padded by 16 bytes: consecutive K rows then start in different
-        // banks, which the 8 x 8 matrix loads and stores (eight 16-byte rows per instruction phase) need to be conflict-free
-        constexpr uint32_t P_LDS_PAD    = 16 / sizeof(PIn);
-        constexpr uint32_t P_LDS_LD     = (std::is_same<PLayoutLds, row_major>::value ? P_LDS_WIDTH : P_LDS_HEIGHT) + P_LDS_PAD;
-        constexpr uint32_t P_LDS_ALLOC  = P_LDS_LD * (std::is_same<PLayoutLds, row_major>::value ? P_LDS_HEIGHT : P_LDS_WIDTH);
-
+        template <uint32_t SLAB_K>
         ROCWMMA_KERNEL void __launch_bounds__(P_TBLOCK_X* P_TBLOCK_Y)
             perf_hgemm_fragment_kernel(uint32_t m, uint32_t n, uint32_t k, PIn const* a, PIn const* b,
                                        POut const* c, POut* d, uint32_t lda, uint32_t ldb, uint32_t ldc,
                                        uint32_t ldd, PCmp alpha, PCmp beta)
         {
+            using S         = PSlab<SLAB_K>;
+            using GlobalA   = typename S::GlobalA;
+            using GlobalB   = typename S::GlobalB;
+            using LdsWriteA = typename S::LdsWriteA;
+            using LdsWriteB = typename S::LdsWriteB;
+            constexpr uint32_t P_LDS_LD = S::LDS_LD;
             extern __shared__ __align__(16) unsigned char lds_raw[];
             PIn* ldsLo = reinterpret_cast<PIn*>(lds_raw);
-            PIn* ldsHi = ldsLo + P_LDS_ALLOC;
+            PIn* ldsHi = ldsLo + S::LDS_ALLOC;
 
             const auto warpCoord  = make_coord2d(threadIdx.x / Constants::AMDGCN_WAVE_SIZE, threadIdx.y);
             const auto warpOffset = warpCoord * make_coord2d(P_WARP_TILE_X, P_WARP_TILE_Y);
@@ -124,8 +138,8 @@ namespace b200wmma
             using MapLB = GetDataLayout_t<LdsWriteB>;
             size_t       offA  = MapGA::fromMatrixCoord(make_coord2d(get<0>(macroCoord), 0u), lda);
             size_t       offB  = MapGB::fromMatrixCoord(make_coord2d(0u, get<1>(macroCoord)), ldb);
-            const size_t stepA = MapGA::fromMatrixCoord(make_coord2d(0u, P_K), lda);
-            const size_t stepB = MapGB::fromMatrixCoord(make_coord2d(P_K, 0u), ldb);
+            const size_t stepA = MapGA::fromMatrixCoord(make_coord2d(0u, SLAB_K), lda);
+            const size_t stepB = MapGB::fromMatrixCoord(make_coord2d(SLAB_K, 0u), ldb);
 
             const uint32_t ldsWriteA = 0u;
             const uint32_t ldsWriteB = MapLA::fromMatrixCoord(make_coord2d(GetIOShape_t<LdsWriteA>::BlockHeight, 0u), P_LDS_LD);
@@ -133,6 +147,7 @@ namespace b200wmma
             const uint32_t ldsReadB  = ldsWriteB + MapLB::fromMatrixCoord(make_coord2d(get<1>(warpOffset), 0u), P_LDS_LD);
             const uint32_t blockStepA = GetDataLayout_t<LdsReadA>::fromMatrixCoord(make_coord2d(GetIOShape_t<LdsReadA>::BlockHeight, 0u), P_LDS_LD);
             const uint32_t blockStepB = GetDataLayout_t<LdsReadB>::fromMatrixCoord(make_coord2d(GetIOShape_t<LdsReadB>::BlockHeight, 0u), P_LDS_LD);
+            const uint32_t kStep      = GetDataLayout_t<LdsReadA>::fromMatrixCoord(make_coord2d(0u, P_K), P_LDS_LD); // one block deeper into the slab
 
             GlobalA grA;
             GlobalB grB;
@@ -156,27 +171,31 @@ namespace b200wmma
                     fill_fragment(acc[i][j], 0.0f);
 
             auto ldsStep = [&](PIn const* lds) {
-                MmaA fa[P_BLOCKS_X];
-                MmaB fb[P_BLOCKS_Y];
 #pragma unroll
-                for(uint32_t i = 0; i < P_BLOCKS_X; ++i)
+                for(uint32_t ks = 0; ks < SLAB_K / P_K; ++ks)
                 {
-                    LdsReadA tmp;
-                    load_matrix_sync(tmp, lds + ldsReadA + i * blockStepA, P_LDS_LD);
-                    fa[i] = applyDataLayout<PLayoutA>(tmp);
-                }
+                    MmaA fa[P_BLOCKS_X];
+                    MmaB fb[P_BLOCKS_Y];
 #pragma unroll
-                for(uint32_t j = 0; j < P_BLOCKS_Y; ++j)
-                {
-                    LdsReadB tmp;
-                    load_matrix_sync(tmp, lds + ldsReadB + j * blockStepB, P_LDS_LD);
-                    fb[j] = applyDataLayout<PLayoutB>(applyTranspose(tmp));
-                }
-#pragma unroll
-                for(uint32_t i = 0; i < P_BLOCKS_X; ++i)
+                    for(uint32_t i = 0; i < P_BLOCKS_X; ++i)
+                    {
+                        LdsReadA tmp;
+                        load_matrix_sync(tmp, lds + ldsReadA + i * blockStepA + ks * kStep, P_LDS_LD);
+                        fa[i] = applyDataLayout<PLayoutA>(tmp);
+                    }
 #pragma unroll
                     for(uint32_t j = 0; j < P_BLOCKS_Y; ++j)
-                        mma_sync(acc[i][j], fa[i], fb[j], acc[i][j]);
+                    {
+                        LdsReadB tmp;
+                        load_matrix_sync(tmp, lds + ldsReadB + j * blockStepB + ks * kStep, P_LDS_LD);
+                        fb[j] = applyDataLayout<PLayoutB>(applyTranspose(tmp));
+                    }
+#pragma unroll
+                    for(uint32_t i = 0; i < P_BLOCKS_X; ++i)
+#pragma unroll
+                        for(uint32_t j = 0; j < P_BLOCKS_Y; ++j)
+                            mma_sync(acc[i][j], fa[i], fb[j], acc[i][j]);
+                }
             };
 
             // prologue: first K slab through registers into the low buffer
@@ -184,9 +203,9 @@ namespace b200wmma
             ldsWrite(ldsLo);
             synchronize_workgroup();
 
-            for(uint32_t kk = P_K; kk < k; kk += P_K)
+            for(uint32_t kk = SLAB_K; kk < k; kk += SLAB_K)
             {
-                globalRead(); // prefetch slab kk while slab kk - P_K is multiplied
+                globalRead(); // prefetch slab kk while slab kk - SLAB_K is multiplied
                 ldsStep(ldsLo);
                 ldsWrite(ldsHi);
                 synchronize_workgroup();
@@ -304,10 +323,36 @@ extern "C" int b200wmma_perf_hgemm_fragment(uint32_t m, uint32_t n, uint32_t k, 
         return e;
     const dim3   block(fragk::P_TBLOCK_X, fragk::P_TBLOCK_Y);
     const dim3   grid(m / fragk::P_MACRO_X, n / fragk::P_MACRO_Y);
-    const size_t lds = 2 * fragk::P_LDS_ALLOC * sizeof(fragk::PIn);
-    fragk::perf_hgemm_fragment_kernel<<<grid, block, lds, as_stream(stream)>>>(
-        m, n, k, static_cast<const fragk::PIn*>(a), static_cast<const fragk::PIn*>(b),
-        static_cast<const fragk::POut*>(c), static_cast<fragk::POut*>(d), lda, ldb, ldc, ldd, alpha, beta);
+    const int  forced = tuning::get(tuning::FRAG_PERF_SLAB_K);
+    const auto launch = [&](auto slab) {
+        constexpr uint32_t SLAB_K = decltype(slab)::value;
+        const size_t       lds    = 2 * fragk::PSlab<SLAB_K>::LDS_ALLOC * sizeof(fragk::PIn);
+        static bool        attr_ok_dev[MAX_DEVICES];
+        bool&              attr_ok = attr_ok_dev[current_device_slot()];
+        if(lds > 48 * 1024 && !attr_ok)
+        {
+            if(cudaFuncSetAttribute(fragk::perf_hgemm_fragment_kernel<SLAB_K>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(lds))
+               != cudaSuccess)
+                return;
+            attr_ok = true;
+        }
+        fragk::perf_hgemm_fragment_kernel<SLAB_K><<<grid, block, lds, as_stream(stream)>>>(
+            m, n, k, static_cast<const fragk::PIn*>(a), static_cast<const fragk::PIn*>(b),
+            static_cast<const fragk::POut*>(c), static_cast<fragk::POut*>(d), lda, ldb, ldc, ldd, alpha, beta);
+    };
+    // One block deep, as in the sample, unless b200wmma_set_tuning asks for a deeper slab that divides k.  Measured at
+    // 8192^3 on one B200: slabs of 16 / 32 / 64 give 81 / 49 / 48 TFLOP/s - the deeper slabs need 206 / 240 registers
+    // per thread, one thread block per SM instead of two, and lose more to occupancy than they gain per barrier.
+    uint32_t slab = 16u;
+    if((forced == 16 || forced == 32 || forced == 64) && k % static_cast<uint32_t>(forced) == 0)
+        slab = static_cast<uint32_t>(forced);
+    if(slab == 64)
+        launch(std::integral_constant<uint32_t, 64>{});
+    else if(slab == 32)
+        launch(std::integral_constant<uint32_t, 32>{});
+    else
+        launch(std::integral_constant<uint32_t, 16>{});
     B200_CHECK_CUDA(cudaGetLastError());
     return B200WMMA_OK;
 }
