@@ -2,9 +2,12 @@
 // (b200wmma_mg_*, b200wmma_shard_range).  The reference has no multi-GPU sample; the GEMM is the perf_hgemm form
 // (samples/perf_hgemm.cpp:713-941: A row-major, B column-major, C / D row-major fp16, alpha = beta = 1).
 //
-// Usage: multi_gpu_hgemm <rank> <nranks> <id file> [m n k]      (default 2048 x 4096 x 1024)
+// Usage: multi_gpu_hgemm <rank> <nranks> <id file> [m n k [run tag]]      (default 2048 x 4096 x 1024)
 // Start one process per rank, all with the same id file path on a file system they share.  Rank r uses device r.
-// Rank 0 creates the NCCL id and publishes it through the file; the others wait for it (30 s at most).
+// Rank 0 creates the NCCL id and publishes it through the file; the others wait for it (30 s at most).  The file
+// holds the run tag (any string, the same for all ranks of one run; give a fresh one per run, e.g. the launcher's pid)
+// in front of the id, and readers ignore a file with another tag: an id left behind by an aborted run is never taken
+// for this run's.  Rank 0 removes a stale file before it creates the id.
 #include "common.hpp"
 
 #include <chrono>
@@ -12,27 +15,40 @@
 #include <string>
 #include <thread>
 
-static bool publish_id(const char* path, const unsigned char* id)
+constexpr size_t TAG_BYTES = 32;
+static void      tag_field(const char* tag, char (&out)[TAG_BYTES])
+{
+    std::memset(out, 0, TAG_BYTES);
+    std::strncpy(out, tag, TAG_BYTES - 1);
+}
+
+static bool publish_id(const char* path, const char* tag, const unsigned char* id)
 {
     const std::string tmp = std::string(path) + ".tmp";
     FILE*             f   = std::fopen(tmp.c_str(), "wb");
     if(!f)
         return false;
-    const bool ok = std::fwrite(id, 1, B200WMMA_MG_ID_BYTES, f) == B200WMMA_MG_ID_BYTES;
+    char field[TAG_BYTES];
+    tag_field(tag, field);
+    const bool ok = std::fwrite(field, 1, TAG_BYTES, f) == TAG_BYTES
+                    && std::fwrite(id, 1, B200WMMA_MG_ID_BYTES, f) == B200WMMA_MG_ID_BYTES;
     std::fclose(f);
     return ok && std::rename(tmp.c_str(), path) == 0; // rename: readers never see a partial file
 }
 
-static bool fetch_id(const char* path, unsigned char* id)
+static bool fetch_id(const char* path, const char* tag, unsigned char* id)
 {
+    char want[TAG_BYTES], have[TAG_BYTES];
+    tag_field(tag, want);
     for(int tries = 0; tries < 300; ++tries)
     {
         if(FILE* f = std::fopen(path, "rb"))
         {
-            const size_t got = std::fread(id, 1, B200WMMA_MG_ID_BYTES, f);
+            const bool got = std::fread(have, 1, TAG_BYTES, f) == TAG_BYTES
+                             && std::fread(id, 1, B200WMMA_MG_ID_BYTES, f) == B200WMMA_MG_ID_BYTES;
             std::fclose(f);
-            if(got == B200WMMA_MG_ID_BYTES)
-                return true;
+            if(got && std::memcmp(want, have, TAG_BYTES) == 0)
+                return true; // (a file with another run's tag is a leftover: keep waiting for this run's)
         }
         std::this_thread::sleep_for(std::chrono::milliseconds(100));
     }
@@ -50,19 +66,21 @@ int main(int argc, char** argv)
     const char*    id_path = argv[3];
     const uint32_t m = argc > 6 ? std::atoi(argv[4]) : 2048, n = argc > 6 ? std::atoi(argv[5]) : 4096,
                    k = argc > 6 ? std::atoi(argv[6]) : 1024;
+    const char* run_tag = argc > 7 ? argv[7] : "untagged";
     CHECK_CUDA(cudaSetDevice(rank));
 
     unsigned char id[B200WMMA_MG_ID_BYTES];
     if(rank == 0)
     {
+        std::remove(id_path); // whatever an earlier run left there
         CHECK_B200(b200wmma_mg_unique_id(id));
-        if(!publish_id(id_path, id))
+        if(!publish_id(id_path, run_tag, id))
         {
             std::printf("cannot write %s\n", id_path);
             return 1;
         }
     }
-    else if(!fetch_id(id_path, id))
+    else if(!fetch_id(id_path, run_tag, id))
     {
         std::printf("rank %d: no id in %s after 30 s\n", rank, id_path);
         return 1;
