@@ -45,13 +45,17 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under profiles/
 # (None where no capture exists yet).
 NCU_TRAFFIC_BYTES = {
-    "gemm_f16": 1.144e9,   # profiles/gemm_tc05_f16_8192.md: 1.022 GB read + 122.4 MB written (512x256 pair kernel)
-    "gemm_i8": 1.416e9,    # profiles/gemm_tc05_i8_8192x8192x16384.md (256x256 pair kernel capture)
-    "gemm_i8_sp24": 8.595e8,  # profiles/gemm_tc05_sp24_8192x8192x16384.md (GEMM kernel; the re-tiling pre-pass adds ~33 MB)
-    "dlrm_fwd": 119.5e6,   # profiles/dlrm_dot_B16384.md
-    "dlrm_bwd": 195.8e6,   # profiles/dlrm_dot_B16384.md
-    "sgemv": 4.299e9,      # profiles/gemv_32768.md
-    "dgemv": 8.595e9,      # profiles/gemv_32768.md
+    "gemm_f16": 1.108e9,      # profiles/gemm_tc05_f16_8192.md: 986.6 MB read + 121.5 MB written (512x256 pair kernel)
+    "gemm_i8": 1.072e9,       # profiles/gemm_tc05_i8_8192x8192x16384.md: 833.4 + 238.2 MB (512x256 pair kernel)
+    "gemm_i8_sp24": 8.591e8,  # profiles/gemm_tc05_sp24_8192x8192x16384.md (GEMM kernel; the re-tiling pre-pass adds ~33 MB)
+    "gemm_i4": 6.234e8,       # profiles/gemm_tc05_i4_8192x8192x16384.md: 386.0 + 237.3 MB
+    "gemm_fp8": 9.165e8,      # profiles/gemm_tc05_fp8_8192.md: 676.4 + 240.1 MB
+    "gemm_f64": 1.354e9,      # profiles/gemm_f64_4096.md: 1233 + 120.4 MB
+    "frag_perf_hgemm": 2.300e9,  # profiles/frag_perf_hgemm_8192.md: 2169 + 131 MB
+    "dlrm_fwd": 119.1e6,      # profiles/dlrm_dot_B16384.md
+    "dlrm_bwd": 192.4e6,      # profiles/dlrm_dot_B16384.md
+    "sgemv": 4.299e9,         # profiles/gemv_32768.md
+    "dgemv": 8.595e9,         # profiles/gemv_32768.md
 }
 
 
