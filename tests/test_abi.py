@@ -96,10 +96,27 @@ def test_argument_checks(call, code):
 
 
 def test_set_tuning_round_trip():
+    """Every key the header documents is accepted at a legal value and reset; unknown keys and values out of range are
+    argument errors."""
     L = _lib.lib()
-    for key in (b"gemm_tile_variant", b"gemm_group_m", b"sp24_force_expand"):
-        assert L.b200wmma_set_tuning(key, 1) == 0
+    keys = {b"gemm_tile_variant": 1, b"gemm_group_m": 4, b"sp24_force_expand": 1, b"gemm_mma_order": 2, b"gemm_split_tail": 2,
+            b"gemm_split_fixup": 16, b"dlrm_bwd_stages": 3, b"dlrm_bwd_warps": 8, b"dlrm_fwd_stages": 3, b"dlrm_fwd_warps": 8,
+            b"gemm_f64_kernel": 1, b"frag_perf_slab_k": 32}
+    header = open(os.path.join(ROOT, "include", "rocwmma_b200.h")).read()
+    for key, value in keys.items():
+        assert f'"{key.decode()}"' in header, f"{key} is not documented in the header"
+        assert L.b200wmma_set_tuning(key, value) == 0
         assert L.b200wmma_set_tuning(key, 0) == 0
+    assert L.b200wmma_set_tuning(b"no_such_key", 1) == 1
+    assert L.b200wmma_set_tuning(b"gemm_f64_kernel", 7) == 1
+    assert L.b200wmma_set_tuning(None, 1) == 1
+
+
+def test_measure_mma_sync_rate_argument_checks():
+    L = _lib.lib()
+    out = C.c_double(0.0)
+    assert L.b200wmma_measure_mma_sync_rate(2, C.byref(out), None) == 1   # kinds are 0 and 1
+    assert L.b200wmma_measure_mma_sync_rate(0, None, None) == 1
 
 
 def test_shard_range_and_destroy_of_null():

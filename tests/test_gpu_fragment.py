@@ -251,3 +251,15 @@ def test_perf_hgemm_fragment_pipeline(m, n, k):
     ref = R.gemm(R.port(), m, n, k, sa.ravel(), b.ravel(), c.ravel(), 2.0, 2.0, np.float16, 1, 0).reshape(m, n)
     bound = R.gemm_abs_bound(m, n, k, a, b, c, 2.0, 2.0)
     assert gemm_rel_err(d.cpu().numpy(), ref, bound) <= TOL_F16_OUT
+
+
+def test_measured_mma_sync_rates_are_plausible():
+    """b200wmma_measure_mma_sync_rate: the register-only issue loops of the two warp-level tensor-core instructions the
+    fragment layer and the fp64 GEMM are built on.  On a B200 the fp16 instruction issues at several hundred TFLOP/s
+    and the fp64 one at 30-40; both repeat to within a few per cent."""
+    from rocwmma_b200 import api
+    f16 = [api.measure_mma_sync_rate(0) for _ in range(2)]
+    f64 = [api.measure_mma_sync_rate(1) for _ in range(2)]
+    assert 200.0 < min(f16) and max(f16) < 1200.0, f16
+    assert 20.0 < min(f64) and max(f64) < 45.0, f64
+    assert abs(f16[0] - f16[1]) / f16[0] < 0.1 and abs(f64[0] - f64[1]) / f64[0] < 0.1
