@@ -427,9 +427,25 @@ namespace
             slice_rows      = (slice_rows + 127u) & ~127u;
             chunk_rows      = slice_rows * static_cast<uint32_t>(nranks);
         }
-        const uint32_t chunks = (m + chunk_rows - 1) / chunk_rows;
+        // chunk i covers rows [bounds[i], bounds[i + 1]).  Single GPU: the call ends with the multiply and the copy-out of
+        // the LAST chunk, which nothing overlaps (the uploads are over by then), so the last 1024 rows go as 512 + 256 +
+        // 256: the tail after the last upload shrinks from a 16 MiB copy-out to a 4 MiB one.
+        std::vector<uint32_t> bounds;
+        for(uint32_t r = 0; r < m; r += chunk_rows)
+            bounds.push_back(r);
+        if(!(mg && nranks > 1) && bounds.size() >= 2 && m - bounds.back() >= 512)
+        {
+            const uint32_t last = bounds.back(), span = m - last;
+            const uint32_t half = (span / 2 + 127u) & ~127u, quarter = ((span - half) / 2 + 127u) & ~127u;
+            bounds.push_back(last + half);
+            if(quarter != 0 && last + half + quarter < m)
+                bounds.push_back(last + half + quarter);
+        }
+        bounds.push_back(m);
+        const uint32_t chunks = static_cast<uint32_t>(bounds.size()) - 1u;
+        const uint32_t padded_rows = ((m + chunk_rows - 1) / chunk_rows) * chunk_rows; // multi GPU: whole chunks
         // A on the device is sized in whole chunks: the last all-gather may move (never-read) rows past m
-        const size_t ba = mg && nranks > 1 ? static_cast<size_t>(chunks) * chunk_rows * lda * in_es : extent(m, k, lda) * in_es;
+        const size_t ba = mg && nranks > 1 ? static_cast<size_t>(padded_rows) * lda * in_es : extent(m, k, lda) * in_es;
         const size_t bb = extent(b_outer, b_inner, ldb) * in_es;
         const size_t bc = extent(m, n, ldc) * out_es, bd = extent(m, n, ldd) * out_es;
         if(int e = ctx_reserve(ctx, 0, ba)) return e;
@@ -469,7 +485,7 @@ namespace
         PIPE_CUDA(cudaEventRecord(ev_start, ctx->s_in));
         for(uint32_t i = 0; i < chunks; ++i)
         {
-            const uint32_t r0 = i * chunk_rows, rows = (m - r0 < chunk_rows) ? m - r0 : chunk_rows;
+            const uint32_t r0 = bounds[i], rows = bounds[i + 1] - bounds[i];
             const size_t   oa = static_cast<size_t>(r0) * lda * in_es, oc = static_cast<size_t>(r0) * ldc * out_es,
                          od = static_cast<size_t>(r0) * ldd * out_es;
             cudaEvent_t* ev = &ctx->events[PER * i]; // [0] A in, [1] exch begin, [2] exch end, [3] C in, [4] / [5] compute, [6] out
