@@ -64,7 +64,7 @@ namespace b200wmma
         static_assert(CHUNKS_A % CHUNKS_PER_PASS == 0 && CHUNKS_B % CHUNKS_PER_PASS == 0, "whole passes over A and B");
         static_assert(WORK_WARPS * EPI_BUF_BYTES <= A_STAGE_BYTES, "aliased staging tiles fit the A region of an int8 stage");
 
-        // 4 packed bytes (8 int4, low nibble = even k) -> 8 int8 in K order.
+        // 4 packed bytes (8 int4, low nibble = even k) -> 8 int8, even K positions first (see the end of the function).
         // A nibble v in a byte of its own sign-extends to v + 0xF0 when bit 3 is set: (v & 8) * 0x1E == 0xF0, and the
         // sum cannot carry into the next byte.
         template <bool SCALED>
@@ -82,8 +82,11 @@ namespace b200wmma
                 los = lo + (lo & 0x08080808u) * 0x1Eu;
                 his = hi + (hi & 0x08080808u) * 0x1Eu;
             }
-            out0 = __byte_perm(los, his, 0x5140); // lo0 hi0 lo1 hi1
-            out1 = __byte_perm(los, his, 0x7362); // lo2 hi2 lo3 hi3
+            // The even-k values and the odd-k values stay in words of their own: A and B are unpacked by this same
+            // function, so both see the same permutation of the eight K positions, and a sum over K does not care about
+            // their order (interleaving them back would cost two more instructions per word).
+            out0 = los; // k = 0, 2, 4, 6 of the eight
+            out1 = his; // k = 1, 3, 5, 7
         }
 
         // One 16-byte packed chunk (32 values) of row `row`, chunk j (0..3) of the slab -> 32 bytes = 16-byte cells
