@@ -66,6 +66,8 @@ int b200wmma_version(void);
  *   "dlrm_fwd_stages", "dlrm_fwd_warps"   the same two for the forward kernel
  *   "gemm_f64_kernel"    b200wmma_gemm_f64: 1 = the cp.async-fed kernel (the one ragged shapes always get), 2 = the TMA-fed
  *                        kernel, B200WMMA_ERR_UNSUPPORTED where it cannot run (a contiguous extent that is no multiple of 4)
+ *   "gemv_rows"          row-major GEMV: 4 = four rows of A per CTA with two loads per thread in flight (the default is
+ *                        one row per CTA with eight)
  *   "frag_perf_slab_k"   b200wmma_perf_hgemm_fragment: K depth of one shared-memory slab, 16 (the default), 32 or 64
  *                        (used when it divides k)
  * Unknown keys and out-of-range values return B200WMMA_ERR_INVALID_ARG.  The library reads no environment variable

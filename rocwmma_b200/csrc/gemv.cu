@@ -8,13 +8,13 @@
 // the read-only path, partial sums are reduced with warp shuffles and one shared-memory
 // step, and alpha / beta are applied in the same pass.
 #include "common.cuh"
+#include "tuning.cuh"
 
 namespace b200wmma
 {
     namespace gemv
     {
         constexpr int THREADS = 256;
-        constexpr int ROWS    = 4; // rows of A per CTA in the row-major kernel (x reuse in registers)
 
         template <typename T>
         struct Vec;
@@ -54,9 +54,9 @@ namespace b200wmma
             return v;
         }
 
-        // Row-major A: one CTA owns ROWS consecutive rows; its 256 threads stride over the
+        // Row-major A: one CTA owns ROWS consecutive rows (one, by default); its 256 threads stride over the
         // columns so that each warp-wide load instruction covers 512 contiguous bytes of a row.
-        template <typename T>
+        template <typename T, int ROWS, int UNROLL>
         __global__ void __launch_bounds__(THREADS)
             gemv_row_major_kernel(uint32_t m, uint32_t n, const T* __restrict__ a, size_t lda,
                                   const T* __restrict__ x, T* __restrict__ y, T alpha, T beta,
@@ -79,7 +79,7 @@ namespace b200wmma
             {
                 const uint32_t nvec = n / VN;
                 const V*       xv   = reinterpret_cast<const V*>(x);
-#pragma unroll 2
+#pragma unroll UNROLL
                 for(uint32_t v = threadIdx.x; v < nvec; v += THREADS)
                 {
                     const V xx = __ldg(xv + v);
@@ -202,8 +202,15 @@ namespace b200wmma
             if(layout_a == B200WMMA_ROW_MAJOR)
             {
                 const int vec_ok = pitch_ok && aligned16(x);
-                gemv_row_major_kernel<T><<<ceil_div(m, ROWS), THREADS, 0, stream>>>(
-                    m, n, a, lda, x, y, alpha, beta, vec_ok);
+                // One row per CTA, eight 16-byte loads per thread in flight: the CTAs are short (128 KiB of A), so the
+                // tail of the launch, when the last CTAs cannot fill the memory system, is short too.  Measured at
+                // 32768 x 32768 on one B200: 1 row 7101-7131 GB/s (fp32) / 7212-7260 (fp64); 2 rows 6815-6910 / 7020-7220;
+                // 4 rows with two loads in flight (the earlier choice, still selectable) 6590-6704 / 6804-6970;
+                // 8 rows 6800 / 5200.
+                if(tuning::get(tuning::GEMV_ROWS) == 4)
+                    gemv_row_major_kernel<T, 4, 2><<<ceil_div(m, 4u), THREADS, 0, stream>>>(m, n, a, lda, x, y, alpha, beta, vec_ok);
+                else
+                    gemv_row_major_kernel<T, 1, 8><<<m, THREADS, 0, stream>>>(m, n, a, lda, x, y, alpha, beta, vec_ok);
             }
             else
             {

@@ -48,6 +48,17 @@ def test_gemv_vs_oracle(dt, tol, m, n, lda_pad, col):
     assert run(m, n, dt, col, lda_pad) <= tol
 
 
+@pytest.mark.parametrize("dt,tol", [(np.float32, TOL_F32_OUT), (np.float64, TOL_F64_OUT)], ids=["f32", "f64"])
+@pytest.mark.parametrize("m,n,lda_pad", [(5, 1024, 0), (130, 515, 1), (1001, 4096, 4)])
+def test_gemv_four_rows_per_cta_kernel(dt, tol, m, n, lda_pad):
+    """The row-major kernel's other shape (four rows of A per thread block, ragged last block), selected by tuning key."""
+    api.set_tuning("gemv_rows", 4)
+    try:
+        assert run(m, n, dt, False, lda_pad) <= tol
+    finally:
+        api.set_tuning("gemv_rows", 0)
+
+
 def test_gemv_reference_fixtures():
     gold = np.load(os.path.join(GOLD, "gemv_ref.npz"))
     for case in GG.GEMV_CASES:
