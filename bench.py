@@ -54,8 +54,8 @@ NCU_TRAFFIC_BYTES = {
     "frag_perf_hgemm": 2.300e9,  # profiles/frag_perf_hgemm_8192.md: 2169 + 131 MB
     "dlrm_fwd": 119.1e6,      # profiles/dlrm_dot_B16384.md
     "dlrm_bwd": 192.4e6,      # profiles/dlrm_dot_B16384.md
-    "sgemv": 4.299e9,         # profiles/gemv_32768.md
-    "dgemv": 8.595e9,         # profiles/gemv_32768.md
+    "sgemv": 4.299e9,         # profiles/gemv_32768.md: 4.295 GB read + 3.6 MB written
+    "dgemv": 8.595e9,         # profiles/gemv_32768.md (the four-rows-per-CTA capture; the fp64 matrix is read once either way)
 }
 
 
