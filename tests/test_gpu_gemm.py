@@ -584,17 +584,19 @@ def test_gemm_i4_full_size_row_sample():
     assert torch.equal(col.to(torch.float64), expect)
 
 
-def test_gemm_f64_bench_size_row_sample():
-    """M=N=K=4096 fp64 (the size bench.py measures), alpha=beta=1: all columns of 64 seeded-random rows within
-    1e-12 of the oracle, and the whole output finite."""
-    m = n = k = 4096
+@pytest.mark.parametrize("size,nrows", [(4096, 64), (7168, 16)], ids=["4096", "7168"])
+def test_gemm_f64_bench_size_row_sample(size, nrows):
+    """fp64 at M=N=K=4096 (the size bench.py measures) and 7168 (the reference's perf_dgemm size,
+    samples/perf_dgemm.cpp:875), alpha=beta=1: all columns of seeded-random rows within 1e-12 of the oracle, and the
+    whole output finite."""
+    m = n = k = size
     f = lambda shape, seed: G.fill_torch(torch.empty(shape, dtype=torch.float64, device="cuda"), seed, "uniform")
     a, bs, c = f((m, k), G.SEED_A), f((n, k), G.SEED_B), f((m, n), G.SEED_C)
     d = nan_filled((m, n), torch.float64)
     api.gemm_f64(m, n, k, a, bs, c, d, k, k, n, n, 1.0, 1.0)
     assert_status_ok()
     assert bool(torch.isfinite(d).all())
-    rows = _rows_sample(m, 64, 95)
+    rows = _rows_sample(m, nrows, 95)
     idx = torch.from_numpy(rows).cuda()
     a_r, c_r, d_r = a[idx].cpu().numpy(), c[idx].cpu().numpy(), d[idx].cpu().numpy()
     b_h = bs.cpu().numpy()
