@@ -4,8 +4,8 @@
 // nibble = even k) have to become int8 before tcgen05.mma.kind::i8 reads them.  Here that happens inside the
 // kernel, between the TMA load and the MMA:
 //
-//   TMA (packed bytes, 64 B of K per row)  ->  raw ring, 4 stages of 24 KiB, unswizzled
-//   16 worker warps turn nibbles into bytes ->  int8 ring, 2 stages of 48 KiB in the K-major SWIZZLE_128B layout the
+//   TMA (packed bytes, 64 B of K per row)  ->  raw ring, 2 stages of 24 KiB, unswizzled
+//   16 worker warps turn nibbles into bytes ->  int8 ring, 3 stages of 48 KiB in the K-major SWIZZLE_128B layout the
 //                                               MMA descriptors of the dense int8 kernel expect
 //   fence.proxy.async + mbarrier            ->  tcgen05.mma.cta_group::2.kind::i8, accumulators in tensor memory
 //
@@ -17,7 +17,8 @@
 //
 // The conversion is on the critical path (an int8 stage has to be rewritten within one stage's worth of MMA time), so
 // its instruction count matters.  SCALED = true moves every nibble into the HIGH half of its byte, which yields the
-// int8 value 16 * v without any sign extension (5 instead of 9 instructions per 8 values); the accumulators are then
+// int8 value 16 * v without any sign extension (and the values are not interleaved back into K order, see unpack8: 3
+// instead of 9 instructions per 8 values); the accumulators are then
 // 256 times the true sums and the drain shifts them right by 8, which is exact.  That holds while 256 * |sum| fits
 // int32: k * 128 * 128 < 2^31, i.e. k < 131072; longer K runs the sign-extending form (SCALED = false).
 //
@@ -41,8 +42,12 @@ namespace b200wmma
         constexpr uint32_t PAIR_M          = 512;
         constexpr uint32_t TILE_N          = 256;
         constexpr uint32_t HALF_N          = 128;
-        constexpr uint32_t RAW_STAGES      = 4;
-        constexpr uint32_t CONV_STAGES     = 2;
+        // Two raw stages cover the TMA latency; three int8 stages let the unpacking run two slabs ahead of the MMAs
+        // instead of one (with 4 + 2 in the same shared memory the two were coupled slab by slab: 2935 against 2989 TOP/s
+        // sustained).
+        constexpr uint32_t RAW_STAGES      = 2;
+        constexpr uint32_t CONV_STAGES     = 3;
+        static_assert(RAW_STAGES <= 4 && CONV_STAGES <= 4, "barrier layout below holds four of each");
         constexpr uint32_t RAW_ROW_BYTES   = BLOCK_K_BYTES / 2; // 64 packed bytes = 128 int4 = one K slab
         constexpr uint32_t RAW_A_BYTES     = CTA_M * RAW_ROW_BYTES; // 16 KiB
         constexpr uint32_t RAW_B_BYTES     = HALF_N * RAW_ROW_BYTES; // 8 KiB
@@ -142,12 +147,12 @@ namespace b200wmma
             const uint32_t     raw_full   = bar_base; // RAW_STAGES x 8
             const uint32_t     raw_empty  = bar_base + 32;
             const uint32_t     conv_full  = bar_base + 64; // CONV_STAGES x 8 (leader's copy in use)
-            const uint32_t     conv_empty = bar_base + 80;
-            const uint32_t     tfull_bar  = bar_base + 96;
-            const uint32_t     tempty_bar = bar_base + 104; // 2 x 8 (leader's copy in use)
-            const uint32_t     drain_bar  = bar_base + 120;
-            const uint32_t     cbar_base  = bar_base + 128; // WORK_WARPS x 2 x 8
-            uint32_t*          tmem_slot  = reinterpret_cast<uint32_t*>(smem + misc_off + 128 + WORK_WARPS * 16);
+            const uint32_t     conv_empty = bar_base + 96;
+            const uint32_t     tfull_bar  = bar_base + 128;
+            const uint32_t     tempty_bar = bar_base + 136; // 2 x 8 (leader's copy in use)
+            const uint32_t     drain_bar  = bar_base + 152;
+            const uint32_t     cbar_base  = bar_base + 160; // WORK_WARPS x 2 x 8
+            uint32_t*          tmem_slot  = reinterpret_cast<uint32_t*>(smem + misc_off + 160 + WORK_WARPS * 16);
             volatile uint32_t* cta_abort  = tmem_slot + 1;
             const uint32_t     alias_off  = conv_a_off + (CONV_STAGES - 1) * A_STAGE_BYTES; // A region of the last int8 stage
 
