@@ -68,6 +68,7 @@ int b200wmma_version(void);
  *                        kernel, B200WMMA_ERR_UNSUPPORTED where it cannot run (a contiguous extent that is no multiple of 4)
  *   "gemv_rows"          row-major GEMV: 4 = four rows of A per CTA with two loads per thread in flight (the default is
  *                        one row per CTA with eight)
+ *   "gemv_col_vn"        column-major GEMV: 2 or 4 = that many consecutive rows per lane (default 1)
  *   "frag_perf_slab_k"   b200wmma_perf_hgemm_fragment: K depth of one shared-memory slab, 16 (the default), 32 or 64
  *                        (used when it divides k)
  * Unknown keys and out-of-range values return B200WMMA_ERR_INVALID_ARG.  The library reads no environment variable

@@ -143,7 +143,8 @@ extern "C" int b200wmma_set_tuning(const char* key, int value)
                  {"dlrm_fwd_warps", tuning::DLRM_FWD_WARPS, 0, 12},
                  {"gemm_f64_kernel", tuning::GEMM_F64_KERNEL, 0, 2},
                  {"frag_perf_slab_k", tuning::FRAG_PERF_SLAB_K, 0, 64},
-                 {"gemv_rows", tuning::GEMV_ROWS, 0, 4}};
+                 {"gemv_rows", tuning::GEMV_ROWS, 0, 4},
+                 {"gemv_col_vn", tuning::GEMV_COL_VN, 0, 4}};
     for(const auto& t : table)
         if(std::strcmp(key, t.name) == 0)
         {

@@ -124,17 +124,30 @@ namespace b200wmma
             }
         }
 
-        // Column-major A (the reference sample's own storage, lda >= m): consecutive rows are
-        // contiguous, so each lane owns VN consecutive rows and the 8 warps of a CTA take
-        // interleaved columns; the per-warp partial sums are combined in shared memory.
-        template <typename T>
+        // Column-major A (the reference sample's own storage, lda >= m): consecutive rows are contiguous, so each lane
+        // owns VN consecutive rows (one 4- to 16-byte load per column) and the 8 warps of a CTA take interleaved columns;
+        // the per-warp partial sums are combined in shared memory.  A CTA owns 32 * VN rows over ALL columns (no
+        // reduction across CTAs), so VN also sets how many CTAs there are and how long each runs: the launch picks the
+        // widest vector that still leaves several CTAs per SM.
+        template <typename T, int VN>
+        struct LaneVec;
+        template <>
+        struct LaneVec<float, 1> { using type = float; };
+        template <>
+        struct LaneVec<float, 2> { using type = float2; };
+        template <>
+        struct LaneVec<float, 4> { using type = float4; };
+        template <>
+        struct LaneVec<double, 1> { using type = double; };
+        template <>
+        struct LaneVec<double, 2> { using type = double2; };
+
+        template <typename T, int VN, int UNROLL>
         __global__ void __launch_bounds__(THREADS)
             gemv_col_major_kernel(uint32_t m, uint32_t n, const T* __restrict__ a, size_t lda,
-                                  const T* __restrict__ x, T* __restrict__ y, T alpha, T beta,
-                                  int vec_ok)
+                                  const T* __restrict__ x, T* __restrict__ y, T alpha, T beta)
         {
-            using V                 = typename Vec<T>::type;
-            constexpr int VN        = Vec<T>::N;
+            using V                 = typename LaneVec<T, VN>::type;
             constexpr int WARPS     = THREADS / 32;
             constexpr int CTA_ROWS  = 32 * VN;
             const int     warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -143,9 +156,9 @@ namespace b200wmma
 #pragma unroll
             for(int i = 0; i < VN; ++i)
                 acc[i] = T(0);
-            if(vec_ok && row + VN <= m)
+            if(row + VN <= m)
             {
-#pragma unroll 4
+#pragma unroll UNROLL
                 for(uint32_t h = warp; h < n; h += WARPS)
                 {
                     const T  xx = __ldg(x + h);
@@ -186,6 +199,18 @@ namespace b200wmma
             }
         }
 
+        // Rows per lane: one, unless b200wmma_set_tuning("gemv_col_vn", 2 | 4) asks for a wider vector and its loads are
+        // aligned (the wider forms measured slower, see the launch code; they are kept for that comparison).
+        template <typename T>
+        static int col_major_vn(uint32_t, const T* a, uint32_t lda, uint32_t)
+        {
+            const int forced = tuning::get(tuning::GEMV_COL_VN);
+            for(int vn = Vec<T>::N; vn > 1; vn >>= 1)
+                if(forced == vn && (reinterpret_cast<uintptr_t>(a) % (vn * sizeof(T))) == 0 && lda % vn == 0)
+                    return vn;
+            return 1;
+        }
+
         template <typename T>
         static int launch(uint32_t m, uint32_t n, const T* a, uint32_t lda, int layout_a, const T* x,
                           T* y, T alpha, T beta, cudaStream_t stream)
@@ -214,9 +239,29 @@ namespace b200wmma
             }
             else
             {
-                const int vec_ok = pitch_ok;
-                gemv_col_major_kernel<T><<<ceil_div(m, 32 * Vec<T>::N), THREADS, 0, stream>>>(
-                    m, n, a, lda, x, y, alpha, beta, vec_ok);
+                int dev = 0, sms = 148;
+                cudaGetDevice(&dev);
+                cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+                // Measured at 32768 x 32768 on one B200 (GB/s, fp32 / fp64): one row per lane with 16 loads in flight
+                // 6467 / 7122; with 8 in flight 6083 / 6888, with 32 (fp32) 6067; two rows per lane 5935 / 4056; four rows
+                // per lane - 256 CTAs of 16 MiB on 148 SMs, the earlier shape - 3566 (fp32; fp64, two rows: 4307).
+                const int vn = col_major_vn<T>(m, a, lda, 4u * static_cast<uint32_t>(sms));
+                if constexpr(sizeof(T) == 4)
+                {
+                    if(vn == 4)
+                        gemv_col_major_kernel<T, 4, 4><<<ceil_div(m, 128u), THREADS, 0, stream>>>(m, n, a, lda, x, y, alpha, beta);
+                    else if(vn == 2)
+                        gemv_col_major_kernel<T, 2, 8><<<ceil_div(m, 64u), THREADS, 0, stream>>>(m, n, a, lda, x, y, alpha, beta);
+                    else
+                        gemv_col_major_kernel<T, 1, 16><<<ceil_div(m, 32u), THREADS, 0, stream>>>(m, n, a, lda, x, y, alpha, beta);
+                }
+                else
+                {
+                    if(vn == 2)
+                        gemv_col_major_kernel<T, 2, 4><<<ceil_div(m, 64u), THREADS, 0, stream>>>(m, n, a, lda, x, y, alpha, beta);
+                    else
+                        gemv_col_major_kernel<T, 1, 16><<<ceil_div(m, 32u), THREADS, 0, stream>>>(m, n, a, lda, x, y, alpha, beta);
+                }
             }
             B200_CHECK_CUDA(cudaGetLastError());
             return B200WMMA_OK;

@@ -22,6 +22,7 @@ namespace b200wmma
             GEMM_F64_KERNEL   = 10, // fp64 GEMM: 1 = the cp.async kernel, 2 = the TMA-fed kernel or an error where it cannot run
             FRAG_PERF_SLAB_K  = 11, // b200wmma_perf_hgemm_fragment: K depth of a shared-memory slab, 16 / 32 / 64
             GEMV_ROWS         = 12, // row-major GEMV: 4 = four rows of A per CTA with two loads in flight (default: one row, eight loads)
+            GEMV_COL_VN       = 13, // column-major GEMV: rows per lane, 2 or 4 (default: 1)
             NUM_KEYS
         };
         int  get(Key k);

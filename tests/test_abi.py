@@ -101,7 +101,7 @@ def test_set_tuning_round_trip():
     L = _lib.lib()
     keys = {b"gemm_tile_variant": 1, b"gemm_group_m": 4, b"sp24_force_expand": 1, b"gemm_mma_order": 2, b"gemm_split_tail": 2,
             b"gemm_split_fixup": 16, b"dlrm_bwd_stages": 3, b"dlrm_bwd_warps": 8, b"dlrm_fwd_stages": 3, b"dlrm_fwd_warps": 8,
-            b"gemm_f64_kernel": 1, b"frag_perf_slab_k": 32, b"gemv_rows": 4}
+            b"gemm_f64_kernel": 1, b"frag_perf_slab_k": 32, b"gemv_rows": 4, b"gemv_col_vn": 2}
     header = open(os.path.join(ROOT, "include", "rocwmma_b200.h")).read()
     for key, value in keys.items():
         assert f'"{key.decode()}"' in header, f"{key} is not documented in the header"

@@ -59,6 +59,19 @@ def test_gemv_four_rows_per_cta_kernel(dt, tol, m, n, lda_pad):
         api.set_tuning("gemv_rows", 0)
 
 
+@pytest.mark.parametrize("dt,tol,vn", [(np.float32, TOL_F32_OUT, 2), (np.float32, TOL_F32_OUT, 4), (np.float64, TOL_F64_OUT, 2)],
+                         ids=["f32x2", "f32x4", "f64x2"])
+@pytest.mark.parametrize("m,n,lda_pad", [(130, 515, 2), (1000, 4096, 0), (4099, 1000, 1)])
+def test_gemv_col_major_wider_lanes(dt, tol, vn, m, n, lda_pad):
+    """The column-major kernel with 2 or 4 consecutive rows per lane (selected by tuning key; where the pitch does not
+    allow the vector loads the library falls back to one row per lane), ragged last block included."""
+    api.set_tuning("gemv_col_vn", vn)
+    try:
+        assert run(m, n, dt, True, lda_pad) <= tol
+    finally:
+        api.set_tuning("gemv_col_vn", 0)
+
+
 def test_gemv_reference_fixtures():
     gold = np.load(os.path.join(GOLD, "gemv_ref.npz"))
     for case in GG.GEMV_CASES:
