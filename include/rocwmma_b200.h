@@ -157,7 +157,8 @@ int b200wmma_gemm_bf16(uint32_t m, uint32_t n, uint32_t k,
  * bfloat16 inputs with bfloat16 C / D and fp32 compute (out_type B200WMMA_OUT_BF16; B200WMMA_OUT_F32 is
  * b200wmma_gemm_bf16), and int8 inputs with int8 C / D and int32 compute: d = int8(alpha * acc + beta * int32(c)), the
  * int32 value cast as the reference's static_cast<OutputT> does (test/reference_impl.hpp:77-78: the low 8 bits).
- * All layout combinations.  The int8-output form drains element-wise (one byte per store). */
+ * All layout combinations.  The int8-output form drains 32 or 16 bytes per access where the C / D rows are aligned
+ * accordingly, byte by byte otherwise. */
 int b200wmma_gemm_bf16_out(uint32_t m, uint32_t n, uint32_t k,
                            const void* a, const void* b, const void* c, void* d,
                            uint32_t lda, uint32_t ldb, uint32_t ldc, uint32_t ldd,

@@ -205,6 +205,40 @@ namespace b200wmma
             }
         }
 
+        // One-byte integer outputs: the thread's 32 columns are 32 contiguous bytes of its row; with 16-byte aligned rows
+        // they are read and written as two 16-byte accesses (one 32-byte access when vec == 2) instead of 32 single
+        // bytes.  Each byte is the low byte of alpha * acc + beta * int32(c), as the element-wise path computes it.
+        template <typename ScalarT, int VW>
+        __device__ __forceinline__ void epilogue_row_chunk_bytes(const uint32_t (&v)[32], const int8_t* __restrict__ c_row,
+                                                                 int8_t* __restrict__ d_row, ScalarT alpha, ScalarT beta,
+                                                                 bool read_c)
+        {
+#pragma unroll
+            for(int g = 0; g < 8 / VW; ++g)
+            {
+                uint32_t cw[VW], ow[VW];
+#pragma unroll
+                for(int j = 0; j < VW; ++j)
+                    cw[j] = 0u;
+                if(read_c)
+                    ldg_words<VW>(reinterpret_cast<const uint32_t*>(c_row) + g * VW, cw);
+#pragma unroll
+                for(int j = 0; j < VW; ++j)
+                {
+                    uint32_t o = 0u;
+#pragma unroll
+                    for(int b = 0; b < 4; ++b)
+                    {
+                        const int32_t cv = static_cast<int8_t>((cw[j] >> (8 * b)) & 0xFFu);
+                        const int32_t r  = epi(static_cast<int32_t>(v[4 * (g * VW + j) + b]), cv, alpha, beta);
+                        o |= (static_cast<uint32_t>(r) & 0xFFu) << (8 * b);
+                    }
+                    ow[j] = o;
+                }
+                stg_words<VW>(reinterpret_cast<uint32_t*>(d_row) + g * VW, ow);
+            }
+        }
+
         // One thread's 32 consecutive output columns of one row.
         // OutT = __half: acc is fp32 bits.  OutT = float: fp32.  OutT = int32_t: int32.
         // vec: 0 = element-wise, 1 = 16-byte accesses, 2 = 32-byte accesses (rows aligned accordingly).
@@ -218,7 +252,13 @@ namespace b200wmma
                                                            bool     read_c,
                                                            int      vec)
         {
-            // (one-byte outputs always take the element-wise path)
+            if constexpr(std::is_same<OutT, int8_t>::value)
+            {
+                if(ncols == 32 && vec == 2)
+                    return epilogue_row_chunk_bytes<ScalarT, 8>(v, c_row, d_row, alpha, beta, read_c);
+                if(ncols == 32 && vec == 1)
+                    return epilogue_row_chunk_bytes<ScalarT, 4>(v, c_row, d_row, alpha, beta, read_c);
+            }
             if(sizeof(OutT) >= 2 && ncols == 32 && vec == 2)
                 epilogue_row_chunk_vec<OutT, ScalarT, 8>(v, c_row, d_row, alpha, beta, read_c);
             else if(sizeof(OutT) >= 2 && ncols == 32 && vec == 1)

@@ -774,8 +774,17 @@ namespace b200wmma
                                                slot_row - SLOT_WORDS, npart);
                     }
                     else if(vec_ok == 0 && first == 0u)
+                    {
+                        // one-byte outputs have no staged path: with aligned rows they still move 16 or 32 bytes at a time
+                        int vec = 0;
+                        if constexpr(sizeof(OutT) == 1)
+                        {
+                            const uintptr_t bits = reinterpret_cast<uintptr_t>(d) | ldd | (read_c ? (reinterpret_cast<uintptr_t>(c) | ldc) : 0u);
+                            vec = (bits % 32u) == 0u ? 2 : ((bits % 16u) == 0u ? 1 : 0);
+                        }
                         drain_accumulator<OutT, ScalarT, TILE_N>(tmem_acc, quad, lane, row_base, col_base, m, n, c, d, ldc,
-                                                                 ldd, alpha, beta, read_c, 0);
+                                                                 ldd, alpha, beta, read_c, vec);
+                    }
                     // (an aligned tile that lies wholly outside the matrix has nothing to store)
                     if(dead)
                         continue;

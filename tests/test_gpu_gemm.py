@@ -212,7 +212,8 @@ def test_gemm_f32_all_layouts(la, lb, lcd, m, n, k):
 @pytest.mark.parametrize("m,n,k,alpha,beta", [(512, 256, 256, 1, 0), (608, 336, 208, 3, -2), (144, 80, 96, 1, 1)])
 def test_gemm_i8_int8_outputs(la, lb, lcd, m, n, k, alpha, beta):
     """The reference's <int8_t, int8_t, int32_t> set (test/gemm/gemm_common_test_params.hpp:53): int32 compute, the
-    result cast to int8 as gemm_CPU's static_cast does.  Bit-exact against the oracle in the same layouts."""
+    result cast to int8 as gemm_CPU's static_cast does.  Bit-exact against the oracle in the same layouts.  The C / D
+    pitches of these shapes are multiples of 32 and of 16 only: the drain's 32-byte and 16-byte forms."""
     lda, ldb, ldcd = _lds(m, n, k, la, lb, lcd)
     store = lambda x, col: np.ascontiguousarray(x.T if col else x)
     a = G.int8_np(G.SEED_A, (m, k)); b = G.int8_np(G.SEED_B, (k, n)); c = G.int8_np(G.SEED_C, (m, n))
@@ -221,6 +222,21 @@ def test_gemm_i8_int8_outputs(la, lb, lcd, m, n, k, alpha, beta):
     api.gemm_i8_i8(m, n, k, dev(sa), dev(sb), dev(sc) if beta else None, d, lda, ldb, ldcd, ldcd, alpha, beta, la, lb, lcd)
     assert_status_ok()
     ref = R.gemm(R.port(), m, n, k, sa.ravel(), sb.ravel(), sc.ravel() if beta else None, alpha, beta, np.int8, la, lb, lcd, lcd)
+    assert np.array_equal(d.cpu().numpy().ravel(), ref)
+
+
+@pytest.mark.parametrize("lcd", [0, 1], ids=["RCR", "RCC"])
+def test_gemm_i8_int8_outputs_unaligned_rows(lcd):
+    """int8 C / D whose rows are not 16-byte aligned (pitch 75 resp. 200): the drain goes byte by byte."""
+    m, n, k, alpha, beta = 200, 75, 128, 2, 1
+    store = lambda x, col: np.ascontiguousarray(x.T if col else x)
+    a = G.int8_np(G.SEED_A, (m, k)); b = G.int8_np(G.SEED_B, (k, n)); c = G.int8_np(G.SEED_C, (m, n))
+    sa, sb, sc = a, store(b, 1), store(c, lcd)
+    ldcd = m if lcd else n
+    d = nan_filled(sc.shape, torch.int8)
+    api.gemm_i8_i8(m, n, k, dev(sa), dev(sb), dev(sc), d, k, k, ldcd, ldcd, alpha, beta, 0, 1, lcd)
+    assert_status_ok()
+    ref = R.gemm(R.port(), m, n, k, sa.ravel(), sb.ravel(), sc.ravel(), alpha, beta, np.int8, 0, 1, lcd, lcd)
     assert np.array_equal(d.cpu().numpy().ravel(), ref)
 
 
