@@ -1105,7 +1105,8 @@ class Harness:
         side.wait_stream(torch.cuda.current_stream())
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.stream(side):
-            with torch.cuda.graph(graph, stream=side):
+            # thread_local: a CUDA call from another thread of the process (NCCL's watchdog) must not end the capture
+            with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
                 for _ in range(steps):
                     fn()
         torch.cuda.current_stream().wait_stream(side)
