@@ -669,7 +669,8 @@ class Dlrm(Workload):
                 "sharding": "single GPU" if world == 1 else f"batch split over {world} ranks",
                 "l2": "independent input batches (4 or more, at least 300 MB together) rotated so that no step re-reads a "
                       "cached input",
-                "launch": "the K timed launches are captured once in a CUDA graph and replayed between the events (a "
+                "launch": getattr(self, "launch_mode", None) or
+                          "the K timed launches are captured once in a CUDA graph and replayed between the events (a "
                           "launch lasts 10-50 us, a launch from Python about 12 us)"}
 
     def value(self, work, seconds):
@@ -1096,22 +1097,29 @@ class Harness:
         self.barrier()
         return self.reduce_max(e0.elapsed_time(e1)), wall
 
-    def timed_graph(self, fn, steps, sampler=None):
+    def timed_graph(self, fn, steps, sampler=None, wl=None):
         """As `timed`, for launches shorter than the host can issue them: the K calls are captured once into a CUDA graph
         on a side stream (nothing runs during capture), the graph is replayed once untimed, then once between the
-        events.  Same K kernels, same buffers, same order as K direct calls."""
+        events.  Same K kernels, same buffers, same order as K direct calls.  A rank whose capture fails times direct
+        launches instead and says so in `config.launch`."""
         torch = self.torch
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.stream(side):
-            # thread_local: a CUDA call from another thread of the process (NCCL's watchdog) must not end the capture
-            with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
-                for _ in range(steps):
-                    fn()
-        torch.cuda.current_stream().wait_stream(side)
-        graph.replay()
-        torch.cuda.synchronize()
+        try:
+            with torch.cuda.stream(side):
+                # thread_local: a CUDA call from another thread of the process (NCCL's watchdog) must not end the capture
+                with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
+                    for _ in range(steps):
+                        fn()
+            torch.cuda.current_stream().wait_stream(side)
+            graph.replay()
+            torch.cuda.synchronize()
+        except RuntimeError as exc:
+            if wl is not None:
+                wl.launch_mode = f"direct launches (graph capture failed: {str(exc)[:80]})"
+            torch.cuda.synchronize()
+            return self.timed(fn, steps, sampler)
         out = self.timed(graph.replay, 1, sampler)
         del graph
         return out
@@ -1138,7 +1146,10 @@ class Harness:
         for _ in range(max(warmup, 3)):
             wl.step()
         sampler = ClockSampler(self.local_rank)
-        timed = self.timed_graph if getattr(wl, "graph_replay", False) else self.timed
+        timed = self.timed
+        if getattr(wl, "graph_replay", False):
+            def timed(fn, k, smp=None):
+                return self.timed_graph(fn, k, smp, wl)
         ms_total, _ = timed(wl.step, steps, sampler)
         if len(sampler.samples) < 5:
             # the timed region was too short for the sampling period: extend the same loop (untimed) under the sampler
