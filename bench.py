@@ -11,7 +11,7 @@ N > 1: one process per GPU.  The problem is sharded by N-column blocks (B, C, D 
 over NCCL before the timed region and reported separately as `a_broadcast_ms`); there is no collective in
 the data path, total work is fixed (strong scaling), value = 2*M*N*K / max-over-ranks time.
 
-The line also carries `"also"`: every other component of the metric (int8 / 2:4-sparse / int4 / bf16 / fp8 / fp64 GEMM,
+The line also carries `"also"`: every other component of the metric (int8 / 2:4-sparse / int4 / bf16 / fp8 / fp32 / fp64 GEMM,
 DLRM forward and backward, sgemv / dgemv, the fragment-API GEMMs) measured in the same process the same way, each with
 its own ms_per_step, roofline, clocks, parity_check and (where a host driver exists) e2e; at N > 1 each is sharded its own
 way (GEMM by N-column blocks, DLRM by batch, GEMV by rows).  `--no-also` skips them, `--workload NAME` makes one of
@@ -1246,7 +1246,7 @@ class Harness:
 
 
 # the other components of the metric, measured after the headline workload in the same process
-ALSO = ["gemm_i8", "gemm_i8_sp24", "gemm_i4", "gemm_bf16", "gemm_fp8", "gemm_f64", "dlrm_fwd", "dlrm_bwd", "sgemv", "dgemv",
+ALSO = ["gemm_i8", "gemm_i8_sp24", "gemm_i4", "gemm_bf16", "gemm_fp8", "gemm_f32", "gemm_f64", "dlrm_fwd", "dlrm_bwd", "sgemv", "dgemv",
         "frag_simple_hgemm", "frag_perf_hgemm"]
 
 
